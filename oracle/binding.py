@@ -1,0 +1,241 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes bindings of the CPU checkers.
+
+`Oracle` wraps libyvx_oracle.so (the C restatement, always buildable).
+`Reference` wraps _ref/libyvex_ref.so (the reference's own CPU code; exists
+only where it was built from the reference tree) and exposes the same methods
+for the functions both provide, so tests can run either against the other.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "libyvx_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libyvex_ref.so")
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_u64 = C.c_ulonglong
+
+
+def build_oracle(reference_tree="/root/reference"):
+    """Compile the restatement, and the reference build when its tree exists."""
+    subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
+    if os.path.isdir(os.path.join(reference_tree, "src", "backend")):
+        subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={reference_tree}"], check=True)
+
+
+class _Gqa:
+    """Shared wrappers; subclasses set self.lib and self.prefix."""
+
+    def _bind_common(self):
+        p = self.prefix
+        lib = self.lib
+        getattr(lib, p + "bf16_decode").restype = C.c_float
+        getattr(lib, p + "bf16_decode").argtypes = [C.c_ushort]
+        getattr(lib, p + "bf16_encode").restype = C.c_ushort
+        getattr(lib, p + "bf16_encode").argtypes = [C.c_float]
+        getattr(lib, p + "f16_decode").restype = C.c_float
+        getattr(lib, p + "f16_decode").argtypes = [C.c_ushort]
+        getattr(lib, p + "f16_encode").restype = C.c_ushort
+        getattr(lib, p + "f16_encode").argtypes = [C.c_float]
+        getattr(lib, p + "q8_0_encode_block").argtypes = [_f32p, _u8p]
+        getattr(lib, p + "q8_0_decode_block").argtypes = [_u8p, _f32p]
+        getattr(lib, p + "op_attention").argtypes = [
+            _f32p, _f32p, _f32p, _u64, _u64, C.c_float, C.c_int, _u64, _f32p, _f32p, _f32p]
+        getattr(lib, p + "gqa_attention").argtypes = [
+            _f32p, _f32p, _f32p, _f32p, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _u64,
+            C.c_float, C.c_int, C.c_uint]
+
+    def bf16_encode(self, x):
+        return int(getattr(self.lib, self.prefix + "bf16_encode")(float(np.float32(x))))
+
+    def bf16_decode(self, bits):
+        return float(getattr(self.lib, self.prefix + "bf16_decode")(int(bits)))
+
+    def f16_encode(self, x):
+        return int(getattr(self.lib, self.prefix + "f16_encode")(float(np.float32(x))))
+
+    def f16_decode(self, bits):
+        return float(getattr(self.lib, self.prefix + "f16_decode")(int(bits)))
+
+    def q8_0_encode_block(self, values):
+        values = np.ascontiguousarray(values, np.float32)
+        assert values.shape == (32,)
+        out = np.zeros(34, np.uint8)
+        ok = getattr(self.lib, self.prefix + "q8_0_encode_block")(values, out)
+        return out if ok else None
+
+    def q8_0_decode_block(self, encoded):
+        encoded = np.ascontiguousarray(encoded, np.uint8)
+        out = np.zeros(32, np.float32)
+        ok = getattr(self.lib, self.prefix + "q8_0_decode_block")(encoded, out)
+        return out if ok else None
+
+    def op_attention(self, q, k, v, position, scale, causal):
+        q = np.ascontiguousarray(q, np.float32)
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        seq, hd = k.shape
+        scores = np.zeros(seq, np.float32)
+        probs = np.zeros(seq, np.float32)
+        out = np.zeros(hd, np.float32)
+        rc = getattr(self.lib, self.prefix + "op_attention")(
+            q, k, v, seq, position, scale, int(causal), hd, scores, probs, out)
+        return rc, out, scores, probs
+
+    def gqa_attention(self, q, k, v, query_start, query_heads, kv_heads, head_dim,
+                      causal=True, scale=None, threads=1,
+                      q_stride=0, k_stride=0, v_stride=0,
+                      query_tokens=None, kv_tokens=None):
+        """q [Tq, Hq*hd] (or strided flat), k/v [Tkv, Hkv*hd]; returns [Tq, Hq*hd]."""
+        q = np.ascontiguousarray(q, np.float32)
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        tq = query_tokens if query_tokens is not None else q.shape[0]
+        tkv = kv_tokens if kv_tokens is not None else k.shape[0]
+        if scale is None:
+            scale = 1.0 / np.sqrt(np.float32(head_dim))
+        out = np.zeros((tq, query_heads * head_dim), np.float32)
+        rc = getattr(self.lib, self.prefix + "gqa_attention")(
+            q.reshape(-1), k.reshape(-1), v.reshape(-1), out.reshape(-1), tq, tkv,
+            query_start, query_heads, kv_heads, head_dim, q_stride, k_stride, v_stride,
+            float(scale), int(causal), threads)
+        if rc != 0:
+            raise RuntimeError(f"{self.prefix}gqa_attention failed: {rc}")
+        return out
+
+
+class Oracle(_Gqa):
+    prefix = "yvx_oracle_"
+
+    def __init__(self):
+        if not os.path.exists(ORACLE_SO):
+            build_oracle()
+        self.lib = C.CDLL(ORACLE_SO)
+        self._bind_common()
+        lib = self.lib
+        lib.yvx_oracle_exp.restype = C.c_double
+        lib.yvx_oracle_exp.argtypes = [C.c_double]
+        lib.yvx_oracle_bf16_decode_array.argtypes = [_u16p, _f32p, C.c_size_t]
+        lib.yvx_oracle_bf16_encode_array.argtypes = [_f32p, _u16p, C.c_size_t]
+        lib.yvx_oracle_q8_0_decode_rows.argtypes = [_u8p, _f32p, C.c_size_t]
+        lib.yvx_oracle_gqa_f32_reference.restype = None
+        lib.yvx_oracle_gqa_f32_reference.argtypes = [
+            _f32p, _f32p, _f32p, _f32p, _u64, _u64, _u64, _u64, _u64, _u64, C.c_int]
+        lib.yvx_oracle_block_row.restype = _u64
+        lib.yvx_oracle_block_row.argtypes = [_i32p, _u64, _u64]
+        lib.yvx_oracle_block_gather_u16.restype = None
+        lib.yvx_oracle_block_gather_u16.argtypes = [_u16p, _i32p, _u64, _u64, _u64, _u16p]
+        lib.yvx_oracle_page_touch.argtypes = [_u64, _u64, _u64, C.POINTER(_u64), C.POINTER(_u64)]
+        lib.yvx_oracle_latent_reduce.argtypes = [
+            _f32p, _f32p, _f32p, _f32p, _u64, _u64, _u64, _u64, _u64, _u64, C.c_int]
+        lib.yvx_oracle_mla_decode.argtypes = [
+            _u16p, _u16p, _u16p, _u16p, _u16p, _f32p, _u64, _u64, _u64, _u64, _u64,
+            C.c_float, C.c_void_p]
+
+    def exp(self, x):
+        return float(self.lib.yvx_oracle_exp(float(x)))
+
+    def bf16_round(self, x):
+        """float32 array -> (uint16 bits, float32 values after bf16 rounding)."""
+        x = np.ascontiguousarray(x, np.float32)
+        bits = np.zeros(x.shape, np.uint16)
+        self.lib.yvx_oracle_bf16_encode_array(x.reshape(-1), bits.reshape(-1), x.size)
+        return bits, self.bf16_widen(bits)
+
+    def bf16_widen(self, bits):
+        bits = np.ascontiguousarray(bits, np.uint16)
+        out = np.zeros(bits.shape, np.float32)
+        self.lib.yvx_oracle_bf16_decode_array(bits.reshape(-1), out.reshape(-1), bits.size)
+        return out
+
+    def q8_0_encode_rows(self, values):
+        """float32 [..., n] with n % 32 == 0 -> uint8 [..., n/32*34] GGUF Q8_0 rows."""
+        values = np.ascontiguousarray(values, np.float32)
+        blocks = values.reshape(-1, 32)
+        out = np.zeros((blocks.shape[0], 34), np.uint8)
+        for i in range(blocks.shape[0]):
+            enc = self.q8_0_encode_block(blocks[i])
+            assert enc is not None
+            out[i] = enc
+        return out.reshape(values.shape[:-1] + (values.shape[-1] // 32 * 34,))
+
+    def q8_0_decode_rows(self, encoded, elements):
+        encoded = np.ascontiguousarray(encoded, np.uint8).reshape(-1)
+        out = np.zeros(elements, np.float32)
+        ok = self.lib.yvx_oracle_q8_0_decode_rows(encoded, out, elements)
+        return out if ok else None
+
+    def gqa_f32_reference(self, q, k, v, query_start, query_heads, kv_heads, head_dim, causal):
+        q = np.ascontiguousarray(q, np.float32)
+        k = np.ascontiguousarray(k, np.float32)
+        v = np.ascontiguousarray(v, np.float32)
+        out = np.zeros((q.shape[0], query_heads * head_dim), np.float32)
+        self.lib.yvx_oracle_gqa_f32_reference(
+            q.reshape(-1), k.reshape(-1), v.reshape(-1), out.reshape(-1), q.shape[0],
+            k.shape[0], query_start, query_heads, kv_heads, head_dim, int(causal))
+        return out
+
+    def block_row(self, table, block_tokens, row):
+        table = np.ascontiguousarray(table, np.int32)
+        return int(self.lib.yvx_oracle_block_row(table, block_tokens, row))
+
+    def block_gather_u16(self, pool, table, block_tokens, rows):
+        pool = np.ascontiguousarray(pool, np.uint16)
+        table = np.ascontiguousarray(table, np.int32)
+        width = pool.shape[-1]
+        out = np.zeros((rows, width), np.uint16)
+        self.lib.yvx_oracle_block_gather_u16(pool.reshape(-1), table, block_tokens, rows,
+                                             width, out.reshape(-1))
+        return out
+
+    def page_touch(self, start, count, page_elements):
+        first, last = _u64(), _u64()
+        ok = self.lib.yvx_oracle_page_touch(start, count, page_elements,
+                                            C.byref(first), C.byref(last))
+        return (first.value, last.value) if ok else None
+
+    def latent_reduce(self, q, rows, sinks, query_start, heads, head_dim, round_bf16=True):
+        q = np.ascontiguousarray(q, np.float32)
+        rows = np.ascontiguousarray(rows, np.float32)
+        sinks = np.ascontiguousarray(sinks, np.float32)
+        out = np.zeros_like(q)
+        ok = self.lib.yvx_oracle_latent_reduce(
+            q.reshape(-1), rows.reshape(-1), sinks, out.reshape(-1), q.shape[0],
+            rows.shape[0], query_start, heads, head_dim, rows.shape[1], int(round_bf16))
+        return out if ok else None
+
+    def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale):
+        """bf16 bit arrays: q_nope [H,dn], q_rope [H,dr], w_uk [H,dn,dc],
+        latent [L,dc], rope_key [L,dr] -> float32 [H,dc]."""
+        heads, nope = q_nope.shape
+        context, dc = latent.shape
+        dr = q_rope.shape[1]
+        out = np.zeros((heads, dc), np.float32)
+        ok = self.lib.yvx_oracle_mla_decode(
+            np.ascontiguousarray(q_nope, np.uint16).reshape(-1),
+            np.ascontiguousarray(q_rope, np.uint16).reshape(-1),
+            np.ascontiguousarray(w_uk, np.uint16).reshape(-1),
+            np.ascontiguousarray(latent, np.uint16).reshape(-1),
+            np.ascontiguousarray(rope_key, np.uint16).reshape(-1),
+            out.reshape(-1), heads, nope, dc, dr, context, float(scale), None)
+        return out if ok else None
+
+
+class Reference(_Gqa):
+    prefix = "yvx_ref_"
+
+    def __init__(self):
+        if not os.path.exists(REF_SO):
+            raise FileNotFoundError(REF_SO)
+        self.lib = C.CDLL(REF_SO)
+        self._bind_common()
+
+
+def reference_available():
+    return os.path.exists(REF_SO)

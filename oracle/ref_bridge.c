@@ -1,0 +1,246 @@
+/* TEST INFRASTRUCTURE ONLY.
+ *
+ * Flat C entry points over the YVEX reference's own CPU code, compiled
+ * together with the reference's sources into oracle/_ref/libyvex_ref.so (see
+ * the Makefile beside this file). The bridge contains no arithmetic of its
+ * own: every number comes out of the reference's public functions
+ * (yvex_backend_op_attention on its CPU backend, the gguf scalar and Q8_0
+ * codecs). It validates the restatement in yvx_oracle.c and serves as the
+ * "reference" CPU baseline of the benchmark.
+ */
+#ifndef _GNU_SOURCE
+#define _GNU_SOURCE
+#endif
+#include <yvex/backend.h>
+#include <yvex/core.h>
+#include <yvex/internal/quant_numeric.h>
+#include <yvex/qtype.h>
+
+#include <pthread.h>
+#include <stdlib.h>
+#include <string.h>
+
+float yvx_ref_bf16_decode(unsigned short bits) { return yvex_quant_bf16_decode(bits); }
+unsigned short yvx_ref_bf16_encode(float value) { return yvex_quant_bf16_encode(value); }
+float yvx_ref_f16_decode(unsigned short bits) { return yvex_quant_f16_decode(bits); }
+unsigned short yvx_ref_f16_encode(float value) { return yvex_quant_f16_encode(value); }
+
+int yvx_ref_q8_0_encode_block(const float *source, unsigned char *encoded)
+{
+    yvex_error err;
+    size_t written = 0;
+    return yvex_quant_encode_block(YVEX_GGUF_QTYPE_Q8_0, source, 32ull, encoded, 34u,
+                                   &written, NULL, &err) == YVEX_OK &&
+           written == 34u;
+}
+
+int yvx_ref_q8_0_decode_block(const unsigned char *encoded, float *out)
+{
+    yvex_error err;
+    return yvex_quant_decode_block(YVEX_GGUF_QTYPE_Q8_0, encoded, 34u, out, 32ull,
+                                   NULL, &err) == YVEX_OK;
+}
+
+typedef struct {
+    yvex_backend *backend;
+    yvex_device_tensor *query, *keys, *values, *scores, *probabilities, *out;
+    unsigned long long seq, hd;
+} ref_head_tensors;
+
+static int ref_tensor(yvex_backend *backend, const char *name, unsigned int rank,
+                      unsigned long long d0, unsigned long long d1,
+                      yvex_device_tensor **out)
+{
+    yvex_backend_tensor_desc desc;
+    yvex_error err;
+    memset(&desc, 0, sizeof(desc));
+    desc.name = name;
+    desc.dtype = YVEX_DTYPE_F32;
+    desc.rank = rank;
+    desc.dims[0] = d0;
+    desc.dims[1] = d1;
+    desc.bytes = d0 * (rank > 1 ? d1 : 1ull) * sizeof(float);
+    return yvex_backend_tensor_alloc(backend, &desc, out, &err) == YVEX_OK;
+}
+
+static void ref_head_release(ref_head_tensors *t)
+{
+    if (!t->backend) return;
+    yvex_backend_tensor_free(t->backend, t->query);
+    yvex_backend_tensor_free(t->backend, t->keys);
+    yvex_backend_tensor_free(t->backend, t->values);
+    yvex_backend_tensor_free(t->backend, t->scores);
+    yvex_backend_tensor_free(t->backend, t->probabilities);
+    yvex_backend_tensor_free(t->backend, t->out);
+    yvex_backend_close(t->backend);
+    memset(t, 0, sizeof(*t));
+}
+
+static int ref_head_prepare(ref_head_tensors *t, unsigned long long seq,
+                            unsigned long long hd)
+{
+    yvex_error err;
+    memset(t, 0, sizeof(*t));
+    t->seq = seq;
+    t->hd = hd;
+    if (yvex_backend_open_cpu(&t->backend, &err) != YVEX_OK) return 0;
+    if (ref_tensor(t->backend, "q", 1, hd, 0, &t->query) &&
+        ref_tensor(t->backend, "k", 2, seq, hd, &t->keys) &&
+        ref_tensor(t->backend, "v", 2, seq, hd, &t->values) &&
+        ref_tensor(t->backend, "s", 1, seq, 0, &t->scores) &&
+        ref_tensor(t->backend, "p", 1, seq, 0, &t->probabilities) &&
+        ref_tensor(t->backend, "o", 1, hd, 0, &t->out))
+        return 1;
+    ref_head_release(t);
+    return 0;
+}
+
+/* One head, one query vector, through yvex_backend_op_attention on the
+ * reference's CPU backend. Returns the reference's status code. */
+int yvx_ref_op_attention(const float *query, const float *keys, const float *values,
+                         unsigned long long seq_len, unsigned long long position,
+                         float scale, int causal, unsigned long long head_dim,
+                         float *score_scratch, float *probability_scratch, float *out)
+{
+    ref_head_tensors t;
+    yvex_error err;
+    int rc;
+    if (!ref_head_prepare(&t, seq_len, head_dim)) return YVEX_ERR_NOMEM;
+    rc = yvex_backend_tensor_write(t.backend, t.query, query, head_dim * 4ull, &err);
+    if (rc == YVEX_OK)
+        rc = yvex_backend_tensor_write(t.backend, t.keys, keys, seq_len * head_dim * 4ull, &err);
+    if (rc == YVEX_OK)
+        rc = yvex_backend_tensor_write(t.backend, t.values, values, seq_len * head_dim * 4ull, &err);
+    if (rc == YVEX_OK)
+        rc = yvex_backend_op_attention(t.backend, t.query, t.keys, t.values, seq_len,
+                                       position, scale, causal, t.scores,
+                                       t.probabilities, t.out, &err);
+    if (rc == YVEX_OK) {
+        yvex_backend_tensor_read(t.backend, t.out, out, head_dim * 4ull, &err);
+        if (score_scratch)
+            yvex_backend_tensor_read(t.backend, t.scores, score_scratch, seq_len * 4ull, &err);
+        if (probability_scratch)
+            yvex_backend_tensor_read(t.backend, t.probabilities, probability_scratch,
+                                     seq_len * 4ull, &err);
+    }
+    ref_head_release(&t);
+    return rc;
+}
+
+typedef struct {
+    const float *query, *key, *value;
+    float *output;
+    unsigned long long query_tokens, key_value_tokens, query_start;
+    unsigned long long query_heads, key_value_heads, head_dimension;
+    unsigned long long query_stride, key_stride, value_stride;
+    float scale;
+    int causal;
+    unsigned int worker, workers;
+    int status;
+} ref_gqa_job;
+
+static void *ref_gqa_worker(void *argument)
+{
+    ref_gqa_job *job = (ref_gqa_job *)argument;
+    const unsigned long long hd = job->head_dimension, seq = job->key_value_tokens;
+    const unsigned long long group = job->query_heads / job->key_value_heads;
+    const unsigned long long items = job->key_value_heads * job->query_tokens * group;
+    float *packed = malloc((size_t)(seq * hd) * sizeof(float));
+    unsigned long long gathered_head = ~0ull, item, row;
+    ref_head_tensors t;
+    yvex_error err;
+    job->status = YVEX_OK;
+    if (!packed || !ref_head_prepare(&t, seq, hd)) {
+        free(packed);
+        job->status = YVEX_ERR_NOMEM;
+        return NULL;
+    }
+    for (item = job->worker; item < items; item += job->workers) {
+        unsigned long long kv_head = item / (job->query_tokens * group);
+        unsigned long long rest = item % (job->query_tokens * group);
+        unsigned long long token = rest / group;
+        unsigned long long query_head = kv_head * group + rest % group;
+        int rc;
+        if (kv_head != gathered_head) {
+            for (row = 0; row < seq; ++row)
+                memcpy(packed + row * hd, job->key + row * job->key_stride + kv_head * hd,
+                       (size_t)hd * sizeof(float));
+            yvex_backend_tensor_write(t.backend, t.keys, packed, seq * hd * 4ull, &err);
+            for (row = 0; row < seq; ++row)
+                memcpy(packed + row * hd, job->value + row * job->value_stride + kv_head * hd,
+                       (size_t)hd * sizeof(float));
+            yvex_backend_tensor_write(t.backend, t.values, packed, seq * hd * 4ull, &err);
+            gathered_head = kv_head;
+        }
+        yvex_backend_tensor_write(t.backend, t.query,
+                                  job->query + token * job->query_stride + query_head * hd,
+                                  hd * 4ull, &err);
+        rc = yvex_backend_op_attention(
+            t.backend, t.query, t.keys, t.values, seq,
+            job->causal ? job->query_start + token : 0ull, job->scale, job->causal,
+            t.scores, t.probabilities, t.out, &err);
+        if (rc != YVEX_OK) {
+            job->status = rc;
+            break;
+        }
+        yvex_backend_tensor_read(t.backend, t.out,
+                                 job->output + (token * job->query_heads + query_head) * hd,
+                                 hd * 4ull, &err);
+    }
+    ref_head_release(&t);
+    free(packed);
+    return NULL;
+}
+
+/* Grouped-query attention as a loop of the reference primitive; argument
+ * meaning matches yvx_oracle_gqa_attention. */
+int yvx_ref_gqa_attention(const float *query, const float *key, const float *value,
+                          float *output, unsigned long long query_tokens,
+                          unsigned long long key_value_tokens,
+                          unsigned long long query_start,
+                          unsigned long long query_heads,
+                          unsigned long long key_value_heads,
+                          unsigned long long head_dimension,
+                          unsigned long long query_stride,
+                          unsigned long long key_stride,
+                          unsigned long long value_stride, float scale, int causal,
+                          unsigned int threads)
+{
+    enum { MAX_THREADS = 256 };
+    pthread_t handles[MAX_THREADS];
+    ref_gqa_job jobs[MAX_THREADS];
+    int created[MAX_THREADS];
+    unsigned int t;
+    int status = YVEX_OK;
+    if (!threads) threads = 1;
+    if (threads > MAX_THREADS) threads = MAX_THREADS;
+    for (t = 0; t < threads; ++t) {
+        ref_gqa_job *job = &jobs[t];
+        job->query = query;
+        job->key = key;
+        job->value = value;
+        job->output = output;
+        job->query_tokens = query_tokens;
+        job->key_value_tokens = key_value_tokens;
+        job->query_start = query_start;
+        job->query_heads = query_heads;
+        job->key_value_heads = key_value_heads;
+        job->head_dimension = head_dimension;
+        job->query_stride = query_stride ? query_stride : query_heads * head_dimension;
+        job->key_stride = key_stride ? key_stride : key_value_heads * head_dimension;
+        job->value_stride = value_stride ? value_stride : key_value_heads * head_dimension;
+        job->scale = scale;
+        job->causal = causal;
+        job->worker = t;
+        job->workers = threads;
+        job->status = YVEX_OK;
+        created[t] = threads > 1 &&
+                     pthread_create(&handles[t], NULL, ref_gqa_worker, job) == 0;
+        if (!created[t]) ref_gqa_worker(job);
+    }
+    for (t = 0; t < threads; ++t)
+        if (created[t]) pthread_join(handles[t], NULL);
+    for (t = 0; t < threads; ++t)
+        if (jobs[t].status != YVEX_OK) status = jobs[t].status;
+    return status;
+}

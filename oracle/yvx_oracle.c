@@ -1,0 +1,676 @@
+/* TEST INFRASTRUCTURE ONLY: CPU restatement of the YVEX reference's attention
+ * arithmetic, used as the checker for the CUDA path. Never shipped, never a
+ * fallback. Parity status: pinned (see yvx_oracle.h).
+ *
+ * Citations name the reference file and lines each function follows.
+ */
+#ifndef _GNU_SOURCE
+#define _GNU_SOURCE
+#endif
+#include "yvx_oracle.h"
+
+#include <limits.h>
+#include <math.h>
+#include <pthread.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ---- scalar codecs ------------------------------------------------------ */
+
+/* src/gguf/quant_scalar.c:123-128: bf16 is the upper half of binary32. */
+float yvx_oracle_bf16_decode(unsigned short bits)
+{
+    uint32_t wide = (uint32_t)bits << 16;
+    float out;
+    memcpy(&out, &wide, sizeof(out));
+    return out;
+}
+
+/* src/gguf/quant_scalar.c:130-143: round to nearest even; NaNs are quieted by
+ * setting the top mantissa bit of the truncated pattern. */
+unsigned short yvx_oracle_bf16_encode(float value)
+{
+    uint32_t bits, high, low;
+    memcpy(&bits, &value, sizeof(bits));
+    high = bits >> 16;
+    low = bits & 0xffffu;
+    if ((bits & 0x7f800000u) == 0x7f800000u && (bits & 0x007fffffu))
+        return (unsigned short)(high | 0x0040u);
+    if (low > 0x8000u || (low == 0x8000u && (high & 1u))) high += 1u;
+    return (unsigned short)high;
+}
+
+/* src/gguf/quant_scalar.c:40-68: binary16 widening, subnormals normalised. */
+float yvx_oracle_f16_decode(unsigned short bits)
+{
+    uint32_t sign = ((uint32_t)bits & 0x8000u) << 16;
+    uint32_t exponent = ((uint32_t)bits >> 10) & 0x1fu;
+    uint32_t mantissa = (uint32_t)bits & 0x3ffu;
+    uint32_t wide;
+    float out;
+    if (exponent == 0u) {
+        if (!mantissa) {
+            wide = sign;
+        } else {
+            uint32_t shift = 0u;
+            while (!(mantissa & 0x400u)) {
+                mantissa <<= 1;
+                ++shift;
+            }
+            wide = sign | ((113u - shift) << 23) | ((mantissa & 0x3ffu) << 13);
+        }
+    } else if (exponent == 0x1fu) {
+        wide = sign | 0x7f800000u | (mantissa << 13);
+        if (mantissa) wide |= 0x00400000u;
+    } else {
+        wide = sign | ((exponent + 112u) << 23) | (mantissa << 13);
+    }
+    memcpy(&out, &wide, sizeof(out));
+    return out;
+}
+
+/* src/gguf/quant_scalar.c:75-121: binary32 -> binary16, nearest even,
+ * overflow to infinity, canonical quiet NaN payload. */
+unsigned short yvx_oracle_f16_encode(float value)
+{
+    uint32_t bits, sign, exponent, mantissa, packed, tail;
+    memcpy(&bits, &value, sizeof(bits));
+    sign = (bits >> 16) & 0x8000u;
+    exponent = (bits >> 23) & 0xffu;
+    mantissa = bits & 0x007fffffu;
+    if (exponent == 0xffu) {
+        if (!mantissa) return (unsigned short)(sign | 0x7c00u);
+        return (unsigned short)(sign | 0x7e00u | ((mantissa >> 13) & 0x1ffu));
+    }
+    if (exponent > 142u) return (unsigned short)(sign | 0x7c00u);
+    if (exponent < 113u) {
+        uint32_t significand, shift, quotient, rest, half;
+        if (exponent < 102u) return (unsigned short)sign;
+        significand = mantissa | 0x00800000u;
+        shift = 126u - exponent;
+        quotient = significand >> shift;
+        rest = significand & ((1u << shift) - 1u);
+        half = 1u << (shift - 1u);
+        if (rest > half || (rest == half && (quotient & 1u))) quotient += 1u;
+        return (unsigned short)(sign | quotient);
+    }
+    packed = ((exponent - 112u) << 10) | (mantissa >> 13);
+    tail = mantissa & 0x1fffu;
+    if (tail > 0x1000u || (tail == 0x1000u && (packed & 1u))) packed += 1u;
+    if ((packed & 0x7c00u) == 0x7c00u) packed &= 0x7c00u;
+    return (unsigned short)(sign | packed);
+}
+
+void yvx_oracle_bf16_decode_array(const unsigned short *bits, float *out, size_t count)
+{
+    size_t i;
+    for (i = 0; i < count; ++i) out[i] = yvx_oracle_bf16_decode(bits[i]);
+}
+
+void yvx_oracle_bf16_encode_array(const float *values, unsigned short *out, size_t count)
+{
+    size_t i;
+    for (i = 0; i < count; ++i) out[i] = yvx_oracle_bf16_encode(values[i]);
+}
+
+/* ---- Q8_0 --------------------------------------------------------------- */
+
+enum { Q8_0_ELEMENTS = 32, Q8_0_BYTES = 34 };
+
+static unsigned short load_u16le(const unsigned char *p)
+{
+    return (unsigned short)((unsigned int)p[0] | ((unsigned int)p[1] << 8));
+}
+
+/* src/gguf/quant_block.c:160-187: scale = amax/127 stored as f16 and re-read,
+ * lanes = roundf(x / scale) clamped to [-127, 127]. */
+int yvx_oracle_q8_0_encode_block(const float *source, unsigned char *encoded)
+{
+    float amax = 0.0f, scale, inverse;
+    unsigned short packed;
+    unsigned int i;
+    for (i = 0; i < Q8_0_ELEMENTS; ++i) {
+        float magnitude = fabsf(source[i]);
+        if (magnitude > amax) amax = magnitude;
+    }
+    packed = yvx_oracle_f16_encode(amax / 127.0f);
+    encoded[0] = (unsigned char)(packed & 0xffu);
+    encoded[1] = (unsigned char)(packed >> 8);
+    scale = yvx_oracle_f16_decode(packed);
+    if (!isfinite(scale) || scale < 0.0f || (amax > 0.0f && scale == 0.0f)) return 0;
+    inverse = scale != 0.0f ? 1.0f / scale : 0.0f;
+    for (i = 0; i < Q8_0_ELEMENTS; ++i) {
+        int lane = (int)roundf(source[i] * inverse);
+        if (lane < -127) lane = -127;
+        if (lane > 127) lane = 127;
+        encoded[2 + i] = (unsigned char)(lane < 0 ? 256 + lane : lane);
+    }
+    return 1;
+}
+
+/* src/gguf/quant_block.c:819-832: x = f16(scale) * (float)int8; a negative or
+ * non-finite scale is a format error. */
+int yvx_oracle_q8_0_decode_block(const unsigned char *encoded, float *out)
+{
+    float scale = yvx_oracle_f16_decode(load_u16le(encoded));
+    unsigned int i;
+    if (!isfinite(scale) || scale < 0.0f) return 0;
+    for (i = 0; i < Q8_0_ELEMENTS; ++i) {
+        int lane = encoded[2 + i] <= 127u ? (int)encoded[2 + i]
+                                          : (int)encoded[2 + i] - 256;
+        out[i] = scale * (float)lane;
+    }
+    return 1;
+}
+
+int yvx_oracle_q8_0_decode_rows(const unsigned char *encoded, float *out, size_t elements)
+{
+    size_t block, blocks = elements / Q8_0_ELEMENTS;
+    if (elements % Q8_0_ELEMENTS) return 0;
+    for (block = 0; block < blocks; ++block)
+        if (!yvx_oracle_q8_0_decode_block(encoded + block * Q8_0_BYTES,
+                                          out + block * Q8_0_ELEMENTS))
+            return 0;
+    return 1;
+}
+
+/* ---- the CPU attention primitive --------------------------------------- */
+
+/* src/backend/cpu.c:217-255: range reduction by ln2 into [-0.5, 0.5], an
+ * 18-term Taylor sum, then scaling by repeated doubling or halving. */
+double yvx_oracle_exp(double x)
+{
+    const double ln2 = 0.69314718055994530942;
+    double term = 1.0, sum = 1.0;
+    int halvings = 0;
+    unsigned int i;
+    if (x < -60.0) return 0.0;
+    if (x > 60.0) x = 60.0;
+    while (x > 0.5) {
+        x -= ln2;
+        ++halvings;
+    }
+    while (x < -0.5) {
+        x += ln2;
+        --halvings;
+    }
+    for (i = 1u; i <= 18u; ++i) {
+        term *= x / (double)i;
+        sum += term;
+    }
+    for (; halvings > 0; --halvings) sum *= 2.0;
+    for (; halvings < 0; ++halvings) sum *= 0.5;
+    return sum;
+}
+
+/* src/backend/cpu.c:307-399: scores in double rounded to float, running
+ * maximum in double, probabilities rounded to float before and after the
+ * division, value mix in double rounded to float. Returns 0 on success, -8
+ * (state error) when the exponent sum is not positive, -7 on a bad position. */
+int yvx_oracle_op_attention(const float *query, const float *keys,
+                            const float *values, unsigned long long seq_len,
+                            unsigned long long position, float scale, int causal,
+                            unsigned long long head_dim, float *score_scratch,
+                            float *probability_scratch, float *out)
+{
+    unsigned long long visible, i, d;
+    double maximum = 0.0, sum = 0.0;
+    if (!seq_len || !head_dim || !isfinite(scale) || scale <= 0.0f) return -10;
+    if (position >= seq_len) return -7;
+    visible = causal ? position + 1ull : seq_len;
+    for (i = 0; i < seq_len; ++i) {
+        double score = 0.0;
+        if (causal && i > position) {
+            score_scratch[i] = 0.0f;
+            probability_scratch[i] = 0.0f;
+            continue;
+        }
+        for (d = 0; d < head_dim; ++d)
+            score += (double)query[d] * (double)keys[i * head_dim + d];
+        score *= (double)scale;
+        score_scratch[i] = (float)score;
+        if (i == 0 || score > maximum) maximum = score;
+    }
+    for (i = 0; i < visible; ++i) {
+        double e = yvx_oracle_exp((double)score_scratch[i] - maximum);
+        probability_scratch[i] = (float)e;
+        sum += e;
+    }
+    if (sum <= 0.0) return -8;
+    for (i = 0; i < visible; ++i)
+        probability_scratch[i] = (float)((double)probability_scratch[i] / sum);
+    for (d = 0; d < head_dim; ++d) {
+        double mixed = 0.0;
+        for (i = 0; i < visible; ++i)
+            mixed += (double)probability_scratch[i] * (double)values[i * head_dim + d];
+        out[d] = (float)mixed;
+    }
+    return 0;
+}
+
+/* ---- grouped-query attention from the primitive ------------------------- */
+
+typedef struct {
+    const float *query, *key, *value;
+    float *output;
+    unsigned long long query_tokens, key_value_tokens, query_start;
+    unsigned long long query_heads, key_value_heads, head_dimension;
+    unsigned long long query_stride, key_stride, value_stride;
+    float scale;
+    int causal;
+    unsigned int worker, workers;
+    int status;
+} gqa_job;
+
+/* One worker owns whole KV heads: it gathers the head's K and V rows into
+ * packed [seq, head_dim] arrays (the shape the primitive admits) once, then
+ * runs the primitive for every query row and every query head of the group.
+ * Work is split by (kv head, query row) pairs so that one long session still
+ * spreads over all workers. */
+static void *gqa_worker(void *argument)
+{
+    gqa_job *job = (gqa_job *)argument;
+    const unsigned long long hd = job->head_dimension, seq = job->key_value_tokens;
+    const unsigned long long group = job->query_heads / job->key_value_heads;
+    const unsigned long long items = job->key_value_heads * job->query_tokens * group;
+    float *keys = malloc((size_t)(seq * hd) * sizeof(float));
+    float *values = malloc((size_t)(seq * hd) * sizeof(float));
+    float *scores = malloc((size_t)seq * sizeof(float));
+    float *probabilities = malloc((size_t)seq * sizeof(float));
+    unsigned long long gathered_head = ULLONG_MAX, item;
+    job->status = 0;
+    if (!keys || !values || !scores || !probabilities) {
+        job->status = -2;
+        goto done;
+    }
+    for (item = job->worker; item < items; item += job->workers) {
+        /* item order: kv head slowest so a worker rarely re-gathers. */
+        unsigned long long kv_head = item / (job->query_tokens * group);
+        unsigned long long rest = item % (job->query_tokens * group);
+        unsigned long long token = rest / group;
+        unsigned long long query_head = kv_head * group + rest % group;
+        unsigned long long row;
+        int rc;
+        if (kv_head != gathered_head) {
+            for (row = 0; row < seq; ++row) {
+                memcpy(keys + row * hd,
+                       job->key + row * job->key_stride + kv_head * hd,
+                       (size_t)hd * sizeof(float));
+                memcpy(values + row * hd,
+                       job->value + row * job->value_stride + kv_head * hd,
+                       (size_t)hd * sizeof(float));
+            }
+            gathered_head = kv_head;
+        }
+        rc = yvx_oracle_op_attention(
+            job->query + token * job->query_stride + query_head * hd, keys, values,
+            seq, job->causal ? job->query_start + token : 0ull, job->scale,
+            job->causal, hd, scores, probabilities,
+            job->output + (token * job->query_heads + query_head) * hd);
+        if (rc != 0) {
+            job->status = rc;
+            break;
+        }
+    }
+done:
+    free(keys);
+    free(values);
+    free(scores);
+    free(probabilities);
+    return NULL;
+}
+
+int yvx_oracle_gqa_attention(const float *query, const float *key,
+                             const float *value, float *output,
+                             unsigned long long query_tokens,
+                             unsigned long long key_value_tokens,
+                             unsigned long long query_start,
+                             unsigned long long query_heads,
+                             unsigned long long key_value_heads,
+                             unsigned long long head_dimension,
+                             unsigned long long query_stride,
+                             unsigned long long key_stride,
+                             unsigned long long value_stride, float scale,
+                             int causal, unsigned int threads)
+{
+    enum { MAX_THREADS = 256 };
+    pthread_t handles[MAX_THREADS];
+    gqa_job jobs[MAX_THREADS];
+    unsigned int t, started = 0;
+    int status = 0;
+    if (!query || !key || !value || !output || !query_tokens || !key_value_tokens ||
+        !query_heads || !key_value_heads || query_heads % key_value_heads ||
+        !head_dimension || query_start + query_tokens > key_value_tokens)
+        return -10;
+    if (!threads) threads = 1;
+    if (threads > MAX_THREADS) threads = MAX_THREADS;
+    for (t = 0; t < threads; ++t) {
+        gqa_job *job = &jobs[t];
+        job->query = query;
+        job->key = key;
+        job->value = value;
+        job->output = output;
+        job->query_tokens = query_tokens;
+        job->key_value_tokens = key_value_tokens;
+        job->query_start = query_start;
+        job->query_heads = query_heads;
+        job->key_value_heads = key_value_heads;
+        job->head_dimension = head_dimension;
+        job->query_stride = query_stride ? query_stride : query_heads * head_dimension;
+        job->key_stride = key_stride ? key_stride : key_value_heads * head_dimension;
+        job->value_stride = value_stride ? value_stride : key_value_heads * head_dimension;
+        job->scale = scale;
+        job->causal = causal;
+        job->worker = t;
+        job->workers = threads;
+        job->status = 0;
+        if (threads == 1) {
+            gqa_worker(job);
+            started = 0;
+        } else if (pthread_create(&handles[t], NULL, gqa_worker, job) == 0) {
+            ++started;
+        } else {
+            gqa_worker(job);
+        }
+    }
+    if (threads > 1)
+        for (t = 0; t < started; ++t) pthread_join(handles[t], NULL);
+    for (t = 0; t < threads; ++t)
+        if (jobs[t].status) status = jobs[t].status;
+    return status;
+}
+
+/* tests/unit/cuda/quant_qtype.c:2343-2391: the float scalar oracle the
+ * reference's CUDA tests compare the operator with (two passes, expf). */
+void yvx_oracle_gqa_f32_reference(const float *query, const float *key,
+                                  const float *value, float *output,
+                                  unsigned long long query_tokens,
+                                  unsigned long long key_value_tokens,
+                                  unsigned long long query_start,
+                                  unsigned long long query_heads,
+                                  unsigned long long key_value_heads,
+                                  unsigned long long head_dimension, int causal)
+{
+    const float scale = 1.0f / sqrtf((float)head_dimension);
+    const unsigned long long group = query_heads / key_value_heads;
+    unsigned long long token, head, source, lane;
+    for (token = 0; token < query_tokens; ++token)
+        for (head = 0; head < query_heads; ++head) {
+            const float *q = query + (token * query_heads + head) * head_dimension;
+            float *o = output + (token * query_heads + head) * head_dimension;
+            unsigned long long kv_head = head / group;
+            unsigned long long visible = causal ? query_start + token + 1ull
+                                                : key_value_tokens;
+            float maximum = -INFINITY, denominator = 0.0f;
+            for (source = 0; source < visible; ++source) {
+                const float *k = key + (source * key_value_heads + kv_head) * head_dimension;
+                float score = 0.0f;
+                for (lane = 0; lane < head_dimension; ++lane) score += q[lane] * k[lane];
+                if (score * scale > maximum) maximum = score * scale;
+            }
+            for (lane = 0; lane < head_dimension; ++lane) o[lane] = 0.0f;
+            for (source = 0; source < visible; ++source) {
+                const float *k = key + (source * key_value_heads + kv_head) * head_dimension;
+                const float *v = value + (source * key_value_heads + kv_head) * head_dimension;
+                float score = 0.0f, probability;
+                for (lane = 0; lane < head_dimension; ++lane) score += q[lane] * k[lane];
+                probability = expf(score * scale - maximum);
+                denominator += probability;
+                for (lane = 0; lane < head_dimension; ++lane) o[lane] += probability * v[lane];
+            }
+            for (lane = 0; lane < head_dimension; ++lane) o[lane] /= denominator;
+        }
+}
+
+/* ---- block-table addressing --------------------------------------------- */
+
+/* The reference keeps session KV rows contiguous in virtual address space
+ * (src/runtime/state_residency.c:958-1028); a block table is this library's
+ * extension. Row r of a session lives in pool row table[r / B] * B + r % B. */
+unsigned long long yvx_oracle_block_row(const int *block_table,
+                                        unsigned long long block_tokens,
+                                        unsigned long long row)
+{
+    return (unsigned long long)block_table[row / block_tokens] * block_tokens +
+           row % block_tokens;
+}
+
+void yvx_oracle_block_gather_u16(const unsigned short *pool, const int *block_table,
+                                 unsigned long long block_tokens,
+                                 unsigned long long rows,
+                                 unsigned long long row_elements,
+                                 unsigned short *out)
+{
+    unsigned long long row;
+    for (row = 0; row < rows; ++row)
+        memcpy(out + row * row_elements,
+               pool + yvx_oracle_block_row(block_table, block_tokens, row) * row_elements,
+               (size_t)row_elements * sizeof(*out));
+}
+
+/* ---- page geometry -------------------------------------------------------- */
+
+static unsigned long long gcd_u64(unsigned long long a, unsigned long long b)
+{
+    while (b) {
+        unsigned long long r = a % b;
+        a = b;
+        b = r;
+    }
+    return a;
+}
+
+static int mul_u64(unsigned long long a, unsigned long long b, unsigned long long *out)
+{
+    if (a && b > ULLONG_MAX / a) return 0;
+    *out = a * b;
+    return 1;
+}
+
+static int lcm_u64(unsigned long long a, unsigned long long b, unsigned long long *out)
+{
+    unsigned long long g;
+    if (!a || !b) return 0;
+    g = gcd_u64(a, b);
+    return mul_u64(a / g, b, out);
+}
+
+/* src/deployment/plan.c:208-283: page_tokens is the multiple of
+ * lcm(logical block, kernel tile, promotion granularity, alignment-in-tokens)
+ * that minimises table + fragmentation + copy-on-write + promotion bytes,
+ * bounded by the device page size; ties go to the smaller page. */
+int yvx_oracle_page_tokens(const yvx_oracle_page_request *r,
+                           unsigned long long *page_tokens,
+                           unsigned long long *page_bytes)
+{
+    unsigned long long base, alignment_blocks, alignment_tokens, maximum, candidate;
+    unsigned long long best_score = ULLONG_MAX, best = 0ull;
+    if (!r || !r->logical_block_tokens || !r->kernel_tile_tokens ||
+        !r->promotion_granularity_tokens || !r->alignment_bytes || !r->bytes_per_block)
+        return 0;
+    if (!lcm_u64(r->logical_block_tokens, r->kernel_tile_tokens, &base) ||
+        !lcm_u64(base, r->promotion_granularity_tokens, &base))
+        return 0;
+    alignment_blocks = r->alignment_bytes / gcd_u64(r->bytes_per_block, r->alignment_bytes);
+    if (!mul_u64(r->logical_block_tokens, alignment_blocks, &alignment_tokens) ||
+        !lcm_u64(base, alignment_tokens, &base))
+        return 0;
+    maximum = r->device_page_bytes / r->bytes_per_block;
+    if (!mul_u64(maximum, r->logical_block_tokens, &maximum)) return 0;
+    maximum -= maximum % base;
+    if (maximum < base) maximum = base;
+    for (candidate = base; candidate <= maximum;) {
+        unsigned long long pages, rounded, blocks, bytes, table, waste, score;
+        pages = r->logical_tokens / candidate + (r->logical_tokens % candidate != 0ull);
+        if (!mul_u64(pages, candidate, &rounded) || candidate % r->logical_block_tokens)
+            return 0;
+        blocks = candidate / r->logical_block_tokens;
+        if (!blocks || !mul_u64(blocks, r->bytes_per_block, &bytes)) return 0;
+        if (bytes % r->alignment_bytes == 0ull) {
+            unsigned long long spare = rounded - r->logical_tokens;
+            if (!mul_u64(pages, r->page_table_entry_bytes, &table)) return 0;
+            blocks = spare / r->logical_block_tokens + (spare % r->logical_block_tokens != 0ull);
+            if (!mul_u64(blocks, r->bytes_per_block, &waste)) return 0;
+            score = table + waste + (r->copy_on_write ? bytes : 0ull) +
+                    (r->candidate_extent ? waste : 0ull);
+            if (score < best_score || (score == best_score && candidate < best)) {
+                best_score = score;
+                best = candidate;
+            }
+        }
+        if (maximum - candidate < base) break;
+        candidate += base;
+    }
+    if (!best) return 0;
+    *page_tokens = best;
+    return mul_u64(best / r->logical_block_tokens, r->bytes_per_block, page_bytes);
+}
+
+/* src/graph/state_pages.c:660-669: first and last page of an element range. */
+int yvx_oracle_page_touch(unsigned long long element_start,
+                          unsigned long long element_count,
+                          unsigned long long page_elements,
+                          unsigned long long *first_page,
+                          unsigned long long *last_page)
+{
+    if (!element_count || !page_elements ||
+        element_start > ULLONG_MAX - element_count)
+        return 0;
+    *first_page = element_start / page_elements;
+    *last_page = (element_start + element_count - 1ull) / page_elements;
+    return 1;
+}
+
+/* ---- shared-latent reduction -------------------------------------------- */
+
+/* src/graph/core.c:361-390 (row visit), :466-508 (head reduce). All query
+ * heads share one row per position and the row is both key and value. The
+ * sink logit seeds the maximum and contributes exp(sink - max) to the
+ * denominator only. Two passes in double; the value accumulator is float as
+ * in the reference; the quotient is optionally rounded to bf16. Row r is
+ * visible to query row t when r <= query_start + t. */
+int yvx_oracle_latent_reduce(const float *query, const float *rows,
+                             const float *sinks, float *out,
+                             unsigned long long query_tokens,
+                             unsigned long long row_count,
+                             unsigned long long query_start,
+                             unsigned long long query_heads,
+                             unsigned long long head_dimension,
+                             unsigned long long row_stride, int round_bf16)
+{
+    const double scale = 1.0 / sqrt((double)head_dimension);
+    unsigned long long token, head, r, lane;
+    if (!row_stride) row_stride = head_dimension;
+    for (token = 0; token < query_tokens; ++token)
+        for (head = 0; head < query_heads; ++head) {
+            const float *q = query + (token * query_heads + head) * head_dimension;
+            float *o = out + (token * query_heads + head) * head_dimension;
+            unsigned long long visible = query_start + token + 1ull;
+            double maximum = (double)sinks[head], denominator;
+            if (visible > row_count) visible = row_count;
+            if (!isfinite(maximum)) return 0;
+            for (r = 0; r < visible; ++r) {
+                const float *row = rows + r * row_stride;
+                double score = 0.0;
+                for (lane = 0; lane < head_dimension; ++lane)
+                    score += (double)q[lane] * (double)row[lane];
+                score *= scale;
+                if (!isfinite(score)) return 0;
+                if (score > maximum) maximum = score;
+            }
+            denominator = exp((double)sinks[head] - maximum);
+            memset(o, 0, (size_t)head_dimension * sizeof(*o));
+            for (r = 0; r < visible; ++r) {
+                const float *row = rows + r * row_stride;
+                double score = 0.0;
+                for (lane = 0; lane < head_dimension; ++lane)
+                    score += (double)q[lane] * (double)row[lane];
+                score = exp(score * scale - maximum);
+                denominator += score;
+                for (lane = 0; lane < head_dimension; ++lane)
+                    o[lane] += (float)(score * row[lane]);
+            }
+            if (!isfinite(denominator) || denominator <= 0.0) return 0;
+            for (lane = 0; lane < head_dimension; ++lane) {
+                o[lane] = (float)((double)o[lane] / denominator);
+                if (round_bf16)
+                    o[lane] = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(o[lane]));
+            }
+        }
+    return 1;
+}
+
+/* ---- latent decode with a split rope key -------------------------------- */
+
+/* The reference has no counterpart for this variant (its rope dimensions live
+ * inside the shared latent row). The restatement keeps the reference's
+ * ordering and precision rules for the reduce (src/graph/core.c:361-508: two
+ * passes, double scores, libm exp) and its bf16 publication rule for the
+ * projected query (src/graph/numeric.c bf16 rounding of linear outputs):
+ *   q_lat[h,c] = bf16( sum_i q_nope[h,i] * W_uk[h,i,c] )        (double sum)
+ *   s[h,t]     = scale * ( q_lat[h,:].latent[t,:] + q_rope[h,:].k_rope[t,:] )
+ *   out[h,:]   = sum_t softmax_t(s[h,t]) * latent[t,:]            (float32)
+ */
+int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
+                          const unsigned short *q_rope_bf16,
+                          const unsigned short *w_uk_bf16,
+                          const unsigned short *latent_bf16,
+                          const unsigned short *rope_key_bf16, float *out,
+                          unsigned long long heads, unsigned long long nope_dim,
+                          unsigned long long latent_dim,
+                          unsigned long long rope_dim,
+                          unsigned long long context, float scale,
+                          float *absorbed_query_out)
+{
+    float *latent = malloc((size_t)(context * latent_dim) * sizeof(float));
+    float *rope = malloc((size_t)(context * rope_dim) * sizeof(float));
+    float *q_lat = malloc((size_t)latent_dim * sizeof(float));
+    double *scores = malloc((size_t)context * sizeof(double));
+    double *mixed = malloc((size_t)latent_dim * sizeof(double));
+    unsigned long long h, t, c, i;
+    int ok = 0;
+    if (!latent || !rope || !q_lat || !scores || !mixed) goto done;
+    yvx_oracle_bf16_decode_array(latent_bf16, latent, (size_t)(context * latent_dim));
+    yvx_oracle_bf16_decode_array(rope_key_bf16, rope, (size_t)(context * rope_dim));
+    for (h = 0; h < heads; ++h) {
+        double maximum = -INFINITY, denominator = 0.0;
+        for (c = 0; c < latent_dim; ++c) {
+            double sum = 0.0;
+            for (i = 0; i < nope_dim; ++i)
+                sum += (double)yvx_oracle_bf16_decode(q_nope_bf16[h * nope_dim + i]) *
+                       (double)yvx_oracle_bf16_decode(
+                           w_uk_bf16[(h * nope_dim + i) * latent_dim + c]);
+            q_lat[c] = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode((float)sum));
+            if (absorbed_query_out) absorbed_query_out[h * latent_dim + c] = q_lat[c];
+        }
+        for (t = 0; t < context; ++t) {
+            double score = 0.0;
+            for (c = 0; c < latent_dim; ++c)
+                score += (double)q_lat[c] * (double)latent[t * latent_dim + c];
+            for (i = 0; i < rope_dim; ++i)
+                score += (double)yvx_oracle_bf16_decode(q_rope_bf16[h * rope_dim + i]) *
+                         (double)rope[t * rope_dim + i];
+            scores[t] = score * (double)scale;
+            if (scores[t] > maximum) maximum = scores[t];
+        }
+        for (c = 0; c < latent_dim; ++c) mixed[c] = 0.0;
+        for (t = 0; t < context; ++t) {
+            double weight = exp(scores[t] - maximum);
+            denominator += weight;
+            for (c = 0; c < latent_dim; ++c)
+                mixed[c] += weight * (double)latent[t * latent_dim + c];
+        }
+        if (!isfinite(denominator) || denominator <= 0.0) goto done;
+        for (c = 0; c < latent_dim; ++c)
+            out[h * latent_dim + c] = (float)(mixed[c] / denominator);
+    }
+    ok = 1;
+done:
+    free(latent);
+    free(rope);
+    free(q_lat);
+    free(scores);
+    free(mixed);
+    return ok;
+}

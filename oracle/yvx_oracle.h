@@ -1,0 +1,121 @@
+/* TEST INFRASTRUCTURE ONLY.
+ *
+ * CPU restatement of the YVEX reference's attention arithmetic. It is the
+ * checker for the CUDA path: only the test-suite, the smoke check and the
+ * benchmark's CPU-baseline leg may build, load or call it. Nothing in the
+ * shipped library links against it and it is never a fallback.
+ *
+ * Parity status: pinned. Each function is checked against the reference's own
+ * golden vectors (tests/golden/) and, where the reference's CPU sources are
+ * available at build time, against the reference's compiled code
+ * (oracle/_ref/libyvex_ref.so) on random inputs.
+ */
+#ifndef YVX_ORACLE_H
+#define YVX_ORACLE_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Scalar codecs. */
+float yvx_oracle_bf16_decode(unsigned short bits);
+unsigned short yvx_oracle_bf16_encode(float value);
+float yvx_oracle_f16_decode(unsigned short bits);
+unsigned short yvx_oracle_f16_encode(float value);
+void yvx_oracle_bf16_decode_array(const unsigned short *bits, float *out, size_t count);
+void yvx_oracle_bf16_encode_array(const float *values, unsigned short *out, size_t count);
+
+/* Q8_0 block codec over GGUF rows: 34-byte blocks, [f16 scale][32 x int8]. */
+int yvx_oracle_q8_0_encode_block(const float *source, unsigned char *encoded);
+int yvx_oracle_q8_0_decode_block(const unsigned char *encoded, float *out);
+int yvx_oracle_q8_0_decode_rows(const unsigned char *encoded, float *out,
+                                size_t elements);
+
+/* The reference CPU exponential and the single-head attention primitive. */
+double yvx_oracle_exp(double x);
+int yvx_oracle_op_attention(const float *query, const float *keys,
+                            const float *values, unsigned long long seq_len,
+                            unsigned long long position, float scale, int causal,
+                            unsigned long long head_dim, float *score_scratch,
+                            float *probability_scratch, float *out);
+
+/* Grouped-query attention assembled from the primitive, one call per
+ * (query row, query head). Strides are in elements; zero means packed. */
+int yvx_oracle_gqa_attention(const float *query, const float *key,
+                             const float *value, float *output,
+                             unsigned long long query_tokens,
+                             unsigned long long key_value_tokens,
+                             unsigned long long query_start,
+                             unsigned long long query_heads,
+                             unsigned long long key_value_heads,
+                             unsigned long long head_dimension,
+                             unsigned long long query_stride,
+                             unsigned long long key_stride,
+                             unsigned long long value_stride, float scale,
+                             int causal, unsigned int threads);
+
+/* The single-precision scalar oracle the reference's CUDA tests compare with. */
+void yvx_oracle_gqa_f32_reference(const float *query, const float *key,
+                                  const float *value, float *output,
+                                  unsigned long long query_tokens,
+                                  unsigned long long key_value_tokens,
+                                  unsigned long long query_start,
+                                  unsigned long long query_heads,
+                                  unsigned long long key_value_heads,
+                                  unsigned long long head_dimension, int causal);
+
+/* Block-table addressing: logical row -> pool row. */
+unsigned long long yvx_oracle_block_row(const int *block_table,
+                                        unsigned long long block_tokens,
+                                        unsigned long long row);
+void yvx_oracle_block_gather_u16(const unsigned short *pool, const int *block_table,
+                                 unsigned long long block_tokens,
+                                 unsigned long long rows,
+                                 unsigned long long row_elements,
+                                 unsigned short *out);
+
+/* KV page geometry (integer, bit-exact). */
+typedef struct {
+    unsigned long long logical_block_tokens, kernel_tile_tokens;
+    unsigned long long promotion_granularity_tokens, alignment_bytes;
+    unsigned long long bytes_per_block, page_table_entry_bytes;
+    unsigned long long device_page_bytes, logical_tokens;
+    int copy_on_write, candidate_extent;
+} yvx_oracle_page_request;
+int yvx_oracle_page_tokens(const yvx_oracle_page_request *request,
+                           unsigned long long *page_tokens,
+                           unsigned long long *page_bytes);
+int yvx_oracle_page_touch(unsigned long long element_start,
+                          unsigned long long element_count,
+                          unsigned long long page_elements,
+                          unsigned long long *first_page,
+                          unsigned long long *last_page);
+
+/* Shared-latent (K == V) reduction with a per-head sink logit. */
+int yvx_oracle_latent_reduce(const float *query, const float *rows,
+                             const float *sinks, float *out,
+                             unsigned long long query_tokens,
+                             unsigned long long row_count,
+                             unsigned long long query_start,
+                             unsigned long long query_heads,
+                             unsigned long long head_dimension,
+                             unsigned long long row_stride, int round_bf16);
+
+/* Latent decode with a separate rope key and an absorbed up-projection. */
+int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
+                          const unsigned short *q_rope_bf16,
+                          const unsigned short *w_uk_bf16,
+                          const unsigned short *latent_bf16,
+                          const unsigned short *rope_key_bf16, float *out,
+                          unsigned long long heads, unsigned long long nope_dim,
+                          unsigned long long latent_dim,
+                          unsigned long long rope_dim,
+                          unsigned long long context, float scale,
+                          float *absorbed_query_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YVX_ORACLE_H */
