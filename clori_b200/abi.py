@@ -1,0 +1,240 @@
+"""ctypes mirror of include/yvex_b200/*.h: the C-ABI of libyvex_b200.so.
+
+Loading fails loudly when the shared library has not been built; nothing in
+this package can compute on the host.
+"""
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libyvex_b200.so")
+
+# yvex_status (include/yvex_b200/abi.h)
+YVEX_OK = 0
+YVEX_ERR = -1
+YVEX_ERR_NOMEM = -2
+YVEX_ERR_IO = -3
+YVEX_ERR_FORMAT = -4
+YVEX_ERR_UNSUPPORTED = -5
+YVEX_ERR_BACKEND = -6
+YVEX_ERR_BOUNDS = -7
+YVEX_ERR_STATE = -8
+YVEX_ERR_CANCELLED = -9
+YVEX_ERR_INVALID_ARG = -10
+YVEX_ERR_TIMEOUT = -11
+
+# yvex_dtype
+DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_F64 = 1, 2, 3, 4
+DTYPE_I8, DTYPE_I16, DTYPE_I32, DTYPE_I64 = 5, 6, 7, 8
+DTYPE_Q8_0 = 13
+DTYPE_BYTES = {DTYPE_F32: 4, DTYPE_F16: 2, DTYPE_BF16: 2, DTYPE_F64: 8, DTYPE_I8: 1,
+               DTYPE_I16: 2, DTYPE_I32: 4, DTYPE_I64: 8}
+
+LAYOUT_TOKEN_HEAD_DIM = 1
+MASK_FULL, MASK_CAUSAL = 1, 2
+NUMERIC_EXACT_F32 = 1
+NUMERIC_BF16_F32_ACCUMULATE = 2
+NUMERIC_Q8_0_KV_F32_ACCUMULATE = 3
+BACKEND_KIND_CPU, BACKEND_KIND_CUDA = 0, 1
+KV_CONTIGUOUS, KV_BLOCK_TABLE = 0, 1
+MAX_DIMS = 8
+u64 = C.c_ulonglong
+
+
+class Error(C.Structure):
+    _fields_ = [("code", C.c_int), ("where", C.c_char * 96), ("message", C.c_char * 256)]
+
+
+class DeviceTensor(C.Structure):
+    _fields_ = [
+        ("owner", C.c_void_p), ("owner_id", u64), ("name", C.c_char_p), ("dtype", C.c_int),
+        ("rank", C.c_uint), ("dims", u64 * MAX_DIMS), ("bytes", u64), ("data", C.c_void_p),
+        ("host_data", C.c_void_p), ("backend_allocation", C.c_void_p), ("resident_bytes", u64),
+        ("virtual_reserved", C.c_int), ("is_written", C.c_int), ("host_accessible", C.c_int),
+        ("borrowed_host", C.c_int),
+    ]
+
+
+class TensorDesc(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int), ("rank", C.c_uint),
+                ("dims", u64 * MAX_DIMS), ("bytes", u64)]
+
+
+class OperationFacts(C.Structure):
+    _fields_ = [(n, u64) for n in (
+        "h2d_bytes", "d2h_bytes", "d2d_bytes", "kernel_launches", "upload_count",
+        "download_count", "queue_synchronizations", "device_synchronizations",
+        "active_weight_bytes", "state_bytes", "activation_bytes", "temporary_bytes",
+        "accelerated_matrix_launches")] + [("compulsory_memory_facts_available", C.c_int)]
+
+
+class AttentionRequirement(C.Structure):
+    _fields_ = [(n, u64) for n in (
+        "query_tokens", "key_value_tokens", "query_start", "query_heads", "key_value_heads",
+        "head_dimension", "query_token_stride", "key_token_stride", "value_token_stride")] + [
+        ("query_dtype", C.c_int), ("key_dtype", C.c_int), ("value_dtype", C.c_int),
+        ("output_dtype", C.c_int), ("layout", C.c_int), ("mask", C.c_int),
+        ("numeric_contract", C.c_int), ("deterministic", C.c_int)]
+
+
+class AttentionRequest(C.Structure):
+    _fields_ = [("requirement", AttentionRequirement), ("query", C.POINTER(DeviceTensor)),
+                ("key", C.POINTER(DeviceTensor)), ("value", C.POINTER(DeviceTensor)),
+                ("output", C.POINTER(DeviceTensor))]
+
+
+class BackendOptions(C.Structure):
+    _fields_ = [("kind", C.c_int), ("device", C.c_char_p), ("memory_limit_bytes", u64)]
+
+
+WORKSPACE_FN = C.CFUNCTYPE(C.c_int, C.POINTER(AttentionRequirement), C.POINTER(u64),
+                           C.POINTER(Error))
+EXECUTE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(AttentionRequest),
+                         C.POINTER(OperationFacts), C.POINTER(Error))
+
+
+class TransformerOperations(C.Structure):
+    _fields_ = [("attention_workspace_required", WORKSPACE_FN),
+                ("attention_execute", EXECUTE_FN)]
+
+
+class BatchRequest(C.Structure):
+    _fields_ = [("requirement", AttentionRequirement), ("session_count", u64),
+                ("kv_layout", C.c_int), ("query", C.POINTER(DeviceTensor)),
+                ("key", C.POINTER(DeviceTensor)), ("value", C.POINTER(DeviceTensor)),
+                ("kv_tokens", C.POINTER(DeviceTensor)), ("block_table", C.POINTER(DeviceTensor)),
+                ("block_tokens", u64), ("max_blocks_per_session", u64),
+                ("kv_session_stride", u64), ("kv_block_stride", u64), ("kv_head_stride", u64),
+                ("output", C.POINTER(DeviceTensor))]
+
+
+class PageRequest(C.Structure):
+    _fields_ = [(n, u64) for n in (
+        "logical_block_tokens", "kernel_tile_tokens", "promotion_granularity_tokens",
+        "alignment_bytes", "bytes_per_block", "page_table_entry_bytes", "device_page_bytes",
+        "logical_tokens")] + [("copy_on_write", C.c_int), ("candidate_extent", C.c_int)]
+
+
+class GqaProblem(C.Structure):
+    """yvx_gqa_problem (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [
+        ("sessions", C.c_uint), ("query_rows", C.c_uint), ("query_heads", C.c_uint),
+        ("kv_heads", C.c_uint), ("head_dim", C.c_uint), ("causal", C.c_uint),
+        ("scale", C.c_float), ("query_dtype", C.c_int), ("kv_dtype", C.c_int),
+        ("output_dtype", C.c_int),
+        ("query", C.c_void_p), ("query_row_stride", u64), ("query_session_stride", u64),
+        ("output", C.c_void_p),
+        ("key", C.c_void_p), ("value", C.c_void_p),
+        ("key_token_stride", u64), ("value_token_stride", u64),
+        ("key_head_stride", u64), ("value_head_stride", u64),
+        ("key_session_stride", u64), ("value_session_stride", u64),
+        ("block_table", C.c_void_p), ("block_tokens", C.c_uint), ("block_table_stride", C.c_uint),
+        ("pool_blocks", C.c_uint),
+        ("key_block_stride", u64), ("value_block_stride", u64),
+        ("kv_tokens", C.c_void_p), ("kv_tokens_uniform", C.c_uint), ("kv_tokens_max", C.c_uint),
+        ("query_start", C.c_void_p), ("query_start_uniform", C.c_uint),
+        ("query_start_from_end", C.c_uint), ("kv_position_base", C.c_uint),
+        ("chunk_tokens", C.c_uint), ("max_splits", C.c_uint),
+        ("partials", C.c_void_p), ("partial_output", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
+# Every symbol the headers declare; tests check the library exports each one.
+EXPORTED_SYMBOLS = [
+    # attention.h
+    "yvex_error_clear", "yvex_error_set", "yvex_status_name",
+    "yvex_backend_open", "yvex_backend_close_checked", "yvex_backend_close",
+    "yvex_backend_cuda_available", "yvex_backend_sync",
+    "yvex_backend_tensor_alloc", "yvex_backend_tensor_release", "yvex_backend_tensor_free",
+    "yvex_backend_tensor_write", "yvex_backend_tensor_read", "yvex_backend_tensor_zero",
+    "yvex_backend_tensor_f32_subview", "yvex_b200_tensor_wrap",
+    "yvex_b200_backend_bind_stream", "yvex_b200_backend_stream", "yvex_b200_backend_sm_count",
+    "yvex_b200_transformer_operations_get",
+    "yvex_b200_transformer_attention_workspace_required",
+    "yvex_b200_transformer_attention_execute",
+    "yvex_backend_op_attention", "yvex_b200_attention_batch_execute",
+    "yvex_b200_kv_page_tokens", "yvex_b200_kv_page_touch", "yvex_b200_kv_block_row",
+    # cuda_shim.h
+    "yvx_cuda_device_count", "yvx_cuda_device_select", "yvx_cuda_device_properties",
+    "yvx_cuda_malloc", "yvx_cuda_free", "yvx_cuda_host_alloc", "yvx_cuda_host_free",
+    "yvx_cuda_memset_async", "yvx_cuda_upload_async", "yvx_cuda_download_async",
+    "yvx_cuda_copy_async", "yvx_cuda_stream_create", "yvx_cuda_stream_destroy",
+    "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
+    "yvx_cuda_event_record", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
+    "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
+    "yvx_cuda_lse_combine", "yvx_cuda_op_attention_f32",
+]
+
+_lib = None
+
+
+def load():
+    """Load libyvex_b200.so; raise if it is missing (there is no fallback)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is not built; run `python -m clori_b200._build` "
+            "(the attention path has no CPU or library fallback)")
+    lib = C.CDLL(LIB_PATH)
+    P = C.POINTER
+    vp = C.c_void_p
+    lib.yvex_status_name.restype = C.c_char_p
+    lib.yvex_status_name.argtypes = [C.c_int]
+    lib.yvex_backend_open.argtypes = [P(vp), P(BackendOptions), P(Error)]
+    lib.yvex_backend_close_checked.argtypes = [P(vp), P(Error)]
+    lib.yvex_backend_close.restype = None
+    lib.yvex_backend_close.argtypes = [vp]
+    lib.yvex_backend_sync.argtypes = [vp, P(Error)]
+    lib.yvex_backend_tensor_alloc.argtypes = [vp, P(TensorDesc), P(P(DeviceTensor)), P(Error)]
+    lib.yvex_b200_tensor_wrap.argtypes = [vp, P(TensorDesc), vp, P(P(DeviceTensor)), P(Error)]
+    lib.yvex_backend_tensor_release.argtypes = [vp, P(P(DeviceTensor)), P(Error)]
+    lib.yvex_backend_tensor_write.argtypes = [vp, P(DeviceTensor), vp, u64, P(Error)]
+    lib.yvex_backend_tensor_read.argtypes = [vp, P(DeviceTensor), vp, u64, P(Error)]
+    lib.yvex_backend_tensor_zero.argtypes = [vp, P(DeviceTensor), P(Error)]
+    lib.yvex_backend_tensor_f32_subview.argtypes = [P(DeviceTensor), u64, u64, P(DeviceTensor)]
+    lib.yvex_b200_backend_bind_stream.argtypes = [vp, vp, C.c_int, P(Error)]
+    lib.yvex_b200_backend_stream.restype = vp
+    lib.yvex_b200_backend_stream.argtypes = [vp]
+    lib.yvex_b200_backend_sm_count.argtypes = [vp]
+    lib.yvex_b200_transformer_operations_get.restype = P(TransformerOperations)
+    lib.yvex_b200_transformer_operations_get.argtypes = [vp]
+    lib.yvex_b200_transformer_attention_workspace_required.argtypes = [
+        P(AttentionRequirement), P(u64), P(Error)]
+    lib.yvex_b200_transformer_attention_execute.argtypes = [
+        vp, P(AttentionRequest), P(OperationFacts), P(Error)]
+    lib.yvex_backend_op_attention.argtypes = [
+        vp, P(DeviceTensor), P(DeviceTensor), P(DeviceTensor), u64, u64, C.c_float, C.c_int,
+        P(DeviceTensor), P(DeviceTensor), P(DeviceTensor), P(Error)]
+    lib.yvex_b200_attention_batch_execute.argtypes = [
+        vp, P(BatchRequest), P(OperationFacts), P(Error)]
+    lib.yvex_b200_kv_page_tokens.argtypes = [P(PageRequest), P(u64), P(u64)]
+    lib.yvex_b200_kv_page_touch.argtypes = [u64, u64, u64, P(u64), P(u64)]
+    lib.yvex_b200_kv_block_row.restype = u64
+    lib.yvex_b200_kv_block_row.argtypes = [P(C.c_int), u64, u64]
+    lib.yvx_cuda_last_error_text.restype = C.c_char_p
+    lib.yvx_cuda_device_count.argtypes = [P(C.c_int)]
+    lib.yvx_cuda_malloc.argtypes = [P(vp), u64]
+    lib.yvx_cuda_free.argtypes = [vp]
+    lib.yvx_cuda_host_alloc.argtypes = [P(vp), u64]
+    lib.yvx_cuda_host_free.argtypes = [vp]
+    lib.yvx_cuda_memset_async.argtypes = [vp, C.c_int, u64, vp]
+    lib.yvx_cuda_upload_async.argtypes = [vp, vp, u64, vp]
+    lib.yvx_cuda_download_async.argtypes = [vp, vp, u64, vp]
+    lib.yvx_cuda_copy_async.argtypes = [vp, vp, u64, vp]
+    lib.yvx_cuda_stream_create.argtypes = [P(vp)]
+    lib.yvx_cuda_stream_destroy.argtypes = [vp]
+    lib.yvx_cuda_stream_synchronize.argtypes = [vp]
+    lib.yvx_cuda_event_create.argtypes = [P(vp)]
+    lib.yvx_cuda_event_destroy.argtypes = [vp]
+    lib.yvx_cuda_event_record.argtypes = [vp, vp]
+    lib.yvx_cuda_event_elapsed_ms.argtypes = [vp, vp, P(C.c_float)]
+    lib.yvx_cuda_gqa_partials_bytes.restype = u64
+    lib.yvx_cuda_gqa_partials_bytes.argtypes = [P(GqaProblem)]
+    lib.yvx_cuda_gqa_plan_splits.restype = None
+    lib.yvx_cuda_gqa_plan_splits.argtypes = [P(GqaProblem), C.c_int]
+    lib.yvx_cuda_gqa_attention.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
+    lib.yvx_cuda_lse_combine.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, C.c_int, vp, vp]
+    _lib = lib
+    return lib

@@ -1,0 +1,71 @@
+// Device-side helpers shared by the attention kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "yvex_b200/abi.h"
+#include "yvex_b200/cuda_shim.h"
+
+#define YVX_STATUS_OK 0
+#define YVX_STATUS_NONFINITE 1
+#define YVX_STATUS_CONTRACT 2
+#define YVX_STATUS_TIMEOUT 3
+
+// Maps a CUDA runtime error to the yvex_status the reference reports for
+// launch and copy failures (YVEX_ERR_BACKEND) and remembers the text.
+int yvx_cuda_check(cudaError_t error, const char *what);
+
+#define YVX_CUDA_TRY(call)                                 \
+    do {                                                   \
+        int yvx_rc_ = yvx_cuda_check((call), #call);       \
+        if (yvx_rc_ != 0) return yvx_rc_;                  \
+    } while (0)
+
+namespace yvx {
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+    return v;
+}
+
+__device__ __forceinline__ float load_as_float(const float *p) { return *p; }
+__device__ __forceinline__ float load_as_float(const __nv_bfloat16 *p)
+{
+    return __bfloat162float(*p);
+}
+
+// Round-to-nearest-even bf16 publication with the reference's NaN quieting
+// (src/gguf/quant_scalar.c:130-143; CUDA twin kernel_primitives.h:89).
+__device__ __forceinline__ unsigned short bf16_bits_rne(float value)
+{
+    uint32_t bits = __float_as_uint(value);
+    uint32_t high = bits >> 16, low = bits & 0xffffu;
+    if ((bits & 0x7f800000u) == 0x7f800000u && (bits & 0x007fffffu))
+        return (unsigned short)(high | 0x0040u);
+    if (low > 0x8000u || (low == 0x8000u && (high & 1u))) high += 1u;
+    return (unsigned short)high;
+}
+
+__device__ __forceinline__ void store_output(void *base, int dtype, unsigned long long index,
+                                             float value)
+{
+    if (dtype == YVEX_DTYPE_BF16)
+        reinterpret_cast<unsigned short *>(base)[index] = bf16_bits_rne(value);
+    else
+        reinterpret_cast<float *>(base)[index] = value;
+}
+
+}  // namespace yvx

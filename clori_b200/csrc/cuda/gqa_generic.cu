@@ -1,0 +1,363 @@
+// General split-KV grouped-query attention for sm_100a: any head_dim <= 256,
+// F32 or BF16 operands, contiguous strided KV rows or a block table. This is
+// the exact-F32 contract's kernel and the path every shape without a
+// specialised kernel takes. It is bandwidth-shaped: one warp streams KV rows
+// with coalesced 128-byte loads, lanes own head dimensions, every KV row is
+// read once for the whole query-head group and all verify rows, and the
+// softmax statistics live in registers.
+//
+// Replaces yvex_gqa_f32_body (src/backend/cuda/transformer_kernels.cu:137-238
+// in the reference), which walks all KV rows serially in one CTA per query
+// head with two barriers per row and re-reads each KV head once per query
+// head.
+#include "common.cuh"
+
+namespace yvx {
+
+constexpr int kGenericThreads = 128;
+constexpr int kGenericWarps = kGenericThreads / 32;
+
+struct SessionView {
+    unsigned int kv_tokens;
+    long long query_start_local;  // query_start - kv_position_base (may be negative)
+};
+
+__device__ __forceinline__ SessionView session_view(const yvx_gqa_problem &p, unsigned int b)
+{
+    SessionView s;
+    s.kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    long long start;
+    if (p.query_start)
+        start = (long long)p.query_start[b];
+    else if (p.query_start_from_end)
+        start = (long long)p.kv_position_base + (long long)s.kv_tokens - (long long)p.query_rows;
+    else
+        start = (long long)p.query_start_uniform;
+    s.query_start_local = start - (long long)p.kv_position_base;
+    return s;
+}
+
+// Address of one KV row of one head. A block-table entry outside the pool is a
+// contract failure: it is recorded in the status word and the row reads pool
+// block 0 instead of an arbitrary address (the result is discarded by the host).
+template <typename KT>
+__device__ __forceinline__ const KT *kv_row(const void *base, const yvx_gqa_problem &p,
+                                            unsigned int b, unsigned int token,
+                                            unsigned int kv_head, bool is_key)
+{
+    const unsigned long long token_stride = is_key ? p.key_token_stride : p.value_token_stride;
+    const unsigned long long head_stride = is_key ? p.key_head_stride : p.value_head_stride;
+    unsigned long long offset;
+    if (p.block_table) {
+        const unsigned int block = token / p.block_tokens;
+        const unsigned int within = token - block * p.block_tokens;
+        int pool_block = p.block_table[(unsigned long long)b * p.block_table_stride + block];
+        if (pool_block < 0 || (unsigned int)pool_block >= p.pool_blocks) {
+            atomicCAS(p.status, 0, YVX_STATUS_CONTRACT);
+            pool_block = 0;
+        }
+        offset = (unsigned long long)pool_block * (is_key ? p.key_block_stride : p.value_block_stride) +
+                 (unsigned long long)within * token_stride;
+    } else {
+        offset = (unsigned long long)b * (is_key ? p.key_session_stride : p.value_session_stride) +
+                 (unsigned long long)token * token_stride;
+    }
+    return reinterpret_cast<const KT *>(base) + offset + (unsigned long long)kv_head * head_stride;
+}
+
+// grid: x = split, y = kv_head * vector_tiles + tile, z = session.
+// A "vector" is one (query row, query head of the group) pair; a CTA carries
+// VT of them so each KV row it loads serves VT dot products.
+template <typename QT, typename KT, int SLOTS, int VT>
+__global__ void __launch_bounds__(kGenericThreads)
+gqa_split_generic_kernel(const yvx_gqa_problem p)
+{
+    constexpr int HD_CAP = SLOTS * 32;
+    __shared__ float sm_acc[kGenericWarps][VT][HD_CAP];
+    __shared__ float sm_m[kGenericWarps][VT];
+    __shared__ float sm_l[kGenericWarps][VT];
+
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned int group = p.query_heads / p.kv_heads;
+    const unsigned int vectors = p.query_rows * group;
+    const unsigned int tiles = (vectors + VT - 1) / VT;
+    const unsigned int kv_head = blockIdx.y / tiles, tile = blockIdx.y % tiles;
+    const unsigned int b = blockIdx.z, split = blockIdx.x;
+    const unsigned int hd = p.head_dim;
+    const SessionView s = session_view(p, b);
+
+    const unsigned int t0 = split * p.chunk_tokens;
+    if (t0 >= s.kv_tokens) return;
+    unsigned int t1 = min(s.kv_tokens, t0 + p.chunk_tokens);
+
+    // Per-vector query registers and visibility limits.
+    float q[VT][SLOTS];
+    long long limit[VT];
+    bool live[VT];
+    long long tile_limit = -1;
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+        const unsigned int v = tile * VT + i;
+        live[i] = v < vectors;
+        const unsigned int row = live[i] ? v / group : 0u;
+        const unsigned int qhead = kv_head * group + (live[i] ? v % group : 0u);
+        limit[i] = !live[i] ? -1
+                   : p.causal ? s.query_start_local + (long long)row
+                              : (long long)s.kv_tokens - 1;
+        tile_limit = limit[i] > tile_limit ? limit[i] : tile_limit;
+        const QT *qp = reinterpret_cast<const QT *>(p.query) +
+                       (unsigned long long)b * p.query_session_stride +
+                       (unsigned long long)row * p.query_row_stride +
+                       (unsigned long long)qhead * hd;
+#pragma unroll
+        for (int sl = 0; sl < SLOTS; ++sl) {
+            const unsigned int d = lane + 32u * sl;
+            q[i][sl] = (live[i] && d < hd) ? load_as_float(qp + d) * p.scale : 0.0f;
+        }
+    }
+    if (tile_limit + 1 < (long long)t1) t1 = tile_limit + 1 > 0 ? (unsigned int)(tile_limit + 1) : 0u;
+
+    float m[VT], l[VT], acc[VT][SLOTS];
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.0f;
+#pragma unroll
+        for (int sl = 0; sl < SLOTS; ++sl) acc[i][sl] = 0.0f;
+    }
+
+    // Register double-buffer: the next row's loads are in flight while the
+    // current row is reduced.
+    float kc[SLOTS], vc[SLOTS], kn[SLOTS], vn[SLOTS];
+    unsigned int t = t0 + warp;
+    if (t < t1) {
+        const KT *kp = kv_row<KT>(p.key, p, b, t, kv_head, true);
+        const KT *vp = kv_row<KT>(p.value, p, b, t, kv_head, false);
+#pragma unroll
+        for (int sl = 0; sl < SLOTS; ++sl) {
+            const unsigned int d = lane + 32u * sl;
+            kn[sl] = d < hd ? load_as_float(kp + d) : 0.0f;
+            vn[sl] = d < hd ? load_as_float(vp + d) : 0.0f;
+        }
+    }
+    for (; t < t1; t += kGenericWarps) {
+#pragma unroll
+        for (int sl = 0; sl < SLOTS; ++sl) {
+            kc[sl] = kn[sl];
+            vc[sl] = vn[sl];
+        }
+        const unsigned int tn = t + kGenericWarps;
+        if (tn < t1) {
+            const KT *kp = kv_row<KT>(p.key, p, b, tn, kv_head, true);
+            const KT *vp = kv_row<KT>(p.value, p, b, tn, kv_head, false);
+#pragma unroll
+            for (int sl = 0; sl < SLOTS; ++sl) {
+                const unsigned int d = lane + 32u * sl;
+                kn[sl] = d < hd ? load_as_float(kp + d) : 0.0f;
+                vn[sl] = d < hd ? load_as_float(vp + d) : 0.0f;
+            }
+        }
+        float dot[VT];
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            float partial = 0.0f;
+#pragma unroll
+            for (int sl = 0; sl < SLOTS; ++sl) partial = fmaf(q[i][sl], kc[sl], partial);
+            dot[i] = partial;
+        }
+#pragma unroll
+        for (int offset = 16; offset; offset >>= 1)
+#pragma unroll
+            for (int i = 0; i < VT; ++i)
+                dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], offset);
+#pragma unroll
+        for (int i = 0; i < VT; ++i) {
+            if ((long long)t <= limit[i]) {
+                const float fresh = fmaxf(m[i], dot[i]);
+                const float keep = m[i] == -INFINITY ? 0.0f : expf(m[i] - fresh);
+                const float weight = expf(dot[i] - fresh);
+                l[i] = l[i] * keep + weight;
+#pragma unroll
+                for (int sl = 0; sl < SLOTS; ++sl)
+                    acc[i][sl] = acc[i][sl] * keep + weight * vc[sl];
+                m[i] = fresh;
+            }
+        }
+    }
+
+    // Merge the four warps' running states.
+#pragma unroll
+    for (int i = 0; i < VT; ++i) {
+        if (lane == 0) {
+            sm_m[warp][i] = m[i];
+            sm_l[warp][i] = l[i];
+        }
+#pragma unroll
+        for (int sl = 0; sl < SLOTS; ++sl) sm_acc[warp][i][lane + 32 * sl] = acc[i][sl];
+    }
+    __syncthreads();
+
+    const bool direct = p.max_splits == 1u;
+    for (int i = 0; i < VT; ++i) {
+        const unsigned int v = tile * VT + i;
+        if (v >= vectors) break;
+        const unsigned int row = v / group, qhead = kv_head * group + v % group;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kGenericWarps; ++w) mm = fmaxf(mm, sm_m[w][i]);
+        float scale_w[kGenericWarps], ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kGenericWarps; ++w) {
+            scale_w[w] = sm_m[w][i] == -INFINITY ? 0.0f : expf(sm_m[w][i] - mm);
+            ll += sm_l[w][i] * scale_w[w];
+        }
+        const float inverse = ll > 0.0f ? 1.0f / ll : 0.0f;
+        const unsigned long long item =
+            ((unsigned long long)b * p.query_rows + row) * p.query_heads + qhead;
+        for (unsigned int d = threadIdx.x; d < hd; d += kGenericThreads) {
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kGenericWarps; ++w) o += sm_acc[w][i][d] * scale_w[w];
+            if (direct && !p.partial_output) {
+                const float value = o / ll;
+                if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+                store_output(p.output, p.output_dtype, item * hd + d, value);
+            } else {
+                float *part = direct ? p.partial_output + item * (hd + 2ull)
+                                     : p.partials + (item * p.max_splits + split) * (hd + 2ull);
+                part[d] = o * inverse;
+                if (d == 0) {
+                    part[hd] = mm;
+                    part[hd + 1] = ll;
+                }
+            }
+        }
+    }
+}
+
+// One CTA per (session, row, query head): folds the per-split (o, m, l)
+// triples in split order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(128)
+gqa_combine_kernel(const yvx_gqa_problem p)
+{
+    const unsigned long long item = blockIdx.x;
+    const unsigned int b = (unsigned int)(item / ((unsigned long long)p.query_rows * p.query_heads));
+    const unsigned int hd = p.head_dim;
+    const SessionView s = session_view(p, b);
+    const unsigned int splits = (s.kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens;
+    const float *parts = p.partials + item * p.max_splits * (hd + 2ull);
+
+    float mm = -INFINITY;
+    for (unsigned int j = 0; j < splits; ++j) mm = fmaxf(mm, parts[j * (hd + 2ull) + hd]);
+    float ll = 0.0f;
+    for (unsigned int j = 0; j < splits; ++j) {
+        const float mj = parts[j * (hd + 2ull) + hd];
+        ll += mj == -INFINITY ? 0.0f : parts[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
+    }
+    for (unsigned int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.0f;
+        for (unsigned int j = 0; j < splits; ++j) {
+            const float mj = parts[j * (hd + 2ull) + hd];
+            const float w = mj == -INFINITY ? 0.0f : parts[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
+            o = fmaf(parts[j * (hd + 2ull) + d], w, o);
+        }
+        if (p.partial_output) {
+            float *part = p.partial_output + item * (hd + 2ull);
+            part[d] = ll > 0.0f ? o / ll : 0.0f;
+            if (d == 0) {
+                part[hd] = mm;
+                part[hd + 1] = ll;
+            }
+        } else {
+            const float value = o / ll;
+            if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+            store_output(p.output, p.output_dtype, item * hd + d, value);
+        }
+    }
+}
+
+// Combine of externally gathered partials: parts[item][part][hd+2].
+__global__ void __launch_bounds__(128)
+lse_combine_kernel(const float *parts, unsigned int part_count, unsigned int hd, void *output,
+                   int output_dtype, int *status)
+{
+    const unsigned long long item = blockIdx.x;
+    const float *base = parts + item * part_count * (hd + 2ull);
+    float mm = -INFINITY, ll = 0.0f;
+    for (unsigned int j = 0; j < part_count; ++j) mm = fmaxf(mm, base[j * (hd + 2ull) + hd]);
+    for (unsigned int j = 0; j < part_count; ++j) {
+        const float mj = base[j * (hd + 2ull) + hd];
+        ll += mj == -INFINITY ? 0.0f : base[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
+    }
+    for (unsigned int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.0f;
+        for (unsigned int j = 0; j < part_count; ++j) {
+            const float mj = base[j * (hd + 2ull) + hd];
+            const float w = mj == -INFINITY ? 0.0f : base[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
+            o = fmaf(base[j * (hd + 2ull) + d], w, o);
+        }
+        const float value = o / ll;
+        if (!isfinite(value)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
+        store_output(output, output_dtype, item * hd + d, value);
+    }
+}
+
+template <typename QT, typename KT, int SLOTS>
+static int launch_generic(const yvx_gqa_problem &p, cudaStream_t stream)
+{
+    const unsigned int group = p.query_heads / p.kv_heads;
+    const unsigned int vectors = p.query_rows * group;
+    if (vectors <= 4u) {
+        const dim3 grid(p.max_splits, p.kv_heads * ((vectors + 3u) / 4u), p.sessions);
+        gqa_split_generic_kernel<QT, KT, SLOTS, 4><<<grid, kGenericThreads, 0, stream>>>(p);
+    } else {
+        const dim3 grid(p.max_splits, p.kv_heads * ((vectors + 7u) / 8u), p.sessions);
+        gqa_split_generic_kernel<QT, KT, SLOTS, 8><<<grid, kGenericThreads, 0, stream>>>(p);
+    }
+    return yvx_cuda_check(cudaGetLastError(), "gqa_split_generic_kernel");
+}
+
+template <typename QT, typename KT>
+static int launch_generic_slots(const yvx_gqa_problem &p, cudaStream_t stream)
+{
+    if (p.head_dim <= 128u) return launch_generic<QT, KT, 4>(p, stream);
+    return launch_generic<QT, KT, 8>(p, stream);
+}
+
+int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, unsigned int *launches)
+{
+    int rc;
+    if (p.head_dim == 0u || p.head_dim > 256u) return YVEX_ERR_UNSUPPORTED;
+    if (p.query_dtype == YVEX_DTYPE_F32 && p.kv_dtype == YVEX_DTYPE_F32)
+        rc = launch_generic_slots<float, float>(p, stream);
+    else if (p.query_dtype == YVEX_DTYPE_BF16 && p.kv_dtype == YVEX_DTYPE_BF16)
+        rc = launch_generic_slots<__nv_bfloat16, __nv_bfloat16>(p, stream);
+    else if (p.query_dtype == YVEX_DTYPE_F32 && p.kv_dtype == YVEX_DTYPE_BF16)
+        rc = launch_generic_slots<float, __nv_bfloat16>(p, stream);
+    else
+        return YVEX_ERR_UNSUPPORTED;
+    if (rc != 0) return rc;
+    *launches = 1u;
+    if (p.max_splits > 1u) {
+        const unsigned long long items =
+            (unsigned long long)p.sessions * p.query_rows * p.query_heads;
+        gqa_combine_kernel<<<(unsigned int)items, 128, 0, stream>>>(p);
+        rc = yvx_cuda_check(cudaGetLastError(), "gqa_combine_kernel");
+        if (rc != 0) return rc;
+        *launches = 2u;
+    }
+    return 0;
+}
+
+}  // namespace yvx
+
+extern "C" int yvx_cuda_lse_combine(const float *parts, unsigned int items,
+                                    unsigned int part_count, unsigned int head_dim,
+                                    void *output, int output_dtype, int *status, void *stream)
+{
+    if (!parts || !items || !part_count || !head_dim || !output || !status)
+        return YVEX_ERR_INVALID_ARG;
+    yvx::lse_combine_kernel<<<items, 128, 0, (cudaStream_t)stream>>>(
+        parts, part_count, head_dim, output, output_dtype, status);
+    return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
+}

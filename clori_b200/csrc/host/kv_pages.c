@@ -1,0 +1,98 @@
+/* KV block and page indexing: integer arithmetic that must agree bit for bit
+ * with the reference's capacity plan and page store. */
+#include "private.h"
+
+static unsigned long long pages_gcd(unsigned long long a, unsigned long long b)
+{
+    while (b) {
+        unsigned long long r = a % b;
+        a = b;
+        b = r;
+    }
+    return a;
+}
+
+static int pages_lcm(unsigned long long a, unsigned long long b, unsigned long long *out)
+{
+    if (!a || !b) return 0;
+    return yvx_u64_mul(a / pages_gcd(a, b), b, out);
+}
+
+/* src/deployment/plan.c:208-283 (capacity_state_geometry): candidates are the
+ * multiples of lcm(logical block, kernel tile, promotion granularity,
+ * alignment expressed in tokens) up to what one device page holds; the score
+ * of a candidate is page-table bytes + fragmentation bytes + one page when
+ * copy-on-write + fragmentation again for a candidate-extent class; candidates
+ * whose page bytes miss the alignment are skipped; ties go to fewer tokens. */
+int yvex_b200_kv_page_tokens(const yvex_b200_page_request *r, unsigned long long *page_tokens,
+                             unsigned long long *page_bytes)
+{
+    unsigned long long base, align_blocks, align_tokens, limit, candidate;
+    unsigned long long best = 0ull, best_score = ULLONG_MAX;
+    if (!r || !page_tokens || !page_bytes || !r->logical_block_tokens ||
+        !r->kernel_tile_tokens || !r->promotion_granularity_tokens || !r->alignment_bytes ||
+        !r->bytes_per_block)
+        return 0;
+    if (!pages_lcm(r->logical_block_tokens, r->kernel_tile_tokens, &base) ||
+        !pages_lcm(base, r->promotion_granularity_tokens, &base))
+        return 0;
+    align_blocks = r->alignment_bytes / pages_gcd(r->bytes_per_block, r->alignment_bytes);
+    if (!yvx_u64_mul(r->logical_block_tokens, align_blocks, &align_tokens) ||
+        !pages_lcm(base, align_tokens, &base))
+        return 0;
+    limit = r->device_page_bytes / r->bytes_per_block;
+    if (!yvx_u64_mul(limit, r->logical_block_tokens, &limit)) return 0;
+    limit -= limit % base;
+    if (limit < base) limit = base;
+    for (candidate = base; candidate <= limit;) {
+        unsigned long long pages, rounded, blocks, bytes, table, waste, score, spare;
+        pages = r->logical_tokens / candidate + (r->logical_tokens % candidate ? 1ull : 0ull);
+        if (!yvx_u64_mul(pages, candidate, &rounded)) return 0;
+        blocks = candidate / r->logical_block_tokens;
+        if (candidate % r->logical_block_tokens || !blocks ||
+            !yvx_u64_mul(blocks, r->bytes_per_block, &bytes))
+            return 0;
+        if (!(bytes % r->alignment_bytes)) {
+            if (!yvx_u64_mul(pages, r->page_table_entry_bytes, &table)) return 0;
+            spare = rounded - r->logical_tokens;
+            blocks = spare / r->logical_block_tokens + (spare % r->logical_block_tokens ? 1ull : 0ull);
+            if (!yvx_u64_mul(blocks, r->bytes_per_block, &waste)) return 0;
+            score = table;
+            if (!yvx_u64_add(score, waste, &score) ||
+                !yvx_u64_add(score, r->copy_on_write ? bytes : 0ull, &score) ||
+                !yvx_u64_add(score, r->candidate_extent ? waste : 0ull, &score))
+                return 0;
+            if (score < best_score || (score == best_score && candidate < best)) {
+                best_score = score;
+                best = candidate;
+            }
+        }
+        if (limit - candidate < base) break;
+        candidate += base;
+    }
+    if (!best) return 0;
+    *page_tokens = best;
+    return yvx_u64_mul(best / r->logical_block_tokens, r->bytes_per_block, page_bytes);
+}
+
+/* src/graph/state_pages.c:660-669: first = start / page, last = (end-1) / page. */
+int yvex_b200_kv_page_touch(unsigned long long element_start, unsigned long long element_count,
+                            unsigned long long page_elements, unsigned long long *first_page,
+                            unsigned long long *last_page)
+{
+    unsigned long long end;
+    if (!element_count || !page_elements || !first_page || !last_page ||
+        !yvx_u64_add(element_start, element_count, &end))
+        return 0;
+    *first_page = element_start / page_elements;
+    *last_page = (end - 1ull) / page_elements;
+    return 1;
+}
+
+/* Logical KV row -> pool row under a block table (extension). */
+unsigned long long yvex_b200_kv_block_row(const int *block_table,
+                                          unsigned long long block_tokens,
+                                          unsigned long long row)
+{
+    return (unsigned long long)block_table[row / block_tokens] * block_tokens + row % block_tokens;
+}

@@ -1,0 +1,59 @@
+/* Host-side state shared by the C11 operator files. Host code never includes
+ * a CUDA header: everything device-side goes through yvex_b200/cuda_shim.h. */
+#ifndef YVEX_B200_HOST_PRIVATE_H
+#define YVEX_B200_HOST_PRIVATE_H
+
+#include <limits.h>
+#include <stddef.h>
+
+#include "yvex_b200/attention.h"
+#include "yvex_b200/cuda_shim.h"
+
+struct yvex_backend {
+    int device, sm_count, cc_major, cc_minor;
+    char device_name[128];
+    void *own_stream, *stream;
+    int synchronous;
+    /* A failed launch or synchronisation is sticky, as in the reference
+     * (src/backend/cuda/capability.c:757-817): later operators are refused. */
+    int failed;
+    unsigned long long tensor_id_next, allocated_bytes, memory_limit_bytes, live_tensors;
+    /* Grow-only device scratch for split-KV partials; backend-owned, like the
+     * reference's transient work allocations. */
+    void *scratch;
+    unsigned long long scratch_bytes;
+    int *status_device; /* device status word the kernels publish into */
+    int *status_host;   /* pinned mirror */
+    int status_pending; /* an asynchronous operator has not been checked yet */
+};
+
+static inline int yvx_u64_add(unsigned long long a, unsigned long long b,
+                              unsigned long long *out)
+{
+    if (a > ULLONG_MAX - b) return 0;
+    *out = a + b;
+    return 1;
+}
+
+static inline int yvx_u64_mul(unsigned long long a, unsigned long long b,
+                              unsigned long long *out)
+{
+    if (a && b > ULLONG_MAX / a) return 0;
+    *out = a * b;
+    return 1;
+}
+
+int yvx_fail(yvex_error *err, yvex_status code, const char *where, const char *message);
+int yvx_backend_admit(yvex_backend *backend, const char *where, yvex_error *err);
+int yvx_backend_scratch(yvex_backend *backend, unsigned long long bytes, void **out,
+                        const char *where, yvex_error *err);
+int yvx_backend_device_fail(yvex_backend *backend, int rc, const char *where, yvex_error *err);
+/* Clears the status word before an operator and reads it back after: returns
+ * YVEX_ERR_FORMAT when a kernel published a non-finite or contract failure. */
+int yvx_backend_status_arm(yvex_backend *backend, const char *where, yvex_error *err);
+int yvx_backend_status_collect(yvex_backend *backend, yvex_backend_operation_facts *facts,
+                               const char *where, yvex_error *err);
+int yvx_tensor_owned(const yvex_backend *backend, const yvex_device_tensor *tensor);
+unsigned long long yvx_dtype_bytes(yvex_dtype dtype);
+
+#endif

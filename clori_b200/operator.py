@@ -1,0 +1,274 @@
+"""Python view of the operator interface in include/yvex_b200/attention.h.
+
+Names and argument meaning follow the reference's C interface
+(include/yvex/backend.h, include/yvex/internal/transformer.h:245-294); every
+method is one call through the C-ABI and returns the reference's status codes
+(raised as YvexError when non-zero unless `check=False`).
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import abi
+
+
+class YvexError(RuntimeError):
+    def __init__(self, code, where, message):
+        super().__init__(f"{abi.load().yvex_status_name(code).decode()} ({code}) at {where}: {message}")
+        self.code, self.where, self.message = code, where, message
+
+
+def _raise(err):
+    raise YvexError(err.code, err.where.decode(errors="replace"), err.message.decode(errors="replace"))
+
+
+def f32_to_bf16_bits(x):
+    """Round-to-nearest-even bf16 bits of a float32 array (NaNs quieted)."""
+    x = np.ascontiguousarray(x, np.float32)
+    bits = x.view(np.uint32)
+    high = bits >> 16
+    low = bits & 0xFFFF
+    nan = ((bits & 0x7F800000) == 0x7F800000) & ((bits & 0x007FFFFF) != 0)
+    up = (low > 0x8000) | ((low == 0x8000) & ((high & 1) == 1))
+    out = np.where(nan, high | 0x40, high + up.astype(np.uint32))
+    return out.astype(np.uint16)
+
+
+def bf16_bits_to_f32(bits):
+    return (np.ascontiguousarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def attention_requirement(query_tokens, key_value_tokens, query_start, query_heads,
+                          key_value_heads, head_dimension, causal=True, dtype=abi.DTYPE_F32,
+                          output_dtype=None, numeric_contract=abi.NUMERIC_EXACT_F32,
+                          query_token_stride=0, key_token_stride=0, value_token_stride=0,
+                          query_dtype=None):
+    r = abi.AttentionRequirement()
+    r.query_tokens, r.key_value_tokens, r.query_start = query_tokens, key_value_tokens, query_start
+    r.query_heads, r.key_value_heads, r.head_dimension = query_heads, key_value_heads, head_dimension
+    r.query_token_stride, r.key_token_stride, r.value_token_stride = (
+        query_token_stride, key_token_stride, value_token_stride)
+    r.query_dtype = dtype if query_dtype is None else query_dtype
+    r.key_dtype = r.value_dtype = dtype
+    r.output_dtype = dtype if output_dtype is None else output_dtype
+    r.layout = abi.LAYOUT_TOKEN_HEAD_DIM
+    r.mask = abi.MASK_CAUSAL if causal else abi.MASK_FULL
+    r.numeric_contract = numeric_contract
+    r.deterministic = 1
+    return r
+
+
+_NP_DTYPES = {abi.DTYPE_F32: np.float32, abi.DTYPE_BF16: np.uint16, abi.DTYPE_F16: np.uint16,
+              abi.DTYPE_I32: np.int32, abi.DTYPE_I8: np.int8, abi.DTYPE_I64: np.int64}
+
+
+class Tensor:
+    """A yvex_device_tensor owned by (or wrapped into) a Backend."""
+
+    def __init__(self, backend, pointer, shape, dtype):
+        self.backend, self.ptr, self.shape, self.dtype = backend, pointer, tuple(shape), dtype
+
+    @property
+    def struct(self):
+        return self.ptr.contents
+
+    @property
+    def data_ptr(self):
+        return self.ptr.contents.data
+
+    @property
+    def nbytes(self):
+        return self.ptr.contents.bytes
+
+    def write(self, array):
+        array = np.ascontiguousarray(array)
+        assert array.nbytes <= self.nbytes, (array.nbytes, self.nbytes)
+        err = abi.Error()
+        rc = self.backend.lib.yvex_backend_tensor_write(
+            self.backend.handle, self.ptr, array.ctypes.data_as(C.c_void_p), array.nbytes, C.byref(err))
+        if rc:
+            _raise(err)
+        return self
+
+    def read(self, np_dtype=None, shape=None):
+        np_dtype = np_dtype or _NP_DTYPES[self.dtype]
+        out = np.empty(self.nbytes // np.dtype(np_dtype).itemsize, np_dtype)
+        err = abi.Error()
+        rc = self.backend.lib.yvex_backend_tensor_read(
+            self.backend.handle, self.ptr, out.ctypes.data_as(C.c_void_p), out.nbytes, C.byref(err))
+        if rc:
+            _raise(err)
+        return out.reshape(shape or self.shape)
+
+    def f32_subview(self, offset, count):
+        view = abi.DeviceTensor()
+        ok = self.backend.lib.yvex_backend_tensor_f32_subview(self.ptr, offset, count, C.byref(view))
+        if not ok:
+            return None
+        return Tensor(self.backend, C.pointer(view), (count,), abi.DTYPE_F32)
+
+    def release(self):
+        if self.ptr is not None:
+            err = abi.Error()
+            handle = self.ptr
+            rc = self.backend.lib.yvex_backend_tensor_release(self.backend.handle, C.byref(handle), C.byref(err))
+            self.ptr = None
+            if rc:
+                _raise(err)
+
+
+class Backend:
+    """yvex_backend on one B200 (yvex_backend_open with kind CUDA)."""
+
+    def __init__(self, device=0, kind=abi.BACKEND_KIND_CUDA):
+        self.lib = abi.load()
+        self.handle = C.c_void_p()
+        options = abi.BackendOptions(kind, str(device).encode(), 0)
+        err = abi.Error()
+        rc = self.lib.yvex_backend_open(C.byref(self.handle), C.byref(options), C.byref(err))
+        if rc:
+            _raise(err)
+        self.device = device
+        self._tensors = []
+
+    # -- tensors -------------------------------------------------------------
+    def _desc(self, name, dtype, shape, nbytes=None):
+        desc = abi.TensorDesc()
+        desc.name = name.encode()
+        desc.dtype = dtype
+        desc.rank = len(shape)
+        for i, d in enumerate(shape):
+            desc.dims[i] = int(d)
+        desc.bytes = int(nbytes if nbytes is not None else int(np.prod(shape)) * abi.DTYPE_BYTES[dtype])
+        return desc
+
+    def alloc(self, name, dtype, shape, nbytes=None):
+        desc = self._desc(name, dtype, shape, nbytes)
+        ptr = C.POINTER(abi.DeviceTensor)()
+        err = abi.Error()
+        rc = self.lib.yvex_backend_tensor_alloc(self.handle, C.byref(desc), C.byref(ptr), C.byref(err))
+        if rc:
+            _raise(err)
+        t = Tensor(self, ptr, shape, dtype)
+        self._tensors.append(t)
+        return t
+
+    def wrap(self, name, dtype, shape, device_pointer, nbytes=None):
+        desc = self._desc(name, dtype, shape, nbytes)
+        ptr = C.POINTER(abi.DeviceTensor)()
+        err = abi.Error()
+        rc = self.lib.yvex_b200_tensor_wrap(self.handle, C.byref(desc), C.c_void_p(device_pointer),
+                                            C.byref(ptr), C.byref(err))
+        if rc:
+            _raise(err)
+        t = Tensor(self, ptr, shape, dtype)
+        self._tensors.append(t)
+        return t
+
+    def tensor(self, name, array, dtype=None):
+        """Allocate a tensor shaped like `array` and upload it."""
+        array = np.ascontiguousarray(array)
+        if dtype is None:
+            dtype = {np.dtype(np.float32): abi.DTYPE_F32, np.dtype(np.uint16): abi.DTYPE_BF16,
+                     np.dtype(np.int32): abi.DTYPE_I32, np.dtype(np.int8): abi.DTYPE_I8}[array.dtype]
+        return self.alloc(name, dtype, array.shape, array.nbytes).write(array)
+
+    # -- operators -----------------------------------------------------------
+    def attention_workspace_required(self, requirement, check=True):
+        ops = self.lib.yvex_b200_transformer_operations_get(self.handle)
+        nbytes = abi.u64(2**64 - 1)
+        err = abi.Error()
+        rc = ops.contents.attention_workspace_required(C.byref(requirement), C.byref(nbytes), C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc, nbytes.value
+
+    def attention_execute(self, requirement, query, key, value, output, check=True):
+        """operations->attention_execute(backend, request, facts, err)."""
+        ops = self.lib.yvex_b200_transformer_operations_get(self.handle)
+        request = abi.AttentionRequest()
+        request.requirement = requirement
+        request.query = query.ptr if query is not None else None
+        request.key = key.ptr if key is not None else None
+        request.value = value.ptr if value is not None else None
+        request.output = output.ptr if output is not None else None
+        facts = abi.OperationFacts()
+        err = abi.Error()
+        rc = ops.contents.attention_execute(self.handle, C.byref(request), C.byref(facts), C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc, facts
+
+    def attention_batch_execute(self, requirement, query, key, value, kv_tokens, output,
+                                block_table=None, block_tokens=0, max_blocks_per_session=0,
+                                kv_session_stride=0, kv_block_stride=0, kv_head_stride=0,
+                                check=True):
+        request = abi.BatchRequest()
+        request.requirement = requirement
+        request.session_count = kv_tokens.shape[0]
+        request.kv_layout = abi.KV_BLOCK_TABLE if block_table is not None else abi.KV_CONTIGUOUS
+        request.query, request.key, request.value = query.ptr, key.ptr, value.ptr
+        request.kv_tokens = kv_tokens.ptr
+        request.block_table = block_table.ptr if block_table is not None else None
+        request.block_tokens = block_tokens
+        request.max_blocks_per_session = max_blocks_per_session
+        request.kv_session_stride = kv_session_stride
+        request.kv_block_stride = kv_block_stride
+        request.kv_head_stride = kv_head_stride
+        request.output = output.ptr
+        facts = abi.OperationFacts()
+        err = abi.Error()
+        rc = self.lib.yvex_b200_attention_batch_execute(self.handle, C.byref(request), C.byref(facts), C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc, facts
+
+    def op_attention(self, query, keys, values, seq_len, position, scale, causal, scores,
+                     probabilities, out, check=True):
+        err = abi.Error()
+        rc = self.lib.yvex_backend_op_attention(
+            self.handle, query.ptr, keys.ptr, values.ptr, seq_len, position, scale, int(causal),
+            scores.ptr, probabilities.ptr, out.ptr, C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc
+
+    # -- lifecycle -----------------------------------------------------------
+    def bind_stream(self, stream, synchronous=True):
+        err = abi.Error()
+        rc = self.lib.yvex_b200_backend_bind_stream(self.handle, C.c_void_p(stream), int(synchronous), C.byref(err))
+        if rc:
+            _raise(err)
+
+    @property
+    def stream(self):
+        return self.lib.yvex_b200_backend_stream(self.handle)
+
+    @property
+    def sm_count(self):
+        return self.lib.yvex_b200_backend_sm_count(self.handle)
+
+    def sync(self, check=True):
+        err = abi.Error()
+        rc = self.lib.yvex_backend_sync(self.handle, C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc
+
+    def close(self):
+        if self.handle:
+            for t in self._tensors:
+                if t.ptr is not None:
+                    t.release()
+            self._tensors = []
+            err = abi.Error()
+            rc = self.lib.yvex_backend_close_checked(C.byref(self.handle), C.byref(err))
+            if rc:
+                _raise(err)
+            self.handle = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

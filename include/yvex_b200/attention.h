@@ -1,0 +1,166 @@
+/* Operator-level C-ABI of the B200 attention drop-in (libyvex_b200.so).
+ *
+ * These are the entry points the YVEX reference runtime binds for its
+ * attention hot path, with the reference's names, argument meaning and error
+ * behaviour; the citation beside each names the reference declaration it
+ * replaces. Functions without a counterpart in the reference say so.
+ *
+ * There is no CPU backend behind this library and no fallback of any kind: if
+ * no sm_100 device is usable, opening a backend fails and every operator
+ * refuses with YVEX_ERR_UNSUPPORTED or YVEX_ERR_BACKEND.
+ */
+#ifndef YVEX_B200_ATTENTION_H
+#define YVEX_B200_ATTENTION_H
+
+#include "yvex_b200/abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error helpers: include/yvex/core.h:42-48 ---------------------------- */
+void yvex_error_clear(yvex_error *err);
+void yvex_error_set(yvex_error *err, yvex_status code, const char *where, const char *message);
+const char *yvex_status_name(yvex_status status);
+
+/* ---- backend lifecycle and tensors: include/yvex/backend.h:148-206 -------- */
+typedef enum {
+    YVEX_BACKEND_KIND_CPU = 0,
+    YVEX_BACKEND_KIND_CUDA,
+    YVEX_BACKEND_KIND_METAL,
+    YVEX_BACKEND_KIND_ROCM
+} yvex_backend_kind;
+
+typedef struct {
+    yvex_backend_kind kind;
+    const char *device;                 /* decimal device index, NULL = "0" */
+    unsigned long long memory_limit_bytes;
+} yvex_backend_options;
+
+/* Only YVEX_BACKEND_KIND_CUDA opens; every other kind is refused with
+ * YVEX_ERR_UNSUPPORTED (the reference's CPU backend has no exact-attention
+ * table either: src/runtime/stateful_attention.c:294-298). */
+int yvex_backend_open(yvex_backend **out, const yvex_backend_options *options, yvex_error *err);
+int yvex_backend_close_checked(yvex_backend **backend, yvex_error *err);
+void yvex_backend_close(yvex_backend *backend);
+int yvex_backend_cuda_available(void);
+int yvex_backend_sync(yvex_backend *backend, yvex_error *err);
+
+int yvex_backend_tensor_alloc(yvex_backend *backend, const yvex_backend_tensor_desc *desc,
+                              yvex_device_tensor **out, yvex_error *err);
+int yvex_backend_tensor_release(yvex_backend *backend, yvex_device_tensor **tensor,
+                                yvex_error *err);
+void yvex_backend_tensor_free(yvex_backend *backend, yvex_device_tensor *tensor);
+int yvex_backend_tensor_write(yvex_backend *backend, yvex_device_tensor *tensor,
+                              const void *src, unsigned long long len, yvex_error *err);
+int yvex_backend_tensor_read(yvex_backend *backend, const yvex_device_tensor *tensor,
+                             void *dst, unsigned long long len, yvex_error *err);
+int yvex_backend_tensor_zero(yvex_backend *backend, yvex_device_tensor *tensor, yvex_error *err);
+/* include/yvex/internal/backend.h:258-260: an F32 window [offset, offset+count)
+ * of a tensor, sharing its storage. Returns 1 on success, 0 on refusal. */
+int yvex_backend_tensor_f32_subview(const yvex_device_tensor *source, unsigned long long offset,
+                                    unsigned long long count, yvex_device_tensor *view);
+/* No counterpart in the reference: wraps device memory the caller owns (for
+ * instance a KV bank of the reference's state residency, or a framework
+ * allocation) as a borrowed tensor of this backend. The wrapper is released
+ * with yvex_backend_tensor_release; the memory is never freed by the library. */
+int yvex_b200_tensor_wrap(yvex_backend *backend, const yvex_backend_tensor_desc *desc,
+                          void *device_pointer, yvex_device_tensor **out, yvex_error *err);
+/* No counterpart in the reference: binds the backend's operations to a CUDA
+ * stream the caller owns (cudaStream_t as void*); NULL restores the backend's
+ * own stream. `synchronous` = 0 makes operators return after enqueueing (the
+ * status word is then checked by yvex_backend_sync). */
+int yvex_b200_backend_bind_stream(yvex_backend *backend, void *stream, int synchronous,
+                                  yvex_error *err);
+void *yvex_b200_backend_stream(const yvex_backend *backend);
+int yvex_b200_backend_sm_count(const yvex_backend *backend);
+
+/* ---- exact attention operator: include/yvex/internal/transformer.h:291-294,
+ * reached through yvex_backend_transformer_operations_get() in the reference
+ * (src/backend/core.c:118; CUDA table src/backend/cuda/capability.c:21-42).
+ * Implementation replaced: src/backend/cuda/exact_attention.c:55-108. ------- */
+typedef struct yvex_b200_transformer_operations {
+    int (*attention_workspace_required)(const yvex_transformer_attention_requirement *,
+                                        unsigned long long *, yvex_error *);
+    int (*attention_execute)(yvex_backend *, const yvex_transformer_attention_request *,
+                             yvex_backend_operation_facts *, yvex_error *);
+} yvex_b200_transformer_operations;
+
+const yvex_b200_transformer_operations *yvex_b200_transformer_operations_get(
+    const yvex_backend *backend);
+int yvex_b200_transformer_attention_workspace_required(
+    const yvex_transformer_attention_requirement *requirement, unsigned long long *bytes,
+    yvex_error *err);
+int yvex_b200_transformer_attention_execute(yvex_backend *backend,
+                                            const yvex_transformer_attention_request *request,
+                                            yvex_backend_operation_facts *facts,
+                                            yvex_error *err);
+
+/* ---- single-head primitive: include/yvex/backend.h:249-260 ---------------- */
+int yvex_backend_op_attention(yvex_backend *backend, const yvex_device_tensor *query,
+                              const yvex_device_tensor *keys, const yvex_device_tensor *values,
+                              unsigned long long seq_len, unsigned long long position,
+                              float scale, int causal, yvex_device_tensor *score_scratch,
+                              yvex_device_tensor *probability_scratch, yvex_device_tensor *out,
+                              yvex_error *err);
+
+/* ---- batched attention over session KV caches (extension) ------------------
+ * No counterpart in the reference, whose operator has no batch dimension, no
+ * bf16 or Q8_0 KV and no block table. Per session the semantics are exactly
+ * those of the exact attention operator above with query_start = kv length -
+ * query rows (decode: 1 row; speculative verify: 2..8 rows, causal among
+ * themselves). Unknown combinations are refused with YVEX_ERR_UNSUPPORTED. */
+typedef enum {
+    YVEX_B200_KV_CONTIGUOUS = 0, /* [session][token][kv_head*head_dim], strided */
+    YVEX_B200_KV_BLOCK_TABLE = 1 /* pool of fixed-size token blocks + int32 table */
+} yvex_b200_kv_layout;
+
+typedef struct yvex_b200_attention_batch_request {
+    /* heads, head_dimension, dtypes, mask, numeric_contract, deterministic are
+     * read from here; query_tokens = rows per session; key_value_tokens = the
+     * largest session length; query_start is ignored (taken from the end). */
+    yvex_transformer_attention_requirement requirement;
+    unsigned long long session_count;
+    yvex_b200_kv_layout kv_layout;
+    const yvex_device_tensor *query;   /* [session][row][query_heads*head_dim] */
+    const yvex_device_tensor *key, *value; /* contiguous sessions or the pools */
+    const yvex_device_tensor *kv_tokens;   /* I32 [session]: length of each session */
+    const yvex_device_tensor *block_table; /* I32 [session][max_blocks]; block layout only */
+    unsigned long long block_tokens;       /* tokens per pool block (64) */
+    unsigned long long max_blocks_per_session;
+    /* element strides; zero selects the packed default of the layout */
+    unsigned long long kv_session_stride;  /* contiguous: elements between sessions */
+    unsigned long long kv_block_stride;    /* block layout: elements between pool blocks */
+    unsigned long long kv_head_stride;     /* elements between kv heads (default head_dim) */
+    yvex_device_tensor *output;            /* [session][row][query_heads*head_dim] */
+} yvex_b200_attention_batch_request;
+
+int yvex_b200_attention_batch_execute(yvex_backend *backend,
+                                      const yvex_b200_attention_batch_request *request,
+                                      yvex_backend_operation_facts *facts, yvex_error *err);
+
+/* ---- KV block and page indexing (integer, bit-exact) ------------------------
+ * Page geometry follows include/yvex/internal/deployment.h:112-132 and
+ * src/deployment/plan.c:208-283; page touch follows
+ * src/graph/state_pages.c:660-669. The block-row map is this library's
+ * extension (the reference keeps KV contiguous in virtual address space). */
+typedef struct {
+    unsigned long long logical_block_tokens, kernel_tile_tokens;
+    unsigned long long promotion_granularity_tokens, alignment_bytes;
+    unsigned long long bytes_per_block, page_table_entry_bytes;
+    unsigned long long device_page_bytes, logical_tokens;
+    int copy_on_write, candidate_extent;
+} yvex_b200_page_request;
+int yvex_b200_kv_page_tokens(const yvex_b200_page_request *request,
+                             unsigned long long *page_tokens, unsigned long long *page_bytes);
+int yvex_b200_kv_page_touch(unsigned long long element_start, unsigned long long element_count,
+                            unsigned long long page_elements, unsigned long long *first_page,
+                            unsigned long long *last_page);
+unsigned long long yvex_b200_kv_block_row(const int *block_table,
+                                          unsigned long long block_tokens,
+                                          unsigned long long row);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YVEX_B200_ATTENTION_H */

@@ -1,0 +1,123 @@
+/* Thin C-ABI over the sm_100a attention kernels.
+ *
+ * Plain pointers and sizes only. Host code (C11) includes this header and never
+ * a CUDA header, the same rule the reference keeps between its host code and
+ * its driver shim (src/backend/cuda/private.h:16-21). Every function returns 0
+ * on success or a negative yvex_status; device pointers are raw addresses and
+ * `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ *
+ * Each launch entry replaces one launch site of the reference, named beside it.
+ */
+#ifndef YVEX_B200_CUDA_SHIM_H
+#define YVEX_B200_CUDA_SHIM_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- device runtime plumbing (reference: src/backend/cuda/backend.c open,
+ * alloc, copy and synchronize paths) ------------------------------------- */
+int yvx_cuda_device_count(int *count);
+int yvx_cuda_device_select(int device);
+int yvx_cuda_device_properties(int device, int *sm_count, int *cc_major, int *cc_minor,
+                               unsigned long long *global_bytes, char *name, size_t name_cap);
+int yvx_cuda_malloc(void **out, unsigned long long bytes);
+int yvx_cuda_free(void *pointer);
+int yvx_cuda_host_alloc(void **out, unsigned long long bytes);
+int yvx_cuda_host_free(void *pointer);
+int yvx_cuda_memset_async(void *device, int value, unsigned long long bytes, void *stream);
+int yvx_cuda_upload_async(void *device, const void *host, unsigned long long bytes, void *stream);
+int yvx_cuda_download_async(void *host, const void *device, unsigned long long bytes, void *stream);
+int yvx_cuda_copy_async(void *destination, const void *source, unsigned long long bytes, void *stream);
+int yvx_cuda_stream_create(void **stream);
+int yvx_cuda_stream_destroy(void *stream);
+int yvx_cuda_stream_synchronize(void *stream);
+int yvx_cuda_event_create(void **event);
+int yvx_cuda_event_destroy(void *event);
+int yvx_cuda_event_record(void *event, void *stream);
+int yvx_cuda_event_elapsed_ms(void *start, void *stop, float *milliseconds);
+const char *yvx_cuda_last_error_text(void);
+
+/* ---- grouped-query attention over a KV cache ------------------------------
+ * Replaces the launch of yvex_gqa_f32 / yvex_gqa_wide_f32
+ * (src/backend/cuda/transformer.c:787-806, kernels in
+ * src/backend/cuda/transformer_kernels.cu:137-238) and the tiled MHA sequence
+ * (src/backend/cuda/transformer.c:493-677). One description covers decode
+ * (1 row), speculative verify (2..8 rows) and general causal/full attention,
+ * over one session or a batch, with contiguous strided KV rows or a block
+ * table over a shared pool.
+ *
+ *   O[b,t,h,:] = softmax_s( scale * Q[b,t,h,:] . K[b,s,h/g,:] ) V[b,s,h/g,:]
+ *   causal: s visible iff  kv_position_base + s <= query_start[b] + t
+ *
+ * All strides are in ELEMENTS of the tensor's dtype. */
+typedef struct yvx_gqa_problem {
+    unsigned int sessions;        /* batch of independent sessions */
+    unsigned int query_rows;      /* query rows per session (uniform) */
+    unsigned int query_heads, kv_heads, head_dim;
+    unsigned int causal;          /* 0 = full, 1 = causal */
+    float scale;
+    int query_dtype, kv_dtype, output_dtype; /* yvex_dtype ids */
+
+    const void *query;            /* [session][row][query_heads*head_dim] */
+    unsigned long long query_row_stride, query_session_stride;
+    void *output;                 /* packed [session][row][query_heads*head_dim] */
+
+    const void *key, *value;      /* session 0 / pool block 0, token 0, head 0 */
+    unsigned long long key_token_stride, value_token_stride;
+    unsigned long long key_head_stride, value_head_stride;
+    unsigned long long key_session_stride, value_session_stride; /* contiguous layout */
+    const int *block_table;       /* device [sessions][block_table_stride]; NULL = contiguous */
+    unsigned int block_tokens, block_table_stride;
+    unsigned int pool_blocks;     /* table entries outside [0, pool_blocks) are a contract failure */
+    unsigned long long key_block_stride, value_block_stride;
+
+    const unsigned int *kv_tokens;   /* device [sessions]; NULL = uniform */
+    unsigned int kv_tokens_uniform;
+    unsigned int kv_tokens_max;      /* host-side upper bound of every length */
+    const unsigned int *query_start; /* device [sessions]; NULL = uniform / from end */
+    unsigned int query_start_uniform;
+    unsigned int query_start_from_end; /* 1: query_start = kv length - query_rows */
+    unsigned int kv_position_base;   /* absolute position of local KV token 0 */
+
+    unsigned int chunk_tokens;       /* KV tokens per split; multiple of 64 */
+    unsigned int max_splits;         /* ceil(kv_tokens_max / chunk_tokens) */
+    float *partials;                 /* scratch [session][row][qhead][split][head_dim+2] */
+    float *partial_output;           /* non-NULL: emit (o, m, l) per (session,row,qhead)
+                                        instead of the final output: [..][head_dim+2] */
+    int *status;                     /* device status word; 0 ok, 1 non-finite, 2 contract */
+} yvx_gqa_problem;
+
+/* Scratch bytes `partials` must hold for a problem (0 when one split suffices). */
+unsigned long long yvx_cuda_gqa_partials_bytes(const yvx_gqa_problem *problem);
+/* Picks chunk_tokens/max_splits for a device with `sm_count` SMs. Deterministic
+ * in the problem's shape only. */
+void yvx_cuda_gqa_plan_splits(yvx_gqa_problem *problem, int sm_count);
+/* Launches the attention (1 launch) and, when max_splits > 1, the combine
+ * (1 more). `launches` receives the number of kernels enqueued. */
+int yvx_cuda_gqa_attention(const yvx_gqa_problem *problem, void *stream,
+                           unsigned int *launches);
+
+/* ---- log-sum-exp combine of partial results ---------------------------------
+ * parts: [items][part_count][head_dim + 2] holding (o normalised, m, l).
+ * Used after the cross-GPU all-gather of sequence-sharded partials. No
+ * counterpart in the reference (it has no split or sharded attention). */
+int yvx_cuda_lse_combine(const float *parts, unsigned int items, unsigned int part_count,
+                         unsigned int head_dim, void *output, int output_dtype,
+                         int *status, void *stream);
+
+/* ---- single-head primitive (reference: yvex_attention_f32,
+ * src/backend/cuda/kernels.cu:362-434, launched from
+ * src/backend/cuda/ops.c:1717-1808) ----------------------------------------- */
+int yvx_cuda_op_attention_f32(const float *query, const float *keys, const float *values,
+                              unsigned long long seq_len, unsigned long long position,
+                              float scale, int causal, unsigned long long head_dim,
+                              float *scores, float *probabilities, float *out,
+                              void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* YVEX_B200_CUDA_SHIM_H */

@@ -1,0 +1,132 @@
+"""The C-ABI library loads without a GPU and exports every declared symbol;
+host-side logic that needs no device (page and block indexing, admission
+errors raised before any device call) behaves as the reference's."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+import clori_b200
+from clori_b200 import abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    names = set()
+    pattern = re.compile(r"^\s*(?:const\s+)?[A-Za-z_][\w\s\*]*?\b(yv(?:ex|x)_\w+)\s*\(", re.M)
+    for header in ("attention.h", "cuda_shim.h"):
+        text = open(os.path.join(ROOT, "include", "yvex_b200", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        for m in pattern.finditer(text):
+            names.add(m.group(1))
+    return names
+
+
+def test_library_exports_every_declared_symbol(library):
+    declared = _declared_functions()
+    assert len(declared) >= 45
+    missing = [n for n in sorted(declared) if not hasattr(library, n)]
+    assert not missing, missing
+    assert set(abi.EXPORTED_SYMBOLS) >= declared
+
+
+def test_struct_sizes_match_the_reference_abi():
+    # include/yvex/core.h: code + 96 + 256; include/yvex/internal/backend.h:215-228
+    assert C.sizeof(abi.Error) == 356
+    assert C.sizeof(abi.DeviceTensor) == 152
+    assert C.sizeof(abi.OperationFacts) == 13 * 8 + 8
+    assert C.sizeof(abi.AttentionRequirement) == 9 * 8 + 8 * 4
+    assert C.sizeof(abi.AttentionRequest) == C.sizeof(abi.AttentionRequirement) + 4 * 8
+
+
+def test_open_refuses_without_a_fallback(library):
+    err = abi.Error()
+    handle = C.c_void_p()
+    options = abi.BackendOptions(abi.BACKEND_KIND_CPU, None, 0)
+    rc = library.yvex_backend_open(C.byref(handle), C.byref(options), C.byref(err))
+    assert rc == abi.YVEX_ERR_UNSUPPORTED and not handle.value
+    assert b"no CPU fallback" in err.message
+
+
+def test_workspace_admission_codes(library):
+    # src/backend/cuda/exact_attention.c:8-53 refusal order.
+    def ask(**changes):
+        r = clori_b200.attention_requirement(2, 4, 2, 8, 2, 128)
+        for k, v in changes.items():
+            setattr(r, k, v)
+        nbytes = abi.u64(123)
+        err = abi.Error()
+        rc = library.yvex_b200_transformer_attention_workspace_required(
+            C.byref(r), C.byref(nbytes), C.byref(err))
+        return rc, nbytes.value
+    assert ask() == (abi.YVEX_OK, 0)
+    assert ask(query_start=3)[0] == abi.YVEX_ERR_INVALID_ARG      # query range beyond KV
+    assert ask(query_heads=7)[0] == abi.YVEX_ERR_INVALID_ARG      # not a multiple of KV heads
+    assert ask(value_token_stride=255)[0] == abi.YVEX_ERR_INVALID_ARG
+    assert ask(head_dimension=257)[0] == abi.YVEX_ERR_UNSUPPORTED
+    assert ask(output_dtype=abi.DTYPE_BF16)[0] == abi.YVEX_ERR_UNSUPPORTED
+    assert ask(deterministic=0)[0] == abi.YVEX_ERR_UNSUPPORTED
+    assert ask(numeric_contract=abi.NUMERIC_BF16_F32_ACCUMULATE)[0] == abi.YVEX_ERR_UNSUPPORTED
+    assert ask(mask=0)[0] == abi.YVEX_ERR_UNSUPPORTED
+
+
+def test_page_geometry_matches_reference_fixtures(library):
+    # tests/unit/runtime_execution.c:203-279 expectations of the capacity plan.
+    def page(**kw):
+        r = abi.PageRequest()
+        base = dict(logical_block_tokens=1, kernel_tile_tokens=1, promotion_granularity_tokens=1,
+                    alignment_bytes=256, bytes_per_block=256, page_table_entry_bytes=16,
+                    device_page_bytes=65536, logical_tokens=131072)
+        base.update(kw)
+        for k, v in base.items():
+            setattr(r, k, v)
+        tokens, nbytes = abi.u64(), abi.u64()
+        assert library.yvex_b200_kv_page_tokens(C.byref(r), C.byref(tokens), C.byref(nbytes))
+        return tokens.value, nbytes.value
+    assert page(bytes_per_block=4096, logical_tokens=128) == (16, 65536)
+    assert page(logical_block_tokens=8, kernel_tile_tokens=8, bytes_per_block=4096)[0] == 128
+    assert page(bytes_per_block=32768, promotion_granularity_tokens=6, logical_tokens=5,
+                candidate_extent=1)[0] == 6
+    assert page(bytes_per_block=4104, logical_tokens=128, device_page_bytes=4096) == (32, 131328)
+    # tests/unit/runtime_state.c:2069-2105: page_bytes = page_tokens / block * bytes_per_block
+    for block, tokens in ((1, 16), (128, 128), (128, 256)):
+        assert tokens // block * 4096 == {16: 65536, 128: 4096, 256: 8192}[tokens]
+
+
+def test_page_and_block_indexing_equal_the_oracle(library, oracle):
+    rng = np.random.default_rng(3)
+    for _ in range(200):
+        start, count, page = int(rng.integers(0, 10**6)), int(rng.integers(1, 10**4)), int(rng.integers(1, 5000))
+        first, last = abi.u64(), abi.u64()
+        assert library.yvex_b200_kv_page_touch(start, count, page, C.byref(first), C.byref(last))
+        assert (first.value, last.value) == oracle.page_touch(start, count, page)
+    assert not library.yvex_b200_kv_page_touch(1, 0, 4, C.byref(first), C.byref(last))
+    table = rng.permutation(500).astype(np.int32)
+    ptr = table.ctypes.data_as(C.POINTER(C.c_int))
+    for row in rng.integers(0, 500 * 64, 300):
+        assert library.yvex_b200_kv_block_row(ptr, 64, int(row)) == oracle.block_row(table, 64, int(row))
+
+
+def test_split_plan_is_deterministic_and_bounded(library):
+    p = abi.GqaProblem()
+    p.sessions, p.kv_heads, p.kv_tokens_max, p.query_rows, p.query_heads, p.head_dim = 1, 8, 4096, 1, 32, 128
+    library.yvx_cuda_gqa_plan_splits(C.byref(p), 148)
+    assert (p.chunk_tokens, p.max_splits) == (64, 64)
+    p.sessions, p.kv_tokens_max = 64, 32768
+    library.yvx_cuda_gqa_plan_splits(C.byref(p), 148)
+    assert p.chunk_tokens == 1024 and p.max_splits == 32
+    assert library.yvx_cuda_gqa_partials_bytes(C.byref(p)) == 64 * 32 * 32 * 130 * 4
+    p.sessions, p.kv_tokens_max = 1, 3
+    library.yvx_cuda_gqa_plan_splits(C.byref(p), 148)
+    assert p.max_splits == 1 and library.yvx_cuda_gqa_partials_bytes(C.byref(p)) == 0
+
+
+def test_bf16_helpers_equal_the_oracle(oracle):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal(5000).astype(np.float32) * np.float32(10.0) ** rng.integers(-20, 20, 5000).astype(np.float32)
+    x[:4] = [np.nan, np.inf, -np.inf, -0.0]
+    bits, widened = oracle.bf16_round(x)
+    assert np.array_equal(clori_b200.f32_to_bf16_bits(x), bits)
+    assert np.array_equal(clori_b200.bf16_bits_to_f32(bits).view(np.uint32), widened.view(np.uint32))
