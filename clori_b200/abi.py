@@ -162,7 +162,8 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
-    "yvx_cuda_lse_combine", "yvx_cuda_op_attention_f32",
+    "yvx_cuda_lse_combine", "yvx_cuda_op_attention_f32", "yvx_cuda_gqa_attention_profiled",
+    "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
 ]
 
 _lib = None
@@ -235,6 +236,10 @@ def load():
     lib.yvx_cuda_gqa_plan_splits.restype = None
     lib.yvx_cuda_gqa_plan_splits.argtypes = [P(GqaProblem), C.c_int]
     lib.yvx_cuda_gqa_attention.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
+    lib.yvx_cuda_gqa_attention_profiled.argtypes = [P(GqaProblem), vp, vp * 3, P(C.c_uint)]
+    lib.yvx_cuda_fill_normal.argtypes = [vp, C.c_int, u64, u64, C.c_float, vp]
+    lib.yvx_cuda_fill_q8_lanes.argtypes = [vp, u64, u64, vp]
+    lib.yvx_cuda_fill_f16_uniform.argtypes = [vp, u64, u64, C.c_float, C.c_float, vp]
     lib.yvx_cuda_lse_combine.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, C.c_int, vp, vp]
     _lib = lib
     return lib

@@ -2,7 +2,8 @@
 #include "common.cuh"
 
 namespace yvx {
-int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, unsigned int *launches);
+int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, cudaEvent_t *events,
+                       unsigned int *launches);
 }
 
 extern "C" {
@@ -33,7 +34,8 @@ unsigned long long yvx_cuda_gqa_partials_bytes(const yvx_gqa_problem *p)
            (p->head_dim + 2ull) * sizeof(float);
 }
 
-int yvx_cuda_gqa_attention(const yvx_gqa_problem *p, void *stream, unsigned int *launches)
+static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *events,
+                      unsigned int *launches)
 {
     unsigned int count = 0;
     if (launches) *launches = 0;
@@ -42,9 +44,22 @@ int yvx_cuda_gqa_attention(const yvx_gqa_problem *p, void *stream, unsigned int 
         p->query_heads % p->kv_heads || !p->head_dim || !p->chunk_tokens || !p->max_splits ||
         (p->max_splits > 1u && !p->partials) || (p->block_table && !p->block_tokens))
         return YVEX_ERR_INVALID_ARG;
-    int rc = yvx::gqa_generic_launch(*p, (cudaStream_t)stream, &count);
+    int rc = yvx::gqa_generic_launch(*p, (cudaStream_t)stream, events, &count);
     if (launches) *launches = count;
     return rc;
+}
+
+int yvx_cuda_gqa_attention(const yvx_gqa_problem *p, void *stream, unsigned int *launches)
+{
+    return gqa_launch(p, stream, nullptr, launches);
+}
+
+int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *p, void *stream, void *events[3],
+                                    unsigned int *launches)
+{
+    if (!events || !events[0] || !events[1] || !events[2]) return YVEX_ERR_INVALID_ARG;
+    cudaEvent_t typed[3] = {(cudaEvent_t)events[0], (cudaEvent_t)events[1], (cudaEvent_t)events[2]};
+    return gqa_launch(p, stream, typed, launches);
 }
 
 }  // extern "C"

@@ -324,10 +324,12 @@ static int launch_generic_slots(const yvx_gqa_problem &p, cudaStream_t stream)
     return launch_generic<QT, KT, 8>(p, stream);
 }
 
-int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, unsigned int *launches)
+int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, cudaEvent_t *events,
+                       unsigned int *launches)
 {
     int rc;
     if (p.head_dim == 0u || p.head_dim > 256u) return YVEX_ERR_UNSUPPORTED;
+    if (events) cudaEventRecord(events[0], stream);
     if (p.query_dtype == YVEX_DTYPE_F32 && p.kv_dtype == YVEX_DTYPE_F32)
         rc = launch_generic_slots<float, float>(p, stream);
     else if (p.query_dtype == YVEX_DTYPE_BF16 && p.kv_dtype == YVEX_DTYPE_BF16)
@@ -338,6 +340,7 @@ int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, unsigned i
         return YVEX_ERR_UNSUPPORTED;
     if (rc != 0) return rc;
     *launches = 1u;
+    if (events) cudaEventRecord(events[1], stream);
     if (p.max_splits > 1u) {
         const unsigned long long items =
             (unsigned long long)p.sessions * p.query_rows * p.query_heads;
@@ -346,6 +349,7 @@ int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, unsigned i
         if (rc != 0) return rc;
         *launches = 2u;
     }
+    if (events) cudaEventRecord(events[2], stream);
     return 0;
 }
 

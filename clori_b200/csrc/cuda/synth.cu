@@ -1,0 +1,108 @@
+// Device-side seeded fills for the benchmark workloads: the full-size KV pools
+// are several GB, so they are generated where they live. Counter-based
+// (splitmix64 of seed and element index), hence independent of launch shape.
+#include "common.cuh"
+
+namespace yvx {
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+// Box-Muller on two 32-bit uniforms drawn from one 64-bit hash; each thread
+// produces the pair (2i, 2i+1).
+__global__ void fill_normal_kernel(void *dst, int dtype, unsigned long long count,
+                                   unsigned long long seed, float sigma)
+{
+    const unsigned long long pair =
+        (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = pair; i * 2ull < count; i += stride) {
+        const uint64_t h = splitmix64(seed * 0xD1342543DE82EF95ull + i);
+        const float u1 = ((float)(uint32_t)(h >> 32) + 1.0f) * (1.0f / 4294967296.0f);
+        const float u2 = (float)(uint32_t)h * (1.0f / 4294967296.0f);
+        const float radius = sqrtf(-2.0f * logf(u1)) * sigma;
+        float s, c;
+        sincospif(2.0f * u2, &s, &c);
+        const float a = radius * c, b = radius * s;
+        if (dtype == YVEX_DTYPE_BF16) {
+            unsigned short *out = reinterpret_cast<unsigned short *>(dst);
+            out[2 * i] = bf16_bits_rne(a);
+            if (2 * i + 1 < count) out[2 * i + 1] = bf16_bits_rne(b);
+        } else {
+            float *out = reinterpret_cast<float *>(dst);
+            out[2 * i] = a;
+            if (2 * i + 1 < count) out[2 * i + 1] = b;
+        }
+    }
+}
+
+// int8 lanes uniform in [-127, 127].
+__global__ void fill_lanes_kernel(signed char *dst, unsigned long long count,
+                                  unsigned long long seed)
+{
+    const unsigned long long start =
+        ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) * 8ull;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x * 8ull;
+    for (unsigned long long i = start; i < count; i += stride) {
+        uint64_t h = splitmix64(seed * 0xD1342543DE82EF95ull + i);
+        for (int j = 0; j < 8 && i + j < count; ++j) {
+            // 255 values from one byte-sized draw; 0xFF re-hashes to stay uniform.
+            uint32_t byte = (uint32_t)(h >> (8 * j)) & 0xffu;
+            uint64_t again = h;
+            while (byte == 255u) {
+                again = splitmix64(again + j + 1);
+                byte = (uint32_t)again & 0xffu;
+            }
+            dst[i + j] = (signed char)((int)byte - 127);
+        }
+    }
+}
+
+// f16 scales uniform in [lo, hi).
+__global__ void fill_scales_kernel(__half *dst, unsigned long long count,
+                                   unsigned long long seed, float lo, float hi)
+{
+    const unsigned long long start = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = start; i < count; i += stride) {
+        const uint64_t h = splitmix64(seed * 0xD1342543DE82EF95ull + i);
+        const float u = (float)(uint32_t)(h >> 32) * (1.0f / 4294967296.0f);
+        dst[i] = __float2half_rn(lo + (hi - lo) * u);
+    }
+}
+
+}  // namespace yvx
+
+extern "C" {
+
+int yvx_cuda_fill_normal(void *dst, int dtype, unsigned long long count,
+                         unsigned long long seed, float sigma, void *stream)
+{
+    if (!dst || !count || (dtype != YVEX_DTYPE_F32 && dtype != YVEX_DTYPE_BF16))
+        return YVEX_ERR_INVALID_ARG;
+    yvx::fill_normal_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(dst, dtype, count, seed, sigma);
+    return yvx_cuda_check(cudaGetLastError(), "fill_normal_kernel");
+}
+
+int yvx_cuda_fill_q8_lanes(void *dst, unsigned long long count, unsigned long long seed,
+                           void *stream)
+{
+    if (!dst || !count) return YVEX_ERR_INVALID_ARG;
+    yvx::fill_lanes_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((signed char *)dst, count, seed);
+    return yvx_cuda_check(cudaGetLastError(), "fill_lanes_kernel");
+}
+
+int yvx_cuda_fill_f16_uniform(void *dst, unsigned long long count, unsigned long long seed,
+                              float lo, float hi, void *stream)
+{
+    if (!dst || !count) return YVEX_ERR_INVALID_ARG;
+    yvx::fill_scales_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((__half *)dst, count, seed, lo, hi);
+    return yvx_cuda_check(cudaGetLastError(), "fill_scales_kernel");
+}
+
+}  // extern "C"

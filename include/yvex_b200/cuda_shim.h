@@ -99,6 +99,11 @@ void yvx_cuda_gqa_plan_splits(yvx_gqa_problem *problem, int sm_count);
  * (1 more). `launches` receives the number of kernels enqueued. */
 int yvx_cuda_gqa_attention(const yvx_gqa_problem *problem, void *stream,
                            unsigned int *launches);
+/* Same launches with three events (cudaEvent_t as void*) recorded on `stream`:
+ * before the attention kernel, between it and the combine, after the combine.
+ * For measuring the dominant kernel alone; no counterpart in the reference. */
+int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *problem, void *stream,
+                                    void *events[3], unsigned int *launches);
 
 /* ---- log-sum-exp combine of partial results ---------------------------------
  * parts: [items][part_count][head_dim + 2] holding (o normalised, m, l).
@@ -116,6 +121,17 @@ int yvx_cuda_op_attention_f32(const float *query, const float *keys, const float
                               float scale, int causal, unsigned long long head_dim,
                               float *scores, float *probabilities, float *out,
                               void *stream);
+
+/* ---- seeded device-side fills for benchmark workloads ------------------------
+ * No counterpart in the reference. Counter-based (splitmix64 of seed and
+ * element index): N(0, sigma^2) as F32 or BF16, int8 lanes uniform in
+ * [-127, 127], f16 values uniform in [lo, hi). */
+int yvx_cuda_fill_normal(void *dst, int dtype, unsigned long long count,
+                         unsigned long long seed, float sigma, void *stream);
+int yvx_cuda_fill_q8_lanes(void *dst, unsigned long long count, unsigned long long seed,
+                           void *stream);
+int yvx_cuda_fill_f16_uniform(void *dst, unsigned long long count, unsigned long long seed,
+                              float lo, float hi, void *stream);
 
 #ifdef __cplusplus
 }
