@@ -2,8 +2,9 @@
 #include "common.cuh"
 
 namespace yvx {
-int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, cudaEvent_t *events,
-                       unsigned int *launches);
+int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 }
 
 extern "C" {
@@ -44,9 +45,24 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
         p->query_heads % p->kv_heads || !p->head_dim || !p->chunk_tokens || !p->max_splits ||
         (p->max_splits > 1u && !p->partials) || (p->block_table && !p->block_tokens))
         return YVEX_ERR_INVALID_ARG;
-    int rc = yvx::gqa_generic_launch(*p, (cudaStream_t)stream, events, &count);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (events) cudaEventRecord(events[0], s);
+    // Specialised kernels return 1 when they took the problem, 0 when its shape
+    // is not theirs; the general kernel takes everything else.
+    int rc = p->force_general ? 0 : yvx::gqa_decode_mma_launch(*p, s);
+    if (rc == 0) rc = yvx::gqa_generic_main_launch(*p, s);
+    else if (rc == 1) rc = 0;
+    if (rc != 0) return rc;
+    count = 1u;
+    if (events) cudaEventRecord(events[1], s);
+    if (p->max_splits > 1u) {
+        rc = yvx::gqa_combine_launch(*p, s);
+        if (rc != 0) return rc;
+        count = 2u;
+    }
+    if (events) cudaEventRecord(events[2], s);
     if (launches) *launches = count;
-    return rc;
+    return 0;
 }
 
 int yvx_cuda_gqa_attention(const yvx_gqa_problem *p, void *stream, unsigned int *launches)

@@ -324,33 +324,25 @@ static int launch_generic_slots(const yvx_gqa_problem &p, cudaStream_t stream)
     return launch_generic<QT, KT, 8>(p, stream);
 }
 
-int gqa_generic_launch(const yvx_gqa_problem &p, cudaStream_t stream, cudaEvent_t *events,
-                       unsigned int *launches)
+// Launches the general attention kernel only (no combine).
+int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream)
 {
-    int rc;
     if (p.head_dim == 0u || p.head_dim > 256u) return YVEX_ERR_UNSUPPORTED;
-    if (events) cudaEventRecord(events[0], stream);
     if (p.query_dtype == YVEX_DTYPE_F32 && p.kv_dtype == YVEX_DTYPE_F32)
-        rc = launch_generic_slots<float, float>(p, stream);
-    else if (p.query_dtype == YVEX_DTYPE_BF16 && p.kv_dtype == YVEX_DTYPE_BF16)
-        rc = launch_generic_slots<__nv_bfloat16, __nv_bfloat16>(p, stream);
-    else if (p.query_dtype == YVEX_DTYPE_F32 && p.kv_dtype == YVEX_DTYPE_BF16)
-        rc = launch_generic_slots<float, __nv_bfloat16>(p, stream);
-    else
-        return YVEX_ERR_UNSUPPORTED;
-    if (rc != 0) return rc;
-    *launches = 1u;
-    if (events) cudaEventRecord(events[1], stream);
-    if (p.max_splits > 1u) {
-        const unsigned long long items =
-            (unsigned long long)p.sessions * p.query_rows * p.query_heads;
-        gqa_combine_kernel<<<(unsigned int)items, 128, 0, stream>>>(p);
-        rc = yvx_cuda_check(cudaGetLastError(), "gqa_combine_kernel");
-        if (rc != 0) return rc;
-        *launches = 2u;
-    }
-    if (events) cudaEventRecord(events[2], stream);
-    return 0;
+        return launch_generic_slots<float, float>(p, stream);
+    if (p.query_dtype == YVEX_DTYPE_BF16 && p.kv_dtype == YVEX_DTYPE_BF16)
+        return launch_generic_slots<__nv_bfloat16, __nv_bfloat16>(p, stream);
+    if (p.query_dtype == YVEX_DTYPE_F32 && p.kv_dtype == YVEX_DTYPE_BF16)
+        return launch_generic_slots<float, __nv_bfloat16>(p, stream);
+    return YVEX_ERR_UNSUPPORTED;
+}
+
+// Folds the per-split partials; needed whenever max_splits > 1.
+int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream)
+{
+    const unsigned long long items = (unsigned long long)p.sessions * p.query_rows * p.query_heads;
+    gqa_combine_kernel<<<(unsigned int)items, 128, 0, stream>>>(p);
+    return yvx_cuda_check(cudaGetLastError(), "gqa_combine_kernel");
 }
 
 }  // namespace yvx

@@ -87,7 +87,10 @@ typedef struct yvx_gqa_problem {
     float *partials;                 /* scratch [session][row][qhead][split][head_dim+2] */
     float *partial_output;           /* non-NULL: emit (o, m, l) per (session,row,qhead)
                                         instead of the final output: [..][head_dim+2] */
-    int *status;                     /* device status word; 0 ok, 1 non-finite, 2 contract */
+    int *status;                     /* device status word; 0 ok, 1 non-finite, 2 contract,
+                                        3 a bounded device-side wait gave up */
+    int force_general;               /* 1: take the general kernel even when a specialised
+                                        one admits the shape (cross-checks in tests) */
 } yvx_gqa_problem;
 
 /* Scratch bytes `partials` must hold for a problem (0 when one split suffices). */
