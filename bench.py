@@ -69,7 +69,7 @@ class ClockSampler:
             os.close(handle)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -321,11 +321,14 @@ def run_reference(args, rank):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
-    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--sessions", type=int, default=SESSIONS,
+                        help="shrink the batch (profiling captures only; not a bench value)")
     args = parser.parse_args()
+    globals()["SESSIONS"] = args.sessions
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -359,12 +362,12 @@ def main():
 
     # ---- device-resident throughput: operator call, asynchronous ----------
     b.bind_stream(None, synchronous=False)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         facts = w.step()
     b.sync()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     start, stop = w.event(), w.event()
     lib.yvx_cuda_stream_synchronize(b.stream)
     w.record(start)
@@ -394,7 +397,7 @@ def main():
     barrier()
 
     # ---- the attention kernel alone ----------------------------------------
-    kernel_ms, combine_ms, (chunk, splits) = w.kernel_ms(max(args.steps, 10))
+    kernel_ms, combine_ms, (chunk, splits) = w.kernel_ms(min(max(args.steps, 10), 100))
     clocks = sampler.stop()
 
     if rank != 0:
@@ -411,7 +414,7 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs_exceed_l2 (KV pool %.2f GB per GPU)" % (
+        "config": {"workload": WORKLOAD if SESSIONS == 64 else f"REDUCED to {SESSIONS} sessions (profiling only): " + WORKLOAD, "l2": "inputs_exceed_l2 (KV pool %.2f GB per GPU)" % (
                        2 * w.pool_blocks * BLOCK_TOKENS * KV_HEADS * HEAD_DIM * 2 / 1e9),
                    "kv_tokens_total": int(w.lengths.sum()), "chunk_tokens": chunk,
                    "max_splits": splits, "sharding": "sessions per rank, no collective"},
