@@ -39,6 +39,9 @@ sys.path.insert(0, ROOT)
 
 SESSIONS, QUERY_HEADS, KV_HEADS, HEAD_DIM, BLOCK_TOKENS = 64, 40, 8, 128, 64
 LOW, HIGH, SEED = 512, 32768, 1
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the ncu capture
+# summarised in profiles/gqa_decode_mma__batched_block_table_decode.md.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.011
 METRIC = "decode_attention_tokens_per_s"
 UNIT = "tokens/s"
 WORKLOAD = ("batched_decode_block_table: 64 sessions, ctx~U[512,32768] seed 1, 40q/8kv heads, "
@@ -425,7 +428,10 @@ def main():
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "frac": achieved / peak, "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * w.bytes,
+                     "traffic_source": "ncu dram read+write of a reduced launch (8 sessions), "
+                                       "scaled by KV tokens: 1.011 x algorithmic bytes",
+                     "peak_kind": peak_kind,
                      "kernel": "gqa split attention (combine excluded)",
                      "kernel_ms": kernel_ms, "combine_ms": combine_ms,
                      "algorithmic_bytes": w.bytes, "frac_of_8000_spec": achieved / 8000.0},
