@@ -165,6 +165,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_op_attention_f32", "yvx_cuda_gqa_attention_profiled",
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
+    "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
 ]
 
 _lib = None
@@ -241,6 +242,9 @@ def load():
     lib.yvx_cuda_fill_normal.argtypes = [vp, C.c_int, u64, u64, C.c_float, vp]
     lib.yvx_cuda_fill_q8_lanes.argtypes = [vp, u64, u64, vp]
     lib.yvx_cuda_fill_f16_uniform.argtypes = [vp, u64, u64, C.c_float, C.c_float, vp]
+    lib.yvx_cuda_gqa_static_scratch_capacity.restype = u64
+    lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
+    lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
     lib.yvx_cuda_lse_combine.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, C.c_int, vp, vp]
     _lib = lib
     return lib

@@ -108,6 +108,26 @@ int yvx_cuda_gqa_attention(const yvx_gqa_problem *problem, void *stream,
 int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *problem, void *stream,
                                     void *events[3], unsigned int *launches);
 
+/* The same attention for callers that cannot allocate device memory on this
+ * path (a host that gave the whole GPU to its own pool, a latency-critical step
+ * that cannot afford an allocation's synchronisation, a plug-in handed only its
+ * inputs and outputs). It has no counterpart in the reference. `problem->partials`
+ * is ignored: the split scratch is a fixed 16 MiB array inside the library's
+ * device image (held by every GPU that loads the library until the process
+ * exits). Problems whose yvx_cuda_gqa_partials_bytes() exceeds
+ * yvx_cuda_gqa_static_scratch_capacity() are refused with YVEX_ERR_BOUNDS and a
+ * message in yvx_cuda_last_error_text(). The call itself performs no device or
+ * host allocation. The first call on each device looks the array's address up
+ * once (with that device current); make that first call before any stream
+ * capture begins. All calls on a device share the one array and it keeps the
+ * previous call's bytes: nothing in it has to start at zero, because every
+ * partial the combine reads is written by the attention kernel of the same call,
+ * but two calls that overlap on the GPU (different streams, or graphs replayed
+ * concurrently) race on it. Serialise them. */
+unsigned long long yvx_cuda_gqa_static_scratch_capacity(void);
+int yvx_cuda_gqa_attention_static_scratch(const yvx_gqa_problem *problem, void *stream,
+                                          unsigned int *launches);
+
 /* ---- log-sum-exp combine of partial results ---------------------------------
  * parts: [items][part_count][head_dim + 2] holding (o normalised, m, l).
  * Used after the cross-GPU all-gather of sequence-sharded partials. No

@@ -13,7 +13,7 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
                 k_token_stride, v_token_stride, k_head_stride, v_head_stride,
                 k_outer_stride, v_outer_stride, v_offset_elems=0, kv_max=None,
                 force_general=False, chunk_tokens=None, query_start=None, position_base=0,
-                partial_output=False):
+                partial_output=False, entry="yvx_cuda_gqa_attention", own_scratch=True):
     """q: device Tensor [sessions, rows, hq*hd]; k, v: device Tensors holding the
     cache in any layout described by the strides (elements). Returns the output
     array (or the (o, m, l) partials) and the launch count."""
@@ -50,9 +50,12 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
     if chunk_tokens:
         p.chunk_tokens = chunk_tokens
         p.max_splits = (p.kv_tokens_max + chunk_tokens - 1) // chunk_tokens
-    scratch = backend.alloc("partials", abi.DTYPE_F32, (1,), max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
     status = backend.tensor("status", np.zeros(1, np.int32))
-    p.partials, p.status = scratch.data_ptr, status.data_ptr
+    p.status = status.data_ptr
+    if own_scratch:
+        scratch = backend.alloc("partials", abi.DTYPE_F32, (1,),
+                                max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+        p.partials = scratch.data_ptr
     if partial_output:
         out = backend.alloc("parts", abi.DTYPE_F32, (sessions, rows, hq, hd + 2))
         p.partial_output = out.data_ptr
@@ -60,7 +63,9 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
         out = backend.alloc("out", out_dtype, (sessions, rows, hq * hd))
         p.output = out.data_ptr
     launches = C.c_uint()
-    rc = lib.yvx_cuda_gqa_attention(C.byref(p), backend.stream, C.byref(launches))
+    rc = getattr(lib, entry)(C.byref(p), backend.stream, C.byref(launches))
+    if rc != 0 and entry != "yvx_cuda_gqa_attention":
+        return None, rc, 0, (p.chunk_tokens, p.max_splits)
     assert rc == 0, lib.yvx_cuda_last_error_text()
     assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
     out.struct.is_written = 1
