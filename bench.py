@@ -40,7 +40,7 @@ sys.path.insert(0, ROOT)
 SESSIONS, QUERY_HEADS, KV_HEADS, HEAD_DIM, BLOCK_TOKENS = 64, 40, 8, 128, 64
 LOW, HIGH, SEED = 512, 32768, 1
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the ncu capture
-# summarised in profiles/gqa_decode_mma__batched_block_table_decode.md.
+# summarised under profiles/ (decode kernel, batched block-table workload).
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.011
 METRIC = "decode_attention_tokens_per_s"
 UNIT = "tokens/s"

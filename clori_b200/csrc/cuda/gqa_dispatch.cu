@@ -5,6 +5,7 @@ namespace yvx {
 int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 }
 
 extern "C" {
@@ -40,7 +41,8 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
 {
     unsigned int count = 0;
     if (launches) *launches = 0;
-    if (!p || !p->query || !p->key || !p->value || (!p->output && !p->partial_output) ||
+    if (!p || !p->query || !p->key || (!p->value && p->kv_dtype != YVEX_DTYPE_Q8_0) ||
+        (!p->output && !p->partial_output) ||
         !p->status || !p->sessions || !p->query_rows || !p->query_heads || !p->kv_heads ||
         p->query_heads % p->kv_heads || !p->head_dim || !p->chunk_tokens || !p->max_splits ||
         (p->max_splits > 1u && !p->partials) || (p->block_table && !p->block_tokens))
@@ -49,7 +51,8 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     if (events) cudaEventRecord(events[0], s);
     // Specialised kernels return 1 when they took the problem, 0 when its shape
     // is not theirs; the general kernel takes everything else.
-    int rc = p->force_general ? 0 : yvx::gqa_decode_mma_launch(*p, s);
+    int rc = yvx::gqa_decode_q8_launch(*p, s);
+    if (rc == 0 && !p->force_general) rc = yvx::gqa_decode_mma_launch(*p, s);
     if (rc == 0) rc = yvx::gqa_generic_main_launch(*p, s);
     else if (rc == 1) rc = 0;
     if (rc != 0) return rc;

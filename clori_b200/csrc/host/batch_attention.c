@@ -29,7 +29,11 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
     unsigned int launches = 0;
     void *scratch = NULL;
     int rc;
-    if (!request || !facts || !request->query || !request->key || !request->value ||
+    int q8;
+    if (!request || !facts || !request->query || !request->key ||
+        (!request->value &&
+         request->requirement.numeric_contract !=
+             YVEX_TRANSFORMER_ATTENTION_NUMERIC_Q8_0_KV_F32_ACCUMULATE) ||
         !request->output || !request->kv_tokens)
         return yvx_fail(err, YVEX_ERR_INVALID_ARG, where,
                         "complete batch tensors and result facts are required");
@@ -53,6 +57,10 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
           (r->numeric_contract == YVEX_TRANSFORMER_ATTENTION_NUMERIC_BF16_F32_ACCUMULATE &&
            (r->query_dtype == YVEX_DTYPE_BF16 || r->query_dtype == YVEX_DTYPE_F32) &&
            r->key_dtype == YVEX_DTYPE_BF16 &&
+           (r->output_dtype == YVEX_DTYPE_F32 || r->output_dtype == YVEX_DTYPE_BF16)) ||
+          (r->numeric_contract == YVEX_TRANSFORMER_ATTENTION_NUMERIC_Q8_0_KV_F32_ACCUMULATE &&
+           r->query_dtype == YVEX_DTYPE_BF16 && r->key_dtype == YVEX_DTYPE_Q8_0 &&
+           r->head_dimension == 128ull && !r->key_token_stride && !r->value_token_stride &&
            (r->output_dtype == YVEX_DTYPE_F32 || r->output_dtype == YVEX_DTYPE_BF16))))
         return yvx_fail(err, YVEX_ERR_UNSUPPORTED, where,
                         "unsupported layout, mask, numeric contract or dtype combination");
@@ -60,13 +68,46 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
     rc = yvx_backend_admit(backend, where, err);
     if (rc != YVEX_OK) return rc;
 
+    q8 = r->key_dtype == YVEX_DTYPE_Q8_0;
     kv_token_stride = r->key_token_stride ? r->key_token_stride : kv_width;
     value_token_stride = r->value_token_stride ? r->value_token_stride : kv_width;
     head_stride = request->kv_head_stride ? request->kv_head_stride : r->head_dimension;
     query_elements = request->session_count * r->query_tokens *
                      (r->query_token_stride ? r->query_token_stride : query_width);
     output_elements = request->session_count * r->query_tokens * query_width;
-    if (request->kv_layout == YVEX_B200_KV_BLOCK_TABLE) {
+    if (q8) {
+        /* Records: strides are bytes; one record per (64-token block, kv head). */
+        const unsigned long long record = yvx_cuda_q8_record_bytes();
+        unsigned long long blocks_per_session = (r->key_value_tokens + 63ull) / 64ull;
+        head_stride = request->kv_head_stride ? request->kv_head_stride : record;
+        block_stride = request->kv_block_stride ? request->kv_block_stride
+                                                : head_stride * r->key_value_heads;
+        if (head_stride < record || block_stride < head_stride * r->key_value_heads)
+            return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "Q8 record strides are too small");
+        if (request->kv_layout == YVEX_B200_KV_BLOCK_TABLE) {
+            if (!request->block_table || request->block_tokens != 64ull ||
+                request->max_blocks_per_session < blocks_per_session)
+                return yvx_fail(err, YVEX_ERR_INVALID_ARG, where,
+                                "a 64-token block table covering the longest session is required");
+            pool_blocks = request->key->bytes / block_stride;
+            table_elements = request->session_count * request->max_blocks_per_session;
+            if (!pool_blocks || pool_blocks > 0x7fffffffull ||
+                !batch_view(backend, request->block_table, YVEX_DTYPE_I32, table_elements))
+                return yvx_fail(err, YVEX_ERR_FORMAT, where,
+                                "block table and record pool do not match the declared geometry");
+            kv_elements = block_stride;
+        } else if (request->kv_layout == YVEX_B200_KV_CONTIGUOUS) {
+            session_stride = request->kv_session_stride ? request->kv_session_stride
+                                                        : blocks_per_session * block_stride;
+            kv_elements = (request->session_count - 1ull) * session_stride +
+                          blocks_per_session * block_stride;
+        } else {
+            return yvx_fail(err, YVEX_ERR_UNSUPPORTED, where, "unknown KV layout");
+        }
+        if (!yvx_tensor_owned(backend, request->key) || request->key->bytes < kv_elements)
+            return yvx_fail(err, YVEX_ERR_FORMAT, where,
+                            "the Q8 record tensor is smaller than the declared geometry");
+    } else if (request->kv_layout == YVEX_B200_KV_BLOCK_TABLE) {
         if (!request->block_table || !request->block_tokens || request->block_tokens % 64ull ||
             !request->max_blocks_per_session ||
             request->max_blocks_per_session * request->block_tokens < r->key_value_tokens)
@@ -95,8 +136,8 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
     }
     if (!batch_view(backend, request->query, r->query_dtype, query_elements) ||
         !request->query->is_written ||
-        !batch_view(backend, request->key, r->key_dtype, kv_elements) ||
-        !batch_view(backend, request->value, r->value_dtype, kv_elements) ||
+        (!q8 && (!batch_view(backend, request->key, r->key_dtype, kv_elements) ||
+                 !batch_view(backend, request->value, r->value_dtype, kv_elements))) ||
         !batch_view(backend, request->output, r->output_dtype, output_elements) ||
         !batch_view(backend, request->kv_tokens, YVEX_DTYPE_I32, request->session_count))
         return yvx_fail(err, YVEX_ERR_FORMAT, where,
@@ -118,11 +159,12 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
     problem.query_session_stride = problem.query_row_stride * r->query_tokens;
     problem.output = request->output->data;
     problem.key = request->key->data;
-    problem.value = request->value->data;
+    problem.value = q8 ? request->key->data : request->value->data;
     problem.key_token_stride = kv_token_stride;
     problem.value_token_stride = value_token_stride;
     problem.key_head_stride = problem.value_head_stride = head_stride;
     problem.key_session_stride = problem.value_session_stride = session_stride;
+    if (q8) problem.key_block_stride = problem.value_block_stride = block_stride;
     if (request->kv_layout == YVEX_B200_KV_BLOCK_TABLE) {
         problem.block_table = (const int *)request->block_table->data;
         problem.block_tokens = (unsigned int)request->block_tokens;

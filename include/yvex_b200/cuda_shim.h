@@ -52,7 +52,14 @@ const char *yvx_cuda_last_error_text(void);
  *   O[b,t,h,:] = softmax_s( scale * Q[b,t,h,:] . K[b,s,h/g,:] ) V[b,s,h/g,:]
  *   causal: s visible iff  kv_position_base + s <= query_start[b] + t
  *
- * All strides are in ELEMENTS of the tensor's dtype. */
+ * All strides are in ELEMENTS of the tensor's dtype.
+ *
+ * kv_dtype = YVEX_DTYPE_Q8_0 selects the quantised cache: `key` points at Q8
+ * records (see yvx_cuda_q8_kv_pack), `value` is unused, head_dim must be 128,
+ * block_tokens 64, and key_head_stride / key_block_stride / key_session_stride
+ * are in BYTES (record of head h of block j: key + j*key_block_stride +
+ * h*key_head_stride; without a block table, block j of session b is
+ * b*key_session_stride/key_block_stride + j). */
 typedef struct yvx_gqa_problem {
     unsigned int sessions;        /* batch of independent sessions */
     unsigned int query_rows;      /* query rows per session (uniform) */
@@ -144,6 +151,28 @@ int yvx_cuda_op_attention_f32(const float *query, const float *keys, const float
                               float scale, int causal, unsigned long long head_dim,
                               float *scores, float *probabilities, float *out,
                               void *stream);
+
+/* ---- Q8_0 KV records -----------------------------------------------------------
+ * No counterpart in the reference (its KV state is F32; Q8_0 exists there as a
+ * weight qtype only: src/gguf/quant_block.c:160-187,819-832). A record is the
+ * Q8_0 data of 64 tokens of one KV head (head_dim 128) as 17408 contiguous
+ * bytes, a byte permutation of the tokens' GGUF Q8_0 rows:
+ *   [K lanes 8192][V lanes 8192][K scales 512][V scales 512]
+ * K lane of (token t, dim d): ((t/8*2 + d/64)*32 + (t%8)*4 + (d%16%8)/2)*16
+ *                              + (d%64/16)*4 + (d%2) + 2*(d%16/8)
+ * V lane of (t, d): 8192 + (((t/16*4 + d/32)*32 + (d%8)*4 + (t%16%8)/2)*4 + d/8%4)*4
+ *                              + (t%2) + 2*(t%16/8)
+ * K scale of (t, 32-lane block q): 16384 + (t*4 + q)*2
+ * V scale of (t, q): 16896 + (((t/16*4 + (t%16%8)/2)*4 + q)*4 + (t%2) + 2*(t%16/8))*2
+ * yvx_cuda_q8_kv_pack scatters `tokens` GGUF Q8_0 rows ([token][kv_heads*4*34]
+ * bytes, K and V) starting at absolute token `first_token` of a session into
+ * its records; block_ids maps the session's block index to a pool block (NULL =
+ * identity). Records must be zero-filled before their first token is packed. */
+unsigned long long yvx_cuda_q8_record_bytes(void);
+int yvx_cuda_q8_kv_pack(const void *k_rows, const void *v_rows, unsigned int tokens,
+                        unsigned int kv_heads, void *records, const int *block_ids,
+                        unsigned long long block_stride, unsigned long long head_stride,
+                        unsigned int first_token, void *stream);
 
 /* ---- seeded device-side fills for benchmark workloads ------------------------
  * No counterpart in the reference. Counter-based (splitmix64 of seed and
