@@ -201,7 +201,7 @@ class Workload:
         return pin["q"][1] + pin["lens"][1] + pin["table"][1], pin["out"][1]
 
     # -- the dominant kernel alone -------------------------------------------
-    def kernel_ms(self, repeats):
+    def kernel_ms(self, repeats, chunk=0):
         """Average duration of the attention kernel (without the combine)."""
         abi, lib, b = self.abi, self.lib, self.backend
         p = abi.GqaProblem()
@@ -220,6 +220,8 @@ class Workload:
         p.kv_tokens, p.kv_tokens_max = self.kv_tokens.data_ptr, int(self.lengths.max())
         p.query_start_from_end = 1
         lib.yvx_cuda_gqa_plan_splits(C.byref(p), b.sm_count)
+        if chunk:
+            p.chunk_tokens, p.max_splits = chunk, (p.kv_tokens_max + chunk - 1) // chunk
         scratch, status = C.c_void_p(), C.c_void_p()
         assert lib.yvx_cuda_malloc(C.byref(scratch), max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16)) == 0
         assert lib.yvx_cuda_malloc(C.byref(status), 4) == 0
@@ -258,6 +260,187 @@ class Workload:
             self.lib.yvx_cuda_stream_synchronize(self.backend.stream)
             out.append(self.cl.bf16_bits_to_f32(rows[:length]))
         return self.cl.bf16_bits_to_f32(self.q_host[s]), out[0], out[1]
+
+
+
+# ---------------------------------------------------------------------------
+# The other single-GPU configurations: measured in the same run and reported
+# under "other_workloads" (the headline line stays the batched decode).
+# ---------------------------------------------------------------------------
+
+def _alloc(lib, nbytes):
+    p = C.c_void_p()
+    assert lib.yvx_cuda_malloc(C.byref(p), nbytes) == 0, lib.yvx_cuda_last_error_text()
+    return p
+
+
+def _timed_launches(lib, backend, problems, repeats):
+    """Profiled launches cycling through `problems` (copies of the inputs larger
+    than L2 in total); returns mean ms of the attention kernel and the combine."""
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    for i in range(3):
+        n = C.c_uint()
+        assert lib.yvx_cuda_gqa_attention(C.byref(problems[i % len(problems)]), backend.stream, C.byref(n)) == 0
+    triples = [(event(), event(), event()) for _ in range(repeats)]
+    for i, triple in enumerate(triples):
+        n = C.c_uint()
+        rc = lib.yvx_cuda_gqa_attention_profiled(C.byref(problems[i % len(problems)]), backend.stream,
+                                                 (C.c_void_p * 3)(*triple), C.byref(n))
+        assert rc == 0, lib.yvx_cuda_last_error_text()
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    ms = C.c_float()
+    main, combine = [], []
+    for a, b, c in triples:
+        lib.yvx_cuda_event_elapsed_ms(a, b, C.byref(ms)); main.append(ms.value)
+        lib.yvx_cuda_event_elapsed_ms(b, c, C.byref(ms)); combine.append(ms.value)
+        for e in (a, b, c):
+            lib.yvx_cuda_event_destroy(e)
+    return float(np.mean(main)), float(np.mean(combine)), n.value
+
+
+def bench_decode_f32(lib, backend, abi, peak, repeats):
+    """Config 1: 1 session, 1 query token, 32/8 heads, hd 128, KV 4096, F32."""
+    hq, hkv, hd, tokens, copies = 32, 8, 128, 4096, 16
+    width = hkv * hd
+    kv_elems = tokens * width
+    k = _alloc(lib, copies * kv_elems * 4)
+    v = _alloc(lib, copies * kv_elems * 4)
+    q = _alloc(lib, hq * hd * 4)
+    out = _alloc(lib, hq * hd * 4)
+    status = _alloc(lib, 4)
+    lib.yvx_cuda_fill_normal(k, abi.DTYPE_F32, copies * kv_elems, 101, 1.0, backend.stream)
+    lib.yvx_cuda_fill_normal(v, abi.DTYPE_F32, copies * kv_elems, 102, 1.0, backend.stream)
+    lib.yvx_cuda_fill_normal(q, abi.DTYPE_F32, hq * hd, 103, 1.0, backend.stream)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    problems, scratch = [], None
+    for i in range(copies):
+        p = abi.GqaProblem()
+        p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, 1, hq, hkv, hd
+        p.causal, p.scale = 1, 1.0 / np.sqrt(hd)
+        p.query_dtype = p.kv_dtype = p.output_dtype = abi.DTYPE_F32
+        p.query, p.query_row_stride, p.output = q, hq * hd, out
+        p.key, p.value = k.value + i * kv_elems * 4, v.value + i * kv_elems * 4
+        p.key_token_stride = p.value_token_stride = width
+        p.key_head_stride = p.value_head_stride = hd
+        p.kv_tokens_uniform = p.kv_tokens_max = tokens
+        p.query_start_uniform = tokens - 1
+        lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+        if scratch is None:
+            scratch = _alloc(lib, max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+        p.partials, p.status = scratch, status
+        problems.append(p)
+    main, combine, launches = _timed_launches(lib, backend, problems, repeats)
+    # full-size parity of copy (repeats-1) % copies against the CPU oracle
+    last = (repeats - 1) % copies
+    host = {}
+    for name, ptr, count in (("q", q.value, hq * hd), ("k", k.value + last * kv_elems * 4, kv_elems),
+                             ("v", v.value + last * kv_elems * 4, kv_elems), ("o", out.value, hq * hd)):
+        host[name] = np.empty(count, np.float32)
+        lib.yvx_cuda_download_async(host[name].ctypes.data, ptr, count * 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    nbytes = 2 * kv_elems * 4 + 2 * hq * hd * 4
+    result = {"workload": "decode 1x1 token, 32q/8kv heads, hd128, KV 4096, F32 (exact-F32 contract)",
+              "kernel": "gqa split attention (general F32 kernel)", "launches_per_step": launches,
+              "kernel_ms": main, "combine_ms": combine, "algorithmic_bytes": nbytes,
+              "achieved_gbs": nbytes / (main * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (main * 1e-3) / 1e9 / peak,
+              "tokens_per_s": 1.0 / ((main + combine) * 1e-3),
+              "l2": f"{copies} rotating KV copies ({copies * 2 * kv_elems * 4 / 1e6:.0f} MB) exceed L2",
+              "chunk_tokens": problems[0].chunk_tokens}
+    for ptr in (k, v, q, out, status, scratch):
+        lib.yvx_cuda_free(ptr)
+    return result, host
+
+
+def bench_verify_q8(lib, backend, abi, peak, repeats, chunk=None):
+    """Config 4 on one GPU: 1 session, KV 131072, 32/8 heads, hd 128, Q8_0 KV,
+    4 speculative rows causal among themselves."""
+    from clori_b200 import q8_records
+    hq, hkv, hd, tokens, rows, copies = 32, 8, 128, 131072, 4, 2
+    blocks = tokens // 64
+    record = q8_records.RECORD_BYTES
+    pool_bytes = blocks * hkv * record
+    records = _alloc(lib, copies * pool_bytes)
+    q = _alloc(lib, rows * hq * hd * 2)
+    out = _alloc(lib, rows * hq * hd * 4)
+    status = _alloc(lib, 4)
+    lib.yvx_cuda_fill_q8_records(records, copies * blocks * hkv, 201, 0.002, 0.02, backend.stream)
+    lib.yvx_cuda_fill_normal(q, abi.DTYPE_BF16, rows * hq * hd, 202, 1.0, backend.stream)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    problems, scratch = [], None
+    for i in range(copies):
+        p = abi.GqaProblem()
+        p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, rows, hq, hkv, hd
+        p.causal, p.scale = 1, 1.0 / np.sqrt(hd)
+        p.query_dtype, p.kv_dtype, p.output_dtype = abi.DTYPE_BF16, abi.DTYPE_Q8_0, abi.DTYPE_F32
+        p.query, p.query_row_stride, p.query_session_stride, p.output = q, hq * hd, rows * hq * hd, out
+        p.key = records.value + i * pool_bytes
+        p.key_head_stride, p.key_block_stride, p.block_tokens = record, hkv * record, 64
+        p.kv_tokens_uniform = p.kv_tokens_max = tokens
+        p.query_start_from_end = 1
+        lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+        if chunk:
+            p.chunk_tokens, p.max_splits = chunk, (tokens + chunk - 1) // chunk
+        if scratch is None:
+            scratch = _alloc(lib, max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+        p.partials, p.status = scratch, status
+        problems.append(p)
+    main, combine, launches = _timed_launches(lib, backend, problems, repeats)
+    last = (repeats - 1) % copies
+    # sample for the CPU check: KV head 0 (query heads 0..3), every record of it
+    head0 = np.empty((blocks, record), np.uint8)
+    for j in range(blocks):
+        lib.yvx_cuda_download_async(head0.ctypes.data + j * record,
+                                    records.value + last * pool_bytes + j * hkv * record, record, backend.stream)
+    q_host = np.empty(rows * hq * hd, np.uint16)
+    o_host = np.empty(rows * hq * hd, np.float32)
+    lib.yvx_cuda_download_async(q_host.ctypes.data, q, q_host.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(o_host.ctypes.data, out, o_host.nbytes, backend.stream)
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    nbytes = pool_bytes + rows * hq * hd * (2 + 4)
+    result = {"workload": "speculative verify, 1 session, KV 131072, 32q/8kv heads, hd128, Q8_0 KV, 4 rows",
+              "kernel": "gqa_decode_q8_kernel", "launches_per_step": launches, "kernel_ms": main,
+              "combine_ms": combine, "algorithmic_bytes": nbytes, "status_word": int(st[0]),
+              "achieved_gbs": nbytes / (main * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (main * 1e-3) / 1e9 / peak,
+              "tokens_per_s": rows / ((main + combine) * 1e-3),
+              "l2": f"{copies} rotating record pools ({copies * pool_bytes / 1e6:.0f} MB) exceed L2",
+              "chunk_tokens": problems[0].chunk_tokens}
+    for ptr in (records, q, out, status, scratch):
+        lib.yvx_cuda_free(ptr)
+    return result, (head0, q_host.reshape(rows, hq * hd), o_host.reshape(rows, hq * hd))
+
+
+def check_decode_f32(engine, host, threads):
+    start = time.perf_counter()
+    ref = engine.gqa_attention(host["q"].reshape(1, -1), host["k"].reshape(4096, -1), host["v"].reshape(4096, -1),
+                               4095, 32, 8, 128, threads=threads)
+    seconds = time.perf_counter() - start
+    return float(np.abs(ref.reshape(-1) - host["o"]).max()), seconds
+
+
+def check_verify_q8(engine, sample, threads):
+    """CPU attention of KV head 0's group (4 query heads x 4 rows) over all 131072 tokens."""
+    from clori_b200 import bf16_bits_to_f32, q8_records
+    head0, q_bits, o = sample
+    k_lane, v_lane, k_scale, v_scale = q8_records.record_offsets()
+    blocks = head0.shape[0]
+    def dequant(lane, scale):
+        lanes = head0[:, lane.reshape(-1)].reshape(blocks * 64, 128).view(np.int8).astype(np.float32)
+        lo = head0[:, scale.reshape(-1)].astype(np.uint16)
+        hi = head0[:, (scale + 1).reshape(-1)].astype(np.uint16)
+        d = (lo | (hi << 8)).view(np.float16).astype(np.float32).reshape(blocks * 64, 4)
+        return lanes * np.repeat(d, 32, axis=1)
+    k, v = dequant(k_lane, k_scale), dequant(v_lane, v_scale)
+    q = bf16_bits_to_f32(q_bits).reshape(4, 32, 128)[:, :4].reshape(4, 4 * 128)
+    start = time.perf_counter()
+    ref = engine.gqa_attention(np.ascontiguousarray(q), k, v, k.shape[0] - 4, 4, 1, 128, threads=threads)
+    seconds = time.perf_counter() - start
+    got = o.reshape(4, 32, 128)[:, :4].reshape(4, 4 * 128)
+    return float(np.abs(ref - got).max()), seconds
 
 
 def cpu_engine():
@@ -328,6 +511,14 @@ def main():
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--workload", default="headline",
+                        choices=["headline", "decode_f32", "verify_q8"],
+                        help="run ONE of the other configurations alone and print its numbers "
+                             "(for profiler captures; not the bench line)")
+    parser.add_argument("--chunk", type=int, default=0,
+                        help="override the split size of --workload verify_q8 (experiments)")
+    parser.add_argument("--headline-only", action="store_true",
+                        help="skip the other single-GPU configurations")
     parser.add_argument("--sessions", type=int, default=SESSIONS,
                         help="shrink the batch (profiling captures only; not a bench value)")
     args = parser.parse_args()
@@ -359,6 +550,16 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{local_rank}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.workload != "headline":
+        import clori_b200
+        from clori_b200 import abi
+        backend = clori_b200.Backend(local_rank)
+        run = {"decode_f32": bench_decode_f32, "verify_q8": bench_verify_q8}[args.workload]
+        extra = {"chunk": args.chunk} if args.workload == "verify_q8" and args.chunk else {}
+        result, _ = run(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3), **extra)
+        print(json.dumps({"workload_only": args.workload, **result}))
+        return
 
     w = Workload(local_rank, SEED + 1000 * rank if world > 1 else SEED)
     lib, b = w.lib, w.backend
@@ -400,8 +601,13 @@ def main():
     barrier()
 
     # ---- the attention kernel alone ----------------------------------------
-    kernel_ms, combine_ms, (chunk, splits) = w.kernel_ms(min(max(args.steps, 10), 100))
+    kernel_ms, combine_ms, (chunk, splits) = w.kernel_ms(min(max(args.steps, 10), 100), args.chunk)
     clocks = sampler.stop()
+    others, other_samples = {}, {}
+    if world == 1 and not args.headline_only:
+        hbm_peak = measured_peaks()[0]
+        others["decode_f32_config1"], other_samples["f32"] = bench_decode_f32(lib, b, w.abi, hbm_peak, 64)
+        others["verify_q8_config4_1gpu"], other_samples["q8"] = bench_verify_q8(lib, b, w.abi, hbm_peak, 20)
 
     if rank != 0:
         if dist is not None:
@@ -453,6 +659,16 @@ def main():
                       f"({int(w.lengths[sample_ids].sum())} of {int(w.lengths.sum())} KV tokens), "
                       "best of 3 passes, KV copied back from the device and widened to F32",
             "seconds": best, "gpu_vs_cpu_max_abs_on_sample": worst}
+        if "f32" in other_samples:
+            err, seconds = check_decode_f32(engine, other_samples["f32"], threads)
+            others["decode_f32_config1"].update(gpu_vs_cpu_max_abs=err, cpu_ms=seconds * 1e3, cpu_cores=threads)
+        if "q8" in other_samples:
+            err, seconds = check_verify_q8(engine, other_samples["q8"], threads)
+            others["verify_q8_config4_1gpu"].update(
+                gpu_vs_cpu_max_abs_on_sample=err, cpu_sample="KV head 0: 4 query heads x 4 rows x 131072 tokens",
+                cpu_sample_ms=seconds * 1e3, cpu_cores=threads)
+    if others:
+        line["other_workloads"] = others
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -166,7 +166,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_lse_combine", "yvx_cuda_op_attention_f32", "yvx_cuda_gqa_attention_profiled",
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
-    "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack",
+    "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
 ]
 
 _lib = None
@@ -246,6 +246,7 @@ def load():
     lib.yvx_cuda_gqa_static_scratch_capacity.restype = u64
     lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
     lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
+    lib.yvx_cuda_fill_q8_records.argtypes = [vp, u64, u64, C.c_float, C.c_float, vp]
     lib.yvx_cuda_q8_record_bytes.restype = u64
     lib.yvx_cuda_q8_record_bytes.argtypes = []
     lib.yvx_cuda_q8_kv_pack.argtypes = [vp, vp, C.c_uint, C.c_uint, vp, vp, u64, u64, C.c_uint, vp]

@@ -16,7 +16,7 @@
 // the per-32-lane scale multiplies the f32 partial sum of its block, which is
 // the reference's dequantisation x = f16(d) * int8 (quant_block.c:819-832)
 // carried out exactly. For V the scale is folded into the f16 operand (one
-// rounding, 2^-12 relative). P is carried as f16 head + tail. Softmax and all
+// rounding, 2^-12 relative). P is f16 (11 significant bits). Softmax and all
 // accumulation are f32.
 #include "pipeline.cuh"
 
@@ -33,7 +33,6 @@ constexpr int kQ8QRowBytes = kQ8HeadDim * 2 + 16;
 constexpr int kQ8MergeRowFloats = kQ8HeadDim + 4;
 constexpr int kQ8SmemBytes = kQ8Stages * kQ8RecordBytes + 16 * kQ8QRowBytes + 1024 + 256;
 constexpr float kQ8Log2e = 1.4426950408889634f;
-constexpr float kQ8Ln2 = 0.6931471805599453f;
 
 struct Q8Session {
     unsigned int kv_tokens;
@@ -67,6 +66,26 @@ __device__ __forceinline__ void q8_lanes_to_f16(uint32_t word, uint32_t &lo, uin
     asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(b), "r"(0x64806480u));
 }
 
+// D = A * B + C with C given separately (so a chain can start from a constant).
+__device__ __forceinline__ void mma_f16_from(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1, float c0, float c1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%11,%11};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
+}
+
+// Four signed bytes -> two f16x2 registers holding 1152 + lane (no subtraction):
+// used where the constant is cancelled through the accumulator's initial value.
+__device__ __forceinline__ void q8_lanes_to_f16_biased(uint32_t word, uint32_t &lo, uint32_t &hi)
+{
+    const uint32_t biased = word ^ 0x80808080u;
+    asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(lo) : "r"(biased), "r"(0x64646464u));
+    asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(hi) : "r"(biased), "r"(0x64646464u));
+}
+
 __device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b)
 {
     uint32_t r;
@@ -94,6 +113,7 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
     unsigned char *q_smem = smem + kQ8Stages * kQ8RecordBytes;
     uint64_t *full = reinterpret_cast<uint64_t *>(q_smem + 16 * kQ8QRowBytes);
     uint64_t *empty = full + kQ8Stages;
+    __shared__ float k_bias_smem[64];
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int group = p.query_heads / p.kv_heads;
@@ -147,6 +167,18 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
         *reinterpret_cast<uint4 *>(q_smem + row * kQ8QRowBytes + chunk * 16u) = out;
     }
     __syncthreads();
+    // K lanes enter the MMA as 1152 + lane; the surplus 1152 * sum_k q[row][k]
+    // over each 32-lane block is cancelled by starting that block's accumulator
+    // at its negative. One sum per (row, block), computed once per CTA.
+    if (threadIdx.x < 64u) {
+        const unsigned int row = threadIdx.x >> 2, db = threadIdx.x & 3u;
+        const __half *qrow = reinterpret_cast<const __half *>(q_smem + row * kQ8QRowBytes) + 32u * db;
+        float sum = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 32; ++k) sum += __half2float(qrow[k]);
+        k_bias_smem[row * 4u + db] = -1152.0f * sum;
+    }
+    __syncthreads();
 
     if (warp == kQ8ConsumerWarps) {
         if (lane == 0) {
@@ -181,13 +213,9 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
     }
 
     const unsigned int g = lane >> 2, c = lane & 3u;
-    uint32_t qa[8][4];
-    {
-        const unsigned int j = lane >> 3, i = lane & 7u;
-        const uint32_t base = smem_u32(q_smem) + (8u * (j & 1u) + i) * kQ8QRowBytes + 16u * (j >> 1);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], base + ks * 32u);
-    }
+    // ldmatrix address of this lane's row of the Q tile (A operand, k-step 0).
+    const uint32_t q_frag_base = smem_u32(q_smem) + (8u * ((lane >> 3) & 1u) + (lane & 7u)) * kQ8QRowBytes +
+                                 16u * (lane >> 4);
     long long limit[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -199,8 +227,15 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
         else
             limit[h] = (long long)s.kv_tokens - 1;
     }
+    // Tokens up to `unmasked_until` are visible to every live row of this CTA.
+    long long unmasked_until;
+    if (p.causal)
+        unmasked_until = s.query_start_local + (long long)(vector_base / group);
+    else
+        unmasked_until = (long long)s.kv_tokens - 1;
+    if (unmasked_until > (long long)s.kv_tokens - 1) unmasked_until = (long long)s.kv_tokens - 1;
     const float score_scale = p.scale * kQ8Log2e;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};   // m in raw score units
     float o[16][4];
 #pragma unroll
     for (int n = 0; n < 16; ++n)
@@ -217,30 +252,41 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
         const unsigned int tile_token = t0 + i * kQ8TileTokens + 16u * warp;
 
         // ---- S = Q K^T: per 32-lane block, exact integer dot then scale ----
+        // Q fragments are re-read from shared memory per block (registers are the
+        // scarcer resource: three CTAs share an SM).
         float sc[2][4];
+        uint4 ks[2];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
-            const unsigned int nt = 2u * warp + n;
             // scales of tokens (8nt + 2c) and (8nt + 2c + 1): 2 x 4 f16
-            const uint4 ks = *reinterpret_cast<const uint4 *>(record + kQ8KScales + (8u * nt + 2u * c) * 8u);
-            const uint32_t ks_words[4] = {ks.x, ks.y, ks.z, ks.w};
+            ks[n] = *reinterpret_cast<const uint4 *>(record + kQ8KScales + (8u * (2u * warp + n) + 2u * c) * 8u);
 #pragma unroll
             for (int e = 0; e < 4; ++e) sc[n][e] = 0.0f;
+        }
 #pragma unroll
-            for (int kg = 0; kg < 2; ++kg) {
-                const uint4 kq = *reinterpret_cast<const uint4 *>(
-                    record + kQ8KLanes + ((nt * 2u + kg) * 32u + lane) * 16u);
-                const uint32_t kq_words[4] = {kq.x, kq.y, kq.z, kq.w};
+        for (int kg = 0; kg < 2; ++kg) {
+            uint4 kq[2];
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int db = 2 * kg + half;
-                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int n = 0; n < 2; ++n)
+                kq[n] = *reinterpret_cast<const uint4 *>(
+                    record + kQ8KLanes + (((2u * warp + n) * 2u + kg) * 32u + lane) * 16u);
 #pragma unroll
-                    for (int k2 = 0; k2 < 2; ++k2) {
-                        uint32_t b0, b1;
-                        q8_lanes_to_f16(kq_words[2 * half + k2], b0, b1);
-                        mma_f16(acc, qa[4 * kg + 2 * half + k2], b0, b1);
-                    }
+            for (int half = 0; half < 2; ++half) {
+                const int db = 2 * kg + half;
+                uint32_t qa0[4], qa1[4];
+                ldmatrix_x4(qa0, q_frag_base + (4 * kg + 2 * half) * 32u);
+                ldmatrix_x4(qa1, q_frag_base + (4 * kg + 2 * half + 1) * 32u);
+                const float bias0 = k_bias_smem[g * 4u + db], bias1 = k_bias_smem[(g + 8u) * 4u + db];
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+                    const uint32_t kq_words[4] = {kq[n].x, kq[n].y, kq[n].z, kq[n].w};
+                    const uint32_t ks_words[4] = {ks[n].x, ks[n].y, ks[n].z, ks[n].w};
+                    float acc[4];
+                    uint32_t b0, b1;
+                    q8_lanes_to_f16_biased(kq_words[2 * half], b0, b1);
+                    mma_f16_from(acc, qa0, b0, b1, bias0, bias1);
+                    q8_lanes_to_f16_biased(kq_words[2 * half + 1], b0, b1);
+                    mma_f16(acc, qa1, b0, b1);
                     // token 2c uses ks_words[0..1], token 2c+1 uses ks_words[2..3]
                     const uint32_t pair0 = ks_words[db >> 1], pair1 = ks_words[2 + (db >> 1)];
                     const float d0 = (db & 1) ? f16_hi(pair0) : f16_lo(pair0);
@@ -252,30 +298,32 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
                 }
             }
         }
-        // ---- masking + online softmax --------------------------------------
-        float tile_max[2] = {-INFINITY, -INFINITY};
+        // ---- masking (only on tiles that cross a visibility limit) ----------
+        if ((long long)tile_token + 15 > unmasked_until) {
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
+            for (int n = 0; n < 2; ++n)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const long long token = (long long)tile_token + 8 * n + 2 * c + (e & 1);
-                const float value = token <= limit[h] ? sc[n][e] * score_scale : -INFINITY;
-                sc[n][e] = value;
-                tile_max[h] = fmaxf(tile_max[h], value);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    const long long token = (long long)tile_token + 8 * n + 2 * c + (e & 1);
+                    if (token > limit[e >> 1]) sc[n][e] = -INFINITY;
+                }
+        }
+        // ---- online softmax: m in raw score units, exponent = (s - m) * scale
+        float tile_max[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+            tile_max[h] = fmaxf(fmaxf(sc[0][2 * h], sc[0][2 * h + 1]), fmaxf(sc[1][2 * h], sc[1][2 * h + 1]));
             tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
             tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
         }
-        float keep[2];
+        float keep[2], offset[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const float fresh = fmaxf(m[h], tile_max[h]);
-            keep[h] = fresh == -INFINITY ? 1.0f : exp2_approx(m[h] - fresh);
+            keep[h] = fresh == -INFINITY ? 1.0f : exp2_approx((m[h] - fresh) * score_scale);
             m[h] = fresh;
             l[h] *= keep[h];
+            offset[h] = fresh == -INFINITY ? 0.0f : -fresh * score_scale;
         }
         if (__any_sync(0xffffffffu, keep[0] != 1.0f || keep[1] != 1.0f)) {
 #pragma unroll
@@ -286,18 +334,15 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
                 o[n][3] *= keep[1];
             }
         }
-        uint32_t p_head[4], p_tail[4];
+        uint32_t p_head[4];
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float base = m[h] == -INFINITY ? 0.0f : m[h];
-                const float p0 = exp2_approx(sc[n][2 * h] - base);
-                const float p1 = exp2_approx(sc[n][2 * h + 1] - base);
+                const float p0 = exp2_approx(fmaf(sc[n][2 * h], score_scale, offset[h]));
+                const float p1 = exp2_approx(fmaf(sc[n][2 * h + 1], score_scale, offset[h]));
                 l[h] += p0 + p1;
-                const uint32_t head = pack_f16(p0, p1);
-                p_head[2 * n + h] = head;
-                p_tail[2 * n + h] = pack_f16(p0 - f16_lo(head), p1 - f16_hi(head));
+                p_head[2 * n + h] = pack_f16(p0, p1);
             }
         // ---- O += P V: lanes -> f16, scale folded into the operand ----------
         {
@@ -332,7 +377,6 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
                     b0 = mul_f16x2(b0, vs01[db]);
                     b1 = mul_f16x2(b1, vs23[db]);
                     mma_f16(o[4 * db + i4], p_head, b0, b1);
-                    mma_f16(o[4 * db + i4], p_tail, b0, b1);
                 }
             }
         }
@@ -375,7 +419,7 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
 #pragma unroll
         for (int w = 0; w < kQ8ConsumerWarps; ++w) {
             const float mw = merge_m[w * 16 + row];
-            const float weight = mw == -INFINITY ? 0.0f : exp2_approx(mw - mm);
+            const float weight = mw == -INFINITY ? 0.0f : exp2_approx((mw - mm) * score_scale);
             ll += merge_l[w * 16 + row] * weight;
             acc += merge_o[(w * 16 + row) * kQ8MergeRowFloats + d] * weight;
         }
@@ -392,7 +436,7 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
                                  : p.partials + (item * p.max_splits + split) * (kQ8HeadDim + 2ull);
             part[d] = ll > 0.0f ? acc / ll : 0.0f;
             if (d == 0) {
-                part[kQ8HeadDim] = mm == -INFINITY ? -INFINITY : mm * kQ8Ln2;
+                part[kQ8HeadDim] = mm == -INFINITY ? -INFINITY : mm * p.scale;  // natural-log units
                 part[kQ8HeadDim + 1] = ll;
             }
         }

@@ -10,21 +10,41 @@ int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 
 extern "C" {
 
-// Splits exist to fill the machine: the chunk is the smallest multiple of 64
-// tokens that keeps the number of (session, kv head, split) work items near
-// eight CTAs per SM, bounded to [64, 1024]. It depends only on the problem's
-// shape, so repeated calls split identically and results repeat bit for bit.
+// Splits exist to fill the machine. Two CTAs of the attention kernels are
+// resident per SM, so one "wave" is 2 * sm_count work items. The chunk is the
+// largest multiple of 64 tokens, at most 4096, for which the work items
+// (sessions x kv heads x row tiles x splits, counted with the longest session)
+// make at least one wave and fill their last wave to 90 %; failing that, the
+// best-filled choice with at least one wave; failing that, 64. It depends on the
+// problem's shape only, so repeated calls split identically and results repeat
+// bit for bit.
 void yvx_cuda_gqa_plan_splits(yvx_gqa_problem *p, int sm_count)
 {
     if (!p) return;
-    const unsigned long long target = (unsigned long long)(sm_count > 0 ? sm_count : 148) * 8ull;
-    const unsigned long long rows_total =
-        (unsigned long long)p->kv_tokens_max * p->sessions * p->kv_heads;
-    unsigned long long chunk = (rows_total + target - 1ull) / target;
-    chunk = (chunk + 63ull) / 64ull * 64ull;
-    if (chunk < 64ull) chunk = 64ull;
-    if (chunk > 1024ull) chunk = 1024ull;
-    p->chunk_tokens = (unsigned int)chunk;
+    const unsigned long long wave = 2ull * (unsigned long long)(sm_count > 0 ? sm_count : 148);
+    const unsigned int group = p->kv_heads ? p->query_heads / p->kv_heads : 1u;
+    const unsigned long long row_tiles = ((unsigned long long)p->query_rows * group + 15ull) / 16ull;
+    const unsigned long long lanes =
+        (unsigned long long)p->sessions * p->kv_heads * (row_tiles ? row_tiles : 1ull);
+    unsigned int chosen = 64u, best = 0u;
+    double best_fill = -1.0;
+    for (unsigned int chunk = 4096u; chunk >= 64u; chunk -= 64u) {
+        const unsigned long long splits = ((unsigned long long)p->kv_tokens_max + chunk - 1ull) / chunk;
+        const unsigned long long items = lanes * splits;
+        if (items < wave) continue;
+        const unsigned long long waves = (items + wave - 1ull) / wave;
+        const double fill = (double)items / (double)(waves * wave);
+        if (fill >= 0.9) {
+            best = chunk;
+            break;
+        }
+        if (fill > best_fill) {
+            best_fill = fill;
+            best = chunk;
+        }
+    }
+    if (best) chosen = best;
+    p->chunk_tokens = chosen;
     p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
     if (!p->max_splits) p->max_splits = 1u;
 }

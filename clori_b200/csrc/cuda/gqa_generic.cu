@@ -17,6 +17,14 @@ namespace yvx {
 constexpr int kGenericThreads = 128;
 constexpr int kGenericWarps = kGenericThreads / 32;
 
+// 2^x, max error 2 ulp over the normal range (ex2.approx), -inf -> 0.
+__device__ __forceinline__ float exp2_fast(float x)
+{
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct SessionView {
     unsigned int kv_tokens;
     long long query_start_local;  // query_start - kv_position_base (may be negative)
@@ -112,7 +120,8 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
 #pragma unroll
         for (int sl = 0; sl < SLOTS; ++sl) {
             const unsigned int d = lane + 32u * sl;
-            q[i][sl] = (live[i] && d < hd) ? load_as_float(qp + d) * p.scale : 0.0f;
+            // scores are kept in log2 units: q carries scale * log2(e)
+            q[i][sl] = (live[i] && d < hd) ? load_as_float(qp + d) * (p.scale * 1.4426950408889634f) : 0.0f;
         }
     }
     if (tile_limit + 1 < (long long)t1) t1 = tile_limit + 1 > 0 ? (unsigned int)(tile_limit + 1) : 0u;
@@ -126,61 +135,64 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
         for (int sl = 0; sl < SLOTS; ++sl) acc[i][sl] = 0.0f;
     }
 
-    // Register double-buffer: the next row's loads are in flight while the
-    // current row is reduced.
-    float kc[SLOTS], vc[SLOTS], kn[SLOTS], vn[SLOTS];
-    unsigned int t = t0 + warp;
-    if (t < t1) {
-        const KT *kp = kv_row<KT>(p.key, p, b, t, kv_head, true);
-        const KT *vp = kv_row<KT>(p.value, p, b, t, kv_head, false);
+    // Each warp takes U consecutive tokens per pass and issues all of their K
+    // and V loads before any arithmetic, so 2*U rows per warp are in flight.
+    constexpr int U = SLOTS <= 4 ? 4 : 2;
+    for (unsigned int base = t0 + warp * U; base < t1; base += kGenericWarps * U) {
+        float kc[U][SLOTS], vc[U][SLOTS];
 #pragma unroll
-        for (int sl = 0; sl < SLOTS; ++sl) {
-            const unsigned int d = lane + 32u * sl;
-            kn[sl] = d < hd ? load_as_float(kp + d) : 0.0f;
-            vn[sl] = d < hd ? load_as_float(vp + d) : 0.0f;
-        }
-    }
-    for (; t < t1; t += kGenericWarps) {
-#pragma unroll
-        for (int sl = 0; sl < SLOTS; ++sl) {
-            kc[sl] = kn[sl];
-            vc[sl] = vn[sl];
-        }
-        const unsigned int tn = t + kGenericWarps;
-        if (tn < t1) {
-            const KT *kp = kv_row<KT>(p.key, p, b, tn, kv_head, true);
-            const KT *vp = kv_row<KT>(p.value, p, b, tn, kv_head, false);
+        for (int u = 0; u < U; ++u) {
+            const unsigned int t = base + u;
+            const bool in_range = t < t1;
+            const KT *kp = kv_row<KT>(p.key, p, b, in_range ? t : t0, kv_head, true);
+            const KT *vp = kv_row<KT>(p.value, p, b, in_range ? t : t0, kv_head, false);
 #pragma unroll
             for (int sl = 0; sl < SLOTS; ++sl) {
                 const unsigned int d = lane + 32u * sl;
-                kn[sl] = d < hd ? load_as_float(kp + d) : 0.0f;
-                vn[sl] = d < hd ? load_as_float(vp + d) : 0.0f;
+                kc[u][sl] = (in_range && d < hd) ? load_as_float(kp + d) : 0.0f;
+                vc[u][sl] = (in_range && d < hd) ? load_as_float(vp + d) : 0.0f;
             }
         }
-        float dot[VT];
+        float dot[U][VT];
 #pragma unroll
-        for (int i = 0; i < VT; ++i) {
-            float partial = 0.0f;
+        for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int sl = 0; sl < SLOTS; ++sl) partial = fmaf(q[i][sl], kc[sl], partial);
-            dot[i] = partial;
-        }
+            for (int i = 0; i < VT; ++i) {
+                float partial = 0.0f;
+#pragma unroll
+                for (int sl = 0; sl < SLOTS; ++sl) partial = fmaf(q[i][sl], kc[u][sl], partial);
+                dot[u][i] = partial;
+            }
 #pragma unroll
         for (int offset = 16; offset; offset >>= 1)
 #pragma unroll
-            for (int i = 0; i < VT; ++i)
-                dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], offset);
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int i = 0; i < VT; ++i) {
-            if ((long long)t <= limit[i]) {
-                const float fresh = fmaxf(m[i], dot[i]);
-                const float keep = m[i] == -INFINITY ? 0.0f : expf(m[i] - fresh);
-                const float weight = expf(dot[i] - fresh);
-                l[i] = l[i] * keep + weight;
+                for (int i = 0; i < VT; ++i)
+                    dot[u][i] += __shfl_xor_sync(0xffffffffu, dot[u][i], offset);
 #pragma unroll
-                for (int sl = 0; sl < SLOTS; ++sl)
-                    acc[i][sl] = acc[i][sl] * keep + weight * vc[sl];
-                m[i] = fresh;
+        for (int u = 0; u < U; ++u) {
+            const unsigned int t = base + u;
+            if (t >= t1) break;
+#pragma unroll
+            for (int i = 0; i < VT; ++i) {
+                if ((long long)t <= limit[i]) {
+                    // dot is identical on every lane, so both branches are warp-uniform.
+                    if (dot[u][i] <= m[i]) {
+                        const float weight = exp2_fast(dot[u][i] - m[i]);
+                        l[i] += weight;
+#pragma unroll
+                        for (int sl = 0; sl < SLOTS; ++sl)
+                            acc[i][sl] = fmaf(weight, vc[u][sl], acc[i][sl]);
+                    } else {
+                        const float keep = exp2_fast(m[i] - dot[u][i]);  // 0 when m is -inf
+                        l[i] = fmaf(l[i], keep, 1.0f);
+#pragma unroll
+                        for (int sl = 0; sl < SLOTS; ++sl)
+                            acc[i][sl] = fmaf(acc[i][sl], keep, vc[u][sl]);
+                        m[i] = dot[u][i];
+                    }
+                }
             }
         }
     }
@@ -208,7 +220,7 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
         float scale_w[kGenericWarps], ll = 0.0f;
 #pragma unroll
         for (int w = 0; w < kGenericWarps; ++w) {
-            scale_w[w] = sm_m[w][i] == -INFINITY ? 0.0f : expf(sm_m[w][i] - mm);
+            scale_w[w] = sm_m[w][i] == -INFINITY ? 0.0f : exp2_fast(sm_m[w][i] - mm);
             ll += sm_l[w][i] * scale_w[w];
         }
         const float inverse = ll > 0.0f ? 1.0f / ll : 0.0f;
@@ -227,7 +239,7 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
                                      : p.partials + (item * p.max_splits + split) * (hd + 2ull);
                 part[d] = o * inverse;
                 if (d == 0) {
-                    part[hd] = mm;
+                    part[hd] = mm * 0.6931471805599453f;  // natural-log units
                     part[hd + 1] = ll;
                 }
             }
@@ -236,8 +248,71 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
 }
 
 // One CTA per (session, row, query head): folds the per-split (o, m, l)
-// triples in split order, so the result does not depend on scheduling.
-__global__ void __launch_bounds__(128)
+// triples. Eight warps share the splits (warp w takes splits w, w+8, ...), lanes
+// own head dimensions; per-warp sums are merged in warp order, so the result
+// is a fixed function of the inputs and does not depend on scheduling.
+constexpr int kCombineWarps = 8;
+
+__device__ __forceinline__ void combine_parts(const float *parts, unsigned int count,
+                                              unsigned int stride, unsigned int hd, void *output,
+                                              int output_dtype, unsigned long long out_index,
+                                              float *partial_out, int *status)
+{
+    __shared__ float sm_max[kCombineWarps];
+    __shared__ float sm_sum[kCombineWarps];
+    __shared__ float sm_acc[kCombineWarps][256];
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    // global maximum of m over the parts
+    float mm = -INFINITY;
+    for (unsigned int j = threadIdx.x; j < count; j += blockDim.x)
+        mm = fmaxf(mm, parts[(unsigned long long)j * stride + hd]);
+    mm = warp_max(mm);
+    if (lane == 0) sm_max[warp] = mm;
+    __syncthreads();
+    mm = sm_max[0];
+#pragma unroll
+    for (int w = 1; w < kCombineWarps; ++w) mm = fmaxf(mm, sm_max[w]);
+    // weighted sums over this warp's parts
+    float acc[8], ll = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (unsigned int j = warp; j < count; j += kCombineWarps) {
+        const float *part = parts + (unsigned long long)j * stride;
+        const float mj = part[hd];
+        const float weight = mj == -INFINITY ? 0.0f : part[hd + 1] * expf(mj - mm);
+        ll += weight;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const unsigned int d = lane + 32u * i;
+            if (d < hd) acc[i] = fmaf(part[d], weight, acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm_acc[warp][lane + 32 * i] = acc[i];
+    if (lane == 0) sm_sum[warp] = ll;
+    __syncthreads();
+    ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) ll += sm_sum[w];
+    for (unsigned int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kCombineWarps; ++w) o += sm_acc[w][d];
+        if (partial_out) {
+            partial_out[d] = ll > 0.0f ? o / ll : 0.0f;
+            if (d == 0) {
+                partial_out[hd] = mm;
+                partial_out[hd + 1] = ll;
+            }
+        } else {
+            const float value = o / ll;
+            if (!isfinite(value)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
+            store_output(output, output_dtype, out_index + d, value);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kCombineWarps * 32)
 gqa_combine_kernel(const yvx_gqa_problem p)
 {
     const unsigned long long item = blockIdx.x;
@@ -245,61 +320,19 @@ gqa_combine_kernel(const yvx_gqa_problem p)
     const unsigned int hd = p.head_dim;
     const SessionView s = session_view(p, b);
     const unsigned int splits = (s.kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens;
-    const float *parts = p.partials + item * p.max_splits * (hd + 2ull);
-
-    float mm = -INFINITY;
-    for (unsigned int j = 0; j < splits; ++j) mm = fmaxf(mm, parts[j * (hd + 2ull) + hd]);
-    float ll = 0.0f;
-    for (unsigned int j = 0; j < splits; ++j) {
-        const float mj = parts[j * (hd + 2ull) + hd];
-        ll += mj == -INFINITY ? 0.0f : parts[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
-    }
-    for (unsigned int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float o = 0.0f;
-        for (unsigned int j = 0; j < splits; ++j) {
-            const float mj = parts[j * (hd + 2ull) + hd];
-            const float w = mj == -INFINITY ? 0.0f : parts[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
-            o = fmaf(parts[j * (hd + 2ull) + d], w, o);
-        }
-        if (p.partial_output) {
-            float *part = p.partial_output + item * (hd + 2ull);
-            part[d] = ll > 0.0f ? o / ll : 0.0f;
-            if (d == 0) {
-                part[hd] = mm;
-                part[hd + 1] = ll;
-            }
-        } else {
-            const float value = o / ll;
-            if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
-            store_output(p.output, p.output_dtype, item * hd + d, value);
-        }
-    }
+    combine_parts(p.partials + item * p.max_splits * (hd + 2ull), splits, hd + 2u, hd, p.output,
+                  p.output_dtype, item * hd,
+                  p.partial_output ? p.partial_output + item * (hd + 2ull) : nullptr, p.status);
 }
 
 // Combine of externally gathered partials: parts[item][part][hd+2].
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kCombineWarps * 32)
 lse_combine_kernel(const float *parts, unsigned int part_count, unsigned int hd, void *output,
                    int output_dtype, int *status)
 {
     const unsigned long long item = blockIdx.x;
-    const float *base = parts + item * part_count * (hd + 2ull);
-    float mm = -INFINITY, ll = 0.0f;
-    for (unsigned int j = 0; j < part_count; ++j) mm = fmaxf(mm, base[j * (hd + 2ull) + hd]);
-    for (unsigned int j = 0; j < part_count; ++j) {
-        const float mj = base[j * (hd + 2ull) + hd];
-        ll += mj == -INFINITY ? 0.0f : base[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
-    }
-    for (unsigned int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float o = 0.0f;
-        for (unsigned int j = 0; j < part_count; ++j) {
-            const float mj = base[j * (hd + 2ull) + hd];
-            const float w = mj == -INFINITY ? 0.0f : base[j * (hd + 2ull) + hd + 1] * expf(mj - mm);
-            o = fmaf(base[j * (hd + 2ull) + d], w, o);
-        }
-        const float value = o / ll;
-        if (!isfinite(value)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
-        store_output(output, output_dtype, item * hd + d, value);
-    }
+    combine_parts(parts + item * part_count * (hd + 2ull), part_count, hd + 2u, hd, output,
+                  output_dtype, item * hd, nullptr, status);
 }
 
 template <typename QT, typename KT, int SLOTS>
@@ -341,7 +374,7 @@ int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream)
 int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream)
 {
     const unsigned long long items = (unsigned long long)p.sessions * p.query_rows * p.query_heads;
-    gqa_combine_kernel<<<(unsigned int)items, 128, 0, stream>>>(p);
+    gqa_combine_kernel<<<(unsigned int)items, kCombineWarps * 32, 0, stream>>>(p);
     return yvx_cuda_check(cudaGetLastError(), "gqa_combine_kernel");
 }
 
@@ -353,7 +386,7 @@ extern "C" int yvx_cuda_lse_combine(const float *parts, unsigned int items,
 {
     if (!parts || !items || !part_count || !head_dim || !output || !status)
         return YVEX_ERR_INVALID_ARG;
-    yvx::lse_combine_kernel<<<items, 128, 0, (cudaStream_t)stream>>>(
+    yvx::lse_combine_kernel<<<items, yvx::kCombineWarps * 32, 0, (cudaStream_t)stream>>>(
         parts, part_count, head_dim, output, output_dtype, status);
     return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
 }

@@ -106,3 +106,50 @@ int yvx_cuda_fill_f16_uniform(void *dst, unsigned long long count, unsigned long
 }
 
 }  // extern "C"
+
+namespace yvx {
+
+// Q8 records: int8 lanes uniform in [-127,127] in the lane regions and f16
+// scales uniform in [lo, hi) in the scale regions of every 17408-byte record.
+__global__ void fill_q8_records_kernel(unsigned char *records, unsigned long long record_count,
+                                       unsigned long long seed, float lo, float hi)
+{
+    const unsigned long long words_per_record = 17408ull / 4ull;
+    const unsigned long long total = record_count * words_per_record;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += stride) {
+        const unsigned long long within = (i % words_per_record) * 4ull;
+        uint64_t h = splitmix64(seed * 0xD1342543DE82EF95ull + i);
+        uint32_t word;
+        if (within < 16384ull) {
+            word = 0u;
+            for (int j = 0; j < 4; ++j) {
+                uint32_t byte = (uint32_t)(h >> (8 * j)) & 0xffu;
+                uint64_t again = h;
+                while (byte == 255u) {
+                    again = splitmix64(again + j + 1);
+                    byte = (uint32_t)again & 0xffu;
+                }
+                word |= ((uint32_t)((int)byte - 127) & 0xffu) << (8 * j);
+            }
+        } else {
+            const float u0 = (float)(uint32_t)(h >> 32) * (1.0f / 4294967296.0f);
+            const float u1 = (float)(uint32_t)h * (1.0f / 4294967296.0f);
+            word = (uint32_t)__half_as_ushort(__float2half_rn(lo + (hi - lo) * u0)) |
+                   ((uint32_t)__half_as_ushort(__float2half_rn(lo + (hi - lo) * u1)) << 16);
+        }
+        reinterpret_cast<uint32_t *>(records)[i] = word;
+    }
+}
+
+}  // namespace yvx
+
+extern "C" int yvx_cuda_fill_q8_records(void *records, unsigned long long record_count,
+                                        unsigned long long seed, float lo, float hi, void *stream)
+{
+    if (!records || !record_count) return YVEX_ERR_INVALID_ARG;
+    yvx::fill_q8_records_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(
+        (unsigned char *)records, record_count, seed, lo, hi);
+    return yvx_cuda_check(cudaGetLastError(), "fill_q8_records_kernel");
+}

@@ -184,6 +184,10 @@ int yvx_cuda_fill_q8_lanes(void *dst, unsigned long long count, unsigned long lo
                            void *stream);
 int yvx_cuda_fill_f16_uniform(void *dst, unsigned long long count, unsigned long long seed,
                               float lo, float hi, void *stream);
+/* Whole Q8 records: uniform lanes in the lane regions, f16 scales uniform in
+ * [lo, hi) in the scale regions. */
+int yvx_cuda_fill_q8_records(void *records, unsigned long long record_count,
+                             unsigned long long seed, float lo, float hi, void *stream);
 
 #ifdef __cplusplus
 }

@@ -116,8 +116,11 @@ def test_split_plan_is_deterministic_and_bounded(library):
     assert (p.chunk_tokens, p.max_splits) == (64, 64)
     p.sessions, p.kv_tokens_max = 64, 32768
     library.yvx_cuda_gqa_plan_splits(C.byref(p), 148)
-    assert p.chunk_tokens == 1024 and p.max_splits == 32
-    assert library.yvx_cuda_gqa_partials_bytes(C.byref(p)) == 64 * 32 * 32 * 130 * 4
+    assert p.chunk_tokens == 4096 and p.max_splits == 8
+    assert library.yvx_cuda_gqa_partials_bytes(C.byref(p)) == 64 * 32 * 8 * 130 * 4
+    p.sessions, p.kv_tokens_max, p.query_rows = 1, 131072, 4   # one long session: exactly one wave
+    library.yvx_cuda_gqa_plan_splits(C.byref(p), 148)
+    assert p.chunk_tokens == 3584 and p.max_splits == 37
     p.sessions, p.kv_tokens_max = 1, 3
     library.yvx_cuda_gqa_plan_splits(C.byref(p), 148)
     assert p.max_splits == 1 and library.yvx_cuda_gqa_partials_bytes(C.byref(p)) == 0
