@@ -414,6 +414,78 @@ def bench_verify_q8(lib, backend, abi, peak, repeats, chunk=None):
     return result, (head0, q_host.reshape(rows, hq * hd), o_host.reshape(rows, hq * hd))
 
 
+
+def bench_prefill(lib, backend, abi, repeats, tokens=8192, batch=2):
+    """Config 3: causal prefill, batch x tokens, 40/8 heads, hd 128, bf16 in and out.
+    Device-generated N(0, 0.5^2): RoPE is a rotation, so post-RoPE values of i.i.d.
+    normal inputs have the same distribution."""
+    hq, hkv, hd = 40, 8, 128
+    qn, kn = batch * tokens * hq * hd, batch * tokens * hkv * hd
+    q, k, v, out = _alloc(lib, qn * 2), _alloc(lib, kn * 2), _alloc(lib, kn * 2), _alloc(lib, qn * 2)
+    status = _alloc(lib, 4)
+    for ptr, n, seed in ((q, qn, 301), (k, kn, 302), (v, kn, 303)):
+        lib.yvx_cuda_fill_normal(ptr, abi.DTYPE_BF16, n, seed, 0.5, backend.stream)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    p = abi.GqaProblem()
+    p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = batch, tokens, hq, hkv, hd
+    p.causal, p.scale = 1, 1.0 / np.sqrt(hd)
+    p.query_dtype = p.kv_dtype = p.output_dtype = abi.DTYPE_BF16
+    p.query, p.query_row_stride, p.query_session_stride, p.output = q, hq * hd, tokens * hq * hd, out
+    p.key, p.value = k, v
+    p.key_token_stride = p.value_token_stride = hkv * hd
+    p.key_head_stride = p.value_head_stride = hd
+    p.key_session_stride = p.value_session_stride = tokens * hkv * hd
+    p.kv_tokens_uniform = p.kv_tokens_max = tokens
+    p.query_start_uniform = 0
+    lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+    scratch = _alloc(lib, max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+    p.partials, p.status = scratch, status
+    main, combine, launches = _timed_launches(lib, backend, [p], repeats)
+    flops = 4.0 * batch * hq * hd * tokens * (tokens + 1) / 2.0
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    # sample for the CPU check: batch 0, KV head 0, query head 0, the last 128 rows
+    rows = 128
+    q_host = np.empty((rows, hq * hd), np.uint16)
+    o_host = np.empty((rows, hq * hd), np.uint16)
+    k_host = np.empty((tokens, hkv * hd), np.uint16)
+    v_host = np.empty((tokens, hkv * hd), np.uint16)
+    lib.yvx_cuda_download_async(q_host.ctypes.data, q.value + (tokens - rows) * hq * hd * 2, q_host.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(o_host.ctypes.data, out.value + (tokens - rows) * hq * hd * 2, o_host.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(k_host.ctypes.data, k, k_host.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(v_host.ctypes.data, v, v_host.nbytes, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tf_peak, tf_kind = 1590.0, "fallback"
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            tf_peak, tf_kind = float(json.load(f)["bf16_tflops"]), "measured"
+    achieved = flops / (main * 1e-3) / 1e12
+    result = {"workload": f"causal prefill {batch} x {tokens} tokens, 40q/8kv heads, hd128, bf16",
+              "kernel": "prefill_tcgen05_kernel", "launches_per_step": launches, "kernel_ms": main,
+              "flops_causal": flops, "achieved_tflops": achieved, "peak_tflops": tf_peak,
+              "peak_kind": tf_kind + " (burst, kernel timed alone)", "frac_of_bf16_peak": achieved / tf_peak,
+              "tokens_per_s": batch * tokens / (main * 1e-3), "status_word": int(st[0]),
+              "l2": "Q+K+V+O = %.0f MB exceed L2" % ((2 * qn + 2 * kn) * 2 / 1e6)}
+    for ptr in (q, k, v, out, status, scratch):
+        lib.yvx_cuda_free(ptr)
+    return result, (q_host, k_host, v_host, o_host, tokens, rows)
+
+
+def check_prefill(engine, sample, threads):
+    from clori_b200 import bf16_bits_to_f32
+    q, k, v, o, tokens, rows = sample
+    hd = 128
+    qf = bf16_bits_to_f32(q)[:, :hd]
+    kf, vf = bf16_bits_to_f32(k)[:, :hd], bf16_bits_to_f32(v)[:, :hd]
+    start = time.perf_counter()
+    ref = engine.gqa_attention(np.ascontiguousarray(qf), np.ascontiguousarray(kf), np.ascontiguousarray(vf),
+                               tokens - rows, 1, 1, hd, threads=threads)
+    seconds = time.perf_counter() - start
+    got = bf16_bits_to_f32(o)[:, :hd]
+    return float(np.abs(ref - got).max()), seconds
+
+
 def check_decode_f32(engine, host, threads):
     start = time.perf_counter()
     ref = engine.gqa_attention(host["q"].reshape(1, -1), host["k"].reshape(4096, -1), host["v"].reshape(4096, -1),
@@ -512,9 +584,11 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "decode_f32", "verify_q8"],
+                        choices=["headline", "decode_f32", "verify_q8", "prefill"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
+    parser.add_argument("--tokens", type=int, default=8192,
+                        help="sequence length of --workload prefill (profiling captures)")
     parser.add_argument("--chunk", type=int, default=0,
                         help="override the split size of --workload verify_q8 (experiments)")
     parser.add_argument("--headline-only", action="store_true",
@@ -555,9 +629,12 @@ def main():
         import clori_b200
         from clori_b200 import abi
         backend = clori_b200.Backend(local_rank)
-        run = {"decode_f32": bench_decode_f32, "verify_q8": bench_verify_q8}[args.workload]
-        extra = {"chunk": args.chunk} if args.workload == "verify_q8" and args.chunk else {}
-        result, _ = run(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3), **extra)
+        if args.workload == "prefill":
+            result, _ = bench_prefill(abi.load(), backend, abi, max(args.steps, 3), tokens=args.tokens)
+        else:
+            run = {"decode_f32": bench_decode_f32, "verify_q8": bench_verify_q8}[args.workload]
+            extra = {"chunk": args.chunk} if args.workload == "verify_q8" and args.chunk else {}
+            result, _ = run(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3), **extra)
         print(json.dumps({"workload_only": args.workload, **result}))
         return
 
@@ -608,6 +685,7 @@ def main():
         hbm_peak = measured_peaks()[0]
         others["decode_f32_config1"], other_samples["f32"] = bench_decode_f32(lib, b, w.abi, hbm_peak, 64)
         others["verify_q8_config4_1gpu"], other_samples["q8"] = bench_verify_q8(lib, b, w.abi, hbm_peak, 20)
+        others["prefill_config3"], other_samples["prefill"] = bench_prefill(lib, b, w.abi, 10)
 
     if rank != 0:
         if dist is not None:
@@ -667,6 +745,11 @@ def main():
             others["verify_q8_config4_1gpu"].update(
                 gpu_vs_cpu_max_abs_on_sample=err, cpu_sample="KV head 0: 4 query heads x 4 rows x 131072 tokens",
                 cpu_sample_ms=seconds * 1e3, cpu_cores=threads)
+        if "prefill" in other_samples:
+            err, seconds = check_prefill(engine, other_samples["prefill"], threads)
+            others["prefill_config3"].update(
+                gpu_vs_cpu_max_abs_on_sample=err, cpu_sample_ms=seconds * 1e3, cpu_cores=threads,
+                cpu_sample="batch 0, query head 0: last 128 rows x 8192 tokens")
     if others:
         line["other_workloads"] = others
     print(json.dumps(line))

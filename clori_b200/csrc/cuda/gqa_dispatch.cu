@@ -6,6 +6,7 @@ int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 }
 
 extern "C" {
@@ -71,14 +72,19 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     if (events) cudaEventRecord(events[0], s);
     // Specialised kernels return 1 when they took the problem, 0 when its shape
     // is not theirs; the general kernel takes everything else.
+    // 1 = attention launched (a combine follows when the KV was split), 2 = launched and
+    // final, 0 = not this kernel's shape, negative = error.
     int rc = yvx::gqa_decode_q8_launch(*p, s);
-    if (rc == 0 && !p->force_general) rc = yvx::gqa_decode_mma_launch(*p, s);
+    const unsigned int vectors = p->query_rows * (p->query_heads / p->kv_heads);
+    if (rc == 0 && !p->force_general)
+        rc = vectors <= 64u ? yvx::gqa_decode_mma_launch(*p, s) : yvx::prefill_tcgen05_launch(*p, s);
+    const bool final_output = rc == 2;
     if (rc == 0) rc = yvx::gqa_generic_main_launch(*p, s);
-    else if (rc == 1) rc = 0;
+    else if (rc == 1 || rc == 2) rc = 0;
     if (rc != 0) return rc;
     count = 1u;
     if (events) cudaEventRecord(events[1], s);
-    if (p->max_splits > 1u) {
+    if (p->max_splits > 1u && !final_output) {
         rc = yvx::gqa_combine_launch(*p, s);
         if (rc != 0) return rc;
         count = 2u;

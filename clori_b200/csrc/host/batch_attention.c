@@ -39,14 +39,14 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
                         "complete batch tensors and result facts are required");
     r = &request->requirement;
     if (!request->session_count || request->session_count > 0xffffull || !r->query_tokens ||
-        r->query_tokens > 8ull || !r->key_value_tokens ||
+        r->query_tokens > 0xffffffffull || !r->key_value_tokens ||
         r->key_value_tokens > 0xffffffffull - 1024ull || r->query_tokens > r->key_value_tokens ||
         !r->query_heads || !r->key_value_heads || r->query_heads % r->key_value_heads ||
         !r->head_dimension || !yvx_u64_mul(r->query_heads, r->head_dimension, &query_width) ||
         !yvx_u64_mul(r->key_value_heads, r->head_dimension, &kv_width) ||
         (r->query_token_stride && r->query_token_stride < query_width))
         return yvx_fail(err, YVEX_ERR_INVALID_ARG, where,
-                        "complete batched attention geometry is required (1..8 rows per session)");
+                        "complete batched attention geometry is required");
     if (r->layout != YVEX_TRANSFORMER_ATTENTION_LAYOUT_TOKEN_HEAD_DIM ||
         r->mask < YVEX_TRANSFORMER_ATTENTION_MASK_FULL ||
         r->mask > YVEX_TRANSFORMER_ATTENTION_MASK_CAUSAL || r->head_dimension > 256ull ||
