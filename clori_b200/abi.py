@@ -140,6 +140,20 @@ class GqaProblem(C.Structure):
     ]
 
 
+class MlaProblem(C.Structure):
+    """yvx_mla_problem (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [
+        ("sessions", C.c_uint), ("heads", C.c_uint), ("nope_dim", C.c_uint), ("latent_dim", C.c_uint),
+        ("rope_dim", C.c_uint), ("scale", C.c_float),
+        ("q_nope", C.c_void_p), ("q_rope", C.c_void_p), ("w_uk", C.c_void_p), ("latent", C.c_void_p),
+        ("rope_key", C.c_void_p), ("latent_session_stride", u64), ("rope_session_stride", u64),
+        ("kv_tokens", C.c_void_p), ("kv_tokens_uniform", C.c_uint), ("kv_tokens_max", C.c_uint),
+        ("chunk_tokens", C.c_uint), ("max_splits", C.c_uint),
+        ("q_absorbed", C.c_void_p), ("partials", C.c_void_p), ("output", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 # Every symbol the headers declare; tests check the library exports each one.
 EXPORTED_SYMBOLS = [
     # attention.h
@@ -167,6 +181,8 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
+    "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
+    "yvx_cuda_mla_decode",
 ]
 
 _lib = None
@@ -246,6 +262,13 @@ def load():
     lib.yvx_cuda_gqa_static_scratch_capacity.restype = u64
     lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
     lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
+    lib.yvx_cuda_mla_plan.restype = None
+    lib.yvx_cuda_mla_plan.argtypes = [P(MlaProblem), C.c_int]
+    lib.yvx_cuda_mla_absorbed_bytes.restype = u64
+    lib.yvx_cuda_mla_absorbed_bytes.argtypes = [P(MlaProblem)]
+    lib.yvx_cuda_mla_partials_bytes.restype = u64
+    lib.yvx_cuda_mla_partials_bytes.argtypes = [P(MlaProblem)]
+    lib.yvx_cuda_mla_decode.argtypes = [P(MlaProblem), vp, vp, P(C.c_uint)]
     lib.yvx_cuda_fill_q8_records.argtypes = [vp, u64, u64, C.c_float, C.c_float, vp]
     lib.yvx_cuda_q8_record_bytes.restype = u64
     lib.yvx_cuda_q8_record_bytes.argtypes = []

@@ -1,0 +1,472 @@
+// Latent-compressed (MLA-style) decode on sm_100a: 128 query heads over one
+// shared [latent 512 | rope 64] row per position, bf16, f32 accumulation.
+//
+// Arithmetic intensity sits at the machine's ridge (about 242 flop per byte),
+// so the attention runs on the 5th-generation tensor cores with all 128 heads
+// in the M dimension of one tcgen05.mma:
+//   S[128 x 32]  = Q_abs[128 x 576] . K_tile^T        (36 k-steps, A and B in smem)
+//   O[128 x 256] += P[128 x 32] . latent_tile[32 x 256] (A = P in tensor memory)
+// A 32-token tile is loaded ONCE into shared memory and serves as K (K-major)
+// and as V (the same bytes read MN-major). The f32 output of 128 heads x 512
+// dims would fill all of tensor memory, so a CTA owns one half of the latent
+// dims (256 accumulator columns) and recomputes S; the two CTAs of a pair run
+// side by side and share their tile through L2.
+#include "tcgen05.cuh"
+
+namespace yvx {
+
+constexpr int kMlaHeads = 128, kMlaNope = 128, kMlaLatent = 512, kMlaRope = 64;
+constexpr int kMlaWidth = kMlaLatent + kMlaRope;          // 576
+constexpr int kMlaN = 32;                                  // tokens per tile
+constexpr int kMlaHalf = kMlaLatent / 2;                   // accumulator columns per CTA
+constexpr int kMlaStages = 2;
+constexpr int kMlaThreads = 192;
+constexpr int kMlaQSubBytes = kMlaHeads * 64 * 2;          // [128][64] bf16 = 16 KB
+constexpr int kMlaQBytes = (kMlaWidth / 64) * kMlaQSubBytes;   // 9 sub-tiles
+constexpr int kMlaKvSubBytes = kMlaN * 64 * 2;             // [32][64] bf16 = 4 KB
+constexpr int kMlaKvBytes = (kMlaWidth / 64) * kMlaKvSubBytes; // 36 KB
+constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256;
+constexpr uint32_t kMlaTmemColumns = 512;
+constexpr float kMlaRescaleThreshold = 8.0f;
+
+struct MlaMaps {
+    CUtensorMap query, latent, rope;
+};
+
+struct MlaBarriers {
+    uint64_t q_full;
+    uint64_t kv_full[kMlaStages], k_done[kMlaStages], v_done[kMlaStages];
+    uint64_t s_full[2], p_full[2];
+    uint64_t pv_done;
+    uint32_t tmem_base;
+};
+
+// ---- absorb: q_abs[b][h] = [ bf16(q_nope[b][h] . W_uk[h]) | q_rope[b][h] ] ----------
+// grid (heads, ceil(sessions/16)); 4 warps, warp w owns latent columns [128w, 128w+128).
+constexpr int kAbsorbPitch = 128 * 2 + 16;  // padded row of 128 bf16
+constexpr int kAbsorbSmem = 16 * kAbsorbPitch + 4 * 128 * kAbsorbPitch;
+
+__global__ void __launch_bounds__(128)
+mla_absorb_kernel(const yvx_mla_problem p)
+{
+    extern __shared__ unsigned char absorb_smem[];
+    unsigned char *a_smem = absorb_smem;                       // [16 sessions][128 nope]
+    unsigned char *w_smem = absorb_smem + 16 * kAbsorbPitch;   // [4 warps][128 k][128 n]
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned int head = blockIdx.x, session0 = blockIdx.y * 16u;
+    const __nv_bfloat16 *q_nope = reinterpret_cast<const __nv_bfloat16 *>(p.q_nope);
+    const __nv_bfloat16 *w = reinterpret_cast<const __nv_bfloat16 *>(p.w_uk) +
+                             (unsigned long long)head * kMlaNope * kMlaLatent;
+    // A: 16 rows x 16 chunks of 16 bytes
+    for (unsigned int i = threadIdx.x; i < 16u * 16u; i += 128u) {
+        const unsigned int row = i >> 4, chunk = i & 15u;
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (session0 + row < p.sessions)
+            value = *reinterpret_cast<const uint4 *>(
+                q_nope + ((unsigned long long)(session0 + row) * kMlaHeads + head) * kMlaNope + chunk * 8u);
+        *reinterpret_cast<uint4 *>(a_smem + row * kAbsorbPitch + chunk * 16u) = value;
+    }
+    // B: each warp stages its [128 k][128 n] block of W_uk[head]
+    unsigned char *wb = w_smem + warp * 128 * kAbsorbPitch;
+    for (unsigned int i = lane; i < 128u * 16u; i += 32u) {
+        const unsigned int k = i >> 4, chunk = i & 15u;
+        *reinterpret_cast<uint4 *>(wb + k * kAbsorbPitch + chunk * 16u) =
+            *reinterpret_cast<const uint4 *>(w + (unsigned long long)k * kMlaLatent + warp * 128u + chunk * 8u);
+    }
+    __syncthreads();
+    uint32_t qa[8][4];
+    {
+        const unsigned int j = lane >> 3, i = lane & 7u;
+        const uint32_t base = smem_u32(a_smem) + (8u * (j & 1u) + i) * kAbsorbPitch + 16u * (j >> 1);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], base + ks * 32u);
+    }
+    float acc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.0f;
+    {
+        const unsigned int j = lane >> 3, i = lane & 7u;
+        const uint32_t wbase = smem_u32(wb);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, wbase + (16u * ks + 8u * (j & 1u) + i) * kAbsorbPitch +
+                                         (16u * np + 8u * (j >> 1)) * 2u);
+                mma_bf16(acc[2 * np], qa[ks], b[0], b[1]);
+                mma_bf16(acc[2 * np + 1], qa[ks], b[2], b[3]);
+            }
+    }
+    const unsigned int g = lane >> 2, c = lane & 3u;
+    unsigned short *out = reinterpret_cast<unsigned short *>(p.q_absorbed);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const unsigned int session = session0 + g + 8u * h;
+        if (session >= p.sessions) continue;
+        unsigned short *dst = out + ((unsigned long long)session * kMlaHeads + head) * kMlaWidth + warp * 128u;
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+            *reinterpret_cast<uint32_t *>(dst + 8 * n + 2 * c) = pack_bf16(acc[n][2 * h], acc[n][2 * h + 1]);
+    }
+    // rope part: copied through
+    const unsigned short *q_rope = reinterpret_cast<const unsigned short *>(p.q_rope);
+    for (unsigned int i = threadIdx.x; i < 16u * 8u; i += 128u) {
+        const unsigned int row = i >> 3, chunk = i & 7u;
+        if (session0 + row >= p.sessions) continue;
+        const unsigned long long item = (unsigned long long)(session0 + row) * kMlaHeads + head;
+        *reinterpret_cast<uint4 *>(out + item * kMlaWidth + kMlaLatent + chunk * 8u) =
+            *reinterpret_cast<const uint4 *>(q_rope + item * kMlaRope + chunk * 8u);
+    }
+}
+
+// ---- attention: grid (2 latent halves, splits, sessions) -----------------------------
+__global__ void __launch_bounds__(kMlaThreads, 1)
+mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps maps)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    unsigned char *q_tile = smem;
+    unsigned char *kv_tiles = smem + kMlaQBytes;
+    MlaBarriers *bars = reinterpret_cast<MlaBarriers *>(kv_tiles + kMlaStages * kMlaKvBytes);
+
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned int half = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+    const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    const unsigned int t0 = split * p.chunk_tokens;
+    const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
+    const unsigned long long part_stride = kMlaHalf + 2;
+    if (t0 >= t1) {
+        // Nothing of this session falls into the split: publish an empty partial.
+        if (threadIdx.x < (unsigned)kMlaHeads) {
+            float *part = p.partials +
+                          ((((unsigned long long)b * kMlaHeads + threadIdx.x) * 2ull + half) * p.max_splits + split) *
+                              part_stride;
+            for (int d = 0; d < kMlaHalf; ++d) part[d] = 0.0f;
+            part[kMlaHalf] = -INFINITY;
+            part[kMlaHalf + 1] = 0.0f;
+        }
+        return;
+    }
+    const unsigned int tiles = (t1 - t0 + kMlaN - 1) / kMlaN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        for (int i = 0; i < kMlaStages; ++i) {
+            mbar_init(&bars->kv_full[i], 1);
+            mbar_init(&bars->k_done[i], 1);
+            mbar_init(&bars->v_done[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->s_full[i], 1);
+            mbar_init(&bars->p_full[i], kMlaHeads);
+        }
+        mbar_init(&bars->pv_done, 1);
+        fence_barrier_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(&bars->tmem_base, kMlaTmemColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = bars->tmem_base;
+    const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf;  // O: 256 columns, then two 32-column S buffers
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_expect_tx(&bars->q_full, kMlaQBytes);
+            for (int st = 0; st < kMlaWidth / 64; ++st)
+                tma_load_3d(q_tile + st * kMlaQSubBytes, &maps.query, &bars->q_full, 64 * st, 0, (int)b);
+            for (unsigned int j = 0; j < tiles; ++j) {
+                const unsigned int stage = j % kMlaStages;
+                if (j >= (unsigned)kMlaStages &&
+                    !mbar_wait(&bars->v_done[stage], ((j / kMlaStages) - 1u) & 1u)) {
+                    atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+                    break;
+                }
+                unsigned char *dst = kv_tiles + stage * kMlaKvBytes;
+                const int token = (int)(t0 + j * kMlaN);
+                mbar_expect_tx(&bars->kv_full[stage], kMlaKvBytes);
+                for (int st = 0; st < kMlaLatent / 64; ++st)
+                    tma_load_3d(dst + st * kMlaKvSubBytes, &maps.latent, &bars->kv_full[stage], 64 * st, token, (int)b);
+                tma_load_3d(dst + (kMlaLatent / 64) * kMlaKvSubBytes, &maps.rope, &bars->kv_full[stage], 0, token, (int)b);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
+            constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
+            const uint32_t q_addr = smem_u32(q_tile);
+            bool ok = mbar_wait(&bars->q_full, 0);
+            auto issue_qk = [&](unsigned int j) -> bool {
+                const unsigned int stage = j % kMlaStages;
+                if (!mbar_wait(&bars->kv_full[stage], (j / kMlaStages) & 1u)) return false;
+                tc_fence_after_sync();
+                const uint32_t kv_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
+                const uint32_t d = tmem_s + (j & 1u) * kMlaN;
+#pragma unroll 4
+                for (int ks = 0; ks < kMlaWidth / 16; ++ks) {
+                    const uint32_t sub = ks >> 2, off = (ks & 3) * 32;
+                    tc_mma_ss(d, smem_desc_sw128(q_addr + sub * kMlaQSubBytes + off, 16, 1024),
+                              smem_desc_sw128(kv_addr + sub * kMlaKvSubBytes + off, 16, 1024), idesc_qk,
+                              ks ? 1u : 0u);
+                }
+                tc_commit(&bars->s_full[j & 1u]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (unsigned int j = 0; ok && j < tiles; ++j) {
+                if (j + 1 < tiles) ok = issue_qk(j + 1);
+                if (!ok) break;
+                const unsigned int stage = j % kMlaStages;
+                if (!mbar_wait(&bars->p_full[j & 1u], (j >> 1) & 1u)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t v_addr = smem_u32(kv_tiles + stage * kMlaKvBytes) + 4u * half * kMlaKvSubBytes;
+                const uint32_t p_tmem = tmem_s + (j & 1u) * kMlaN;
+#pragma unroll
+                for (int kk = 0; kk < kMlaN / 16; ++kk)
+                    tc_mma_ts(tmem_o, p_tmem + kk * 8, smem_desc_sw128(v_addr + kk * 2048, kMlaKvSubBytes, 1024),
+                              idesc_pv, (j || kk) ? 1u : 0u);
+                tc_commit(&bars->v_done[stage]);
+                tc_commit(&bars->pv_done);
+            }
+            if (!ok) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+        }
+    } else {
+        // ------------------------------ softmax warps -----------------------------
+        const unsigned int head = threadIdx.x;
+        const uint32_t lane_base = ((warp * 32u) << 16);
+        const float sscale = p.scale * 1.4426950408889634f;
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (unsigned int j = 0; j < tiles; ++j) {
+            const unsigned int buf = j & 1u;
+            if (!mbar_wait(&bars->s_full[buf], (j >> 1) & 1u)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            uint32_t s[32];
+            tmem_ld32(tmem_s + lane_base + buf * kMlaN, s);
+            tmem_wait_ld();
+            const unsigned int k0 = t0 + j * kMlaN;
+            float row_max = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                if (k0 + c >= t1) s[c] = 0xff800000u;
+                row_max = fmaxf(row_max, __uint_as_float(s[c]));
+            }
+            const float m_tile = row_max * sscale;
+            const bool grow = m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_used, m_tile);
+                const float factor = m_new == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
+                l *= factor;
+                m_used = m_new;
+                if (j > 0) {
+                    if (!mbar_wait(&bars->pv_done, (j - 1u) & 1u)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll 1
+                    for (int i = 0; i < kMlaHalf / 32; ++i) {
+                        uint32_t o[32];
+                        tmem_ld32(tmem_o + lane_base + 32 * i, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                        tmem_st32(tmem_o + lane_base + 32 * i, o);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            const float offset = m_used == -INFINITY ? 0.0f : -m_used;
+            uint32_t packed[16];
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                const float p0 = exp2_approx(fmaf(__uint_as_float(s[c]), sscale, offset));
+                const float p1 = exp2_approx(fmaf(__uint_as_float(s[c + 1]), sscale, offset));
+                const uint32_t pair = pack_bf16(p0, p1);
+                sum += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
+                packed[c >> 1] = pair;
+            }
+            l += sum;
+            tmem_st16(tmem_s + lane_base + buf * kMlaN, packed);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bars->p_full[buf]);
+        }
+        if (ok) ok = mbar_wait(&bars->pv_done, (tiles - 1u) & 1u);
+        if (!__all_sync(0xffffffffu, ok)) {
+            atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+        } else {
+            tc_fence_after_sync();
+            const float inverse = l > 0.0f ? 1.0f / l : 0.0f;
+            float *part = p.partials +
+                          ((((unsigned long long)b * kMlaHeads + head) * 2ull + half) * p.max_splits + split) *
+                              part_stride;
+#pragma unroll 1
+            for (int i = 0; i < kMlaHalf / 32; ++i) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_base + 32 * i, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    *reinterpret_cast<float2 *>(part + 32 * i + c) =
+                        make_float2(__uint_as_float(o[c]) * inverse, __uint_as_float(o[c + 1]) * inverse);
+            }
+            part[kMlaHalf] = m_used == -INFINITY ? -INFINITY : m_used * 0.6931471805599453f;
+            part[kMlaHalf + 1] = l;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, kMlaTmemColumns);
+}
+
+// ---- host side ------------------------------------------------------------------------
+
+typedef CUresult (*MlaEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                     const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static MlaEncodeTiledFn mla_encode_entry()
+{
+    static MlaEncodeTiledFn entry = nullptr;
+    static bool resolved = false;
+    if (!resolved) {
+        void *symbol = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &query) ==
+                cudaSuccess &&
+            query == cudaDriverEntryPointSuccess)
+            entry = reinterpret_cast<MlaEncodeTiledFn>(symbol);
+        resolved = true;
+    }
+    return entry;
+}
+
+// 3-D bf16 map {width, rows, outer}, box 64 x box_rows x 1, 128-byte swizzle.
+static bool mla_encode(CUtensorMap *map, const void *base, unsigned long long width,
+                       unsigned long long rows, unsigned long long outer,
+                       unsigned long long outer_stride, unsigned int box_rows)
+{
+    MlaEncodeTiledFn encode = mla_encode_entry();
+    if (!encode || (reinterpret_cast<uintptr_t>(base) & 15u)) return false;
+    unsigned long long ob = outer_stride * 2ull;
+    if (outer <= 1ull || !ob) {
+        if (outer > 1ull) return false;
+        outer = 1ull;
+        ob = rows * width * 2ull;
+    }
+    if (ob & 15ull) return false;
+    cuuint64_t dims[3] = {width, rows, outer};
+    cuuint64_t strides[2] = {width * 2ull, ob};
+    cuuint32_t box[3] = {64, box_rows, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims, strides,
+                  box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace yvx
+
+extern "C" {
+
+// One CTA per SM is resident (shared memory), so a wave is sm_count work items:
+// sessions x 2 halves x splits. The chunk is the largest multiple of 32 tokens,
+// at most 8192, that makes at least one wave and fills the last one to 90 %.
+void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
+{
+    if (!p) return;
+    const unsigned long long wave = (unsigned long long)(sm_count > 0 ? sm_count : 148);
+    const unsigned long long lanes = 2ull * p->sessions;
+    unsigned int best = 0u;
+    double best_fill = -1.0;
+    for (unsigned int chunk = 8192u; chunk >= 32u; chunk -= 32u) {
+        const unsigned long long splits = ((unsigned long long)p->kv_tokens_max + chunk - 1ull) / chunk;
+        const unsigned long long items = lanes * splits;
+        if (items < wave) continue;
+        const unsigned long long waves = (items + wave - 1ull) / wave;
+        const double fill = (double)items / (double)(waves * wave);
+        if (fill >= 0.9) {
+            best = chunk;
+            break;
+        }
+        if (fill > best_fill) {
+            best_fill = fill;
+            best = chunk;
+        }
+    }
+    p->chunk_tokens = best ? best : 32u;
+    p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
+    if (!p->max_splits) p->max_splits = 1u;
+}
+
+unsigned long long yvx_cuda_mla_absorbed_bytes(const yvx_mla_problem *p)
+{
+    return p ? (unsigned long long)p->sessions * p->heads * (p->latent_dim + p->rope_dim) * 2ull : 0ull;
+}
+
+unsigned long long yvx_cuda_mla_partials_bytes(const yvx_mla_problem *p)
+{
+    return p ? (unsigned long long)p->sessions * p->heads * 2ull * p->max_splits *
+                   (p->latent_dim / 2ull + 2ull) * sizeof(float)
+             : 0ull;
+}
+
+int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4], unsigned int *launches)
+{
+    using namespace yvx;
+    if (launches) *launches = 0;
+    if (!p || !p->q_nope || !p->q_rope || !p->w_uk || !p->latent || !p->rope_key || !p->q_absorbed ||
+        !p->partials || !p->output || !p->status || !p->sessions || !p->kv_tokens_max ||
+        !p->chunk_tokens || !p->max_splits || p->chunk_tokens % kMlaN)
+        return YVEX_ERR_INVALID_ARG;
+    if (p->heads != (unsigned)kMlaHeads || p->nope_dim != (unsigned)kMlaNope ||
+        p->latent_dim != (unsigned)kMlaLatent || p->rope_dim != (unsigned)kMlaRope)
+        return YVEX_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    MlaMaps maps;
+    if (!mla_encode(&maps.query, p->q_absorbed, kMlaWidth, kMlaHeads, p->sessions,
+                    (unsigned long long)kMlaHeads * kMlaWidth, kMlaHeads) ||
+        !mla_encode(&maps.latent, p->latent, kMlaLatent, p->kv_tokens_max, p->sessions,
+                    p->latent_session_stride, kMlaN) ||
+        !mla_encode(&maps.rope, p->rope_key, kMlaRope, p->kv_tokens_max, p->sessions,
+                    p->rope_session_stride, kMlaN))
+        return YVEX_ERR_UNSUPPORTED;
+    cudaError_t error = cudaFuncSetAttribute(mla_absorb_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kAbsorbSmem);
+    if (error == cudaSuccess)
+        error = cudaFuncSetAttribute(mla_decode_tcgen05_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes);
+    if (error != cudaSuccess) return yvx_cuda_check(error, "mla kernel attributes");
+    if (events) cudaEventRecord((cudaEvent_t)events[0], s);
+    mla_absorb_kernel<<<dim3(kMlaHeads, (p->sessions + 15u) / 16u), 128, kAbsorbSmem, s>>>(*p);
+    if (events) cudaEventRecord((cudaEvent_t)events[1], s);
+    mla_decode_tcgen05_kernel<<<dim3(2, p->max_splits, p->sessions), kMlaThreads, kMlaSmemBytes, s>>>(*p, maps);
+    if (events) cudaEventRecord((cudaEvent_t)events[2], s);
+    int rc = yvx_cuda_check(cudaGetLastError(), "mla kernels");
+    if (rc != 0) return rc;
+    rc = yvx_cuda_lse_combine(p->partials, p->sessions * kMlaHeads * 2u, p->max_splits, kMlaHalf,
+                              p->output, YVEX_DTYPE_F32, p->status, stream);
+    if (events) cudaEventRecord((cudaEvent_t)events[3], s);
+    if (rc != 0) return rc;
+    if (launches) *launches = 3u;
+    return 0;
+}
+
+}  // extern "C"

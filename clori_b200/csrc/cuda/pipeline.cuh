@@ -75,6 +75,17 @@ __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, u
         : "memory");
 }
 
+// 3-D tiled TMA load into shared memory, completion counted on `bar`.
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar,
+                                            int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
 // Linear bulk copy global -> shared (16-byte aligned addresses and size).
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes,
                                           uint64_t *bar)

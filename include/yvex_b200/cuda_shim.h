@@ -152,6 +152,41 @@ int yvx_cuda_op_attention_f32(const float *query, const float *keys, const float
                               float *scores, float *probabilities, float *out,
                               void *stream);
 
+/* ---- latent-compressed (MLA-style) decode -----------------------------------------
+ * One query token per session; every query head attends over ONE shared row per
+ * position: score = scale * (q_lat[h] . latent[t] + q_rope[h] . rope_key[t]),
+ * out[h] = sum_t softmax_t(score) * latent[t]. The up-projection is absorbed into
+ * the query first: q_lat[h] = bf16(q_nope[h] . W_uk[h]) (f32 accumulation).
+ * The reference's latent path (yvex_attention_reduce_native,
+ * src/backend/cuda/attention_kernels.cu:259-406) keeps its rope dimensions inside
+ * the shared row and has no absorbed projection; this variant is an extension.
+ * Shapes: heads 128, nope 128, latent 512, rope 64, all bf16; output f32.
+ * Strides are elements. */
+typedef struct yvx_mla_problem {
+    unsigned int sessions, heads, nope_dim, latent_dim, rope_dim;
+    float scale;
+    const void *q_nope;    /* bf16 [session][head][nope_dim] */
+    const void *q_rope;    /* bf16 [session][head][rope_dim] */
+    const void *w_uk;      /* bf16 [head][nope_dim][latent_dim] */
+    const void *latent;    /* bf16 [session][token][latent_dim] */
+    const void *rope_key;  /* bf16 [session][token][rope_dim] */
+    unsigned long long latent_session_stride, rope_session_stride;
+    const unsigned int *kv_tokens; /* device [sessions]; NULL = uniform */
+    unsigned int kv_tokens_uniform, kv_tokens_max;
+    unsigned int chunk_tokens, max_splits; /* filled by yvx_cuda_mla_plan */
+    void *q_absorbed;      /* scratch bf16 [session][head][latent_dim + rope_dim] */
+    float *partials;       /* scratch [session][head][2][max_splits][latent_dim/2 + 2] */
+    float *output;         /* f32 [session][head][latent_dim] */
+    int *status;
+} yvx_mla_problem;
+void yvx_cuda_mla_plan(yvx_mla_problem *problem, int sm_count);
+unsigned long long yvx_cuda_mla_absorbed_bytes(const yvx_mla_problem *problem);
+unsigned long long yvx_cuda_mla_partials_bytes(const yvx_mla_problem *problem);
+/* Absorb, attention, combine: 3 launches. events (optional, 4 cudaEvent_t as
+ * void*): before absorb, after absorb, after attention, after combine. */
+int yvx_cuda_mla_decode(const yvx_mla_problem *problem, void *stream, void *events[4],
+                        unsigned int *launches);
+
 /* ---- Q8_0 KV records -----------------------------------------------------------
  * No counterpart in the reference (its KV state is F32; Q8_0 exists there as a
  * weight qtype only: src/gguf/quant_block.c:160-187,819-832). A record is the

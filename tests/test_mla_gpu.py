@@ -1,0 +1,80 @@
+"""Latent-compressed (MLA-style) decode on a B200 against the CPU restatement
+(no reference counterpart exists for the split-rope / absorbed variant; the
+restatement follows the reference's ordering and precision rules). bf16
+operands: max-abs <= 2e-3, cosine >= 0.9999."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import clori_b200
+from clori_b200 import abi, workloads
+
+pytestmark = pytest.mark.gpu
+
+
+def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale):
+    lib = backend.lib
+    sessions, heads, nope = q_nope.shape
+    cap, dc = latent.shape[1], latent.shape[2]
+    dr = q_rope.shape[2]
+    p = abi.MlaProblem()
+    p.sessions, p.heads, p.nope_dim, p.latent_dim, p.rope_dim, p.scale = sessions, heads, nope, dc, dr, scale
+    t = {n: backend.tensor(n, a) for n, a in (("qn", q_nope), ("qr", q_rope), ("w", w_uk), ("lat", latent),
+                                              ("rk", rope_key))}
+    p.q_nope, p.q_rope, p.w_uk = t["qn"].data_ptr, t["qr"].data_ptr, t["w"].data_ptr
+    p.latent, p.rope_key = t["lat"].data_ptr, t["rk"].data_ptr
+    p.latent_session_stride, p.rope_session_stride = cap * dc, cap * dr
+    lens = backend.tensor("lens", np.asarray(lengths, np.int32))
+    p.kv_tokens, p.kv_tokens_max = lens.data_ptr, cap
+    lib.yvx_cuda_mla_plan(C.byref(p), backend.sm_count)
+    q_abs = backend.alloc("qabs", abi.DTYPE_BF16, (sessions, heads, dc + dr))
+    parts = backend.alloc("parts", abi.DTYPE_F32, (1,), lib.yvx_cuda_mla_partials_bytes(C.byref(p)))
+    out = backend.alloc("out", abi.DTYPE_F32, (sessions, heads, dc))
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    p.q_absorbed, p.partials, p.output, p.status = q_abs.data_ptr, parts.data_ptr, out.data_ptr, status.data_ptr
+    launches = C.c_uint()
+    rc = lib.yvx_cuda_mla_decode(C.byref(p), backend.stream, None, C.byref(launches))
+    assert rc == 0, lib.yvx_cuda_last_error_text()
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    out.struct.is_written = 1
+    q_abs.struct.is_written = 1
+    return out.read(), q_abs.read(), int(status.read()[0]), launches.value, (p.chunk_tokens, p.max_splits)
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64).ravel(), b.astype(np.float64).ravel()
+    return float(a @ b / np.sqrt((a @ a) * (b @ b)))
+
+
+@pytest.mark.parametrize("sessions,context", [(1, 32), (2, 100), (3, 700)])
+def test_mla_decode_matches_restatement(backend, oracle, sessions, context):
+    qn, qr, w, lat, rk = workloads.mla_decode_bf16(seed=4, batch=sessions, context=context)
+    lengths = [context] * sessions
+    if sessions > 1:
+        lengths[1] = max(1, context - 37)  # ragged: a length that is not a tile multiple
+    scale = 1.0 / np.sqrt(192.0)
+    out, q_abs, status, launches, plan = run_mla(backend, qn, qr, w, lat, rk, lengths, scale)
+    assert status == 0 and launches == 3
+    for s in range(sessions):
+        n = lengths[s]
+        ref = oracle.mla_decode(qn[s], qr[s], w, lat[s, :n], rk[s, :n], scale)
+        assert np.abs(out[s] - ref).max() <= 2e-3, float(np.abs(out[s] - ref).max())
+        assert cosine(out[s], ref) >= 0.9999
+    # the absorbed query: bf16 of an f32-accumulated product, within one bf16 ulp of the f64 one
+    f = clori_b200.bf16_bits_to_f32
+    exact = np.einsum("bhi,hic->bhc", f(qn).astype(np.float64), f(w).astype(np.float64))
+    got = f(q_abs[:, :, :512]).astype(np.float64)
+    assert np.all(np.abs(got - exact) <= 2.0 ** -8 * np.abs(exact) + 1e-6)
+    assert np.array_equal(q_abs[:, :, 512:], qr)
+
+
+def test_mla_refuses_other_geometries(backend):
+    p = abi.MlaProblem()
+    p.sessions, p.heads, p.nope_dim, p.latent_dim, p.rope_dim = 1, 64, 128, 512, 64
+    p.kv_tokens_max, p.chunk_tokens, p.max_splits = 64, 32, 2
+    dummy = backend.alloc("d", abi.DTYPE_F32, (64,))
+    for f in ("q_nope", "q_rope", "w_uk", "latent", "rope_key", "q_absorbed", "partials", "output", "status"):
+        setattr(p, f, dummy.data_ptr)
+    n = C.c_uint()
+    assert backend.lib.yvx_cuda_mla_decode(C.byref(p), backend.stream, None, C.byref(n)) == abi.YVEX_ERR_UNSUPPORTED
