@@ -486,6 +486,95 @@ def check_prefill(engine, sample, threads):
     return float(np.abs(ref - got).max()), seconds
 
 
+
+def bench_mla(lib, backend, abi, hbm_peak, repeats, sessions=32, context=16384):
+    """Config 5: latent-compressed decode, 128 heads, latent 512 + rope 64, bf16."""
+    heads, nope, dc, dr = 128, 128, 512, 64
+    sizes = {"q_nope": sessions * heads * nope, "q_rope": sessions * heads * dr, "w_uk": heads * nope * dc,
+             "latent": sessions * context * dc, "rope_key": sessions * context * dr}
+    bufs = {k: _alloc(lib, n * 2) for k, n in sizes.items()}
+    for i, (k, n) in enumerate(sizes.items()):
+        sigma = 1.0 / np.sqrt(dc) if k == "w_uk" else 1.0
+        lib.yvx_cuda_fill_normal(bufs[k], abi.DTYPE_BF16, n, 401 + i, sigma, backend.stream)
+    p = abi.MlaProblem()
+    p.sessions, p.heads, p.nope_dim, p.latent_dim, p.rope_dim = sessions, heads, nope, dc, dr
+    p.scale = 1.0 / np.sqrt(192.0)
+    p.q_nope, p.q_rope, p.w_uk = bufs["q_nope"], bufs["q_rope"], bufs["w_uk"]
+    p.latent, p.rope_key = bufs["latent"], bufs["rope_key"]
+    p.latent_session_stride, p.rope_session_stride = context * dc, context * dr
+    p.kv_tokens_uniform = p.kv_tokens_max = context
+    lib.yvx_cuda_mla_plan(C.byref(p), backend.sm_count)
+    q_abs = _alloc(lib, lib.yvx_cuda_mla_absorbed_bytes(C.byref(p)))
+    parts = _alloc(lib, lib.yvx_cuda_mla_partials_bytes(C.byref(p)))
+    out = _alloc(lib, sessions * heads * dc * 4)
+    status = _alloc(lib, 4)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    p.q_absorbed, p.partials, p.output, p.status = q_abs, parts, out, status
+
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    n = C.c_uint()
+    for _ in range(3):
+        assert lib.yvx_cuda_mla_decode(C.byref(p), backend.stream, None, C.byref(n)) == 0, lib.yvx_cuda_last_error_text()
+    quads = [tuple(event() for _ in range(4)) for _ in range(repeats)]
+    for quad in quads:
+        rc = lib.yvx_cuda_mla_decode(C.byref(p), backend.stream, (C.c_void_p * 4)(*quad), C.byref(n))
+        assert rc == 0, lib.yvx_cuda_last_error_text()
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    ms = C.c_float()
+    spans = [[], [], []]
+    for quad in quads:
+        for i in range(3):
+            lib.yvx_cuda_event_elapsed_ms(quad[i], quad[i + 1], C.byref(ms))
+            spans[i].append(ms.value)
+        for e in quad:
+            lib.yvx_cuda_event_destroy(e)
+    absorb, attend, combine = (float(np.mean(x)) for x in spans)
+    nbytes = sessions * context * (dc + dr) * 2 + sizes["w_uk"] * 2 + sessions * heads * ((nope + dr) * 2 + dc * 4)
+    flops = 2.0 * sessions * heads * context * (dc + dr + dc) + 2.0 * sessions * heads * nope * dc
+    # sample for the CPU check: session 0, heads 0..7
+    h = 8
+    host = {"q_nope": np.empty((h, nope), np.uint16), "q_rope": np.empty((h, dr), np.uint16),
+            "w_uk": np.empty((h, nope, dc), np.uint16), "latent": np.empty((context, dc), np.uint16),
+            "rope_key": np.empty((context, dr), np.uint16)}
+    for k, a in host.items():
+        lib.yvx_cuda_download_async(a.ctypes.data, bufs[k], a.nbytes, backend.stream)
+    o_host = np.empty((h, dc), np.float32)
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(o_host.ctypes.data, out, o_host.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    total = absorb + attend + combine
+    tf_peak = 1699.0
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            tf_peak = float(json.load(f)["bf16_tflops"])
+    result = {"workload": f"latent decode, {sessions} sessions x {context} tokens, 128 heads, latent 512 + rope 64, bf16",
+              "kernel": "mla_decode_tcgen05_kernel", "launches_per_step": int(n.value),
+              "absorb_ms": absorb, "kernel_ms": attend, "combine_ms": combine,
+              "algorithmic_bytes": nbytes, "flops": flops,
+              "achieved_gbs": nbytes / (attend * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (attend * 1e-3) / 1e9 / hbm_peak,
+              "achieved_tflops": flops / (attend * 1e-3) / 1e12, "frac_of_bf16_peak": flops / (attend * 1e-3) / 1e12 / tf_peak,
+              "tokens_per_s": sessions / (total * 1e-3), "status_word": int(st[0]),
+              "chunk_tokens": p.chunk_tokens, "max_splits": p.max_splits,
+              "l2": "latent + rope cache %.0f MB exceed L2" % (sessions * context * (dc + dr) * 2 / 1e6)}
+    for ptr in list(bufs.values()) + [q_abs, parts, out, status]:
+        lib.yvx_cuda_free(ptr)
+    return result, (host, o_host)
+
+
+def check_mla(sample):
+    from oracle.binding import Oracle
+    host, o = sample
+    start = time.perf_counter()
+    ref = Oracle().mla_decode(host["q_nope"], host["q_rope"], host["w_uk"], host["latent"], host["rope_key"],
+                              1.0 / np.sqrt(192.0))
+    return float(np.abs(ref - o).max()), time.perf_counter() - start
+
+
 def check_decode_f32(engine, host, threads):
     start = time.perf_counter()
     ref = engine.gqa_attention(host["q"].reshape(1, -1), host["k"].reshape(4096, -1), host["v"].reshape(4096, -1),
@@ -584,7 +673,7 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "decode_f32", "verify_q8", "prefill"],
+                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -629,7 +718,10 @@ def main():
         import clori_b200
         from clori_b200 import abi
         backend = clori_b200.Backend(local_rank)
-        if args.workload == "prefill":
+        if args.workload == "mla":
+            result, _ = bench_mla(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
+                                  sessions=min(args.sessions, 32))
+        elif args.workload == "prefill":
             result, _ = bench_prefill(abi.load(), backend, abi, max(args.steps, 3), tokens=args.tokens)
         else:
             run = {"decode_f32": bench_decode_f32, "verify_q8": bench_verify_q8}[args.workload]
@@ -686,6 +778,7 @@ def main():
         others["decode_f32_config1"], other_samples["f32"] = bench_decode_f32(lib, b, w.abi, hbm_peak, 64)
         others["verify_q8_config4_1gpu"], other_samples["q8"] = bench_verify_q8(lib, b, w.abi, hbm_peak, 20)
         others["prefill_config3"], other_samples["prefill"] = bench_prefill(lib, b, w.abi, 10)
+        others["latent_decode_config5"], other_samples["mla"] = bench_mla(lib, b, w.abi, hbm_peak, 10)
 
     if rank != 0:
         if dist is not None:
@@ -750,6 +843,11 @@ def main():
             others["prefill_config3"].update(
                 gpu_vs_cpu_max_abs_on_sample=err, cpu_sample_ms=seconds * 1e3, cpu_cores=threads,
                 cpu_sample="batch 0, query head 0: last 128 rows x 8192 tokens")
+        if "mla" in other_samples:
+            err, seconds = check_mla(other_samples["mla"])
+            others["latent_decode_config5"].update(
+                gpu_vs_cpu_max_abs_on_sample=err, cpu_sample_ms=seconds * 1e3, cpu_cores=1,
+                cpu_sample="session 0, heads 0..7 (CPU restatement; no reference counterpart)")
     if others:
         line["other_workloads"] = others
     print(json.dumps(line))

@@ -169,6 +169,7 @@ EXPORTED_SYMBOLS = [
     "yvex_b200_transformer_attention_execute",
     "yvex_backend_op_attention", "yvex_b200_attention_batch_execute",
     "yvex_b200_kv_page_tokens", "yvex_b200_kv_page_touch", "yvex_b200_kv_block_row",
+    "yvex_b200_kv_sequence_shard",
     # cuda_shim.h
     "yvx_cuda_device_count", "yvx_cuda_device_select", "yvx_cuda_device_properties",
     "yvx_cuda_malloc", "yvx_cuda_free", "yvx_cuda_host_alloc", "yvx_cuda_host_free",
@@ -177,7 +178,8 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
-    "yvx_cuda_lse_combine", "yvx_cuda_op_attention_f32", "yvx_cuda_gqa_attention_profiled",
+    "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
+    "yvx_cuda_gqa_attention_profiled",
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
@@ -273,6 +275,8 @@ def load():
     lib.yvx_cuda_q8_record_bytes.restype = u64
     lib.yvx_cuda_q8_record_bytes.argtypes = []
     lib.yvx_cuda_q8_kv_pack.argtypes = [vp, vp, C.c_uint, C.c_uint, vp, vp, u64, u64, C.c_uint, vp]
+    lib.yvex_b200_kv_sequence_shard.argtypes = [u64, C.c_uint, C.c_uint, u64, P(u64), P(u64)]
+    lib.yvx_cuda_lse_combine_strided.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, u64, u64, vp, C.c_int, vp, vp]
     lib.yvx_cuda_lse_combine.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, C.c_int, vp, vp]
     _lib = lib
     return lib

@@ -325,13 +325,15 @@ gqa_combine_kernel(const yvx_gqa_problem p)
                   p.partial_output ? p.partial_output + item * (hd + 2ull) : nullptr, p.status);
 }
 
-// Combine of externally gathered partials: parts[item][part][hd+2].
+// Combine of externally gathered partials: part j of item i starts at
+// parts + i * item_stride + j * part_stride (floats) and holds (o[hd], m, l).
 __global__ void __launch_bounds__(kCombineWarps * 32)
-lse_combine_kernel(const float *parts, unsigned int part_count, unsigned int hd, void *output,
+lse_combine_kernel(const float *parts, unsigned int part_count, unsigned int hd,
+                   unsigned long long item_stride, unsigned long long part_stride, void *output,
                    int output_dtype, int *status)
 {
     const unsigned long long item = blockIdx.x;
-    combine_parts(parts + item * part_count * (hd + 2ull), part_count, hd + 2u, hd, output,
+    combine_parts(parts + item * item_stride, part_count, (unsigned int)part_stride, hd, output,
                   output_dtype, item * hd, nullptr, status);
 }
 
@@ -387,6 +389,21 @@ extern "C" int yvx_cuda_lse_combine(const float *parts, unsigned int items,
     if (!parts || !items || !part_count || !head_dim || !output || !status)
         return YVEX_ERR_INVALID_ARG;
     yvx::lse_combine_kernel<<<items, yvx::kCombineWarps * 32, 0, (cudaStream_t)stream>>>(
-        parts, part_count, head_dim, output, output_dtype, status);
+        parts, part_count, head_dim, (unsigned long long)part_count * (head_dim + 2ull), head_dim + 2ull,
+        output, output_dtype, status);
+    return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
+}
+
+extern "C" int yvx_cuda_lse_combine_strided(const float *parts, unsigned int items,
+                                            unsigned int part_count, unsigned int head_dim,
+                                            unsigned long long item_stride,
+                                            unsigned long long part_stride, void *output,
+                                            int output_dtype, int *status, void *stream)
+{
+    if (!parts || !items || !part_count || !head_dim || !output || !status ||
+        part_stride < head_dim + 2ull || part_stride > 0xffffffffull)
+        return YVEX_ERR_INVALID_ARG;
+    yvx::lse_combine_kernel<<<items, yvx::kCombineWarps * 32, 0, (cudaStream_t)stream>>>(
+        parts, part_count, head_dim, item_stride, part_stride, output, output_dtype, status);
     return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
 }

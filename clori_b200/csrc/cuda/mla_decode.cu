@@ -4,27 +4,33 @@
 // Arithmetic intensity sits at the machine's ridge (about 242 flop per byte),
 // so the attention runs on the 5th-generation tensor cores with all 128 heads
 // in the M dimension of one tcgen05.mma:
-//   S[128 x 32]  = Q_abs[128 x 576] . K_tile^T        (36 k-steps, A and B in smem)
-//   O[128 x 256] += P[128 x 32] . latent_tile[32 x 256] (A = P in tensor memory)
-// A 32-token tile is loaded ONCE into shared memory and serves as K (K-major)
+//   S[128 x 64]  = Q_abs[128 x 576] . K_tile^T          (36 k-steps of 128x64x16)
+//   O[128 x 256] += P[128 x 64] . latent_tile[64 x 256]  (A = P in tensor memory)
+// A 64-token tile is loaded ONCE into shared memory and serves as K (K-major)
 // and as V (the same bytes read MN-major). The f32 output of 128 heads x 512
 // dims would fill all of tensor memory, so a CTA owns one half of the latent
 // dims (256 accumulator columns) and recomputes S; the two CTAs of a pair run
-// side by side and share their tile through L2.
+// side by side and share their tile through L2. Shared memory cannot hold the
+// whole absorbed query next to two 72 KB tiles, so the first 384 query dims
+// live in tensor memory (192 columns, A operand of the first 24 k-steps) and
+// only the last 192 dims are staged in shared memory.
+// Tensor memory map: O [0,256) | S [256,320), P aliases its first 32 | Q [320,512).
 #include "tcgen05.cuh"
 
 namespace yvx {
 
 constexpr int kMlaHeads = 128, kMlaNope = 128, kMlaLatent = 512, kMlaRope = 64;
 constexpr int kMlaWidth = kMlaLatent + kMlaRope;          // 576
-constexpr int kMlaN = 32;                                  // tokens per tile
+constexpr int kMlaN = 64;                                  // tokens per tile
 constexpr int kMlaHalf = kMlaLatent / 2;                   // accumulator columns per CTA
 constexpr int kMlaStages = 2;
 constexpr int kMlaThreads = 192;
 constexpr int kMlaQSubBytes = kMlaHeads * 64 * 2;          // [128][64] bf16 = 16 KB
-constexpr int kMlaQBytes = (kMlaWidth / 64) * kMlaQSubBytes;   // 9 sub-tiles
-constexpr int kMlaKvSubBytes = kMlaN * 64 * 2;             // [32][64] bf16 = 4 KB
-constexpr int kMlaKvBytes = (kMlaWidth / 64) * kMlaKvSubBytes; // 36 KB
+constexpr int kMlaQTmemDims = 384;                         // query dims held in tensor memory
+constexpr int kMlaQSmemSubs = (kMlaWidth - kMlaQTmemDims) / 64;  // 3 sub-tiles stay in shared memory
+constexpr int kMlaQBytes = kMlaQSmemSubs * kMlaQSubBytes;
+constexpr int kMlaKvSubBytes = kMlaN * 64 * 2;             // [64][64] bf16 = 8 KB
+constexpr int kMlaKvBytes = (kMlaWidth / 64) * kMlaKvSubBytes; // 72 KB
 constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256;
 constexpr uint32_t kMlaTmemColumns = 512;
 constexpr float kMlaRescaleThreshold = 8.0f;
@@ -34,9 +40,9 @@ struct MlaMaps {
 };
 
 struct MlaBarriers {
-    uint64_t q_full;
-    uint64_t kv_full[kMlaStages], k_done[kMlaStages], v_done[kMlaStages];
-    uint64_t s_full[2], p_full[2];
+    uint64_t q_full, q_tmem_full;
+    uint64_t kv_full[kMlaStages], v_done[kMlaStages];
+    uint64_t s_full, p_full;
     uint64_t pv_done;
     uint32_t tmem_base;
 };
@@ -155,15 +161,13 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->q_tmem_full, kMlaHeads);
         for (int i = 0; i < kMlaStages; ++i) {
             mbar_init(&bars->kv_full[i], 1);
-            mbar_init(&bars->k_done[i], 1);
             mbar_init(&bars->v_done[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], kMlaHeads);
-        }
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->p_full, kMlaHeads);
         mbar_init(&bars->pv_done, 1);
         fence_barrier_init();
     }
@@ -175,14 +179,15 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
-    const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf;  // O: 256 columns, then two 32-column S buffers
+    const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf, tmem_q = tmem + kMlaHalf + kMlaN;
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             mbar_expect_tx(&bars->q_full, kMlaQBytes);
-            for (int st = 0; st < kMlaWidth / 64; ++st)
-                tma_load_3d(q_tile + st * kMlaQSubBytes, &maps.query, &bars->q_full, 64 * st, 0, (int)b);
+            for (int st = 0; st < kMlaQSmemSubs; ++st)
+                tma_load_3d(q_tile + st * kMlaQSubBytes, &maps.query, &bars->q_full,
+                            kMlaQTmemDims + 64 * st, 0, (int)b);
             for (unsigned int j = 0; j < tiles; ++j) {
                 const unsigned int stage = j % kMlaStages;
                 if (j >= (unsigned)kMlaStages &&
@@ -204,38 +209,38 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
             constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
             const uint32_t q_addr = smem_u32(q_tile);
-            bool ok = mbar_wait(&bars->q_full, 0);
-            auto issue_qk = [&](unsigned int j) -> bool {
-                const unsigned int stage = j % kMlaStages;
-                if (!mbar_wait(&bars->kv_full[stage], (j / kMlaStages) & 1u)) return false;
-                tc_fence_after_sync();
-                const uint32_t kv_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
-                const uint32_t d = tmem_s + (j & 1u) * kMlaN;
-#pragma unroll 4
-                for (int ks = 0; ks < kMlaWidth / 16; ++ks) {
-                    const uint32_t sub = ks >> 2, off = (ks & 3) * 32;
-                    tc_mma_ss(d, smem_desc_sw128(q_addr + sub * kMlaQSubBytes + off, 16, 1024),
-                              smem_desc_sw128(kv_addr + sub * kMlaKvSubBytes + off, 16, 1024), idesc_qk,
-                              ks ? 1u : 0u);
-                }
-                tc_commit(&bars->s_full[j & 1u]);
-                return true;
-            };
-            if (ok) ok = issue_qk(0);
+            bool ok = mbar_wait(&bars->q_full, 0) && mbar_wait(&bars->q_tmem_full, 0);
             for (unsigned int j = 0; ok && j < tiles; ++j) {
-                if (j + 1 < tiles) ok = issue_qk(j + 1);
-                if (!ok) break;
                 const unsigned int stage = j % kMlaStages;
-                if (!mbar_wait(&bars->p_full[j & 1u], (j >> 1) & 1u)) {
+                if (!mbar_wait(&bars->kv_full[stage], (j / kMlaStages) & 1u)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(kv_tiles + stage * kMlaKvBytes) + 4u * half * kMlaKvSubBytes;
-                const uint32_t p_tmem = tmem_s + (j & 1u) * kMlaN;
+                const uint32_t kv_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
+                // S = Q K^T: query dims [0,384) from tensor memory, the rest from shared memory.
+#pragma unroll 4
+                for (int ks = 0; ks < kMlaQTmemDims / 16; ++ks)
+                    tc_mma_ts(tmem_s, tmem_q + ks * 8,
+                              smem_desc_sw128(kv_addr + (ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32, 16, 1024),
+                              idesc_qk, ks ? 1u : 0u);
+#pragma unroll 4
+                for (int ks = kMlaQTmemDims / 16; ks < kMlaWidth / 16; ++ks) {
+                    const uint32_t sub = ks >> 2, off = (ks & 3) * 32;
+                    tc_mma_ss(tmem_s,
+                              smem_desc_sw128(q_addr + (sub - kMlaQTmemDims / 64) * kMlaQSubBytes + off, 16, 1024),
+                              smem_desc_sw128(kv_addr + sub * kMlaKvSubBytes + off, 16, 1024), idesc_qk, 1u);
+                }
+                tc_commit(&bars->s_full);
+                if (!mbar_wait(&bars->p_full, j & 1u)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t v_addr = kv_addr + 4u * half * kMlaKvSubBytes;
 #pragma unroll
                 for (int kk = 0; kk < kMlaN / 16; ++kk)
-                    tc_mma_ts(tmem_o, p_tmem + kk * 8, smem_desc_sw128(v_addr + kk * 2048, kMlaKvSubBytes, 1024),
+                    tc_mma_ts(tmem_o, tmem_s + kk * 8, smem_desc_sw128(v_addr + kk * 2048, kMlaKvSubBytes, 1024),
                               idesc_pv, (j || kk) ? 1u : 0u);
                 tc_commit(&bars->v_done[stage]);
                 tc_commit(&bars->pv_done);
@@ -246,26 +251,51 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         // ------------------------------ softmax warps -----------------------------
         const unsigned int head = threadIdx.x;
         const uint32_t lane_base = ((warp * 32u) << 16);
+        // This head's first 384 absorbed-query dims go to tensor memory: bf16 pairs
+        // are already the 32-bit words the A operand wants.
+        {
+            const uint4 *src = reinterpret_cast<const uint4 *>(
+                reinterpret_cast<const unsigned short *>(p.q_absorbed) +
+                ((unsigned long long)b * kMlaHeads + head) * kMlaWidth);
+#pragma unroll 1
+            for (int i = 0; i < kMlaQTmemDims / 64; ++i) {
+                uint32_t words[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = src[8 * i + c];
+                    words[4 * c] = v.x;
+                    words[4 * c + 1] = v.y;
+                    words[4 * c + 2] = v.z;
+                    words[4 * c + 3] = v.w;
+                }
+                tmem_st32(tmem_q + lane_base + 32 * i, words);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bars->q_tmem_full);
+        }
         const float sscale = p.scale * 1.4426950408889634f;
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         for (unsigned int j = 0; j < tiles; ++j) {
-            const unsigned int buf = j & 1u;
-            if (!mbar_wait(&bars->s_full[buf], (j >> 1) & 1u)) {
+            if (!mbar_wait(&bars->s_full, j & 1u)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            uint32_t s[32];
-            tmem_ld32(tmem_s + lane_base + buf * kMlaN, s);
+            uint32_t s[2][32];
+            tmem_ld32(tmem_s + lane_base, s[0]);
+            tmem_ld32(tmem_s + lane_base + 32, s[1]);
             tmem_wait_ld();
             const unsigned int k0 = t0 + j * kMlaN;
             float row_max = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                if (k0 + c >= t1) s[c] = 0xff800000u;
-                row_max = fmaxf(row_max, __uint_as_float(s[c]));
-            }
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    if (k0 + 32 * i + c >= t1) s[i][c] = 0xff800000u;
+                    row_max = fmaxf(row_max, __uint_as_float(s[i][c]));
+                }
             const float m_tile = row_max * sscale;
             const bool grow = m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY;
             if (__any_sync(0xffffffffu, grow)) {
@@ -274,10 +304,7 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 l *= factor;
                 m_used = m_new;
                 if (j > 0) {
-                    if (!mbar_wait(&bars->pv_done, (j - 1u) & 1u)) {
-                        ok = false;
-                        break;
-                    }
+                    // P V of the previous tile has completed: S(j) was issued after it.
                     tc_fence_after_sync();
 #pragma unroll 1
                     for (int i = 0; i < kMlaHalf / 32; ++i) {
@@ -292,21 +319,23 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 }
             }
             const float offset = m_used == -INFINITY ? 0.0f : -m_used;
-            uint32_t packed[16];
+            uint32_t packed[32];
             float sum = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-                const float p0 = exp2_approx(fmaf(__uint_as_float(s[c]), sscale, offset));
-                const float p1 = exp2_approx(fmaf(__uint_as_float(s[c + 1]), sscale, offset));
-                const uint32_t pair = pack_bf16(p0, p1);
-                sum += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
-                packed[c >> 1] = pair;
-            }
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = exp2_approx(fmaf(__uint_as_float(s[i][c]), sscale, offset));
+                    const float p1 = exp2_approx(fmaf(__uint_as_float(s[i][c + 1]), sscale, offset));
+                    const uint32_t pair = pack_bf16(p0, p1);
+                    sum += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
+                    packed[16 * i + (c >> 1)] = pair;
+                }
             l += sum;
-            tmem_st16(tmem_s + lane_base + buf * kMlaN, packed);
+            tmem_st32(tmem_s + lane_base, packed);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&bars->p_full[buf]);
+            mbar_arrive(&bars->p_full);
         }
         if (ok) ok = mbar_wait(&bars->pv_done, (tiles - 1u) & 1u);
         if (!__all_sync(0xffffffffu, ok)) {
@@ -387,7 +416,7 @@ static bool mla_encode(CUtensorMap *map, const void *base, unsigned long long wi
 extern "C" {
 
 // One CTA per SM is resident (shared memory), so a wave is sm_count work items:
-// sessions x 2 halves x splits. The chunk is the largest multiple of 32 tokens,
+// sessions x 2 halves x splits. The chunk is the largest multiple of 64 tokens,
 // at most 8192, that makes at least one wave and fills the last one to 90 %.
 void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
 {
@@ -396,7 +425,7 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
     const unsigned long long lanes = 2ull * p->sessions;
     unsigned int best = 0u;
     double best_fill = -1.0;
-    for (unsigned int chunk = 8192u; chunk >= 32u; chunk -= 32u) {
+    for (unsigned int chunk = 8192u; chunk >= 64u; chunk -= 64u) {
         const unsigned long long splits = ((unsigned long long)p->kv_tokens_max + chunk - 1ull) / chunk;
         const unsigned long long items = lanes * splits;
         if (items < wave) continue;
@@ -411,7 +440,7 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
             best = chunk;
         }
     }
-    p->chunk_tokens = best ? best : 32u;
+    p->chunk_tokens = best ? best : 64u;
     p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
     if (!p->max_splits) p->max_splits = 1u;
 }
@@ -434,11 +463,12 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
     if (launches) *launches = 0;
     if (!p || !p->q_nope || !p->q_rope || !p->w_uk || !p->latent || !p->rope_key || !p->q_absorbed ||
         !p->partials || !p->output || !p->status || !p->sessions || !p->kv_tokens_max ||
-        !p->chunk_tokens || !p->max_splits || p->chunk_tokens % kMlaN)
+        !p->chunk_tokens || !p->max_splits)
         return YVEX_ERR_INVALID_ARG;
     if (p->heads != (unsigned)kMlaHeads || p->nope_dim != (unsigned)kMlaNope ||
         p->latent_dim != (unsigned)kMlaLatent || p->rope_dim != (unsigned)kMlaRope)
         return YVEX_ERR_UNSUPPORTED;
+    if (p->chunk_tokens % kMlaN) return YVEX_ERR_INVALID_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     MlaMaps maps;
     if (!mla_encode(&maps.query, p->q_absorbed, kMlaWidth, kMlaHeads, p->sessions,

@@ -96,3 +96,22 @@ unsigned long long yvex_b200_kv_block_row(const int *block_table,
 {
     return (unsigned long long)block_table[row / block_tokens] * block_tokens + row % block_tokens;
 }
+
+/* Contiguous block-aligned token ranges for KV-sequence sharding: the first
+ * (blocks % shards) shards take one block more than the others. */
+int yvex_b200_kv_sequence_shard(unsigned long long tokens, unsigned int shards, unsigned int index,
+                                unsigned long long block_tokens, unsigned long long *begin,
+                                unsigned long long *end)
+{
+    unsigned long long blocks, base, extra, first;
+    if (!shards || index >= shards || !block_tokens || !begin || !end) return 0;
+    blocks = tokens / block_tokens + (tokens % block_tokens ? 1ull : 0ull);
+    base = blocks / shards;
+    extra = blocks % shards;
+    first = (unsigned long long)index * base + (index < extra ? index : extra);
+    *begin = first * block_tokens;
+    *end = (first + base + (index < extra ? 1ull : 0ull)) * block_tokens;
+    if (*begin > tokens) *begin = tokens;
+    if (*end > tokens) *end = tokens;
+    return 1;
+}

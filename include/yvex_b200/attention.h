@@ -156,6 +156,14 @@ int yvex_b200_kv_page_tokens(const yvex_b200_page_request *request,
 int yvex_b200_kv_page_touch(unsigned long long element_start, unsigned long long element_count,
                             unsigned long long page_elements, unsigned long long *first_page,
                             unsigned long long *last_page);
+/* KV-sequence sharding of one long session over `shards` GPUs (extension; the
+ * reference is single-device): shard `index` owns the contiguous token range
+ * [*begin, *end), boundaries aligned to `block_tokens`, sizes differing by at
+ * most one block, empty ranges allowed when there are more shards than blocks.
+ * Returns 1 on success, 0 on bad arguments. */
+int yvex_b200_kv_sequence_shard(unsigned long long tokens, unsigned int shards, unsigned int index,
+                                unsigned long long block_tokens, unsigned long long *begin,
+                                unsigned long long *end);
 unsigned long long yvex_b200_kv_block_row(const int *block_table,
                                           unsigned long long block_tokens,
                                           unsigned long long row);

@@ -142,6 +142,14 @@ int yvx_cuda_gqa_attention_static_scratch(const yvx_gqa_problem *problem, void *
 int yvx_cuda_lse_combine(const float *parts, unsigned int items, unsigned int part_count,
                          unsigned int head_dim, void *output, int output_dtype,
                          int *status, void *stream);
+/* The same with explicit strides (in floats): part j of item i starts at
+ * parts + i*item_stride + j*part_stride. An all-gather of per-rank
+ * [items][head_dim+2] buffers is [rank][items][head_dim+2], i.e. item_stride =
+ * head_dim+2 and part_stride = items*(head_dim+2): no transpose is needed. */
+int yvx_cuda_lse_combine_strided(const float *parts, unsigned int items, unsigned int part_count,
+                                 unsigned int head_dim, unsigned long long item_stride,
+                                 unsigned long long part_stride, void *output, int output_dtype,
+                                 int *status, void *stream);
 
 /* ---- single-head primitive (reference: yvex_attention_f32,
  * src/backend/cuda/kernels.cu:362-434, launched from
