@@ -575,6 +575,107 @@ def check_mla(sample):
     return float(np.abs(ref - o).max()), time.perf_counter() - start
 
 
+
+def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats):
+    """Config 4 across `world` GPUs: the KV sequence of ONE session is sharded in
+    contiguous block-aligned ranges; every rank runs the same kernel over its shard
+    (absolute positions through kv_position_base) and emits (o, m, l) per (row, head);
+    one NCCL all-gather of 66 560 bytes per rank; the LSE combine folds the shards in
+    rank order. Every rank fills the whole record pool identically (same seed) and
+    reads only its slice, so rank 0 can also run the unsharded problem as a cross-check."""
+    from clori_b200 import q8_records
+    hq, hkv, hd, tokens, rows = 32, 8, 128, 131072, 4
+    record = q8_records.RECORD_BYTES
+    blocks = tokens // 64
+    pool_bytes = blocks * hkv * record
+    copies = 2
+    records = _alloc(lib, copies * pool_bytes)
+    q = _alloc(lib, rows * hq * hd * 2)
+    status = _alloc(lib, 4)
+    for i in range(copies):
+        lib.yvx_cuda_fill_q8_records(records.value + i * pool_bytes, blocks * hkv, 201 + i, 0.002, 0.02, backend.stream)
+    lib.yvx_cuda_fill_normal(q, abi.DTYPE_BF16, rows * hq * hd, 202, 1.0, backend.stream)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    begin, end = abi.u64(), abi.u64()
+    assert lib.yvex_b200_kv_sequence_shard(tokens, world, rank, 64, C.byref(begin), C.byref(end))
+    items = rows * hq
+    device = torch.device("cuda", torch.cuda.current_device())
+    mine = torch.zeros((items, hd + 2), dtype=torch.float32, device=device)
+    gathered = torch.zeros((world, items, hd + 2), dtype=torch.float32, device=device)
+    out = torch.zeros((rows, hq * hd), dtype=torch.float32, device=device)
+
+    def problem(copy, lo, hi, partial):
+        p = abi.GqaProblem()
+        p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, rows, hq, hkv, hd
+        p.causal, p.scale = 1, 1.0 / np.sqrt(hd)
+        p.query_dtype, p.kv_dtype, p.output_dtype = abi.DTYPE_BF16, abi.DTYPE_Q8_0, abi.DTYPE_F32
+        p.query, p.query_row_stride, p.query_session_stride = q, hq * hd, rows * hq * hd
+        p.key = records.value + copy * pool_bytes + (lo // 64) * hkv * record
+        p.key_head_stride, p.key_block_stride, p.block_tokens = record, hkv * record, 64
+        p.kv_tokens_uniform = p.kv_tokens_max = hi - lo
+        p.query_start_uniform, p.kv_position_base = tokens - rows, lo
+        if partial is not None:
+            p.partial_output = partial.data_ptr()
+        else:
+            p.output = out.data_ptr()
+        lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+        p.status = status
+        return p
+    local = [problem(i, begin.value, end.value, mine) for i in range(copies)]
+    scratch = _alloc(lib, max(max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)) for p in local), 16))
+    for p in local:
+        p.partials = scratch
+
+    def step(i):
+        n = C.c_uint()
+        rc = lib.yvx_cuda_gqa_attention(C.byref(local[i % copies]), backend.stream, C.byref(n))
+        assert rc == 0, lib.yvx_cuda_last_error_text()
+        dist.all_gather_into_tensor(gathered, mine)
+        rc = lib.yvx_cuda_lse_combine_strided(gathered.data_ptr(), items, world, hd, hd + 2, items * (hd + 2),
+                                              out.data_ptr(), abi.DTYPE_F32, status, backend.stream)
+        assert rc == 0, lib.yvx_cuda_last_error_text()
+        return n.value + 1
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(repeats):
+        launches = step(i)
+    stop.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([start.elapsed_time(stop) / repeats], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    sharded = out.clone()
+    # cross-check on rank 0: the same pool copy, unsharded, on one GPU
+    diff = None
+    if rank == 0:
+        whole = problem((repeats - 1) % copies, 0, tokens, None)
+        whole_scratch = _alloc(lib, max(lib.yvx_cuda_gqa_partials_bytes(C.byref(whole)), 16))
+        whole.partials = whole_scratch
+        n = C.c_uint()
+        assert lib.yvx_cuda_gqa_attention(C.byref(whole), backend.stream, C.byref(n)) == 0
+        torch.cuda.synchronize()
+        diff = float((out - sharded).abs().max().item())
+        lib.yvx_cuda_free(whole_scratch)
+    st = torch.zeros(1, dtype=torch.int32)
+    lib.yvx_cuda_download_async(st.data_ptr(), status, 4, backend.stream)
+    torch.cuda.synchronize()
+    nbytes = pool_bytes + rows * hq * hd * (2 + 4)
+    result = {"workload": "speculative verify, 1 session, KV 131072 sharded over %d GPUs, Q8_0 KV, 4 rows" % world,
+              "n_gpus": world, "scaling": "strong", "ms_per_step": ms, "tokens_per_s": rows / (ms * 1e-3),
+              "aggregate_gbs": nbytes / (ms * 1e-3) / 1e9, "launches_per_step": launches,
+              "collective": "one NCCL all-gather of %d bytes per rank" % (items * (hd + 2) * 4),
+              "shard_tokens": end.value - begin.value, "status_word": int(st[0]),
+              "sharded_vs_single_gpu_max_abs": diff}
+    for ptr in (records, q, status, scratch):
+        lib.yvx_cuda_free(ptr)
+    return result
+
+
 def check_decode_f32(engine, host, threads):
     start = time.perf_counter()
     ref = engine.gqa_attention(host["q"].reshape(1, -1), host["k"].reshape(4096, -1), host["v"].reshape(4096, -1),
@@ -772,6 +873,17 @@ def main():
     # ---- the attention kernel alone ----------------------------------------
     kernel_ms, combine_ms, (chunk, splits) = w.kernel_ms(min(max(args.steps, 10), 100), args.chunk)
     clocks = sampler.stop()
+    sharded = None
+    if world > 1 and not args.headline_only:
+        import torch
+        # The kernels and the NCCL all-gather must be ordered on ONE stream: a torch
+        # side stream (the legacy default stream has no handle to bind).
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            b.bind_stream(side.cuda_stream, synchronous=False)
+            sharded = bench_verify_q8_sharded(lib, b, w.abi, rank, world, dist, torch, 20)
+        side.synchronize()
+        b.bind_stream(None, synchronous=True)
     others, other_samples = {}, {}
     if world == 1 and not args.headline_only:
         hbm_peak = measured_peaks()[0]
@@ -848,6 +960,8 @@ def main():
             others["latent_decode_config5"].update(
                 gpu_vs_cpu_max_abs_on_sample=err, cpu_sample_ms=seconds * 1e3, cpu_cores=1,
                 cpu_sample="session 0, heads 0..7 (CPU restatement; no reference counterpart)")
+    if sharded:
+        others["verify_q8_config4_sharded"] = sharded
     if others:
         line["other_workloads"] = others
     print(json.dumps(line))

@@ -130,3 +130,50 @@ def test_q8_contract_refusals(backend):
     assert call(head_dimension=64) in (abi.YVEX_ERR_UNSUPPORTED, abi.YVEX_ERR_INVALID_ARG)
     assert call(query_dtype=abi.DTYPE_F32) == abi.YVEX_ERR_UNSUPPORTED
     assert call(key_value_tokens=100) == abi.YVEX_ERR_FORMAT  # records smaller than declared
+
+
+def test_sequence_sharded_q8_partials_combine_to_the_whole(backend, oracle):
+    # The KV sequence split into 3 block-aligned shards (as on 3 GPUs): each shard
+    # emits (o, m, l) with its absolute base position, the gathered [shard][item]
+    # buffer is folded by the strided LSE combine, and the result equals attention
+    # over the whole sequence.
+    hq, hkv, rows, tokens, shards = 32, 8, 4, 64 * 23 + 17, 3
+    k_rows, v_rows = workloads.q8_0_kv(seed=9, kv_tokens=tokens, kv_heads=hkv)
+    q = workloads.verify_queries_bf16(seed=9, rows=rows, query_heads=hq)
+    blocks = (tokens + 63) // 64
+    records = device_pack(backend, k_rows, v_rows, hkv, None, blocks)
+    tq = backend.tensor("q", q)
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    items = rows * hq
+    gathered = backend.alloc("gathered", abi.DTYPE_F32, (shards, items, HD + 2))
+    lib = backend.lib
+    record = q8_records.RECORD_BYTES
+    for g in range(shards):
+        lo, hi = abi.u64(), abi.u64()
+        assert lib.yvex_b200_kv_sequence_shard(tokens, shards, g, 64, C.byref(lo), C.byref(hi))
+        p = abi.GqaProblem()
+        p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, rows, hq, hkv, HD
+        p.causal, p.scale = 1, 1.0 / np.sqrt(HD)
+        p.query_dtype, p.kv_dtype, p.output_dtype = abi.DTYPE_BF16, abi.DTYPE_Q8_0, abi.DTYPE_F32
+        p.query, p.query_row_stride, p.query_session_stride = tq.data_ptr, hq * HD, rows * hq * HD
+        p.key = records.data_ptr + (lo.value // 64) * hkv * record
+        p.key_head_stride, p.key_block_stride, p.block_tokens = record, hkv * record, 64
+        p.kv_tokens_uniform = p.kv_tokens_max = hi.value - lo.value
+        p.query_start_uniform, p.kv_position_base = tokens - rows, lo.value
+        p.partial_output = gathered.data_ptr + g * items * (HD + 2) * 4
+        p.chunk_tokens, p.max_splits = 256, (hi.value - lo.value + 255) // 256
+        scratch = backend.alloc("scratch", abi.DTYPE_F32, (1,), max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+        p.partials, p.status = scratch.data_ptr, status.data_ptr
+        n = C.c_uint()
+        assert lib.yvx_cuda_gqa_attention(C.byref(p), backend.stream, C.byref(n)) == 0
+    out = backend.alloc("out", abi.DTYPE_F32, (rows, hq * HD))
+    rc = lib.yvx_cuda_lse_combine_strided(gathered.data_ptr, items, shards, HD, HD + 2, items * (HD + 2),
+                                          out.data_ptr, abi.DTYPE_F32, status.data_ptr, backend.stream)
+    assert rc == 0 and lib.yvx_cuda_stream_synchronize(backend.stream) == 0
+    out.struct.is_written = 1
+    assert int(status.read()[0]) == 0
+    kf, vf = dequant(oracle, k_rows, tokens, hkv * HD), dequant(oracle, v_rows, tokens, hkv * HD)
+    ref = oracle.gqa_attention(clori_b200.bf16_bits_to_f32(q), kf, vf, tokens - rows, hq, hkv, HD, threads=8)
+    got = out.read()
+    assert np.abs(got - ref).max() <= 2e-3
+    assert cosine(got, ref) >= 0.9999
