@@ -125,7 +125,9 @@ class Workload:
         self.lib = abi.load()
         self.backend = clori_b200.Backend(device)
         b = self.backend
-        self.lengths = workloads.session_lengths(seed, SESSIONS, LOW, HIGH)
+        # Every rank draws the SAME session lengths (seed 1), so per-GPU work is identical
+        # (weak scaling); the block-table permutation and the data differ per rank.
+        self.lengths = workloads.session_lengths(SEED, SESSIONS, LOW, HIGH)
         self.table, self.pool_blocks = workloads.block_table(self.lengths, BLOCK_TOKENS, seed)
         width = KV_HEADS * HEAD_DIM
         pool_elems = self.pool_blocks * BLOCK_TOKENS * width
