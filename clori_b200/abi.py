@@ -140,6 +140,21 @@ class GqaProblem(C.Structure):
     ]
 
 
+class LatentReduceArgs(C.Structure):
+    """yvx_latent_reduce_args (include/yvex_b200/cuda_shim.h); the first 19 fields are
+    also the layout of the CPU checker's argument struct."""
+    _fields_ = [
+        ("query", C.c_void_p), ("local", C.c_void_p), ("local_positions", C.c_void_p),
+        ("initial_local_count", u64), ("local_stride", u64),
+        ("compressed", C.c_void_p), ("compressed_positions", C.c_void_p), ("compressed_stride", u64),
+        ("selected", C.c_void_p), ("selected_count", C.c_void_p), ("topk_capacity", u64),
+        ("sinks", C.c_void_p), ("query_heads", u64), ("head_dim", u64), ("sliding_window", u64),
+        ("ratio", u64), ("attention_class", C.c_uint), ("phase_start_position", u64),
+        ("token_count", u64), ("candidate_block_visible", C.c_int),
+        ("out", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 class MlaProblem(C.Structure):
     """yvx_mla_problem (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [
@@ -183,7 +198,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
-    "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
+    "yvx_cuda_latent_reduce", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
     "yvx_cuda_mla_decode",
 ]
 
@@ -264,6 +279,7 @@ def load():
     lib.yvx_cuda_gqa_static_scratch_capacity.restype = u64
     lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
     lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
+    lib.yvx_cuda_latent_reduce.argtypes = [P(LatentReduceArgs), vp]
     lib.yvx_cuda_mla_plan.restype = None
     lib.yvx_cuda_mla_plan.argtypes = [P(MlaProblem), C.c_int]
     lib.yvx_cuda_mla_absorbed_bytes.restype = u64

@@ -170,7 +170,8 @@ class Backend:
         array = np.ascontiguousarray(array)
         if dtype is None:
             dtype = {np.dtype(np.float32): abi.DTYPE_F32, np.dtype(np.uint16): abi.DTYPE_BF16,
-                     np.dtype(np.int32): abi.DTYPE_I32, np.dtype(np.int8): abi.DTYPE_I8}[array.dtype]
+                     np.dtype(np.int32): abi.DTYPE_I32, np.dtype(np.int8): abi.DTYPE_I8,
+                     np.dtype(np.int64): abi.DTYPE_I64}[array.dtype]
         return self.alloc(name, dtype, array.shape, array.nbytes).write(array)
 
     # -- operators -----------------------------------------------------------

@@ -160,6 +160,38 @@ int yvx_cuda_op_attention_f32(const float *query, const float *keys, const float
                               float *scores, float *probabilities, float *out,
                               void *stream);
 
+/* ---- shared-latent attention reduce ------------------------------------------------
+ * Replaces the launch of yvex_attention_reduce_native
+ * (src/backend/cuda/attention.c:1386-1422, kernel src/backend/cuda/attention_kernels.cu:
+ * 259-406); the fields are that kernel's parameters with the same meaning. All heads
+ * share one row per position (the row is key and value); sinks[head] seeds the softmax
+ * maximum and adds exp(sink - max) to the denominator; pass 0 = local window rows
+ * (positions in [pos+1-W, pos], or every local row when candidate_block_visible),
+ * pass 1 = compressed rows (class 1: selected[token][0..selected_count), ratio 4;
+ * class 2: all rows with position + ratio - 1 <= pos, ratio 128; class 0: none).
+ * out = quotient rounded to bf16 (nearest even), stored as F32. status: 1 non-finite,
+ * 2 contract. head_dim <= 512. */
+typedef struct yvx_latent_reduce_args {
+    const float *query;                       /* [token][heads*head_dim] */
+    const float *local;                       /* [initial_local_count + token_count][local_stride] */
+    const unsigned long long *local_positions;
+    unsigned long long initial_local_count, local_stride;
+    const float *compressed;
+    const unsigned long long *compressed_positions;
+    unsigned long long compressed_stride;
+    const unsigned long long *selected;
+    const unsigned long long *selected_count;
+    unsigned long long topk_capacity;
+    const float *sinks;
+    unsigned long long query_heads, head_dim, sliding_window, ratio;
+    unsigned int attention_class;
+    unsigned long long phase_start_position, token_count;
+    int candidate_block_visible;
+    float *out;                               /* [token][heads*head_dim] */
+    int *status;
+} yvx_latent_reduce_args;
+int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *args, void *stream);
+
 /* ---- latent-compressed (MLA-style) decode -----------------------------------------
  * One query token per session; every query head attends over ONE shared row per
  * position: score = scale * (q_lat[h] . latent[t] + q_rope[h] . rope_key[t]),

@@ -134,6 +134,7 @@ class Oracle(_Gqa):
         lib.yvx_oracle_page_touch.argtypes = [_u64, _u64, _u64, C.POINTER(_u64), C.POINTER(_u64)]
         lib.yvx_oracle_latent_reduce.argtypes = [
             _f32p, _f32p, _f32p, _f32p, _u64, _u64, _u64, _u64, _u64, _u64, C.c_int]
+        lib.yvx_oracle_latent_reduce_full.argtypes = [C.c_void_p, _f32p]
         lib.yvx_oracle_mla_decode.argtypes = [
             _u16p, _u16p, _u16p, _u16p, _u16p, _f32p, _u64, _u64, _u64, _u64, _u64,
             C.c_float, C.c_void_p]
@@ -208,6 +209,13 @@ class Oracle(_Gqa):
         ok = self.lib.yvx_oracle_latent_reduce(
             q.reshape(-1), rows.reshape(-1), sinks, out.reshape(-1), q.shape[0],
             rows.shape[0], query_start, heads, head_dim, rows.shape[1], int(round_bf16))
+        return out if ok else None
+
+    def latent_reduce_full(self, args_struct, tokens, heads, head_dim):
+        """args_struct: a ctypes struct whose leading fields are yvx_oracle_latent_args
+        (host pointers). Returns float32 [tokens, heads*head_dim] or None."""
+        out = np.zeros((tokens, heads * head_dim), np.float32)
+        ok = self.lib.yvx_oracle_latent_reduce_full(C.addressof(args_struct), out.reshape(-1))
         return out if ok else None
 
     def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale):

@@ -674,3 +674,105 @@ done:
     free(mixed);
     return ok;
 }
+
+/* ---- shared-latent reduce over window + compressed rows ------------------- */
+
+/* Row visibility as the reference's reduce stage defines it
+ * (src/backend/cuda/attention_kernels.cu:69-100, CPU twin src/graph/core.c:392-464).
+ * Pass 0 walks the local rows [history tail | current tokens]: without
+ * candidate_block_visible only the last `sliding_window` rows up to the token are
+ * candidates and a row counts when its position lies in [pos+1-W, pos]; with it
+ * every local row counts. Pass 1 walks compressed rows (class 1: the token's
+ * selected indices; class 2: all rows up to pos/ratio), a row counts when
+ * position + ratio - 1 <= pos. Returns the row or NULL. */
+static const float *latent_row(const yvx_oracle_latent_args *a, unsigned long long pass,
+                               unsigned long long ordinal, unsigned long long candidate,
+                               unsigned long long local_offset)
+{
+    const unsigned long long token_position = a->phase_start_position + ordinal;
+    if (pass == 0ull) {
+        unsigned long long position, first;
+        candidate += local_offset;
+        position = a->local_positions[candidate];
+        if (!a->candidate_block_visible) {
+            first = token_position + 1ull > a->sliding_window
+                        ? token_position + 1ull - a->sliding_window : 0ull;
+            if (position < first || position > token_position) return NULL;
+        }
+        return a->local + candidate * a->local_stride;
+    } else {
+        unsigned long long index = a->attention_class == 2u
+                                       ? candidate
+                                       : a->selected[ordinal * a->topk_capacity + candidate];
+        unsigned long long position = a->compressed_positions[index];
+        if (position > token_position || position > ~0ull - a->ratio + 1ull ||
+            position + a->ratio - 1ull > token_position)
+            return NULL;
+        return a->compressed + index * a->compressed_stride;
+    }
+}
+
+/* src/graph/core.c:466-508 (reduce_head): the sink logit seeds the maximum and
+ * adds exp(sink - max) to the denominator; two passes in double; float value
+ * accumulator; quotient rounded to bf16 (the reduce stage's publication). */
+int yvx_oracle_latent_reduce_full(const yvx_oracle_latent_args *a, float *out)
+{
+    const double scale = 1.0 / sqrt((double)a->head_dim);
+    unsigned long long ordinal, head, pass, candidate, lane;
+    for (ordinal = 0; ordinal < a->token_count; ++ordinal) {
+        const unsigned long long token_position = a->phase_start_position + ordinal;
+        unsigned long long local_offset, local_count, compressed_count;
+        if (a->candidate_block_visible) {
+            local_offset = 0ull;
+            local_count = a->initial_local_count + a->token_count;
+        } else {
+            unsigned long long before = a->initial_local_count + ordinal;
+            unsigned long long history = token_position < a->sliding_window - 1ull
+                                             ? token_position : a->sliding_window - 1ull;
+            if (history > before) return 0;
+            local_offset = before - history;
+            local_count = history + 1ull;
+        }
+        compressed_count = a->attention_class == 0u ? 0ull
+                           : a->attention_class == 1u
+                               ? a->selected_count[ordinal]
+                               : token_position / a->ratio + ((token_position + 1ull) % a->ratio == 0ull);
+        for (head = 0; head < a->query_heads; ++head) {
+            const float *q = a->query + (ordinal * a->query_heads + head) * a->head_dim;
+            float *o = out + (ordinal * a->query_heads + head) * a->head_dim;
+            double maximum = (double)a->sinks[head], denominator;
+            int phase;
+            if (!isfinite(maximum)) return 0;
+            memset(o, 0, (size_t)a->head_dim * sizeof(*o));
+            denominator = 0.0;
+            for (phase = 0; phase < 2; ++phase) {
+                if (phase == 1) denominator = exp((double)a->sinks[head] - maximum);
+                for (pass = 0; pass < 2ull; ++pass) {
+                    unsigned long long count = pass == 0ull ? local_count : compressed_count;
+                    for (candidate = 0; candidate < count; ++candidate) {
+                        const float *row = latent_row(a, pass, ordinal, candidate, local_offset);
+                        double score = 0.0;
+                        if (!row) continue;
+                        for (lane = 0; lane < a->head_dim; ++lane)
+                            score += (double)q[lane] * (double)row[lane];
+                        score *= scale;
+                        if (!isfinite(score)) return 0;
+                        if (phase == 0) {
+                            if (score > maximum) maximum = score;
+                        } else {
+                            score = exp(score - maximum);
+                            denominator += score;
+                            for (lane = 0; lane < a->head_dim; ++lane)
+                                o[lane] += (float)(score * row[lane]);
+                        }
+                    }
+                }
+            }
+            if (!isfinite(denominator) || denominator <= 0.0) return 0;
+            for (lane = 0; lane < a->head_dim; ++lane)
+                o[lane] = yvx_oracle_bf16_decode(
+                    yvx_oracle_bf16_encode((float)((double)o[lane] / denominator)));
+        }
+    }
+    return 1;
+}

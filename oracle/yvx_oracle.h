@@ -103,6 +103,26 @@ int yvx_oracle_latent_reduce(const float *query, const float *rows,
                              unsigned long long head_dimension,
                              unsigned long long row_stride, int round_bf16);
 
+/* The reduce stage's full argument set (window + compressed rows, sink). */
+typedef struct {
+    const float *query;                       /* [token][heads*head_dim] */
+    const float *local;                       /* [initial_local_count + token_count][local_stride] */
+    const unsigned long long *local_positions;
+    unsigned long long initial_local_count, local_stride;
+    const float *compressed;                  /* [rows][compressed_stride] */
+    const unsigned long long *compressed_positions;
+    unsigned long long compressed_stride;
+    const unsigned long long *selected;       /* [token][topk_capacity] (class 1) */
+    const unsigned long long *selected_count; /* [token] (class 1) */
+    unsigned long long topk_capacity;
+    const float *sinks;                       /* [heads] */
+    unsigned long long query_heads, head_dim, sliding_window, ratio;
+    unsigned int attention_class;             /* 0 window only, 1 selected rows, 2 all rows */
+    unsigned long long phase_start_position, token_count;
+    int candidate_block_visible;
+} yvx_oracle_latent_args;
+int yvx_oracle_latent_reduce_full(const yvx_oracle_latent_args *args, float *out);
+
 /* Latent decode with a separate rope key and an absorbed up-projection. */
 int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
                           const unsigned short *q_rope_bf16,

@@ -199,3 +199,33 @@ def test_mla_restatement_matches_dense_recomputation(oracle):
     p = np.exp(s - s.max(axis=1, keepdims=True))
     p /= p.sum(axis=1, keepdims=True)
     assert np.allclose(out, p @ f(lat[0]), atol=1e-6)
+
+
+def test_full_latent_reduce_restatement_cross_checks(oracle):
+    # Window-only class with a window wider than the history is plain shared-row
+    # attention with a sink: it must equal the simpler restatement, and the sink
+    # known-answer vector of the reference must come out of it too.
+    import ctypes as C
+    from clori_b200 import abi
+    rng = np.random.default_rng(12)
+    heads, hd, rows_n, tokens = 3, 32, 20, 2
+    q = rng.standard_normal((tokens, heads * hd)).astype(np.float32)
+    rows = rng.standard_normal((rows_n, hd)).astype(np.float32)
+    sinks = rng.standard_normal(heads).astype(np.float32)
+    positions = np.arange(rows_n, dtype=np.uint64)
+    zeros = np.zeros(4, np.uint64)
+    a = abi.LatentReduceArgs()
+    a.query, a.local, a.local_positions = q.ctypes.data, rows.ctypes.data, positions.ctypes.data
+    a.initial_local_count, a.local_stride = rows_n - tokens, hd
+    a.compressed = a.compressed_positions = a.selected = a.selected_count = zeros.ctypes.data
+    a.sinks, a.query_heads, a.head_dim = sinks.ctypes.data, heads, hd
+    a.sliding_window, a.ratio, a.attention_class = 128, 0, 0
+    a.phase_start_position, a.token_count = rows_n - tokens, tokens
+    full = oracle.latent_reduce_full(a, tokens, heads, hd)
+    simple = oracle.latent_reduce(q, rows, sinks, query_start=rows_n - tokens, heads=heads, head_dim=hd)
+    assert np.array_equal(full, simple)
+    # a window of 4 hides the older rows
+    a.sliding_window = 4
+    windowed = oracle.latent_reduce_full(a, tokens, heads, hd)
+    visible = oracle.latent_reduce(q[1:], rows[rows_n - 4:], sinks, query_start=3, heads=heads, head_dim=hd)
+    assert np.array_equal(windowed[1:], visible)
