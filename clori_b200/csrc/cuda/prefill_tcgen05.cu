@@ -1,21 +1,27 @@
 // Causal / full prefill attention on the 5th-generation tensor cores (sm_100a):
-// bf16 Q/K/V, head_dim 128, f32 softmax and accumulation, one 128-row query
-// tile of one query head per CTA.
+// bf16 Q/K/V, head_dim 128, f32 softmax and accumulation. One CTA owns TWO
+// 128-row query tiles (A, B: 256 consecutive rows) of one query head: every
+// K / V tile brought into shared memory feeds twice the tensor work, and while
+// one tile is in its softmax phase the other is in its matrix phase.
 //
-//   warp 4      TMA producer: the Q tile once, then 128-token K and V tiles into
-//               two-stage rings (128-byte swizzle, full/empty mbarriers)
-//   warp 5      allocates tensor memory and issues tcgen05.mma from one lane:
-//               S = Q K^T  (A, B in shared memory, 8 k-steps of 128x128x16)
-//               O += P V   (A = P in tensor memory, B = V tile, MN-major)
-//   warps 0-3   softmax: thread r owns query row r == TMEM lane r. It reads its
-//               128 scores with tcgen05.ld, keeps the running max / sum in
-//               registers, rescales O in tensor memory only when the max grew by
-//               more than 2^8 (the stale max keeps P <= 256, exact in f32/bf16
-//               range), writes P as packed bf16 back into the score columns with
-//               tcgen05.st, and hands it to the MMA warp.
-// Two score buffers let S(j+1) be computed while softmax works on S(j).
-// Tensor memory map (512 columns): S0 [0,128) S1 [128,256) O [256,384); P(j)
-// aliases the first 64 columns of S(j%2).
+//   warp 8      TMA producer: both Q tiles once, then 128-token K and V tiles
+//               into two-stage rings (128-byte swizzle, full/empty mbarriers)
+//   warp 9      allocates tensor memory and issues tcgen05.mma; all 32 lanes run
+//               the loop converged and one elected lane issues, which keeps the
+//               descriptors in uniform registers:
+//               S_x = Q_x K^T (A, B in shared memory, 8 k-steps of 128x128x16)
+//               O_x += P_x V  (A = P in tensor memory, B = V tile, MN-major)
+//               in the order PV_A(j) QK_A(j+1) PV_B(j) QK_B(j+1)
+//   warps 0-3   softmax of tile A, warps 4-7 softmax of tile B: thread r owns
+//               query row r == TMEM lane r. It reads its 128 scores with
+//               tcgen05.ld, keeps the running max / sum in registers, rescales O
+//               in tensor memory only when the max grew by more than 2^8 (the
+//               stale max keeps P <= 256, exact in f32/bf16 range), and writes P
+//               as packed bf16 back into the score columns with tcgen05.st in two
+//               halves of 64 tokens, each handed to the MMA warp as soon as it is
+//               stored, so P V starts while the second half is exponentiated.
+// Tensor memory map (512 columns): S_A [0,128) S_B [128,256) O_A [256,384)
+// O_B [384,512); P_x aliases the first 64 columns of S_x.
 //
 // Replaces the reference's tiled MHA prefill (src/backend/cuda/transformer.c:
 // 493-677: cuBLAS SGEMM QK^T, softmax kernel, SGEMM PV over a materialised
@@ -24,14 +30,14 @@
 
 namespace yvx {
 
-constexpr int kPfM = 128;          // query rows per CTA
+constexpr int kPfM = 128;          // query rows per tile (two tiles per CTA)
 constexpr int kPfN = 128;          // KV tokens per tile
 constexpr int kPfD = 128;          // head_dim
 constexpr int kPfStages = 2;
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 320;
 constexpr int kPfHalfBytes = kPfM * 64 * 2;        // one [128][64] bf16 swizzled half tile
 constexpr int kPfTileBytes = 2 * kPfHalfBytes;     // 32 KB
-constexpr int kPfSmemBytes = (1 + 2 * kPfStages) * kPfTileBytes + 1024 + 512;
+constexpr int kPfSmemBytes = (2 + 2 * kPfStages) * kPfTileBytes + 1024 + 512;
 constexpr float kPfRescaleThreshold = 8.0f;        // log2 units
 constexpr uint32_t kPfTmemColumns = 512;
 
@@ -43,11 +49,11 @@ struct PrefillBarriers {
     uint64_t q_full;
     uint64_t k_full[kPfStages], k_empty[kPfStages];
     uint64_t v_full[kPfStages], v_empty[kPfStages];
-    uint64_t s_full[2], p_full[2];
-    uint64_t pv_done;
+    uint64_t s_full[2], p_half[2][2], pv_done[2];  // per query tile; P is handed over in halves
     uint32_t tmem_base;
     int abort_flag;
 };
+static_assert(sizeof(PrefillBarriers) <= 512, "barrier block outgrew its shared-memory slot");
 
 __device__ __forceinline__ void prefill_fail(const yvx_gqa_problem &p, PrefillBarriers *bars)
 {
@@ -55,7 +61,28 @@ __device__ __forceinline__ void prefill_fail(const yvx_gqa_problem &p, PrefillBa
     bars->abort_flag = 1;
 }
 
-// grid: x = query tile (longest first), y = query head, z = session.
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// Number of 128-token KV tiles the rows [row0, row0 + 128) of the query can see.
+__device__ __forceinline__ unsigned int prefill_tile_count(const yvx_gqa_problem &p,
+                                                           unsigned int row0, long long query_start,
+                                                           unsigned int kv_tokens)
+{
+    if (row0 >= p.query_rows) return 0u;
+    long long visible_end = kv_tokens;
+    if (p.causal) {
+        const long long last = query_start + (long long)min(row0 + kPfM, p.query_rows);
+        if (last < visible_end) visible_end = last;
+    }
+    return visible_end > 0 ? (unsigned int)((visible_end + kPfN - 1) / kPfN) : 0u;
+}
+
+// grid: x = pair of query tiles (longest first), y = query head, z = session.
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillMaps maps,
                        const int head_major)
@@ -63,15 +90,14 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
-    unsigned char *q_tile = smem;
-    unsigned char *k_tiles = smem + kPfTileBytes;
+    unsigned char *q_tiles_smem = smem;                          // tile A, then tile B
+    unsigned char *k_tiles = smem + 2 * kPfTileBytes;
     unsigned char *v_tiles = k_tiles + kPfStages * kPfTileBytes;
     PrefillBarriers *bars = reinterpret_cast<PrefillBarriers *>(v_tiles + kPfStages * kPfTileBytes);
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const unsigned int q_tiles = (p.query_rows + kPfM - 1) / kPfM;
-    const unsigned int q_tile_index = q_tiles - 1u - blockIdx.x;
-    const unsigned int q0 = q_tile_index * kPfM;
+    const unsigned int pairs = (p.query_rows + 2 * kPfM - 1) / (2 * kPfM);
+    const unsigned int q0 = (pairs - 1u - blockIdx.x) * 2u * kPfM;
     const unsigned int qhead = blockIdx.y, b = blockIdx.z;
     const unsigned int kv_head = qhead / (p.query_heads / p.kv_heads);
     const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
@@ -79,13 +105,9 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
         p.query_start ? (long long)p.query_start[b]
                       : (p.query_start_from_end ? (long long)kv_tokens - (long long)p.query_rows
                                                 : (long long)p.query_start_uniform);
-    // Tokens any row of this tile can see.
-    long long visible_end = kv_tokens;
-    if (p.causal) {
-        const long long last = query_start + (long long)min(q0 + kPfM, p.query_rows);
-        if (last < visible_end) visible_end = last;
-    }
-    const unsigned int tiles = visible_end > 0 ? (unsigned int)((visible_end + kPfN - 1) / kPfN) : 0u;
+    const unsigned int tiles_a = prefill_tile_count(p, q0, query_start, kv_tokens);
+    const unsigned int tiles_b = prefill_tile_count(p, q0 + kPfM, query_start, kv_tokens);
+    const unsigned int tiles = max(tiles_a, tiles_b);
 
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
@@ -97,13 +119,14 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], kPfM);
+            mbar_init(&bars->p_half[i][0], kPfM);
+            mbar_init(&bars->p_half[i][1], kPfM);
+            mbar_init(&bars->pv_done[i], 1);
         }
-        mbar_init(&bars->pv_done, 1);
         bars->abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(&bars->tmem_base, kPfTmemColumns);
         tmem_relinquish();
     }
@@ -112,12 +135,16 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
     tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0 && tiles) {
-            mbar_expect_tx(&bars->q_full, kPfTileBytes);
-            tma_load_4d(q_tile, &maps.query, &bars->q_full, 0, (int)qhead, (int)q0, (int)b);
-            tma_load_4d(q_tile + kPfHalfBytes, &maps.query, &bars->q_full, 64, (int)qhead, (int)q0, (int)b);
+            mbar_expect_tx(&bars->q_full, (tiles_b ? 2u : 1u) * kPfTileBytes);
+            for (unsigned int x = 0; x < (tiles_b ? 2u : 1u); ++x) {
+                unsigned char *qd = q_tiles_smem + x * kPfTileBytes;
+                const int row = (int)(q0 + x * kPfM);
+                tma_load_4d(qd, &maps.query, &bars->q_full, 0, (int)qhead, row, (int)b);
+                tma_load_4d(qd + kPfHalfBytes, &maps.query, &bars->q_full, 64, (int)qhead, row, (int)b);
+            }
             for (unsigned int j = 0; j < tiles; ++j) {
                 const unsigned int stage = j % kPfStages;
                 const uint32_t parity = ((j / kPfStages) - 1u) & 1u;
@@ -142,89 +169,112 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
                 tma_load_4d(vd + kPfHalfBytes, &maps.value, &bars->v_full[stage], 64, c1, c2, (int)b);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0 && tiles) {
+        // All 32 lanes run the loop converged; one elected lane issues each instruction.
+        if (tiles) {
             constexpr uint32_t idesc_qk = idesc_bf16_f32(kPfM, kPfN, false);
             constexpr uint32_t idesc_pv = idesc_bf16_f32(kPfM, kPfD, true);
-            const uint32_t q_addr = smem_u32(q_tile);
-            bool ok = mbar_wait(&bars->q_full, 0);
-            auto issue_qk = [&](unsigned int j) -> bool {
-                const unsigned int stage = j % kPfStages;
-                if (!mbar_wait(&bars->k_full[stage], (j / kPfStages) & 1u)) return false;
-                tc_fence_after_sync();
-                const uint32_t k_addr = smem_u32(k_tiles + stage * kPfTileBytes);
-                const uint32_t d = tmem + (j & 1u) * kPfN;
+            const uint32_t q_addr = smem_u32(q_tiles_smem);
+            const unsigned int tiles_x[2] = {tiles_a, tiles_b};
+            // S_x(j) = Q_x K(j)^T; the K stage is known to be full.
+            auto issue_qk = [&](unsigned int x, unsigned int j) {
+                const uint32_t k_addr = smem_u32(k_tiles + (j % kPfStages) * kPfTileBytes);
+                const uint32_t qa = q_addr + x * kPfTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (ks >> 2) * kPfHalfBytes + (ks & 3) * 32;
-                    tc_mma_ss(d, smem_desc_sw128(q_addr + off, 16, 1024),
+                    tc_mma_ss_elect(tmem + x * kPfN, smem_desc_sw128(qa + off, 16, 1024),
                               smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks ? 1u : 0u);
                 }
-                tc_commit(&bars->k_empty[stage]);
-                tc_commit(&bars->s_full[j & 1u]);
+                tc_commit_elect(&bars->s_full[x]);
+            };
+            // O_x += P_x(j) V(j); the V stage is known to be full.
+            auto issue_pv = [&](unsigned int x, unsigned int j) -> bool {
+                const uint32_t v_addr = smem_u32(v_tiles + (j % kPfStages) * kPfTileBytes);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    // The weights of the first 64 tokens arrive while the softmax warps
+                    // are still exponentiating the last 64.
+                    if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_half[x][h], j & 1u))) return false;
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+                        tc_mma_ts_elect(tmem + (2 + x) * kPfN, tmem + x * kPfN + kk * 8,
+                                        smem_desc_sw128(v_addr + kk * 2048, kPfHalfBytes, 1024),
+                                        idesc_pv, (j || kk) ? 1u : 0u);
+                }
+                tc_commit_elect(&bars->pv_done[x]);
                 return true;
             };
-            if (ok) ok = issue_qk(0);
-            for (unsigned int j = 0; ok && j < tiles; ++j) {
-                if (j + 1 < tiles) ok = issue_qk(j + 1);
-                if (!ok) break;
-                const unsigned int stage = j % kPfStages;
-                if (!mbar_wait(&bars->p_full[j & 1u], (j >> 1) & 1u) ||
-                    !mbar_wait(&bars->v_full[stage], (j / kPfStages) & 1u)) {
-                    ok = false;
-                    break;
-                }
+            bool ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full, 0));
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->k_full[0], 0));
+            if (ok) {
                 tc_fence_after_sync();
-                const uint32_t v_addr = smem_u32(v_tiles + stage * kPfTileBytes);
-                const uint32_t p_tmem = tmem + (j & 1u) * kPfN;
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    tc_mma_ts(tmem + 2 * kPfN, p_tmem + kk * 8,
-                              smem_desc_sw128(v_addr + kk * 2048, kPfHalfBytes, 1024), idesc_pv,
-                              (j || kk) ? 1u : 0u);
-                tc_commit(&bars->v_empty[stage]);
-                tc_commit(&bars->pv_done);
+                for (unsigned int x = 0; x < 2; ++x)
+                    if (tiles_x[x]) issue_qk(x, 0);
+                tc_commit_elect(&bars->k_empty[0]);
             }
-            if (!ok) prefill_fail(p, bars);
+            for (unsigned int j = 0; ok && j < tiles; ++j) {
+                const unsigned int stage = j % kPfStages, next = (j + 1) % kPfStages;
+                const bool more = j + 1 < tiles;
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars->v_full[stage], (j / kPfStages) & 1u));
+                if (ok && more)
+                    ok = __all_sync(0xffffffffu,
+                                    mbar_wait(&bars->k_full[next], ((j + 1) / kPfStages) & 1u));
+#pragma unroll
+                for (unsigned int x = 0; x < 2; ++x) {
+                    if (ok && j < tiles_x[x]) ok = issue_pv(x, j);
+                    if (ok && j + 1 < tiles_x[x]) issue_qk(x, j + 1);
+                }
+                if (!ok) break;
+                tc_commit_elect(&bars->v_empty[stage]);
+                if (more) tc_commit_elect(&bars->k_empty[next]);
+            }
+            if (!ok && lane == 0) prefill_fail(p, bars);
         }
     } else {
         // ------------------------------ softmax warps -----------------------------
-        const unsigned int row = threadIdx.x;  // query row in the tile == TMEM lane
-        const uint32_t lane_base = tmem + ((warp * 32u) << 16);
-        const long long qi = (long long)q0 + row;
+        const unsigned int x = warp >> 2;                 // 0: tile A, 1: tile B
+        const unsigned int row = threadIdx.x & 127u;      // query row in the tile == TMEM lane
+        const unsigned int my_tiles = x ? tiles_b : tiles_a;
+        const uint32_t lane_base = tmem + (((warp & 3u) * 32u) << 16);
+        const uint32_t s_col = lane_base + x * kPfN, o_col = lane_base + (2u + x) * kPfN;
+        const long long qi = (long long)q0 + x * kPfM + row;
         long long row_limit = (long long)kv_tokens - 1;
         if (p.causal && query_start + qi < row_limit) row_limit = query_start + qi;
         const float sscale = p.scale * 1.4426950408889634f;
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
-        for (unsigned int j = 0; j < tiles; ++j) {
-            const unsigned int buf = j & 1u;
-            if (!mbar_wait(&bars->s_full[buf], (j >> 1) & 1u)) {
+        for (unsigned int j = 0; j < my_tiles; ++j) {
+            if (!mbar_wait(&bars->s_full[x], j & 1u)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
             uint32_t s[4][32];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) tmem_ld32(lane_base + buf * kPfN + 32 * i, s[i]);
+            for (int i = 0; i < 4; ++i) tmem_ld32(s_col + 32 * i, s[i]);
             tmem_wait_ld();
             const long long k0 = (long long)j * kPfN;
-            float row_max = -INFINITY;
+            // Masked entries become -inf; the maximum runs over four independent
+            // chains of three-input max instructions.
             if (k0 + kPfN - 1 > row_limit) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        if (k0 + 32 * i + c > row_limit) s[i][c] = 0xff800000u;  // -inf
-                        row_max = fmaxf(row_max, __uint_as_float(s[i][c]));
-                    }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) row_max = fmaxf(row_max, __uint_as_float(s[i][c]));
+                    for (int c = 0; c < 32; ++c)
+                        if (k0 + 32 * i + c > row_limit) s[i][c] = 0xff800000u;
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[i][c]),
+                                            __uint_as_float(s[i][c + 1]));
+            const float row_max = max3(mx[0], mx[1], fmaxf(mx[2], mx[3]));
             const float m_tile = row_max * sscale;  // -inf stays -inf (sscale > 0)
             const bool grow = m_tile > m_used + kPfRescaleThreshold || m_used == -INFINITY;
             if (__any_sync(0xffffffffu, grow)) {
@@ -234,47 +284,48 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
                 m_used = m_new;
                 if (j > 0) {
                     // O may only be touched once the previous tile's P V has landed.
-                    if (!mbar_wait(&bars->pv_done, (j - 1u) & 1u)) {
+                    if (!mbar_wait(&bars->pv_done[x], (j - 1u) & 1u)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t o[32];
-                        tmem_ld32(lane_base + 2 * kPfN + 32 * i, o);
+                    for (int i = 0; i < 8; ++i) {
+                        uint32_t o[16];
+                        tmem_ld16(o_col + 16 * i, o);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-                        tmem_st32(lane_base + 2 * kPfN + 32 * i, o);
+                        for (int c = 0; c < 16; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                        tmem_st16(o_col + 16 * i, o);
                     }
                     tmem_wait_st();
                 }
             }
             const float offset = m_used == -INFINITY ? 0.0f : -m_used;
-            uint32_t packed[2][32];
-            float sum = 0.0f;
+            float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int h = 0; h < 2; ++h) {
+                uint32_t packed[32];
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(s[i][c]), sscale, offset));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(s[i][c + 1]), sscale, offset));
-                    // The row sum uses the bf16-rounded weights the MMA will use,
-                    // so the normalised weights stay consistent with the value mix.
-                    const uint32_t pair = pack_bf16(p0, p1);
-                    sum += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
-                    packed[i >> 1][(i & 1) * 16 + (c >> 1)] = pair;
-                }
-            l += sum;
-            tmem_st32(lane_base + buf * kPfN, packed[0]);
-            tmem_st32(lane_base + buf * kPfN + 32, packed[1]);
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(&bars->p_full[buf]);
+                for (int i = 2 * h; i < 2 * h + 2; ++i)
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        const float p0 = exp2_approx(fmaf(__uint_as_float(s[i][c]), sscale, offset));
+                        const float p1 = exp2_approx(fmaf(__uint_as_float(s[i][c + 1]), sscale, offset));
+                        sum0 += p0;
+                        sum1 += p1;
+                        packed[(i & 1) * 16 + (c >> 1)] = pack_bf16(p0, p1);
+                    }
+                // Hand over the weights of tokens 64 * h .. 64 * h + 63.
+                tmem_st32(s_col + 32 * h, packed);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(&bars->p_half[x][h]);
+            }
+            l += sum0 + sum1;
         }
         // ------------------------------ epilogue ------------------------------------
-        if (ok && tiles) ok = mbar_wait(&bars->pv_done, (tiles - 1u) & 1u);
+        if (ok && my_tiles) ok = mbar_wait(&bars->pv_done[x], (my_tiles - 1u) & 1u);
         // Every lane takes part in the tensor-memory loads; only rows that exist store.
         const bool all_ok = __all_sync(0xffffffffu, ok);
         if (!all_ok) {
@@ -286,14 +337,14 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
             const unsigned long long item =
                 (((unsigned long long)b * p.query_rows + (unsigned long long)(exists ? qi : 0)) *
                      p.query_heads + qhead) * kPfD;
-            bool finite = tiles != 0u;
+            bool finite = my_tiles != 0u;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 uint32_t o[32];
 #pragma unroll
                 for (int c = 0; c < 32; ++c) o[c] = 0u;
-                if (tiles) {
-                    tmem_ld32(lane_base + 2 * kPfN + 32 * i, o);
+                if (my_tiles) {
+                    tmem_ld32(o_col + 32 * i, o);
                     tmem_wait_ld();
                 }
                 float v[32];
@@ -321,7 +372,7 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, kPfTmemColumns);
+    if (warp == 9) tmem_dealloc(tmem, kPfTmemColumns);
 }
 
 // ---- host side ------------------------------------------------------------------
@@ -401,7 +452,7 @@ int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream)
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kPfSmemBytes);
     if (error != cudaSuccess) return yvx_cuda_check(error, "prefill_tcgen05_kernel attribute");
-    const dim3 grid((p.query_rows + kPfM - 1) / kPfM, p.query_heads, p.sessions);
+    const dim3 grid((p.query_rows + 2 * kPfM - 1) / (2 * kPfM), p.query_heads, p.sessions);
     prefill_tcgen05_kernel<<<grid, kPfThreads, kPfSmemBytes, stream>>>(p, maps, kv_head_first ? 1 : 0);
     const int rc = yvx_cuda_check(cudaGetLastError(), "prefill_tcgen05_kernel");
     return rc != 0 ? rc : 2;
