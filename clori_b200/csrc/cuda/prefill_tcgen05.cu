@@ -82,7 +82,9 @@ __device__ __forceinline__ unsigned int prefill_tile_count(const yvx_gqa_problem
     return visible_end > 0 ? (unsigned int)((visible_end + kPfN - 1) / kPfN) : 0u;
 }
 
-// grid: x = pair of query tiles (longest first), y = query head, z = session.
+// grid: one dimension, ordered longest first over the whole launch: the pair of
+// query tiles varies slowest, (session, query head) fastest, so the CTAs left
+// for the tail of the launch are the short ones and neighbours share K / V.
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillMaps maps,
                        const int head_major)
@@ -97,8 +99,10 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int pairs = (p.query_rows + 2 * kPfM - 1) / (2 * kPfM);
-    const unsigned int q0 = (pairs - 1u - blockIdx.x) * 2u * kPfM;
-    const unsigned int qhead = blockIdx.y, b = blockIdx.z;
+    const unsigned int lanes_of_work = p.query_heads * p.sessions;
+    const unsigned int q0 = (pairs - 1u - blockIdx.x / lanes_of_work) * 2u * kPfM;
+    const unsigned int qhead = (blockIdx.x % lanes_of_work) % p.query_heads;
+    const unsigned int b = (blockIdx.x % lanes_of_work) / p.query_heads;
     const unsigned int kv_head = qhead / (p.query_heads / p.kv_heads);
     const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
     const long long query_start =
@@ -452,7 +456,10 @@ int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream)
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kPfSmemBytes);
     if (error != cudaSuccess) return yvx_cuda_check(error, "prefill_tcgen05_kernel attribute");
-    const dim3 grid((p.query_rows + 2 * kPfM - 1) / (2 * kPfM), p.query_heads, p.sessions);
+    const unsigned long long ctas = (unsigned long long)((p.query_rows + 2 * kPfM - 1) / (2 * kPfM)) *
+                                    p.query_heads * p.sessions;
+    if (ctas == 0ull || ctas > 0x7fffffffull) return 0;
+    const dim3 grid((unsigned int)ctas, 1, 1);
     prefill_tcgen05_kernel<<<grid, kPfThreads, kPfSmemBytes, stream>>>(p, maps, kv_head_first ? 1 : 0);
     const int rc = yvx_cuda_check(cudaGetLastError(), "prefill_tcgen05_kernel");
     return rc != 0 ? rc : 2;
