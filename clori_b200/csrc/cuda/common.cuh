@@ -26,6 +26,19 @@ int yvx_cuda_check(cudaError_t error, const char *what);
 
 namespace yvx {
 
+// Programmatic dependent launch: a kernel launched with the programmatic stream
+// serialization attribute may be scheduled once every CTA of the kernel before
+// it has called pdl_launch_dependents() (or exited); it must call pdl_wait()
+// before touching that kernel's results. Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

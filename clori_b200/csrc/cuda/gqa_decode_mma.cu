@@ -334,6 +334,8 @@ gqa_decode_mma_kernel(const yvx_gqa_problem p, const __grid_constant__ DecodeMap
     }
     named_barrier(1, kConsumerWarps * 32);
 
+    // The main loop is over: let the combine kernel's launch overlap the epilogue.
+    pdl_launch_dependents();
     const bool direct = p.max_splits == 1u;
     const unsigned int d = threadIdx.x;  // 0..127: one head dimension per consumer thread
     for (unsigned int row = 0; row < live; ++row) {

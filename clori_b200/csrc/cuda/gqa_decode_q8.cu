@@ -409,6 +409,8 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
     }
     named_barrier(1, kQ8ConsumerWarps * 32);
 
+    // The main loop is over: let the combine kernel's launch overlap the epilogue.
+    pdl_launch_dependents();
     const bool direct = p.max_splits == 1u;
     const unsigned int d = threadIdx.x;
     for (unsigned int row = 0; row < live; ++row) {

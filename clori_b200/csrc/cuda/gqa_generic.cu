@@ -209,6 +209,8 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
     }
     __syncthreads();
 
+    // The main loop is over: let the combine kernel's launch overlap the epilogue.
+    pdl_launch_dependents();
     const bool direct = p.max_splits == 1u;
     for (int i = 0; i < VT; ++i) {
         const unsigned int v = tile * VT + i;
@@ -248,12 +250,16 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
 }
 
 // One CTA per (session, row, query head): folds the per-split (o, m, l)
-// triples. Eight warps share the splits (warp w takes splits w, w+8, ...), lanes
-// own head dimensions; per-warp sums are merged in warp order, so the result
-// is a fixed function of the inputs and does not depend on scheduling.
+// triples in a single pass over global memory. Eight warps share the splits
+// (warp w takes splits w, w+8, ...) and keep a running (max, sum, weighted
+// value) each; lanes own head dimensions. The loads of four splits are issued
+// together, so a warp's whole share is usually one round trip. Per-warp
+// results are merged in warp order: the result is a fixed function of the
+// inputs and does not depend on scheduling.
 constexpr int kCombineWarps = 8;
+constexpr int kCombineBatch = 4;
 
-__device__ __forceinline__ void combine_parts(const float *parts, unsigned int count,
+__device__ __forceinline__ void combine_parts(const float *__restrict__ parts, unsigned int count,
                                               unsigned int stride, unsigned int hd, void *output,
                                               int output_dtype, unsigned long long out_index,
                                               float *partial_out, int *status)
@@ -262,42 +268,56 @@ __device__ __forceinline__ void combine_parts(const float *parts, unsigned int c
     __shared__ float sm_sum[kCombineWarps];
     __shared__ float sm_acc[kCombineWarps][256];
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    // global maximum of m over the parts
-    float mm = -INFINITY;
-    for (unsigned int j = threadIdx.x; j < count; j += blockDim.x)
-        mm = fmaxf(mm, parts[(unsigned long long)j * stride + hd]);
-    mm = warp_max(mm);
-    if (lane == 0) sm_max[warp] = mm;
-    __syncthreads();
-    mm = sm_max[0];
-#pragma unroll
-    for (int w = 1; w < kCombineWarps; ++w) mm = fmaxf(mm, sm_max[w]);
-    // weighted sums over this warp's parts
-    float acc[8], ll = 0.0f;
+    float acc[8], run_max = -INFINITY, run_sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-    for (unsigned int j = warp; j < count; j += kCombineWarps) {
-        const float *part = parts + (unsigned long long)j * stride;
-        const float mj = part[hd];
-        const float weight = mj == -INFINITY ? 0.0f : part[hd + 1] * expf(mj - mm);
-        ll += weight;
+    for (unsigned int j0 = warp; j0 < count; j0 += kCombineWarps * kCombineBatch) {
+        float mj[kCombineBatch], lj[kCombineBatch], oj[kCombineBatch][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const unsigned int d = lane + 32u * i;
-            if (d < hd) acc[i] = fmaf(part[d], weight, acc[i]);
+        for (int u = 0; u < kCombineBatch; ++u) {
+            const unsigned int j = j0 + u * kCombineWarps;
+            const bool live = j < count;
+            const float *part = parts + (unsigned long long)(live ? j : j0) * stride;
+            mj[u] = live ? part[hd] : -INFINITY;
+            lj[u] = part[hd + 1];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const unsigned int d = lane + 32u * i;
+                oj[u][i] = d < hd ? part[d] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kCombineBatch; ++u) {
+            if (mj[u] == -INFINITY) continue;  // empty split or past the end (warp-uniform)
+            const float new_max = fmaxf(run_max, mj[u]);
+            const float keep = expf(run_max - new_max);  // exp(-inf) = 0 on the first live split
+            const float weight = lj[u] * expf(mj[u] - new_max);
+            run_sum = fmaf(run_sum, keep, weight);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(acc[i], keep, oj[u][i] * weight);
+            run_max = new_max;
         }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) sm_acc[warp][lane + 32 * i] = acc[i];
-    if (lane == 0) sm_sum[warp] = ll;
+    if (lane == 0) {
+        sm_max[warp] = run_max;
+        sm_sum[warp] = run_sum;
+    }
     __syncthreads();
-    ll = 0.0f;
+    float mm = sm_max[0];
 #pragma unroll
-    for (int w = 0; w < kCombineWarps; ++w) ll += sm_sum[w];
+    for (int w = 1; w < kCombineWarps; ++w) mm = fmaxf(mm, sm_max[w]);
+    float scale_w[kCombineWarps], ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kCombineWarps; ++w) {
+        scale_w[w] = sm_max[w] == -INFINITY ? 0.0f : expf(sm_max[w] - mm);
+        ll = fmaf(sm_sum[w], scale_w[w], ll);
+    }
     for (unsigned int d = threadIdx.x; d < hd; d += blockDim.x) {
         float o = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kCombineWarps; ++w) o += sm_acc[w][d];
+        for (int w = 0; w < kCombineWarps; ++w) o = fmaf(sm_acc[w][d], scale_w[w], o);
         if (partial_out) {
             partial_out[d] = ll > 0.0f ? o / ll : 0.0f;
             if (d == 0) {
@@ -315,6 +335,7 @@ __device__ __forceinline__ void combine_parts(const float *parts, unsigned int c
 __global__ void __launch_bounds__(kCombineWarps * 32)
 gqa_combine_kernel(const yvx_gqa_problem p)
 {
+    pdl_wait();  // the split kernel's partials must be complete and visible
     const unsigned long long item = blockIdx.x;
     const unsigned int b = (unsigned int)(item / ((unsigned long long)p.query_rows * p.query_heads));
     const unsigned int hd = p.head_dim;
@@ -376,7 +397,20 @@ int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream)
 int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream)
 {
     const unsigned long long items = (unsigned long long)p.sessions * p.query_rows * p.query_heads;
-    gqa_combine_kernel<<<(unsigned int)items, kCombineWarps * 32, 0, stream>>>(p);
+    // Launched so that its scheduling overlaps the tail of the split kernel
+    // before it in the stream; the kernel itself waits for that kernel's results.
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned int)items, 1, 1);
+    config.blockDim = dim3(kCombineWarps * 32, 1, 1);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    const cudaError_t launched = cudaLaunchKernelEx(&config, gqa_combine_kernel, p);
+    if (launched != cudaSuccess) return yvx_cuda_check(launched, "gqa_combine_kernel");
     return yvx_cuda_check(cudaGetLastError(), "gqa_combine_kernel");
 }
 
