@@ -10,11 +10,17 @@
 // and as V (the same bytes read MN-major). The f32 output of 128 heads x 512
 // dims would fill all of tensor memory, so a CTA owns one half of the latent
 // dims (256 accumulator columns) and recomputes S; the two CTAs of a pair run
-// side by side and share their tile through L2. Shared memory cannot hold the
-// whole absorbed query next to two 72 KB tiles, so the first 384 query dims
-// live in tensor memory (192 columns, A operand of the first 24 k-steps) and
-// only the last 192 dims are staged in shared memory.
-// Tensor memory map: O [0,256) | S [256,320), P aliases its first 32 | Q [320,512).
+// side by side and share their tile through L2.
+//
+// Each stage of the two-stage tile ring has two parts with their own full /
+// free barriers: the CTA's own latent half (32 KB: K of the last 16 k-steps and
+// V of P V, free after P V) and the scores-only part (other half + rope, 40 KB,
+// free after the first 20 k-steps). The matching query dims of the own half sit
+// in tensor memory (128 columns), the rest in shared memory (80 KB). The score
+// buffer is double: the tensor pipe runs S(j+1) part one, P(j) V(j), S(j+1)
+// part two, so the softmax of tile j and the tile loads hide under the MMAs.
+// Tensor memory map: O [0,256) | S0 [256,320) S1 [320,384), P(j) aliases the
+// first 32 columns of S(j % 2) | Q [384,512).
 #include "tcgen05.cuh"
 
 namespace yvx {
@@ -26,11 +32,13 @@ constexpr int kMlaHalf = kMlaLatent / 2;                   // accumulator column
 constexpr int kMlaStages = 2;
 constexpr int kMlaThreads = 192;
 constexpr int kMlaQSubBytes = kMlaHeads * 64 * 2;          // [128][64] bf16 = 16 KB
-constexpr int kMlaQTmemDims = 384;                         // query dims held in tensor memory
-constexpr int kMlaQSmemSubs = (kMlaWidth - kMlaQTmemDims) / 64;  // 3 sub-tiles stay in shared memory
+constexpr int kMlaQTmemDims = kMlaHalf;                   // own-half query dims held in tensor memory                         // query dims held in tensor memory
+constexpr int kMlaQSmemSubs = (kMlaWidth - kMlaQTmemDims) / 64;  // 5 sub-tiles stay in shared memory
 constexpr int kMlaQBytes = kMlaQSmemSubs * kMlaQSubBytes;
 constexpr int kMlaKvSubBytes = kMlaN * 64 * 2;             // [64][64] bf16 = 8 KB
 constexpr int kMlaKvBytes = (kMlaWidth / 64) * kMlaKvSubBytes; // 72 KB
+constexpr int kMlaVPartBytes = (kMlaHalf / 64) * kMlaKvSubBytes;    // own latent half, first in a stage
+constexpr int kMlaKOnlyBytes = kMlaKvBytes - kMlaVPartBytes;       // other half + rope
 constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256;
 constexpr uint32_t kMlaTmemColumns = 512;
 constexpr float kMlaRescaleThreshold = 8.0f;
@@ -41,11 +49,14 @@ struct MlaMaps {
 
 struct MlaBarriers {
     uint64_t q_full, q_tmem_full;
-    uint64_t kv_full[kMlaStages], v_done[kMlaStages];
-    uint64_t s_full, p_full;
+    uint64_t ka_full[kMlaStages], kb_full[kMlaStages];  // scores-only part / own-half part loaded
+    uint64_t ka_done[kMlaStages], v_done[kMlaStages];   // ... and free again
+    uint64_t s_full[2], p_full[2];
     uint64_t pv_done;
     uint32_t tmem_base;
 };
+static_assert(sizeof(MlaBarriers) <= 256, "barrier block outgrew its shared-memory slot");
+static_assert(kMlaStages == 2, "score buffers and stages are indexed by tile parity");
 
 // ---- absorb: q_abs[b][h] = [ bf16(q_nope[b][h] . W_uk[h]) | q_rope[b][h] ] ----------
 // grid (heads, ceil(sessions/16)); 4 warps, warp w owns latent columns [128w, 128w+128).
@@ -158,16 +169,20 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         return;
     }
     const unsigned int tiles = (t1 - t0 + kMlaN - 1) / kMlaN;
+    // Sub-tile (64 dims) indices: this CTA's own latent half, and the other one.
+    const int own0 = 4 * (int)half, other0 = 4 * (1 - (int)half);
 
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
         mbar_init(&bars->q_tmem_full, kMlaHeads);
         for (int i = 0; i < kMlaStages; ++i) {
-            mbar_init(&bars->kv_full[i], 1);
+            mbar_init(&bars->ka_full[i], 1);
+            mbar_init(&bars->kb_full[i], 1);
+            mbar_init(&bars->ka_done[i], 1);
             mbar_init(&bars->v_done[i], 1);
+            mbar_init(&bars->s_full[i], 1);
+            mbar_init(&bars->p_full[i], kMlaHeads);
         }
-        mbar_init(&bars->s_full, 1);
-        mbar_init(&bars->p_full, kMlaHeads);
         mbar_init(&bars->pv_done, 1);
         fence_barrier_init();
     }
@@ -179,84 +194,116 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
-    const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf, tmem_q = tmem + kMlaHalf + kMlaN;
+    const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf, tmem_q = tmem + kMlaHalf + 2 * kMlaN;
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             mbar_expect_tx(&bars->q_full, kMlaQBytes);
-            for (int st = 0; st < kMlaQSmemSubs; ++st)
-                tma_load_3d(q_tile + st * kMlaQSubBytes, &maps.query, &bars->q_full,
-                            kMlaQTmemDims + 64 * st, 0, (int)b);
+            for (int u = 0; u < kMlaQSmemSubs; ++u)
+                tma_load_3d(q_tile + u * kMlaQSubBytes, &maps.query, &bars->q_full,
+                            u < 4 ? 64 * (other0 + u) : kMlaLatent, 0, (int)b);
             for (unsigned int j = 0; j < tiles; ++j) {
                 const unsigned int stage = j % kMlaStages;
-                if (j >= (unsigned)kMlaStages &&
-                    !mbar_wait(&bars->v_done[stage], ((j / kMlaStages) - 1u) & 1u)) {
+                const uint32_t parity = ((j / kMlaStages) - 1u) & 1u;
+                unsigned char *dst = kv_tiles + stage * kMlaKvBytes;
+                const int token = (int)(t0 + j * kMlaN);
+                // Scores-only part: free as soon as the first 20 k-steps of Q K^T have run.
+                if (j >= (unsigned)kMlaStages && !mbar_wait(&bars->ka_done[stage], parity)) {
                     atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
                     break;
                 }
-                unsigned char *dst = kv_tiles + stage * kMlaKvBytes;
-                const int token = (int)(t0 + j * kMlaN);
-                mbar_expect_tx(&bars->kv_full[stage], kMlaKvBytes);
-                for (int st = 0; st < kMlaLatent / 64; ++st)
-                    tma_load_3d(dst + st * kMlaKvSubBytes, &maps.latent, &bars->kv_full[stage], 64 * st, token, (int)b);
-                tma_load_3d(dst + (kMlaLatent / 64) * kMlaKvSubBytes, &maps.rope, &bars->kv_full[stage], 0, token, (int)b);
+                mbar_expect_tx(&bars->ka_full[stage], kMlaKOnlyBytes);
+                for (int u = 0; u < 4; ++u)
+                    tma_load_3d(dst + kMlaVPartBytes + u * kMlaKvSubBytes, &maps.latent,
+                                &bars->ka_full[stage], 64 * (other0 + u), token, (int)b);
+                tma_load_3d(dst + kMlaVPartBytes + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka_full[stage], 0,
+                            token, (int)b);
+                // Own latent half: K of the last 16 k-steps and V of P V; free after P V.
+                if (j >= (unsigned)kMlaStages && !mbar_wait(&bars->v_done[stage], parity)) {
+                    atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+                    break;
+                }
+                mbar_expect_tx(&bars->kb_full[stage], kMlaVPartBytes);
+                for (int u = 0; u < 4; ++u)
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full[stage],
+                                64 * (own0 + u), token, (int)b);
             }
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
-            constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
-            const uint32_t q_addr = smem_u32(q_tile);
-            bool ok = mbar_wait(&bars->q_full, 0) && mbar_wait(&bars->q_tmem_full, 0);
-            for (unsigned int j = 0; ok && j < tiles; ++j) {
-                const unsigned int stage = j % kMlaStages;
-                if (!mbar_wait(&bars->kv_full[stage], (j / kMlaStages) & 1u)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t kv_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
-                // S = Q K^T: query dims [0,384) from tensor memory, the rest from shared memory.
-#pragma unroll 4
-                for (int ks = 0; ks < kMlaQTmemDims / 16; ++ks)
-                    tc_mma_ts(tmem_s, tmem_q + ks * 8,
-                              smem_desc_sw128(kv_addr + (ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32, 16, 1024),
-                              idesc_qk, ks ? 1u : 0u);
-#pragma unroll 4
-                for (int ks = kMlaQTmemDims / 16; ks < kMlaWidth / 16; ++ks) {
-                    const uint32_t sub = ks >> 2, off = (ks & 3) * 32;
-                    tc_mma_ss(tmem_s,
-                              smem_desc_sw128(q_addr + (sub - kMlaQTmemDims / 64) * kMlaQSubBytes + off, 16, 1024),
-                              smem_desc_sw128(kv_addr + sub * kMlaKvSubBytes + off, 16, 1024), idesc_qk, 1u);
-                }
-                tc_commit(&bars->s_full);
-                if (!mbar_wait(&bars->p_full, j & 1u)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t v_addr = kv_addr + 4u * half * kMlaKvSubBytes;
+        // All 32 lanes run the loop converged; one elected lane issues each instruction.
+        constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
+        constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
+        const uint32_t q_addr = smem_u32(q_tile);
+        // First 20 k-steps of S(j): the other latent half and the rope dims, both
+        // operands in shared memory. Frees the scores-only part of the stage.
+        auto qk_a = [&](unsigned int j) -> bool {
+            const unsigned int stage = j % kMlaStages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->ka_full[stage], (j / kMlaStages) & 1u))) return false;
+            tc_fence_after_sync();
+            const uint32_t k_addr = smem_u32(kv_tiles + stage * kMlaKvBytes + kMlaVPartBytes);
 #pragma unroll
-                for (int kk = 0; kk < kMlaN / 16; ++kk)
-                    tc_mma_ts(tmem_o, tmem_s + kk * 8, smem_desc_sw128(v_addr + kk * 2048, kMlaKvSubBytes, 1024),
-                              idesc_pv, (j || kk) ? 1u : 0u);
-                tc_commit(&bars->v_done[stage]);
-                tc_commit(&bars->pv_done);
+            for (int ks = 0; ks < 4 * kMlaQSmemSubs; ++ks) {
+                const uint32_t off = (ks & 3) * 32;
+                tc_mma_ss_elect(tmem_s + (j & 1u) * kMlaN,
+                                smem_desc_sw128(q_addr + (ks >> 2) * kMlaQSubBytes + off, 16, 1024),
+                                smem_desc_sw128(k_addr + (ks >> 2) * kMlaKvSubBytes + off, 16, 1024),
+                                idesc_qk, ks ? 1u : 0u);
             }
-            if (!ok) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+            tc_commit_elect(&bars->ka_done[stage]);
+            return true;
+        };
+        // Last 16 k-steps: this CTA's own latent half, query operand in tensor memory.
+        auto qk_b = [&](unsigned int j) -> bool {
+            const unsigned int stage = j % kMlaStages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->kb_full[stage], (j / kMlaStages) & 1u))) return false;
+            tc_fence_after_sync();
+            const uint32_t k_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
+#pragma unroll
+            for (int ks = 0; ks < kMlaQTmemDims / 16; ++ks)
+                tc_mma_ts_elect(tmem_s + (j & 1u) * kMlaN, tmem_q + ks * 8,
+                                smem_desc_sw128(k_addr + (ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32, 16, 1024),
+                                idesc_qk, 1u);
+            tc_commit_elect(&bars->s_full[j & 1u]);
+            return true;
+        };
+        auto pv = [&](unsigned int j) -> bool {
+            const unsigned int stage = j % kMlaStages;
+            if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[j & 1u], (j >> 1) & 1u))) return false;
+            tc_fence_after_sync();
+            const uint32_t v_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
+#pragma unroll
+            for (int kk = 0; kk < kMlaN / 16; ++kk)
+                tc_mma_ts_elect(tmem_o, tmem_s + (j & 1u) * kMlaN + kk * 8,
+                                smem_desc_sw128(v_addr + kk * 2048, kMlaKvSubBytes, 1024), idesc_pv,
+                                (j || kk) ? 1u : 0u);
+            tc_commit_elect(&bars->v_done[stage]);
+            tc_commit_elect(&bars->pv_done);
+            return true;
+        };
+        bool ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full, 0)) &&
+                  __all_sync(0xffffffffu, mbar_wait(&bars->q_tmem_full, 0));
+        ok = ok && qk_a(0) && qk_b(0);
+        // Tensor-pipe order per tile: S(j+1) first part, P(j) V(j), S(j+1) second part.
+        // The softmax of tile j runs under the first and the load of the own half of
+        // tile j+1 (which had to wait for P V of tile j-1) lands under the first two.
+        for (unsigned int j = 0; ok && j < tiles; ++j) {
+            if (j + 1 < tiles) ok = qk_a(j + 1);
+            ok = ok && pv(j);
+            if (ok && j + 1 < tiles) ok = qk_b(j + 1);
         }
+        if (!ok && lane == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
     } else {
         // ------------------------------ softmax warps -----------------------------
         const unsigned int head = threadIdx.x;
         const uint32_t lane_base = ((warp * 32u) << 16);
-        // This head's first 384 absorbed-query dims go to tensor memory: bf16 pairs
-        // are already the 32-bit words the A operand wants.
+        // This head's absorbed-query dims of the CTA's own latent half go to tensor
+        // memory: bf16 pairs are already the 32-bit words the A operand wants.
         {
             const uint4 *src = reinterpret_cast<const uint4 *>(
                 reinterpret_cast<const unsigned short *>(p.q_absorbed) +
-                ((unsigned long long)b * kMlaHeads + head) * kMlaWidth);
+                ((unsigned long long)b * kMlaHeads + head) * kMlaWidth + (unsigned long long)half * kMlaHalf);
 #pragma unroll 1
             for (int i = 0; i < kMlaQTmemDims / 64; ++i) {
                 uint32_t words[32];
@@ -278,24 +325,32 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         float m_used = -INFINITY, l = 0.0f;
         bool ok = true;
         for (unsigned int j = 0; j < tiles; ++j) {
-            if (!mbar_wait(&bars->s_full, j & 1u)) {
+            const uint32_t s_col = tmem_s + lane_base + (j & 1u) * kMlaN;
+            if (!mbar_wait(&bars->s_full[j & 1u], (j >> 1) & 1u)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
             uint32_t s[2][32];
-            tmem_ld32(tmem_s + lane_base, s[0]);
-            tmem_ld32(tmem_s + lane_base + 32, s[1]);
+            tmem_ld32(s_col, s[0]);
+            tmem_ld32(s_col + 32, s[1]);
             tmem_wait_ld();
             const unsigned int k0 = t0 + j * kMlaN;
-            float row_max = -INFINITY;
+            if (k0 + kMlaN > t1) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (k0 + 32 * i + c >= t1) s[i][c] = 0xff800000u;  // -inf
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    if (k0 + 32 * i + c >= t1) s[i][c] = 0xff800000u;
-                    row_max = fmaxf(row_max, __uint_as_float(s[i][c]));
-                }
+                for (int c = 0; c < 32; c += 2)
+                    mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[i][c]),
+                                            __uint_as_float(s[i][c + 1]));
+            const float row_max = max3(mx[0], mx[1], fmaxf(mx[2], mx[3]));
             const float m_tile = row_max * sscale;
             const bool grow = m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY;
             if (__any_sync(0xffffffffu, grow)) {
@@ -304,7 +359,11 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 l *= factor;
                 m_used = m_new;
                 if (j > 0) {
-                    // P V of the previous tile has completed: S(j) was issued after it.
+                    // O may only be touched once the previous tile's P V has landed.
+                    if (!mbar_wait(&bars->pv_done, (j - 1u) & 1u)) {
+                        ok = false;
+                        break;
+                    }
                     tc_fence_after_sync();
 #pragma unroll 1
                     for (int i = 0; i < kMlaHalf / 32; ++i) {
@@ -320,22 +379,22 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             }
             const float offset = m_used == -INFINITY ? 0.0f : -m_used;
             uint32_t packed[32];
-            float sum = 0.0f;
+            float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
                     const float p0 = exp2_approx(fmaf(__uint_as_float(s[i][c]), sscale, offset));
                     const float p1 = exp2_approx(fmaf(__uint_as_float(s[i][c + 1]), sscale, offset));
-                    const uint32_t pair = pack_bf16(p0, p1);
-                    sum += __uint_as_float(pair << 16) + __uint_as_float(pair & 0xffff0000u);
-                    packed[16 * i + (c >> 1)] = pair;
+                    sum0 += p0;
+                    sum1 += p1;
+                    packed[16 * i + (c >> 1)] = pack_bf16(p0, p1);
                 }
-            l += sum;
-            tmem_st32(tmem_s + lane_base, packed);
+            l += sum0 + sum1;
+            tmem_st32(s_col, packed);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(&bars->p_full);
+            mbar_arrive(&bars->p_full[j & 1u]);
         }
         if (ok) ok = mbar_wait(&bars->pv_done, (tiles - 1u) & 1u);
         if (!__all_sync(0xffffffffu, ok)) {

@@ -138,6 +138,14 @@ __device__ __forceinline__ float exp2_approx(float x)
     return y;
 }
 
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // (lo, hi) -> packed bf16x2 with lo in the low half, round to nearest even.
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 {

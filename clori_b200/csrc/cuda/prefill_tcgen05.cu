@@ -61,13 +61,6 @@ __device__ __forceinline__ void prefill_fail(const yvx_gqa_problem &p, PrefillBa
     bars->abort_flag = 1;
 }
 
-__device__ __forceinline__ float max3(float a, float b, float c)
-{
-    float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-
 // Number of 128-token KV tiles the rows [row0, row0 + 128) of the query can see.
 __device__ __forceinline__ unsigned int prefill_tile_count(const yvx_gqa_problem &p,
                                                            unsigned int row0, long long query_start,
