@@ -353,9 +353,64 @@ lse_combine_kernel(const float *parts, unsigned int part_count, unsigned int hd,
                    unsigned long long item_stride, unsigned long long part_stride, void *output,
                    int output_dtype, int *status)
 {
+    pdl_wait();
     const unsigned long long item = blockIdx.x;
     combine_parts(parts + item * item_stride, part_count, (unsigned int)part_stride, hd, output,
                   output_dtype, item * hd, nullptr, status);
+}
+
+// One WARP per item, for many items with few parts each (latent decode: 8192
+// items x 9 parts): no shared memory, no block barrier, parts folded in index
+// order, four loaded at a time.
+__global__ void __launch_bounds__(kCombineWarps * 32)
+lse_combine_warp_kernel(const float *__restrict__ parts, unsigned int items, unsigned int part_count,
+                        unsigned int hd, unsigned long long item_stride,
+                        unsigned long long part_stride, void *output, int output_dtype, int *status)
+{
+    pdl_wait();
+    const unsigned int lane = threadIdx.x & 31u;
+    const unsigned long long item = (unsigned long long)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const float *base = parts + item * item_stride;
+    float acc[8], run_max = -INFINITY, run_sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (unsigned int j0 = 0; j0 < part_count; j0 += kCombineBatch) {
+        float mj[kCombineBatch], lj[kCombineBatch], oj[kCombineBatch][8];
+#pragma unroll
+        for (int u = 0; u < kCombineBatch; ++u) {
+            const bool live = j0 + u < part_count;
+            const float *part = base + (unsigned long long)(live ? j0 + u : j0) * part_stride;
+            mj[u] = live ? part[hd] : -INFINITY;
+            lj[u] = part[hd + 1];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const unsigned int d = lane + 32u * i;
+                oj[u][i] = d < hd ? part[d] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kCombineBatch; ++u) {
+            if (mj[u] == -INFINITY) continue;
+            const float new_max = fmaxf(run_max, mj[u]);
+            const float keep = expf(run_max - new_max);
+            const float weight = lj[u] * expf(mj[u] - new_max);
+            run_sum = fmaf(run_sum, keep, weight);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(acc[i], keep, oj[u][i] * weight);
+            run_max = new_max;
+        }
+    }
+    bool finite = true;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const unsigned int d = lane + 32u * i;
+        if (d >= hd) continue;
+        const float value = acc[i] / run_sum;
+        finite = finite && isfinite(value);
+        store_output(output, output_dtype, item * hd + d, value);
+    }
+    if (!finite) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
 }
 
 template <typename QT, typename KT, int SLOTS>
@@ -416,16 +471,50 @@ int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream)
 
 }  // namespace yvx
 
+namespace yvx {
+
+// Launches the gathered-partials combine as a programmatic dependent of the
+// kernel before it in the stream (the kernels wait for that kernel's results
+// themselves). Many items with few parts each go one warp per item.
+static int lse_combine_launch(const float *parts, unsigned int items, unsigned int part_count,
+                              unsigned int hd, unsigned long long item_stride,
+                              unsigned long long part_stride, void *output, int output_dtype,
+                              int *status, cudaStream_t stream)
+{
+    cudaLaunchConfig_t config = {};
+    config.blockDim = dim3(kCombineWarps * 32, 1, 1);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaError_t launched;
+    if (items >= 1024u && part_count <= 32u && hd <= 256u) {
+        config.gridDim = dim3((items + kCombineWarps - 1u) / kCombineWarps, 1, 1);
+        launched = cudaLaunchKernelEx(&config, lse_combine_warp_kernel, parts, items, part_count, hd,
+                                      item_stride, part_stride, output, output_dtype, status);
+    } else {
+        config.gridDim = dim3(items, 1, 1);
+        launched = cudaLaunchKernelEx(&config, lse_combine_kernel, parts, part_count, hd, item_stride,
+                                      part_stride, output, output_dtype, status);
+    }
+    if (launched != cudaSuccess) return yvx_cuda_check(launched, "lse_combine_kernel");
+    return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
+}
+
+}  // namespace yvx
+
 extern "C" int yvx_cuda_lse_combine(const float *parts, unsigned int items,
                                     unsigned int part_count, unsigned int head_dim,
                                     void *output, int output_dtype, int *status, void *stream)
 {
-    if (!parts || !items || !part_count || !head_dim || !output || !status)
+    if (!parts || !items || !part_count || !head_dim || head_dim > 256u || !output || !status)
         return YVEX_ERR_INVALID_ARG;
-    yvx::lse_combine_kernel<<<items, yvx::kCombineWarps * 32, 0, (cudaStream_t)stream>>>(
-        parts, part_count, head_dim, (unsigned long long)part_count * (head_dim + 2ull), head_dim + 2ull,
-        output, output_dtype, status);
-    return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
+    return yvx::lse_combine_launch(parts, items, part_count, head_dim,
+                                   (unsigned long long)part_count * (head_dim + 2ull), head_dim + 2ull,
+                                   output, output_dtype, status, (cudaStream_t)stream);
 }
 
 extern "C" int yvx_cuda_lse_combine_strided(const float *parts, unsigned int items,
@@ -434,10 +523,9 @@ extern "C" int yvx_cuda_lse_combine_strided(const float *parts, unsigned int ite
                                             unsigned long long part_stride, void *output,
                                             int output_dtype, int *status, void *stream)
 {
-    if (!parts || !items || !part_count || !head_dim || !output || !status ||
+    if (!parts || !items || !part_count || !head_dim || head_dim > 256u || !output || !status ||
         part_stride < head_dim + 2ull || part_stride > 0xffffffffull)
         return YVEX_ERR_INVALID_ARG;
-    yvx::lse_combine_kernel<<<items, yvx::kCombineWarps * 32, 0, (cudaStream_t)stream>>>(
-        parts, part_count, head_dim, item_stride, part_stride, output, output_dtype, status);
-    return yvx_cuda_check(cudaGetLastError(), "lse_combine_kernel");
+    return yvx::lse_combine_launch(parts, items, part_count, head_dim, item_stride, part_stride, output,
+                                   output_dtype, status, (cudaStream_t)stream);
 }

@@ -304,16 +304,19 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             const uint4 *src = reinterpret_cast<const uint4 *>(
                 reinterpret_cast<const unsigned short *>(p.q_absorbed) +
                 ((unsigned long long)b * kMlaHeads + head) * kMlaWidth + (unsigned long long)half * kMlaHalf);
-#pragma unroll 1
+            // All 32 loads are issued before the first store so they share one round trip.
+            uint4 v[kMlaQTmemDims / 8];
+#pragma unroll
+            for (int c = 0; c < kMlaQTmemDims / 8; ++c) v[c] = src[c];
+#pragma unroll
             for (int i = 0; i < kMlaQTmemDims / 64; ++i) {
                 uint32_t words[32];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint4 v = src[8 * i + c];
-                    words[4 * c] = v.x;
-                    words[4 * c + 1] = v.y;
-                    words[4 * c + 2] = v.z;
-                    words[4 * c + 3] = v.w;
+                    words[4 * c] = v[8 * i + c].x;
+                    words[4 * c + 1] = v[8 * i + c].y;
+                    words[4 * c + 2] = v[8 * i + c].z;
+                    words[4 * c + 3] = v[8 * i + c].w;
                 }
                 tmem_st32(tmem_q + lane_base + 32 * i, words);
             }
@@ -397,14 +400,19 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             mbar_arrive(&bars->p_full[j & 1u]);
         }
         if (ok) ok = mbar_wait(&bars->pv_done, (tiles - 1u) & 1u);
-        if (!__all_sync(0xffffffffu, ok)) {
-            atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
-        } else {
+        // The tile loop is over: let the combine kernel's launch overlap the epilogue.
+        pdl_launch_dependents();
+        // A wait that gave up is recorded; the rows are still written out so that
+        // every softmax thread reaches the named barrier below exactly once.
+        if (!__all_sync(0xffffffffu, ok)) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+        {
             tc_fence_after_sync();
             const float inverse = l > 0.0f ? 1.0f / l : 0.0f;
-            float *part = p.partials +
-                          ((((unsigned long long)b * kMlaHeads + head) * 2ull + half) * p.max_splits + split) *
-                              part_stride;
+            // Every tile has been consumed, so the tile ring is free: the normalised
+            // rows go through it, and each warp then writes whole partial rows with
+            // coalesced 8-byte stores (a partial row is 8-byte aligned only).
+            float *staged = reinterpret_cast<float *>(kv_tiles);
+            float *mine = staged + head * (unsigned)part_stride;
 #pragma unroll 1
             for (int i = 0; i < kMlaHalf / 32; ++i) {
                 uint32_t o[32];
@@ -412,11 +420,19 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 tmem_wait_ld();
 #pragma unroll
                 for (int c = 0; c < 32; c += 2)
-                    *reinterpret_cast<float2 *>(part + 32 * i + c) =
+                    *reinterpret_cast<float2 *>(mine + 32 * i + c) =
                         make_float2(__uint_as_float(o[c]) * inverse, __uint_as_float(o[c + 1]) * inverse);
             }
-            part[kMlaHalf] = m_used == -INFINITY ? -INFINITY : m_used * 0.6931471805599453f;
-            part[kMlaHalf + 1] = l;
+            *reinterpret_cast<float2 *>(mine + kMlaHalf) =
+                make_float2(m_used == -INFINITY ? -INFINITY : m_used * 0.6931471805599453f, l);
+            named_barrier(1, kMlaHeads);
+            for (unsigned int r = warp; r < (unsigned)kMlaHeads; r += 4u) {
+                float2 *dst = reinterpret_cast<float2 *>(
+                    p.partials +
+                    ((((unsigned long long)b * kMlaHeads + r) * 2ull + half) * p.max_splits + split) * part_stride);
+                const float2 *src = reinterpret_cast<const float2 *>(staged + r * (unsigned)part_stride);
+                for (unsigned int k = lane; k < (unsigned)part_stride / 2u; k += 32u) dst[k] = src[k];
+            }
         }
     }
     tc_fence_before_sync();
@@ -475,31 +491,30 @@ static bool mla_encode(CUtensorMap *map, const void *base, unsigned long long wi
 extern "C" {
 
 // One CTA per SM is resident (shared memory), so a wave is sm_count work items:
-// sessions x 2 halves x splits. The chunk is the largest multiple of 64 tokens,
-// at most 8192, that makes at least one wave and fills the last one to 90 %.
+// sessions x 2 halves x splits. Every work item pays a fixed cost (query staging,
+// first tile latency, writing its partial rows) worth about ten 64-token tiles,
+// so the chunk minimises waves x (tiles per chunk + 10): a single wave that
+// leaves a few SMs idle beats four full waves of short chunks.
 void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
 {
     if (!p) return;
     const unsigned long long wave = (unsigned long long)(sm_count > 0 ? sm_count : 148);
     const unsigned long long lanes = 2ull * p->sessions;
-    unsigned int best = 0u;
-    double best_fill = -1.0;
-    for (unsigned int chunk = 8192u; chunk >= 64u; chunk -= 64u) {
+    const unsigned int longest = ((p->kv_tokens_max + 63u) / 64u) * 64u;
+    const unsigned long long fixed_tiles = 10ull;
+    unsigned int best = 64u;
+    unsigned long long best_cost = ~0ull;
+    for (unsigned int chunk = longest ? longest : 64u; chunk >= 64u; chunk -= 64u) {
         const unsigned long long splits = ((unsigned long long)p->kv_tokens_max + chunk - 1ull) / chunk;
-        const unsigned long long items = lanes * splits;
-        if (items < wave) continue;
+        const unsigned long long items = lanes * (splits ? splits : 1ull);
         const unsigned long long waves = (items + wave - 1ull) / wave;
-        const double fill = (double)items / (double)(waves * wave);
-        if (fill >= 0.9) {
-            best = chunk;
-            break;
-        }
-        if (fill > best_fill) {
-            best_fill = fill;
+        const unsigned long long cost = waves * (chunk / 64ull + fixed_tiles);
+        if (cost < best_cost) {  // ties keep the larger chunk (fewer partial rows)
+            best_cost = cost;
             best = chunk;
         }
     }
-    p->chunk_tokens = best ? best : 64u;
+    p->chunk_tokens = best;
     p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
     if (!p->max_splits) p->max_splits = 1u;
 }
