@@ -580,6 +580,65 @@ def bench_mla(lib, backend, abi, hbm_peak, repeats, sessions=32, context=16384):
     return result, (host, o_host)
 
 
+def bench_kv_append(lib, backend, abi, hbm_peak, repeats, sessions=2, tokens=8192):
+    """KV append + rotary for the new rows of a step (prefill-sized: sessions x tokens rows,
+    40q/8kv heads, hd 128, full rotary width, bf16-staged arithmetic): Q rotated in place,
+    K rotated and V copied into bf16 pools behind an identity block table."""
+    hq, hkv, hd, block = 40, 8, 128, 64
+    rows = sessions * tokens
+    sizes = {"q": rows * hq * hd, "k": rows * hkv * hd, "v": rows * hkv * hd, "cos": rows * hd, "sin": rows * hd}
+    bufs = {k: _alloc(lib, n * 4) for k, n in sizes.items()}
+    for i, (k, n) in enumerate(sizes.items()):
+        lib.yvx_cuda_fill_normal(bufs[k], abi.DTYPE_F32, n, 601 + i, 0.5, backend.stream)
+    blocks = (tokens + block - 1) // block
+    kpool, vpool = _alloc(lib, rows * hkv * hd * 2), _alloc(lib, rows * hkv * hd * 2)
+    table_host = np.arange(sessions * blocks, dtype=np.int32).reshape(sessions, blocks)
+    table, status = _alloc(lib, table_host.nbytes), _alloc(lib, 4)
+    lib.yvx_cuda_upload_async(table, table_host.ctypes.data, table_host.nbytes, backend.stream)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    a = abi.KvAppendArgs()
+    a.sessions, a.tokens, a.query_heads, a.kv_heads, a.head_dim, a.rotary_dim = sessions, tokens, hq, hkv, hd, hd
+    a.staged_bf16 = 1
+    a.query, a.key, a.value, a.cosines, a.sines = bufs["q"], bufs["k"], bufs["v"], bufs["cos"], bufs["sin"]
+    a.kv_tokens_uniform = 0
+    a.key_pool, a.value_pool, a.block_table = kpool, vpool, table
+    a.block_tokens, a.block_table_stride, a.pool_blocks = block, blocks, sessions * blocks
+    a.pool_token_stride, a.pool_head_stride, a.pool_block_stride = hkv * hd, hd, block * hkv * hd
+    a.status = status
+
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    for _ in range(3):
+        assert lib.yvx_cuda_kv_append_rotary(C.byref(a), backend.stream) == 0
+    first, last = event(), event()
+    lib.yvx_cuda_event_record(first, backend.stream)
+    for _ in range(repeats):
+        assert lib.yvx_cuda_kv_append_rotary(C.byref(a), backend.stream) == 0
+    lib.yvx_cuda_event_record(last, backend.stream)
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    ms = C.c_float()
+    lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+    step = ms.value / repeats
+    # per row: Q read + written (F32), K and V read (F32), tables read, K and V written (bf16)
+    nbytes = rows * (2 * hq * hd * 4 + 2 * hkv * hd * 4 + 2 * hd * 4 + 2 * hkv * hd * 2)
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    result = {"workload": f"KV append + rotary, {sessions} x {tokens} new rows, 40q/8kv heads, hd128, "
+                          "F32 in, bf16 pools behind a block table",
+              "kernel": "kv_append_rotary_kernel", "launches_per_step": 1, "kernel_ms": step,
+              "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (step * 1e-3) / 1e9,
+              "frac_of_measured_hbm": nbytes / (step * 1e-3) / 1e9 / hbm_peak,
+              "rows_per_s": rows / (step * 1e-3), "status_word": int(st[0]),
+              "l2": "%.0f MB per launch exceed L2" % (nbytes / 1e6),
+              "replaces": "2 rotary launches + 2 device copies per new token + a position upload"}
+    for ptr in list(bufs.values()) + [kpool, vpool, table, status]:
+        lib.yvx_cuda_free(ptr)
+    return result, None
+
+
 def check_mla(sample):
     from oracle.binding import Oracle
     host, o = sample
@@ -788,7 +847,7 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla"],
+                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -836,6 +895,9 @@ def main():
         if args.workload == "mla":
             result, _ = bench_mla(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                   sessions=min(args.sessions, 32))
+        elif args.workload == "kv_append":
+            result, _ = bench_kv_append(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
+                                        tokens=args.tokens)
         elif args.workload == "prefill":
             result, _ = bench_prefill(abi.load(), backend, abi, max(args.steps, 3), tokens=args.tokens)
         else:
@@ -905,6 +967,7 @@ def main():
         others["verify_q8_config4_1gpu"], other_samples["q8"] = bench_verify_q8(lib, b, w.abi, hbm_peak, 20)
         others["prefill_config3"], other_samples["prefill"] = bench_prefill(lib, b, w.abi, 10)
         others["latent_decode_config5"], other_samples["mla"] = bench_mla(lib, b, w.abi, hbm_peak, 10)
+        others["kv_append_rotary"], _ = bench_kv_append(lib, b, w.abi, hbm_peak, 10)
 
     if rank != 0:
         if dist is not None:

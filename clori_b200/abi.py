@@ -155,6 +155,25 @@ class LatentReduceArgs(C.Structure):
     ]
 
 
+class KvAppendArgs(C.Structure):
+    """yvx_kv_append_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [
+        ("sessions", C.c_uint), ("tokens", C.c_uint),
+        ("query_heads", C.c_uint), ("kv_heads", C.c_uint), ("head_dim", C.c_uint), ("rotary_dim", C.c_uint),
+        ("staged_bf16", C.c_int),
+        ("query", C.c_void_p), ("key", C.c_void_p), ("value", C.c_void_p),
+        ("cosines", C.c_void_p), ("sines", C.c_void_p),
+        ("kv_tokens", C.c_void_p), ("kv_tokens_uniform", C.c_uint),
+        ("state_values", C.c_void_p), ("state_session_stride", u64), ("state_row_stride", u64),
+        ("state_positions", C.c_void_p), ("state_position_stride", u64),
+        ("token_position", C.c_void_p),
+        ("key_pool", C.c_void_p), ("value_pool", C.c_void_p), ("block_table", C.c_void_p),
+        ("block_tokens", C.c_uint), ("block_table_stride", C.c_uint), ("pool_blocks", C.c_uint),
+        ("pool_token_stride", u64), ("pool_head_stride", u64), ("pool_block_stride", u64),
+        ("status", C.c_void_p),
+    ]
+
+
 class MlaProblem(C.Structure):
     """yvx_mla_problem (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [
@@ -198,7 +217,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
-    "yvx_cuda_latent_reduce", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
+    "yvx_cuda_latent_reduce", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
     "yvx_cuda_mla_decode",
 ]
 
@@ -280,6 +299,7 @@ def load():
     lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
     lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
     lib.yvx_cuda_latent_reduce.argtypes = [P(LatentReduceArgs), vp]
+    lib.yvx_cuda_kv_append_rotary.argtypes = [P(KvAppendArgs), vp]
     lib.yvx_cuda_mla_plan.restype = None
     lib.yvx_cuda_mla_plan.argtypes = [P(MlaProblem), C.c_int]
     lib.yvx_cuda_mla_absorbed_bytes.restype = u64

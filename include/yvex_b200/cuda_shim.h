@@ -192,6 +192,46 @@ typedef struct yvx_latent_reduce_args {
 } yvx_latent_reduce_args;
 int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *args, void *stream);
 
+/* ---- KV append with rotary embedding (one launch per step) ---------------------------
+ * Replaces, for the new rows of a step, the two rotate-half launches on Q and K
+ * (yvex_cuda_transformer_rotary_half / _rotary_half_f32, src/backend/cuda/transformer.c:
+ * 413-469; kernels src/backend/cuda/transformer_kernels.cu:78-134; called from
+ * src/runtime/decoder.c:1112-1131) and the per-token device copies of K and V into the
+ * state bank with the position upload (stateful_copy_projection,
+ * src/runtime/stateful_attention.c:183-243).
+ * Q is rotated in place; K is rotated on its way into the history; V is copied.
+ * cosines / sines are the explicit tables the reference passes, [session][token][rotary_dim];
+ * pair p of a head is (p, p + rotary_dim/2), dims >= rotary_dim are left alone.
+ * staged_bf16 != 0: products and sum rounded to bf16 (yvex_rotary_half_f32 kernel, the
+ * decoder's variant); 0: plain single precision, no fused multiply-add.
+ * Row of session b's token t: kv_tokens[b] + t. Destination A (state_values != NULL): F32
+ * rows [row][K heads | V heads] with state_row_stride floats between rows, and
+ * state_positions[b][row] = token_position[b] + t (NULL: kv_tokens[b] + t).
+ * Destination B (key_pool != NULL): bf16 pools behind a block table, strides in
+ * elements, values rounded to nearest even. Either or both may be given.
+ * status: 2 when a block-table entry lies outside the pool (the row is skipped). */
+typedef struct yvx_kv_append_args {
+    unsigned int sessions, tokens;            /* new rows per session */
+    unsigned int query_heads, kv_heads, head_dim, rotary_dim;
+    int staged_bf16;
+    float *query;                             /* [session][token][query_heads*head_dim] or NULL */
+    const float *key, *value;                 /* [session][token][kv_heads*head_dim] */
+    const float *cosines, *sines;             /* [session][token][rotary_dim] */
+    const int *kv_tokens;                     /* [session] rows already present; NULL: uniform */
+    unsigned int kv_tokens_uniform;
+    float *state_values;
+    unsigned long long state_session_stride, state_row_stride;
+    unsigned long long *state_positions;
+    unsigned long long state_position_stride;
+    const unsigned long long *token_position;
+    void *key_pool, *value_pool;
+    const int *block_table;
+    unsigned int block_tokens, block_table_stride, pool_blocks;
+    unsigned long long pool_token_stride, pool_head_stride, pool_block_stride;
+    int *status;
+} yvx_kv_append_args;
+int yvx_cuda_kv_append_rotary(const yvx_kv_append_args *args, void *stream);
+
 /* ---- latent-compressed (MLA-style) decode -----------------------------------------
  * One query token per session; every query head attends over ONE shared row per
  * position: score = scale * (q_lat[h] . latent[t] + q_rope[h] . rope_key[t]),

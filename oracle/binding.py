@@ -139,6 +139,26 @@ class Oracle(_Gqa):
             _u16p, _u16p, _u16p, _u16p, _u16p, _f32p, _u64, _u64, _u64, _u64, _u64,
             C.c_float, C.c_void_p]
 
+    def rotary_half(self, values, cosines, sines, heads, head_dim, rotary_dim, staged):
+        """values [tokens, heads*head_dim] float32; returns the rotated copy."""
+        out = np.ascontiguousarray(values, np.float32).copy()
+        cos = np.ascontiguousarray(cosines, np.float32)
+        sin = np.ascontiguousarray(sines, np.float32)
+        self.lib.yvx_oracle_rotary_half.argtypes = [_f32p, _f32p, _f32p, _u64, _u64, _u64, _u64, C.c_int]
+        ok = self.lib.yvx_oracle_rotary_half(out.reshape(-1), cos.reshape(-1), sin.reshape(-1), out.shape[0],
+                                             heads, head_dim, rotary_dim, int(staged))
+        assert ok == 1
+        return out
+
+    def rope_tables(self, token_start, tokens, width, theta):
+        cos = np.empty((tokens, width), np.float32)
+        sin = np.empty((tokens, width), np.float32)
+        self.lib.yvx_oracle_rope_tables.argtypes = [_u64, _u64, _u64, C.c_double, _f32p, _f32p]
+        ok = self.lib.yvx_oracle_rope_tables(token_start, tokens, width, float(theta),
+                                             cos.reshape(-1), sin.reshape(-1))
+        assert ok == 1
+        return cos, sin
+
     def exp(self, x):
         return float(self.lib.yvx_oracle_exp(float(x)))
 

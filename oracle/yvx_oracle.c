@@ -776,3 +776,65 @@ int yvx_oracle_latent_reduce_full(const yvx_oracle_latent_args *a, float *out)
     }
     return 1;
 }
+
+/* Rotate-half applied in place to packed [token][head][head_dim] vectors with
+ * explicit tables [token][rotary_dim]; dims >= rotary_dim are left alone.
+ * staged != 0: every product and the sum are rounded to bf16, as
+ * yvex_rotary_half_f32 does (src/backend/cuda/transformer_kernels.cu:78-108);
+ * staged == 0: plain single-precision multiply and add without contraction,
+ * yvex_rotary_half_plain_f32 (:110-134). Known answers:
+ * tests/unit/cuda/quant_qtype.c:1989-2062 and :3057-3104. */
+int yvx_oracle_rotary_half(float *values, const float *cosines, const float *sines,
+                           unsigned long long tokens, unsigned long long heads,
+                           unsigned long long head_dim, unsigned long long rotary_dim, int staged)
+{
+    const unsigned long long half = rotary_dim / 2ull;
+    unsigned long long token, head, lane;
+    if (!values || !cosines || !sines || !tokens || !heads || !half || (rotary_dim & 1ull) ||
+        rotary_dim > head_dim)
+        return 0;
+    for (token = 0; token < tokens; ++token)
+        for (head = 0; head < heads; ++head) {
+            float *v = values + (token * heads + head) * head_dim;
+            for (lane = 0; lane < half; ++lane) {
+                const float cosine = cosines[token * rotary_dim + lane];
+                const float sine = sines[token * rotary_dim + lane];
+                const float first = v[lane], second = v[half + lane];
+                if (staged) {
+                    volatile float a = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(first * cosine));
+                    volatile float b = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(second * sine));
+                    volatile float c = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(second * cosine));
+                    volatile float d = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(first * sine));
+                    v[lane] = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(a - b));
+                    v[half + lane] = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(c + d));
+                } else {
+                    volatile float a = first * cosine, b = second * sine;
+                    volatile float c = second * cosine, d = first * sine;
+                    v[lane] = a - b;
+                    v[half + lane] = c + d;
+                }
+            }
+        }
+    return 1;
+}
+
+/* Rotary tables of the decoder (src/runtime/decoder.c:1060-1095): for position
+ * p and coordinate c, pair = c mod (width/2), angle = p * theta^(-2 pair / width)
+ * in double; cosine and sine narrowed to float and rounded to bf16. */
+int yvx_oracle_rope_tables(unsigned long long token_start, unsigned long long tokens,
+                           unsigned long long width, double theta, float *cosines, float *sines)
+{
+    unsigned long long token, coordinate;
+    if (!width || (width & 1ull) || !cosines || !sines) return 0;
+    for (token = 0; token < tokens; ++token)
+        for (coordinate = 0; coordinate < width; ++coordinate) {
+            const unsigned long long pair = coordinate % (width / 2ull);
+            const double frequency = pow(theta, -(double)(2ull * pair) / (double)width);
+            const double angle = (double)(token_start + token) * frequency;
+            cosines[token * width + coordinate] =
+                yvx_oracle_bf16_decode(yvx_oracle_bf16_encode((float)cos(angle)));
+            sines[token * width + coordinate] =
+                yvx_oracle_bf16_decode(yvx_oracle_bf16_encode((float)sin(angle)));
+        }
+    return 1;
+}

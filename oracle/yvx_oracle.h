@@ -135,6 +135,13 @@ int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
                           unsigned long long context, float scale,
                           float *absorbed_query_out);
 
+/* Rotate-half with explicit tables (bf16-staged or plain) and the decoder's tables. */
+int yvx_oracle_rotary_half(float *values, const float *cosines, const float *sines,
+                           unsigned long long tokens, unsigned long long heads,
+                           unsigned long long head_dim, unsigned long long rotary_dim, int staged);
+int yvx_oracle_rope_tables(unsigned long long token_start, unsigned long long tokens,
+                           unsigned long long width, double theta, float *cosines, float *sines);
+
 #ifdef __cplusplus
 }
 #endif

@@ -229,3 +229,30 @@ def test_full_latent_reduce_restatement_cross_checks(oracle):
     windowed = oracle.latent_reduce_full(a, tokens, heads, hd)
     visible = oracle.latent_reduce(q[1:], rows[rows_n - 4:], sinks, query_start=3, heads=heads, head_dim=hd)
     assert np.array_equal(windowed[1:], visible)
+
+
+def test_rotary_half_known_answers_of_the_reference(oracle):
+    # bf16-staged products: tests/unit/cuda/quant_qtype.c:1989-2062
+    rb = lambda x: float(oracle.bf16_round(np.array([x], np.float32))[1][0])
+    values = np.array([[-1.34375, -2.0625, 3.0, 4.0]], np.float32)
+    cos = np.full((1, 2), 0.63671875, np.float32)
+    sin = np.full((1, 2), 0.546875, np.float32)
+    got = oracle.rotary_half(values, cos, sin, 1, 4, 2, staged=True)
+    first = rb(rb(np.float32(-1.34375) * np.float32(0.63671875)) - rb(np.float32(-2.0625) * np.float32(0.546875)))
+    second = rb(rb(np.float32(-2.0625) * np.float32(0.63671875)) + rb(np.float32(-1.34375) * np.float32(0.546875)))
+    assert got.tolist() == [[first, second, 3.0, 4.0]]
+    # plain single precision: tests/unit/cuda/quant_qtype.c:3057-3104
+    values = np.array([[1.0, 2.0, 7.0, 8.0]], np.float32)
+    got = oracle.rotary_half(values, np.full((1, 2), 0.75, np.float32), np.full((1, 2), 0.5, np.float32),
+                             2, 2, 2, staged=False)
+    assert got.tolist() == [[-0.25, 2.0, 1.25, 9.5]]
+
+
+def test_rope_tables_follow_the_decoder_convention(oracle):
+    # src/runtime/decoder.c:1080-1094: pair = coordinate mod width/2, bf16-rounded cos/sin
+    cos, sin = oracle.rope_tables(3, 2, 8, 1.0e6)
+    assert cos.shape == (2, 8) and np.array_equal(cos[:, :4], cos[:, 4:]) and np.array_equal(sin[:, :4], sin[:, 4:])
+    angle = 4.0 * (1.0e6 ** (-2.0 * 1 / 8.0))
+    assert cos[1, 1] == oracle.bf16_round(np.array([np.cos(angle)], np.float32))[1][0]
+    assert sin[1, 5] == oracle.bf16_round(np.array([np.sin(angle)], np.float32))[1][0]
+    assert cos[0, 0] == oracle.bf16_round(np.array([np.cos(3.0)], np.float32))[1][0]
