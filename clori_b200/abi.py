@@ -136,7 +136,7 @@ class GqaProblem(C.Structure):
         ("query_start_from_end", C.c_uint), ("kv_position_base", C.c_uint),
         ("chunk_tokens", C.c_uint), ("max_splits", C.c_uint),
         ("partials", C.c_void_p), ("partial_output", C.c_void_p), ("status", C.c_void_p),
-        ("force_general", C.c_int),
+        ("force_general", C.c_int), ("query_head_stride", u64),
     ]
 
 

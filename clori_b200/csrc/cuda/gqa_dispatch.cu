@@ -74,9 +74,12 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     // is not theirs; the general kernel takes everything else.
     // 1 = attention launched (a combine follows when the KV was split), 2 = launched and
     // final, 0 = not this kernel's shape, negative = error.
-    int rc = yvx::gqa_decode_q8_launch(*p, s);
+    // Query heads that are not packed at head_dim are the general kernel's alone.
+    const bool packed_heads = !p->query_head_stride || p->query_head_stride == p->head_dim;
+    int rc = packed_heads ? yvx::gqa_decode_q8_launch(*p, s)
+                          : (p->kv_dtype == YVEX_DTYPE_Q8_0 ? YVEX_ERR_UNSUPPORTED : 0);
     const unsigned int vectors = p->query_rows * (p->query_heads / p->kv_heads);
-    if (rc == 0 && !p->force_general)
+    if (rc == 0 && !p->force_general && packed_heads)
         rc = vectors <= 64u ? yvx::gqa_decode_mma_launch(*p, s) : yvx::prefill_tcgen05_launch(*p, s);
     const bool final_output = rc == 2;
     if (rc == 0) rc = yvx::gqa_generic_main_launch(*p, s);

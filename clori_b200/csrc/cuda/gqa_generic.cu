@@ -116,7 +116,7 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
         const QT *qp = reinterpret_cast<const QT *>(p.query) +
                        (unsigned long long)b * p.query_session_stride +
                        (unsigned long long)row * p.query_row_stride +
-                       (unsigned long long)qhead * hd;
+                       (unsigned long long)qhead * (p.query_head_stride ? p.query_head_stride : hd);
 #pragma unroll
         for (int sl = 0; sl < SLOTS; ++sl) {
             const unsigned int d = lane + 32u * sl;

@@ -98,6 +98,9 @@ typedef struct yvx_gqa_problem {
                                         3 a bounded device-side wait gave up */
     int force_general;               /* 1: take the general kernel even when a specialised
                                         one admits the shape (cross-checks in tests) */
+    unsigned long long query_head_stride; /* elements between query heads of a row; 0 = head_dim.
+                                        Anything else (interleaved [head][Q|K|V][dim] rows,
+                                        src/graph/numeric.c:1771-1826) takes the general kernel */
 } yvx_gqa_problem;
 
 /* Scratch bytes `partials` must hold for a problem (0 when one split suffices). */

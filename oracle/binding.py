@@ -150,6 +150,16 @@ class Oracle(_Gqa):
         assert ok == 1
         return out
 
+    def full_attention_f32(self, qkv, heads, head_width):
+        """qkv [rows, heads*3*head_width] float32 -> [rows, heads*head_width]."""
+        qkv = np.ascontiguousarray(qkv, np.float32)
+        rows = qkv.shape[0]
+        out = np.empty((rows, heads * head_width), np.float32)
+        scratch = np.empty(rows, np.float32)
+        self.lib.yvx_oracle_full_attention_f32.argtypes = [_f32p, _u64, _u64, _u64, _f32p, _f32p]
+        ok = self.lib.yvx_oracle_full_attention_f32(qkv.reshape(-1), rows, heads, head_width, out.reshape(-1), scratch)
+        return out if ok == 1 else None
+
     def rope_tables(self, token_start, tokens, width, theta):
         cos = np.empty((tokens, width), np.float32)
         sin = np.empty((tokens, width), np.float32)

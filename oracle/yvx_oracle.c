@@ -838,3 +838,44 @@ int yvx_oracle_rope_tables(unsigned long long token_start, unsigned long long to
         }
     return 1;
 }
+
+/* Full (non-causal) attention over interleaved [row][head][Q | K | V][width] rows in
+ * single precision, three passes (scores and maximum, exponentials and sum, weighted
+ * values), restating yvex_graph_full_attention_f32 (src/graph/numeric.c:1771-1826).
+ * Known answer: tests/unit/minimax_h3.c:641-681. scratch holds `rows` floats. */
+int yvx_oracle_full_attention_f32(const float *qkv, unsigned long long rows,
+                                  unsigned long long heads, unsigned long long head_width,
+                                  float *output, float *scratch)
+{
+    const unsigned long long hidden = heads * head_width, qkv_width = hidden * 3ull;
+    const float scale = 1.0f / sqrtf((float)head_width);
+    unsigned long long query, head, key, coordinate;
+    if (!qkv || !rows || !heads || !head_width || !output || !scratch) return 0;
+    memset(output, 0, (size_t)(rows * hidden) * sizeof(*output));
+    for (query = 0; query < rows; ++query)
+        for (head = 0; head < heads; ++head) {
+            const float *q = qkv + query * qkv_width + head * head_width * 3ull;
+            float maximum = -INFINITY, sum = 0.0f;
+            for (key = 0; key < rows; ++key) {
+                const float *k = qkv + key * qkv_width + head * head_width * 3ull + head_width;
+                float score = 0.0f;
+                for (coordinate = 0; coordinate < head_width; ++coordinate)
+                    score += q[coordinate] * k[coordinate];
+                scratch[key] = score * scale;
+                if (scratch[key] > maximum) maximum = scratch[key];
+            }
+            for (key = 0; key < rows; ++key) {
+                scratch[key] = expf(scratch[key] - maximum);
+                sum += scratch[key];
+            }
+            if (!isfinite(sum) || sum <= 0.0f) return 0;
+            for (key = 0; key < rows; ++key) {
+                const float *value = qkv + key * qkv_width + head * head_width * 3ull + head_width * 2ull;
+                const float probability = scratch[key] / sum;
+                float *destination = output + query * hidden + head * head_width;
+                for (coordinate = 0; coordinate < head_width; ++coordinate)
+                    destination[coordinate] += probability * value[coordinate];
+            }
+        }
+    return 1;
+}

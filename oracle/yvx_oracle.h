@@ -142,6 +142,11 @@ int yvx_oracle_rotary_half(float *values, const float *cosines, const float *sin
 int yvx_oracle_rope_tables(unsigned long long token_start, unsigned long long tokens,
                            unsigned long long width, double theta, float *cosines, float *sines);
 
+/* Full attention over interleaved [row][head][Q|K|V][width] rows, single precision. */
+int yvx_oracle_full_attention_f32(const float *qkv, unsigned long long rows,
+                                  unsigned long long heads, unsigned long long head_width,
+                                  float *output, float *scratch);
+
 #ifdef __cplusplus
 }
 #endif

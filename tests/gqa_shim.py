@@ -13,7 +13,8 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
                 k_token_stride, v_token_stride, k_head_stride, v_head_stride,
                 k_outer_stride, v_outer_stride, v_offset_elems=0, kv_max=None,
                 force_general=False, chunk_tokens=None, query_start=None, position_base=0,
-                partial_output=False, entry="yvx_cuda_gqa_attention", own_scratch=True):
+                partial_output=False, entry="yvx_cuda_gqa_attention", own_scratch=True,
+                k_offset_elems=0, q_row_stride=None, q_head_stride=0):
     """q: device Tensor [sessions, rows, hq*hd]; k, v: device Tensors holding the
     cache in any layout described by the strides (elements). Returns the output
     array (or the (o, m, l) partials) and the launch count."""
@@ -24,9 +25,10 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
     p.causal, p.scale = int(causal), 1.0 / np.sqrt(hd)
     p.query_dtype = p.kv_dtype = dtype
     p.output_dtype = out_dtype
-    p.query, p.query_row_stride, p.query_session_stride = q.data_ptr, hq * hd, rows * hq * hd
+    p.query, p.query_row_stride = q.data_ptr, q_row_stride or hq * hd
+    p.query_session_stride, p.query_head_stride = rows * p.query_row_stride, q_head_stride
     esize = abi.DTYPE_BYTES[dtype]
-    p.key, p.value = k.data_ptr, v.data_ptr + v_offset_elems * esize
+    p.key, p.value = k.data_ptr + k_offset_elems * esize, v.data_ptr + v_offset_elems * esize
     p.key_token_stride, p.value_token_stride = k_token_stride, v_token_stride
     p.key_head_stride, p.value_head_stride = k_head_stride, v_head_stride
     lens = backend.tensor("lens", np.asarray(lengths, np.int32))

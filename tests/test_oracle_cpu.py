@@ -256,3 +256,12 @@ def test_rope_tables_follow_the_decoder_convention(oracle):
     assert cos[1, 1] == oracle.bf16_round(np.array([np.cos(angle)], np.float32))[1][0]
     assert sin[1, 5] == oracle.bf16_round(np.array([np.sin(angle)], np.float32))[1][0]
     assert cos[0, 0] == oracle.bf16_round(np.array([np.cos(3.0)], np.float32))[1][0]
+
+
+def test_full_attention_known_answer_of_the_reference(oracle):
+    # tests/unit/minimax_h3.c:641-681
+    qkv = np.array([[1, 0, 1, 0, 1, 2], [0, 1, 0, 1, 3, 4]], np.float32)
+    selected = np.exp(np.float32(1.0) / np.sqrt(np.float32(2.0)))
+    first = (selected * 1.0 + 3.0) / (selected + 1.0)
+    out = oracle.full_attention_f32(qkv, 1, 2)
+    assert abs(out[0, 0] - first) < 1e-6 and abs(out[0, 1] - (first + 1.0)) < 1e-6
