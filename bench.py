@@ -357,7 +357,7 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
     lib.yvx_cuda_stream_synchronize(backend.stream)
     nbytes = 2 * kv_elems * 4 + 2 * hq * hd * 4
     result = {"workload": "decode 1x1 token, 32q/8kv heads, hd128, KV 4096, F32 (exact-F32 contract)",
-              "kernel": "gqa split attention (general F32 kernel)", "launches_per_step": launches,
+              "kernel": "gqa_decode_f32_kernel", "launches_per_step": launches,
               "kernel_ms": main, "combine_ms": combine, "algorithmic_bytes": nbytes,
               "achieved_gbs": nbytes / (main * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (main * 1e-3) / 1e9 / peak,
               "step_ms": _timed_launches.step_ms, "tokens_per_s": 1.0 / (_timed_launches.step_ms * 1e-3),

@@ -1,0 +1,380 @@
+// Decode / verify over F32 KV rows under the exact-F32 contract (head_dim 128,
+// at most 8 query vectors per KV head, contiguous KV), for launches too short
+// for a streaming loop to reach the DRAM rate: a CTA's chunk (up to 112 tokens
+// of K and V for one KV head) is requested with TMA at the start, in sub-chunks
+// of 16 tokens with their own mbarriers, and each warp consumes sub-chunks as
+// they land. Six sub-chunk buffers (96 KB, two CTAs per SM); a seventh sub-chunk
+// goes into buffer 0 once the warp that owns that buffer has consumed it. All
+// arithmetic is single-precision FMA.
+//
+//   scores   lanes own 4 dims; the 16 partial dot products per vector are summed
+//            across lanes by a halving exchange (16 shuffles for 16 tokens, four
+//            vectors interleaved), after which lanes 2t and 2t+1 hold token t's score
+//   softmax  running max per vector (warp-uniform), exp2 domain
+//   values   the 16 weights go through shared memory and come back as broadcast
+//            loads; lanes own 4 output dims
+//
+// Same partial format and combine as the general kernel, which it replaces for
+// these shapes (reference: yvex_gqa_f32_body, src/backend/cuda/
+// transformer_kernels.cu:137-238, one CTA per query head walking all rows).
+#include "pipeline.cuh"
+
+namespace yvx {
+
+constexpr int kF32Threads = 128, kF32Warps = 4;
+constexpr int kF32HeadDim = 128;
+constexpr int kF32Sub = 16;                       // tokens per sub-chunk
+#ifndef F32_MAXSUBS
+#define F32_MAXSUBS 7
+#endif
+constexpr int kF32MaxSubs = F32_MAXSUBS;                    // 112 tokens per CTA
+constexpr int kF32Buffers = 6;                    // sub-chunk buffers (K and V each)
+constexpr int kF32SubBytes = kF32Sub * kF32HeadDim * 4;          // 8 KB
+constexpr int kF32SmemBytes = 2 * kF32Buffers * kF32SubBytes + 1024 + 256;
+constexpr unsigned int kF32MaxSplits = 256;
+
+struct F32Maps {
+    CUtensorMap key, value;
+};
+
+__device__ __forceinline__ float f32_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Sums x[v][t] over the warp for 16 tokens of four vectors at once: afterwards
+// every lane holds, per vector, the total of token (lane >> 1). The four vectors'
+// exchanges are independent, so their shuffle latencies overlap.
+__device__ __forceinline__ void reduce16x4(float (&x)[4][16], unsigned int lane, float (&total)[4])
+{
+#pragma unroll
+    for (int width = 8, offset = 16; width >= 1; width >>= 1, offset >>= 1) {
+        const bool upper = lane & offset;
+#pragma unroll
+        for (int i = 0; i < width; ++i)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const float keep = upper ? x[v][i + width] : x[v][i];
+                const float send = upper ? x[v][i] : x[v][i + width];
+                x[v][i] = keep + __shfl_xor_sync(0xffffffffu, send, offset);
+            }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) total[v] = x[v][0] + __shfl_xor_sync(0xffffffffu, x[v][0], 1);
+}
+
+// grid: x = split, y = kv head, z = session. VT = vectors per CTA (4 or 8).
+template <int VT>
+__global__ void __launch_bounds__(kF32Threads)
+gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps maps, const int head_major)
+{
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    float *k_smem = reinterpret_cast<float *>(smem);
+    float *v_smem = reinterpret_cast<float *>(smem + kF32Buffers * kF32SubBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * kF32Buffers * kF32SubBytes);
+    __shared__ float weights[kF32Warps][VT][kF32Sub];
+    __shared__ float merge_m[kF32Warps][VT], merge_l[kF32Warps][VT];
+
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned int group = p.query_heads / p.kv_heads;
+    const unsigned int vectors = p.query_rows * group;
+    const unsigned int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
+    const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    long long query_start;
+    if (p.query_start)
+        query_start = (long long)p.query_start[b];
+    else if (p.query_start_from_end)
+        query_start = (long long)kv_tokens - (long long)p.query_rows;
+    else
+        query_start = (long long)p.query_start_uniform;
+
+    const unsigned int t0 = split * p.chunk_tokens;
+    if (t0 >= kv_tokens) return;
+    unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
+    if (p.causal) {
+        const long long last = query_start + (long long)p.query_rows;  // exclusive
+        if (last < (long long)t1) t1 = last > (long long)t0 ? (unsigned int)last : t0;
+    }
+    const unsigned int subs = (t1 - t0 + kF32Sub - 1) / kF32Sub;
+
+    // Sub-chunk i lives in buffer i % 6 and is requested by `request`.
+    auto request = [&](unsigned int i) {
+        const unsigned int buffer = i % kF32Buffers;
+        const int token = (int)(t0 + i * kF32Sub);
+        const int c1 = head_major ? (int)kv_head : token, c2 = head_major ? token : (int)kv_head;
+        mbar_expect_tx(&bars[buffer], 2 * kF32SubBytes);
+        tma_load_4d(k_smem + buffer * kF32Sub * kF32HeadDim, &maps.key, &bars[buffer], 0, c1, c2, (int)b);
+        tma_load_4d(v_smem + buffer * kF32Sub * kF32HeadDim, &maps.value, &bars[buffer], 0, c1, c2, (int)b);
+    };
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.key) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.value) : "memory");
+        for (int i = 0; i < kF32Buffers; ++i) mbar_init(&bars[i], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    // Warp 3 owns a single buffer, so its first lane has time to issue the requests.
+    if (threadIdx.x == 96)
+        for (unsigned int i = 0; i < min(subs, (unsigned int)kF32Buffers); ++i) request(i);
+
+    // Per-vector query (scores in log2 units), visibility limit, running state.
+    float4 q[VT];
+    long long limit[VT];
+    float m[VT], l[VT];
+    float4 acc[VT];
+#pragma unroll
+    for (int v = 0; v < VT; ++v) {
+        const bool live = (unsigned int)v < vectors;
+        const unsigned int row = live ? v / group : 0u;
+        const unsigned int qhead = kv_head * group + (live ? v % group : 0u);
+        const float *qp = reinterpret_cast<const float *>(p.query) +
+                          (unsigned long long)b * p.query_session_stride +
+                          (unsigned long long)row * p.query_row_stride + (unsigned long long)qhead * kF32HeadDim;
+        const float scale = p.scale * 1.4426950408889634f;
+        float4 value = live ? *reinterpret_cast<const float4 *>(qp + 4u * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        q[v] = make_float4(value.x * scale, value.y * scale, value.z * scale, value.w * scale);
+        limit[v] = !live ? -1 : p.causal ? query_start + (long long)row : (long long)kv_tokens - 1;
+        m[v] = -INFINITY;
+        l[v] = 0.0f;
+        acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    bool ok = true;
+    // A buffer belongs to one warp (buffer % 4), so the warp that has consumed
+    // sub-chunk sb can itself request sub-chunk sb + 6 into the same buffer.
+    for (unsigned int sb = 0; sb < subs; ++sb) {
+        const unsigned int buffer = sb % kF32Buffers;
+        if (buffer % kF32Warps != warp) continue;
+        if (ok) ok = mbar_wait(&bars[buffer], (sb / kF32Buffers) & 1u);
+        const float *kb = k_smem + buffer * kF32Sub * kF32HeadDim, *vb = v_smem + buffer * kF32Sub * kF32HeadDim;
+        const long long base = (long long)t0 + (long long)sb * kF32Sub;
+        const unsigned int valid = min((unsigned int)kF32Sub, t1 - (unsigned int)base);
+        float4 krow[kF32Sub];
+#pragma unroll
+        for (int t = 0; t < kF32Sub; ++t) krow[t] = reinterpret_cast<const float4 *>(kb + t * kF32HeadDim)[lane];
+#pragma unroll
+        for (int v0 = 0; v0 < VT; v0 += 4) {
+            float part[4][kF32Sub], score[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int t = 0; t < kF32Sub; ++t)
+                    part[u][t] = fmaf(q[v0 + u].w, krow[t].w,
+                                      fmaf(q[v0 + u].z, krow[t].z, fmaf(q[v0 + u].y, krow[t].y, q[v0 + u].x * krow[t].x)));
+            reduce16x4(part, lane, score);
+            const long long token = base + (long long)(lane >> 1);
+            float tile_max[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (token > limit[v0 + u] || (lane >> 1) >= valid) score[u] = -INFINITY;
+                tile_max[u] = score[u];
+            }
+#pragma unroll
+            for (int offset = 2; offset < 32; offset <<= 1)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    tile_max[u] = fmaxf(tile_max[u], __shfl_xor_sync(0xffffffffu, tile_max[u], offset));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u;
+                const float fresh = fmaxf(m[v], tile_max[u]);
+                const float keep = fresh == -INFINITY ? 1.0f : f32_exp2(m[v] - fresh);
+                const float weight = fresh == -INFINITY ? 0.0f : f32_exp2(score[u] - fresh);
+                m[v] = fresh;
+                l[v] = l[v] * keep + ((lane & 1u) ? 0.0f : weight);
+                acc[v] = make_float4(acc[v].x * keep, acc[v].y * keep, acc[v].z * keep, acc[v].w * keep);
+                if (!(lane & 1u)) weights[warp][v][lane >> 1] = weight;
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int t4 = 0; t4 < kF32Sub / 4; ++t4) {
+            if (4u * t4 >= valid) break;  // rows past the chunk may hold anything
+            float4 vrow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                vrow[j] = reinterpret_cast<const float4 *>(vb + (4 * t4 + j) * kF32HeadDim)[lane];
+#pragma unroll
+            for (int v = 0; v < VT; ++v) {
+                const float4 w = *reinterpret_cast<const float4 *>(&weights[warp][v][4 * t4]);
+                const float ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (4u * t4 + j >= valid) continue;
+                    acc[v].x = fmaf(ws[j], vrow[j].x, acc[v].x);
+                    acc[v].y = fmaf(ws[j], vrow[j].y, acc[v].y);
+                    acc[v].z = fmaf(ws[j], vrow[j].z, acc[v].z);
+                    acc[v].w = fmaf(ws[j], vrow[j].w, acc[v].w);
+                }
+            }
+        }
+        __syncwarp();
+        if (sb + kF32Buffers < subs && lane == 0) {
+            fence_proxy_async();  // this warp's reads of the buffer come before the next copy into it
+            request(sb + kF32Buffers);
+        }
+    }
+    if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+
+    // The main loop is over: let the combine kernel's launch overlap the epilogue.
+    pdl_launch_dependents();
+    // Merge the four warps through the (now consumed) K region.
+    __syncthreads();
+    float *merge_acc = k_smem;  // [warp][VT][128]
+#pragma unroll
+    for (int v = 0; v < VT; ++v) {
+        const float total = warp_sum(l[v]);
+        if (lane == 0) {
+            merge_m[warp][v] = m[v];
+            merge_l[warp][v] = total;
+        }
+        reinterpret_cast<float4 *>(merge_acc + (warp * VT + v) * kF32HeadDim)[lane] = acc[v];
+    }
+    __syncthreads();
+    const bool direct = p.max_splits == 1u;
+    const unsigned int d = threadIdx.x;  // one head dimension per thread
+    for (unsigned int v = 0; v < min((unsigned int)VT, vectors); ++v) {
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kF32Warps; ++w) mm = fmaxf(mm, merge_m[w][v]);
+        float ll = 0.0f, o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kF32Warps; ++w) {
+            const float scale = merge_m[w][v] == -INFINITY ? 0.0f : f32_exp2(merge_m[w][v] - mm);
+            ll = fmaf(merge_l[w][v], scale, ll);
+            o = fmaf(merge_acc[(w * VT + v) * kF32HeadDim + d], scale, o);
+        }
+        const unsigned int row = v / group, qhead = kv_head * group + v % group;
+        const unsigned long long item = ((unsigned long long)b * p.query_rows + row) * p.query_heads + qhead;
+        if (direct) {
+            const float value = o / ll;
+            if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+            store_output(p.output, p.output_dtype, item * kF32HeadDim + d, value);
+        } else {
+            float *part = p.partials + (item * p.max_splits + split) * (kF32HeadDim + 2ull);
+            part[d] = ll > 0.0f ? o / ll : 0.0f;
+            if (d == 0) {
+                part[kF32HeadDim] = mm * 0.6931471805599453f;  // natural-log units
+                part[kF32HeadDim + 1] = ll;
+            }
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------------
+
+typedef CUresult (*F32EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                     const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static F32EncodeTiledFn f32_encode_entry()
+{
+    static F32EncodeTiledFn entry = nullptr;
+    static bool resolved = false;
+    if (!resolved) {
+        void *symbol = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &query) ==
+                cudaSuccess &&
+            query == cudaDriverEntryPointSuccess)
+            entry = reinterpret_cast<F32EncodeTiledFn>(symbol);
+        resolved = true;
+    }
+    return entry;
+}
+
+// 4-D f32 map {128 dims, a, b, session}; the 16-token dimension is whichever of
+// the two middle dimensions has the token stride. No swizzle: a row is 512 bytes.
+static bool f32_encode(CUtensorMap *map, const void *base, unsigned long long token_stride,
+                       unsigned long long head_stride, unsigned long long session_stride,
+                       unsigned long long tokens, unsigned long long heads, unsigned long long sessions,
+                       bool head_first)
+{
+    F32EncodeTiledFn encode = f32_encode_entry();
+    if (!encode) return false;
+    const unsigned long long tb = token_stride * 4ull, hb = head_stride * 4ull;
+    unsigned long long sb = session_stride * 4ull;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (tb & 15ull) || (hb & 15ull) || (sb & 15ull) || !tb || !hb)
+        return false;
+    if (sessions <= 1ull || !sb) {
+        if (sessions > 1ull) return false;
+        sessions = 1ull;
+        sb = ((head_first ? tb * tokens : hb * heads) + 15ull) & ~15ull;
+    }
+    cuuint64_t dims[4] = {kF32HeadDim, head_first ? heads : tokens, head_first ? tokens : heads, sessions};
+    cuuint64_t strides[3] = {head_first ? hb : tb, head_first ? tb : hb, sb};
+    cuuint32_t box[4] = {kF32HeadDim, head_first ? 1u : (cuuint32_t)kF32Sub, head_first ? (cuuint32_t)kF32Sub : 1u, 1};
+    cuuint32_t elem[4] = {1, 1, 1, 1};
+    for (int i = 0; i < 3; ++i)
+        if (strides[i] >= (1ull << 40)) return false;
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void *>(base), dims, strides, box,
+                  elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Shapes this kernel takes (also used by the split planner).
+bool gqa_decode_f32_admits(const yvx_gqa_problem &p)
+{
+    if (p.head_dim != (unsigned)kF32HeadDim || p.query_dtype != YVEX_DTYPE_F32 || p.kv_dtype != YVEX_DTYPE_F32 ||
+        p.block_table || p.partial_output || p.kv_position_base || !p.kv_heads || p.query_heads % p.kv_heads)
+        return false;
+    if (p.query_head_stride && p.query_head_stride != p.head_dim) return false;
+    const unsigned int vectors = p.query_rows * (p.query_heads / p.kv_heads);
+    if (vectors == 0u || vectors > 8u) return false;
+    if ((reinterpret_cast<uintptr_t>(p.query) & 15u) || (p.query_row_stride & 3ull) || (p.query_session_stride & 3ull))
+        return false;
+    return p.kv_tokens_max <= kF32MaxSplits * (unsigned)(kF32MaxSubs * kF32Sub);
+}
+
+// Chunk that puts two CTAs on every SM in a single wave: a multiple of 16 tokens, at most 112.
+void gqa_decode_f32_plan(yvx_gqa_problem *p, int sm_count)
+{
+    const unsigned long long lanes = (unsigned long long)p->sessions * p->kv_heads;
+    const unsigned long long target = 2ull * (unsigned long long)(sm_count > 0 ? sm_count : 148);
+    unsigned long long splits = lanes ? target / lanes : 1ull;
+    if (splits < 1ull) splits = 1ull;
+    unsigned long long chunk = ((unsigned long long)p->kv_tokens_max + splits - 1ull) / splits;
+    chunk = ((chunk + kF32Sub - 1ull) / kF32Sub) * kF32Sub;
+    if (chunk < (unsigned)kF32Sub) chunk = kF32Sub;
+    if (chunk > (unsigned)(kF32MaxSubs * kF32Sub)) chunk = kF32MaxSubs * kF32Sub;
+    p->chunk_tokens = (unsigned int)chunk;
+    p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
+    if (!p->max_splits) p->max_splits = 1u;
+}
+
+// Returns 1 when the launch was made (a combine follows when the KV was split),
+// 0 when the shape is not this kernel's, negative on a launch error.
+int gqa_decode_f32_launch(const yvx_gqa_problem &p, cudaStream_t stream)
+{
+    if (!gqa_decode_f32_admits(p) || p.chunk_tokens % kF32Sub || p.chunk_tokens > (unsigned)(kF32MaxSubs * kF32Sub))
+        return 0;
+    const bool head_first = p.key_head_stride < p.key_token_stride;
+    if ((p.value_head_stride < p.value_token_stride) != head_first) return 0;
+    F32Maps maps;
+    if (!f32_encode(&maps.key, p.key, p.key_token_stride, p.key_head_stride, p.key_session_stride,
+                    p.kv_tokens_max, p.kv_heads, p.sessions, head_first) ||
+        !f32_encode(&maps.value, p.value, p.value_token_stride, p.value_head_stride, p.value_session_stride,
+                    p.kv_tokens_max, p.kv_heads, p.sessions, head_first))
+        return 0;
+    const unsigned int vectors = p.query_rows * (p.query_heads / p.kv_heads);
+    const dim3 grid(p.max_splits, p.kv_heads, p.sessions);
+    cudaError_t error;
+    if (vectors <= 4u) {
+        error = cudaFuncSetAttribute(gqa_decode_f32_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
+        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
+        gqa_decode_f32_kernel<4><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0);
+    } else {
+        error = cudaFuncSetAttribute(gqa_decode_f32_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
+        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
+        gqa_decode_f32_kernel<8><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0);
+    }
+    const int rc = yvx_cuda_check(cudaGetLastError(), "gqa_decode_f32_kernel");
+    return rc != 0 ? rc : 1;
+}
+
+}  // namespace yvx

@@ -4,6 +4,9 @@
 namespace yvx {
 int gqa_generic_main_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_combine_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+bool gqa_decode_f32_admits(const yvx_gqa_problem &p);
+void gqa_decode_f32_plan(yvx_gqa_problem *p, int sm_count);
+int gqa_decode_f32_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream);
@@ -22,6 +25,11 @@ extern "C" {
 void yvx_cuda_gqa_plan_splits(yvx_gqa_problem *p, int sm_count)
 {
     if (!p) return;
+    // Short F32 decode launches have their own kernel and their own chunk (16..112 tokens).
+    if (!p->force_general && yvx::gqa_decode_f32_admits(*p)) {
+        yvx::gqa_decode_f32_plan(p, sm_count);
+        return;
+    }
     const unsigned long long wave = 2ull * (unsigned long long)(sm_count > 0 ? sm_count : 148);
     const unsigned int group = p->kv_heads ? p->query_heads / p->kv_heads : 1u;
     const unsigned long long row_tiles = ((unsigned long long)p->query_rows * group + 15ull) / 16ull;
@@ -79,6 +87,7 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     int rc = packed_heads ? yvx::gqa_decode_q8_launch(*p, s)
                           : (p->kv_dtype == YVEX_DTYPE_Q8_0 ? YVEX_ERR_UNSUPPORTED : 0);
     const unsigned int vectors = p->query_rows * (p->query_heads / p->kv_heads);
+    if (rc == 0 && !p->force_general && packed_heads) rc = yvx::gqa_decode_f32_launch(*p, s);
     if (rc == 0 && !p->force_general && packed_heads)
         rc = vectors <= 64u ? yvx::gqa_decode_mma_launch(*p, s) : yvx::prefill_tcgen05_launch(*p, s);
     const bool final_output = rc == 2;
