@@ -211,6 +211,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_copy_async", "yvx_cuda_stream_create", "yvx_cuda_stream_destroy",
     "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
+    "yvx_cuda_graph_capture_begin", "yvx_cuda_graph_capture_end", "yvx_cuda_graph_launch", "yvx_cuda_graph_destroy",
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
     "yvx_cuda_gqa_attention_profiled",
@@ -285,6 +286,10 @@ def load():
     lib.yvx_cuda_event_create.argtypes = [P(vp)]
     lib.yvx_cuda_event_destroy.argtypes = [vp]
     lib.yvx_cuda_event_record.argtypes = [vp, vp]
+    lib.yvx_cuda_graph_capture_begin.argtypes = [vp]
+    lib.yvx_cuda_graph_capture_end.argtypes = [vp, P(vp)]
+    lib.yvx_cuda_graph_launch.argtypes = [vp, vp]
+    lib.yvx_cuda_graph_destroy.argtypes = [vp]
     lib.yvx_cuda_event_elapsed_ms.argtypes = [vp, vp, P(C.c_float)]
     lib.yvx_cuda_gqa_partials_bytes.restype = u64
     lib.yvx_cuda_gqa_partials_bytes.argtypes = [P(GqaProblem)]

@@ -133,6 +133,44 @@ int yvx_cuda_stream_synchronize(void *stream)
     return 0;
 }
 
+// Stream capture into a CUDA graph: the attention entry points enqueue kernels
+// only (no allocation, no synchronisation), so a decode step's calls can be
+// captured once and replayed. The reference's operators are capture-aware for
+// the same reason (yvex_cuda_capture_active, src/backend/cuda/capability.c:802-805).
+int yvx_cuda_graph_capture_begin(void *stream)
+{
+    if (!stream) return YVEX_ERR_INVALID_ARG;  // the legacy default stream cannot be captured
+    YVX_CUDA_TRY(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    return 0;
+}
+
+int yvx_cuda_graph_capture_end(void *stream, void **executable)
+{
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (!stream || !executable) return YVEX_ERR_INVALID_ARG;
+    YVX_CUDA_TRY(cudaStreamEndCapture((cudaStream_t)stream, &graph));
+    const cudaError_t error = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (error != cudaSuccess) return yvx_cuda_check(error, "cudaGraphInstantiate");
+    *executable = (void *)exec;
+    return 0;
+}
+
+int yvx_cuda_graph_launch(void *executable, void *stream)
+{
+    if (!executable) return YVEX_ERR_INVALID_ARG;
+    YVX_CUDA_TRY(cudaGraphLaunch((cudaGraphExec_t)executable, (cudaStream_t)stream));
+    return 0;
+}
+
+int yvx_cuda_graph_destroy(void *executable)
+{
+    if (!executable) return 0;
+    YVX_CUDA_TRY(cudaGraphExecDestroy((cudaGraphExec_t)executable));
+    return 0;
+}
+
 int yvx_cuda_event_create(void **event)
 {
     cudaEvent_t created;

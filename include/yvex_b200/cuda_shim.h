@@ -38,6 +38,14 @@ int yvx_cuda_event_create(void **event);
 int yvx_cuda_event_destroy(void *event);
 int yvx_cuda_event_record(void *event, void *stream);
 int yvx_cuda_event_elapsed_ms(void *start, void *stop, float *milliseconds);
+/* Capture of the calls made on `stream` into a replayable graph (no reference entry
+ * point of this name; the reference's operators are capture-aware, src/backend/cuda/
+ * capability.c:802-805). The yvx_cuda_gqa_attention, _mla_decode, _latent_reduce,
+ * _kv_append_rotary and _lse_combine entries may be called between begin and end. */
+int yvx_cuda_graph_capture_begin(void *stream);
+int yvx_cuda_graph_capture_end(void *stream, void **executable);
+int yvx_cuda_graph_launch(void *executable, void *stream);
+int yvx_cuda_graph_destroy(void *executable);
 const char *yvx_cuda_last_error_text(void);
 
 /* ---- grouped-query attention over a KV cache ------------------------------

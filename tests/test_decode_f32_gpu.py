@@ -74,3 +74,39 @@ def test_rows_past_the_length_may_hold_nan(backend, oracle):
         k_head_stride=HD, v_head_stride=HD, k_outer_stride=cap * width, v_outer_stride=cap * width, kv_max=cap)
     ref = oracle.gqa_attention(q[0], k[0, :n], v[0, :n], n - 1, hq, hkv, HD, threads=4)
     assert status == 0 and close(got[0], ref)
+
+
+def test_calls_can_be_captured_into_a_graph_and_replayed(backend, oracle):
+    """Split attention + dependent-launched combine inside a stream capture: the replayed
+    graph produces the same bits as the direct call."""
+    import ctypes as C
+    rng = np.random.Generator(np.random.PCG64(13))
+    hq, hkv, n = 32, 8, 1500
+    width = hkv * HD
+    q = rng.standard_normal((1, 1, hq * HD), dtype=np.float32)
+    k = rng.standard_normal((1, n, width), dtype=np.float32)
+    v = rng.standard_normal((1, n, width), dtype=np.float32)
+    kw = dict(q=backend.tensor("q", q), k=backend.tensor("k", k), v=backend.tensor("v", v), lengths=[n], rows=1,
+              hq=hq, hkv=hkv, hd=HD, dtype=abi.DTYPE_F32, k_token_stride=width, v_token_stride=width,
+              k_head_stride=HD, v_head_stride=HD, k_outer_stride=n * width, v_outer_stride=n * width)
+    direct, status, _, _ = run_problem(backend, **kw)
+    assert status == 0
+    lib = backend.lib
+    captured = {}
+
+    def capture_entry(problem, stream, launches):
+        assert lib.yvx_cuda_graph_capture_begin(stream) == 0, lib.yvx_cuda_last_error_text()
+        rc = lib.yvx_cuda_gqa_attention(problem, stream, launches)
+        graph = C.c_void_p()
+        assert lib.yvx_cuda_graph_capture_end(stream, C.byref(graph)) == 0, lib.yvx_cuda_last_error_text()
+        for _ in range(2):
+            assert lib.yvx_cuda_graph_launch(graph, stream) == 0
+        captured["graph"] = graph
+        return rc
+
+    lib.capture_entry = capture_entry
+    replayed, status, launches, _ = run_problem(backend, entry="capture_entry", **kw)
+    assert status == 0 and launches == 2
+    assert np.array_equal(replayed, direct)
+    assert lib.yvx_cuda_graph_destroy(captured["graph"]) == 0
+    del lib.capture_entry
