@@ -59,83 +59,94 @@ static_assert(sizeof(MlaBarriers) <= 256, "barrier block outgrew its shared-memo
 static_assert(kMlaStages == 2, "score buffers and stages are indexed by tile parity");
 
 // ---- absorb: q_abs[b][h] = [ bf16(q_nope[b][h] . W_uk[h]) | q_rope[b][h] ] ----------
-// grid (heads, ceil(sessions/16)); 4 warps, warp w owns latent columns [128w, 128w+128).
+// grid (heads, 4 latent quarters): a CTA stages its [128 k][128 n] block of W_uk[head]
+// (32 KB, all loads of a thread issued before its first store, so one round trip),
+// then walks the sessions 16 at a time; warp w owns 32 of the quarter's columns.
+// 512 small CTAs are all resident at once, so the 16.8 MB of W_uk stream in one wave.
 constexpr int kAbsorbPitch = 128 * 2 + 16;  // padded row of 128 bf16
-constexpr int kAbsorbSmem = 16 * kAbsorbPitch + 4 * 128 * kAbsorbPitch;
+constexpr int kAbsorbSmem = 16 * kAbsorbPitch + 128 * kAbsorbPitch;
 
 __global__ void __launch_bounds__(128)
 mla_absorb_kernel(const yvx_mla_problem p)
 {
     extern __shared__ unsigned char absorb_smem[];
     unsigned char *a_smem = absorb_smem;                       // [16 sessions][128 nope]
-    unsigned char *w_smem = absorb_smem + 16 * kAbsorbPitch;   // [4 warps][128 k][128 n]
+    unsigned char *w_smem = absorb_smem + 16 * kAbsorbPitch;   // [128 k][128 n]
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const unsigned int head = blockIdx.x, session0 = blockIdx.y * 16u;
+    const unsigned int head = blockIdx.x, quarter = blockIdx.y;
     const __nv_bfloat16 *q_nope = reinterpret_cast<const __nv_bfloat16 *>(p.q_nope);
     const __nv_bfloat16 *w = reinterpret_cast<const __nv_bfloat16 *>(p.w_uk) +
-                             (unsigned long long)head * kMlaNope * kMlaLatent;
-    // A: 16 rows x 16 chunks of 16 bytes
-    for (unsigned int i = threadIdx.x; i < 16u * 16u; i += 128u) {
-        const unsigned int row = i >> 4, chunk = i & 15u;
-        uint4 value = make_uint4(0u, 0u, 0u, 0u);
-        if (session0 + row < p.sessions)
-            value = *reinterpret_cast<const uint4 *>(
-                q_nope + ((unsigned long long)(session0 + row) * kMlaHeads + head) * kMlaNope + chunk * 8u);
-        *reinterpret_cast<uint4 *>(a_smem + row * kAbsorbPitch + chunk * 16u) = value;
-    }
-    // B: each warp stages its [128 k][128 n] block of W_uk[head]
-    unsigned char *wb = w_smem + warp * 128 * kAbsorbPitch;
-    for (unsigned int i = lane; i < 128u * 16u; i += 32u) {
-        const unsigned int k = i >> 4, chunk = i & 15u;
-        *reinterpret_cast<uint4 *>(wb + k * kAbsorbPitch + chunk * 16u) =
-            *reinterpret_cast<const uint4 *>(w + (unsigned long long)k * kMlaLatent + warp * 128u + chunk * 8u);
-    }
-    __syncthreads();
-    uint32_t qa[8][4];
+                             (unsigned long long)head * kMlaNope * kMlaLatent + quarter * 128u;
     {
-        const unsigned int j = lane >> 3, i = lane & 7u;
-        const uint32_t base = smem_u32(a_smem) + (8u * (j & 1u) + i) * kAbsorbPitch + 16u * (j >> 1);
+        uint4 staged[16];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], base + ks * 32u);
+        for (int u = 0; u < 16; ++u) {
+            const unsigned int i = threadIdx.x + 128u * u, k = i >> 4, chunk = i & 15u;
+            staged[u] = *reinterpret_cast<const uint4 *>(w + (unsigned long long)k * kMlaLatent + chunk * 8u);
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            const unsigned int i = threadIdx.x + 128u * u, k = i >> 4, chunk = i & 15u;
+            *reinterpret_cast<uint4 *>(w_smem + k * kAbsorbPitch + chunk * 16u) = staged[u];
+        }
     }
-    float acc[16][4];
+    unsigned short *out = reinterpret_cast<unsigned short *>(p.q_absorbed);
+    const unsigned int g = lane >> 2, c = lane & 3u;
+    for (unsigned int session0 = 0; session0 < p.sessions; session0 += 16u) {
+        __syncthreads();  // the previous tile's fragments have been read (and W is staged)
+        // A: 16 rows x 16 chunks of 16 bytes
+        for (unsigned int i = threadIdx.x; i < 16u * 16u; i += 128u) {
+            const unsigned int row = i >> 4, chunk = i & 15u;
+            uint4 value = make_uint4(0u, 0u, 0u, 0u);
+            if (session0 + row < p.sessions)
+                value = *reinterpret_cast<const uint4 *>(
+                    q_nope + ((unsigned long long)(session0 + row) * kMlaHeads + head) * kMlaNope + chunk * 8u);
+            *reinterpret_cast<uint4 *>(a_smem + row * kAbsorbPitch + chunk * 16u) = value;
+        }
+        __syncthreads();
+        uint32_t qa[8][4];
+        const unsigned int j = lane >> 3, i8 = lane & 7u;
+        {
+            const uint32_t base = smem_u32(a_smem) + (8u * (j & 1u) + i8) * kAbsorbPitch + 16u * (j >> 1);
 #pragma unroll
-    for (int n = 0; n < 16; ++n)
+            for (int ks = 0; ks < 8; ++ks) ldmatrix_x4(qa[ks], base + ks * 32u);
+        }
+        float acc[4][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[n][e] = 0.0f;
-    {
-        const unsigned int j = lane >> 3, i = lane & 7u;
-        const uint32_t wbase = smem_u32(wb);
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[n][e] = 0.0f;
+        const uint32_t wbase = smem_u32(w_smem) + warp * 64u;  // this warp's 32 columns
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
 #pragma unroll
-            for (int np = 0; np < 8; ++np) {
+            for (int np = 0; np < 2; ++np) {
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, wbase + (16u * ks + 8u * (j & 1u) + i) * kAbsorbPitch +
+                ldmatrix_x4_trans(b, wbase + (16u * ks + 8u * (j & 1u) + i8) * kAbsorbPitch +
                                          (16u * np + 8u * (j >> 1)) * 2u);
                 mma_bf16(acc[2 * np], qa[ks], b[0], b[1]);
                 mma_bf16(acc[2 * np + 1], qa[ks], b[2], b[3]);
             }
-    }
-    const unsigned int g = lane >> 2, c = lane & 3u;
-    unsigned short *out = reinterpret_cast<unsigned short *>(p.q_absorbed);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const unsigned int session = session0 + g + 8u * h;
-        if (session >= p.sessions) continue;
-        unsigned short *dst = out + ((unsigned long long)session * kMlaHeads + head) * kMlaWidth + warp * 128u;
+        for (int h = 0; h < 2; ++h) {
+            const unsigned int session = session0 + g + 8u * h;
+            if (session >= p.sessions) continue;
+            unsigned short *dst = out + ((unsigned long long)session * kMlaHeads + head) * kMlaWidth +
+                                  quarter * 128u + warp * 32u;
 #pragma unroll
-        for (int n = 0; n < 16; ++n)
-            *reinterpret_cast<uint32_t *>(dst + 8 * n + 2 * c) = pack_bf16(acc[n][2 * h], acc[n][2 * h + 1]);
+            for (int n = 0; n < 4; ++n)
+                *reinterpret_cast<uint32_t *>(dst + 8 * n + 2 * c) = pack_bf16(acc[n][2 * h], acc[n][2 * h + 1]);
+        }
     }
-    // rope part: copied through
-    const unsigned short *q_rope = reinterpret_cast<const unsigned short *>(p.q_rope);
-    for (unsigned int i = threadIdx.x; i < 16u * 8u; i += 128u) {
-        const unsigned int row = i >> 3, chunk = i & 7u;
-        if (session0 + row >= p.sessions) continue;
-        const unsigned long long item = (unsigned long long)(session0 + row) * kMlaHeads + head;
-        *reinterpret_cast<uint4 *>(out + item * kMlaWidth + kMlaLatent + chunk * 8u) =
-            *reinterpret_cast<const uint4 *>(q_rope + item * kMlaRope + chunk * 8u);
+    // rope part: copied through by the first quarter's CTA
+    if (quarter == 0u) {
+        const unsigned short *q_rope = reinterpret_cast<const unsigned short *>(p.q_rope);
+        for (unsigned int i = threadIdx.x; i < p.sessions * 8u; i += 128u) {
+            const unsigned int row = i >> 3, chunk = i & 7u;
+            const unsigned long long item = (unsigned long long)row * kMlaHeads + head;
+            *reinterpret_cast<uint4 *>(out + item * kMlaWidth + kMlaLatent + chunk * 8u) =
+                *reinterpret_cast<const uint4 *>(q_rope + item * kMlaRope + chunk * 8u);
+        }
     }
 }
 
@@ -559,7 +570,7 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemBytes);
     if (error != cudaSuccess) return yvx_cuda_check(error, "mla kernel attributes");
     if (events) cudaEventRecord((cudaEvent_t)events[0], s);
-    mla_absorb_kernel<<<dim3(kMlaHeads, (p->sessions + 15u) / 16u), 128, kAbsorbSmem, s>>>(*p);
+    mla_absorb_kernel<<<dim3(kMlaHeads, 4), 128, kAbsorbSmem, s>>>(*p);
     if (events) cudaEventRecord((cudaEvent_t)events[1], s);
     mla_decode_tcgen05_kernel<<<dim3(2, p->max_splits, p->sessions), kMlaThreads, kMlaSmemBytes, s>>>(*p, maps);
     if (events) cudaEventRecord((cudaEvent_t)events[2], s);
