@@ -235,6 +235,7 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
         unmasked_until = (long long)s.kv_tokens - 1;
     if (unmasked_until > (long long)s.kv_tokens - 1) unmasked_until = (long long)s.kv_tokens - 1;
     const float score_scale = p.scale * kQ8Log2e;
+    const float slack = 8.0f / score_scale;  // raw-score distance worth 2^8 in the weights
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};   // m in raw score units
     float o[16][4];
 #pragma unroll
@@ -308,24 +309,30 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
                     if (token > limit[e >> 1]) sc[n][e] = -INFINITY;
                 }
         }
-        // ---- online softmax: m in raw score units, exponent = (s - m) * scale
-        float tile_max[2];
+        // ---- online softmax: m in raw score units, exponent = (s - m) * scale.
+        // The reference maximum is stale by design: it moves (quad shuffles, rescale of O)
+        // only when some score of the warp exceeds it by more than 2^8 in the exponent,
+        // so the common tile costs one vote instead of four shuffles and a rescale;
+        // weights stay <= 256, exact in f16 / f32 range.
+        bool grow = false;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            tile_max[h] = fmaxf(fmaxf(sc[0][2 * h], sc[0][2 * h + 1]), fmaxf(sc[1][2 * h], sc[1][2 * h + 1]));
-            tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
-            tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
-        }
-        float keep[2], offset[2];
+            const float bound = m[h] + slack;  // -inf while the row has seen nothing
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const float fresh = fmaxf(m[h], tile_max[h]);
-            keep[h] = fresh == -INFINITY ? 1.0f : exp2_approx((m[h] - fresh) * score_scale);
-            m[h] = fresh;
-            l[h] *= keep[h];
-            offset[h] = fresh == -INFINITY ? 0.0f : -fresh * score_scale;
+            for (int n = 0; n < 2; ++n) grow = grow || sc[n][2 * h] > bound || sc[n][2 * h + 1] > bound;
         }
-        if (__any_sync(0xffffffffu, keep[0] != 1.0f || keep[1] != 1.0f)) {
+        if (__any_sync(0xffffffffu, grow)) {
+            float tile_max[2], keep[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                tile_max[h] = fmaxf(fmaxf(sc[0][2 * h], sc[0][2 * h + 1]), fmaxf(sc[1][2 * h], sc[1][2 * h + 1]));
+                tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+                tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+                const float fresh = fmaxf(m[h], tile_max[h]);
+                keep[h] = fresh == -INFINITY ? 1.0f : exp2_approx((m[h] - fresh) * score_scale);
+                m[h] = fresh;
+                l[h] *= keep[h];
+            }
 #pragma unroll
             for (int n = 0; n < 16; ++n) {
                 o[n][0] *= keep[0];
@@ -334,6 +341,9 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
                 o[n][3] *= keep[1];
             }
         }
+        float offset[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) offset[h] = m[h] == -INFINITY ? 0.0f : -m[h] * score_scale;
         uint32_t p_head[4];
 #pragma unroll
         for (int n = 0; n < 2; ++n)
