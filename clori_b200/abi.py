@@ -155,6 +155,53 @@ class LatentReduceArgs(C.Structure):
     ]
 
 
+class AttentionFailure(C.Structure):
+    """yvex_b200_attention_failure (include/yvex_b200/attention.h)."""
+    _fields_ = [("code", C.c_int), ("stage", C.c_char_p), ("expected", u64), ("actual", u64)]
+
+
+class AttentionReduceRequest(C.Structure):
+    """yvex_b200_attention_reduce_request (include/yvex_b200/attention.h)."""
+    _fields_ = [
+        ("attention_class", C.c_int), ("token_position", u64), ("token_count", u64),
+        ("query_heads", u64), ("head_dimension", u64),
+        ("sliding_window", u64), ("compression_ratio", u64), ("indexer_topk", u64),
+        ("candidate_block_visible", C.c_int),
+        ("query", C.c_void_p), ("local", C.c_void_p), ("local_positions", C.c_void_p),
+        ("local_count", u64), ("local_stride", u64),
+        ("compressed", C.c_void_p), ("compressed_positions", C.c_void_p),
+        ("compressed_count", u64), ("compressed_stride", u64),
+        ("selected", C.c_void_p), ("selected_count", C.c_void_p),
+        ("sinks", C.c_void_p), ("output", C.c_void_p),
+    ]
+
+
+class KvAppendRequest(C.Structure):
+    """yvex_b200_kv_append_request (include/yvex_b200/attention.h)."""
+    _fields_ = [
+        ("session_count", u64), ("token_count", u64),
+        ("query_heads", u64), ("key_value_heads", u64), ("head_dimension", u64), ("rotary_dimension", u64),
+        ("bf16_staged_products", C.c_int),
+        ("query", C.c_void_p), ("key", C.c_void_p), ("value", C.c_void_p),
+        ("cosines", C.c_void_p), ("sines", C.c_void_p),
+        ("kv_tokens", C.c_void_p), ("max_kv_tokens", u64), ("token_position", C.c_void_p),
+        ("state_values", C.c_void_p), ("state_positions", C.c_void_p),
+        ("state_capacity", u64), ("state_row_stride", u64),
+        ("key_pool", C.c_void_p), ("value_pool", C.c_void_p), ("block_table", C.c_void_p),
+        ("block_tokens", u64), ("max_blocks_per_session", u64), ("pool_blocks", u64),
+    ]
+
+
+class MlaDecodeRequest(C.Structure):
+    """yvex_b200_mla_decode_request (include/yvex_b200/attention.h)."""
+    _fields_ = [
+        ("session_count", u64), ("heads", u64), ("nope_dimension", u64), ("latent_dimension", u64),
+        ("rope_dimension", u64), ("context_capacity", u64), ("max_kv_tokens", u64), ("scale", C.c_float),
+        ("q_nope", C.c_void_p), ("q_rope", C.c_void_p), ("w_uk", C.c_void_p),
+        ("latent", C.c_void_p), ("rope_key", C.c_void_p), ("kv_tokens", C.c_void_p), ("output", C.c_void_p),
+    ]
+
+
 class KvAppendArgs(C.Structure):
     """yvx_kv_append_args (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [
@@ -202,6 +249,7 @@ EXPORTED_SYMBOLS = [
     "yvex_b200_transformer_attention_workspace_required",
     "yvex_b200_transformer_attention_execute",
     "yvex_backend_op_attention", "yvex_b200_attention_batch_execute",
+    "yvex_b200_attention_reduce_execute", "yvex_b200_kv_append_rotary_execute", "yvex_b200_mla_decode_execute",
     "yvex_b200_kv_page_tokens", "yvex_b200_kv_page_touch", "yvex_b200_kv_block_row",
     "yvex_b200_kv_sequence_shard",
     # cuda_shim.h
@@ -266,6 +314,10 @@ def load():
         P(DeviceTensor), P(DeviceTensor), P(DeviceTensor), P(Error)]
     lib.yvex_b200_attention_batch_execute.argtypes = [
         vp, P(BatchRequest), P(OperationFacts), P(Error)]
+    lib.yvex_b200_attention_reduce_execute.argtypes = [
+        vp, P(AttentionReduceRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
+    lib.yvex_b200_kv_append_rotary_execute.argtypes = [vp, P(KvAppendRequest), P(OperationFacts), P(Error)]
+    lib.yvex_b200_mla_decode_execute.argtypes = [vp, P(MlaDecodeRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_kv_page_tokens.argtypes = [P(PageRequest), P(u64), P(u64)]
     lib.yvex_b200_kv_page_touch.argtypes = [u64, u64, u64, P(u64), P(u64)]
     lib.yvex_b200_kv_block_row.restype = u64

@@ -1,0 +1,327 @@
+/* Operator-level entry points for the latent attention stages and the KV
+ * append: borrowed yvex_device_tensor arguments, ownership and extent checks,
+ * the reference's refusal codes, the backend's status word, facts.
+ *
+ * yvex_b200_attention_reduce_execute is the reduce stage of the encoded
+ * attention job (yvex_backend_attention_execute, include/yvex/internal/
+ * backend.h:193-195; stage in src/backend/cuda/attention.c:1386-1422), with
+ * the reference's typed failure {code, stage, expected, actual}
+ * (include/yvex/internal/backend.h:144-161).
+ * yvex_b200_kv_append_rotary_execute stands where src/runtime/decoder.c:
+ * 1112-1131 and src/runtime/stateful_attention.c:183-243 rotate and copy.
+ * yvex_b200_mla_decode_execute has no counterpart in the reference. */
+#include "private.h"
+
+#include <math.h>
+#include <string.h>
+
+static int view_ok(const yvex_backend *backend, const yvex_device_tensor *tensor, yvex_dtype dtype,
+                   unsigned long long elements)
+{
+    unsigned long long bytes;
+    return yvx_tensor_owned(backend, tensor) && tensor->dtype == dtype &&
+           yvx_u64_mul(elements, yvx_dtype_bytes(dtype), &bytes) && tensor->bytes >= bytes;
+}
+
+static int reduce_refuse(yvex_b200_attention_failure *failure, yvex_b200_attention_failure_code code,
+                         unsigned long long expected, unsigned long long actual, yvex_error *err,
+                         yvex_status status, const char *message)
+{
+    if (failure) {
+        failure->code = code;
+        failure->stage = "reduce";
+        failure->expected = expected;
+        failure->actual = actual;
+    }
+    return yvx_fail(err, status, "b200.attention.reduce", message);
+}
+
+static int finish(yvex_backend *backend, yvex_backend_operation_facts *facts, unsigned int launches,
+                  unsigned long long temporary, const char *where, yvex_error *err)
+{
+    facts->kernel_launches = launches;
+    facts->temporary_bytes = temporary;
+    facts->compulsory_memory_facts_available = 1;
+    if (backend->synchronous) return yvx_backend_status_collect(backend, facts, where, err);
+    backend->status_pending = 1;
+    return YVEX_OK;
+}
+
+int yvex_b200_attention_reduce_execute(yvex_backend *backend,
+                                       const yvex_b200_attention_reduce_request *r,
+                                       yvex_b200_attention_failure *failure,
+                                       yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.attention.reduce";
+    unsigned long long width, local_rows, elements = 0ull;
+    yvx_latent_reduce_args a;
+    int rc;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    if (!r || !facts || !r->query || !r->local || !r->local_positions || !r->sinks || !r->output)
+        return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                             YVEX_ERR_INVALID_ARG, "query, local rows, positions, sinks and output are required");
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (!r->token_count || !r->query_heads || !r->head_dimension || !r->sliding_window ||
+        !yvx_u64_mul(r->query_heads, r->head_dimension, &width) ||
+        !yvx_u64_add(r->local_count, r->token_count, &local_rows) || r->local_stride < r->head_dimension)
+        return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->head_dimension,
+                             r->local_stride, err, YVEX_ERR_INVALID_ARG,
+                             "token count, heads, head dimension, window and local stride must be consistent");
+    if (r->head_dimension > 512ull || r->attention_class > YVEX_B200_ATTENTION_HCA)
+        return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_CAPABILITY, 512ull, r->head_dimension, err,
+                             YVEX_ERR_UNSUPPORTED, "head dimension above 512 or unknown attention class");
+    if (r->attention_class != YVEX_B200_ATTENTION_SWA) {
+        if (!r->compressed || !r->compressed_positions || !r->compression_ratio ||
+            r->compressed_stride < r->head_dimension)
+            return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->head_dimension,
+                                 r->compressed_stride, err, YVEX_ERR_INVALID_ARG,
+                                 "compressed rows, positions and ratio are required for this class");
+        if (r->attention_class == YVEX_B200_ATTENTION_CSA && (!r->selected || !r->selected_count || !r->indexer_topk))
+            return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                                 YVEX_ERR_INVALID_ARG, "selected rows and counts are required for sparse attention");
+    }
+    if (!yvx_u64_mul(r->token_count, width, &elements) || !view_ok(backend, r->query, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->output, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->sinks, YVEX_DTYPE_F32, r->query_heads) ||
+        !yvx_u64_mul(local_rows, r->local_stride, &elements) || !view_ok(backend, r->local, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->local_positions, YVEX_DTYPE_I64, local_rows))
+        return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements,
+                             r->local ? r->local->bytes : 0ull, err, YVEX_ERR_FORMAT,
+                             "tensor views do not cover the stated geometry");
+    if (r->attention_class != YVEX_B200_ATTENTION_SWA) {
+        if (!yvx_u64_mul(r->compressed_count ? r->compressed_count : 1ull, r->compressed_stride, &elements) ||
+            !view_ok(backend, r->compressed, YVEX_DTYPE_F32, elements) ||
+            !view_ok(backend, r->compressed_positions, YVEX_DTYPE_I64, r->compressed_count ? r->compressed_count : 1ull))
+            return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements,
+                                 r->compressed->bytes, err, YVEX_ERR_FORMAT,
+                                 "compressed views do not cover the stated geometry");
+        if (r->attention_class == YVEX_B200_ATTENTION_CSA &&
+            (!yvx_u64_mul(r->token_count, r->indexer_topk, &elements) ||
+             !view_ok(backend, r->selected, YVEX_DTYPE_I64, elements) ||
+             !view_ok(backend, r->selected_count, YVEX_DTYPE_I64, r->token_count)))
+            return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements,
+                                 r->selected->bytes, err, YVEX_ERR_FORMAT,
+                                 "selected views do not cover the stated geometry");
+    }
+    memset(&a, 0, sizeof(a));
+    a.query = (const float *)r->query->data;
+    a.local = (const float *)r->local->data;
+    a.local_positions = (const unsigned long long *)r->local_positions->data;
+    a.initial_local_count = r->local_count;
+    a.local_stride = r->local_stride;
+    if (r->attention_class != YVEX_B200_ATTENTION_SWA) {
+        a.compressed = (const float *)r->compressed->data;
+        a.compressed_positions = (const unsigned long long *)r->compressed_positions->data;
+        a.compressed_stride = r->compressed_stride;
+        a.ratio = r->compression_ratio;
+    }
+    if (r->attention_class == YVEX_B200_ATTENTION_CSA) {
+        a.selected = (const unsigned long long *)r->selected->data;
+        a.selected_count = (const unsigned long long *)r->selected_count->data;
+        a.topk_capacity = r->indexer_topk;
+    }
+    a.sinks = (const float *)r->sinks->data;
+    a.query_heads = r->query_heads;
+    a.head_dim = r->head_dimension;
+    a.sliding_window = r->sliding_window;
+    a.attention_class = (unsigned int)r->attention_class;
+    a.phase_start_position = r->token_position;
+    a.token_count = r->token_count;
+    a.candidate_block_visible = r->candidate_block_visible;
+    a.out = (float *)r->output->data;
+    a.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_latent_reduce(&a, backend->stream);
+    if (rc != 0) {
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
+            failure->stage = "reduce";
+        }
+        return yvx_backend_device_fail(backend, rc, where, err);
+    }
+    rc = finish(backend, facts, 1u, 0ull, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC
+                                                  : YVEX_B200_ATTENTION_FAILURE_SYNCHRONIZE;
+            failure->stage = "reduce";
+        }
+        return rc;
+    }
+    r->output->is_written = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_b200_kv_append_rotary_execute(yvex_backend *backend, const yvex_b200_kv_append_request *r,
+                                       yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.kv.append_rotary";
+    unsigned long long rows, query_width, kv_width, elements;
+    yvx_kv_append_args a;
+    int rc;
+    if (!r || !facts || !r->key || !r->value || !r->cosines || !r->sines)
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "new key and value rows and rotary tables are required");
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (!r->session_count || !r->token_count || !r->key_value_heads || !r->head_dimension ||
+        !r->rotary_dimension || (r->rotary_dimension & 1ull) || r->rotary_dimension > r->head_dimension ||
+        (r->query && !r->query_heads) || r->session_count > 65535ull || r->token_count > 0x7fffffffull ||
+        !yvx_u64_mul(r->session_count, r->token_count, &rows) ||
+        !yvx_u64_mul(r->query_heads, r->head_dimension, &query_width) ||
+        !yvx_u64_mul(r->key_value_heads, r->head_dimension, &kv_width))
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "sessions, rows, heads and rotary width must be consistent");
+    if (!r->state_values && !r->key_pool)
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "a state bank or a block-table pool is required");
+    if ((r->query && (!yvx_u64_mul(rows, query_width, &elements) || !view_ok(backend, r->query, YVEX_DTYPE_F32, elements))) ||
+        !yvx_u64_mul(rows, kv_width, &elements) || !view_ok(backend, r->key, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->value, YVEX_DTYPE_F32, elements) ||
+        !yvx_u64_mul(rows, r->rotary_dimension, &elements) || !view_ok(backend, r->cosines, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->sines, YVEX_DTYPE_F32, elements) ||
+        (r->kv_tokens && !view_ok(backend, r->kv_tokens, YVEX_DTYPE_I32, r->session_count)) ||
+        (r->token_position && !view_ok(backend, r->token_position, YVEX_DTYPE_I64, r->session_count)))
+        return yvx_fail(err, YVEX_ERR_FORMAT, where, "packed F32 rows and explicit rotary tables are required");
+    memset(&a, 0, sizeof(a));
+    if (r->state_values) {
+        /* the caller bounds the bank: rows [0, state_capacity) of state_row_stride floats per session */
+        if (r->state_row_stride < 2ull * kv_width || !r->state_capacity ||
+            !yvx_u64_mul(r->state_capacity, r->state_row_stride, &elements) ||
+            !yvx_u64_mul(elements, r->session_count, &elements) ||
+            !view_ok(backend, r->state_values, YVEX_DTYPE_F32, elements) ||
+            (r->state_positions &&
+             (!yvx_u64_mul(r->state_capacity, r->session_count, &elements) ||
+              !view_ok(backend, r->state_positions, YVEX_DTYPE_I64, elements))) ||
+            r->max_kv_tokens > r->state_capacity || r->token_count > r->state_capacity - r->max_kv_tokens)
+            return yvx_fail(err, YVEX_ERR_BOUNDS, where, "new rows exceed the admitted state view");
+        a.state_values = (float *)r->state_values->data;
+        a.state_row_stride = r->state_row_stride;
+        a.state_session_stride = r->state_capacity * r->state_row_stride;
+        if (r->state_positions) {
+            a.state_positions = (unsigned long long *)r->state_positions->data;
+            a.state_position_stride = r->state_capacity;
+        }
+    }
+    if (r->key_pool) {
+        unsigned long long blocks_needed, block_elements;
+        if (!r->value_pool || !r->block_table || !r->block_tokens || !r->max_blocks_per_session ||
+            !yvx_u64_mul(r->block_tokens, kv_width, &block_elements) || !r->pool_blocks ||
+            !yvx_u64_mul(r->pool_blocks, block_elements, &elements) ||
+            !view_ok(backend, r->key_pool, YVEX_DTYPE_BF16, elements) ||
+            !view_ok(backend, r->value_pool, YVEX_DTYPE_BF16, elements) ||
+            !yvx_u64_mul(r->session_count, r->max_blocks_per_session, &elements) ||
+            !view_ok(backend, r->block_table, YVEX_DTYPE_I32, elements))
+            return yvx_fail(err, YVEX_ERR_FORMAT, where, "bf16 pools and an int32 block table are required");
+        blocks_needed = (r->max_kv_tokens + r->token_count + r->block_tokens - 1ull) / r->block_tokens;
+        if (blocks_needed > r->max_blocks_per_session)
+            return yvx_fail(err, YVEX_ERR_BOUNDS, where, "new rows exceed the block table");
+        a.key_pool = r->key_pool->data;
+        a.value_pool = r->value_pool->data;
+        a.block_table = (const int *)r->block_table->data;
+        a.block_tokens = (unsigned int)r->block_tokens;
+        a.block_table_stride = (unsigned int)r->max_blocks_per_session;
+        a.pool_blocks = (unsigned int)r->pool_blocks;
+        a.pool_token_stride = kv_width;
+        a.pool_head_stride = r->head_dimension;
+        a.pool_block_stride = block_elements;
+    }
+    a.sessions = (unsigned int)r->session_count;
+    a.tokens = (unsigned int)r->token_count;
+    a.query_heads = (unsigned int)r->query_heads;
+    a.kv_heads = (unsigned int)r->key_value_heads;
+    a.head_dim = (unsigned int)r->head_dimension;
+    a.rotary_dim = (unsigned int)r->rotary_dimension;
+    a.staged_bf16 = r->bf16_staged_products;
+    a.query = r->query ? (float *)r->query->data : NULL;
+    a.key = (const float *)r->key->data;
+    a.value = (const float *)r->value->data;
+    a.cosines = (const float *)r->cosines->data;
+    a.sines = (const float *)r->sines->data;
+    a.kv_tokens = r->kv_tokens ? (const int *)r->kv_tokens->data : NULL;
+    a.kv_tokens_uniform = (unsigned int)r->max_kv_tokens;
+    a.token_position = r->token_position ? (const unsigned long long *)r->token_position->data : NULL;
+    a.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_kv_append_rotary(&a, backend->stream);
+    if (rc != 0) return yvx_backend_device_fail(backend, rc, where, err);
+    facts->d2d_bytes = rows * 2ull * kv_width * (r->state_values ? 4ull : 0ull) +
+                       rows * 2ull * kv_width * (r->key_pool ? 2ull : 0ull);
+    rc = finish(backend, facts, 1u, 0ull, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (r->query) r->query->is_written = 1;
+    if (r->state_values) r->state_values->is_written = 1;
+    if (r->state_positions) r->state_positions->is_written = 1;
+    if (r->key_pool) r->key_pool->is_written = r->value_pool->is_written = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_b200_mla_decode_execute(yvex_backend *backend, const yvex_b200_mla_decode_request *r,
+                                 yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.attention.mla_decode";
+    unsigned long long items, elements, absorbed, partials;
+    yvx_mla_problem p;
+    unsigned int launches = 0;
+    void *scratch = NULL;
+    int rc;
+    if (!r || !facts || !r->q_nope || !r->q_rope || !r->w_uk || !r->latent || !r->rope_key || !r->output)
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "queries, up-projection, caches and output are required");
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (!r->session_count || !r->context_capacity || !r->max_kv_tokens || r->max_kv_tokens > r->context_capacity ||
+        r->session_count > 65535ull || r->context_capacity > 0x7fffffffull || !(r->scale > 0.0f) || !isfinite(r->scale))
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "sessions, context and a positive finite scale are required");
+    if (r->heads != 128ull || r->nope_dimension != 128ull || r->latent_dimension != 512ull || r->rope_dimension != 64ull)
+        return yvx_fail(err, YVEX_ERR_UNSUPPORTED, where, "128 heads, 128 nope, 512 latent and 64 rope dims are supported");
+    items = r->session_count * r->heads;
+    if (!view_ok(backend, r->q_nope, YVEX_DTYPE_BF16, items * r->nope_dimension) ||
+        !view_ok(backend, r->q_rope, YVEX_DTYPE_BF16, items * r->rope_dimension) ||
+        !view_ok(backend, r->w_uk, YVEX_DTYPE_BF16, r->heads * r->nope_dimension * r->latent_dimension) ||
+        !yvx_u64_mul(r->session_count * r->context_capacity, r->latent_dimension, &elements) ||
+        !view_ok(backend, r->latent, YVEX_DTYPE_BF16, elements) ||
+        !view_ok(backend, r->rope_key, YVEX_DTYPE_BF16, r->session_count * r->context_capacity * r->rope_dimension) ||
+        !view_ok(backend, r->output, YVEX_DTYPE_F32, items * r->latent_dimension) ||
+        (r->kv_tokens && !view_ok(backend, r->kv_tokens, YVEX_DTYPE_I32, r->session_count)))
+        return yvx_fail(err, YVEX_ERR_FORMAT, where, "bf16 queries and caches, F32 output and I32 lengths are required");
+    memset(&p, 0, sizeof(p));
+    p.sessions = (unsigned int)r->session_count;
+    p.heads = 128u;
+    p.nope_dim = 128u;
+    p.latent_dim = 512u;
+    p.rope_dim = 64u;
+    p.scale = r->scale;
+    p.q_nope = r->q_nope->data;
+    p.q_rope = r->q_rope->data;
+    p.w_uk = r->w_uk->data;
+    p.latent = r->latent->data;
+    p.rope_key = r->rope_key->data;
+    p.latent_session_stride = r->context_capacity * r->latent_dimension;
+    p.rope_session_stride = r->context_capacity * r->rope_dimension;
+    p.kv_tokens = r->kv_tokens ? (const unsigned int *)r->kv_tokens->data : NULL;
+    p.kv_tokens_uniform = (unsigned int)r->max_kv_tokens;
+    p.kv_tokens_max = (unsigned int)r->max_kv_tokens;
+    yvx_cuda_mla_plan(&p, backend->sm_count);
+    absorbed = (yvx_cuda_mla_absorbed_bytes(&p) + 255ull) & ~255ull;
+    partials = yvx_cuda_mla_partials_bytes(&p);
+    rc = yvx_backend_scratch(backend, absorbed + partials, &scratch, where, err);
+    if (rc != YVEX_OK) return rc;
+    p.q_absorbed = scratch;
+    p.partials = (float *)((unsigned char *)scratch + absorbed);
+    p.output = (float *)r->output->data;
+    p.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_mla_decode(&p, backend->stream, NULL, &launches);
+    if (rc != 0) return yvx_backend_device_fail(backend, rc, where, err);
+    rc = finish(backend, facts, launches, absorbed + partials, where, err);
+    if (rc != YVEX_OK) return rc;
+    r->output->is_written = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}

@@ -139,6 +139,101 @@ int yvex_b200_attention_batch_execute(yvex_backend *backend,
                                       const yvex_b200_attention_batch_request *request,
                                       yvex_backend_operation_facts *facts, yvex_error *err);
 
+/* ---- latent attention: the reduce stage of the encoded attention job ---------
+ * The reference reaches this stage inside yvex_backend_attention_execute
+ * (include/yvex/internal/backend.h:193-195; src/backend/cuda/attention.c:1386-1422).
+ * The request names the job fields that stage consumes (include/yvex/internal/
+ * backend.h:94-124): phase geometry, the phase's query, local window rows with
+ * positions, compressed rows with positions, the selected lists of sparse
+ * attention, and the per-head sinks. The failure record is the reference's
+ * {code, stage, expected, actual} (include/yvex/internal/backend.h:144-161). */
+typedef enum {
+    YVEX_B200_ATTENTION_SWA = 0, /* window only */
+    YVEX_B200_ATTENTION_CSA,     /* window + selected compressed rows */
+    YVEX_B200_ATTENTION_HCA      /* window + every visible compressed row */
+} yvex_b200_attention_class;
+typedef enum {
+    YVEX_B200_ATTENTION_FAILURE_NONE = 0,
+    YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT,
+    YVEX_B200_ATTENTION_FAILURE_CAPABILITY,
+    YVEX_B200_ATTENTION_FAILURE_BUDGET,
+    YVEX_B200_ATTENTION_FAILURE_ALLOCATION,
+    YVEX_B200_ATTENTION_FAILURE_COPY,
+    YVEX_B200_ATTENTION_FAILURE_LAUNCH,
+    YVEX_B200_ATTENTION_FAILURE_SYNCHRONIZE,
+    YVEX_B200_ATTENTION_FAILURE_NUMERIC
+} yvex_b200_attention_failure_code;
+typedef struct {
+    yvex_b200_attention_failure_code code;
+    const char *stage;
+    unsigned long long expected, actual;
+} yvex_b200_attention_failure;
+typedef struct yvex_b200_attention_reduce_request {
+    yvex_b200_attention_class attention_class;
+    unsigned long long token_position, token_count;   /* first position and rows of this phase */
+    unsigned long long query_heads, head_dimension;
+    unsigned long long sliding_window, compression_ratio, indexer_topk;
+    int candidate_block_visible;
+    const yvex_device_tensor *query;                  /* F32 [token][heads*head_dim] */
+    const yvex_device_tensor *local, *local_positions; /* F32 [local_count+token_count][local_stride], I64 */
+    unsigned long long local_count, local_stride;     /* rows before this phase's own */
+    const yvex_device_tensor *compressed, *compressed_positions; /* F32 [count][stride], I64 */
+    unsigned long long compressed_count, compressed_stride;
+    const yvex_device_tensor *selected, *selected_count; /* I64 [token][indexer_topk], I64 [token] */
+    const yvex_device_tensor *sinks;                  /* F32 [heads] */
+    yvex_device_tensor *output;                       /* F32 [token][heads*head_dim], bf16-rounded values */
+} yvex_b200_attention_reduce_request;
+int yvex_b200_attention_reduce_execute(yvex_backend *backend,
+                                       const yvex_b200_attention_reduce_request *request,
+                                       yvex_b200_attention_failure *failure,
+                                       yvex_backend_operation_facts *facts, yvex_error *err);
+
+/* ---- KV append + rotary for the new rows of a step ----------------------------
+ * One call where the reference makes two rotate-half launches
+ * (yvex_cuda_transformer_rotary_half, src/backend/cuda/transformer.c:449-457, from
+ * src/runtime/decoder.c:1112-1131), two device copies per new token and a position
+ * upload (src/runtime/stateful_attention.c:183-243). Refusals: geometry ->
+ * YVEX_ERR_INVALID_ARG; views that are not packed F32 rows / explicit tables ->
+ * YVEX_ERR_FORMAT (as src/backend/cuda/transformer.c:431-433); rows beyond the
+ * admitted state view or block table -> YVEX_ERR_BOUNDS (as stateful_attention.c:
+ * 203-206). */
+typedef struct yvex_b200_kv_append_request {
+    unsigned long long session_count, token_count;    /* new rows per session */
+    unsigned long long query_heads, key_value_heads, head_dimension, rotary_dimension;
+    int bf16_staged_products;                         /* 1: the decoder's rotary arithmetic */
+    yvex_device_tensor *query;                        /* F32 [session][token][heads*hd], in place; may be NULL */
+    const yvex_device_tensor *key, *value;            /* F32 [session][token][kv_heads*hd] */
+    const yvex_device_tensor *cosines, *sines;        /* F32 [session][token][rotary_dimension] */
+    const yvex_device_tensor *kv_tokens;              /* I32 [session] rows present; NULL: max_kv_tokens for all */
+    unsigned long long max_kv_tokens;                 /* upper bound of every session's rows present */
+    const yvex_device_tensor *token_position;         /* I64 [session]; NULL: position = row index */
+    yvex_device_tensor *state_values;                 /* F32 [session][state_capacity][state_row_stride] or NULL */
+    yvex_device_tensor *state_positions;              /* I64 [session][state_capacity] or NULL */
+    unsigned long long state_capacity, state_row_stride;
+    yvex_device_tensor *key_pool, *value_pool;        /* BF16 [block][block_tokens][kv_heads*hd] or NULL */
+    const yvex_device_tensor *block_table;            /* I32 [session][max_blocks_per_session] */
+    unsigned long long block_tokens, max_blocks_per_session, pool_blocks;
+} yvex_b200_kv_append_request;
+int yvex_b200_kv_append_rotary_execute(yvex_backend *backend, const yvex_b200_kv_append_request *request,
+                                       yvex_backend_operation_facts *facts, yvex_error *err);
+
+/* ---- latent decode with a separate rope key and an absorbed up-projection -------
+ * No counterpart in the reference (its latent rows carry the rope dims inside the
+ * 512 and serve as key and value). 128 heads, 128 nope, 512 latent, 64 rope dims;
+ * any other geometry is refused with YVEX_ERR_UNSUPPORTED. */
+typedef struct yvex_b200_mla_decode_request {
+    unsigned long long session_count, heads, nope_dimension, latent_dimension, rope_dimension;
+    unsigned long long context_capacity, max_kv_tokens;
+    float scale;
+    const yvex_device_tensor *q_nope, *q_rope;        /* BF16 [session][head][nope | rope] */
+    const yvex_device_tensor *w_uk;                   /* BF16 [head][nope][latent] */
+    const yvex_device_tensor *latent, *rope_key;      /* BF16 [session][context_capacity][latent | rope] */
+    const yvex_device_tensor *kv_tokens;              /* I32 [session]; NULL: max_kv_tokens for all */
+    yvex_device_tensor *output;                       /* F32 [session][head][latent] */
+} yvex_b200_mla_decode_request;
+int yvex_b200_mla_decode_execute(yvex_backend *backend, const yvex_b200_mla_decode_request *request,
+                                 yvex_backend_operation_facts *facts, yvex_error *err);
+
 /* ---- KV block and page indexing (integer, bit-exact) ------------------------
  * Page geometry follows include/yvex/internal/deployment.h:112-132 and
  * src/deployment/plan.c:208-283; page touch follows
