@@ -155,6 +155,12 @@ class LatentReduceArgs(C.Structure):
     ]
 
 
+class KvCopy(C.Structure):
+    """yvex_b200_kv_copy (include/yvex_b200/attention.h)."""
+    _fields_ = [("needed", C.c_int), ("source_block", C.c_int), ("destination_block", C.c_int),
+                ("rows", C.c_uint)]
+
+
 class AttentionFailure(C.Structure):
     """yvex_b200_attention_failure (include/yvex_b200/attention.h)."""
     _fields_ = [("code", C.c_int), ("stage", C.c_char_p), ("expected", u64), ("actual", u64)]
@@ -250,6 +256,10 @@ EXPORTED_SYMBOLS = [
     "yvex_b200_transformer_attention_execute",
     "yvex_backend_op_attention", "yvex_b200_attention_batch_execute",
     "yvex_b200_attention_reduce_execute", "yvex_b200_kv_append_rotary_execute", "yvex_b200_mla_decode_execute",
+    "yvex_b200_kv_pool_create", "yvex_b200_kv_pool_destroy", "yvex_b200_kv_pool_session_open",
+    "yvex_b200_kv_pool_session_fork", "yvex_b200_kv_pool_session_close", "yvex_b200_kv_pool_reserve",
+    "yvex_b200_kv_pool_commit", "yvex_b200_kv_pool_table", "yvex_b200_kv_pool_committed",
+    "yvex_b200_kv_pool_reserved", "yvex_b200_kv_pool_free_blocks", "yvex_b200_kv_pool_block_refcount",
     "yvex_b200_kv_page_tokens", "yvex_b200_kv_page_touch", "yvex_b200_kv_block_row",
     "yvex_b200_kv_sequence_shard",
     # cuda_shim.h
@@ -318,6 +328,25 @@ def load():
         vp, P(AttentionReduceRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
     lib.yvex_b200_kv_append_rotary_execute.argtypes = [vp, P(KvAppendRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_mla_decode_execute.argtypes = [vp, P(MlaDecodeRequest), P(OperationFacts), P(Error)]
+    lib.yvex_b200_kv_pool_create.restype = vp
+    lib.yvex_b200_kv_pool_create.argtypes = [C.c_uint, C.c_uint, C.c_uint, C.c_uint]
+    lib.yvex_b200_kv_pool_destroy.restype = None
+    lib.yvex_b200_kv_pool_destroy.argtypes = [vp]
+    lib.yvex_b200_kv_pool_session_open.argtypes = [vp, P(C.c_uint)]
+    lib.yvex_b200_kv_pool_session_fork.argtypes = [vp, C.c_uint, P(C.c_uint)]
+    lib.yvex_b200_kv_pool_session_close.argtypes = [vp, C.c_uint]
+    lib.yvex_b200_kv_pool_reserve.argtypes = [vp, C.c_uint, C.c_uint, P(KvCopy)]
+    lib.yvex_b200_kv_pool_commit.argtypes = [vp, C.c_uint, C.c_uint]
+    lib.yvex_b200_kv_pool_table.restype = P(C.c_int)
+    lib.yvex_b200_kv_pool_table.argtypes = [vp, C.c_uint]
+    lib.yvex_b200_kv_pool_committed.restype = u64
+    lib.yvex_b200_kv_pool_committed.argtypes = [vp, C.c_uint]
+    lib.yvex_b200_kv_pool_reserved.restype = u64
+    lib.yvex_b200_kv_pool_reserved.argtypes = [vp, C.c_uint]
+    lib.yvex_b200_kv_pool_free_blocks.restype = C.c_uint
+    lib.yvex_b200_kv_pool_free_blocks.argtypes = [vp]
+    lib.yvex_b200_kv_pool_block_refcount.restype = C.c_uint
+    lib.yvex_b200_kv_pool_block_refcount.argtypes = [vp, C.c_uint]
     lib.yvex_b200_kv_page_tokens.argtypes = [P(PageRequest), P(u64), P(u64)]
     lib.yvex_b200_kv_page_touch.argtypes = [u64, u64, u64, P(u64), P(u64)]
     lib.yvex_b200_kv_block_row.restype = u64

@@ -259,6 +259,37 @@ int yvex_b200_kv_page_touch(unsigned long long element_start, unsigned long long
 int yvex_b200_kv_sequence_shard(unsigned long long tokens, unsigned int shards, unsigned int index,
                                 unsigned long long block_tokens, unsigned long long *begin,
                                 unsigned long long *end);
+/* ---- block pool bookkeeping (host side; extension) ----------------------------
+ * Which pool blocks a session owns in the pooled KV layout, with shared prefixes
+ * (fork), copy-on-write of a shared partial block, and the committed / candidate
+ * split of speculative decoding. Stands where the reference keeps two banks per
+ * layer and commits pages lazily (src/runtime/state_residency.c:346-483,
+ * :678-776; candidate rows become visible through select_prefix,
+ * src/graph/state.c:1329-1413). Rows [0, committed) are visible; reserve(n) makes
+ * rows [committed, committed + n) writable (the session's own verify step may
+ * read them: pass committed + n as its length); commit(accepted) moves the
+ * boundary and forgets the rest. Status codes: YVEX_ERR_INVALID_ARG,
+ * YVEX_ERR_BOUNDS (table or session slots exhausted), YVEX_ERR_NOMEM (pool full). */
+typedef struct yvex_b200_kv_pool yvex_b200_kv_pool;
+typedef struct {
+    int needed;                       /* 1: copy rows [0, rows) of source into destination, K and V */
+    int source_block, destination_block;
+    unsigned int rows;
+} yvex_b200_kv_copy;
+yvex_b200_kv_pool *yvex_b200_kv_pool_create(unsigned int blocks, unsigned int block_tokens,
+                                            unsigned int max_sessions, unsigned int max_blocks_per_session);
+void yvex_b200_kv_pool_destroy(yvex_b200_kv_pool *pool);
+int yvex_b200_kv_pool_session_open(yvex_b200_kv_pool *pool, unsigned int *session);
+int yvex_b200_kv_pool_session_fork(yvex_b200_kv_pool *pool, unsigned int parent, unsigned int *child);
+int yvex_b200_kv_pool_session_close(yvex_b200_kv_pool *pool, unsigned int session);
+int yvex_b200_kv_pool_reserve(yvex_b200_kv_pool *pool, unsigned int session, unsigned int new_rows,
+                              yvex_b200_kv_copy *copy);
+int yvex_b200_kv_pool_commit(yvex_b200_kv_pool *pool, unsigned int session, unsigned int accepted_rows);
+const int *yvex_b200_kv_pool_table(const yvex_b200_kv_pool *pool, unsigned int session);
+unsigned long long yvex_b200_kv_pool_committed(const yvex_b200_kv_pool *pool, unsigned int session);
+unsigned long long yvex_b200_kv_pool_reserved(const yvex_b200_kv_pool *pool, unsigned int session);
+unsigned int yvex_b200_kv_pool_free_blocks(const yvex_b200_kv_pool *pool);
+unsigned int yvex_b200_kv_pool_block_refcount(const yvex_b200_kv_pool *pool, unsigned int block);
 unsigned long long yvex_b200_kv_block_row(const int *block_table,
                                           unsigned long long block_tokens,
                                           unsigned long long row);
