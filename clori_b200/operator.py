@@ -234,6 +234,30 @@ class Backend:
             _raise(err)
         return rc
 
+    def kv_append_rotary(self, key, value, cosines, sines, *, kv_heads, head_dim, rotary_dim, max_kv_tokens,
+                         query=None, query_heads=0, kv_tokens=None, token_position=None, staged=True,
+                         state_values=None, state_positions=None, state_capacity=0, state_row_stride=0,
+                         key_pool=None, value_pool=None, block_table=None, block_tokens=0, check=True):
+        """yvex_b200_kv_append_rotary_execute: key/value [sessions, tokens, kv_heads*head_dim] F32 tensors."""
+        cast = lambda t: C.cast(t.ptr, C.c_void_p) if t is not None else None
+        r = abi.KvAppendRequest()
+        r.session_count, r.token_count = key.shape[0], key.shape[1]
+        r.query_heads, r.key_value_heads, r.head_dimension, r.rotary_dimension = query_heads, kv_heads, head_dim, rotary_dim
+        r.bf16_staged_products = int(staged)
+        r.query, r.key, r.value, r.cosines, r.sines = cast(query), cast(key), cast(value), cast(cosines), cast(sines)
+        r.kv_tokens, r.max_kv_tokens, r.token_position = cast(kv_tokens), max_kv_tokens, cast(token_position)
+        r.state_values, r.state_positions = cast(state_values), cast(state_positions)
+        r.state_capacity, r.state_row_stride = state_capacity, state_row_stride
+        r.key_pool, r.value_pool, r.block_table = cast(key_pool), cast(value_pool), cast(block_table)
+        if block_table is not None:
+            r.block_tokens, r.max_blocks_per_session = block_tokens, block_table.shape[1]
+            r.pool_blocks = key_pool.shape[0]
+        facts, err = abi.OperationFacts(), abi.Error()
+        rc = self.lib.yvex_b200_kv_append_rotary_execute(self.handle, C.byref(r), C.byref(facts), C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc, facts
+
     # -- lifecycle -----------------------------------------------------------
     def bind_stream(self, stream, synchronous=True):
         err = abi.Error()
@@ -273,3 +297,55 @@ class Backend:
 
     def __exit__(self, *exc):
         self.close()
+
+
+class KvPool:
+    """Host-side block bookkeeping of the pooled KV layout (yvex_b200_kv_pool_*)."""
+
+    def __init__(self, blocks, block_tokens, max_sessions, max_blocks_per_session):
+        self.lib = abi.load()
+        self.per = max_blocks_per_session
+        self.handle = self.lib.yvex_b200_kv_pool_create(blocks, block_tokens, max_sessions, max_blocks_per_session)
+        if not self.handle:
+            raise ValueError("bad block pool geometry")
+
+    def _check(self, rc):
+        if rc:
+            raise YvexError(rc, "b200.kv.pool", abi.load().yvex_status_name(rc).decode())
+
+    def open(self):
+        s = C.c_uint()
+        self._check(self.lib.yvex_b200_kv_pool_session_open(self.handle, C.byref(s)))
+        return s.value
+
+    def fork(self, parent):
+        s = C.c_uint()
+        self._check(self.lib.yvex_b200_kv_pool_session_fork(self.handle, parent, C.byref(s)))
+        return s.value
+
+    def close_session(self, session):
+        self._check(self.lib.yvex_b200_kv_pool_session_close(self.handle, session))
+
+    def reserve(self, session, rows):
+        """Returns None, or (source_block, destination_block, rows) to copy for K and V before appending."""
+        copy = abi.KvCopy()
+        self._check(self.lib.yvex_b200_kv_pool_reserve(self.handle, session, rows, C.byref(copy)))
+        return (copy.source_block, copy.destination_block, copy.rows) if copy.needed else None
+
+    def commit(self, session, accepted):
+        self._check(self.lib.yvex_b200_kv_pool_commit(self.handle, session, accepted))
+
+    def table(self, session):
+        row = self.lib.yvex_b200_kv_pool_table(self.handle, session)
+        return np.array([row[i] for i in range(self.per)], np.int32)
+
+    def committed(self, session):
+        return int(self.lib.yvex_b200_kv_pool_committed(self.handle, session))
+
+    def free_blocks(self):
+        return int(self.lib.yvex_b200_kv_pool_free_blocks(self.handle))
+
+    def destroy(self):
+        if self.handle:
+            self.lib.yvex_b200_kv_pool_destroy(self.handle)
+            self.handle = None
