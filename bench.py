@@ -784,7 +784,7 @@ def check_verify_q8(engine, sample, threads):
     k_lane, v_lane, k_scale, v_scale = q8_records.record_offsets()
     blocks = head0.shape[0]
     def dequant(lane, scale):
-        lanes = head0[:, lane.reshape(-1)].reshape(blocks * 64, 128).view(np.int8).astype(np.float32)
+        lanes = (head0[:, lane.reshape(-1)] ^ q8_records.LANE_BIAS).reshape(blocks * 64, 128).view(np.int8).astype(np.float32)
         lo = head0[:, scale.reshape(-1)].astype(np.uint16)
         hi = head0[:, (scale + 1).reshape(-1)].astype(np.uint16)
         d = (lo | (hi << 8)).view(np.float16).astype(np.float32).reshape(blocks * 64, 4)

@@ -54,11 +54,10 @@ __device__ __forceinline__ Q8Session q8_session(const yvx_gqa_problem &p, unsign
     return s;
 }
 
-// Four signed bytes -> two f16x2 registers holding the exact integers.
-// (b ^ 0x80) placed under exponent 0x64 reads as 1024 + (b + 128); minus 1152.
-__device__ __forceinline__ void q8_lanes_to_f16(uint32_t word, uint32_t &lo, uint32_t &hi)
+// Four stored lanes (lane + 128, one byte each) -> two f16x2 registers holding the
+// exact integers: a byte u placed under exponent 0x64 reads as 1024 + u; minus 1152.
+__device__ __forceinline__ void q8_lanes_to_f16(uint32_t biased, uint32_t &lo, uint32_t &hi)
 {
-    const uint32_t biased = word ^ 0x80808080u;
     uint32_t a, b;
     asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(a) : "r"(biased), "r"(0x64646464u));
     asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(b) : "r"(biased), "r"(0x64646464u));
@@ -79,9 +78,8 @@ __device__ __forceinline__ void mma_f16_from(float (&d)[4], const uint32_t (&a)[
 
 // Four signed bytes -> two f16x2 registers holding 1152 + lane (no subtraction):
 // used where the constant is cancelled through the accumulator's initial value.
-__device__ __forceinline__ void q8_lanes_to_f16_biased(uint32_t word, uint32_t &lo, uint32_t &hi)
+__device__ __forceinline__ void q8_lanes_to_f16_biased(uint32_t biased, uint32_t &lo, uint32_t &hi)
 {
-    const uint32_t biased = word ^ 0x80808080u;
     asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(lo) : "r"(biased), "r"(0x64646464u));
     asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(hi) : "r"(biased), "r"(0x64646464u));
 }
@@ -515,12 +513,12 @@ __global__ void q8_kv_pack_kernel(const unsigned char *k_rows, const unsigned ch
         {   // K: fragment order of the QK^T B operand
             const unsigned int nt = t / 8u, g = t % 8u, kg = dim / 64u, ks = (dim % 64u) / 16u;
             const unsigned int e = dim % 16u, c = (e % 8u) / 2u, j = (e % 2u) + 2u * (e / 8u);
-            record[kQ8KLanes + ((nt * 2u + kg) * 32u + g * 4u + c) * 16u + ks * 4u + j] = kb[2u + lane32];
+            record[kQ8KLanes + ((nt * 2u + kg) * 32u + g * 4u + c) * 16u + ks * 4u + j] = kb[2u + lane32] ^ 0x80u;
         }
         {   // V: fragment order of the PV B operand
             const unsigned int w = t / 16u, e = t % 16u, c = (e % 8u) / 2u, j = (e % 2u) + 2u * (e / 8u);
             const unsigned int nd = dim / 8u, g = dim % 8u;
-            record[kQ8VLanes + (((w * 4u + nd / 4u) * 32u + g * 4u + c) * 4u + nd % 4u) * 4u + j] = vb[2u + lane32];
+            record[kQ8VLanes + (((w * 4u + nd / 4u) * 32u + g * 4u + c) * 4u + nd % 4u) * 4u + j] = vb[2u + lane32] ^ 0x80u;
         }
     }
 }

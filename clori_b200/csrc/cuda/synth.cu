@@ -109,7 +109,7 @@ int yvx_cuda_fill_f16_uniform(void *dst, unsigned long long count, unsigned long
 
 namespace yvx {
 
-// Q8 records: int8 lanes uniform in [-127,127] in the lane regions and f16
+// Q8 records: lanes uniform in [-127,127] (stored as lane + 128) in the lane regions and f16
 // scales uniform in [lo, hi) in the scale regions of every 17408-byte record.
 __global__ void fill_q8_records_kernel(unsigned char *records, unsigned long long record_count,
                                        unsigned long long seed, float lo, float hi)
@@ -131,7 +131,7 @@ __global__ void fill_q8_records_kernel(unsigned char *records, unsigned long lon
                     again = splitmix64(again + j + 1);
                     byte = (uint32_t)again & 0xffu;
                 }
-                word |= ((uint32_t)((int)byte - 127) & 0xffu) << (8 * j);
+                word |= ((byte + 1u) & 0xffu) << (8 * j);  // (byte - 127) + 128
             }
         } else {
             const float u0 = (float)(uint32_t)(h >> 32) * (1.0f / 4294967296.0f);

@@ -1,7 +1,9 @@
 """Host-side description of the Q8 KV record (see include/yvex_b200/cuda_shim.h).
 
 `record_offsets()` gives, for every (token, dim) of a 64-token x 128-dim head
-block, where its int8 lane and its f16 scale live inside the 17408-byte record.
+block, where its lane and its f16 scale live inside the 17408-byte record. A lane
+is stored as one byte holding int8 + 128 (the GGUF byte with its top bit flipped),
+which is the form the kernel's byte-to-f16 placement wants.
 It is the layout's definition in executable form: tests check the device pack
 kernel against it byte for byte, and callers can use it to append or inspect
 tokens without the library.
@@ -10,6 +12,7 @@ import numpy as np
 
 RECORD_BYTES = 17408
 K_LANES, V_LANES, K_SCALES, V_SCALES = 0, 8192, 16384, 16896
+LANE_BIAS = np.uint8(0x80)   # stored byte = GGUF int8 byte ^ 0x80 = int8 + 128
 
 
 def record_offsets():
@@ -27,7 +30,7 @@ def record_offsets():
 
 def pack_records(k_rows, v_rows, kv_heads, block_ids=None, pool_blocks=None):
     """GGUF Q8_0 rows uint8 [tokens, kv_heads*4*34] -> records uint8
-    [pool_blocks, kv_heads, 17408]; unused slots are zero."""
+    [pool_blocks, kv_heads, 17408]; unused slots are zero bytes."""
     tokens = k_rows.shape[0]
     blocks = (tokens + 63) // 64
     if block_ids is None:
@@ -42,8 +45,8 @@ def pack_records(k_rows, v_rows, kv_heads, block_ids=None, pool_blocks=None):
         n = hi - lo
         for h in range(kv_heads):
             rec = out[block_ids[j], h]
-            rec[k_lane[:n].reshape(-1)] = kb[lo:hi, h, :, 2:].reshape(n, 128).reshape(-1)
-            rec[v_lane[:n].reshape(-1)] = vb[lo:hi, h, :, 2:].reshape(n, 128).reshape(-1)
+            rec[k_lane[:n].reshape(-1)] = kb[lo:hi, h, :, 2:].reshape(n, 128).reshape(-1) ^ LANE_BIAS
+            rec[v_lane[:n].reshape(-1)] = vb[lo:hi, h, :, 2:].reshape(n, 128).reshape(-1) ^ LANE_BIAS
             for byte in range(2):
                 rec[(k_scale[:n] + byte).reshape(-1)] = kb[lo:hi, h, :, byte].reshape(-1)
                 rec[(v_scale[:n] + byte).reshape(-1)] = vb[lo:hi, h, :, byte].reshape(-1)

@@ -97,7 +97,8 @@ typedef struct yvx_gqa_problem {
     unsigned int query_start_from_end; /* 1: query_start = kv length - query_rows */
     unsigned int kv_position_base;   /* absolute position of local KV token 0 */
 
-    unsigned int chunk_tokens;       /* KV tokens per split; multiple of 64 */
+    unsigned int chunk_tokens;       /* KV tokens per split: a multiple of 64 (the short F32
+                                        decode plan uses multiples of 16, at most 112) */
     unsigned int max_splits;         /* ceil(kv_tokens_max / chunk_tokens) */
     float *partials;                 /* scratch [session][row][qhead][split][head_dim+2] */
     float *partial_output;           /* non-NULL: emit (o, m, l) per (session,row,qhead)
@@ -282,7 +283,9 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *problem, void *stream, void *even
  * No counterpart in the reference (its KV state is F32; Q8_0 exists there as a
  * weight qtype only: src/gguf/quant_block.c:160-187,819-832). A record is the
  * Q8_0 data of 64 tokens of one KV head (head_dim 128) as 17408 contiguous
- * bytes, a byte permutation of the tokens' GGUF Q8_0 rows:
+ * bytes, a byte permutation of the tokens' GGUF Q8_0 rows in which every lane byte
+ * has its top bit flipped (a stored lane is int8 + 128, the operand form of the
+ * kernel's byte-to-f16 placement; scales are the GGUF f16 bits unchanged):
  *   [K lanes 8192][V lanes 8192][K scales 512][V scales 512]
  * K lane of (token t, dim d): ((t/8*2 + d/64)*32 + (t%8)*4 + (d%16%8)/2)*16
  *                              + (d%64/16)*4 + (d%2) + 2*(d%16/8)

@@ -140,11 +140,11 @@ def test_q8_verify_at_full_size(backend):
     lib.yvx_cuda_fill_q8_records(records, blocks * hkv, 201, 0.002, 0.02, s)
     planned, fine = run(0), run(1024)
     assert np.isfinite(planned).all() and np.abs(planned - fine).max() <= 1e-5
-    # every byte 0x2C: lanes 44, scales f16 0x2C2C -> every K row equal, every value 44 * scale
+    # every byte 0x2C: stored lanes 0x2C = 44 - 128, scales f16 0x2C2C -> every K row equal, every value -84 * scale
     lib.yvx_cuda_memset_async(records, 0x2C, pool_bytes, s)
     scale = float(np.array([0x2C2C], np.uint16).view(np.float16)[0])
     flat = run(0)
-    assert np.abs(flat - 44.0 * scale).max() <= 44.0 * scale * 2.0 ** -9
+    assert np.abs(flat - (-84.0) * scale).max() <= 84.0 * scale * 2.0 ** -9
     st = _download(lib, s, status, np.zeros(1, np.int32))
     assert st[0] == 0
     for ptr in (records, q, out, status):

@@ -28,7 +28,7 @@ def test_pack_round_trips_through_the_offsets(oracle):
     for token in (0, 63, 64, 149):
         rec = records[table[token // 64], 1]
         t = token % 64
-        assert np.array_equal(rec[k_lane[t]], kb[token, 1, :, 2:].reshape(128))
+        assert np.array_equal(rec[k_lane[t]], kb[token, 1, :, 2:].reshape(128) ^ q8_records.LANE_BIAS)  # int8 + 128
         assert np.array_equal(rec[k_scale[t]], kb[token, 1, :, 0])
     assert not records[1].any()                      # pool block 1 is not in the table
     assert not records[3, 0][k_lane[22:].ravel()].any()  # slots beyond token 149 stay zero
