@@ -155,6 +155,12 @@ class LatentReduceArgs(C.Structure):
     ]
 
 
+class LseExchange(C.Structure):
+    """yvx_lse_exchange (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [("ranks", C.c_uint), ("rank", C.c_uint), ("epoch", C.c_uint),
+                ("gather", C.c_void_p), ("arrivals", C.c_void_p)]
+
+
 class KvCopy(C.Structure):
     """yvex_b200_kv_copy (include/yvex_b200/attention.h)."""
     _fields_ = [("needed", C.c_int), ("source_block", C.c_int), ("destination_block", C.c_int),
@@ -269,6 +275,8 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_copy_async", "yvx_cuda_stream_create", "yvx_cuda_stream_destroy",
     "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
+    "yvx_cuda_lse_exchange_bytes", "yvx_cuda_lse_exchange_counter_offset", "yvx_cuda_gqa_attention_exchange",
+    "yvx_cuda_lse_exchange_emulated", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
     "yvx_cuda_graph_capture_begin", "yvx_cuda_graph_capture_end", "yvx_cuda_graph_launch", "yvx_cuda_graph_destroy",
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
@@ -367,6 +375,15 @@ def load():
     lib.yvx_cuda_event_create.argtypes = [P(vp)]
     lib.yvx_cuda_event_destroy.argtypes = [vp]
     lib.yvx_cuda_event_record.argtypes = [vp, vp]
+    lib.yvx_cuda_lse_exchange_bytes.restype = u64
+    lib.yvx_cuda_lse_exchange_bytes.argtypes = [C.c_uint, C.c_uint, C.c_uint]
+    lib.yvx_cuda_lse_exchange_counter_offset.restype = u64
+    lib.yvx_cuda_lse_exchange_counter_offset.argtypes = [C.c_uint, C.c_uint, C.c_uint]
+    lib.yvx_cuda_gqa_attention_exchange.argtypes = [P(GqaProblem), P(LseExchange), vp, P(C.c_uint)]
+    lib.yvx_cuda_lse_exchange_emulated.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, vp, C.c_uint, vp, vp, vp]
+    lib.yvx_cuda_ipc_export.argtypes = [vp, vp]
+    lib.yvx_cuda_ipc_open.argtypes = [vp, P(vp)]
+    lib.yvx_cuda_ipc_close.argtypes = [vp]
     lib.yvx_cuda_graph_capture_begin.argtypes = [vp]
     lib.yvx_cuda_graph_capture_end.argtypes = [vp, P(vp)]
     lib.yvx_cuda_graph_launch.argtypes = [vp, vp]

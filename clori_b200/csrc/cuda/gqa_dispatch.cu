@@ -10,6 +10,7 @@ int gqa_decode_f32_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+int lse_exchange_launch(const yvx_gqa_problem &p, const yvx_lse_exchange &x, cudaStream_t stream);
 }
 
 extern "C" {
@@ -66,7 +67,7 @@ unsigned long long yvx_cuda_gqa_partials_bytes(const yvx_gqa_problem *p)
 }
 
 static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *events,
-                      unsigned int *launches)
+                      unsigned int *launches, const yvx_lse_exchange *exchange = nullptr)
 {
     unsigned int count = 0;
     if (launches) *launches = 0;
@@ -96,7 +97,13 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     if (rc != 0) return rc;
     count = 1u;
     if (events) cudaEventRecord(events[1], s);
-    if (p->max_splits > 1u && !final_output) {
+    if (exchange) {
+        // the fold of this rank's splits happens inside the exchange kernel
+        if (final_output || !p->partial_output) return YVEX_ERR_UNSUPPORTED;
+        rc = yvx::lse_exchange_launch(*p, *exchange, s);
+        if (rc != 0) return rc;
+        count = 2u;
+    } else if (p->max_splits > 1u && !final_output) {
         rc = yvx::gqa_combine_launch(*p, s);
         if (rc != 0) return rc;
         count = 2u;
@@ -109,6 +116,25 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
 int yvx_cuda_gqa_attention(const yvx_gqa_problem *p, void *stream, unsigned int *launches)
 {
     return gqa_launch(p, stream, nullptr, launches);
+}
+
+int yvx_cuda_gqa_attention_exchange(const yvx_gqa_problem *p, const yvx_lse_exchange *exchange,
+                                    void *stream, unsigned int *launches)
+{
+    if (!exchange) return YVEX_ERR_INVALID_ARG;
+    return gqa_launch(p, stream, nullptr, launches, exchange);
+}
+
+unsigned long long yvx_cuda_lse_exchange_counter_offset(unsigned int ranks, unsigned int items,
+                                                        unsigned int head_dim)
+{
+    const unsigned long long bytes = 2ull * ranks * items * (head_dim + 2ull) * sizeof(float);
+    return (bytes + 255ull) & ~255ull;
+}
+
+unsigned long long yvx_cuda_lse_exchange_bytes(unsigned int ranks, unsigned int items, unsigned int head_dim)
+{
+    return yvx_cuda_lse_exchange_counter_offset(ranks, items, head_dim) + (unsigned long long)items * 4ull;
 }
 
 int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *p, void *stream, void *events[3],

@@ -171,6 +171,32 @@ int yvx_cuda_graph_destroy(void *executable)
     return 0;
 }
 
+int yvx_cuda_ipc_export(void *device_pointer, void *handle_64_bytes)
+{
+    cudaIpcMemHandle_t handle;
+    static_assert(sizeof(handle) == 64, "IPC handle size");
+    if (!device_pointer || !handle_64_bytes) return YVEX_ERR_INVALID_ARG;
+    YVX_CUDA_TRY(cudaIpcGetMemHandle(&handle, device_pointer));
+    memcpy(handle_64_bytes, &handle, sizeof(handle));
+    return 0;
+}
+
+int yvx_cuda_ipc_open(const void *handle_64_bytes, void **device_pointer)
+{
+    cudaIpcMemHandle_t handle;
+    if (!device_pointer || !handle_64_bytes) return YVEX_ERR_INVALID_ARG;
+    memcpy(&handle, handle_64_bytes, sizeof(handle));
+    YVX_CUDA_TRY(cudaIpcOpenMemHandle(device_pointer, handle, cudaIpcMemLazyEnablePeerAccess));
+    return 0;
+}
+
+int yvx_cuda_ipc_close(void *device_pointer)
+{
+    if (!device_pointer) return 0;
+    YVX_CUDA_TRY(cudaIpcCloseMemHandle(device_pointer));
+    return 0;
+}
+
 int yvx_cuda_event_create(void **event)
 {
     cudaEvent_t created;

@@ -127,6 +127,43 @@ int yvx_cuda_gqa_attention(const yvx_gqa_problem *problem, void *stream,
 int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *problem, void *stream,
                                     void *events[3], unsigned int *launches);
 
+/* ---- split attention + cross-GPU fold over NVLink peer memory -------------------
+ * For one session whose KV sequence is sharded over `ranks` GPUs (one process per
+ * GPU): the attention kernel, then ONE kernel that folds this rank's splits, stores
+ * the resulting (o, m, l) row of every item into every rank's exchange area with
+ * peer stores, counts arrivals, waits (bounded, status 3 on expiry) for the rows of
+ * all ranks and folds them in rank order into `problem->output`. No reference
+ * counterpart (the reference is single-device); it replaces the sequence local
+ * combine -> NCCL all-gather -> yvx_cuda_lse_combine_strided.
+ * Each rank allocates an area of yvx_cuda_lse_exchange_bytes(ranks, items, head_dim)
+ * bytes: [2][ranks][items][head_dim + 2] floats followed by [items] 32-bit arrival
+ * counters, zero-filled once; exports it with yvx_cuda_ipc_export, opens its peers'
+ * handles with yvx_cuda_ipc_open, and passes device arrays of the `ranks` area
+ * pointers and counter pointers (own entries are the local addresses). `epoch`
+ * counts calls from 1 and must be the same on every rank for the same step.
+ * problem->partial_output (a local [items][head_dim + 2] row buffer) must be set. */
+typedef struct yvx_lse_exchange {
+    unsigned int ranks, rank, epoch;
+    float *const *gather;            /* device array [ranks]: base of rank r's area */
+    unsigned int *const *arrivals;   /* device array [ranks]: rank r's arrival counters */
+} yvx_lse_exchange;
+unsigned long long yvx_cuda_lse_exchange_bytes(unsigned int ranks, unsigned int items, unsigned int head_dim);
+unsigned long long yvx_cuda_lse_exchange_counter_offset(unsigned int ranks, unsigned int items,
+                                                        unsigned int head_dim);
+int yvx_cuda_gqa_attention_exchange(const yvx_gqa_problem *problem, const yvx_lse_exchange *exchange,
+                                    void *stream, unsigned int *launches);
+/* The same exchange with every rank played by one cooperative launch on one GPU
+ * (rows[rank][item][head_dim + 2] in, output[rank][item][head_dim] out): for tests. */
+int yvx_cuda_lse_exchange_emulated(const float *rows, unsigned int ranks, unsigned int items,
+                                   unsigned int head_dim, float *const *gather,
+                                   unsigned int *const *arrivals, unsigned int epoch, float *output,
+                                   int *status, void *stream);
+/* CUDA IPC for the exchange areas: a 64-byte handle of a yvx_cuda_malloc allocation,
+ * and the mapping of a peer's handle into this process (peer access is enabled). */
+int yvx_cuda_ipc_export(void *device_pointer, void *handle_64_bytes);
+int yvx_cuda_ipc_open(const void *handle_64_bytes, void **device_pointer);
+int yvx_cuda_ipc_close(void *device_pointer);
+
 /* The same attention for callers that cannot allocate device memory on this
  * path (a host that gave the whole GPU to its own pool, a latency-critical step
  * that cannot afford an allocation's synchronisation, a plug-in handed only its
