@@ -258,6 +258,23 @@ class Backend:
             _raise(err)
         return rc, facts
 
+    def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, output, *, max_kv_tokens, scale,
+                   kv_tokens=None, check=True):
+        """yvex_b200_mla_decode_execute: bf16 tensors [sessions, 128, 128 | 64], [128, 128, 512],
+        caches [sessions, capacity, 512 | 64]; output F32 [sessions, 128, 512]."""
+        cast = lambda t: C.cast(t.ptr, C.c_void_p) if t is not None else None
+        r = abi.MlaDecodeRequest()
+        r.session_count, r.heads, r.nope_dimension = q_nope.shape[0], q_nope.shape[1], q_nope.shape[2]
+        r.latent_dimension, r.rope_dimension = latent.shape[2], rope_key.shape[2]
+        r.context_capacity, r.max_kv_tokens, r.scale = latent.shape[1], max_kv_tokens, scale
+        r.q_nope, r.q_rope, r.w_uk = cast(q_nope), cast(q_rope), cast(w_uk)
+        r.latent, r.rope_key, r.kv_tokens, r.output = cast(latent), cast(rope_key), cast(kv_tokens), cast(output)
+        facts, err = abi.OperationFacts(), abi.Error()
+        rc = self.lib.yvex_b200_mla_decode_execute(self.handle, C.byref(r), C.byref(facts), C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc, facts
+
     # -- lifecycle -----------------------------------------------------------
     def bind_stream(self, stream, synchronous=True):
         err = abi.Error()
