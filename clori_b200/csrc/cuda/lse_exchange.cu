@@ -50,11 +50,13 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
         for (unsigned int d = threadIdx.x; d < stride; d += kExchangeThreads) dst[d] = row[d];
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        // One system-wide fence after the barrier orders every thread's peer stores
-        // (they happen before it through the barrier) ahead of the arrival counts.
+    // Thread r tells rank r. Its system-wide fence after the barrier orders every
+    // thread's peer stores (they happen before it through the barrier) ahead of the count.
+    if (threadIdx.x < x.ranks) {
         __threadfence_system();
-        for (unsigned int r = 0; r < x.ranks; ++r) atomicAdd_system(x.arrivals[r] + item, 1u);
+        atomicAdd_system(x.arrivals[threadIdx.x] + item, 1u);
+    }
+    if (threadIdx.x == 0) {
         // 3. bounded wait for the rows of all ranks
         const volatile unsigned int *counter = x.arrivals[rank] + item;
         const unsigned int target = x.epoch * x.ranks;
