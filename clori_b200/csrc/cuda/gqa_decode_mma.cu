@@ -191,12 +191,10 @@ gqa_decode_mma_kernel(const yvx_gqa_problem p, const __grid_constant__ DecodeMap
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[n][e] = 0.0f;
 
-    bool aborted = false;
     for (unsigned int i = 0; i < tiles; ++i) {
         const unsigned int stage = i % kDecodeStages;
         if (!mbar_wait(&full[stage], (i / kDecodeStages) & 1u)) {
             atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
-            aborted = true;
             break;
         }
         const uint32_t k_base = smem_u32(stages + stage * kStageBytes);
@@ -307,7 +305,6 @@ gqa_decode_mma_kernel(const yvx_gqa_problem p, const __grid_constant__ DecodeMap
         if (tile_token + 16u > s.kv_tokens) fence_proxy_async();
         if (lane == 0) mbar_arrive(&empty[stage]);
     }
-    (void)aborted;
 
     // ---- merge the four warps and publish ---------------------------------
 #pragma unroll
