@@ -115,7 +115,8 @@ typedef struct yvx_gqa_problem {
 /* Scratch bytes `partials` must hold for a problem (0 when one split suffices). */
 unsigned long long yvx_cuda_gqa_partials_bytes(const yvx_gqa_problem *problem);
 /* Picks chunk_tokens/max_splits for a device with `sm_count` SMs. Deterministic
- * in the problem's shape only. */
+ * in the problem's shape, dtypes, layout flags and pointer alignment only; call it
+ * after every other field is set (short F32 decode shapes get their own plan). */
 void yvx_cuda_gqa_plan_splits(yvx_gqa_problem *problem, int sm_count);
 /* Launches the attention (1 launch) and, when max_splits > 1, the combine
  * (1 more). `launches` receives the number of kernels enqueued. */
