@@ -21,6 +21,13 @@ namespace yvx {
 constexpr int kExchangeThreads = kCombineWarps * 32;
 constexpr unsigned int kExchangeSpinLimit = 1u << 23;  // about a second of 100 ns polls, then status 3
 
+// Release / acquire at system scope (peers are other GPUs); lighter than the
+// sequentially consistent fence and all this protocol needs.
+__device__ __forceinline__ void fence_acq_rel_system()
+{
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(kExchangeThreads)
 lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const unsigned int items,
                     const int emulated)
@@ -53,7 +60,7 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
     // Thread r tells rank r. Its system-wide fence after the barrier orders every
     // thread's peer stores (they happen before it through the barrier) ahead of the count.
     if (threadIdx.x < x.ranks) {
-        __threadfence_system();
+        fence_acq_rel_system();
         atomicAdd_system(x.arrivals[threadIdx.x] + item, 1u);
     }
     if (threadIdx.x == 0) {
@@ -68,6 +75,9 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
             }
             __nanosleep(100);
         }
+        // Acquire side: this fence, then the barrier, order every thread's reads of the
+        // peers' rows after the observation of the counter.
+        fence_acq_rel_system();
         arrived = ok;
     }
     __syncthreads();
@@ -75,21 +85,34 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
         if (threadIdx.x == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
         return;
     }
-    __threadfence_system();
-    // 4. fold the ranks' rows in rank order; peers wrote them, so bypass L1
+    // 4. fold the ranks' rows in rank order; peers wrote them, so bypass L1. All loads
+    // of up to eight ranks are issued before the first use (one trip to L2 per batch).
     const float *base = x.gather[rank] + ((unsigned long long)(x.epoch & 1u) * x.ranks * items + item) * stride;
     const unsigned long long rank_stride = (unsigned long long)items * stride;
-    float mm = -INFINITY;
-    for (unsigned int r = 0; r < x.ranks; ++r) mm = fmaxf(mm, __ldcg(base + r * rank_stride + hd));
     for (unsigned int d = threadIdx.x; d < hd; d += kExchangeThreads) {
-        float ll = 0.0f, o = 0.0f;
-        for (unsigned int r = 0; r < x.ranks; ++r) {
-            const float mr = __ldcg(base + r * rank_stride + hd);
-            const float weight = mr == -INFINITY ? 0.0f : __ldcg(base + r * rank_stride + hd + 1u) * expf(mr - mm);
-            ll += weight;
-            o = fmaf(__ldcg(base + r * rank_stride + d), weight, o);
+        float run_max = -INFINITY, run_sum = 0.0f, acc = 0.0f;
+        for (unsigned int r0 = 0; r0 < x.ranks; r0 += 8u) {
+            float mr[8], lr[8], orow[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool live = r0 + u < x.ranks;
+                const float *part = base + (unsigned long long)(live ? r0 + u : r0) * rank_stride;
+                mr[u] = live ? __ldcg(part + hd) : -INFINITY;
+                lr[u] = __ldcg(part + hd + 1u);
+                orow[u] = __ldcg(part + d);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (mr[u] == -INFINITY) continue;  // empty shard or past the last rank
+                const float new_max = fmaxf(run_max, mr[u]);
+                const float keep = expf(run_max - new_max);
+                const float weight = lr[u] * expf(mr[u] - new_max);
+                run_sum = fmaf(run_sum, keep, weight);
+                acc = fmaf(acc, keep, orow[u] * weight);
+                run_max = new_max;
+            }
         }
-        const float value = o / ll;
+        const float value = acc / run_sum;
         if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
         store_output(emulated ? (void *)((float *)p.output + (unsigned long long)rank * items * hd) : p.output,
                      p.output_dtype, (unsigned long long)item * hd + d, value);
