@@ -141,8 +141,8 @@ class GqaProblem(C.Structure):
 
 
 class LatentReduceArgs(C.Structure):
-    """yvx_latent_reduce_args (include/yvex_b200/cuda_shim.h); the first 19 fields are
-    also the layout of the CPU checker's argument struct."""
+    """yvx_latent_reduce_args (include/yvex_b200/cuda_shim.h); the CPU checker's argument
+    struct has the same layout."""
     _fields_ = [
         ("query", C.c_void_p), ("local", C.c_void_p), ("local_positions", C.c_void_p),
         ("initial_local_count", u64), ("local_stride", u64),
@@ -152,6 +152,7 @@ class LatentReduceArgs(C.Structure):
         ("ratio", u64), ("attention_class", C.c_uint), ("phase_start_position", u64),
         ("token_count", u64), ("candidate_block_visible", C.c_int),
         ("out", C.c_void_p), ("status", C.c_void_p),
+        ("rope_dims", u64), ("rope_frequency", C.c_void_p),
     ]
 
 

@@ -20,6 +20,31 @@ _u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _u64 = C.c_ulonglong
+_u64p = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
+_f64p = np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")
+
+
+class PositionPolicy(C.Structure):
+    """yvx_oracle_position_policy."""
+    _fields_ = [(name, _u64) for name in ("theta", "scaling_factor", "original_context", "beta_fast", "beta_slow")]
+
+
+class Indexer(C.Structure):
+    """yvx_oracle_indexer (host pointers)."""
+    _fields_ = [("keys", C.c_void_p), ("positions", C.c_void_p), ("rows", _u64), ("key_stride", _u64),
+                ("query", C.c_void_p), ("weights", C.c_void_p), ("heads", _u64), ("head_dim", _u64),
+                ("topk", _u64), ("ratio", _u64)]
+
+
+def indexer_struct(keys, positions, query, weights, heads, head_dim, topk, ratio):
+    """The arrays must stay alive while the struct is in use; they are attached to it."""
+    ix = Indexer()
+    ix.arrays = [np.ascontiguousarray(keys, np.float32), np.ascontiguousarray(positions, np.uint64),
+                 np.ascontiguousarray(query, np.float32), np.ascontiguousarray(weights, np.float32)]
+    ix.keys, ix.positions, ix.query, ix.weights = (a.ctypes.data for a in ix.arrays)
+    ix.rows, ix.key_stride = ix.arrays[0].shape
+    ix.heads, ix.head_dim, ix.topk, ix.ratio = heads, head_dim, topk, ratio
+    return ix
 
 
 def build_oracle(reference_tree="/root/reference"):
@@ -169,6 +194,37 @@ class Oracle(_Gqa):
         assert ok == 1
         return cos, sin
 
+    def rope_frequencies(self, policy, rope_dims):
+        out = np.zeros(rope_dims // 2, np.float64)
+        self.lib.yvx_oracle_rope_frequencies.argtypes = [C.c_void_p, _u64, _f64p]
+        assert self.lib.yvx_oracle_rope_frequencies(C.addressof(policy), rope_dims, out) == 1
+        return out
+
+    def rope_apply(self, values, rope_dims, position, frequency, inverse):
+        out = np.ascontiguousarray(values, np.float32).copy()
+        self.lib.yvx_oracle_rope_apply.argtypes = [_f32p, _u64, _u64, _u64, _f64p, C.c_int]
+        ok = self.lib.yvx_oracle_rope_apply(out, out.size, rope_dims, position,
+                                            np.ascontiguousarray(frequency, np.float64), int(inverse))
+        return out if ok == 1 else None
+
+    def topk_select(self, scores, ordinals, k):
+        scores = np.ascontiguousarray(scores, np.float32)
+        ordinals = np.ascontiguousarray(ordinals, np.uint64)
+        out, n = np.zeros(max(len(scores), 1), np.uint64), _u64()
+        self.lib.yvx_oracle_topk_select.argtypes = [_f32p, _u64p, _u64, _u64, _u64p, C.POINTER(_u64)]
+        ok = self.lib.yvx_oracle_topk_select(scores, ordinals, len(scores), k, out, C.byref(n))
+        return out[:n.value].copy() if ok == 1 else None
+
+    def csa_select(self, indexer, token, query_position):
+        """-> (selected row indices in ranked order, valid candidate count, float score per row)."""
+        out, n, valid = np.zeros(max(indexer.rows, 1), np.uint64), _u64(), _u64()
+        scores = np.zeros(max(indexer.rows, 1), np.float32)
+        self.lib.yvx_oracle_csa_select.argtypes = [C.c_void_p, _u64, _u64, _u64p, C.POINTER(_u64),
+                                                   C.POINTER(_u64), _f32p]
+        ok = self.lib.yvx_oracle_csa_select(C.addressof(indexer), token, query_position, out, C.byref(n),
+                                            C.byref(valid), scores)
+        return (out[:n.value].copy(), valid.value, scores[:indexer.rows]) if ok == 1 else None
+
     def exp(self, x):
         return float(self.lib.yvx_oracle_exp(float(x)))
 
@@ -273,6 +329,42 @@ class Reference(_Gqa):
             raise FileNotFoundError(REF_SO)
         self.lib = C.CDLL(REF_SO)
         self._bind_common()
+
+    def rope_apply(self, values, rope_dims, position, policy, inverse):
+        out = np.ascontiguousarray(values, np.float32).copy()
+        self.lib.yvx_ref_rope_apply.argtypes = [_f32p, _u64, _u64, _u64, C.c_void_p, C.c_int]
+        ok = self.lib.yvx_ref_rope_apply(out, out.size, rope_dims, position, C.addressof(policy), int(inverse))
+        return out if ok == 1 else None
+
+    def topk_select(self, scores, ordinals, k):
+        scores = np.ascontiguousarray(scores, np.float32)
+        ordinals = np.ascontiguousarray(ordinals, np.uint64)
+        out, n = np.zeros(max(len(scores), 1), np.uint64), _u64()
+        self.lib.yvx_ref_topk_select.argtypes = [_f32p, _u64p, _u64, _u64, _u64p, C.POINTER(_u64)]
+        ok = self.lib.yvx_ref_topk_select(scores, ordinals, len(scores), k, out, C.byref(n))
+        return out[:n.value].copy() if ok == 1 else None
+
+    def csa_select(self, indexer, token, query_position):
+        out, n, valid = np.zeros(max(indexer.rows, 1), np.uint64), _u64(), _u64()
+        self.lib.yvx_ref_csa_select.argtypes = [C.c_void_p, _u64, _u64, _u64p, C.POINTER(_u64), C.POINTER(_u64)]
+        ok = self.lib.yvx_ref_csa_select(C.addressof(indexer), token, query_position, out, C.byref(n),
+                                         C.byref(valid))
+        return (out[:n.value].copy(), valid.value) if ok == 1 else None
+
+    def latent_reduce_chunk(self, args_struct, compressed_rows, policy, indexer, tokens, heads, head_dim):
+        """The reference's whole CPU reduce of a phase (selection, two passes, publication,
+        inverse rotation, publication) -> (out [tokens, heads*head_dim], per-token selected
+        counts, per-token selected positions) or None when the reference refuses."""
+        out = np.zeros((tokens, heads * head_dim), np.float32)
+        topk = int(indexer.topk) if indexer is not None else 1
+        counts, positions = np.zeros(tokens, np.uint64), np.zeros((tokens, topk), np.uint64)
+        self.lib.yvx_ref_latent_reduce_chunk.argtypes = [C.c_void_p, _u64, C.c_void_p, C.c_void_p, _f32p,
+                                                         _u64p, _u64p]
+        ok = self.lib.yvx_ref_latent_reduce_chunk(
+            C.addressof(args_struct), compressed_rows, C.addressof(policy),
+            C.addressof(indexer) if indexer is not None else None, out.reshape(-1),
+            counts, positions.reshape(-1))
+        return (out, counts, positions) if ok == 1 else None
 
 
 def reference_available():

@@ -244,3 +244,143 @@ int yvx_ref_gqa_attention(const float *query, const float *key, const float *val
         if (jobs[t].status != YVEX_OK) status = jobs[t].status;
     return status;
 }
+
+/* ---- graph-level latent attention: reduce, index selection, top-k, rotation ----
+ * Flat entry points over the reference's CPU functions in src/graph/core.c,
+ * attention.c and numeric.c. The structs come from the checker's header so one
+ * set of Python structures serves both libraries; every number is computed by
+ * the reference. */
+/* the header the reference's own focused tests include for these functions */
+#include <src/graph/private.h>
+#include "yvx_oracle.h"
+
+static void ref_position(const yvx_oracle_position_policy *policy, unsigned long long rope_dims,
+                         yvex_attention_position_policy *out)
+{
+    memset(out, 0, sizeof(*out));
+    out->rope_dimension = rope_dims;
+    out->theta = policy->theta;
+    out->scaling_factor = policy->scaling_factor;
+    out->original_context = policy->original_context;
+    out->beta_fast = policy->beta_fast;
+    out->beta_slow = policy->beta_slow;
+    out->partial_rope = 1;
+    out->inverse_output_rotation = 1;
+}
+
+int yvx_ref_rope_apply(float *values, unsigned long long count, unsigned long long rope_dims,
+                       unsigned long long token_position,
+                       const yvx_oracle_position_policy *policy, int inverse)
+{
+    yvex_attention_position_policy position;
+    ref_position(policy, rope_dims, &position);
+    return yvex_attention_rope_apply(values, count, rope_dims, token_position, &position, inverse);
+}
+
+int yvx_ref_topk_select(const float *scores, const unsigned long long *ordinals,
+                        unsigned long long count, unsigned long long k,
+                        unsigned long long *selected, unsigned long long *selected_count)
+{
+    yvex_attention_scratch_budget scratch;
+    yvex_attention_failure failure;
+    yvex_error err;
+    memset(&scratch, 0, sizeof(scratch));
+    memset(&failure, 0, sizeof(failure));
+    return yvex_attention_topk_select(scores, ordinals, count, k, selected, selected_count,
+                                      &scratch, &failure, &err) == YVEX_OK;
+}
+
+static void ref_indexer_layer(const yvx_oracle_indexer *indexer, yvex_attention_layer_plan *layer,
+                              yvex_attention_history_view *history)
+{
+    layer->attention_class = YVEX_ATTENTION_CLASS_CSA;
+    layer->compression_ratio = indexer->ratio;
+    layer->indexer_required = 1;
+    layer->indexer_heads = indexer->heads;
+    layer->indexer_head_dimension = indexer->head_dim;
+    layer->indexer_topk = indexer->topk;
+    layer->sparse_topk.required = 1;
+    layer->sparse_topk.k = indexer->topk;
+    history->indexer_entry_count = indexer->rows;
+    history->indexer_kv = indexer->keys;
+    history->indexer_kv_stride = indexer->key_stride;
+    history->indexer_positions = indexer->positions;
+}
+
+int yvx_ref_csa_select(const yvx_oracle_indexer *indexer, unsigned long long token,
+                       unsigned long long query_position, unsigned long long *selected,
+                       unsigned long long *selected_count, unsigned long long *valid_count)
+{
+    yvex_attention_layer_plan layer;
+    yvex_attention_history_view history;
+    yvex_attention_scratch_budget scratch;
+    yvex_attention_failure failure;
+    yvex_error err;
+    memset(&layer, 0, sizeof(layer));
+    memset(&history, 0, sizeof(history));
+    memset(&scratch, 0, sizeof(scratch));
+    memset(&failure, 0, sizeof(failure));
+    ref_indexer_layer(indexer, &layer, &history);
+    return yvex_attention_csa_select(&layer, &history, NULL, 0ull, 0ull, NULL,
+                                     indexer->query + token * indexer->heads * indexer->head_dim,
+                                     indexer->weights + token * indexer->heads, query_position,
+                                     selected, selected_count, valid_count, &scratch, &failure,
+                                     &err) == YVEX_OK;
+}
+
+/* The whole CPU reduce of a phase: selection (class 1), both passes, the bf16
+ * publication, the inverse output rotation and the second publication. Every
+ * row is handed over as history except the phase's own local rows.
+ * trace_counts / trace_positions (class 1, may be NULL): per token the number of
+ * selected rows and their positions in ranked order, [token][indexer->topk]. */
+int yvx_ref_latent_reduce_chunk(const yvx_oracle_latent_args *a,
+                                unsigned long long compressed_rows,
+                                const yvx_oracle_position_policy *policy,
+                                const yvx_oracle_indexer *indexer, float *out,
+                                unsigned long long *trace_counts,
+                                unsigned long long *trace_positions)
+{
+    yvex_attention_layer_plan layer;
+    yvex_attention_history_view history;
+    yvex_attention_scratch_budget scratch;
+    yvex_attention_failure failure;
+    yvex_attention_cpu_result result;
+    yvex_error err;
+    memset(&layer, 0, sizeof(layer));
+    memset(&history, 0, sizeof(history));
+    memset(&scratch, 0, sizeof(scratch));
+    memset(&failure, 0, sizeof(failure));
+    memset(&result, 0, sizeof(result));
+    if (a->attention_class == 1u) {
+        if (!indexer || indexer->rows != compressed_rows) return 0;
+        ref_indexer_layer(indexer, &layer, &history);
+    }
+    layer.attention_class = a->attention_class == 0u   ? YVEX_ATTENTION_CLASS_SWA
+                            : a->attention_class == 1u ? YVEX_ATTENTION_CLASS_CSA
+                                                       : YVEX_ATTENTION_CLASS_HCA;
+    layer.compression_ratio = a->ratio;
+    layer.sliding_window = a->sliding_window;
+    layer.query_heads = a->query_heads;
+    layer.kv_heads = 1ull;
+    layer.head_dimension = a->head_dim;
+    layer.rope_head_dimension = a->rope_dims;
+    layer.compute_contract = YVEX_ATTENTION_COMPUTE_BF16_F32_RNE_V1;
+    ref_position(policy, a->rope_dims, &layer.position);
+    history.local_tail_count = a->initial_local_count;
+    history.local_kv = a->local;
+    history.local_kv_stride = a->local_stride;
+    history.local_positions = a->local_positions;
+    history.compressed_entry_count = a->attention_class ? compressed_rows : 0ull;
+    history.compressed_kv = a->compressed;
+    history.compressed_kv_stride = a->compressed_stride;
+    history.compressed_positions = a->compressed_positions;
+    history.immutable = 1;
+    return yvex_attention_reduce_chunk(
+               &layer, a->query, &history, a->local + a->initial_local_count * a->local_stride,
+               a->local_stride, NULL, 0ull, 0ull, NULL, NULL, 0ull, 0ull, NULL,
+               indexer ? indexer->query : NULL, indexer ? indexer->heads * indexer->head_dim : 0ull,
+               indexer ? indexer->weights : NULL, indexer ? indexer->heads : 0ull, a->sinks,
+               a->token_count, a->phase_start_position, out, a->candidate_block_visible,
+               trace_counts, trace_positions, indexer ? indexer->topk : 0ull, &scratch, &result,
+               &failure, &err) == YVEX_OK;
+}

@@ -772,9 +772,206 @@ int yvx_oracle_latent_reduce_full(const yvx_oracle_latent_args *a, float *out)
             for (lane = 0; lane < a->head_dim; ++lane)
                 o[lane] = yvx_oracle_bf16_decode(
                     yvx_oracle_bf16_encode((float)((double)o[lane] / denominator)));
+            /* :498-507: the published row is rotated back and published again */
+            if (a->rope_dims) {
+                if (!yvx_oracle_rope_apply(o, a->head_dim, a->rope_dims, token_position,
+                                           a->rope_frequency, 1))
+                    return 0;
+                for (lane = 0; lane < a->head_dim; ++lane)
+                    o[lane] = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(o[lane]));
+            }
         }
     }
     return 1;
+}
+
+/* ---- position rotation, sparse index scores, ranked top-k ------------------ */
+
+/* attention_yarn_frequency (src/graph/numeric.c:877-917): theta^(-2p/rope_dims),
+ * and with an original context and a scaling factor the ramp between the
+ * beta_fast and beta_slow correction dims blends in frequency / factor. */
+int yvx_oracle_rope_frequencies(const yvx_oracle_position_policy *policy,
+                                unsigned long long rope_dims, double *frequency)
+{
+    static const double pi = 3.14159265358979323846;
+    unsigned long long pair;
+    if (!policy || !frequency || rope_dims < 2ull || policy->theta <= 1ull) return 0;
+    if (rope_dims & 1ull) rope_dims--;  /* the rotation drops an odd last lane first (:933) */
+    for (pair = 0; pair < rope_dims / 2ull; ++pair) {
+        double exponent = (double)(pair * 2ull) / (double)rope_dims;
+        double f = 1.0 / pow((double)policy->theta, exponent);
+        if (policy->original_context && policy->scaling_factor) {
+            double denominator = 2.0 * log((double)policy->theta);
+            double low = floor((double)rope_dims *
+                               log((double)policy->original_context /
+                                   ((double)policy->beta_fast * 2.0 * pi)) / denominator);
+            double high = ceil((double)rope_dims *
+                               log((double)policy->original_context /
+                                   ((double)policy->beta_slow * 2.0 * pi)) / denominator);
+            double ramp, smooth;
+            if (low < 0.0) low = 0.0;
+            if (high > (double)rope_dims - 1.0) high = (double)rope_dims - 1.0;
+            if (low == high) high += 0.001;
+            ramp = ((double)pair - low) / (high - low);
+            if (ramp < 0.0) ramp = 0.0;
+            if (ramp > 1.0) ramp = 1.0;
+            smooth = 1.0 - ramp;
+            f = f / (double)policy->scaling_factor * (1.0 - smooth) + f * smooth;
+        }
+        frequency[pair] = f;
+    }
+    return 1;
+}
+
+/* yvex_attention_rope_apply (src/graph/numeric.c:919-949): the last rope_dims
+ * lanes as adjacent (x, y) pairs, angle = position * frequency, double
+ * arithmetic, results narrowed to float. Known answer:
+ * tests/reference/deepseek_attention.c:2690-2695. */
+int yvx_oracle_rope_apply(float *values, unsigned long long count, unsigned long long rope_dims,
+                          unsigned long long token_position, const double *frequency, int inverse)
+{
+    unsigned long long start, i;
+    if (!values || !count || !frequency || rope_dims < 2ull || rope_dims > count) return 0;
+    if (rope_dims & 1ull) rope_dims--;
+    start = count - rope_dims;
+    for (i = 0; i < rope_dims; i += 2ull) {
+        double angle = (double)token_position * frequency[i / 2ull];
+        double c = cos(angle);
+        double sn = inverse ? -sin(angle) : sin(angle);
+        double x = values[start + i], y = values[start + i + 1ull];
+        if (!isfinite(x) || !isfinite(y) || !isfinite(c) || !isfinite(sn)) return 0;
+        values[start + i] = (float)(x * c - y * sn);
+        values[start + i + 1ull] = (float)(x * sn + y * c);
+    }
+    return 1;
+}
+
+typedef struct {
+    float score;
+    unsigned long long ordinal, index;
+} topk_entry;
+
+/* Ranking of yvex_attention_topk_select (src/graph/numeric.c:957-1000): higher
+ * score first, +0 and -0 equal, equal scores by ascending ordinal. */
+static int topk_before(const void *left, const void *right)
+{
+    const topk_entry *a = (const topk_entry *)left, *b = (const topk_entry *)right;
+    if (a->score != b->score) return a->score > b->score ? -1 : 1;
+    if (a->ordinal != b->ordinal) return a->ordinal < b->ordinal ? -1 : 1;
+    return 0;
+}
+
+static int topk_by_ordinal(const void *left, const void *right)
+{
+    const topk_entry *a = (const topk_entry *)left, *b = (const topk_entry *)right;
+    return a->ordinal < b->ordinal ? -1 : a->ordinal > b->ordinal;
+}
+
+/* yvex_attention_topk_select (src/graph/numeric.c:1086-1150): refuses non-finite
+ * scores and duplicate ordinals; the first min(count, k) ranked candidates, as
+ * indices into the input, in ranked order. */
+int yvx_oracle_topk_select(const float *scores, const unsigned long long *ordinals,
+                           unsigned long long count, unsigned long long k,
+                           unsigned long long *selected, unsigned long long *selected_count)
+{
+    topk_entry *entries;
+    unsigned long long i, keep;
+    if (!scores || !ordinals || !selected || !selected_count) return 0;
+    *selected_count = 0ull;
+    if (!count || !k) return 1;
+    entries = (topk_entry *)malloc((size_t)count * sizeof(*entries));
+    if (!entries) return 0;
+    for (i = 0; i < count; ++i) {
+        if (!isfinite(scores[i])) {
+            free(entries);
+            return 0;
+        }
+        entries[i].score = scores[i];
+        entries[i].ordinal = ordinals[i];
+        entries[i].index = i;
+    }
+    qsort(entries, (size_t)count, sizeof(*entries), topk_by_ordinal);
+    for (i = 1; i < count; ++i)
+        if (entries[i - 1ull].ordinal == entries[i].ordinal) {
+            free(entries);
+            return 0;
+        }
+    qsort(entries, (size_t)count, sizeof(*entries), topk_before);
+    keep = count < k ? count : k;
+    for (i = 0; i < keep; ++i) selected[i] = entries[i].index;
+    *selected_count = keep;
+    free(entries);
+    return 1;
+}
+
+/* yvex_attention_csa_select (src/graph/attention.c:369-497): a compressed row is
+ * a candidate when position + ratio - 1 <= query position; its score is
+ * sum_h weight[h] * max(0, q_h . key) in double, scaled by 1/sqrt(head_dim) and
+ * 1/sqrt(heads), narrowed to float; candidates are ranked by (score, position).
+ * selected[] holds row indices in ranked order. scores_out (may be NULL) gets the
+ * float score of every row, NaN for rows that are not candidates. */
+int yvx_oracle_csa_select(const yvx_oracle_indexer *ix, unsigned long long token,
+                          unsigned long long query_position, unsigned long long *selected,
+                          unsigned long long *selected_count, unsigned long long *valid_count,
+                          float *scores_out)
+{
+    const float *query, *weights;
+    float *scores;
+    unsigned long long *ordinals, *rows, *ranked;
+    unsigned long long candidate, head, lane, valid = 0ull, ranked_count = 0ull, i;
+    int ok = 0;
+    if (!ix || !selected || !selected_count || !valid_count) return 0;
+    *selected_count = *valid_count = 0ull;
+    if (!ix->rows) return 1;
+    query = ix->query + token * ix->heads * ix->head_dim;
+    weights = ix->weights + token * ix->heads;
+    scores = (float *)malloc((size_t)ix->rows * sizeof(*scores));
+    ordinals = (unsigned long long *)malloc((size_t)ix->rows * sizeof(*ordinals));
+    rows = (unsigned long long *)malloc((size_t)ix->rows * sizeof(*rows));
+    ranked = (unsigned long long *)malloc((size_t)ix->rows * sizeof(*ranked));
+    if (!scores || !ordinals || !rows || !ranked) goto done;
+    for (candidate = 0; candidate < ix->rows; ++candidate) {
+        const float *key = ix->keys + candidate * ix->key_stride;
+        const unsigned long long position = ix->positions[candidate];
+        double score = 0.0;
+        if (scores_out) scores_out[candidate] = NAN;
+        if (position > query_position || position > ~0ull - ix->ratio + 1ull ||
+            position + ix->ratio - 1ull > query_position)
+            continue;
+        for (head = 0; head < ix->heads; ++head) {
+            const float *q = query + head * ix->head_dim;
+            double dot = 0.0;
+            for (lane = 0; lane < ix->head_dim; ++lane) {
+                if (!isfinite(q[lane]) || !isfinite(key[lane])) goto done;
+                dot += (double)q[lane] * (double)key[lane];
+            }
+            if (dot < 0.0) dot = 0.0;
+            if (!isfinite(weights[head])) goto done;
+            score += dot * (double)weights[head];
+        }
+        score *= 1.0 / sqrt((double)ix->head_dim);
+        score *= 1.0 / sqrt((double)ix->heads);
+        if (!isfinite(score)) goto done;
+        scores[valid] = (float)score;
+        if (scores_out) scores_out[candidate] = (float)score;
+        ordinals[valid] = position;
+        rows[valid] = candidate;
+        valid++;
+    }
+    if (valid) {
+        if (!yvx_oracle_topk_select(scores, ordinals, valid, ix->topk, ranked, &ranked_count))
+            goto done;
+        for (i = 0; i < ranked_count; ++i) selected[i] = rows[ranked[i]];
+        *selected_count = ranked_count;
+    }
+    *valid_count = valid;
+    ok = 1;
+done:
+    free(scores);
+    free(ordinals);
+    free(rows);
+    free(ranked);
+    return ok;
 }
 
 /* Rotate-half applied in place to packed [token][head][head_dim] vectors with

@@ -120,8 +120,37 @@ typedef struct {
     unsigned int attention_class;             /* 0 window only, 1 selected rows, 2 all rows */
     unsigned long long phase_start_position, token_count;
     int candidate_block_visible;
+    float *device_out;                        /* unused here: keeps the device library's layout */
+    int *device_status;                       /* unused here */
+    unsigned long long rope_dims;             /* 0: publish without the output rotation */
+    const double *rope_frequency;             /* [rope_dims/2] radians per position */
 } yvx_oracle_latent_args;
 int yvx_oracle_latent_reduce_full(const yvx_oracle_latent_args *args, float *out);
+
+/* Position rotation of the last rope_dims lanes (adjacent pairs), the frequencies
+ * behind it, the sparse index scores and the ranked top-k selection. */
+typedef struct {
+    unsigned long long theta, scaling_factor, original_context, beta_fast, beta_slow;
+} yvx_oracle_position_policy;
+int yvx_oracle_rope_frequencies(const yvx_oracle_position_policy *policy,
+                                unsigned long long rope_dims, double *frequency);
+int yvx_oracle_rope_apply(float *values, unsigned long long count, unsigned long long rope_dims,
+                          unsigned long long token_position, const double *frequency, int inverse);
+typedef struct {
+    const float *keys;                        /* [rows][key_stride], one per compressed row */
+    const unsigned long long *positions;      /* [rows] */
+    unsigned long long rows, key_stride;
+    const float *query;                       /* [token][heads*head_dim] */
+    const float *weights;                     /* [token][heads] */
+    unsigned long long heads, head_dim, topk, ratio;
+} yvx_oracle_indexer;
+int yvx_oracle_topk_select(const float *scores, const unsigned long long *ordinals,
+                           unsigned long long count, unsigned long long k,
+                           unsigned long long *selected, unsigned long long *selected_count);
+int yvx_oracle_csa_select(const yvx_oracle_indexer *indexer, unsigned long long token,
+                          unsigned long long query_position, unsigned long long *selected,
+                          unsigned long long *selected_count, unsigned long long *valid_count,
+                          float *scores_out);
 
 /* Latent decode with a separate rope key and an absorbed up-projection. */
 int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,

@@ -12,52 +12,10 @@ import pytest
 
 import clori_b200
 from clori_b200 import abi
+from latent_cases import bf16_valued, build, host_args  # noqa: F401
 
 pytestmark = pytest.mark.gpu
 u64 = np.uint64
-
-
-def bf16_valued(rng, shape, scale=1.0):
-    x = rng.standard_normal(shape).astype(np.float32) * np.float32(scale)
-    return clori_b200.bf16_bits_to_f32(clori_b200.f32_to_bf16_bits(x))
-
-
-def build(rng, heads, hd, window, attention_class, tokens, start):
-    ratio = {0: 0, 1: 4, 2: 128}[attention_class]
-    history = min(start, window - 1)
-    local_positions = np.arange(start - history, start + tokens, dtype=u64)
-    local = bf16_valued(rng, (len(local_positions), hd + 16))  # padded stride
-    last = start + tokens - 1
-    n_comp = (last + 1) // ratio if ratio else 0
-    comp = bf16_valued(rng, (max(n_comp, 1), hd))
-    comp_pos = (np.arange(max(n_comp, 1), dtype=u64) * u64(max(ratio, 1)))
-    topk = 8
-    selected = np.zeros((tokens, topk), u64)
-    selected_count = np.zeros(tokens, u64)
-    if attention_class == 1:
-        for t in range(tokens):
-            visible = (start + t + 1) // ratio
-            k = min(topk, visible)
-            selected_count[t] = k
-            if k:
-                selected[t, :k] = rng.choice(visible, size=k, replace=False).astype(u64)
-    return dict(query=bf16_valued(rng, (tokens, heads * hd)), local=local, local_positions=local_positions,
-                initial=history, compressed=comp, compressed_positions=comp_pos, selected=selected,
-                selected_count=selected_count, topk=topk, sinks=rng.standard_normal(heads).astype(np.float32),
-                heads=heads, hd=hd, window=window, ratio=ratio, cls=attention_class, start=start, tokens=tokens)
-
-
-def host_args(case, block_visible=0):
-    a = abi.LatentReduceArgs()
-    ptr = lambda x: x.ctypes.data
-    a.query, a.local, a.local_positions = ptr(case["query"]), ptr(case["local"]), ptr(case["local_positions"])
-    a.initial_local_count, a.local_stride = case["initial"], case["local"].shape[1]
-    a.compressed, a.compressed_positions, a.compressed_stride = ptr(case["compressed"]), ptr(case["compressed_positions"]), case["hd"]
-    a.selected, a.selected_count, a.topk_capacity = ptr(case["selected"]), ptr(case["selected_count"]), case["topk"]
-    a.sinks, a.query_heads, a.head_dim = ptr(case["sinks"]), case["heads"], case["hd"]
-    a.sliding_window, a.ratio, a.attention_class = case["window"], case["ratio"], case["cls"]
-    a.phase_start_position, a.token_count, a.candidate_block_visible = case["start"], case["tokens"], block_visible
-    return a
 
 
 def run_gpu(backend, case, block_visible=0):
