@@ -186,6 +186,35 @@ class AttentionReduceRequest(C.Structure):
         ("compressed_count", u64), ("compressed_stride", u64),
         ("selected", C.c_void_p), ("selected_count", C.c_void_p),
         ("sinks", C.c_void_p), ("output", C.c_void_p),
+        ("rope_dimension", u64), ("rope_frequency", C.c_void_p),
+    ]
+
+
+class PositionPolicy(C.Structure):
+    """yvex_b200_position_policy (include/yvex_b200/attention.h)."""
+    _fields_ = [(name, u64) for name in ("theta", "scaling_factor", "original_context", "beta_fast", "beta_slow")]
+
+
+class AttentionSelectRequest(C.Structure):
+    """yvex_b200_attention_select_request (include/yvex_b200/attention.h)."""
+    _fields_ = [
+        ("token_position", u64), ("token_count", u64),
+        ("indexer_heads", u64), ("indexer_head_dimension", u64), ("indexer_topk", u64), ("compression_ratio", u64),
+        ("index_keys", C.c_void_p), ("positions", C.c_void_p), ("count", u64), ("key_stride", u64),
+        ("index_query", C.c_void_p), ("index_weights", C.c_void_p),
+        ("scores", C.c_void_p), ("selected", C.c_void_p), ("selected_count", C.c_void_p),
+    ]
+
+
+class CsaSelectArgs(C.Structure):
+    """yvx_csa_select_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [
+        ("keys", C.c_void_p), ("positions", C.c_void_p), ("rows", u64), ("key_stride", u64),
+        ("query", C.c_void_p), ("weights", C.c_void_p),
+        ("heads", C.c_uint), ("head_dim", C.c_uint), ("topk", C.c_uint),
+        ("ratio", u64), ("phase_start_position", u64), ("token_count", u64),
+        ("scores", C.c_void_p), ("selected", C.c_void_p), ("selected_count", C.c_void_p),
+        ("topk_capacity", u64), ("workspace", C.c_void_p), ("status", C.c_void_p),
     ]
 
 
@@ -263,6 +292,7 @@ EXPORTED_SYMBOLS = [
     "yvex_b200_transformer_attention_execute",
     "yvex_backend_op_attention", "yvex_b200_attention_batch_execute",
     "yvex_b200_attention_reduce_execute", "yvex_b200_kv_append_rotary_execute", "yvex_b200_mla_decode_execute",
+    "yvex_b200_attention_select_execute", "yvex_b200_rope_frequencies",
     "yvex_b200_kv_pool_create", "yvex_b200_kv_pool_destroy", "yvex_b200_kv_pool_session_open",
     "yvex_b200_kv_pool_session_fork", "yvex_b200_kv_pool_session_close", "yvex_b200_kv_pool_reserve",
     "yvex_b200_kv_pool_commit", "yvex_b200_kv_pool_table", "yvex_b200_kv_pool_committed",
@@ -285,7 +315,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
-    "yvx_cuda_latent_reduce", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
+    "yvx_cuda_latent_reduce", "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
     "yvx_cuda_mla_decode",
 ]
 
@@ -335,6 +365,9 @@ def load():
         vp, P(BatchRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_attention_reduce_execute.argtypes = [
         vp, P(AttentionReduceRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
+    lib.yvex_b200_attention_select_execute.argtypes = [
+        vp, P(AttentionSelectRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
+    lib.yvex_b200_rope_frequencies.argtypes = [P(PositionPolicy), u64, vp]
     lib.yvex_b200_kv_append_rotary_execute.argtypes = [vp, P(KvAppendRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_mla_decode_execute.argtypes = [vp, P(MlaDecodeRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_kv_pool_create.restype = vp
@@ -403,6 +436,9 @@ def load():
     lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
     lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
     lib.yvx_cuda_latent_reduce.argtypes = [P(LatentReduceArgs), vp]
+    lib.yvx_cuda_csa_select_workspace_bytes.restype = u64
+    lib.yvx_cuda_csa_select_workspace_bytes.argtypes = [u64, u64, C.c_uint]
+    lib.yvx_cuda_csa_select.argtypes = [P(CsaSelectArgs), vp, P(C.c_uint)]
     lib.yvx_cuda_kv_append_rotary.argtypes = [P(KvAppendArgs), vp]
     lib.yvx_cuda_mla_plan.restype = None
     lib.yvx_cuda_mla_plan.argtypes = [P(MlaProblem), C.c_int]

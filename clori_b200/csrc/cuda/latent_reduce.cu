@@ -10,7 +10,8 @@
 // accumulator in registers, eight heads of a token share a CTA so a row fetched
 // once from L2 serves eight heads, and the softmax state never leaves the warp.
 // Row visibility and the published value (quotient rounded to bf16, stored as
-// F32) are the reference's.
+// F32) are the reference's; the reference's output rotation and second
+// publication (src/graph/core.c:498-507) can be fused into the epilogue.
 #include "common.cuh"
 
 namespace yvx {
@@ -121,15 +122,38 @@ latent_reduce_kernel(const yvx_latent_reduce_args a)
         return;
     }
     float *out = a.out + (ordinal * a.query_heads + head) * a.head_dim;
+    const unsigned long long rope_start = a.rope_frequency ? a.head_dim - a.rope_dims : a.head_dim;
+    bool published_finite = true;
 #pragma unroll
     for (int s = 0; s < SLOTS; ++s) {
         const unsigned long long d = lane + 32ull * s;
+        float published = acc[s] / l;
+        published_finite = published_finite && isfinite(published);
+        published = __uint_as_float((uint32_t)bf16_bits_rne(published) << 16);
+        // Output rotation of the reference (rope_apply with inverse = 1, then the second
+        // publication): pairs are adjacent lanes, so the partner sits in the neighbouring
+        // lane of the same slot. Uniform per slot: every lane reaches the shuffle.
+        if (rope_start < a.head_dim && 32ull * s + 32ull > rope_start) {
+            const float partner = __shfl_xor_sync(0xffffffffu, published, 1);
+            if (d >= rope_start && d < a.head_dim) {
+                const unsigned long long i = d - rope_start;
+                const double angle = __dmul_rn((double)token_position, a.rope_frequency[i >> 1]);
+                double sn, c;
+                sincos(angle, &sn, &c);
+                sn = -sn;
+                const double x = (i & 1ull) ? (double)partner : (double)published;
+                const double y = (i & 1ull) ? (double)published : (double)partner;
+                const double rotated = (i & 1ull) ? __dadd_rn(__dmul_rn(x, sn), __dmul_rn(y, c))
+                                                  : __dsub_rn(__dmul_rn(x, c), __dmul_rn(y, sn));
+                published_finite = published_finite && isfinite(c) && isfinite(sn);
+                published = __uint_as_float((uint32_t)bf16_bits_rne(__double2float_rn(rotated)) << 16);
+            }
+        }
         if (d < a.head_dim) {
-            const float published = acc[s] / l;
-            if (!isfinite(published))
+            if (!published_finite)
                 atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
             else
-                out[d] = __uint_as_float((uint32_t)bf16_bits_rne(published) << 16);
+                out[d] = published;
         }
     }
 }
@@ -150,6 +174,10 @@ extern "C" int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *a, void *str
         (a->attention_class == 1u && a->ratio != 4ull) ||
         (a->attention_class == 2u && a->ratio != 128ull) ||
         (a->attention_class == 0u && a->ratio != 0ull))
+        return YVEX_ERR_INVALID_ARG;
+    if (a->rope_frequency &&
+        (a->rope_dims < 2ull || a->rope_dims > a->head_dim || (a->rope_dims & 1ull) ||
+         ((a->head_dim - a->rope_dims) & 1ull)))
         return YVEX_ERR_INVALID_ARG;
     if (a->head_dim > 512ull || a->token_count > 65535ull) return YVEX_ERR_UNSUPPORTED;
     const dim3 grid((unsigned int)((a->query_heads + yvx::kLatentWarps - 1) / yvx::kLatentWarps),

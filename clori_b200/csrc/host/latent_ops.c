@@ -9,6 +9,8 @@
  * (include/yvex/internal/backend.h:144-161).
  * yvex_b200_kv_append_rotary_execute stands where src/runtime/decoder.c:
  * 1112-1131 and src/runtime/stateful_attention.c:183-243 rotate and copy.
+ * yvex_b200_attention_select_execute is the sparse index selection in front of
+ * that stage (CPU reference src/graph/attention.c:369-497).
  * yvex_b200_mla_decode_execute has no counterpart in the reference. */
 #include "private.h"
 
@@ -132,6 +134,19 @@ int yvex_b200_attention_reduce_execute(yvex_backend *backend,
     a.candidate_block_visible = r->candidate_block_visible;
     a.out = (float *)r->output->data;
     a.status = backend->status_device;
+    if (r->rope_frequency) {
+        if (r->rope_dimension < 2ull || (r->rope_dimension & 1ull) || r->rope_dimension > r->head_dimension ||
+            ((r->head_dimension - r->rope_dimension) & 1ull))
+            return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->head_dimension,
+                                 r->rope_dimension, err, YVEX_ERR_INVALID_ARG,
+                                 "rotated width must be even, at least 2 and leave an even unrotated width");
+        if (!view_ok(backend, r->rope_frequency, YVEX_DTYPE_F64, r->rope_dimension / 2ull))
+            return reduce_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->rope_dimension / 2ull,
+                                 r->rope_frequency->bytes, err, YVEX_ERR_FORMAT,
+                                 "frequency view does not cover the rotated pairs");
+        a.rope_dims = r->rope_dimension;
+        a.rope_frequency = (const double *)r->rope_frequency->data;
+    }
     rc = yvx_backend_status_arm(backend, where, err);
     if (rc != YVEX_OK) return rc;
     rc = yvx_cuda_latent_reduce(&a, backend->stream);
@@ -152,6 +167,140 @@ int yvex_b200_attention_reduce_execute(yvex_backend *backend,
         return rc;
     }
     r->output->is_written = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_b200_rope_frequencies(const yvex_b200_position_policy *policy,
+                               unsigned long long rope_dimension, double *frequency)
+{
+    static const double pi = 3.14159265358979323846;
+    unsigned long long pair;
+    if (!policy || !frequency || rope_dimension < 2ull || policy->theta <= 1ull) return YVEX_ERR_INVALID_ARG;
+    rope_dimension &= ~1ull;
+    for (pair = 0; pair < rope_dimension / 2ull; ++pair) {
+        double value = 1.0 / pow((double)policy->theta, (double)(pair * 2ull) / (double)rope_dimension);
+        if (policy->original_context && policy->scaling_factor) {
+            const double span = 2.0 * log((double)policy->theta);
+            double low = floor((double)rope_dimension *
+                               log((double)policy->original_context / ((double)policy->beta_fast * 2.0 * pi)) / span);
+            double high = ceil((double)rope_dimension *
+                               log((double)policy->original_context / ((double)policy->beta_slow * 2.0 * pi)) / span);
+            double ramp, keep;
+            if (low < 0.0) low = 0.0;
+            if (high > (double)rope_dimension - 1.0) high = (double)rope_dimension - 1.0;
+            if (low == high) high += 0.001;
+            ramp = ((double)pair - low) / (high - low);
+            ramp = ramp < 0.0 ? 0.0 : ramp > 1.0 ? 1.0 : ramp;
+            keep = 1.0 - ramp;
+            value = value / (double)policy->scaling_factor * (1.0 - keep) + value * keep;
+        }
+        frequency[pair] = value;
+    }
+    return YVEX_OK;
+}
+
+static int select_refuse(yvex_b200_attention_failure *failure, yvex_b200_attention_failure_code code,
+                         unsigned long long expected, unsigned long long actual, yvex_error *err,
+                         yvex_status status, const char *message)
+{
+    if (failure) {
+        failure->code = code;
+        failure->stage = "select";
+        failure->expected = expected;
+        failure->actual = actual;
+    }
+    return yvx_fail(err, status, "b200.attention.select", message);
+}
+
+int yvex_b200_attention_select_execute(yvex_backend *backend, const yvex_b200_attention_select_request *r,
+                                       yvex_b200_attention_failure *failure,
+                                       yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.attention.select";
+    unsigned long long width, elements = 0ull, workspace;
+    unsigned int launches = 0u;
+    void *scratch = NULL;
+    yvx_csa_select_args a;
+    int rc;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    if (!r || !facts || !r->index_keys || !r->positions || !r->index_query || !r->index_weights || !r->scores ||
+        !r->selected || !r->selected_count)
+        return select_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                             YVEX_ERR_INVALID_ARG, "index keys, positions, queries, weights and outputs are required");
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (!r->token_count || !r->count || !r->indexer_heads || !r->indexer_head_dimension || !r->indexer_topk ||
+        !r->compression_ratio || r->key_stride < r->indexer_head_dimension ||
+        !yvx_u64_mul(r->indexer_heads, r->indexer_head_dimension, &width))
+        return select_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->indexer_head_dimension,
+                             r->key_stride, err, YVEX_ERR_INVALID_ARG,
+                             "token count, row count, heads, width, top-k, ratio and key stride must be consistent");
+    if (r->indexer_heads > 64ull || r->indexer_head_dimension > 256ull || r->indexer_topk > 1024ull ||
+        r->count >= (1ull << 31) || r->token_count > 65535ull)
+        return select_refuse(failure, YVEX_B200_ATTENTION_FAILURE_CAPABILITY, 64ull, r->indexer_heads, err,
+                             YVEX_ERR_UNSUPPORTED, "at most 64 index heads of width 256, top-k 1024");
+    if (!yvx_u64_mul(r->count, r->key_stride, &elements) || !view_ok(backend, r->index_keys, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->positions, YVEX_DTYPE_I64, r->count) ||
+        !yvx_u64_mul(r->token_count, width, &elements) || !view_ok(backend, r->index_query, YVEX_DTYPE_F32, elements) ||
+        !yvx_u64_mul(r->token_count, r->indexer_heads, &elements) ||
+        !view_ok(backend, r->index_weights, YVEX_DTYPE_F32, elements) ||
+        !yvx_u64_mul(r->token_count, r->count, &elements) || !view_ok(backend, r->scores, YVEX_DTYPE_F32, elements) ||
+        !yvx_u64_mul(r->token_count, r->indexer_topk, &elements) ||
+        !view_ok(backend, r->selected, YVEX_DTYPE_I64, elements) ||
+        !view_ok(backend, r->selected_count, YVEX_DTYPE_I64, r->token_count))
+        return select_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements, 0ull, err,
+                             YVEX_ERR_FORMAT, "tensor views do not cover the stated geometry");
+    workspace = yvx_cuda_csa_select_workspace_bytes(r->count, r->token_count, (unsigned int)r->indexer_topk);
+    rc = yvx_backend_scratch(backend, workspace, &scratch, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_ALLOCATION;
+            failure->stage = "select";
+            failure->expected = workspace;
+        }
+        return rc;
+    }
+    memset(&a, 0, sizeof(a));
+    a.keys = (const float *)r->index_keys->data;
+    a.positions = (const unsigned long long *)r->positions->data;
+    a.rows = r->count;
+    a.key_stride = r->key_stride;
+    a.query = (const float *)r->index_query->data;
+    a.weights = (const float *)r->index_weights->data;
+    a.heads = (unsigned int)r->indexer_heads;
+    a.head_dim = (unsigned int)r->indexer_head_dimension;
+    a.topk = (unsigned int)r->indexer_topk;
+    a.ratio = r->compression_ratio;
+    a.phase_start_position = r->token_position;
+    a.token_count = r->token_count;
+    a.scores = (float *)r->scores->data;
+    a.selected = (unsigned long long *)r->selected->data;
+    a.selected_count = (unsigned long long *)r->selected_count->data;
+    a.topk_capacity = r->indexer_topk;
+    a.workspace = scratch;
+    a.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_csa_select(&a, backend->stream, &launches);
+    if (rc != 0) {
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
+            failure->stage = "select";
+        }
+        return yvx_backend_device_fail(backend, rc, where, err);
+    }
+    rc = finish(backend, facts, launches, workspace, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC
+                                                  : YVEX_B200_ATTENTION_FAILURE_SYNCHRONIZE;
+            failure->stage = "select";
+        }
+        return rc;
+    }
+    r->scores->is_written = r->selected->is_written = r->selected_count->is_written = 1;
     yvex_error_clear(err);
     return YVEX_OK;
 }

@@ -59,7 +59,8 @@ def attention_requirement(query_tokens, key_value_tokens, query_start, query_hea
 
 
 _NP_DTYPES = {abi.DTYPE_F32: np.float32, abi.DTYPE_BF16: np.uint16, abi.DTYPE_F16: np.uint16,
-              abi.DTYPE_I32: np.int32, abi.DTYPE_I8: np.int8, abi.DTYPE_I64: np.int64}
+              abi.DTYPE_I32: np.int32, abi.DTYPE_I8: np.int8, abi.DTYPE_I64: np.int64,
+              abi.DTYPE_F64: np.float64}
 
 
 class Tensor:
@@ -171,7 +172,7 @@ class Backend:
         if dtype is None:
             dtype = {np.dtype(np.float32): abi.DTYPE_F32, np.dtype(np.uint16): abi.DTYPE_BF16,
                      np.dtype(np.int32): abi.DTYPE_I32, np.dtype(np.int8): abi.DTYPE_I8,
-                     np.dtype(np.int64): abi.DTYPE_I64}[array.dtype]
+                     np.dtype(np.int64): abi.DTYPE_I64, np.dtype(np.float64): abi.DTYPE_F64}[array.dtype]
         return self.alloc(name, dtype, array.shape, array.nbytes).write(array)
 
     # -- operators -----------------------------------------------------------

@@ -182,7 +182,43 @@ typedef struct yvex_b200_attention_reduce_request {
     const yvex_device_tensor *selected, *selected_count; /* I64 [token][indexer_topk], I64 [token] */
     const yvex_device_tensor *sinks;                  /* F32 [heads] */
     yvex_device_tensor *output;                       /* F32 [token][heads*head_dim], bf16-rounded values */
+    /* rope_frequency != NULL: the reference's inverse output rotation and second bf16
+     * publication (src/graph/core.c:498-507) run in the same launch. */
+    unsigned long long rope_dimension;
+    const yvex_device_tensor *rope_frequency;         /* F64 [rope_dimension/2], radians per position */
 } yvex_b200_attention_reduce_request;
+/* The rotation frequencies of the reference's position policy
+ * (attention_yarn_frequency, src/graph/numeric.c:877-917), computed on the host in
+ * double precision: theta^(-2p/rope_dimension), blended with frequency/scaling_factor
+ * over the ramp between the beta_fast and beta_slow correction dims when
+ * original_context and scaling_factor are non-zero. frequency[rope_dimension/2]. */
+typedef struct {
+    unsigned long long theta, scaling_factor, original_context, beta_fast, beta_slow;
+} yvex_b200_position_policy;
+int yvex_b200_rope_frequencies(const yvex_b200_position_policy *policy,
+                               unsigned long long rope_dimension, double *frequency);
+
+/* The sparse index selection that feeds the reduce stage of class CSA: scores of
+ * every compressed row against the phase's index queries and the ranked top-k rows
+ * (CPU reference: yvex_attention_csa_select src/graph/attention.c:369-497,
+ * yvex_attention_topk_select src/graph/numeric.c:1086-1150). selected /
+ * selected_count are the tensors the reduce request takes. */
+typedef struct yvex_b200_attention_select_request {
+    unsigned long long token_position, token_count;
+    unsigned long long indexer_heads, indexer_head_dimension, indexer_topk, compression_ratio;
+    const yvex_device_tensor *index_keys;             /* F32 [count][key_stride], row i = compressed row i */
+    const yvex_device_tensor *positions;              /* I64 [count], strictly increasing */
+    unsigned long long count, key_stride;
+    const yvex_device_tensor *index_query;            /* F32 [token][heads*head_dim] */
+    const yvex_device_tensor *index_weights;          /* F32 [token][heads] */
+    yvex_device_tensor *scores;                       /* F32 [token][count] */
+    yvex_device_tensor *selected, *selected_count;    /* I64 [token][indexer_topk], I64 [token] */
+} yvex_b200_attention_select_request;
+int yvex_b200_attention_select_execute(yvex_backend *backend,
+                                       const yvex_b200_attention_select_request *request,
+                                       yvex_b200_attention_failure *failure,
+                                       yvex_backend_operation_facts *facts, yvex_error *err);
+
 int yvex_b200_attention_reduce_execute(yvex_backend *backend,
                                        const yvex_b200_attention_reduce_request *request,
                                        yvex_b200_attention_failure *failure,

@@ -220,7 +220,15 @@ int yvx_cuda_op_attention_f32(const float *query, const float *keys, const float
  * pass 1 = compressed rows (class 1: selected[token][0..selected_count), ratio 4;
  * class 2: all rows with position + ratio - 1 <= pos, ratio 128; class 0: none).
  * out = quotient rounded to bf16 (nearest even), stored as F32. status: 1 non-finite,
- * 2 contract. head_dim <= 512. */
+ * 2 contract. head_dim <= 512.
+ * rope_frequency != NULL fuses what the reference runs after the reduce on every
+ * published row (CPU: src/graph/core.c:498-507, yvex_attention_rope_apply
+ * src/graph/numeric.c:919-949 with inverse = 1; CUDA: the yarn-rope launch of
+ * src/backend/cuda/attention.c:1424-1451): the last rope_dims lanes, taken as adjacent
+ * (x, y) pairs, are rotated by -position * rope_frequency[pair] in double precision,
+ * narrowed to float and rounded to bf16 again. rope_frequency is a device array of
+ * rope_dims / 2 doubles, radians per position (yvex_b200_rope_frequencies computes the
+ * reference's values on the host); rope_dims and head_dim - rope_dims must be even. */
 typedef struct yvx_latent_reduce_args {
     const float *query;                       /* [token][heads*head_dim] */
     const float *local;                       /* [initial_local_count + token_count][local_stride] */
@@ -239,8 +247,49 @@ typedef struct yvx_latent_reduce_args {
     int candidate_block_visible;
     float *out;                               /* [token][heads*head_dim] */
     int *status;
+    unsigned long long rope_dims;             /* used when rope_frequency != NULL */
+    const double *rope_frequency;             /* [rope_dims/2] or NULL */
 } yvx_latent_reduce_args;
 int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *args, void *stream);
+
+/* ---- sparse index selection: scores + ranked top-k ---------------------------------
+ * Replaces, for one phase, the reference's index scoring and top-k
+ * (CPU: yvex_attention_csa_select src/graph/attention.c:369-497 and
+ * yvex_attention_topk_select src/graph/numeric.c:1086-1150; CUDA stage: the compress /
+ * indexer / topk launches of src/backend/cuda/attention.c:1237-1385). Row i of `keys`
+ * belongs to compressed row i. For token t at position p = phase_start_position + t a
+ * row is a candidate when positions[i] + ratio - 1 <= p; its score is
+ *   (float)( 1/sqrt(heads) * 1/sqrt(head_dim) * sum_h weights[t][h] * max(0, q[t][h] . key_i) )
+ * with the dot, the sum over heads and the two scalings in double precision in the
+ * reference's order, so scores are bit-equal to the CPU reference. The candidates are
+ * ranked by score descending (+0 equals -0), equal scores by ascending position, and
+ * selected[t][0 .. selected_count[t]) receives the first min(candidates, topk) row
+ * indices in ranked order: the lists yvx_cuda_latent_reduce reads for class 1.
+ * Contract: positions strictly increasing (the reference refuses duplicate positions;
+ * here unordered ones are refused as well), heads <= 64, head_dim <= 256, topk <= 1024,
+ * rows < 2^31. scores [token][rows] receives every candidate's score. workspace:
+ * yvx_cuda_csa_select_workspace_bytes() bytes. status: 1 non-finite, 2 contract.
+ * Launches: 2 when rows <= 4096, else 3 or more. */
+typedef struct yvx_csa_select_args {
+    const float *keys;                        /* [rows][key_stride] */
+    const unsigned long long *positions;      /* [rows] */
+    unsigned long long rows, key_stride;
+    const float *query;                       /* [token][heads*head_dim] */
+    const float *weights;                     /* [token][heads] */
+    unsigned int heads, head_dim, topk;
+    unsigned long long ratio;
+    unsigned long long phase_start_position, token_count;
+    float *scores;                            /* [token][rows] */
+    unsigned long long *selected;             /* [token][topk_capacity] */
+    unsigned long long *selected_count;       /* [token] */
+    unsigned long long topk_capacity;         /* >= topk */
+    void *workspace;
+    int *status;
+} yvx_csa_select_args;
+unsigned long long yvx_cuda_csa_select_workspace_bytes(unsigned long long rows,
+                                                       unsigned long long token_count,
+                                                       unsigned int topk);
+int yvx_cuda_csa_select(const yvx_csa_select_args *args, void *stream, unsigned int *launches);
 
 /* ---- KV append with rotary embedding (one launch per step) ---------------------------
  * Replaces, for the new rows of a step, the two rotate-half launches on Q and K
