@@ -659,6 +659,122 @@ def bench_kv_append(lib, backend, abi, hbm_peak, repeats, sessions=2, tokens=819
     return result, None
 
 
+def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
+    """One decode step of a sparse shared-latent layer at the reference configuration's
+    widths (64 heads x 512 with the last 64 lanes rotated, window 128, ratio 4, 64 index
+    heads x 128, top-k 512) over a `context`-token history: index selection (scores in
+    double precision in the reference's order + ranked top-k), then the reduce with the
+    inverse rotation fused. Checked on the host against the CPU restatement: selected
+    rows identical, published output within the reduce stage's tolerance."""
+    import clori_b200
+    from oracle.binding import Oracle, indexer_struct
+    heads, hd, rope, window, ratio, ih, idim, topk = 64, 512, 64, 128, 4, 64, 128, 512
+    start = context - tokens
+    rows = context // ratio
+    rng = np.random.default_rng(SEED + 77)
+    rounded = lambda x: clori_b200.bf16_bits_to_f32(clori_b200.f32_to_bf16_bits(x.astype(np.float32)))
+    host = dict(keys=rounded(rng.standard_normal((rows, idim))), iq=rounded(rng.standard_normal((tokens, ih * idim))),
+                iw=rounded(rng.standard_normal((tokens, ih)) * 0.5),
+                positions=np.arange(rows, dtype=np.uint64) * np.uint64(ratio),
+                query=rounded(rng.standard_normal((tokens, heads * hd))),
+                local=rounded(rng.standard_normal((window - 1 + tokens, hd))),
+                local_positions=np.arange(start - (window - 1), start + tokens, dtype=np.uint64),
+                compressed=rounded(rng.standard_normal((rows, hd))), sinks=rng.standard_normal(heads).astype(np.float32))
+    policy = (10000, 16, 65536, 32, 1)
+    frequency = np.zeros(rope // 2, np.float64)
+    assert lib.yvex_b200_rope_frequencies(C.byref(abi.PositionPolicy(*policy)), rope, frequency.ctypes.data) == 0
+    host["frequency"] = frequency
+    dev = {}
+    for name, array in host.items():
+        dev[name] = _alloc(lib, array.nbytes)
+        lib.yvx_cuda_upload_async(dev[name], array.ctypes.data, array.nbytes, backend.stream)
+    out_bytes = {"scores": tokens * rows * 4, "selected": tokens * topk * 8, "count": tokens * 8, "status": 4,
+                 "out": tokens * heads * hd * 4,
+                 "work": int(lib.yvx_cuda_csa_select_workspace_bytes(rows, tokens, topk))}
+    for name, nbytes in out_bytes.items():
+        dev[name] = _alloc(lib, nbytes)
+    lib.yvx_cuda_memset_async(dev["status"], 0, 4, backend.stream)
+    s = abi.CsaSelectArgs()
+    s.keys, s.positions, s.rows, s.key_stride = dev["keys"], dev["positions"], rows, idim
+    s.query, s.weights, s.heads, s.head_dim, s.topk = dev["iq"], dev["iw"], ih, idim, topk
+    s.ratio, s.phase_start_position, s.token_count = ratio, start, tokens
+    s.scores, s.selected, s.selected_count = dev["scores"], dev["selected"], dev["count"]
+    s.topk_capacity, s.workspace, s.status = topk, dev["work"], dev["status"]
+    r = abi.LatentReduceArgs()
+    r.query, r.local, r.local_positions = dev["query"], dev["local"], dev["local_positions"]
+    r.initial_local_count, r.local_stride = window - 1, hd
+    r.compressed, r.compressed_positions, r.compressed_stride = dev["compressed"], dev["positions"], hd
+    r.selected, r.selected_count, r.topk_capacity = dev["selected"], dev["count"], topk
+    r.sinks, r.query_heads, r.head_dim, r.sliding_window, r.ratio = dev["sinks"], heads, hd, window, ratio
+    r.attention_class, r.phase_start_position, r.token_count = 1, start, tokens
+    r.out, r.status, r.rope_dims, r.rope_frequency = dev["out"], dev["status"], rope, dev["frequency"]
+    launches = C.c_uint()
+
+    def select():
+        assert lib.yvx_cuda_csa_select(C.byref(s), backend.stream, C.byref(launches)) == 0, lib.yvx_cuda_last_error_text()
+
+    def reduce():
+        assert lib.yvx_cuda_latent_reduce(C.byref(r), backend.stream) == 0, lib.yvx_cuda_last_error_text()
+
+    def timed(*calls):
+        first, last = C.c_void_p(), C.c_void_p()
+        lib.yvx_cuda_event_create(C.byref(first)); lib.yvx_cuda_event_create(C.byref(last))
+        for _ in range(3):
+            for call in calls:
+                call()
+        lib.yvx_cuda_event_record(first, backend.stream)
+        for _ in range(repeats):
+            for call in calls:
+                call()
+        lib.yvx_cuda_event_record(last, backend.stream)
+        assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+        ms = C.c_float()
+        lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+        return ms.value / repeats
+    select_ms, reduce_ms, step_ms = timed(select), timed(reduce), timed(select, reduce)
+    got = {name: np.zeros(shape, dtype) for name, shape, dtype in (
+        ("selected", (tokens, topk), np.uint64), ("count", (tokens,), np.uint64), ("status", (1,), np.int32),
+        ("out", (tokens, heads * hd), np.float32))}
+    for name, array in got.items():
+        lib.yvx_cuda_download_async(array.ctypes.data, dev[name], array.nbytes, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    flops = 2.0 * tokens * rows * ih * idim
+    result = {"workload": f"sparse shared-latent decode step, context {context}, {tokens} token(s): index selection over "
+                          f"{rows} rows (64 index heads x 128, top-k 512) + reduce (64 heads x 512, window 128, "
+                          "512 selected rows) with the inverse rotation fused",
+              "kernels": "csa_score_kernel, csa_rank_rows_kernel, csa_rank_lists_kernel, latent_reduce_kernel",
+              "launches_per_step": int(launches.value) + 1, "select_ms": select_ms, "reduce_ms": reduce_ms,
+              "step_ms": step_ms, "score_fp64_tflops": flops / (select_ms * 1e-3) / 1e12,
+              "score_note": "scores keep the reference's double-precision order: FP64 pipe bound, keys (%.0f MB) stay in L2"
+                            % (rows * idim * 4 / 1e6),
+              "status_word": int(got["status"][0])}
+    oracle = Oracle()
+    begin = time.perf_counter()
+    ix = indexer_struct(host["keys"], host["positions"], host["iq"], host["iw"], ih, idim, topk, ratio)
+    selected, counts = np.zeros((tokens, topk), np.uint64), np.zeros(tokens, np.uint64)
+    for t in range(tokens):
+        picked, _, _ = oracle.csa_select(ix, t, start + t)
+        counts[t], selected[t, :len(picked)] = len(picked), picked
+    a = abi.LatentReduceArgs()
+    ptr = lambda x: x.ctypes.data
+    a.query, a.local, a.local_positions = ptr(host["query"]), ptr(host["local"]), ptr(host["local_positions"])
+    a.initial_local_count, a.local_stride = window - 1, hd
+    a.compressed, a.compressed_positions, a.compressed_stride = ptr(host["compressed"]), ptr(host["positions"]), hd
+    a.selected, a.selected_count, a.topk_capacity = ptr(selected), ptr(counts), topk
+    a.sinks, a.query_heads, a.head_dim, a.sliding_window, a.ratio = ptr(host["sinks"]), heads, hd, window, ratio
+    a.attention_class, a.phase_start_position, a.token_count = 1, start, tokens
+    a.rope_dims, a.rope_frequency = rope, ptr(frequency)
+    ref = oracle.latent_reduce_full(a, tokens, heads, hd)
+    cpu_seconds = time.perf_counter() - begin
+    result.update(selected_rows_equal_cpu=bool(np.array_equal(counts, got["count"]) and
+                                               np.array_equal(selected, got["selected"])),
+                  out_max_abs_vs_cpu=float(np.abs(ref - got["out"]).max()), cpu_port_step_ms=cpu_seconds * 1e3,
+                  cpu_cores=1)
+    for ptr_ in dev.values():
+        lib.yvx_cuda_free(ptr_)
+    return result, None
+
+
 def check_mla(sample):
     from oracle.binding import Oracle
     host, o = sample
@@ -947,7 +1063,7 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append"],
+                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -995,6 +1111,8 @@ def main():
         if args.workload == "mla":
             result, _ = bench_mla(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                   sessions=min(args.sessions, 32))
+        elif args.workload == "latent_sparse":
+            result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
         elif args.workload == "kv_append":
             result, _ = bench_kv_append(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                         tokens=args.tokens)
@@ -1068,6 +1186,7 @@ def main():
         others["prefill_config3"], other_samples["prefill"] = bench_prefill(lib, b, w.abi, 10)
         others["latent_decode_config5"], other_samples["mla"] = bench_mla(lib, b, w.abi, hbm_peak, 10)
         others["kv_append_rotary"], _ = bench_kv_append(lib, b, w.abi, hbm_peak, 10)
+        others["latent_sparse_decode"], _ = bench_latent_sparse(lib, b, w.abi, 20)
 
     if rank != 0:
         if dist is not None:

@@ -14,8 +14,8 @@
 
 namespace yvx {
 
-constexpr int kCsaScoreThreads = 256;
-constexpr int kCsaRowsPerBlock = 32;
+constexpr int kCsaScoreThreads = 128;
+constexpr unsigned int kCsaHeadSlots = 64;  // heads <= 64; unused slots hold zeros
 constexpr int kCsaSortThreads = 1024;
 constexpr int kCsaSortKeys = 4096;  // keys one CTA ranks at a time
 constexpr unsigned long long kCsaAbsent = ~0ull;
@@ -27,66 +27,107 @@ __device__ __forceinline__ bool csa_candidate(unsigned long long position, unsig
            position + ratio - 1ull <= query_position;
 }
 
-// grid: x = block of kCsaRowsPerBlock rows, y = token. threads: heads x (256 / heads) rows.
-// smem: query [heads][head_dim + 1] floats, dots [rows in flight][heads] doubles.
+// Scores. grid: x = CTAs striding over row tiles, y = token; 4 warps. A warp owns all 64
+// head slots x 2*RT rows of the tile: lane = head lane (16) + 16 * row lane (2), a thread
+// accumulates heads {hl, hl+16, hl+32, hl+48} x RT rows, so one step of the lane loop costs
+// 4 + RT shared-memory reads for 4*RT fused multiply-adds and the FP64 pipe is the limit.
+// The query and the tile's keys are widened to double once, in shared memory (pitches
+// hd+1 and hd+2 doubles keep the 16 head lanes and the 2 row lanes on distinct banks).
+// Arithmetic order is the reference's: per (row, head) the lanes in order (the product of
+// two floats is exact in double, so a fused multiply-add rounds once exactly like the
+// reference's multiply-then-add), clamp at zero, then per row the heads in order with a
+// rounded multiply by the weight and a rounded add, then the two scalings.
+template <int RT>
 __global__ void __launch_bounds__(kCsaScoreThreads)
 csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const double inv_sqrt_heads)
 {
+    constexpr unsigned int kTileRows = (kCsaScoreThreads / 32) * 2 * RT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const unsigned int heads = a.heads, hd = a.head_dim, pitch = hd + 1u;
-    float *q = reinterpret_cast<float *>(smem_raw);
-    double *dots = reinterpret_cast<double *>(smem_raw + (((size_t)heads * pitch * 4u + 7u) & ~(size_t)7u));
+    const unsigned int heads = a.heads, hd = a.head_dim;
+    const unsigned int qp = hd + 1u, kp = max(hd + 2u, kCsaHeadSlots + 1u), dp = kCsaHeadSlots + 1u;
+    double *q = reinterpret_cast<double *>(smem_raw);           // [64][qp]
+    double *keys = q + kCsaHeadSlots * qp;                      // [kTileRows][kp]; reused as dots [kTileRows][dp]
+    __shared__ unsigned char visible[kTileRows];
     const unsigned long long token = blockIdx.y;
     const unsigned long long query_position = a.phase_start_position + token;
     const float *query = a.query + token * heads * hd;
     const float *weights = a.weights + token * heads;
     bool finite = true, query_finite = true, any_candidate = false;
-    for (unsigned int i = threadIdx.x; i < heads * hd; i += blockDim.x) {
-        const float v = query[i];
+    for (unsigned int i = threadIdx.x; i < kCsaHeadSlots * hd; i += blockDim.x) {
+        const unsigned int h = i / hd, lane = i % hd;
+        const float v = h < heads ? query[i] : 0.0f;
         query_finite = query_finite && isfinite(v);
-        q[(i / hd) * pitch + i % hd] = v;
+        q[h * qp + lane] = (double)v;
     }
-    __syncthreads();
-    const unsigned int rows_in_flight = blockDim.x / heads;
-    const unsigned int slot = threadIdx.x / heads, head = threadIdx.x % heads;
-    const unsigned long long first = (unsigned long long)blockIdx.x * kCsaRowsPerBlock;
-    for (unsigned int base = 0; base < (unsigned int)kCsaRowsPerBlock; base += rows_in_flight) {
-        const unsigned long long row = first + base + slot;
-        bool candidate = false;
-        if (base + slot < (unsigned int)kCsaRowsPerBlock && row < a.rows) {
-            const unsigned long long position = a.positions[row];
-            if (row > 0ull && a.positions[row - 1ull] >= position && head == 0u)
-                atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
-            candidate = csa_candidate(position, a.ratio, query_position);
+    const unsigned int warp = threadIdx.x >> 5, hl = threadIdx.x & 15u, rl = (threadIdx.x >> 4) & 1u;
+    const unsigned int row0 = warp * 2u * RT + rl * RT;
+    const unsigned long long tiles = (a.rows + kTileRows - 1u) / kTileRows;
+    for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const unsigned long long first = tile * kTileRows;
+        __syncthreads();  // the previous tile's sums are done with the shared region; q is written
+        if (threadIdx.x < kTileRows) {
+            const unsigned long long row = first + threadIdx.x;
+            bool candidate = false;
+            if (row < a.rows) {
+                const unsigned long long position = a.positions[row];
+                if (row > 0ull && a.positions[row - 1ull] >= position) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
+                candidate = csa_candidate(position, a.ratio, query_position);
+            }
+            visible[threadIdx.x] = candidate;
         }
-        if (candidate) {
-            const float *key = a.keys + row * a.key_stride;
-            const float *qh = q + head * pitch;
-            double dot = 0.0;
-            for (unsigned int lane = 0; lane < hd; ++lane) {
-                const float k = __ldg(key + lane);
+        __syncthreads();
+        for (unsigned int i = threadIdx.x; i < kTileRows * hd; i += blockDim.x) {
+            const unsigned int r = i / hd, lane = i % hd;
+            float k = 0.0f;
+            if (visible[r]) {
+                k = __ldg(a.keys + (first + r) * a.key_stride + lane);
                 finite = finite && isfinite(k);
-                dot = __dadd_rn(dot, __dmul_rn((double)qh[lane], (double)k));
+                any_candidate = true;
             }
-            dots[slot * heads + head] = dot < 0.0 ? 0.0 : dot;
+            keys[r * kp + lane] = (double)k;
         }
-        any_candidate = __syncthreads_or(candidate) || any_candidate;
-        if (candidate && head == 0u) {
+        __syncthreads();
+        double acc[4][RT];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int r = 0; r < RT; ++r) acc[j][r] = 0.0;
+        const double *qh = q + hl * qp, *kr = keys + row0 * kp;
+#pragma unroll 2
+        for (unsigned int lane = 0; lane < hd; ++lane) {
+            double qv[4], kv[RT];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qv[j] = qh[j * 16u * qp + lane];
+#pragma unroll
+            for (int r = 0; r < RT; ++r) kv[r] = kr[r * kp + lane];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int r = 0; r < RT; ++r) acc[j][r] = fma(qv[j], kv[r], acc[j][r]);
+        }
+        __syncthreads();  // every warp is done with the keys
+        double *dots = keys;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned int h = hl + 16u * j;
+            const float w = h < heads ? weights[h] : 0.0f;
+            finite = finite && isfinite(w);
+#pragma unroll
+            for (int r = 0; r < RT; ++r)
+                dots[(row0 + r) * dp + h] = __dmul_rn(acc[j][r] < 0.0 ? 0.0 : acc[j][r], (double)w);
+        }
+        __syncthreads();
+        if (threadIdx.x < kTileRows && visible[threadIdx.x]) {
             double score = 0.0;
-            for (unsigned int h = 0; h < heads; ++h) {
-                const float w = weights[h];
-                finite = finite && isfinite(w);
-                score = __dadd_rn(score, __dmul_rn(dots[slot * heads + h], (double)w));
-            }
+            for (unsigned int h = 0; h < heads; ++h) score = __dadd_rn(score, dots[threadIdx.x * dp + h]);
             score = __dmul_rn(score, inv_sqrt_dim);
             score = __dmul_rn(score, inv_sqrt_heads);
             finite = finite && isfinite(score);
-            a.scores[token * a.rows + row] = __double2float_rn(score);
+            a.scores[token * a.rows + first + threadIdx.x] = __double2float_rn(score);
         }
-        __syncthreads();
     }
-    // the reference inspects the query only while it scores a candidate
-    if (!finite || (any_candidate && !query_finite)) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+    // the reference inspects the query and the weights only while it scores a candidate
+    if (__syncthreads_or(any_candidate) && (!finite || !query_finite)) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
 }
 
 // Ascending key order = the reference's ranked order: higher score first (+0 and -0
@@ -214,18 +255,25 @@ extern "C" int yvx_cuda_csa_select(const yvx_csa_select_args *a, void *stream, u
     cudaStream_t s = (cudaStream_t)stream;
     unsigned int count = 0u;
     {
-        const unsigned int threads = (yvx::kCsaScoreThreads / a->heads) * a->heads;
-        const size_t query_bytes = ((size_t)a->heads * (a->head_dim + 1u) * 4u + 7u) & ~(size_t)7u;
-        const size_t smem = query_bytes + (size_t)(threads / a->heads) * a->heads * sizeof(double);
-        if (smem > 48u * 1024u) {
-            cudaError_t e = cudaFuncSetAttribute(yvx::csa_score_kernel,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return yvx_cuda_check(e, "csa_score_kernel attribute");
-        }
-        const dim3 grid((unsigned int)((a->rows + yvx::kCsaRowsPerBlock - 1) / yvx::kCsaRowsPerBlock),
-                        (unsigned int)a->token_count);
-        yvx::csa_score_kernel<<<grid, threads, smem, s>>>(*a, 1.0 / sqrt((double)a->head_dim),
-                                                          1.0 / sqrt((double)a->heads));
+        // 8 rows per thread while the widened tile fits beside the widened query, else 4
+        const bool wide = a->head_dim <= 128u;
+        const unsigned int tile_rows = (yvx::kCsaScoreThreads / 32) * 2 * (wide ? 8 : 4);
+        const unsigned int kp = a->head_dim + 2u > yvx::kCsaHeadSlots + 1u ? a->head_dim + 2u : yvx::kCsaHeadSlots + 1u;
+        const size_t smem = ((size_t)yvx::kCsaHeadSlots * (a->head_dim + 1u) + (size_t)tile_rows * kp) * sizeof(double);
+        auto kernel = wide ? yvx::csa_score_kernel<8> : yvx::csa_score_kernel<4>;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return yvx_cuda_check(e, "csa_score_kernel attribute");
+        const unsigned long long tiles = (a->rows + tile_rows - 1u) / tile_rows;
+        int sms = 148;
+        int device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess)
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        // a CTA widens the query once and then strides over tiles; spread tokens over the SMs
+        unsigned long long per_token = ((unsigned long long)sms + a->token_count - 1ull) / a->token_count;
+        if (per_token > tiles) per_token = tiles;
+        const dim3 grid((unsigned int)per_token, (unsigned int)a->token_count);
+        kernel<<<grid, yvx::kCsaScoreThreads, smem, s>>>(*a, 1.0 / sqrt((double)a->head_dim),
+                                                        1.0 / sqrt((double)a->heads));
         ++count;
     }
     unsigned long long *ping = (unsigned long long *)a->workspace;
