@@ -708,13 +708,16 @@ def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
     r.sinks, r.query_heads, r.head_dim, r.sliding_window, r.ratio = dev["sinks"], heads, hd, window, ratio
     r.attention_class, r.phase_start_position, r.token_count = 1, start, tokens
     r.out, r.status, r.rope_dims, r.rope_frequency = dev["out"], dev["status"], rope, dev["frequency"]
-    launches = C.c_uint()
+    dev["reduce_work"] = _alloc(lib, max(int(lib.yvx_cuda_latent_reduce_workspace_bytes(C.byref(r))), 16))
+    r.workspace = dev["reduce_work"]
+    launches, reduce_launches = C.c_uint(), C.c_uint()
 
     def select():
         assert lib.yvx_cuda_csa_select(C.byref(s), backend.stream, C.byref(launches)) == 0, lib.yvx_cuda_last_error_text()
 
     def reduce():
-        assert lib.yvx_cuda_latent_reduce(C.byref(r), backend.stream) == 0, lib.yvx_cuda_last_error_text()
+        assert lib.yvx_cuda_latent_reduce_launches(C.byref(r), backend.stream, C.byref(reduce_launches)) == 0, \
+            lib.yvx_cuda_last_error_text()
 
     def timed(*calls):
         first, last = C.c_void_p(), C.c_void_p()
@@ -742,8 +745,8 @@ def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
     result = {"workload": f"sparse shared-latent decode step, context {context}, {tokens} token(s): index selection over "
                           f"{rows} rows (64 index heads x 128, top-k 512) + reduce (64 heads x 512, window 128, "
                           "512 selected rows) with the inverse rotation fused",
-              "kernels": "csa_score_kernel, csa_rank_rows_kernel, csa_rank_lists_kernel, latent_reduce_kernel",
-              "launches_per_step": int(launches.value) + 1, "select_ms": select_ms, "reduce_ms": reduce_ms,
+              "kernels": "csa_score_kernel, csa_rank_rows_kernel, csa_rank_lists_kernel, latent_reduce_kernel, latent_fold_kernel",
+              "launches_per_step": int(launches.value) + int(reduce_launches.value), "select_ms": select_ms, "reduce_ms": reduce_ms,
               "step_ms": step_ms, "score_fp64_tflops": flops / (select_ms * 1e-3) / 1e12,
               "score_note": "scores keep the reference's double-precision order: FP64 pipe bound, keys (%.0f MB) stay in L2"
                             % (rows * idim * 4 / 1e6),

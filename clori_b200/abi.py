@@ -152,7 +152,7 @@ class LatentReduceArgs(C.Structure):
         ("ratio", u64), ("attention_class", C.c_uint), ("phase_start_position", u64),
         ("token_count", u64), ("candidate_block_visible", C.c_int),
         ("out", C.c_void_p), ("status", C.c_void_p),
-        ("rope_dims", u64), ("rope_frequency", C.c_void_p),
+        ("rope_dims", u64), ("rope_frequency", C.c_void_p), ("workspace", C.c_void_p),
     ]
 
 
@@ -315,7 +315,8 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
-    "yvx_cuda_latent_reduce", "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
+    "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
+    "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
     "yvx_cuda_mla_decode",
 ]
 
@@ -436,6 +437,9 @@ def load():
     lib.yvx_cuda_gqa_static_scratch_capacity.argtypes = []
     lib.yvx_cuda_gqa_attention_static_scratch.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
     lib.yvx_cuda_latent_reduce.argtypes = [P(LatentReduceArgs), vp]
+    lib.yvx_cuda_latent_reduce_launches.argtypes = [P(LatentReduceArgs), vp, P(C.c_uint)]
+    lib.yvx_cuda_latent_reduce_workspace_bytes.restype = u64
+    lib.yvx_cuda_latent_reduce_workspace_bytes.argtypes = [P(LatentReduceArgs)]
     lib.yvx_cuda_csa_select_workspace_bytes.restype = u64
     lib.yvx_cuda_csa_select_workspace_bytes.argtypes = [u64, u64, C.c_uint]
     lib.yvx_cuda_csa_select.argtypes = [P(CsaSelectArgs), vp, P(C.c_uint)]

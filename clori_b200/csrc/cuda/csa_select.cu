@@ -62,6 +62,26 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
     const unsigned int warp = threadIdx.x >> 5, hl = threadIdx.x & 15u, rl = (threadIdx.x >> 4) & 1u;
     const unsigned int row0 = warp * 2u * RT + rl * RT;
     const unsigned long long tiles = (a.rows + kTileRows - 1u) / kTileRows;
+    // The tile after the current one travels through registers while the current one is
+    // being scored, so its load latency hides behind the FP64 work. kPrefetch float4 per
+    // thread cover the tile when hd <= 128 (vector path: hd and key_stride multiples of 4).
+    constexpr unsigned int kPrefetch = kTileRows * 128u / 4u / kCsaScoreThreads;
+    const bool vector_path = (hd & 3u) == 0u && (a.key_stride & 3ull) == 0ull && hd <= 128u &&
+                             (reinterpret_cast<unsigned long long>(a.keys) & 15ull) == 0ull;
+    const unsigned int quads = hd >> 2;  // float4 per row
+    float4 pre[kPrefetch];
+    auto prefetch = [&](unsigned long long tile) {
+        const unsigned long long first = tile * kTileRows;
+#pragma unroll
+        for (unsigned int i = 0; i < kPrefetch; ++i) {
+            const unsigned int slot = threadIdx.x + i * kCsaScoreThreads;
+            const unsigned int r = slot / quads, c = slot % quads;
+            pre[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (tile < tiles && r < kTileRows && first + r < a.rows)
+                pre[i] = __ldg(reinterpret_cast<const float4 *>(a.keys + (first + r) * a.key_stride) + c);
+        }
+    };
+    if (vector_path) prefetch(blockIdx.x);
     for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const unsigned long long first = tile * kTileRows;
         __syncthreads();  // the previous tile's sums are done with the shared region; q is written
@@ -76,15 +96,38 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
             visible[threadIdx.x] = candidate;
         }
         __syncthreads();
-        for (unsigned int i = threadIdx.x; i < kTileRows * hd; i += blockDim.x) {
-            const unsigned int r = i / hd, lane = i % hd;
-            float k = 0.0f;
-            if (visible[r]) {
-                k = __ldg(a.keys + (first + r) * a.key_stride + lane);
-                finite = finite && isfinite(k);
-                any_candidate = true;
+        if (vector_path) {
+#pragma unroll
+            for (unsigned int i = 0; i < kPrefetch; ++i) {
+                const unsigned int slot = threadIdx.x + i * kCsaScoreThreads;
+                const unsigned int r = slot / quads, c = slot % quads;
+                if (r < kTileRows) {
+                    float4 k = pre[i];
+                    if (visible[r]) {
+                        finite = finite && isfinite(k.x) && isfinite(k.y) && isfinite(k.z) && isfinite(k.w);
+                        any_candidate = true;
+                    } else {
+                        k = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    }
+                    double *dst = keys + r * kp + 4u * c;
+                    dst[0] = (double)k.x;
+                    dst[1] = (double)k.y;
+                    dst[2] = (double)k.z;
+                    dst[3] = (double)k.w;
+                }
             }
-            keys[r * kp + lane] = (double)k;
+            prefetch(tile + gridDim.x);
+        } else {
+            for (unsigned int i = threadIdx.x; i < kTileRows * hd; i += blockDim.x) {
+                const unsigned int r = i / hd, lane = i % hd;
+                float k = 0.0f;
+                if (visible[r]) {
+                    k = __ldg(a.keys + (first + r) * a.key_stride + lane);
+                    finite = finite && isfinite(k);
+                    any_candidate = true;
+                }
+                keys[r * kp + lane] = (double)k;
+            }
         }
         __syncthreads();
         double acc[4][RT];
@@ -139,23 +182,61 @@ __device__ __forceinline__ unsigned long long csa_key(float score, unsigned int 
     return ((unsigned long long)(~u) << 32) | row;
 }
 
+// Bitonic sort of keys[4096] (ascending) by 1024 threads. A thread keeps four
+// consecutive keys in registers: strides 1 and 2 are exchanges inside the thread,
+// strides 4..64 reach a lane of the same warp by shuffle, and only strides >= 128 go
+// through shared memory (15 of the 78 steps), so the CTA meets at 2 * 15 barriers.
 __device__ __forceinline__ void csa_sort_4096(unsigned long long *keys)
 {
+    const unsigned int t = threadIdx.x;
+    __syncthreads();
+    ulonglong2 lo = reinterpret_cast<const ulonglong2 *>(keys)[2u * t];
+    ulonglong2 hi = reinterpret_cast<const ulonglong2 *>(keys)[2u * t + 1u];
+    unsigned long long e[4] = {lo.x, lo.y, hi.x, hi.y};
+    auto order = [](unsigned long long &x, unsigned long long &y, bool ascending) {
+        const unsigned long long small = x < y ? x : y, large = x < y ? y : x;
+        x = ascending ? small : large;
+        y = ascending ? large : small;
+    };
     for (unsigned int size = 2; size <= (unsigned int)kCsaSortKeys; size <<= 1) {
         for (unsigned int stride = size >> 1; stride > 0; stride >>= 1) {
-            __syncthreads();
-            for (unsigned int t = threadIdx.x; t < (unsigned int)kCsaSortKeys / 2; t += blockDim.x) {
-                const unsigned int low = 2u * t - (t & (stride - 1u));
-                const unsigned int high = low + stride;
-                const bool ascending = (low & size) == 0u;
-                const unsigned long long x = keys[low], y = keys[high];
-                if ((x > y) == ascending) {
-                    keys[low] = y;
-                    keys[high] = x;
+            if (stride >= 4u) {
+                unsigned long long other[4];
+                if (stride >= 128u) {
+                    __syncthreads();  // partners have read the previous contents
+                    reinterpret_cast<ulonglong2 *>(keys)[2u * t] = make_ulonglong2(e[0], e[1]);
+                    reinterpret_cast<ulonglong2 *>(keys)[2u * t + 1u] = make_ulonglong2(e[2], e[3]);
+                    __syncthreads();
+                    const unsigned int partner = t ^ (stride >> 2);
+                    lo = reinterpret_cast<const ulonglong2 *>(keys)[2u * partner];
+                    hi = reinterpret_cast<const ulonglong2 *>(keys)[2u * partner + 1u];
+                    other[0] = lo.x, other[1] = lo.y, other[2] = hi.x, other[3] = hi.y;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, e[i], stride >> 2);
                 }
+                const unsigned int idx = 4u * t;  // bits >= 2 are the same for the four keys
+                const bool keep_small = ((idx & stride) == 0u) == ((idx & size) == 0u);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const bool mine_small = e[i] < other[i];
+                    e[i] = keep_small == mine_small ? e[i] : other[i];
+                }
+            } else if (stride == 2u) {
+                const bool ascending = ((4u * t) & size) == 0u;  // size >= 4 here
+                order(e[0], e[2], ascending);
+                order(e[1], e[3], ascending);
+            } else {
+                const bool first = size == 2u ? true : ((4u * t) & size) == 0u;
+                const bool second = size == 2u ? false : first;
+                order(e[0], e[1], first);
+                order(e[2], e[3], second);
             }
         }
     }
+    __syncthreads();
+    reinterpret_cast<ulonglong2 *>(keys)[2u * t] = make_ulonglong2(e[0], e[1]);
+    reinterpret_cast<ulonglong2 *>(keys)[2u * t + 1u] = make_ulonglong2(e[2], e[3]);
     __syncthreads();
 }
 
@@ -165,7 +246,7 @@ __device__ __forceinline__ void csa_sort_4096(unsigned long long *keys)
 __global__ void __launch_bounds__(kCsaSortThreads)
 csa_rank_rows_kernel(const yvx_csa_select_args a, unsigned long long *level, unsigned int chunks)
 {
-    __shared__ unsigned long long keys[kCsaSortKeys];
+    __shared__ __align__(16) unsigned long long keys[kCsaSortKeys];
     const unsigned long long token = blockIdx.y;
     const unsigned long long query_position = a.phase_start_position + token;
     const unsigned long long first = (unsigned long long)blockIdx.x * kCsaSortKeys;
@@ -199,7 +280,7 @@ __global__ void __launch_bounds__(kCsaSortThreads)
 csa_rank_lists_kernel(const yvx_csa_select_args a, const unsigned long long *from, unsigned int lists,
                       unsigned long long *to, unsigned int groups, unsigned int fan_in)
 {
-    __shared__ unsigned long long keys[kCsaSortKeys];
+    __shared__ __align__(16) unsigned long long keys[kCsaSortKeys];
     const unsigned long long token = blockIdx.y;
     const unsigned int first_list = blockIdx.x * fan_in;
     const unsigned int mine_lists = min(fan_in, lists - first_list);

@@ -7,16 +7,23 @@
 // 259-406 in the reference: one CTA per (token, head), two block barriers per
 // candidate row, output accumulated in global memory, every head re-reading the
 // shared rows). Here one warp owns a (token, head) pair with the query and the
-// accumulator in registers, eight heads of a token share a CTA so a row fetched
-// once from L2 serves eight heads, and the softmax state never leaves the warp.
-// Row visibility and the published value (quotient rounded to bf16, stored as
-// F32) are the reference's; the reference's output rotation and second
-// publication (src/graph/core.c:498-507) can be fused into the epilogue.
+// accumulator in registers and eight heads of a token share a CTA. The CTA
+// resolves a chunk of candidates to row pointers, brings the whole chunk into
+// shared memory with asynchronous 16-byte copies (one memory latency per chunk
+// instead of one per row, the next chunk in flight while the warps work on the
+// current one), and each warp walks the rows from shared memory. A decode step
+// has too few (token, head) pairs to fill the GPU, so the candidate list is also
+// split across CTAs; the partial (m, l, acc) states are folded by a second small
+// launch that also publishes. Row visibility and the published value (quotient
+// rounded to bf16, stored as F32) are the reference's; the reference's output
+// rotation and second publication (src/graph/core.c:498-507) can be fused into
+// the epilogue.
 #include "common.cuh"
 
 namespace yvx {
 
 constexpr int kLatentWarps = 8;
+constexpr int kLatentBufferFloats = 8192;  // one staging buffer: 32 KB, two of them
 
 __device__ __forceinline__ const float *latent_visible_row(const yvx_latent_reduce_args &a,
                                                            unsigned int pass,
@@ -44,83 +51,16 @@ __device__ __forceinline__ const float *latent_visible_row(const yvx_latent_redu
     return a.compressed + index * a.compressed_stride;
 }
 
-// grid: x = head tile (8 heads), y = token. SLOTS * 32 >= head_dim.
+// Publication of one (token, head): quotient, bf16, and with rope_frequency the
+// reference's inverse rotation (rope_apply with inverse = 1) and second publication.
+// Rotated pairs are adjacent lanes, so the partner sits in the neighbouring lane of the
+// same slot; the branch around the shuffle is uniform per slot.
 template <int SLOTS>
-__global__ void __launch_bounds__(kLatentWarps * 32)
-latent_reduce_kernel(const yvx_latent_reduce_args a)
+__device__ __forceinline__ void latent_publish(const yvx_latent_reduce_args &a, unsigned long long ordinal,
+                                               unsigned long long head, unsigned int lane,
+                                               const float (&acc)[SLOTS], float l)
 {
-    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const unsigned long long ordinal = blockIdx.y;
-    const unsigned long long head = (unsigned long long)blockIdx.x * kLatentWarps + warp;
-    if (head >= a.query_heads) return;
     const unsigned long long token_position = a.phase_start_position + ordinal;
-    unsigned long long local_offset, local_count;
-    if (a.candidate_block_visible) {
-        local_offset = 0ull;
-        local_count = a.initial_local_count + a.token_count;
-    } else {
-        const unsigned long long before = a.initial_local_count + ordinal;
-        const unsigned long long history =
-            token_position < a.sliding_window - 1ull ? token_position : a.sliding_window - 1ull;
-        if (history > before) {
-            if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
-            return;
-        }
-        local_offset = before - history;
-        local_count = history + 1ull;
-    }
-    const unsigned long long compressed_count =
-        a.attention_class == 0u ? 0ull
-        : a.attention_class == 1u
-            ? a.selected_count[ordinal]
-            : token_position / a.ratio + ((token_position + 1ull) % a.ratio == 0ull);
-
-    const float log2e = 1.4426950408889634f;
-    const float scale = rsqrtf((float)a.head_dim) * log2e;  // scores in log2 units
-    const float *q = a.query + (ordinal * a.query_heads + head) * a.head_dim;
-    float qr[SLOTS], acc[SLOTS];
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) {
-        const unsigned long long d = lane + 32ull * s;
-        qr[s] = d < a.head_dim ? q[d] * scale : 0.0f;
-        acc[s] = 0.0f;
-    }
-    float m = a.sinks[head] * log2e, l = 1.0f;  // the sink seeds the maximum and the denominator
-    bool finite = isfinite(m);
-    for (unsigned int pass = 0; pass < 2u; ++pass) {
-        const unsigned long long count = pass == 0u ? local_count : compressed_count;
-        for (unsigned long long candidate = 0; candidate < count; ++candidate) {
-            const float *row = latent_visible_row(a, pass, ordinal, candidate, local_offset);
-            if (!row) continue;  // identical on every lane
-            float r[SLOTS], dot = 0.0f;
-#pragma unroll
-            for (int s = 0; s < SLOTS; ++s) {
-                const unsigned long long d = lane + 32ull * s;
-                r[s] = d < a.head_dim ? row[d] : 0.0f;
-                dot = fmaf(qr[s], r[s], dot);
-            }
-            dot = warp_sum(dot);
-            finite = finite && isfinite(dot);
-            if (dot <= m) {
-                float w;
-                asm("ex2.approx.f32 %0, %1;" : "=f"(w) : "f"(dot - m));
-                l += w;
-#pragma unroll
-                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(w, r[s], acc[s]);
-            } else {
-                float keep;
-                asm("ex2.approx.f32 %0, %1;" : "=f"(keep) : "f"(m - dot));
-                l = fmaf(l, keep, 1.0f);
-#pragma unroll
-                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(acc[s], keep, r[s]);
-                m = dot;
-            }
-        }
-    }
-    if (!finite || !isfinite(l) || l <= 0.0f) {
-        if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
-        return;
-    }
     float *out = a.out + (ordinal * a.query_heads + head) * a.head_dim;
     const unsigned long long rope_start = a.rope_frequency ? a.head_dim - a.rope_dims : a.head_dim;
     bool published_finite = true;
@@ -130,9 +70,6 @@ latent_reduce_kernel(const yvx_latent_reduce_args a)
         float published = acc[s] / l;
         published_finite = published_finite && isfinite(published);
         published = __uint_as_float((uint32_t)bf16_bits_rne(published) << 16);
-        // Output rotation of the reference (rope_apply with inverse = 1, then the second
-        // publication): pairs are adjacent lanes, so the partner sits in the neighbouring
-        // lane of the same slot. Uniform per slot: every lane reaches the shuffle.
         if (rope_start < a.head_dim && 32ull * s + 32ull > rope_start) {
             const float partner = __shfl_xor_sync(0xffffffffu, published, 1);
             if (d >= rope_start && d < a.head_dim) {
@@ -158,9 +95,291 @@ latent_reduce_kernel(const yvx_latent_reduce_args a)
     }
 }
 
-}  // namespace yvx
+__device__ __forceinline__ void latent_copy16(float *dst, const float *src)
+{
+    const unsigned int smem = (unsigned int)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(src) : "memory");
+}
 
-extern "C" int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *a, void *stream)
+// grid: x = head tile (8 heads), y = token, z = split of the candidate list.
+// SLOTS * 32 >= head_dim. Split z of a token covers candidates
+// [z * per_split, (z + 1) * per_split) of the list "local rows, then compressed rows".
+// splits == 1: publishes. Otherwise writes (acc[head_dim], m, l) to
+// partials[((token * heads + head) * splits + z) * (head_dim + 2)].
+template <int SLOTS>
+__global__ void __launch_bounds__(kLatentWarps * 32)
+latent_reduce_kernel(const yvx_latent_reduce_args a, const unsigned int splits,
+                     const unsigned long long per_split, float *partials)
+{
+    constexpr unsigned int kRowFloats = SLOTS * 32;
+    constexpr unsigned int kChunkRows = kLatentBufferFloats / kRowFloats;
+    extern __shared__ __align__(16) float staged[];             // [2][kChunkRows][kRowFloats]
+    __shared__ const float *row_of[2][kChunkRows];
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned long long ordinal = blockIdx.y;
+    const unsigned long long head = (unsigned long long)blockIdx.x * kLatentWarps + warp;
+    const bool owner = head < a.query_heads;
+    const unsigned long long token_position = a.phase_start_position + ordinal;
+    unsigned long long local_offset, local_count;
+    if (a.candidate_block_visible) {
+        local_offset = 0ull;
+        local_count = a.initial_local_count + a.token_count;
+    } else {
+        const unsigned long long before = a.initial_local_count + ordinal;
+        const unsigned long long history =
+            token_position < a.sliding_window - 1ull ? token_position : a.sliding_window - 1ull;
+        if (history > before) {  // uniform over the CTA
+            if (threadIdx.x == 0) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
+            return;
+        }
+        local_offset = before - history;
+        local_count = history + 1ull;
+    }
+    const unsigned long long compressed_count =
+        a.attention_class == 0u ? 0ull
+        : a.attention_class == 1u
+            ? a.selected_count[ordinal]
+            : token_position / a.ratio + ((token_position + 1ull) % a.ratio == 0ull);
+    const unsigned long long total = local_count + compressed_count;
+    const unsigned long long begin = min((unsigned long long)blockIdx.z * per_split, total);
+    const unsigned long long end = min(begin + per_split, total);
+
+    const float log2e = 1.4426950408889634f;
+    const float scale = rsqrtf((float)a.head_dim) * log2e;  // scores in log2 units
+    float qr[SLOTS], acc[SLOTS];
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const unsigned long long d = lane + 32ull * s;
+        qr[s] = owner && d < a.head_dim ? a.query[(ordinal * a.query_heads + head) * a.head_dim + d] * scale : 0.0f;
+        acc[s] = 0.0f;
+    }
+    // the sink seeds the maximum and the denominator of the first split
+    float m = -INFINITY, l = 0.0f;
+    bool finite = true;
+    if (blockIdx.z == 0u && owner) {
+        m = a.sinks[head] * log2e;
+        l = 1.0f;
+        finite = isfinite(m);
+    }
+    // 16-byte copies need aligned rows; otherwise the rows are copied float by float
+    const bool vector_rows =
+        (a.head_dim & 3ull) == 0ull && (a.local_stride & 3ull) == 0ull &&
+        (reinterpret_cast<unsigned long long>(a.local) & 15ull) == 0ull &&
+        (a.attention_class == 0u || ((a.compressed_stride & 3ull) == 0ull &&
+                                     (reinterpret_cast<unsigned long long>(a.compressed) & 15ull) == 0ull));
+    const unsigned int chunks = (unsigned int)((end - begin + kChunkRows - 1u) / kChunkRows);
+
+    auto resolve = [&](unsigned int chunk) {  // candidates of a chunk -> row pointers
+        if (threadIdx.x < kChunkRows) {
+            const unsigned long long c = begin + (unsigned long long)chunk * kChunkRows + threadIdx.x;
+            const float *row = nullptr;
+            if (c < end)
+                row = c < local_count ? latent_visible_row(a, 0u, ordinal, c, local_offset)
+                                      : latent_visible_row(a, 1u, ordinal, c - local_count, local_offset);
+            row_of[chunk & 1u][threadIdx.x] = row;
+        }
+    };
+    auto stage = [&](unsigned int chunk) {  // asynchronous copy of the chunk's rows
+        float *buffer = staged + (chunk & 1u) * kLatentBufferFloats;
+        if (vector_rows) {
+            const unsigned int quads = (unsigned int)(a.head_dim >> 2);
+            for (unsigned int i = threadIdx.x; i < kChunkRows * quads; i += blockDim.x) {
+                const unsigned int r = i / quads, c = i % quads;
+                const float *row = row_of[chunk & 1u][r];
+                if (row) latent_copy16(buffer + r * kRowFloats + 4u * c, row + 4u * c);
+            }
+        } else {
+            for (unsigned int i = threadIdx.x; i < kChunkRows * (unsigned int)a.head_dim; i += blockDim.x) {
+                const unsigned int r = i / (unsigned int)a.head_dim, c = i % (unsigned int)a.head_dim;
+                const float *row = row_of[chunk & 1u][r];
+                if (row) buffer[r * kRowFloats + c] = row[c];
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    if (chunks) {
+        resolve(0);
+        __syncthreads();
+        stage(0);
+    }
+    for (unsigned int chunk = 0; chunk < chunks; ++chunk) {
+        if (chunk + 1u < chunks) {
+            resolve(chunk + 1u);  // its buffer was released by the barrier that ended chunk - 1
+            __syncthreads();
+            stage(chunk + 1u);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();  // this chunk's rows are in shared memory for every warp
+        const float *buffer = staged + (chunk & 1u) * kLatentBufferFloats;
+        for (unsigned int r = 0; r < kChunkRows; ++r) {
+            if (!row_of[chunk & 1u][r]) continue;  // identical on every thread
+            const float *row = buffer + r * kRowFloats;
+            float v[SLOTS], dot = 0.0f;
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                const unsigned long long d = lane + 32ull * s;
+                v[s] = d < a.head_dim ? row[d] : 0.0f;
+                dot = fmaf(qr[s], v[s], dot);
+            }
+            dot = warp_sum(dot);
+            finite = finite && isfinite(dot);
+            if (dot <= m) {
+                float w;
+                asm("ex2.approx.f32 %0, %1;" : "=f"(w) : "f"(dot - m));
+                l += w;
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(w, v[s], acc[s]);
+            } else {
+                float keep;
+                asm("ex2.approx.f32 %0, %1;" : "=f"(keep) : "f"(m - dot));
+                l = fmaf(l, keep, 1.0f);
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(acc[s], keep, v[s]);
+                m = dot;
+            }
+        }
+        __syncthreads();  // every warp is done with this buffer
+    }
+    pdl_launch_dependents();
+    if (!owner) return;
+    if (!finite) {
+        if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+        return;
+    }
+    if (splits == 1u) {
+        if (!isfinite(l) || l <= 0.0f) {
+            if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+            return;
+        }
+        latent_publish<SLOTS>(a, ordinal, head, lane, acc, l);
+        return;
+    }
+    float *part = partials + ((ordinal * a.query_heads + head) * splits + blockIdx.z) * (a.head_dim + 2ull);
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+        const unsigned long long d = lane + 32ull * s;
+        if (d < a.head_dim) part[d] = acc[s];
+    }
+    if (lane == 0) {
+        part[a.head_dim] = m;
+        part[a.head_dim + 1ull] = l;
+    }
+}
+
+// Folds the splits of a (token, head) in split order and publishes. grid: x = head tile,
+// y = token; one warp per head.
+template <int SLOTS>
+__global__ void __launch_bounds__(kLatentWarps * 32)
+latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, const float *partials)
+{
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned long long ordinal = blockIdx.y;
+    const unsigned long long head = (unsigned long long)blockIdx.x * kLatentWarps + warp;
+    pdl_wait();
+    if (head >= a.query_heads) return;
+    // a split that refused leaves its partial unwritten: nothing to publish
+    if (*reinterpret_cast<volatile int *>(a.status) != YVX_STATUS_OK) return;
+    const unsigned long long width = a.head_dim + 2ull;
+    const float *part = partials + (ordinal * a.query_heads + head) * splits * width;
+    float m = -INFINITY;
+    for (unsigned int i = lane; i < splits; i += 32u) m = fmaxf(m, __ldcg(part + i * width + a.head_dim));
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, offset));
+    float acc[SLOTS], l = 0.0f;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) acc[s] = 0.0f;
+    for (unsigned int i = 0; i < splits; ++i) {
+        const float *p = part + i * width;
+        const float mi = __ldcg(p + a.head_dim), li = __ldcg(p + a.head_dim + 1ull);
+        if (li == 0.0f) continue;  // a split without visible rows (uniform over the warp)
+        float w;
+        asm("ex2.approx.f32 %0, %1;" : "=f"(w) : "f"(mi - m));
+        l = fmaf(li, w, l);
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const unsigned long long d = lane + 32ull * s;
+            if (d < a.head_dim) acc[s] = fmaf(__ldcg(p + d), w, acc[s]);
+        }
+    }
+    if (!isfinite(l) || l <= 0.0f) {
+        if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+        return;
+    }
+    latent_publish<SLOTS>(a, ordinal, head, lane, acc, l);
+}
+
+struct latent_plan {
+    unsigned int splits;
+    unsigned long long per_split;
+};
+
+// Deterministic in the arguments and the SM count: enough CTAs for two per SM, splits
+// of whole staging chunks, never more splits than chunks in the longest candidate list.
+static latent_plan latent_make_plan(const yvx_latent_reduce_args &a, int sms)
+{
+    const unsigned int slots = a.head_dim <= 128ull ? 4u : a.head_dim <= 256ull ? 8u : 16u;
+    const unsigned long long chunk_rows = kLatentBufferFloats / (slots * 32u);
+    const unsigned long long rows_local = a.initial_local_count + a.token_count;
+    const unsigned long long max_local =
+        a.candidate_block_visible || rows_local < a.sliding_window ? rows_local : a.sliding_window;
+    const unsigned long long last = a.phase_start_position + a.token_count - 1ull;
+    const unsigned long long max_compressed =
+        a.attention_class == 0u ? 0ull : a.attention_class == 1u ? a.topk_capacity : last / a.ratio + 1ull;
+    const unsigned long long max_total = max_local + max_compressed ? max_local + max_compressed : 1ull;
+    const unsigned long long tiles = (a.query_heads + kLatentWarps - 1) / kLatentWarps * a.token_count;
+    unsigned long long splits = (2ull * (unsigned long long)sms + tiles - 1ull) / tiles;
+    const unsigned long long max_splits = (max_total + chunk_rows - 1ull) / chunk_rows;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1ull) splits = 1ull;
+    unsigned long long per_split = (max_total + splits - 1ull) / splits;
+    per_split = (per_split + chunk_rows - 1ull) / chunk_rows * chunk_rows;
+    splits = (max_total + per_split - 1ull) / per_split;
+    latent_plan plan = {(unsigned int)splits, per_split};
+    return plan;
+}
+
+static int latent_sm_count()
+{
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    return sms;
+}
+
+template <int SLOTS>
+static int latent_launch(const yvx_latent_reduce_args &a, cudaStream_t s, unsigned int *launches)
+{
+    latent_plan plan = {1u, ~0ull >> 1};
+    if (a.workspace) plan = latent_make_plan(a, latent_sm_count());
+    if (plan.splits == 1u) plan.per_split = ~0ull >> 1;
+    const size_t smem = 2u * kLatentBufferFloats * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(latent_reduce_kernel<SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return yvx_cuda_check(e, "latent_reduce_kernel attribute");
+    const unsigned int tiles = (unsigned int)((a.query_heads + kLatentWarps - 1) / kLatentWarps);
+    latent_reduce_kernel<SLOTS><<<dim3(tiles, (unsigned int)a.token_count, plan.splits), kLatentWarps * 32, smem, s>>>(
+        a, plan.splits, plan.per_split, (float *)a.workspace);
+    if (launches) *launches = 1u;
+    if (plan.splits > 1u) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(tiles, (unsigned int)a.token_count, 1);
+        config.blockDim = dim3(kLatentWarps * 32, 1, 1);
+        config.stream = s;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attribute[0].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        e = cudaLaunchKernelEx(&config, latent_fold_kernel<SLOTS>, a, plan.splits, (const float *)a.workspace);
+        if (e != cudaSuccess) return yvx_cuda_check(e, "latent_fold_kernel");
+        if (launches) *launches = 2u;
+    }
+    return yvx_cuda_check(cudaGetLastError(), "latent_reduce_kernel");
+}
+
+static int latent_admit(const yvx_latent_reduce_args *a)
 {
     // Admission mirrors the reference kernel's contract checks (attention_kernels.cu:291-306).
     if (!a || !a->query || !a->local || !a->local_positions || !a->sinks || !a->out || !a->status ||
@@ -180,14 +399,31 @@ extern "C" int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *a, void *str
          ((a->head_dim - a->rope_dims) & 1ull)))
         return YVEX_ERR_INVALID_ARG;
     if (a->head_dim > 512ull || a->token_count > 65535ull) return YVEX_ERR_UNSUPPORTED;
-    const dim3 grid((unsigned int)((a->query_heads + yvx::kLatentWarps - 1) / yvx::kLatentWarps),
-                    (unsigned int)a->token_count);
+    return 0;
+}
+
+}  // namespace yvx
+
+extern "C" unsigned long long yvx_cuda_latent_reduce_workspace_bytes(const yvx_latent_reduce_args *a)
+{
+    if (yvx::latent_admit(a) != 0) return 0ull;
+    const yvx::latent_plan plan = yvx::latent_make_plan(*a, yvx::latent_sm_count());
+    if (plan.splits <= 1u) return 0ull;
+    return a->token_count * a->query_heads * plan.splits * (a->head_dim + 2ull) * sizeof(float);
+}
+
+extern "C" int yvx_cuda_latent_reduce_launches(const yvx_latent_reduce_args *a, void *stream, unsigned int *launches)
+{
+    if (launches) *launches = 0u;
+    const int admitted = yvx::latent_admit(a);
+    if (admitted != 0) return admitted;
     cudaStream_t s = (cudaStream_t)stream;
-    if (a->head_dim <= 128ull)
-        yvx::latent_reduce_kernel<4><<<grid, yvx::kLatentWarps * 32, 0, s>>>(*a);
-    else if (a->head_dim <= 256ull)
-        yvx::latent_reduce_kernel<8><<<grid, yvx::kLatentWarps * 32, 0, s>>>(*a);
-    else
-        yvx::latent_reduce_kernel<16><<<grid, yvx::kLatentWarps * 32, 0, s>>>(*a);
-    return yvx_cuda_check(cudaGetLastError(), "latent_reduce_kernel");
+    if (a->head_dim <= 128ull) return yvx::latent_launch<4>(*a, s, launches);
+    if (a->head_dim <= 256ull) return yvx::latent_launch<8>(*a, s, launches);
+    return yvx::latent_launch<16>(*a, s, launches);
+}
+
+extern "C" int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *a, void *stream)
+{
+    return yvx_cuda_latent_reduce_launches(a, stream, nullptr);
 }

@@ -55,7 +55,9 @@ int yvex_b200_attention_reduce_execute(yvex_backend *backend,
                                        yvex_backend_operation_facts *facts, yvex_error *err)
 {
     const char *where = "b200.attention.reduce";
-    unsigned long long width, local_rows, elements = 0ull;
+    unsigned long long width, local_rows, elements = 0ull, workspace;
+    unsigned int launches = 0u;
+    void *scratch = NULL;
     yvx_latent_reduce_args a;
     int rc;
     if (failure) memset(failure, 0, sizeof(*failure));
@@ -147,9 +149,20 @@ int yvex_b200_attention_reduce_execute(yvex_backend *backend,
         a.rope_dims = r->rope_dimension;
         a.rope_frequency = (const double *)r->rope_frequency->data;
     }
+    workspace = yvx_cuda_latent_reduce_workspace_bytes(&a);
+    rc = yvx_backend_scratch(backend, workspace, &scratch, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_ALLOCATION;
+            failure->stage = "reduce";
+            failure->expected = workspace;
+        }
+        return rc;
+    }
+    a.workspace = scratch;
     rc = yvx_backend_status_arm(backend, where, err);
     if (rc != YVEX_OK) return rc;
-    rc = yvx_cuda_latent_reduce(&a, backend->stream);
+    rc = yvx_cuda_latent_reduce_launches(&a, backend->stream, &launches);
     if (rc != 0) {
         if (failure) {
             failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
@@ -157,7 +170,7 @@ int yvex_b200_attention_reduce_execute(yvex_backend *backend,
         }
         return yvx_backend_device_fail(backend, rc, where, err);
     }
-    rc = finish(backend, facts, 1u, 0ull, where, err);
+    rc = finish(backend, facts, launches, workspace, where, err);
     if (rc != YVEX_OK) {
         if (failure) {
             failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC

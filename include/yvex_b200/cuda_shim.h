@@ -249,8 +249,18 @@ typedef struct yvx_latent_reduce_args {
     int *status;
     unsigned long long rope_dims;             /* used when rope_frequency != NULL */
     const double *rope_frequency;             /* [rope_dims/2] or NULL */
+    void *workspace;                          /* yvx_cuda_latent_reduce_workspace_bytes() bytes, or NULL */
 } yvx_latent_reduce_args;
+/* With a workspace the candidate list of a (token, head) is split over several CTAs when
+ * the phase alone cannot fill the GPU (decode, short verify phases) and a second launch
+ * folds the partial states and publishes; the split plan depends only on the arguments
+ * and the SM count. workspace == NULL: one launch, one CTA per (token, 8 heads).
+ * _workspace_bytes returns 0 when the plan has a single split (or the arguments are
+ * refused). _launches is yvx_cuda_latent_reduce that also reports the launch count. */
+unsigned long long yvx_cuda_latent_reduce_workspace_bytes(const yvx_latent_reduce_args *args);
 int yvx_cuda_latent_reduce(const yvx_latent_reduce_args *args, void *stream);
+int yvx_cuda_latent_reduce_launches(const yvx_latent_reduce_args *args, void *stream,
+                                    unsigned int *launches);
 
 /* ---- sparse index selection: scores + ranked top-k ---------------------------------
  * Replaces, for one phase, the reference's index scoring and top-k

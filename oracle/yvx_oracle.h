@@ -124,6 +124,7 @@ typedef struct {
     int *device_status;                       /* unused here */
     unsigned long long rope_dims;             /* 0: publish without the output rotation */
     const double *rope_frequency;             /* [rope_dims/2] radians per position */
+    void *device_workspace;                   /* unused here */
 } yvx_oracle_latent_args;
 int yvx_oracle_latent_reduce_full(const yvx_oracle_latent_args *args, float *out);
 

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 u64 = np.uint64
 
 
-def run_gpu(backend, case, block_visible=0):
+def run_gpu(backend, case, block_visible=0, workspace=True):
     t = {}
     for name in ("query", "local", "compressed", "sinks"):
         t[name] = backend.tensor(name, case[name])
@@ -31,8 +31,15 @@ def run_gpu(backend, case, block_visible=0):
                  "selected_count", "sinks"):
         setattr(a, name, t[name].data_ptr)
     a.out, a.status = out.data_ptr, status.data_ptr
-    rc = backend.lib.yvx_cuda_latent_reduce(C.byref(a), backend.stream)
+    if workspace:  # lets the library split the candidate list over CTAs (second launch folds)
+        nbytes = int(backend.lib.yvx_cuda_latent_reduce_workspace_bytes(C.byref(a)))
+        if nbytes:
+            a.workspace = backend.alloc("work", abi.DTYPE_I8, (nbytes,)).data_ptr
+    launches = C.c_uint()
+    rc = backend.lib.yvx_cuda_latent_reduce_launches(C.byref(a), backend.stream, C.byref(launches))
     assert rc == 0, backend.lib.yvx_cuda_last_error_text()
+    assert launches.value == (2 if a.workspace else 1)
+    run_gpu.launches = launches.value
     assert backend.lib.yvx_cuda_stream_synchronize(backend.stream) == 0
     out.struct.is_written = 1
     return out.read(), int(status.read()[0])
@@ -53,6 +60,28 @@ def test_reduce_matches_restatement(backend, oracle, cls, tokens, start):
     assert close(got, ref)
     # the published values are bf16-representable
     assert np.array_equal(got, clori_b200.bf16_bits_to_f32(clori_b200.f32_to_bf16_bits(got)))
+
+
+@pytest.mark.parametrize("cls", [0, 1, 2])
+def test_split_and_single_launch_agree(backend, oracle, cls):
+    rng = np.random.default_rng(77 + cls)
+    case = build(rng, heads=16, hd=512, window=128, attention_class=cls, tokens=2, start=5000)
+    split, status = run_gpu(backend, case)
+    assert status == 0 and run_gpu.launches == 2
+    single, status = run_gpu(backend, case, workspace=False)
+    assert status == 0 and run_gpu.launches == 1
+    ref = oracle.latent_reduce_full(host_args(case), 2, 16, 512)
+    assert close(split, ref) and close(single, ref) and close(split, single)
+    again, _ = run_gpu(backend, case)
+    assert np.array_equal(again, split)       # the split plan is deterministic
+
+
+def test_long_phase_needs_no_split(backend, oracle):
+    rng = np.random.default_rng(78)
+    case = build(rng, heads=16, hd=128, window=128, attention_class=2, tokens=200, start=900)
+    got, status = run_gpu(backend, case)
+    assert status == 0 and run_gpu.launches == 1
+    assert close(got, oracle.latent_reduce_full(host_args(case), 200, 16, 128))
 
 
 def test_candidate_block_visible_and_small_head(backend, oracle):

@@ -138,6 +138,9 @@ def run_reduce_rotated(backend, case, frequency):
         setattr(a, name, t[name].data_ptr)
     a.out, a.status = out.data_ptr, status.data_ptr
     a.rope_dims, a.rope_frequency = 2 * len(frequency), freq.data_ptr
+    nbytes = int(backend.lib.yvx_cuda_latent_reduce_workspace_bytes(C.byref(a)))
+    if nbytes:
+        a.workspace = backend.alloc("work", abi.DTYPE_I8, (nbytes,)).data_ptr
     assert backend.lib.yvx_cuda_latent_reduce(C.byref(a), backend.stream) == 0, backend.lib.yvx_cuda_last_error_text()
     assert backend.lib.yvx_cuda_stream_synchronize(backend.stream) == 0
     out.struct.is_written = 1
