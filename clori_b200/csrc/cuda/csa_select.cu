@@ -44,7 +44,7 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
     constexpr unsigned int kTileRows = (kCsaScoreThreads / 32) * 2 * RT;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const unsigned int heads = a.heads, hd = a.head_dim;
-    const unsigned int qp = hd + 1u, kp = max(hd + 2u, kCsaHeadSlots + 1u), dp = kCsaHeadSlots + 1u;
+    const unsigned int qp = hd + 1u, kp = max((hd + 3u) & ~1u, kCsaHeadSlots + 2u), dp = kCsaHeadSlots + 1u;
     double *q = reinterpret_cast<double *>(smem_raw);           // [64][qp]
     double *keys = q + kCsaHeadSlots * qp;                      // [kTileRows][kp]; reused as dots [kTileRows][dp]
     __shared__ unsigned char visible[kTileRows];
@@ -53,14 +53,25 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
     const float *query = a.query + token * heads * hd;
     const float *weights = a.weights + token * heads;
     bool finite = true, query_finite = true, any_candidate = false;
-    for (unsigned int i = threadIdx.x; i < kCsaHeadSlots * hd; i += blockDim.x) {
-        const unsigned int h = i / hd, lane = i % hd;
-        const float v = h < heads ? query[i] : 0.0f;
-        query_finite = query_finite && isfinite(v);
-        q[h * qp + lane] = (double)v;
+    for (unsigned int i0 = threadIdx.x; i0 < kCsaHeadSlots * hd; i0 += 8u * blockDim.x) {
+        float v[8];  // eight loads in flight per thread
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const unsigned int i = i0 + u * blockDim.x;
+            v[u] = i < heads * hd ? query[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const unsigned int i = i0 + u * blockDim.x;
+            if (i < kCsaHeadSlots * hd) {
+                query_finite = query_finite && isfinite(v[u]);
+                q[(i / hd) * qp + i % hd] = (double)v[u];
+            }
+        }
     }
     const unsigned int warp = threadIdx.x >> 5, hl = threadIdx.x & 15u, rl = (threadIdx.x >> 4) & 1u;
-    const unsigned int row0 = warp * 2u * RT + rl * RT;
+    // the two row lanes take alternate rows, one key pitch apart: distinct banks in one read
+    const unsigned int row0 = warp * 2u * RT + rl;
     const unsigned long long tiles = (a.rows + kTileRows - 1u) / kTileRows;
     // The tile after the current one travels through registers while the current one is
     // being scored, so its load latency hides behind the FP64 work. kPrefetch float4 per
@@ -70,18 +81,35 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
                              (reinterpret_cast<unsigned long long>(a.keys) & 15ull) == 0ull;
     const unsigned int quads = hd >> 2;  // float4 per row
     float4 pre[kPrefetch];
+    unsigned long long pre_position = 0ull, pre_before = 0ull;  // positions[row], positions[row - 1]
+    // Volatile loads: they must be issued here, ahead of the scoring loop, not sunk to their use.
     auto prefetch = [&](unsigned long long tile) {
         const unsigned long long first = tile * kTileRows;
+        if (threadIdx.x < kTileRows && tile < tiles && first + threadIdx.x < a.rows) {
+            const unsigned long long *p = a.positions + first + threadIdx.x;
+            asm volatile("ld.global.nc.u64 %0, [%1];" : "=l"(pre_position) : "l"(p));
+            if (first + threadIdx.x > 0ull) asm volatile("ld.global.nc.u64 %0, [%1];" : "=l"(pre_before) : "l"(p - 1));
+        }
+        if (!vector_path) return;
 #pragma unroll
         for (unsigned int i = 0; i < kPrefetch; ++i) {
             const unsigned int slot = threadIdx.x + i * kCsaScoreThreads;
             const unsigned int r = slot / quads, c = slot % quads;
             pre[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (tile < tiles && r < kTileRows && first + r < a.rows)
-                pre[i] = __ldg(reinterpret_cast<const float4 *>(a.keys + (first + r) * a.key_stride) + c);
+            if (tile < tiles && r < kTileRows && first + r < a.rows) {
+                const float4 *p = reinterpret_cast<const float4 *>(a.keys + (first + r) * a.key_stride) + c;
+                asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(pre[i].x), "=f"(pre[i].y), "=f"(pre[i].z), "=f"(pre[i].w) : "l"(p));
+            }
         }
     };
-    if (vector_path) prefetch(blockIdx.x);
+    float weight[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const unsigned int h = hl + 16u * j;
+        weight[j] = h < heads ? weights[h] : 0.0f;
+    }
+    prefetch(blockIdx.x);
     for (unsigned long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const unsigned long long first = tile * kTileRows;
         __syncthreads();  // the previous tile's sums are done with the shared region; q is written
@@ -89,9 +117,8 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
             const unsigned long long row = first + threadIdx.x;
             bool candidate = false;
             if (row < a.rows) {
-                const unsigned long long position = a.positions[row];
-                if (row > 0ull && a.positions[row - 1ull] >= position) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
-                candidate = csa_candidate(position, a.ratio, query_position);
+                if (row > 0ull && pre_before >= pre_position) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
+                candidate = csa_candidate(pre_position, a.ratio, query_position);
             }
             visible[threadIdx.x] = candidate;
         }
@@ -109,14 +136,11 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
                     } else {
                         k = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     }
-                    double *dst = keys + r * kp + 4u * c;
-                    dst[0] = (double)k.x;
-                    dst[1] = (double)k.y;
-                    dst[2] = (double)k.z;
-                    dst[3] = (double)k.w;
+                    double2 *dst = reinterpret_cast<double2 *>(keys + r * kp + 4u * c);  // kp is even
+                    dst[0] = make_double2((double)k.x, (double)k.y);
+                    dst[1] = make_double2((double)k.z, (double)k.w);
                 }
             }
-            prefetch(tile + gridDim.x);
         } else {
             for (unsigned int i = threadIdx.x; i < kTileRows * hd; i += blockDim.x) {
                 const unsigned int r = i / hd, lane = i % hd;
@@ -129,6 +153,7 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
                 keys[r * kp + lane] = (double)k;
             }
         }
+        prefetch(tile + gridDim.x);
         __syncthreads();
         double acc[4][RT];
 #pragma unroll
@@ -142,7 +167,7 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
 #pragma unroll
             for (int j = 0; j < 4; ++j) qv[j] = qh[j * 16u * qp + lane];
 #pragma unroll
-            for (int r = 0; r < RT; ++r) kv[r] = kr[r * kp + lane];
+            for (int r = 0; r < RT; ++r) kv[r] = kr[2u * r * kp + lane];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -153,11 +178,10 @@ csa_score_kernel(const yvx_csa_select_args a, const double inv_sqrt_dim, const d
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const unsigned int h = hl + 16u * j;
-            const float w = h < heads ? weights[h] : 0.0f;
-            finite = finite && isfinite(w);
+            finite = finite && isfinite(weight[j]);
 #pragma unroll
             for (int r = 0; r < RT; ++r)
-                dots[(row0 + r) * dp + h] = __dmul_rn(acc[j][r] < 0.0 ? 0.0 : acc[j][r], (double)w);
+                dots[(row0 + 2u * r) * dp + h] = __dmul_rn(acc[j][r] < 0.0 ? 0.0 : acc[j][r], (double)weight[j]);
         }
         __syncthreads();
         if (threadIdx.x < kTileRows && visible[threadIdx.x]) {
@@ -339,7 +363,8 @@ extern "C" int yvx_cuda_csa_select(const yvx_csa_select_args *a, void *stream, u
         // 8 rows per thread while the widened tile fits beside the widened query, else 4
         const bool wide = a->head_dim <= 128u;
         const unsigned int tile_rows = (yvx::kCsaScoreThreads / 32) * 2 * (wide ? 8 : 4);
-        const unsigned int kp = a->head_dim + 2u > yvx::kCsaHeadSlots + 1u ? a->head_dim + 2u : yvx::kCsaHeadSlots + 1u;
+        const unsigned int even = (a->head_dim + 3u) & ~1u;  // an even pitch >= head_dim + 2
+        const unsigned int kp = even > yvx::kCsaHeadSlots + 2u ? even : yvx::kCsaHeadSlots + 2u;
         const size_t smem = ((size_t)yvx::kCsaHeadSlots * (a->head_dim + 1u) + (size_t)tile_rows * kp) * sizeof(double);
         auto kernel = wide ? yvx::csa_score_kernel<8> : yvx::csa_score_kernel<4>;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -214,32 +214,50 @@ latent_reduce_kernel(const yvx_latent_reduce_args a, const unsigned int splits,
         }
         __syncthreads();  // this chunk's rows are in shared memory for every warp
         const float *buffer = staged + (chunk & 1u) * kLatentBufferFloats;
-        for (unsigned int r = 0; r < kChunkRows; ++r) {
-            if (!row_of[chunk & 1u][r]) continue;  // identical on every thread
-            const float *row = buffer + r * kRowFloats;
-            float v[SLOTS], dot = 0.0f;
+        // Four rows per step: four independent dot products and reductions in flight, one
+        // rescale of the running state per step.
+        for (unsigned int r0 = 0; r0 < kChunkRows; r0 += 4u) {
+            float v[4][SLOTS], dot[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const bool present = row_of[chunk & 1u][r0 + i] != nullptr;  // identical on every thread
+                const float *row = buffer + (r0 + i) * kRowFloats;
+                dot[i] = 0.0f;
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) {
+                    const unsigned long long d = lane + 32ull * s;
+                    v[i][s] = present && d < a.head_dim ? row[d] : 0.0f;
+                    dot[i] = fmaf(qr[s], v[i][s], dot[i]);
+                }
+            }
+#pragma unroll
+            for (int offset = 16; offset; offset >>= 1)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dot[i] += __shfl_xor_sync(0xffffffffu, dot[i], offset);
+            float top = m;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                finite = finite && isfinite(dot[i]);
+                if (row_of[chunk & 1u][r0 + i] == nullptr) dot[i] = -INFINITY;
+                top = fmaxf(top, dot[i]);
+            }
+            if (top == -INFINITY) continue;  // no row yet and no sink in this split
+            float keep, w[4];
+            asm("ex2.approx.f32 %0, %1;" : "=f"(keep) : "f"(m - top));  // 0 when m is still -inf
+            l *= keep;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                asm("ex2.approx.f32 %0, %1;" : "=f"(w[i]) : "f"(dot[i] - top));
+                l += w[i];
+            }
 #pragma unroll
             for (int s = 0; s < SLOTS; ++s) {
-                const unsigned long long d = lane + 32ull * s;
-                v[s] = d < a.head_dim ? row[d] : 0.0f;
-                dot = fmaf(qr[s], v[s], dot);
-            }
-            dot = warp_sum(dot);
-            finite = finite && isfinite(dot);
-            if (dot <= m) {
-                float w;
-                asm("ex2.approx.f32 %0, %1;" : "=f"(w) : "f"(dot - m));
-                l += w;
+                float x = acc[s] * keep;
 #pragma unroll
-                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(w, v[s], acc[s]);
-            } else {
-                float keep;
-                asm("ex2.approx.f32 %0, %1;" : "=f"(keep) : "f"(m - dot));
-                l = fmaf(l, keep, 1.0f);
-#pragma unroll
-                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(acc[s], keep, v[s]);
-                m = dot;
+                for (int i = 0; i < 4; ++i) x = fmaf(w[i], v[i][s], x);
+                acc[s] = x;
             }
+            m = top;
         }
         __syncthreads();  // every warp is done with this buffer
     }
@@ -291,19 +309,41 @@ latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, co
     float acc[SLOTS], l = 0.0f;
 #pragma unroll
     for (int s = 0; s < SLOTS; ++s) acc[s] = 0.0f;
-    for (unsigned int i = 0; i < splits; ++i) {
-        const float *p = part + i * width;
-        const float mi = __ldcg(p + a.head_dim), li = __ldcg(p + a.head_dim + 1ull);
-        if (li == 0.0f) continue;  // a split without visible rows (uniform over the warp)
-        float w;
-        asm("ex2.approx.f32 %0, %1;" : "=f"(w) : "f"(mi - m));
-        l = fmaf(li, w, l);
+    // Lane i owns the weight of split base + i; the rows of the splits are then read with
+    // loads that depend on nothing but the split index, so several are in flight at once.
+    for (unsigned int base = 0; base < splits; base += 32u) {
+        const unsigned int mine = base + lane;
+        float w_lane = 0.0f;
+        if (mine < splits) {
+            const float mi = __ldcg(part + mine * width + a.head_dim);
+            const float li = __ldcg(part + mine * width + a.head_dim + 1ull);
+            asm("ex2.approx.f32 %0, %1;" : "=f"(w_lane) : "f"(mi - m));  // 0 for a split without rows
+            l = fmaf(li, w_lane, l);
+        }
+        const unsigned int count = min(32u, splits - base);
+        // kFoldBatch splits at a time: all their loads are issued before the first use
+        constexpr int kFoldBatch = SLOTS >= 16 ? 4 : 8;
+        for (unsigned int j0 = 0; j0 < count; j0 += kFoldBatch) {
+            float v[kFoldBatch][SLOTS], w[kFoldBatch];
 #pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const unsigned long long d = lane + 32ull * s;
-            if (d < a.head_dim) acc[s] = fmaf(__ldcg(p + d), w, acc[s]);
+            for (int j = 0; j < kFoldBatch; ++j) {
+                const bool live = j0 + j < count;
+                const float *p = part + (base + j0 + (live ? j : 0)) * width;
+                w[j] = __shfl_sync(0xffffffffu, w_lane, (j0 + j) & 31u);
+                if (!live) w[j] = 0.0f;
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) {
+                    const unsigned long long d = lane + 32ull * s;
+                    v[j][s] = d < a.head_dim ? __ldcg(p + d) : 0.0f;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kFoldBatch; ++j)
+#pragma unroll
+                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(v[j][s], w[j], acc[s]);
         }
     }
+    l = warp_sum(l);
     if (!isfinite(l) || l <= 0.0f) {
         if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
         return;
