@@ -8,13 +8,13 @@
 // product of two floats is exact in double, so the lane loop is one rounded add per
 // lane; the sum over heads is a rounded multiply and a rounded add per head), which
 // makes every float score bit-equal to the CPU result and the ranking a pure integer
-// problem: a 64-bit key of (inverted ordered score, row index) sorted ascending. Row
+// problem: 64-bit keys of (inverted ordered score, row index), smallest first. Row
 // index order is position order because positions are required to increase.
 #include "common.cuh"
 
 namespace yvx {
 
-constexpr int kCsaScoreThreads = 128;
+constexpr int kCsaScoreThreads = 256;  // two warps per scheduler hide the fixed FP64 and shared-memory latencies
 constexpr unsigned int kCsaHeadSlots = 64;  // heads <= 64; unused slots hold zeros
 constexpr int kCsaSortThreads = 1024;
 constexpr int kCsaSortKeys = 4096;  // keys one CTA ranks at a time
@@ -27,7 +27,7 @@ __device__ __forceinline__ bool csa_candidate(unsigned long long position, unsig
            position + ratio - 1ull <= query_position;
 }
 
-// Scores. grid: x = CTAs striding over row tiles, y = token; 4 warps. A warp owns all 64
+// Scores. grid: x = CTAs striding over row tiles, y = token; 8 warps. A warp owns all 64
 // head slots x 2*RT rows of the tile: lane = head lane (16) + 16 * row lane (2), a thread
 // accumulates heads {hl, hl+16, hl+32, hl+48} x RT rows, so one step of the lane loop costs
 // 4 + RT shared-memory reads for 4*RT fused multiply-adds and the FP64 pipe is the limit.
@@ -206,45 +206,115 @@ __device__ __forceinline__ unsigned long long csa_key(float score, unsigned int 
     return ((unsigned long long)(~u) << 32) | row;
 }
 
-// Bitonic sort of keys[4096] (ascending) by 1024 threads. A thread keeps four
-// consecutive keys in registers: strides 1 and 2 are exchanges inside the thread,
-// strides 4..64 reach a lane of the same warp by shuffle, and only strides >= 128 go
-// through shared memory (15 of the 78 steps), so the CTA meets at 2 * 15 barriers.
-__device__ __forceinline__ void csa_sort_4096(unsigned long long *keys)
+// Ranking. A CTA of 1024 threads holds 4096 keys, four per thread, in registers.
+// The k smallest are found without sorting everything: an 8-bit radix select from the
+// top byte down finds the k-th smallest key exactly (keys are unique: the low word is
+// the row), the keys up to it are compacted into shared memory, and only those k keys
+// are sorted, and only by the launch that publishes (earlier levels pass sets on).
+struct csa_rank_shared {
+    unsigned long long keys[1024];  // the kept keys
+    unsigned int histogram[256];
+    unsigned int digit, rank, kept;
+};
+
+// The need-th smallest (1-based) of the CTA's keys; need <= number of keys below kCsaAbsent.
+__device__ __forceinline__ unsigned long long csa_kth_smallest(const unsigned long long (&e)[4], unsigned int need,
+                                                               csa_rank_shared &sh)
+{
+    const unsigned int lane = threadIdx.x & 31u;
+    unsigned long long prefix = 0ull, decided = 0ull;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        if (threadIdx.x < 256u) sh.histogram[threadIdx.x] = 0u;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool in = (e[i] & decided) == prefix;
+            const unsigned int digit = (unsigned int)(e[i] >> shift) & 255u;
+            const unsigned int active = __ballot_sync(0xffffffffu, in);
+            if (in) {  // one shared-memory add per distinct digit in the warp
+                const unsigned int peers = __match_any_sync(active, digit);
+                if (lane == (unsigned int)__ffs(peers) - 1u) atomicAdd(&sh.histogram[digit], (unsigned int)__popc(peers));
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < 32u) {  // lane owns bins [8 lane, 8 lane + 8)
+            unsigned int bins[8], sum = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bins[j] = sh.histogram[8u * lane + j];
+                sum += bins[j];
+            }
+            unsigned int inclusive = sum;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1) {
+                const unsigned int below = __shfl_up_sync(0xffffffffu, inclusive, offset);
+                if (lane >= (unsigned int)offset) inclusive += below;
+            }
+            unsigned int run = inclusive - sum;
+            if (run < need && need <= inclusive) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (need > run && need <= run + bins[j]) {
+                        sh.digit = 8u * lane + j;
+                        sh.rank = need - run;
+                    }
+                    run += bins[j];
+                }
+            }
+        }
+        __syncthreads();
+        prefix |= (unsigned long long)sh.digit << shift;
+        decided |= 0xffull << shift;
+        need = sh.rank;
+    }
+    return prefix;
+}
+
+// Ascending bitonic sort of sh.keys[0 .. n), n a power of two in [4, 1024]. Thread t < n/4
+// keeps four consecutive keys in registers: strides 1 and 2 are exchanges inside the
+// thread, strides 4..64 reach a lane of the same warp by shuffle, strides >= 128 go through
+// shared memory. Every thread of the CTA calls it (the barriers are CTA-wide).
+__device__ __forceinline__ void csa_sort_kept(csa_rank_shared &sh, unsigned int n)
 {
     const unsigned int t = threadIdx.x;
-    __syncthreads();
-    ulonglong2 lo = reinterpret_cast<const ulonglong2 *>(keys)[2u * t];
-    ulonglong2 hi = reinterpret_cast<const ulonglong2 *>(keys)[2u * t + 1u];
-    unsigned long long e[4] = {lo.x, lo.y, hi.x, hi.y};
+    const bool holder = 4u * t < n;
+    const bool in_warp = t < max(n >> 2, 32u);  // whole warps take part in the shuffles
+    unsigned long long e[4] = {kCsaAbsent, kCsaAbsent, kCsaAbsent, kCsaAbsent};
+    if (holder) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) e[i] = sh.keys[4u * t + i];
+    }
     auto order = [](unsigned long long &x, unsigned long long &y, bool ascending) {
         const unsigned long long small = x < y ? x : y, large = x < y ? y : x;
         x = ascending ? small : large;
         y = ascending ? large : small;
     };
-    for (unsigned int size = 2; size <= (unsigned int)kCsaSortKeys; size <<= 1) {
+    for (unsigned int size = 2; size <= n; size <<= 1) {
         for (unsigned int stride = size >> 1; stride > 0; stride >>= 1) {
-            if (stride >= 4u) {
-                unsigned long long other[4];
-                if (stride >= 128u) {
-                    __syncthreads();  // partners have read the previous contents
-                    reinterpret_cast<ulonglong2 *>(keys)[2u * t] = make_ulonglong2(e[0], e[1]);
-                    reinterpret_cast<ulonglong2 *>(keys)[2u * t + 1u] = make_ulonglong2(e[2], e[3]);
-                    __syncthreads();
-                    const unsigned int partner = t ^ (stride >> 2);
-                    lo = reinterpret_cast<const ulonglong2 *>(keys)[2u * partner];
-                    hi = reinterpret_cast<const ulonglong2 *>(keys)[2u * partner + 1u];
-                    other[0] = lo.x, other[1] = lo.y, other[2] = hi.x, other[3] = hi.y;
-                } else {
+            if (stride >= 128u) {
+                __syncthreads();  // partners have read the previous contents
+                if (holder) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, e[i], stride >> 2);
+                    for (int i = 0; i < 4; ++i) sh.keys[4u * t + i] = e[i];
                 }
-                const unsigned int idx = 4u * t;  // bits >= 2 are the same for the four keys
-                const bool keep_small = ((idx & stride) == 0u) == ((idx & size) == 0u);
+                __syncthreads();
+                if (holder) {
+                    const unsigned int partner = t ^ (stride >> 2);
+                    const bool keep_small = (((4u * t) & stride) == 0u) == (((4u * t) & size) == 0u);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const unsigned long long other = sh.keys[4u * partner + i];
+                        e[i] = keep_small == (e[i] < other) ? e[i] : other;
+                    }
+                }
+            } else if (!in_warp) {
+                continue;
+            } else if (stride >= 4u) {
+                const bool keep_small = (((4u * t) & stride) == 0u) == (((4u * t) & size) == 0u);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const bool mine_small = e[i] < other[i];
-                    e[i] = keep_small == mine_small ? e[i] : other[i];
+                    const unsigned long long other = __shfl_xor_sync(0xffffffffu, e[i], stride >> 2);
+                    e[i] = keep_small == (e[i] < other) ? e[i] : other;
                 }
             } else if (stride == 2u) {
                 const bool ascending = ((4u * t) & size) == 0u;  // size >= 4 here
@@ -259,72 +329,98 @@ __device__ __forceinline__ void csa_sort_4096(unsigned long long *keys)
         }
     }
     __syncthreads();
-    reinterpret_cast<ulonglong2 *>(keys)[2u * t] = make_ulonglong2(e[0], e[1]);
-    reinterpret_cast<ulonglong2 *>(keys)[2u * t + 1u] = make_ulonglong2(e[2], e[3]);
+    if (holder) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sh.keys[4u * t + i] = e[i];
+    }
     __syncthreads();
 }
 
-// First level. grid: x = chunk of 4096 rows, y = token. Ranks the chunk's candidates and
-// keeps its best `keep` keys: straight into selected[] when the chunk is the only one,
-// else into level storage [token][chunk][keep].
+// The shared tail of both ranking kernels: keeps the smallest min(topk, present) of the
+// CTA's keys. publish: sorts them and writes the token's lists. Otherwise writes the set
+// (unsorted, padded with kCsaAbsent to topk keys) to `out`.
+__device__ __forceinline__ void csa_keep_smallest(const yvx_csa_select_args &a, const unsigned long long (&e)[4],
+                                                  unsigned long long token, bool publish, unsigned long long *out,
+                                                  csa_rank_shared &sh)
+{
+    unsigned int present = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) present += (unsigned int)__syncthreads_count(e[i] != kCsaAbsent);
+    const unsigned int keep = min(a.topk, present);
+    if (threadIdx.x == 0) sh.kept = 0u;
+    if (keep == 0u) {  // identical on every thread
+        if (publish) {
+            if (threadIdx.x == 0) a.selected_count[token] = 0ull;
+        } else {
+            for (unsigned int i = threadIdx.x; i < a.topk; i += blockDim.x) out[i] = kCsaAbsent;
+        }
+        return;
+    }
+    const unsigned long long threshold = csa_kth_smallest(e, keep, sh);  // its barriers also publish sh.kept = 0
+    const unsigned int lane = threadIdx.x & 31u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const bool kept = e[i] <= threshold;
+        const unsigned int mask = __ballot_sync(0xffffffffu, kept);
+        unsigned int base = 0u;
+        if (lane == 0u && mask) base = atomicAdd(&sh.kept, (unsigned int)__popc(mask));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (kept) sh.keys[base + __popc(mask & ((1u << lane) - 1u))] = e[i];
+    }
+    __syncthreads();
+    if (!publish) {
+        for (unsigned int i = threadIdx.x; i < a.topk; i += blockDim.x) out[i] = i < keep ? sh.keys[i] : kCsaAbsent;
+        return;
+    }
+    unsigned int n = 4u;
+    while (n < keep) n <<= 1;
+    for (unsigned int i = keep + threadIdx.x; i < n; i += blockDim.x) sh.keys[i] = kCsaAbsent;
+    __syncthreads();
+    csa_sort_kept(sh, n);
+    for (unsigned int i = threadIdx.x; i < keep; i += blockDim.x)
+        a.selected[token * a.topk_capacity + i] = sh.keys[i] & 0xffffffffull;
+    if (threadIdx.x == 0) a.selected_count[token] = (unsigned long long)keep;
+}
+
+// First level. grid: x = chunk of 4096 rows, y = token.
 __global__ void __launch_bounds__(kCsaSortThreads)
 csa_rank_rows_kernel(const yvx_csa_select_args a, unsigned long long *level, unsigned int chunks)
 {
-    __shared__ __align__(16) unsigned long long keys[kCsaSortKeys];
+    __shared__ csa_rank_shared sh;
     const unsigned long long token = blockIdx.y;
     const unsigned long long query_position = a.phase_start_position + token;
-    const unsigned long long first = (unsigned long long)blockIdx.x * kCsaSortKeys;
-    for (unsigned int i = threadIdx.x; i < (unsigned int)kCsaSortKeys; i += blockDim.x) {
+    const unsigned long long first = (unsigned long long)blockIdx.x * kCsaSortKeys + 4ull * threadIdx.x;
+    unsigned long long e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
         const unsigned long long row = first + i;
-        unsigned long long key = kCsaAbsent;
+        e[i] = kCsaAbsent;
         if (row < a.rows && csa_candidate(a.positions[row], a.ratio, query_position))
-            key = csa_key(a.scores[token * a.rows + row], (unsigned int)row);
-        keys[i] = key;
+            e[i] = csa_key(a.scores[token * a.rows + row], (unsigned int)row);
     }
-    csa_sort_4096(keys);
-    if (chunks == 1u) {
-        int mine = 0;
-        for (unsigned int i = threadIdx.x; i < a.topk; i += blockDim.x)
-            if (keys[i] != kCsaAbsent) {
-                a.selected[token * a.topk_capacity + i] = keys[i] & 0xffffffffull;
-                ++mine;
-            }
-        // topk <= 1024 = blockDim.x: every thread holds at most one key
-        const int count = __syncthreads_count(mine);
-        if (threadIdx.x == 0) a.selected_count[token] = (unsigned long long)count;
-    } else {
-        unsigned long long *out = level + (token * chunks + blockIdx.x) * a.topk;
-        for (unsigned int i = threadIdx.x; i < a.topk; i += blockDim.x) out[i] = keys[i];
-    }
+    csa_keep_smallest(a, e, token, chunks == 1u,
+                      chunks == 1u ? nullptr : level + (token * chunks + blockIdx.x) * a.topk, sh);
 }
 
-// Later levels. grid: x = group of fan_in lists, y = token. Merges up to fan_in ranked
-// lists of `topk` keys (fan_in * topk <= 4096) by ranking them together.
+// Later levels. grid: x = group of fan_in key sets, y = token. Keeps the smallest topk of
+// up to fan_in sets of topk keys (fan_in * topk <= 4096).
 __global__ void __launch_bounds__(kCsaSortThreads)
 csa_rank_lists_kernel(const yvx_csa_select_args a, const unsigned long long *from, unsigned int lists,
                       unsigned long long *to, unsigned int groups, unsigned int fan_in)
 {
-    __shared__ __align__(16) unsigned long long keys[kCsaSortKeys];
+    __shared__ csa_rank_shared sh;
     const unsigned long long token = blockIdx.y;
     const unsigned int first_list = blockIdx.x * fan_in;
     const unsigned int mine_lists = min(fan_in, lists - first_list);
     const unsigned long long *source = from + (token * lists + first_list) * a.topk;
-    for (unsigned int i = threadIdx.x; i < (unsigned int)kCsaSortKeys; i += blockDim.x)
-        keys[i] = i < mine_lists * a.topk ? source[i] : kCsaAbsent;
-    csa_sort_4096(keys);
-    if (groups == 1u) {
-        int mine = 0;
-        for (unsigned int i = threadIdx.x; i < a.topk; i += blockDim.x)
-            if (keys[i] != kCsaAbsent) {
-                a.selected[token * a.topk_capacity + i] = keys[i] & 0xffffffffull;
-                ++mine;
-            }
-        const int count = __syncthreads_count(mine);
-        if (threadIdx.x == 0) a.selected_count[token] = (unsigned long long)count;
-    } else {
-        unsigned long long *out = to + (token * groups + blockIdx.x) * a.topk;
-        for (unsigned int i = threadIdx.x; i < a.topk; i += blockDim.x) out[i] = keys[i];
+    unsigned long long e[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned int slot = 4u * threadIdx.x + i;
+        e[i] = slot < mine_lists * a.topk ? source[slot] : kCsaAbsent;
     }
+    csa_keep_smallest(a, e, token, groups == 1u,
+                      groups == 1u ? nullptr : to + (token * groups + blockIdx.x) * a.topk, sh);
 }
 
 static unsigned long long csa_chunks(unsigned long long rows)
@@ -360,13 +456,13 @@ extern "C" int yvx_cuda_csa_select(const yvx_csa_select_args *a, void *stream, u
     cudaStream_t s = (cudaStream_t)stream;
     unsigned int count = 0u;
     {
-        // 8 rows per thread while the widened tile fits beside the widened query, else 4
+        // 8 rows per thread while the widened tile fits beside the widened query, else 2
         const bool wide = a->head_dim <= 128u;
-        const unsigned int tile_rows = (yvx::kCsaScoreThreads / 32) * 2 * (wide ? 8 : 4);
+        const unsigned int tile_rows = (yvx::kCsaScoreThreads / 32) * 2 * (wide ? 8 : 2);
         const unsigned int even = (a->head_dim + 3u) & ~1u;  // an even pitch >= head_dim + 2
         const unsigned int kp = even > yvx::kCsaHeadSlots + 2u ? even : yvx::kCsaHeadSlots + 2u;
         const size_t smem = ((size_t)yvx::kCsaHeadSlots * (a->head_dim + 1u) + (size_t)tile_rows * kp) * sizeof(double);
-        auto kernel = wide ? yvx::csa_score_kernel<8> : yvx::csa_score_kernel<4>;
+        auto kernel = wide ? yvx::csa_score_kernel<8> : yvx::csa_score_kernel<2>;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return yvx_cuda_check(e, "csa_score_kernel attribute");
         const unsigned long long tiles = (a->rows + tile_rows - 1u) / tile_rows;
