@@ -214,7 +214,8 @@ __device__ __forceinline__ unsigned long long csa_key(float score, unsigned int 
 struct csa_rank_shared {
     unsigned long long keys[1024];  // the kept keys
     unsigned int histogram[256];
-    unsigned int digit, rank, kept;
+    unsigned int digit, rank, kept, in_digit;
+    unsigned long long found;
 };
 
 // The need-th smallest (1-based) of the CTA's keys; need <= number of keys below kCsaAbsent.
@@ -257,6 +258,7 @@ __device__ __forceinline__ unsigned long long csa_kth_smallest(const unsigned lo
                     if (need > run && need <= run + bins[j]) {
                         sh.digit = 8u * lane + j;
                         sh.rank = need - run;
+                        sh.in_digit = bins[j];
                     }
                     run += bins[j];
                 }
@@ -266,6 +268,13 @@ __device__ __forceinline__ unsigned long long csa_kth_smallest(const unsigned lo
         prefix |= (unsigned long long)sh.digit << shift;
         decided |= 0xffull << shift;
         need = sh.rank;
+        if (sh.in_digit == 1u && shift > 0) {  // one key left under this prefix: it is the answer
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if ((e[i] & decided) == prefix) sh.found = e[i];
+            __syncthreads();
+            return sh.found;
+        }
     }
     return prefix;
 }

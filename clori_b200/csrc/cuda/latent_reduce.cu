@@ -58,7 +58,7 @@ __device__ __forceinline__ const float *latent_visible_row(const yvx_latent_redu
 template <int SLOTS>
 __device__ __forceinline__ void latent_publish(const yvx_latent_reduce_args &a, unsigned long long ordinal,
                                                unsigned long long head, unsigned int lane,
-                                               const float (&acc)[SLOTS], float l)
+                                               const float (&acc)[SLOTS], float l, unsigned int first_slot = 0u)
 {
     const unsigned long long token_position = a.phase_start_position + ordinal;
     float *out = a.out + (ordinal * a.query_heads + head) * a.head_dim;
@@ -66,11 +66,11 @@ __device__ __forceinline__ void latent_publish(const yvx_latent_reduce_args &a, 
     bool published_finite = true;
 #pragma unroll
     for (int s = 0; s < SLOTS; ++s) {
-        const unsigned long long d = lane + 32ull * s;
+        const unsigned long long d = lane + 32ull * (first_slot + s);
         float published = acc[s] / l;
         published_finite = published_finite && isfinite(published);
         published = __uint_as_float((uint32_t)bf16_bits_rne(published) << 16);
-        if (rope_start < a.head_dim && 32ull * s + 32ull > rope_start) {
+        if (rope_start < a.head_dim && 32ull * (first_slot + s) + 32ull > rope_start) {
             const float partner = __shfl_xor_sync(0xffffffffu, published, 1);
             if (d >= rope_start && d < a.head_dim) {
                 const unsigned long long i = d - rope_start;
@@ -169,15 +169,12 @@ latent_reduce_kernel(const yvx_latent_reduce_args a, const unsigned int splits,
                                      (reinterpret_cast<unsigned long long>(a.compressed) & 15ull) == 0ull));
     const unsigned int chunks = (unsigned int)((end - begin + kChunkRows - 1u) / kChunkRows);
 
-    auto resolve = [&](unsigned int chunk) {  // candidates of a chunk -> row pointers
-        if (threadIdx.x < kChunkRows) {
-            const unsigned long long c = begin + (unsigned long long)chunk * kChunkRows + threadIdx.x;
-            const float *row = nullptr;
-            if (c < end)
-                row = c < local_count ? latent_visible_row(a, 0u, ordinal, c, local_offset)
-                                      : latent_visible_row(a, 1u, ordinal, c - local_count, local_offset);
-            row_of[chunk & 1u][threadIdx.x] = row;
-        }
+    // candidate of this thread in a chunk -> row pointer (nullptr: not visible / past the end)
+    auto resolve = [&](unsigned int chunk) -> const float * {
+        const unsigned long long c = begin + (unsigned long long)chunk * kChunkRows + threadIdx.x;
+        if (threadIdx.x >= kChunkRows || chunk >= chunks || c >= end) return nullptr;
+        return c < local_count ? latent_visible_row(a, 0u, ordinal, c, local_offset)
+                               : latent_visible_row(a, 1u, ordinal, c - local_count, local_offset);
     };
     auto stage = [&](unsigned int chunk) {  // asynchronous copy of the chunk's rows
         float *buffer = staged + (chunk & 1u) * kLatentBufferFloats;
@@ -198,16 +195,22 @@ latent_reduce_kernel(const yvx_latent_reduce_args a, const unsigned int splits,
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
+    // The first two chunks are resolved together (their index and position lookups overlap)
+    // and both copies start before any row is used; later chunks are resolved while the
+    // warps work, in the registers of the resolving threads.
     if (chunks) {
-        resolve(0);
+        const float *first_row = resolve(0), *second_row = resolve(1);
+        if (threadIdx.x < kChunkRows) {
+            row_of[0][threadIdx.x] = first_row;
+            row_of[1][threadIdx.x] = second_row;
+        }
         __syncthreads();
         stage(0);
+        if (chunks > 1u) stage(1);
     }
     for (unsigned int chunk = 0; chunk < chunks; ++chunk) {
+        const float *later_row = resolve(chunk + 2u);
         if (chunk + 1u < chunks) {
-            resolve(chunk + 1u);  // its buffer was released by the barrier that ended chunk - 1
-            __syncthreads();
-            stage(chunk + 1u);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -259,7 +262,12 @@ latent_reduce_kernel(const yvx_latent_reduce_args a, const unsigned int splits,
             }
             m = top;
         }
-        __syncthreads();  // every warp is done with this buffer
+        __syncthreads();  // every warp is done with this buffer and its row pointers
+        if (chunk + 2u < chunks) {
+            if (threadIdx.x < kChunkRows) row_of[chunk & 1u][threadIdx.x] = later_row;
+            __syncthreads();
+            stage(chunk + 2u);
+        }
     }
     pdl_launch_dependents();
     if (!owner) return;
@@ -287,17 +295,18 @@ latent_reduce_kernel(const yvx_latent_reduce_args a, const unsigned int splits,
     }
 }
 
-// Folds the splits of a (token, head) in split order and publishes. grid: x = head tile,
-// y = token; one warp per head.
+// Folds the splits of a (token, head) in split order and publishes. grid: x = head,
+// y = token; SLOTS / 4 warps, each owning four 32-lane slots of the head's row, so that
+// sixteen splits' worth of loads are in flight per warp.
 template <int SLOTS>
-__global__ void __launch_bounds__(kLatentWarps * 32)
+__global__ void __launch_bounds__(SLOTS * 8)
 latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, const float *partials)
 {
+    constexpr int kOwn = 4, kFoldBatch = 16;
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const unsigned long long ordinal = blockIdx.y;
-    const unsigned long long head = (unsigned long long)blockIdx.x * kLatentWarps + warp;
+    const unsigned int first_slot = warp * kOwn;
+    const unsigned long long ordinal = blockIdx.y, head = blockIdx.x;
     pdl_wait();
-    if (head >= a.query_heads) return;
     // a split that refused leaves its partial unwritten: nothing to publish
     if (*reinterpret_cast<volatile int *>(a.status) != YVX_STATUS_OK) return;
     const unsigned long long width = a.head_dim + 2ull;
@@ -306,11 +315,11 @@ latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, co
     for (unsigned int i = lane; i < splits; i += 32u) m = fmaxf(m, __ldcg(part + i * width + a.head_dim));
 #pragma unroll
     for (int offset = 16; offset; offset >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, offset));
-    float acc[SLOTS], l = 0.0f;
+    float acc[kOwn], l = 0.0f;
 #pragma unroll
-    for (int s = 0; s < SLOTS; ++s) acc[s] = 0.0f;
+    for (int s = 0; s < kOwn; ++s) acc[s] = 0.0f;
     // Lane i owns the weight of split base + i; the rows of the splits are then read with
-    // loads that depend on nothing but the split index, so several are in flight at once.
+    // loads that depend on nothing but the split index, a batch of them in flight at once.
     for (unsigned int base = 0; base < splits; base += 32u) {
         const unsigned int mine = base + lane;
         float w_lane = 0.0f;
@@ -321,10 +330,8 @@ latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, co
             l = fmaf(li, w_lane, l);
         }
         const unsigned int count = min(32u, splits - base);
-        // kFoldBatch splits at a time: all their loads are issued before the first use
-        constexpr int kFoldBatch = SLOTS >= 16 ? 4 : 8;
         for (unsigned int j0 = 0; j0 < count; j0 += kFoldBatch) {
-            float v[kFoldBatch][SLOTS], w[kFoldBatch];
+            float v[kFoldBatch][kOwn], w[kFoldBatch];
 #pragma unroll
             for (int j = 0; j < kFoldBatch; ++j) {
                 const bool live = j0 + j < count;
@@ -332,15 +339,15 @@ latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, co
                 w[j] = __shfl_sync(0xffffffffu, w_lane, (j0 + j) & 31u);
                 if (!live) w[j] = 0.0f;
 #pragma unroll
-                for (int s = 0; s < SLOTS; ++s) {
-                    const unsigned long long d = lane + 32ull * s;
+                for (int s = 0; s < kOwn; ++s) {
+                    const unsigned long long d = lane + 32ull * (first_slot + s);
                     v[j][s] = d < a.head_dim ? __ldcg(p + d) : 0.0f;
                 }
             }
 #pragma unroll
             for (int j = 0; j < kFoldBatch; ++j)
 #pragma unroll
-                for (int s = 0; s < SLOTS; ++s) acc[s] = fmaf(v[j][s], w[j], acc[s]);
+                for (int s = 0; s < kOwn; ++s) acc[s] = fmaf(v[j][s], w[j], acc[s]);
         }
     }
     l = warp_sum(l);
@@ -348,7 +355,7 @@ latent_fold_kernel(const yvx_latent_reduce_args a, const unsigned int splits, co
         if (lane == 0) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
         return;
     }
-    latent_publish<SLOTS>(a, ordinal, head, lane, acc, l);
+    latent_publish<kOwn>(a, ordinal, head, lane, acc, l, first_slot);
 }
 
 struct latent_plan {
@@ -404,8 +411,8 @@ static int latent_launch(const yvx_latent_reduce_args &a, cudaStream_t s, unsign
     if (launches) *launches = 1u;
     if (plan.splits > 1u) {
         cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(tiles, (unsigned int)a.token_count, 1);
-        config.blockDim = dim3(kLatentWarps * 32, 1, 1);
+        config.gridDim = dim3((unsigned int)a.query_heads, (unsigned int)a.token_count, 1);
+        config.blockDim = dim3(SLOTS * 8, 1, 1);
         config.stream = s;
         cudaLaunchAttribute attribute[1];
         attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
