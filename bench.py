@@ -659,6 +659,83 @@ def bench_kv_append(lib, backend, abi, hbm_peak, repeats, sessions=2, tokens=819
     return result, None
 
 
+def bench_compressor(lib, backend, abi, hbm_peak, repeats, tokens=32768):
+    """Rolling compressor over a prefill-sized chunk of the sparse class's main rows (ratio 4,
+    head dimension 512, two halves: 1024-lane token rows) with the publication chain (bf16, RMS
+    norm, bf16, rotation of the last 64 lanes, bf16); a CPU-computed sample of rows is compared."""
+    from oracle.binding import Oracle, PositionPolicy, compressor_initial_state
+    ratio, hd, rope, width = 4, 512, 64, 1024
+    oracle = Oracle()
+    frequency = oracle.rope_frequencies(PositionPolicy(10000, 16, 65536, 32, 1), rope)
+    sizes = {"kv": tokens * width, "score": tokens * width, "ape": ratio * width, "norm": hd}
+    dev = {k: _alloc(lib, n * 4) for k, n in sizes.items()}
+    for i, (k, n) in enumerate(sizes.items()):
+        lib.yvx_cuda_fill_normal(dev[k], abi.DTYPE_F32, n, 701 + i, 1.0, backend.stream)
+    kv0, score0 = compressor_initial_state(ratio, hd, 1)
+    emitted = tokens // ratio
+    for name, nbytes in (("skv", kv0.nbytes), ("ssc", kv0.nbytes), ("akv", kv0.nbytes), ("asc", kv0.nbytes),
+                         ("rows", emitted * hd * 4), ("positions", emitted * 8), ("freq", frequency.nbytes),
+                         ("status", 4)):
+        dev[name] = _alloc(lib, nbytes)
+    for name, array in (("skv", kv0), ("ssc", score0), ("freq", frequency)):
+        lib.yvx_cuda_upload_async(dev[name], array.ctypes.data, array.nbytes, backend.stream)
+    lib.yvx_cuda_memset_async(dev["status"], 0, 4, backend.stream)
+    a = abi.CompressorArgs()
+    a.ratio, a.head_dim, a.overlap, a.start_position, a.token_count = ratio, hd, 1, 0, tokens
+    a.token_kv, a.token_score, a.token_stride, a.ape = dev["kv"], dev["score"], width, dev["ape"]
+    a.state_kv, a.state_score, a.after_kv, a.after_score = dev["skv"], dev["ssc"], dev["akv"], dev["asc"]
+    a.compressed, a.compressed_stride, a.positions = dev["rows"], hd, dev["positions"]
+    a.norm_weights, a.epsilon, a.rope_dims, a.rope_frequency = dev["norm"], 1e-6, rope, dev["freq"]
+    a.status = dev["status"]
+    count = C.c_ulonglong()
+
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    for _ in range(3):
+        assert lib.yvx_cuda_compressor_chunk(C.byref(a), backend.stream, C.byref(count)) == 0
+    first, last = event(), event()
+    lib.yvx_cuda_event_record(first, backend.stream)
+    for _ in range(repeats):
+        assert lib.yvx_cuda_compressor_chunk(C.byref(a), backend.stream, C.byref(count)) == 0
+    lib.yvx_cuda_event_record(last, backend.stream)
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    ms = C.c_float()
+    lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+    step = ms.value / repeats
+    # per token: its kv and score rows read once; per emitted row: head_dim floats and a position written
+    nbytes = tokens * 2 * width * 4 + emitted * (hd * 4 + 8)
+    sample_tokens = 64
+    host = {k: np.zeros((sample_tokens, width) if k in ("kv", "score") else ((ratio, width) if k == "ape" else (hd,)),
+                        np.float32) for k in ("kv", "score", "ape", "norm")}
+    rows, st = np.zeros((sample_tokens // ratio, hd), np.float32), np.zeros(1, np.int32)
+    for k, array in host.items():
+        lib.yvx_cuda_download_async(array.ctypes.data, dev[k], array.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(rows.ctypes.data, dev["rows"], rows.nbytes, backend.stream)
+    lib.yvx_cuda_download_async(st.ctypes.data, dev["status"], 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    begin = time.perf_counter()
+    ref = oracle.compressor_chunk(ratio, hd, 1, 0, host["kv"], host["score"], host["ape"], kv0, score0, host["norm"],
+                                  1e-6, rope, frequency)
+    cpu_seconds = time.perf_counter() - begin
+    result = {"workload": f"rolling compressor, {tokens} tokens in one chunk, ratio 4, head dimension 512, two halves "
+                          "(1024-lane rows), publication chain with rotation fused",
+              "kernel": "compressor_chunk_kernel", "launches_per_step": 1, "kernel_ms": step,
+              "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (step * 1e-3) / 1e9,
+              "frac_of_measured_hbm": nbytes / (step * 1e-3) / 1e9 / hbm_peak,
+              "tokens_per_s": tokens / (step * 1e-3), "emitted_rows": int(count.value), "status_word": int(st[0]),
+              "l2": "%.0f MB per launch exceed L2" % (nbytes / 1e6),
+              "replaces": "one single-CTA launch per token that copies the whole state",
+              "rows_differing_from_cpu_on_sample": int((ref[0] != rows).sum()) if ref is not None else -1,
+              "gpu_vs_cpu_max_abs_on_sample": float(np.abs(ref[0] - rows).max()) if ref is not None else -1.0,
+              "cpu_sample": f"first {sample_tokens} tokens (CPU restatement, 1 core)",
+              "cpu_sample_ms": cpu_seconds * 1e3, "cpu_cores": 1}
+    for ptr in dev.values():
+        lib.yvx_cuda_free(ptr)
+    return result, None
+
+
 def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
     """One decode step of a sparse shared-latent layer at the reference configuration's
     widths (64 heads x 512 with the last 64 lanes rotated, window 128, ratio 4, 64 index
@@ -1066,7 +1143,8 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse"],
+                        choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
+                                 "compressor"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1116,6 +1194,9 @@ def main():
                                   sessions=min(args.sessions, 32))
         elif args.workload == "latent_sparse":
             result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
+        elif args.workload == "compressor":
+            result, _ = bench_compressor(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
+                                         tokens=min(args.tokens * 4, 32768))
         elif args.workload == "kv_append":
             result, _ = bench_kv_append(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                         tokens=args.tokens)
@@ -1190,6 +1271,7 @@ def main():
         others["latent_decode_config5"], other_samples["mla"] = bench_mla(lib, b, w.abi, hbm_peak, 10)
         others["kv_append_rotary"], _ = bench_kv_append(lib, b, w.abi, hbm_peak, 10)
         others["latent_sparse_decode"], _ = bench_latent_sparse(lib, b, w.abi, 20)
+        others["rolling_compressor"], _ = bench_compressor(lib, b, w.abi, hbm_peak, 10)
 
     if rank != 0:
         if dist is not None:

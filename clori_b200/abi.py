@@ -206,6 +206,32 @@ class AttentionSelectRequest(C.Structure):
     ]
 
 
+class AttentionCompressRequest(C.Structure):
+    """yvex_b200_attention_compress_request (include/yvex_b200/attention.h)."""
+    _fields_ = [
+        ("kind", C.c_int), ("attention_class", C.c_int), ("token_position", u64), ("token_count", u64),
+        ("compression_ratio", u64), ("head_dimension", u64),
+        ("token_kv", C.c_void_p), ("token_score", C.c_void_p), ("token_stride", u64),
+        ("position_rows", C.c_void_p), ("state_kv", C.c_void_p), ("state_score", C.c_void_p),
+        ("next_state_kv", C.c_void_p), ("next_state_score", C.c_void_p),
+        ("norm_weights", C.c_void_p), ("rms_norm_epsilon", C.c_double),
+        ("rope_dimension", u64), ("rope_frequency", C.c_void_p),
+        ("compressed", C.c_void_p), ("compressed_positions", C.c_void_p), ("emitted", u64),
+    ]
+
+
+class CompressorArgs(C.Structure):
+    """yvx_compressor_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [
+        ("ratio", u64), ("head_dim", u64), ("overlap", C.c_int), ("start_position", u64), ("token_count", u64),
+        ("token_kv", C.c_void_p), ("token_score", C.c_void_p), ("token_stride", u64), ("ape", C.c_void_p),
+        ("state_kv", C.c_void_p), ("state_score", C.c_void_p), ("after_kv", C.c_void_p), ("after_score", C.c_void_p),
+        ("compressed", C.c_void_p), ("compressed_stride", u64), ("positions", C.c_void_p),
+        ("norm_weights", C.c_void_p), ("epsilon", C.c_double), ("rope_dims", u64), ("rope_frequency", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 class CsaSelectArgs(C.Structure):
     """yvx_csa_select_args (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [
@@ -293,6 +319,7 @@ EXPORTED_SYMBOLS = [
     "yvex_backend_op_attention", "yvex_b200_attention_batch_execute",
     "yvex_b200_attention_reduce_execute", "yvex_b200_kv_append_rotary_execute", "yvex_b200_mla_decode_execute",
     "yvex_b200_attention_select_execute", "yvex_b200_rope_frequencies",
+    "yvex_b200_attention_compress_execute",
     "yvex_b200_kv_pool_create", "yvex_b200_kv_pool_destroy", "yvex_b200_kv_pool_session_open",
     "yvex_b200_kv_pool_session_fork", "yvex_b200_kv_pool_session_close", "yvex_b200_kv_pool_reserve",
     "yvex_b200_kv_pool_commit", "yvex_b200_kv_pool_table", "yvex_b200_kv_pool_committed",
@@ -317,7 +344,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
     "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
     "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
-    "yvx_cuda_mla_decode",
+    "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk",
 ]
 
 _lib = None
@@ -369,6 +396,9 @@ def load():
     lib.yvex_b200_attention_select_execute.argtypes = [
         vp, P(AttentionSelectRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
     lib.yvex_b200_rope_frequencies.argtypes = [P(PositionPolicy), u64, vp]
+    lib.yvex_b200_attention_compress_execute.argtypes = [
+        vp, P(AttentionCompressRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
+    lib.yvx_cuda_compressor_chunk.argtypes = [P(CompressorArgs), vp, P(u64)]
     lib.yvex_b200_kv_append_rotary_execute.argtypes = [vp, P(KvAppendRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_mla_decode_execute.argtypes = [vp, P(MlaDecodeRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_kv_pool_create.restype = vp

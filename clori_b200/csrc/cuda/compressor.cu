@@ -1,0 +1,240 @@
+// Rolling compressor over a chunk of tokens in one launch.
+//
+// Replaces yvex_attention_rolling_state (src/backend/cuda/kernels.cu:1536-1631 in
+// the reference: one launch of ONE CTA per token, the whole state copied on every
+// token) and its CPU twin yvex_attention_rolling_state_step_cpu
+// (src/graph/attention.c:745-836). The transition is a ring insert, and an emission
+// only reads the rows of its own group (and, with two halves, of the group before
+// it), so every emission of a chunk is independent given the token rows and the state
+// the chunk started from: CTA g computes emitted row g, the last state_slots CTAs
+// write the state the serial process would end in. With norm_weights the CTA carries
+// on through the publication chain of src/graph/attention_execute.c:776-806
+// (bf16 round, RMS norm, bf16 round, rotation, bf16 round) while the row is still in
+// registers. Per lane the softmax runs in double in the reference's order (previous
+// half before current half, slot by slot), products and sums separately rounded.
+#include "common.cuh"
+
+namespace yvx {
+
+constexpr int kCompressorThreads = 256;
+constexpr int kCompressorLanesPerThread = 4;  // head_dim <= 1024
+
+struct compressor_row {
+    const float *kv, *score, *ape;  // ape == nullptr: the score is stored with it already
+};
+
+// Row `token` (signed: negative means "before this chunk") of the chunk, else the
+// given slot of the state the chunk started from.
+__device__ __forceinline__ compressor_row compressor_source(const yvx_compressor_args &a,
+                                                            long long token, unsigned long long cursor,
+                                                            unsigned long long state_slot,
+                                                            unsigned long long width)
+{
+    compressor_row r;
+    if (token >= 0) {
+        r.kv = a.token_kv + (unsigned long long)token * a.token_stride;
+        r.score = a.token_score + (unsigned long long)token * a.token_stride;
+        r.ape = a.ape + cursor * width;
+    } else {
+        r.kv = a.state_kv + state_slot * width;
+        r.score = a.state_score + state_slot * width;
+        r.ape = nullptr;
+    }
+    return r;
+}
+
+__device__ __forceinline__ float compressor_score(const compressor_row &r, unsigned long long column,
+                                                  bool &finite)
+{
+    if (!r.ape) return r.score[column];
+    const float token_score = r.score[column], ape = r.ape[column];
+    finite = finite && isfinite(token_score) && isfinite(ape);
+    return __fadd_rn(token_score, ape);
+}
+
+__device__ __forceinline__ float compressor_bf16(float v)
+{
+    return __uint_as_float((uint32_t)bf16_bits_rne(v) << 16);
+}
+
+__global__ void __launch_bounds__(kCompressorThreads)
+compressor_chunk_kernel(const yvx_compressor_args a, unsigned long long emitted)
+{
+    const unsigned long long ratio = a.ratio, hd = a.head_dim;
+    const unsigned long long width = a.overlap ? 2ull * hd : hd;
+    const unsigned long long c0 = a.start_position % ratio;
+    const unsigned int tid = threadIdx.x;
+    __shared__ double warp_part[kCompressorThreads / 32];
+    bool finite = true;
+
+    if (blockIdx.x >= emitted) {
+        // ---- the state after the last token, one slot per CTA ----
+        const unsigned long long slot = blockIdx.x - emitted;
+        const long long tokens = (long long)a.token_count;
+        long long token;
+        unsigned long long cursor, before_slot = slot;
+        if (a.overlap && slot < ratio) {
+            cursor = slot;
+            if (!emitted) {
+                token = -1;
+            } else {
+                const long long last = (long long)(ratio - c0 - 1ull + (emitted - 1ull) * ratio);
+                token = last - (long long)(ratio - 1ull - cursor);
+                before_slot = ratio + cursor;
+            }
+        } else {
+            cursor = a.overlap ? slot - ratio : slot;
+            const unsigned long long last_cursor = (c0 + a.token_count + ratio - 1ull) % ratio;
+            token = tokens - 1 - (long long)((last_cursor + ratio - cursor) % ratio);
+            if (!tokens) token = -1;
+        }
+        const compressor_row r = compressor_source(a, token, cursor, before_slot, width);
+        for (unsigned long long column = tid; column < width; column += kCompressorThreads) {
+            const float kv = r.kv[column];
+            const float score = compressor_score(r, column, finite);
+            if (r.ape) finite = finite && isfinite(kv);
+            a.after_kv[slot * width + column] = kv;
+            a.after_score[slot * width + column] = score;
+        }
+        if (!finite) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+        return;
+    }
+
+    // ---- emitted row g ----
+    const unsigned long long g = blockIdx.x;
+    const long long first_current = (long long)(g * ratio) - (long long)c0;
+    const long long first_previous = first_current - (long long)ratio;
+    float value[kCompressorLanesPerThread];
+#pragma unroll
+    for (int k = 0; k < kCompressorLanesPerThread; ++k) {
+        const unsigned long long lane = tid + (unsigned long long)k * kCompressorThreads;
+        value[k] = 0.0f;
+        if (lane >= hd) continue;
+        double maximum = -INFINITY, denominator = 0.0, sum = 0.0;
+        for (unsigned long long s = 0; s < ratio; ++s) {
+            if (a.overlap) {
+                const compressor_row p = compressor_source(a, first_previous + (long long)s, s,
+                                                           g == 0ull ? s : ratio + s, width);
+                const double sp = (double)compressor_score(p, lane, finite);
+                if (sp > maximum) maximum = sp;
+            }
+            const compressor_row c = compressor_source(a, first_current + (long long)s, s,
+                                                       a.overlap ? ratio + s : s, width);
+            const double sc = (double)compressor_score(c, a.overlap ? lane + hd : lane, finite);
+            if (sc > maximum) maximum = sc;
+        }
+        for (unsigned long long s = 0; s < ratio; ++s) {
+            if (a.overlap) {
+                const compressor_row p = compressor_source(a, first_previous + (long long)s, s,
+                                                           g == 0ull ? s : ratio + s, width);
+                const double w = exp(__dsub_rn((double)compressor_score(p, lane, finite), maximum));
+                const float kv = p.kv[lane];
+                if (p.ape) finite = finite && isfinite(kv);
+                denominator = __dadd_rn(denominator, w);
+                sum = __dadd_rn(sum, __dmul_rn(w, (double)kv));
+            }
+            const compressor_row c = compressor_source(a, first_current + (long long)s, s,
+                                                       a.overlap ? ratio + s : s, width);
+            const unsigned long long column = a.overlap ? lane + hd : lane;
+            const double w = exp(__dsub_rn((double)compressor_score(c, column, finite), maximum));
+            const float kv = c.kv[column];
+            if (c.ape) finite = finite && isfinite(kv);
+            denominator = __dadd_rn(denominator, w);
+            sum = __dadd_rn(sum, __dmul_rn(w, (double)kv));
+        }
+        finite = finite && isfinite(denominator) && denominator > 0.0 && isfinite(sum);
+        value[k] = __double2float_rn(__ddiv_rn(sum, denominator));
+        finite = finite && isfinite(value[k]);
+    }
+
+    if (a.norm_weights) {
+        double squares = 0.0;
+#pragma unroll
+        for (int k = 0; k < kCompressorLanesPerThread; ++k) {
+            value[k] = compressor_bf16(value[k]);
+            squares = __dadd_rn(squares, __dmul_rn((double)value[k], (double)value[k]));
+        }
+#pragma unroll
+        for (int offset = 16; offset; offset >>= 1)
+            squares = __dadd_rn(squares, __shfl_xor_sync(0xffffffffu, squares, offset));
+        if ((tid & 31u) == 0u) warp_part[tid >> 5] = squares;
+        __syncthreads();
+        double mean = 0.0;
+#pragma unroll
+        for (int w = 0; w < kCompressorThreads / 32; ++w) mean = __dadd_rn(mean, warp_part[w]);
+        mean = __ddiv_rn(mean, (double)hd);
+        const double inverse = __ddiv_rn(1.0, sqrt(__dadd_rn(mean, a.epsilon)));
+        finite = finite && isfinite(inverse);
+        const unsigned long long rope_start = a.rope_dims ? hd - a.rope_dims : hd;
+        const unsigned long long position = a.start_position + (unsigned long long)first_current;
+#pragma unroll
+        for (int k = 0; k < kCompressorLanesPerThread; ++k) {
+            const unsigned long long lane = tid + (unsigned long long)k * kCompressorThreads;
+            const float weight = lane < hd ? a.norm_weights[lane] : 0.0f;
+            const double scaled = __dmul_rn(__dmul_rn((double)value[k], inverse), (double)weight);
+            float v = __double2float_rn(scaled);
+            finite = finite && isfinite(weight) && isfinite(v);
+            v = compressor_bf16(v);
+            const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+            if (lane >= rope_start && lane < hd) {
+                const unsigned long long i = lane - rope_start;
+                const double angle = __dmul_rn((double)position, a.rope_frequency[i >> 1]);
+                double sn, c;
+                sincos(angle, &sn, &c);
+                const double x = (i & 1ull) ? (double)partner : (double)v;
+                const double y = (i & 1ull) ? (double)v : (double)partner;
+                const double rotated = (i & 1ull) ? __dadd_rn(__dmul_rn(x, sn), __dmul_rn(y, c))
+                                                  : __dsub_rn(__dmul_rn(x, c), __dmul_rn(y, sn));
+                v = __double2float_rn(rotated);
+                finite = finite && isfinite(c) && isfinite(sn) && isfinite(v);
+            }
+            if (a.rope_dims) v = compressor_bf16(v);
+            value[k] = v;
+        }
+    }
+    if (!finite) {
+        atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+        return;
+    }
+    float *out = a.compressed + g * a.compressed_stride;
+#pragma unroll
+    for (int k = 0; k < kCompressorLanesPerThread; ++k) {
+        const unsigned long long lane = tid + (unsigned long long)k * kCompressorThreads;
+        if (lane < hd) out[lane] = value[k];
+    }
+    if (tid == 0u && a.positions) a.positions[g] = a.start_position + (unsigned long long)first_current;
+}
+
+}  // namespace yvx
+
+extern "C" int yvx_cuda_compressor_chunk(const yvx_compressor_args *a, void *stream,
+                                         unsigned long long *emitted_out)
+{
+    if (emitted_out) *emitted_out = 0ull;
+    if (!a || !a->ratio || !a->head_dim || !a->ape || !a->state_kv || !a->state_score ||
+        !a->after_kv || !a->after_score || !a->status ||
+        (a->token_count && (!a->token_kv || !a->token_score)))
+        return YVEX_ERR_INVALID_ARG;
+    const unsigned long long width = a->head_dim * (a->overlap ? 2ull : 1ull);
+    const unsigned long long slots = a->ratio * (a->overlap ? 2ull : 1ull);
+    if (a->after_kv == a->state_kv || a->after_score == a->state_score) return YVEX_ERR_INVALID_ARG;
+    if (a->token_count && a->token_stride < width) return YVEX_ERR_FORMAT;
+    if (a->head_dim > (unsigned long long)yvx::kCompressorThreads * yvx::kCompressorLanesPerThread ||
+        (a->head_dim & 1ull) || a->ratio > (1ull << 20) || a->token_count > (1ull << 40))
+        return YVEX_ERR_UNSUPPORTED;
+    if (a->norm_weights) {
+        if (!(a->epsilon > 0.0) || a->epsilon > 1.0e300) return YVEX_ERR_INVALID_ARG;
+        if (a->rope_dims && (!a->rope_frequency || (a->rope_dims & 1ull) || a->rope_dims > a->head_dim))
+            return YVEX_ERR_INVALID_ARG;
+    }
+    if (a->start_position > ~0ull - a->token_count) return YVEX_ERR_BOUNDS;
+    const unsigned long long emitted = (a->start_position % a->ratio + a->token_count) / a->ratio;
+    if (emitted && (!a->compressed || a->compressed_stride < a->head_dim)) return YVEX_ERR_FORMAT;
+    if (emitted + slots > 0x7fffffffull) return YVEX_ERR_UNSUPPORTED;
+    yvx_compressor_args args = *a;
+    if (!args.norm_weights) args.rope_dims = 0ull;
+    yvx::compressor_chunk_kernel<<<(unsigned int)(emitted + slots), yvx::kCompressorThreads, 0,
+                                   (cudaStream_t)stream>>>(args, emitted);
+    if (emitted_out) *emitted_out = emitted;
+    return yvx_cuda_check(cudaGetLastError(), "compressor_chunk_kernel");
+}

@@ -11,6 +11,8 @@
  * 1112-1131 and src/runtime/stateful_attention.c:183-243 rotate and copy.
  * yvex_b200_attention_select_execute is the sparse index selection in front of
  * that stage (CPU reference src/graph/attention.c:369-497).
+ * yvex_b200_attention_compress_execute is the rolling compressor that feeds both
+ * (CPU reference src/graph/attention.c:745-836, attention_execute.c:730-832).
  * yvex_b200_mla_decode_execute has no counterpart in the reference. */
 #include "private.h"
 
@@ -314,6 +316,132 @@ int yvex_b200_attention_select_execute(yvex_backend *backend, const yvex_b200_at
         return rc;
     }
     r->scores->is_written = r->selected->is_written = r->selected_count->is_written = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+static int compress_refuse(yvex_b200_attention_failure *failure, yvex_b200_attention_failure_code code,
+                           unsigned long long expected, unsigned long long actual, yvex_error *err,
+                           yvex_status status, const char *message)
+{
+    if (failure) {
+        failure->code = code;
+        failure->stage = "compress";
+        failure->expected = expected;
+        failure->actual = actual;
+    }
+    return yvx_fail(err, status, "b200.attention.compress", message);
+}
+
+int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attention_compress_request *r,
+                                         yvex_b200_attention_failure *failure,
+                                         yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.attention.compress";
+    unsigned long long width = 0ull, slots = 0ull, elements = 0ull, emitted, launched = 0ull;
+    yvx_compressor_args a;
+    int overlap, rc;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    if (!r || !facts || !r->position_rows || !r->state_kv || !r->state_score || !r->next_state_kv ||
+        !r->next_state_score || (r->token_count && (!r->token_kv || !r->token_score)))
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                               YVEX_ERR_INVALID_ARG, "token rows, position rows and both states are required");
+    r->emitted = 0ull;
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    /* yvex_attention_rolling_geometry: index rows exist for the sparse class only */
+    if ((r->kind != YVEX_B200_ROLLING_MAIN && r->kind != YVEX_B200_ROLLING_INDEXER) ||
+        (r->attention_class != YVEX_B200_ATTENTION_CSA && r->attention_class != YVEX_B200_ATTENTION_HCA) ||
+        (r->kind == YVEX_B200_ROLLING_INDEXER && r->attention_class != YVEX_B200_ATTENTION_CSA))
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_CAPABILITY, 1ull, 0ull, err,
+                               YVEX_ERR_UNSUPPORTED, "this class keeps no rolling state of this kind");
+    overlap = r->attention_class == YVEX_B200_ATTENTION_CSA;
+    if (!r->compression_ratio || !r->head_dimension ||
+        !yvx_u64_mul(r->head_dimension, overlap ? 2ull : 1ull, &width) ||
+        !yvx_u64_mul(r->compression_ratio, overlap ? 2ull : 1ull, &slots) ||
+        (r->token_count && r->token_stride < width) || r->token_position > ~0ull - r->token_count)
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, width, r->token_stride, err,
+                               YVEX_ERR_INVALID_ARG, "ratio, head dimension, token stride and position must be consistent");
+    if (r->head_dimension > 1024ull || (r->head_dimension & 1ull) || (r->rope_dimension & 1ull) ||
+        r->rope_dimension > r->head_dimension)
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_CAPABILITY, 1024ull, r->head_dimension, err,
+                               YVEX_ERR_UNSUPPORTED, "even head dimension up to 1024 and an even rotated width");
+    if (r->next_state_kv->data == r->state_kv->data || r->next_state_score->data == r->state_score->data)
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 0ull, 1ull, err,
+                               YVEX_ERR_INVALID_ARG, "the next state must not alias the current state");
+    emitted = (r->token_position % r->compression_ratio + r->token_count) / r->compression_ratio;
+    if (!yvx_u64_mul(slots, width, &elements) || !view_ok(backend, r->state_kv, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->state_score, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->next_state_kv, YVEX_DTYPE_F32, elements) ||
+        !view_ok(backend, r->next_state_score, YVEX_DTYPE_F32, elements) ||
+        !yvx_u64_mul(r->compression_ratio, width, &elements) ||
+        !view_ok(backend, r->position_rows, YVEX_DTYPE_F32, elements) ||
+        (r->token_count &&
+         (!yvx_u64_mul(r->token_count, r->token_stride, &elements) ||
+          !view_ok(backend, r->token_kv, YVEX_DTYPE_F32, elements) ||
+          !view_ok(backend, r->token_score, YVEX_DTYPE_F32, elements))) ||
+        (emitted &&
+         (!r->compressed || !yvx_u64_mul(emitted, r->head_dimension, &elements) ||
+          !view_ok(backend, r->compressed, YVEX_DTYPE_F32, elements) ||
+          (r->compressed_positions && !view_ok(backend, r->compressed_positions, YVEX_DTYPE_I64, emitted)))) ||
+        (r->norm_weights && !view_ok(backend, r->norm_weights, YVEX_DTYPE_F32, r->head_dimension)) ||
+        (r->norm_weights && r->rope_dimension &&
+         (!r->rope_frequency || !view_ok(backend, r->rope_frequency, YVEX_DTYPE_F64, r->rope_dimension / 2ull))))
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements, 0ull, err,
+                               YVEX_ERR_FORMAT, "tensor views do not cover the stated geometry");
+    if (r->norm_weights && !(isfinite(r->rms_norm_epsilon) && r->rms_norm_epsilon > 0.0))
+        return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                               YVEX_ERR_INVALID_ARG, "the norm epsilon must be positive and finite");
+    memset(&a, 0, sizeof(a));
+    a.ratio = r->compression_ratio;
+    a.head_dim = r->head_dimension;
+    a.overlap = overlap;
+    a.start_position = r->token_position;
+    a.token_count = r->token_count;
+    a.token_kv = r->token_count ? (const float *)r->token_kv->data : NULL;
+    a.token_score = r->token_count ? (const float *)r->token_score->data : NULL;
+    a.token_stride = r->token_stride;
+    a.ape = (const float *)r->position_rows->data;
+    a.state_kv = (const float *)r->state_kv->data;
+    a.state_score = (const float *)r->state_score->data;
+    a.after_kv = (float *)r->next_state_kv->data;
+    a.after_score = (float *)r->next_state_score->data;
+    a.compressed = emitted ? (float *)r->compressed->data : NULL;
+    a.compressed_stride = r->head_dimension;
+    a.positions = emitted && r->compressed_positions ? (unsigned long long *)r->compressed_positions->data : NULL;
+    if (r->norm_weights) {
+        a.norm_weights = (const float *)r->norm_weights->data;
+        a.epsilon = r->rms_norm_epsilon;
+        a.rope_dims = r->rope_dimension;
+        a.rope_frequency = r->rope_dimension ? (const double *)r->rope_frequency->data : NULL;
+    }
+    a.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_compressor_chunk(&a, backend->stream, &launched);
+    if (rc != 0) {
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
+            failure->stage = "compress";
+        }
+        return yvx_backend_device_fail(backend, rc, where, err);
+    }
+    rc = finish(backend, facts, 1u, 0ull, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC
+                                                  : YVEX_B200_ATTENTION_FAILURE_SYNCHRONIZE;
+            failure->stage = "compress";
+        }
+        return rc;
+    }
+    r->emitted = launched;
+    r->next_state_kv->is_written = r->next_state_score->is_written = 1;
+    if (emitted) {
+        r->compressed->is_written = 1;
+        if (r->compressed_positions) r->compressed_positions->is_written = 1;
+    }
     yvex_error_clear(err);
     return YVEX_OK;
 }

@@ -219,6 +219,44 @@ int yvex_b200_attention_select_execute(yvex_backend *backend,
                                        yvex_b200_attention_failure *failure,
                                        yvex_backend_operation_facts *facts, yvex_error *err);
 
+/* The rolling compressor that produces the compressed rows (and, for the sparse
+ * class, the index rows) the two stages above read: the state transition of every
+ * token of a phase and the rows emitted on the way, published as the reference
+ * publishes them (CPU reference: yvex_attention_rolling_state_step_cpu
+ * src/graph/attention.c:745-836 driven by cpu_chunk_rolling_step
+ * src/graph/attention_execute.c:730-832; CUDA: yvex_attention_rolling_state
+ * src/backend/cuda/kernels.cu:1536-1631). kind and class decide the geometry as
+ * yvex_attention_rolling_geometry does (src/graph/attention.c:500-528): main rows
+ * have two halves for the sparse class only, index rows always. The projected token
+ * rows (kv, score) and the additive position rows come from the caller's projection
+ * stage; the quantising activation after the publication is the caller's too. */
+typedef enum yvex_b200_rolling_kind {
+    YVEX_B200_ROLLING_MAIN = 1,
+    YVEX_B200_ROLLING_INDEXER = 2
+} yvex_b200_rolling_kind;
+typedef struct yvex_b200_attention_compress_request {
+    yvex_b200_rolling_kind kind;
+    yvex_b200_attention_class attention_class;        /* CSA or HCA */
+    unsigned long long token_position, token_count;   /* the state has consumed token_position tokens */
+    unsigned long long compression_ratio, head_dimension;  /* head dimension of this kind's rows */
+    const yvex_device_tensor *token_kv, *token_score; /* F32 [token][token_stride] */
+    unsigned long long token_stride;
+    const yvex_device_tensor *position_rows;          /* F32 [ratio][state_width] */
+    const yvex_device_tensor *state_kv, *state_score; /* F32 [state_slots][state_width] */
+    yvex_device_tensor *next_state_kv, *next_state_score;
+    const yvex_device_tensor *norm_weights;           /* F32 [head_dimension] */
+    double rms_norm_epsilon;
+    unsigned long long rope_dimension;                /* 0: no rotation */
+    const yvex_device_tensor *rope_frequency;         /* F64 [rope_dimension/2] */
+    yvex_device_tensor *compressed;                   /* F32 [emitted][head_dimension] */
+    yvex_device_tensor *compressed_positions;         /* I64 [emitted] */
+    unsigned long long emitted;                       /* out: rows written */
+} yvex_b200_attention_compress_request;
+int yvex_b200_attention_compress_execute(yvex_backend *backend,
+                                         yvex_b200_attention_compress_request *request,
+                                         yvex_b200_attention_failure *failure,
+                                         yvex_backend_operation_facts *facts, yvex_error *err);
+
 int yvex_b200_attention_reduce_execute(yvex_backend *backend,
                                        const yvex_b200_attention_reduce_request *request,
                                        yvex_b200_attention_failure *failure,

@@ -301,6 +301,49 @@ unsigned long long yvx_cuda_csa_select_workspace_bytes(unsigned long long rows,
                                                        unsigned int topk);
 int yvx_cuda_csa_select(const yvx_csa_select_args *args, void *stream, unsigned int *launches);
 
+/* ---- rolling compressor over a chunk of tokens (one launch) -------------------------
+ * Replaces the per-token state transition of the reference
+ * (CPU: yvex_attention_rolling_state_step_cpu src/graph/attention.c:745-836; CUDA:
+ * yvex_attention_rolling_state src/backend/cuda/kernels.cu:1536-1631, one launch of one
+ * CTA per token) and, with norm_weights set, the publication chain that follows each
+ * emission (src/graph/attention_execute.c:776-806: bf16 round, RMS norm with learned
+ * weights, bf16 round, position rotation of the last rope_dims lanes at the group's first
+ * position, bf16 round). The quantising activation step after the chain is not part of it.
+ * A token row has state_width = head_dim * (overlap ? 2 : 1) lanes; the state has
+ * state_slots = ratio * (overlap ? 2 : 1) rows of state_width lanes, packed. The token at
+ * position p is stored with score token_score + ape[p % ratio]; each time p % ratio ==
+ * ratio - 1 one row is emitted: per lane the softmax-weighted mean over the group's ratio
+ * rows (lanes [head_dim, 2 head_dim) with overlap) and, with overlap, the previous group's
+ * rows (lanes [0, head_dim)), in double precision in the reference's order. The cursor
+ * and fills of the reference's state record follow from start_position. Every emission of
+ * the chunk is computed in parallel; after_kv / after_score receive the state the
+ * reference would hold after the last token, slot for slot, and must not alias the input
+ * state. compressed [emitted][compressed_stride], positions [emitted] = first position of
+ * each emitted group; the emitted count = (start_position % ratio + token_count) / ratio is
+ * returned through *emitted. Contract: head_dim <= 1024 and even, rope_dims even and
+ * <= head_dim. status: 1 non-finite input or emission. */
+typedef struct yvx_compressor_args {
+    unsigned long long ratio, head_dim;
+    int overlap;
+    unsigned long long start_position;
+    unsigned long long token_count;
+    const float *token_kv, *token_score;      /* [token][token_stride] */
+    unsigned long long token_stride;
+    const float *ape;                         /* [ratio][state_width] */
+    const float *state_kv, *state_score;      /* [state_slots][state_width] */
+    float *after_kv, *after_score;
+    float *compressed;
+    unsigned long long compressed_stride;
+    unsigned long long *positions;            /* may be NULL */
+    const float *norm_weights;                /* [head_dim]; NULL: raw emission */
+    double epsilon;
+    unsigned long long rope_dims;             /* 0: no rotation */
+    const double *rope_frequency;             /* [rope_dims/2] radians per position */
+    int *status;
+} yvx_compressor_args;
+int yvx_cuda_compressor_chunk(const yvx_compressor_args *args, void *stream,
+                              unsigned long long *emitted);
+
 /* ---- KV append with rotary embedding (one launch per step) ---------------------------
  * Replaces, for the new rows of a step, the two rotate-half launches on Q and K
  * (yvex_cuda_transformer_rotary_half / _rotary_half_f32, src/backend/cuda/transformer.c:

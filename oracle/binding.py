@@ -47,6 +47,61 @@ def indexer_struct(keys, positions, query, weights, heads, head_dim, topk, ratio
     return ix
 
 
+class CompressorArgs(C.Structure):
+    """yvx_oracle_compressor_args (host pointers here, device pointers in the library)."""
+    _fields_ = [("ratio", _u64), ("head_dim", _u64), ("overlap", C.c_int), ("start_position", _u64),
+                ("token_count", _u64), ("token_kv", C.c_void_p), ("token_score", C.c_void_p),
+                ("token_stride", _u64), ("ape", C.c_void_p), ("state_kv", C.c_void_p),
+                ("state_score", C.c_void_p), ("after_kv", C.c_void_p), ("after_score", C.c_void_p),
+                ("compressed", C.c_void_p), ("compressed_stride", _u64), ("positions", C.c_void_p),
+                ("norm_weights", C.c_void_p), ("epsilon", C.c_double), ("rope_dims", _u64),
+                ("rope_frequency", C.c_void_p), ("device_status", C.c_void_p)]
+
+
+def compressor_initial_state(ratio, head_dim, overlap):
+    """The state before any token: zeros, and with two halves the previous half's
+    scores at minus infinity (src/graph/attention.c:540-551)."""
+    width, slots = head_dim * (2 if overlap else 1), ratio * (2 if overlap else 1)
+    kv, score = np.zeros((slots, width), np.float32), np.zeros((slots, width), np.float32)
+    if overlap:
+        score[:ratio, :head_dim] = -np.inf
+    return kv, score
+
+
+def _compressor_call(call, ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv,
+                     state_score, norm_weights, epsilon, rope_dims, rope_frequency):
+    token_kv = np.ascontiguousarray(token_kv, np.float32)
+    token_score = np.ascontiguousarray(token_score, np.float32)
+    ape = np.ascontiguousarray(ape, np.float32)
+    state_kv = np.ascontiguousarray(state_kv, np.float32)
+    state_score = np.ascontiguousarray(state_score, np.float32)
+    tokens = token_kv.shape[0]
+    capacity = max(1, tokens // ratio + 1)
+    after_kv, after_score = np.zeros_like(state_kv), np.zeros_like(state_score)
+    compressed = np.zeros((capacity, head_dim), np.float32)
+    positions = np.zeros(capacity, np.uint64)
+    a = CompressorArgs()
+    a.ratio, a.head_dim, a.overlap, a.start_position, a.token_count = ratio, head_dim, int(overlap), start, tokens
+    a.token_kv, a.token_score = token_kv.ctypes.data, token_score.ctypes.data
+    a.token_stride = token_kv.shape[1] if tokens else head_dim * 2
+    a.ape, a.state_kv, a.state_score = ape.ctypes.data, state_kv.ctypes.data, state_score.ctypes.data
+    a.after_kv, a.after_score = after_kv.ctypes.data, after_score.ctypes.data
+    a.compressed, a.compressed_stride, a.positions = compressed.ctypes.data, head_dim, positions.ctypes.data
+    keep = [token_kv, token_score, ape, state_kv, state_score]
+    if norm_weights is not None:
+        keep.append(np.ascontiguousarray(norm_weights, np.float32))
+        a.norm_weights, a.epsilon, a.rope_dims = keep[-1].ctypes.data, float(epsilon), rope_dims
+        if rope_dims and rope_frequency is not None:
+            keep.append(np.ascontiguousarray(rope_frequency, np.float64))
+            a.rope_frequency = keep[-1].ctypes.data
+    emitted = _u64()
+    ok = call(a, emitted)
+    if ok != 1:
+        return None
+    n = emitted.value
+    return compressed[:n].copy(), positions[:n].copy(), after_kv, after_score
+
+
 def build_oracle(reference_tree="/root/reference"):
     """Compile the restatement, and the reference build when its tree exists."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
@@ -304,6 +359,16 @@ class Oracle(_Gqa):
         ok = self.lib.yvx_oracle_latent_reduce_full(C.addressof(args_struct), out.reshape(-1))
         return out if ok else None
 
+    def compressor_chunk(self, ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv,
+                         state_score, norm_weights=None, epsilon=1e-6, rope_dims=0, rope_frequency=None):
+        """Rolling compressor over a chunk -> (compressed [emitted, head_dim], positions,
+        after_kv, after_score) or None on a refusal."""
+        self.lib.yvx_oracle_compressor_chunk.argtypes = [C.c_void_p, C.POINTER(_u64)]
+        return _compressor_call(
+            lambda a, n: self.lib.yvx_oracle_compressor_chunk(C.addressof(a), C.byref(n)),
+            ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv, state_score,
+            norm_weights, epsilon, rope_dims, rope_frequency)
+
     def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale):
         """bf16 bit arrays: q_nope [H,dn], q_rope [H,dr], w_uk [H,dn,dc],
         latent [L,dc], rope_key [L,dr] -> float32 [H,dc]."""
@@ -365,6 +430,18 @@ class Reference(_Gqa):
             C.addressof(indexer) if indexer is not None else None, out.reshape(-1),
             counts, positions.reshape(-1))
         return (out, counts, positions) if ok == 1 else None
+
+
+    def compressor_chunk(self, kind, ratio, head_dim, overlap, start, token_kv, token_score, ape,
+                         state_kv, state_score, norm_weights=None, epsilon=1e-6, rope_dims=0, policy=None):
+        """The reference's own transition per token and publication chain per emission.
+        kind: 1 main rows, 2 index rows."""
+        self.lib.yvx_ref_compressor_chunk.argtypes = [C.c_void_p, C.c_uint, C.c_void_p, C.POINTER(_u64)]
+        return _compressor_call(
+            lambda a, n: self.lib.yvx_ref_compressor_chunk(
+                C.addressof(a), kind, C.addressof(policy) if policy is not None else None, C.byref(n)),
+            ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv, state_score,
+            norm_weights, epsilon, rope_dims, None)
 
 
 def reference_available():

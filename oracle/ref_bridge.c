@@ -384,3 +384,100 @@ int yvx_ref_latent_reduce_chunk(const yvx_oracle_latent_args *a,
                trace_counts, trace_positions, indexer ? indexer->topk : 0ull, &scratch, &result,
                &failure, &err) == YVEX_OK;
 }
+
+/* The reference's rolling compressor over a chunk of tokens: its own state
+ * transition once per token, and on each emission the publication chain of its
+ * chunk executor (round, RMS norm, round, rotation, round), each step the
+ * reference's own function. kind: 1 the main rows, 2 the index rows. */
+int yvx_ref_compressor_chunk(const yvx_oracle_compressor_args *a, unsigned int kind,
+                             const yvx_oracle_position_policy *policy,
+                             unsigned long long *emitted)
+{
+    yvex_attention_layer_plan layer;
+    yvex_attention_rolling_state_view current;
+    yvex_attention_rolling_state_output after;
+    yvex_attention_failure failure;
+    yvex_error err;
+    unsigned long long width = a->head_dim * (a->overlap ? 2ull : 1ull);
+    unsigned long long slots = a->ratio * (a->overlap ? 2ull : 1ull);
+    unsigned long long extent = width * slots, token, count = 0;
+    float *bank[2] = {NULL, NULL}, *scratch_row = NULL;
+    int ok = 0, which = 0;
+    if (emitted) *emitted = 0;
+    memset(&layer, 0, sizeof(layer));
+    memset(&current, 0, sizeof(current));
+    memset(&failure, 0, sizeof(failure));
+    layer.attention_class = (kind == 2u || a->overlap) ? YVEX_ATTENTION_CLASS_CSA
+                                                       : YVEX_ATTENTION_CLASS_HCA;
+    layer.compression_ratio = a->ratio;
+    layer.head_dimension = kind == 1u ? a->head_dim : 4ull * a->head_dim;
+    layer.indexer_head_dimension = kind == 2u ? a->head_dim : 0ull;
+    layer.rope_head_dimension = a->rope_dims;
+    layer.rms_norm_epsilon = a->epsilon;
+    layer.compute_contract = YVEX_ATTENTION_COMPUTE_BF16_F32_RNE_V1;
+    if (policy) ref_position(policy, a->rope_dims, &layer.position);
+    bank[0] = malloc((size_t)extent * 2u * sizeof(float));
+    bank[1] = malloc((size_t)extent * 2u * sizeof(float));
+    scratch_row = malloc((size_t)a->head_dim * sizeof(float));
+    if (!bank[0] || !bank[1] || !scratch_row) goto done;
+    memcpy(bank[0], a->state_kv, (size_t)extent * sizeof(float));
+    memcpy(bank[0] + extent, a->state_score, (size_t)extent * sizeof(float));
+    current.present = 1;
+    current.schema_version = YVEX_ATTENTION_ROLLING_STATE_SCHEMA_V1;
+    current.kind = kind == 1u ? YVEX_ATTENTION_ROLLING_MAIN : YVEX_ATTENTION_ROLLING_INDEXER;
+    current.attention_class = layer.attention_class;
+    current.next_token_position = a->start_position;
+    current.ratio = a->ratio;
+    current.head_dimension = a->head_dim;
+    current.state_width = width;
+    current.state_slots = slots;
+    current.cursor = current.current_fill = a->start_position % a->ratio;
+    current.previous_fill = a->overlap && a->start_position >= a->ratio ? a->ratio : 0ull;
+    current.kv_state_stride = current.score_state_stride = width;
+    current.kv_state_extent = current.score_state_extent = extent;
+    current.kv_state = bank[0];
+    current.score_state = bank[0] + extent;
+    current.overlap = a->overlap;
+    current.rotated = kind == 2u;
+    for (token = 0; token < a->token_count; ++token) {
+        unsigned long long position = a->start_position + token;
+        float *out = a->compressed ? a->compressed + count * a->compressed_stride : scratch_row;
+        int emitted_now = 0;
+        memset(&after, 0, sizeof(after));
+        after.kv_state = bank[which ^ 1];
+        after.score_state = bank[which ^ 1] + extent;
+        after.kv_state_stride = after.score_state_stride = width;
+        after.kv_state_extent = after.score_state_extent = extent;
+        if (yvex_attention_rolling_state_step_cpu(
+                &layer, &current, a->token_kv + token * a->token_stride,
+                a->token_score + token * a->token_stride, a->ape + (position % a->ratio) * width,
+                &after, out, a->head_dim, &emitted_now, &failure, &err) != YVEX_OK)
+            goto done;
+        if (emitted_now) {
+            if (a->norm_weights) {
+                if (!yvex_attention_compute_round(layer.compute_contract, out, a->head_dim) ||
+                    !yvex_attention_rms_norm(out, a->head_dim, a->norm_weights, a->epsilon) ||
+                    !yvex_attention_compute_round(layer.compute_contract, out, a->head_dim))
+                    goto done;
+                if (a->rope_dims &&
+                    (!yvex_attention_rope_apply(out, a->head_dim, a->rope_dims,
+                                                position + 1ull - a->ratio, &layer.position, 0) ||
+                     !yvex_attention_compute_round(layer.compute_contract, out, a->head_dim)))
+                    goto done;
+            }
+            if (a->positions) a->positions[count] = position + 1ull - a->ratio;
+            ++count;
+        }
+        memcpy(&current, &after, sizeof(current));
+        which ^= 1;
+    }
+    memcpy(a->after_kv, bank[which], (size_t)extent * sizeof(float));
+    memcpy(a->after_score, bank[which] + extent, (size_t)extent * sizeof(float));
+    if (emitted) *emitted = count;
+    ok = 1;
+done:
+    free(bank[0]);
+    free(bank[1]);
+    free(scratch_row);
+    return ok;
+}

@@ -1076,3 +1076,138 @@ int yvx_oracle_full_attention_f32(const float *qkv, unsigned long long rows,
         }
     return 1;
 }
+
+/* ---- rolling compressor ----------------------------------------------------- */
+
+/* attention_rolling_emit (src/graph/attention.c:697-743): per lane a softmax over
+ * the group's scores in double, libm exp, previous half (lane) before current half
+ * (lane + head_dim) slot by slot, quotient narrowed to float. */
+static int compressor_emit(const float *kv, const float *score, unsigned long long width,
+                           unsigned long long head_dim, unsigned long long ratio, int overlap,
+                           float *out)
+{
+    unsigned long long lane, slot;
+    for (lane = 0; lane < head_dim; ++lane) {
+        double maximum = -HUGE_VAL, denominator = 0.0, value = 0.0;
+        for (slot = 0; slot < ratio; ++slot) {
+            double s = score[slot * width + lane];
+            if (overlap) {
+                double s2 = score[(ratio + slot) * width + lane + head_dim];
+                if (s2 > maximum) maximum = s2;
+            }
+            if (s > maximum) maximum = s;
+        }
+        for (slot = 0; slot < ratio; ++slot) {
+            double w = exp((double)score[slot * width + lane] - maximum);
+            denominator += w;
+            value += w * (double)kv[slot * width + lane];
+            if (overlap) {
+                double w2 = exp((double)score[(ratio + slot) * width + lane + head_dim] - maximum);
+                denominator += w2;
+                value += w2 * (double)kv[(ratio + slot) * width + lane + head_dim];
+            }
+        }
+        if (!isfinite(denominator) || denominator <= 0.0 || !isfinite(value)) return 0;
+        out[lane] = (float)(value / denominator);
+    }
+    return 1;
+}
+
+static int compressor_round(float *values, unsigned long long count)
+{
+    unsigned long long i;
+    for (i = 0; i < count; ++i) {
+        if (!isfinite(values[i])) return 0;
+        values[i] = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(values[i]));
+    }
+    return 1;
+}
+
+/* attention_rms_norm_apply (src/graph/numeric.c:630-654): mean of squares and the
+ * scaling in double, lanes in order, narrowed to float. */
+static int compressor_rms_norm(float *values, unsigned long long count, const float *weights,
+                               double epsilon)
+{
+    unsigned long long i;
+    double mean = 0.0, inverse;
+    if (!isfinite(epsilon) || epsilon <= 0.0) return 0;
+    for (i = 0; i < count; ++i) {
+        double v = values[i];
+        if (!isfinite(v) || !isfinite(weights[i])) return 0;
+        mean += v * v;
+    }
+    mean /= (double)count;
+    inverse = 1.0 / sqrt(mean + epsilon);
+    if (!isfinite(inverse)) return 0;
+    for (i = 0; i < count; ++i) {
+        double v = (double)values[i] * inverse;
+        v *= (double)weights[i];
+        if (!isfinite(v)) return 0;
+        values[i] = (float)v;
+    }
+    return 1;
+}
+
+/* yvex_attention_rolling_state_step_cpu (src/graph/attention.c:745-836) once per
+ * token, followed on an emission by the chain of cpu_chunk_rolling_step
+ * (src/graph/attention_execute.c:776-806): round, RMS norm, round, rotation at the
+ * group's first position, round. The state's cursor and fills follow from the
+ * number of consumed tokens (attention_rolling_state_validate, :569-626). */
+int yvx_oracle_compressor_chunk(const yvx_oracle_compressor_args *a, unsigned long long *emitted)
+{
+    unsigned long long width, slots, token, lane, slot, count = 0;
+    if (emitted) *emitted = 0;
+    if (!a || !a->ratio || !a->head_dim || !a->ape || !a->state_kv || !a->state_score ||
+        !a->after_kv || !a->after_score || (a->token_count && (!a->token_kv || !a->token_score)))
+        return 0;
+    width = a->head_dim * (a->overlap ? 2ull : 1ull);
+    slots = a->ratio * (a->overlap ? 2ull : 1ull);
+    if (a->token_count && a->token_stride < width) return 0;
+    if (a->after_kv != a->state_kv)
+        memcpy(a->after_kv, a->state_kv, (size_t)(slots * width) * sizeof(float));
+    if (a->after_score != a->state_score)
+        memcpy(a->after_score, a->state_score, (size_t)(slots * width) * sizeof(float));
+    for (token = 0; token < a->token_count; ++token) {
+        unsigned long long position = a->start_position + token;
+        unsigned long long cursor = position % a->ratio;
+        const float *kv = a->token_kv + token * a->token_stride;
+        const float *score = a->token_score + token * a->token_stride;
+        const float *ape = a->ape + cursor * width;
+        slot = a->overlap ? a->ratio + cursor : cursor;
+        for (lane = 0; lane < width; ++lane)
+            if (!isfinite(kv[lane]) || !isfinite(score[lane]) || !isfinite(ape[lane])) return 0;
+        for (lane = 0; lane < width; ++lane) {
+            a->after_kv[slot * width + lane] = kv[lane];
+            a->after_score[slot * width + lane] = score[lane] + ape[lane];
+        }
+        if (cursor + 1ull != a->ratio) continue;
+        if (a->compressed) {
+            float *out = a->compressed + count * a->compressed_stride;
+            if (a->compressed_stride < a->head_dim ||
+                !compressor_emit(a->after_kv, a->after_score, width, a->head_dim, a->ratio,
+                                 a->overlap, out))
+                return 0;
+            if (a->norm_weights) {
+                if (!compressor_round(out, a->head_dim) ||
+                    !compressor_rms_norm(out, a->head_dim, a->norm_weights, a->epsilon) ||
+                    !compressor_round(out, a->head_dim))
+                    return 0;
+                if (a->rope_dims &&
+                    (!yvx_oracle_rope_apply(out, a->head_dim, a->rope_dims,
+                                            position + 1ull - a->ratio, a->rope_frequency, 0) ||
+                     !compressor_round(out, a->head_dim)))
+                    return 0;
+            }
+        }
+        if (a->positions) a->positions[count] = position + 1ull - a->ratio;
+        ++count;
+        if (a->overlap) {
+            memcpy(a->after_kv, a->after_kv + a->ratio * width,
+                   (size_t)(a->ratio * width) * sizeof(float));
+            memcpy(a->after_score, a->after_score + a->ratio * width,
+                   (size_t)(a->ratio * width) * sizeof(float));
+        }
+    }
+    if (emitted) *emitted = count;
+    return 1;
+}

@@ -153,6 +153,34 @@ int yvx_oracle_csa_select(const yvx_oracle_indexer *indexer, unsigned long long 
                           unsigned long long *selected_count, unsigned long long *valid_count,
                           float *scores_out);
 
+/* Rolling compressor: the per-token state transition that turns every `ratio`
+ * projected rows into one compressed row (softmax-weighted mean per lane), run
+ * over a chunk of tokens, with the publication chain that follows an emission
+ * (bf16 round, RMS norm, bf16 round, position rotation, bf16 round). */
+typedef struct {
+    unsigned long long ratio, head_dim;
+    int overlap;                              /* 1: two halves (sparse class, main and indexer rows) */
+    unsigned long long start_position;        /* tokens already consumed by the state */
+    unsigned long long token_count;
+    const float *token_kv, *token_score;      /* [token][token_stride], state_width lanes used */
+    unsigned long long token_stride;
+    const float *ape;                         /* [ratio][state_width], row = position % ratio */
+    const float *state_kv, *state_score;      /* [state_slots][state_width] before the chunk */
+    float *after_kv, *after_score;            /* [state_slots][state_width] after it */
+    float *compressed;                        /* [emitted][compressed_stride] */
+    unsigned long long compressed_stride;
+    unsigned long long *positions;            /* [emitted] first token of each emitted group */
+    const float *norm_weights;                /* [head_dim]; NULL: raw emission, no publication chain */
+    double epsilon;
+    unsigned long long rope_dims;             /* with norm_weights: 0 skips the rotation */
+    const double *rope_frequency;             /* [rope_dims/2] */
+    int *device_status;                       /* unused here: keeps the device library's layout */
+} yvx_oracle_compressor_args;
+/* state_width = head_dim * (overlap ? 2 : 1), state_slots = ratio * (overlap ? 2 : 1).
+ * Returns 1 and the number of emitted rows, 0 on a refusal. */
+int yvx_oracle_compressor_chunk(const yvx_oracle_compressor_args *args,
+                                unsigned long long *emitted);
+
 /* Latent decode with a separate rope key and an absorbed up-projection. */
 int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
                           const unsigned short *q_rope_bf16,
