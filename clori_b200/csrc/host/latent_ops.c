@@ -340,6 +340,7 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
     const char *where = "b200.attention.compress";
     unsigned long long width = 0ull, slots = 0ull, elements = 0ull, emitted, launched = 0ull;
     yvx_compressor_args a;
+    unsigned int activation_launches = 0u;
     int overlap, rc;
     if (failure) memset(failure, 0, sizeof(*failure));
     if (!r || !facts || !r->position_rows || !r->state_kv || !r->state_score || !r->next_state_kv ||
@@ -390,6 +391,17 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
          (!r->rope_frequency || !view_ok(backend, r->rope_frequency, YVEX_DTYPE_F64, r->rope_dimension / 2ull))))
         return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements, 0ull, err,
                                YVEX_ERR_FORMAT, "tensor views do not cover the stated geometry");
+    if (r->activation_quantization) {
+        unsigned long long active = r->kind == YVEX_B200_ROLLING_MAIN ? r->head_dimension - r->rope_dimension
+                                                                      : r->head_dimension;
+        if (r->activation_quantization != 8u && r->activation_quantization != 4u)
+            return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_NUMERIC, 8ull, r->activation_quantization,
+                                   err, YVEX_ERR_FORMAT, "activation quantisation is unsupported");
+        if (!r->activation_block_width || r->activation_block_width > 1024ull || active % r->activation_block_width)
+            return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->activation_block_width,
+                                   active, err, YVEX_ERR_BOUNDS,
+                                   "activation requires exact block divisibility");
+    }
     if (r->norm_weights && !(isfinite(r->rms_norm_epsilon) && r->rms_norm_epsilon > 0.0))
         return compress_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
                                YVEX_ERR_INVALID_ARG, "the norm epsilon must be positive and finite");
@@ -427,7 +439,31 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
         }
         return yvx_backend_device_fail(backend, rc, where, err);
     }
-    rc = finish(backend, facts, 1u, 0ull, where, err);
+    if (r->activation_quantization && emitted) {
+        /* main rows keep their rotated lanes; index rows are quantised whole
+         * (src/graph/attention_execute.c:807-818) */
+        yvx_activation_args q;
+        memset(&q, 0, sizeof(q));
+        q.values = a.compressed;
+        q.rows = emitted;
+        q.row_stride = r->head_dimension;
+        q.count = r->kind == YVEX_B200_ROLLING_MAIN ? r->head_dimension - r->rope_dimension : r->head_dimension;
+        q.quantization = r->activation_quantization;
+        q.block_width = (unsigned int)r->activation_block_width;
+        q.hadamard = r->activation_hadamard;
+        q.hadamard_scale = 1.0f / sqrtf((float)q.count);
+        q.status = backend->status_device;
+        rc = q.count ? yvx_cuda_activation_quant(&q, backend->stream) : 0;
+        if (rc != 0) {
+            if (failure) {
+                failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
+                failure->stage = "compress";
+            }
+            return yvx_backend_device_fail(backend, rc, where, err);
+        }
+        activation_launches = q.count ? 1u : 0u;
+    }
+    rc = finish(backend, facts, 1u + activation_launches, 0ull, where, err);
     if (rc != YVEX_OK) {
         if (failure) {
             failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC
@@ -442,6 +478,82 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
         r->compressed->is_written = 1;
         if (r->compressed_positions) r->compressed_positions->is_written = 1;
     }
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+static int activation_refuse(yvex_b200_attention_failure *failure, yvex_b200_attention_failure_code code,
+                             unsigned long long expected, unsigned long long actual, yvex_error *err,
+                             yvex_status status, const char *message)
+{
+    if (failure) {
+        failure->code = code;
+        failure->stage = "activation";
+        failure->expected = expected;
+        failure->actual = actual;
+    }
+    return yvx_fail(err, status, "b200.attention.activation", message);
+}
+
+int yvex_b200_attention_activation_execute(yvex_backend *backend,
+                                           const yvex_b200_attention_activation_request *r,
+                                           yvex_b200_attention_failure *failure,
+                                           yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.attention.activation";
+    unsigned long long elements = 0ull;
+    yvx_activation_args q;
+    int rc;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    if (!r || !facts || !r->values || !r->count || !r->block_width)
+        return activation_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                                 YVEX_ERR_INVALID_ARG, "activation requires values and a block width");
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (r->quantization != 8u && r->quantization != 4u)
+        return activation_refuse(failure, YVEX_B200_ATTENTION_FAILURE_NUMERIC, 8ull, r->quantization, err,
+                                 YVEX_ERR_FORMAT, "activation quantisation is unsupported");
+    if (r->count % r->block_width)
+        return activation_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, r->block_width, r->count,
+                                 err, YVEX_ERR_BOUNDS, "activation requires exact block divisibility");
+    if (r->count > 8192ull || r->block_width > 1024ull)
+        return activation_refuse(failure, YVEX_B200_ATTENTION_FAILURE_CAPABILITY, 8192ull, r->count, err,
+                                 YVEX_ERR_UNSUPPORTED, "rows of at most 8192 lanes, blocks of at most 1024");
+    if (r->row_stride < r->count || !yvx_u64_mul(r->rows ? r->rows : 1ull, r->row_stride, &elements) ||
+        !view_ok(backend, r->values, YVEX_DTYPE_F32, elements - (r->row_stride - r->count)))
+        return activation_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements, r->values->bytes,
+                                 err, YVEX_ERR_FORMAT, "tensor view does not cover the stated rows");
+    memset(&q, 0, sizeof(q));
+    q.values = (float *)r->values->data;
+    q.rows = r->rows;
+    q.row_stride = r->row_stride;
+    q.count = r->count;
+    q.quantization = r->quantization;
+    q.block_width = (unsigned int)r->block_width;
+    q.hadamard = r->hadamard;
+    q.hadamard_scale = 1.0f / sqrtf((float)r->count);
+    q.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_activation_quant(&q, backend->stream);
+    if (rc != 0) {
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
+            failure->stage = "activation";
+        }
+        return yvx_backend_device_fail(backend, rc, where, err);
+    }
+    rc = finish(backend, facts, r->rows ? 1u : 0u, 0ull, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC
+                                                  : YVEX_B200_ATTENTION_FAILURE_SYNCHRONIZE;
+            failure->stage = "activation";
+        }
+        return rc;
+    }
+    r->values->is_written = 1;
     yvex_error_clear(err);
     return YVEX_OK;
 }

@@ -251,11 +251,34 @@ typedef struct yvex_b200_attention_compress_request {
     yvex_device_tensor *compressed;                   /* F32 [emitted][head_dimension] */
     yvex_device_tensor *compressed_positions;         /* I64 [emitted] */
     unsigned long long emitted;                       /* out: rows written */
+    /* The quantising activation the reference applies to each emitted row after the chain
+     * (src/graph/attention_execute.c:807-818): 0 none, 8 FP8 E4M3, 4 FP4 E2M1; main rows
+     * leave their rotated lanes alone, index rows are transformed and quantised whole. */
+    unsigned int activation_quantization;
+    unsigned long long activation_block_width;
+    int activation_hadamard;
 } yvex_b200_attention_compress_request;
 int yvex_b200_attention_compress_execute(yvex_backend *backend,
                                          yvex_b200_attention_compress_request *request,
                                          yvex_b200_attention_failure *failure,
                                          yvex_backend_operation_facts *facts, yvex_error *err);
+
+/* Activation fake quantisation in place over the first `count` lanes of `rows` rows of an
+ * F32 tensor (yvex_attention_activation_apply, src/graph/core.c:829-945): what the
+ * reference applies to new local rows, emitted compressed rows and index queries.
+ * Refusals follow the reference: a count that is not a multiple of the block width is
+ * YVEX_ERR_BOUNDS, an unknown quantisation YVEX_ERR_FORMAT, a non-finite lane YVEX_ERR_FORMAT. */
+typedef struct yvex_b200_attention_activation_request {
+    yvex_device_tensor *values;                       /* F32 [rows][row_stride] */
+    unsigned long long rows, row_stride, count;
+    unsigned int quantization;                        /* 8: FP8 E4M3, 4: FP4 E2M1 */
+    unsigned long long block_width;
+    int hadamard;
+} yvex_b200_attention_activation_request;
+int yvex_b200_attention_activation_execute(yvex_backend *backend,
+                                           const yvex_b200_attention_activation_request *request,
+                                           yvex_b200_attention_failure *failure,
+                                           yvex_backend_operation_facts *facts, yvex_error *err);
 
 int yvex_b200_attention_reduce_execute(yvex_backend *backend,
                                        const yvex_b200_attention_reduce_request *request,

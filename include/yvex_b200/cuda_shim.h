@@ -344,6 +344,31 @@ typedef struct yvx_compressor_args {
 int yvx_cuda_compressor_chunk(const yvx_compressor_args *args, void *stream,
                               unsigned long long *emitted);
 
+/* ---- activation fake quantisation of rows in place (one launch) -----------------------
+ * Replaces yvex_attention_activation_apply (src/graph/core.c:829-945; CUDA stage:
+ * yvex_attention_activation_quantize, src/backend/cuda/kernels.cu:1136). Applied by the reference to the non-rotated lanes
+ * of new local rows and of emitted compressed rows (FP8, blocks of 64) and to index
+ * queries and emitted index rows (Hadamard transform, then FP4, blocks of 32).
+ * Per row of `count` lanes: with hadamard != 0 the row, zero-padded to a power of two, goes
+ * through single-precision butterflies of growing stride and its first count lanes are
+ * multiplied by hadamard_scale (the caller passes 1.0f / sqrtf((float)count)); then per
+ * block of block_width lanes: amax = max(|x|, floor) with floor 1e-4 (FP8) or 6 * 2^-126
+ * (FP4), scale = amax / 448 (FP8) or amax / 6 (FP4) rounded up to a power of two, each
+ * lane replaced by bf16(nearest(x / scale) * scale), nearest = the closest FP8 E4M3 (FP4
+ * E2M1) value, exact ties to the even code. Every step is exact or a single rounding, so
+ * results are bit-equal to the reference's. quantization: 8 or 4. Contract: count a
+ * multiple of block_width (else YVEX_ERR_BOUNDS), count <= 8192, block_width <= 1024.
+ * status: 1 when a lane is not finite. */
+typedef struct yvx_activation_args {
+    float *values;                            /* [rows][row_stride], first count lanes of each row */
+    unsigned long long rows, row_stride, count;
+    unsigned int quantization, block_width;
+    int hadamard;
+    float hadamard_scale;
+    int *status;
+} yvx_activation_args;
+int yvx_cuda_activation_quant(const yvx_activation_args *args, void *stream);
+
 /* ---- KV append with rotary embedding (one launch per step) ---------------------------
  * Replaces, for the new rows of a step, the two rotate-half launches on Q and K
  * (yvex_cuda_transformer_rotary_half / _rotary_half_f32, src/backend/cuda/transformer.c:

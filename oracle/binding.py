@@ -102,6 +102,15 @@ def _compressor_call(call, ratio, head_dim, overlap, start, token_kv, token_scor
     return compressed[:n].copy(), positions[:n].copy(), after_kv, after_score
 
 
+def _activation_call(function, rows, quantization, block_width, hadamard):
+    function.argtypes = [_f32p, _u64, C.c_uint, _u64, C.c_int]
+    out = np.ascontiguousarray(rows, np.float32).copy()
+    for row in out.reshape(-1, out.shape[-1]):
+        if function(row, row.size, quantization, block_width, int(hadamard)) != 1:
+            return None
+    return out
+
+
 def build_oracle(reference_tree="/root/reference"):
     """Compile the restatement, and the reference build when its tree exists."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
@@ -369,6 +378,10 @@ class Oracle(_Gqa):
             ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv, state_score,
             norm_weights, epsilon, rope_dims, rope_frequency)
 
+    def activation_quant(self, rows, quantization, block_width, hadamard):
+        """Fake quantisation of every row of a float32 [rows, count] array -> new array, or None."""
+        return _activation_call(self.lib.yvx_oracle_activation_quant, rows, quantization, block_width, hadamard)
+
     def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale):
         """bf16 bit arrays: q_nope [H,dn], q_rope [H,dr], w_uk [H,dn,dc],
         latent [L,dc], rope_key [L,dr] -> float32 [H,dc]."""
@@ -442,6 +455,10 @@ class Reference(_Gqa):
                 C.addressof(a), kind, C.addressof(policy) if policy is not None else None, C.byref(n)),
             ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv, state_score,
             norm_weights, epsilon, rope_dims, None)
+
+
+    def activation_quant(self, rows, quantization, block_width, hadamard):
+        return _activation_call(self.lib.yvx_ref_activation_quant, rows, quantization, block_width, hadamard)
 
 
 def reference_available():

@@ -481,3 +481,28 @@ done:
     free(scratch_row);
     return ok;
 }
+
+/* The reference's activation fake quantisation of one row in place (its policy record
+ * filled as the model family fills it: final-dimension blocks, 8-bit exponent scales). */
+int yvx_ref_activation_quant(float *values, unsigned long long count, unsigned int quantization,
+                             unsigned long long block_width, int hadamard)
+{
+    yvex_attention_activation_policy policy;
+    yvex_attention_scratch_budget scratch;
+    yvex_attention_failure failure;
+    yvex_error err;
+    memset(&policy, 0, sizeof(policy));
+    memset(&scratch, 0, sizeof(scratch));
+    memset(&failure, 0, sizeof(failure));
+    policy.required = 1;
+    policy.quantization = quantization == 8u ? YVEX_ATTENTION_QUANT_FP8_E4M3_UE8M0_FAKE_DEQUANT
+                                             : YVEX_ATTENTION_QUANT_FP4_E2M1_UE8M0_FAKE_DEQUANT;
+    policy.block_axis = YVEX_ATTENTION_AXIS_FINAL_DIMENSION;
+    policy.block_width = block_width;
+    policy.scale_format = YVEX_ATTENTION_SCALE_UE8M0;
+    policy.pre_transform = hadamard ? YVEX_ATTENTION_TRANSFORM_DAO_FHT_V1_1_0_POST2
+                                    : YVEX_ATTENTION_TRANSFORM_NONE;
+    policy.fake_quant_inplace = 1;
+    return yvex_attention_activation_apply(&policy, values, count, 0ull, YVEX_TENSOR_ROLE_UNKNOWN,
+                                           &scratch, &failure, &err) == YVEX_OK;
+}

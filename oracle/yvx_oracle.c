@@ -1211,3 +1211,104 @@ int yvx_oracle_compressor_chunk(const yvx_oracle_compressor_args *a, unsigned lo
     if (emitted) *emitted = count;
     return 1;
 }
+
+/* ---- activation fake quantisation --------------------------------------------- */
+
+/* yvex_quant_fp8_e4m3fn_decode (src/gguf/quant_scalar.c:145-161) */
+static float activation_fp8_decode(unsigned int code)
+{
+    unsigned int exponent = (code >> 3) & 0x0fu, mantissa = code & 0x07u;
+    if (!(code & 0x7fu)) return 0.0f;
+    return exponent == 0u ? ldexpf((float)mantissa, -9)
+                          : ldexpf(1.0f + (float)mantissa / 8.0f, (int)exponent - 7);
+}
+
+static const float activation_fp4_values[8] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f};
+
+/* attention_fp8_e4m3fn_encode / attention_fp4_e2m1_encode (src/graph/numeric.c:1178-1200,
+ * 1277-1299): the code whose value is nearest to the clamped magnitude, an exact tie going to
+ * the even code; the value of that code with the input's sign. */
+static float activation_nearest(float value, unsigned int quantization)
+{
+    const unsigned int codes = quantization == 8u ? 0x7fu : 8u;
+    const float limit = quantization == 8u ? 448.0f : 6.0f;
+    float magnitude = fabsf(value), best_error = INFINITY, decoded;
+    unsigned int code, best = 0u;
+    if (magnitude > limit) magnitude = limit;
+    for (code = 0u; code < codes; ++code) {
+        float candidate = quantization == 8u ? activation_fp8_decode(code) : activation_fp4_values[code];
+        float error = fabsf(candidate - magnitude);
+        if (error < best_error || (error == best_error && !(code & 1u) && (best & 1u))) {
+            best_error = error;
+            best = code;
+        }
+    }
+    decoded = quantization == 8u ? activation_fp8_decode(best) : activation_fp4_values[best];
+    return signbit(value) ? -decoded : decoded;
+}
+
+/* attention_fake_quant_block (src/graph/numeric.c:1210-1258): the block's largest magnitude
+ * (at least 1e-4 for FP8, 6 * 2^-126 for FP4) over the format's largest value, rounded up to a
+ * power of two and stored as an 8-bit exponent (:990-1000, :1157-1171). */
+static int activation_block(float *values, unsigned long long count, unsigned int quantization)
+{
+    const float limit = quantization == 8u ? 448.0f : 6.0f;
+    float amax = quantization == 8u ? 1.0e-4f : 6.0f * ldexpf(1.0f, -126), scale, mantissa;
+    unsigned long long i;
+    int exponent;
+    for (i = 0; i < count; ++i) {
+        if (!isfinite(values[i])) return 0;
+        if (fabsf(values[i]) > amax) amax = fabsf(values[i]);
+    }
+    mantissa = frexpf(amax / limit, &exponent);
+    if (mantissa > 0.5f) exponent++;
+    exponent += 126;                 /* scale = 2^(exponent - 127) */
+    if (exponent < 0) exponent = 0;
+    if (exponent > 254) exponent = 254;
+    scale = exponent ? ldexpf(1.0f, exponent - 127) : ldexpf(1.0f, -127);
+    for (i = 0; i < count; ++i) {
+        float normalized = values[i] / scale;
+        if (quantization == 8u && normalized > limit) normalized = limit;
+        if (quantization == 8u && normalized < -limit) normalized = -limit;
+        values[i] = yvx_oracle_bf16_decode(
+            yvx_oracle_bf16_encode(activation_nearest(normalized, quantization) * scale));
+    }
+    return 1;
+}
+
+/* yvex_attention_activation_apply (src/graph/core.c:829-945) with the transform of
+ * yvex_attention_hadamard_cpu (src/graph/numeric.c:1008-1078): butterflies of growing stride
+ * in single precision over the zero-padded row, the first count lanes scaled by 1/sqrtf(count). */
+int yvx_oracle_activation_quant(float *values, unsigned long long count, unsigned int quantization,
+                                unsigned long long block_width, int hadamard)
+{
+    unsigned long long offset;
+    if (!values || !count || !block_width || (quantization != 8u && quantization != 4u)) return 0;
+    if (hadamard) {
+        unsigned long long padded = 1ull, step, block, lane, i;
+        float scale = 1.0f / sqrtf((float)count), *scratch;
+        while (padded < count) padded *= 2ull;
+        scratch = calloc((size_t)padded, sizeof(*scratch));
+        if (!scratch) return 0;
+        for (i = 0; i < count; ++i) {
+            if (!isfinite(values[i])) {
+                free(scratch);
+                return 0;
+            }
+            scratch[i] = values[i];
+        }
+        for (step = 1ull; step < padded; step *= 2ull)
+            for (block = 0; block < padded; block += step * 2ull)
+                for (lane = 0; lane < step; ++lane) {
+                    float left = scratch[block + lane], right = scratch[block + lane + step];
+                    scratch[block + lane] = left + right;
+                    scratch[block + lane + step] = left - right;
+                }
+        for (i = 0; i < count; ++i) values[i] = scratch[i] * scale;
+        free(scratch);
+    }
+    if (count % block_width) return 0;
+    for (offset = 0; offset < count; offset += block_width)
+        if (!activation_block(values + offset, block_width, quantization)) return 0;
+    return 1;
+}

@@ -181,6 +181,13 @@ typedef struct {
 int yvx_oracle_compressor_chunk(const yvx_oracle_compressor_args *args,
                                 unsigned long long *emitted);
 
+/* Activation fake quantisation of a row in place: an optional Hadamard transform over the
+ * whole row (zero-padded to a power of two, scaled by 1/sqrt(count)), then per block of
+ * block_width lanes a power-of-two scale, the nearest FP8 E4M3 (quantization 8) or FP4
+ * E2M1 (quantization 4) value with ties to the even code, and the product rounded to bf16. */
+int yvx_oracle_activation_quant(float *values, unsigned long long count, unsigned int quantization,
+                                unsigned long long block_width, int hadamard);
+
 /* Latent decode with a separate rope key and an absorbed up-projection. */
 int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
                           const unsigned short *q_rope_bf16,

@@ -1,0 +1,145 @@
+"""Activation fake quantisation on a B200. Every step of it is exact or a single rounding
+(butterfly adds, a power-of-two scale, round-to-nearest-even onto the FP8 / FP4 grid, bf16),
+so the device rows must equal the CPU checker's and the reference-made fixtures bit for bit."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from clori_b200 import abi
+from activation_cases import CASES, rows
+from compressor_cases import CASES as COMPRESSOR_CASES, build
+from oracle.binding import PositionPolicy
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "activation_quant.npz")
+
+
+def same_bits(a, b):
+    return a.shape == b.shape and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def run_gpu(backend, x, quantization, block, hadamard, count=None, expect_rc=0):
+    lib, s = backend.lib, backend.stream
+    t = backend.tensor("x", x)
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    a = abi.ActivationArgs()
+    a.values, a.rows, a.row_stride, a.count = t.data_ptr, x.shape[0], x.shape[1], count or x.shape[1]
+    a.quantization, a.block_width, a.hadamard = quantization, block, hadamard
+    a.hadamard_scale = float(np.float32(1.0) / np.sqrt(np.float32(a.count)))
+    a.status = status.data_ptr
+    rc = lib.yvx_cuda_activation_quant(C.byref(a), s)
+    assert rc == expect_rc, lib.yvx_cuda_last_error_text()
+    if rc:
+        return None
+    assert lib.yvx_cuda_stream_synchronize(s) == 0, lib.yvx_cuda_last_error_text()
+    return t.read(), int(status.read()[0])
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_rows_equal_the_checker(backend, oracle, case):
+    quantization, block, hadamard, count = case
+    x = rows(90 + count, count, n=300)
+    got, status = run_gpu(backend, x, quantization, block, hadamard)
+    assert status == 0 and same_bits(got, oracle.activation_quant(x, quantization, block, hadamard))
+
+
+def test_reference_fixtures(backend):
+    g = np.load(GOLDEN)
+    for i in range(int(g["count"])):
+        quantization, block, hadamard, count = (int(x) for x in g[f"meta{i}"])
+        got, status = run_gpu(backend, g[f"in{i}"], quantization, block, hadamard)
+        assert status == 0 and same_bits(got, g[f"out{i}"])
+
+
+def test_leading_lanes_of_wider_rows_and_full_size(backend, oracle):
+    # the reference quantises the first head_dim - rope lanes of a 512-lane row and leaves the rest
+    x = rows(7, 512, n=8192)
+    got, status = run_gpu(backend, x, 8, 64, 0, count=448)
+    assert status == 0 and same_bits(got[:, 448:], x[:, 448:])
+    sample = slice(0, 8192, 97)
+    assert same_bits(got[sample, :448], oracle.activation_quant(np.ascontiguousarray(x[sample, :448]), 8, 64, 0))
+    # quantising a quantised row again changes nothing when there is no transform in front
+    again, _ = run_gpu(backend, got, 8, 64, 0, count=448)
+    assert same_bits(again, got)
+
+
+def test_refusals_and_status(backend):
+    x = np.ones((4, 128), np.float32)
+    assert run_gpu(backend, x, 8, 48, 0, expect_rc=abi.YVEX_ERR_BOUNDS) is None
+    assert run_gpu(backend, x, 5, 64, 0, expect_rc=abi.YVEX_ERR_INVALID_ARG) is None
+    assert run_gpu(backend, x, 8, 64, 0, count=256, expect_rc=abi.YVEX_ERR_INVALID_ARG) is None
+    x[2, 77] = np.nan
+    assert run_gpu(backend, x, 8, 64, 0)[1] == 1
+    assert run_gpu(backend, x, 4, 32, 1)[1] == 1
+
+
+def ptr(tensor):
+    return C.cast(tensor.ptr, C.c_void_p) if tensor is not None else None
+
+
+def test_operator_entries(backend, oracle):
+    x = rows(11, 128, n=40)
+    t = backend.tensor("x", x)
+    r = abi.AttentionActivationRequest()
+    r.values, r.rows, r.row_stride, r.count = ptr(t), 40, 128, 128
+    r.quantization, r.block_width, r.hadamard = 4, 32, 1
+    failure, facts, err = abi.AttentionFailure(), abi.OperationFacts(), abi.Error()
+    call = lambda: backend.lib.yvex_b200_attention_activation_execute(backend.handle, C.byref(r), C.byref(failure),
+                                                                      C.byref(facts), C.byref(err))
+    assert call() == 0, err.message
+    assert facts.kernel_launches == 1 and same_bits(t.read(), oracle.activation_quant(x, 4, 32, 1))
+    r.block_width = 48
+    assert call() == abi.YVEX_ERR_BOUNDS and failure.stage == b"activation"
+    r.block_width, r.quantization = 32, 3
+    assert call() == abi.YVEX_ERR_FORMAT
+    # the compressor with the activation behind its publication chain: index rows (transform + FP4,
+    # whole row) and main rows (FP8 on the lanes in front of the rotated ones)
+    for case_index, quantization, block, hadamard in ((1, 4, 32, 1), (0, 8, 64, 0)):
+        kind, ratio, hd, overlap, rope, policy, chunks = COMPRESSOR_CASES[case_index]
+        case = build(950 + case_index, ratio, hd, overlap, (13,))
+        freq = oracle.rope_frequencies(PositionPolicy(*policy), rope)
+        kv, score = case["state"]
+        ref = oracle.compressor_chunk(ratio, hd, overlap, 0, case["token_kv"], case["token_score"], case["ape"], kv,
+                                      score, case["norm"], 1e-6, rope, freq)
+        active = hd if kind == 2 else hd - rope
+        expected = ref[0].copy()
+        expected[:, :active] = oracle.activation_quant(np.ascontiguousarray(ref[0][:, :active]), quantization, block,
+                                                       hadamard)
+        d = dict(kv=backend.tensor("kv", case["token_kv"]), score=backend.tensor("sc", case["token_score"]),
+                 ape=backend.tensor("ape", case["ape"]), skv=backend.tensor("skv", kv), ssc=backend.tensor("ssc", score),
+                 akv=backend.alloc("akv", abi.DTYPE_F32, kv.shape), asc=backend.alloc("asc", abi.DTYPE_F32, kv.shape),
+                 norm=backend.tensor("norm", case["norm"]), freq=backend.tensor("freq", freq, dtype=abi.DTYPE_F64),
+                 rows=backend.alloc("rows", abi.DTYPE_F32, (3, hd)), positions=backend.alloc("pos", abi.DTYPE_I64, (3,)))
+        c = abi.AttentionCompressRequest()
+        c.kind, c.attention_class, c.token_position, c.token_count = kind, 1, 0, 13
+        c.compression_ratio, c.head_dimension = ratio, hd
+        c.token_kv, c.token_score, c.token_stride = ptr(d["kv"]), ptr(d["score"]), 2 * hd
+        c.position_rows, c.state_kv, c.state_score = ptr(d["ape"]), ptr(d["skv"]), ptr(d["ssc"])
+        c.next_state_kv, c.next_state_score = ptr(d["akv"]), ptr(d["asc"])
+        c.norm_weights, c.rms_norm_epsilon, c.rope_dimension, c.rope_frequency = ptr(d["norm"]), 1e-6, rope, ptr(d["freq"])
+        c.compressed, c.compressed_positions = ptr(d["rows"]), ptr(d["positions"])
+        c.activation_quantization, c.activation_block_width, c.activation_hadamard = quantization, block, hadamard
+        rc = backend.lib.yvex_b200_attention_compress_execute(backend.handle, C.byref(c), C.byref(failure),
+                                                              C.byref(facts), C.byref(err))
+        assert rc == 0, err.message
+        assert c.emitted == 3 and facts.kernel_launches == 2
+        got = d["rows"].read()
+        # the chain in front may differ from the CPU in a last place (see the compressor tests); where the
+        # published rows agree, the quantised rows must agree exactly
+        unquantised_equal = True
+        plain = abi.AttentionCompressRequest.from_buffer_copy(c)
+        plain.activation_quantization = 0
+        assert backend.lib.yvex_b200_attention_compress_execute(backend.handle, C.byref(plain), C.byref(failure),
+                                                                C.byref(facts), C.byref(err)) == 0
+        published = d["rows"].read()
+        if same_bits(published, ref[0]):
+            assert same_bits(got, expected)
+        else:
+            unquantised_equal = False
+            device_expected = published.copy()
+            device_expected[:, :active] = oracle.activation_quant(np.ascontiguousarray(published[:, :active]),
+                                                                  quantization, block, hadamard)
+            assert same_bits(got, device_expected)
+        assert unquantised_equal or (published != ref[0]).sum() <= max(1, published.size // 200)
