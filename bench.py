@@ -736,6 +736,71 @@ def bench_compressor(lib, backend, abi, hbm_peak, repeats, tokens=32768):
     return result, None
 
 
+def bench_activation(lib, backend, abi, hbm_peak, repeats, rows=131072):
+    """Activation fake quantisation in place: FP8 E4M3 in blocks of 64 over the 448 leading lanes of
+    512-lane rows (what the reference applies to new local rows and emitted compressed rows), and the
+    transform + FP4 E2M1 variant over 128-lane rows (index queries). A sample of rows is compared with
+    the CPU restatement bit for bit."""
+    from oracle.binding import Oracle
+    oracle = Oracle()
+    out = {}
+    for name, stride, count, quantization, block, hadamard in (("fp8_rows_512x448", 512, 448, 8, 64, 0),
+                                                               ("fp4_hadamard_rows_128", 128, 128, 4, 32, 1)):
+        n = rows if stride == 512 else rows * 4
+        values, source, status = _alloc(lib, n * stride * 4), _alloc(lib, n * stride * 4), _alloc(lib, 4)
+        lib.yvx_cuda_fill_normal(source, abi.DTYPE_F32, n * stride, 811, 1.0, backend.stream)
+        lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+        a = abi.ActivationArgs()
+        a.values, a.rows, a.row_stride, a.count = values, n, stride, count
+        a.quantization, a.block_width, a.hadamard = quantization, block, hadamard
+        a.hadamard_scale = float(np.float32(1.0) / np.sqrt(np.float32(count)))
+        a.status = status
+        sample = np.zeros((64, stride), np.float32)
+        lib.yvx_cuda_download_async(sample.ctypes.data, source, sample.nbytes, backend.stream)
+
+        def event():
+            e = C.c_void_p()
+            assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+            return e
+        # the operation is in place and not idempotent behind a transform: time it on a fresh copy each
+        # time and subtract nothing; the copy is timed separately and reported
+        first, middle, last = event(), event(), event()
+        for _ in range(2):
+            lib.yvx_cuda_copy_async(values, source, n * stride * 4, backend.stream)
+            assert lib.yvx_cuda_activation_quant(C.byref(a), backend.stream) == 0
+        total = 0.0
+        for _ in range(repeats):
+            lib.yvx_cuda_copy_async(values, source, n * stride * 4, backend.stream)
+            lib.yvx_cuda_event_record(first, backend.stream)
+            assert lib.yvx_cuda_activation_quant(C.byref(a), backend.stream) == 0
+            lib.yvx_cuda_event_record(last, backend.stream)
+            assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+            ms = C.c_float()
+            lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+            total += ms.value
+        step = total / repeats
+        got, st = np.zeros((64, stride), np.float32), np.zeros(1, np.int32)
+        lib.yvx_cuda_download_async(got.ctypes.data, values, got.nbytes, backend.stream)
+        lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
+        expected = sample.copy()
+        expected[:, :count] = oracle.activation_quant(np.ascontiguousarray(sample[:, :count]), quantization, block,
+                                                      hadamard)
+        nbytes = n * count * 4 * 2     # every active lane read once and written once
+        out[name] = {"rows": n, "kernel_ms": step, "algorithmic_bytes": nbytes,
+                     "achieved_gbs": nbytes / (step * 1e-3) / 1e9,
+                     "frac_of_measured_hbm": nbytes / (step * 1e-3) / 1e9 / hbm_peak,
+                     "status_word": int(st[0]),
+                     "sample_rows_bit_equal_to_cpu": bool(np.array_equal(got.view(np.uint32), expected.view(np.uint32)))}
+        for ptr in (values, source, status):
+            lib.yvx_cuda_free(ptr)
+    result = {"workload": f"activation fake quantisation in place, {rows} rows of 512 lanes (448 quantised, FP8, blocks "
+                          f"of 64) and {rows * 4} rows of 128 lanes (transform + FP4, blocks of 32)",
+              "kernel": "activation_quant_kernel", "launches_per_step": 1,
+              "l2": "each launch works on a fresh 268 MB copy of its rows", **out}
+    return result, None
+
+
 def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
     """One decode step of a sparse shared-latent layer at the reference configuration's
     widths (64 heads x 512 with the last 64 lanes rotated, window 128, ratio 4, 64 index
@@ -1144,7 +1209,7 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
-                                 "compressor"],
+                                 "compressor", "activation"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1194,6 +1259,9 @@ def main():
                                   sessions=min(args.sessions, 32))
         elif args.workload == "latent_sparse":
             result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
+        elif args.workload == "activation":
+            result, _ = bench_activation(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
+                                         rows=min(args.tokens * 16, 131072))
         elif args.workload == "compressor":
             result, _ = bench_compressor(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                          tokens=min(args.tokens * 4, 32768))
@@ -1272,6 +1340,7 @@ def main():
         others["kv_append_rotary"], _ = bench_kv_append(lib, b, w.abi, hbm_peak, 10)
         others["latent_sparse_decode"], _ = bench_latent_sparse(lib, b, w.abi, 20)
         others["rolling_compressor"], _ = bench_compressor(lib, b, w.abi, hbm_peak, 10)
+        others["activation_quant"], _ = bench_activation(lib, b, w.abi, hbm_peak, 5)
 
     if rank != 0:
         if dist is not None:

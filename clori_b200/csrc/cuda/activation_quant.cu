@@ -22,8 +22,9 @@ constexpr int kActivationThreads = 128;
 __device__ __forceinline__ float activation_nearest_fp8(float m)
 {
     if (m < 0.03125f) return __fmul_rn(rintf(__fmul_rn(m, 512.0f)), 0.001953125f);
-    const float step = __uint_as_float((__float_as_uint(m) & 0x7f800000u) - (3u << 23));
-    return __fmul_rn(rintf(__fdiv_rn(m, step)), step);
+    const uint32_t step = (__float_as_uint(m) & 0x7f800000u) - (3u << 23);
+    // dividing by a power of two = multiplying by its (exact) reciprocal
+    return __fmul_rn(rintf(__fmul_rn(m, __uint_as_float(0x7f000000u - step))), __uint_as_float(step));
 }
 
 // nearest of {0, 0.5, 1, 1.5, 2, 3, 4, 6} to a magnitude in [0, 6]
@@ -92,6 +93,73 @@ activation_quant_kernel(const yvx_activation_args a, unsigned int padded)
     if (!finite) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
 }
 
+// One warp per row, four adjacent lanes per thread, 16-byte accesses, no shared memory:
+// rows are walked in segments of 128 lanes; a block of block_width lanes is block_width / 4
+// neighbouring threads, which find their largest magnitude by shuffles. With the transform
+// the row is one segment (at most 128 lanes): strides 1 and 2 are inside a thread, strides
+// 4 to 64 are exchanges with the thread whose index differs in one bit, the lower index
+// holding the left operand as in the serial loop.
+template <bool HADAMARD>
+__global__ void __launch_bounds__(kActivationThreads)
+activation_quant_warp_kernel(const yvx_activation_args a)
+{
+    const unsigned int lane = threadIdx.x & 31u;
+    const unsigned long long r = (unsigned long long)blockIdx.x * (kActivationThreads / 32) + (threadIdx.x >> 5);
+    if (r >= a.rows) return;
+    float *values = a.values + r * a.row_stride;
+    const unsigned int count = (unsigned int)a.count;
+    const unsigned int group = a.block_width / 4u;
+    const bool fp8 = a.quantization == 8u;
+    const float limit = fp8 ? 448.0f : 6.0f;
+    const float floor_amax = fp8 ? 1.0e-4f : __uint_as_float(0x01c00000u);  // 6 * 2^-126
+    bool finite = true;
+#pragma unroll 4
+    for (unsigned int start = 0u; start < (HADAMARD ? 1u : count); start += 128u) {
+        const unsigned int base = start + lane * 4u;
+        const bool active = base < count;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (active) {
+            const float4 x = *reinterpret_cast<const float4 *>(values + base);
+            v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) finite = finite && isfinite(v[k]);
+        if (HADAMARD) {
+            float t0 = __fadd_rn(v[0], v[1]), t1 = __fsub_rn(v[0], v[1]);
+            float t2 = __fadd_rn(v[2], v[3]), t3 = __fsub_rn(v[2], v[3]);
+            v[0] = __fadd_rn(t0, t2), v[2] = __fsub_rn(t0, t2);
+            v[1] = __fadd_rn(t1, t3), v[3] = __fsub_rn(t1, t3);
+#pragma unroll
+            for (unsigned int m = 1u; m < 32u; m <<= 1) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[k], m);
+                    v[k] = (lane & m) ? __fsub_rn(other, v[k]) : __fadd_rn(v[k], other);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = __fmul_rn(v[k], a.hadamard_scale);
+        }
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+        amax = fmaxf(amax, floor_amax);
+        for (unsigned int m = 1u; m < group; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        const uint32_t ratio = __float_as_uint(__fdiv_rn(amax, limit));
+        uint32_t exponent = (ratio >> 23) + ((ratio & 0x007fffffu) ? 1u : 0u);
+        exponent = exponent > 254u ? 254u : exponent;
+        const float scale = __uint_as_float(exponent ? exponent << 23 : 0x00400000u);
+        // 1 / scale is a power of two as well (2^-127 for the largest scale), so the division is a product
+        const float inverse = __uint_as_float(exponent == 254u ? 0x00400000u : (254u - exponent) << 23);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float magnitude = fminf(fabsf(__fmul_rn(v[k], inverse)), limit);
+            const float nearest = fp8 ? activation_nearest_fp8(magnitude) : activation_nearest_fp4(magnitude);
+            v[k] = __uint_as_float((uint32_t)bf16_bits_rne(__fmul_rn(copysignf(nearest, v[k]), scale)) << 16);
+        }
+        if (active) *reinterpret_cast<float4 *>(values + base) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    if (!finite) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
+}
+
 }  // namespace yvx
 
 extern "C" int yvx_cuda_activation_quant(const yvx_activation_args *a, void *stream)
@@ -102,6 +170,19 @@ extern "C" int yvx_cuda_activation_quant(const yvx_activation_args *a, void *str
     if (a->count % a->block_width) return YVEX_ERR_BOUNDS;
     if (a->count > 8192ull || a->block_width > 1024u || a->rows > 0x7fffffffull) return YVEX_ERR_UNSUPPORTED;
     if (!a->rows) return 0;
+    // warp-per-row path: 16-byte rows, blocks of 4 << k lanes that tile a 128-lane segment; with the
+    // transform the (padded) row must be exactly one segment
+    const bool vector = !((unsigned long long)a->values & 15ull) && !(a->row_stride & 3ull) && !(a->count & 3ull) &&
+                        a->block_width >= 4u && a->block_width <= 128u && !(a->block_width & (a->block_width - 1u));
+    const unsigned int warp_grid = (unsigned int)((a->rows + 3ull) / 4ull);
+    if (vector && !a->hadamard) {
+        yvx::activation_quant_warp_kernel<false><<<warp_grid, yvx::kActivationThreads, 0, (cudaStream_t)stream>>>(*a);
+        return yvx_cuda_check(cudaGetLastError(), "activation_quant_warp_kernel");
+    }
+    if (vector && a->count > 64ull && a->count <= 128ull) {
+        yvx::activation_quant_warp_kernel<true><<<warp_grid, yvx::kActivationThreads, 0, (cudaStream_t)stream>>>(*a);
+        return yvx_cuda_check(cudaGetLastError(), "activation_quant_warp_kernel");
+    }
     unsigned int padded = 1u;
     while (padded < a->count) padded <<= 1;
     if (!a->hadamard) padded = (unsigned int)a->count;
