@@ -13,6 +13,8 @@
 // One CTA per row; a warp owns a quantisation block at a time.
 #include "common.cuh"
 
+#include <cuda_fp8.h>
+
 namespace yvx {
 
 constexpr int kActivationThreads = 128;
@@ -25,6 +27,14 @@ __device__ __forceinline__ float activation_nearest_fp8(float m)
     const uint32_t step = (__float_as_uint(m) & 0x7f800000u) - (3u << 23);
     // dividing by a power of two = multiplying by its (exact) reciprocal
     return __fmul_rn(rintf(__fmul_rn(m, __uint_as_float(0x7f000000u - step))), __uint_as_float(step));
+}
+
+// the same through the conversion instructions (round to nearest even, saturating at 448):
+// float -> e4m3 -> half -> float, every step after the first exact
+__device__ __forceinline__ float activation_nearest_fp8_cvt(float m)
+{
+    const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(m, __NV_SATFINITE, __NV_E4M3);
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
 }
 
 // nearest of {0, 0.5, 1, 1.5, 2, 3, 4, 6} to a magnitude in [0, 6]
@@ -152,8 +162,8 @@ activation_quant_warp_kernel(const yvx_activation_args a)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float magnitude = fminf(fabsf(__fmul_rn(v[k], inverse)), limit);
-            const float nearest = fp8 ? activation_nearest_fp8(magnitude) : activation_nearest_fp4(magnitude);
-            v[k] = __uint_as_float((uint32_t)bf16_bits_rne(__fmul_rn(copysignf(nearest, v[k]), scale)) << 16);
+            const float nearest = fp8 ? activation_nearest_fp8_cvt(magnitude) : activation_nearest_fp4(magnitude);
+            v[k] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(copysignf(nearest, v[k]), scale)));  // finite here
         }
         if (active) *reinterpret_cast<float4 *>(values + base) = make_float4(v[0], v[1], v[2], v[3]);
     }
