@@ -227,6 +227,24 @@ class AttentionActivationRequest(C.Structure):
                 ("quantization", C.c_uint), ("block_width", u64), ("hadamard", C.c_int)]
 
 
+class AttentionPublishRequest(C.Structure):
+    """yvex_b200_attention_publish_request (include/yvex_b200/attention.h)."""
+    _fields_ = [("values", C.c_void_p), ("rows", u64), ("rows_per_token", u64), ("row_stride", u64), ("width", u64),
+                ("token_position", u64), ("norm_mode", C.c_int), ("norm_weights", C.c_void_p),
+                ("rms_norm_epsilon", C.c_double), ("rope_dimension", u64), ("rope_frequency", C.c_void_p),
+                ("activation_quantization", C.c_uint), ("activation_count", u64), ("activation_block_width", u64),
+                ("activation_hadamard", C.c_int)]
+
+
+class RowsPublishArgs(C.Structure):
+    """yvx_rows_publish_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [("values", C.c_void_p), ("rows", u64), ("rows_per_token", u64), ("row_stride", u64), ("width", u64),
+                ("norm_mode", C.c_int), ("norm_weights", C.c_void_p), ("epsilon", C.c_double),
+                ("rope_dims", u64), ("rope_frequency", C.c_void_p), ("start_position", u64),
+                ("quantization", C.c_uint), ("activation_count", u64), ("block_width", u64),
+                ("hadamard", C.c_int), ("status", C.c_void_p)]
+
+
 class ActivationArgs(C.Structure):
     """yvx_activation_args (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [("values", C.c_void_p), ("rows", u64), ("row_stride", u64), ("count", u64),
@@ -334,6 +352,7 @@ EXPORTED_SYMBOLS = [
     "yvex_b200_attention_reduce_execute", "yvex_b200_kv_append_rotary_execute", "yvex_b200_mla_decode_execute",
     "yvex_b200_attention_select_execute", "yvex_b200_rope_frequencies",
     "yvex_b200_attention_compress_execute", "yvex_b200_attention_activation_execute",
+    "yvex_b200_attention_publish_execute",
     "yvex_b200_kv_pool_create", "yvex_b200_kv_pool_destroy", "yvex_b200_kv_pool_session_open",
     "yvex_b200_kv_pool_session_fork", "yvex_b200_kv_pool_session_close", "yvex_b200_kv_pool_reserve",
     "yvex_b200_kv_pool_commit", "yvex_b200_kv_pool_table", "yvex_b200_kv_pool_committed",
@@ -358,7 +377,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
     "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
     "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
-    "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk", "yvx_cuda_activation_quant",
+    "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk", "yvx_cuda_activation_quant", "yvx_cuda_rows_publish",
 ]
 
 _lib = None
@@ -416,6 +435,9 @@ def load():
     lib.yvex_b200_attention_activation_execute.argtypes = [
         vp, P(AttentionActivationRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
     lib.yvx_cuda_activation_quant.argtypes = [P(ActivationArgs), vp]
+    lib.yvex_b200_attention_publish_execute.argtypes = [
+        vp, P(AttentionPublishRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
+    lib.yvx_cuda_rows_publish.argtypes = [P(RowsPublishArgs), vp]
     lib.yvex_b200_kv_append_rotary_execute.argtypes = [vp, P(KvAppendRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_mla_decode_execute.argtypes = [vp, P(MlaDecodeRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_kv_pool_create.restype = vp

@@ -11,39 +11,11 @@
 // the same two operands as on the CPU, the scale is a power of two, and the product with
 // it is exact, so results are bit-equal whatever the order the threads run in.
 // One CTA per row; a warp owns a quantisation block at a time.
-#include "common.cuh"
-
-#include <cuda_fp8.h>
+#include "activation.cuh"
 
 namespace yvx {
 
 constexpr int kActivationThreads = 128;
-
-// nearest FP8 E4M3 value to a magnitude in [0, 448]: 2^-9 steps below 2^-5, eight steps
-// per binade above; rintf rounds halves to the even multiple = the even code
-__device__ __forceinline__ float activation_nearest_fp8(float m)
-{
-    if (m < 0.03125f) return __fmul_rn(rintf(__fmul_rn(m, 512.0f)), 0.001953125f);
-    const uint32_t step = (__float_as_uint(m) & 0x7f800000u) - (3u << 23);
-    // dividing by a power of two = multiplying by its (exact) reciprocal
-    return __fmul_rn(rintf(__fmul_rn(m, __uint_as_float(0x7f000000u - step))), __uint_as_float(step));
-}
-
-// the same through the conversion instructions (round to nearest even, saturating at 448):
-// float -> e4m3 -> half -> float, every step after the first exact
-__device__ __forceinline__ float activation_nearest_fp8_cvt(float m)
-{
-    const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(m, __NV_SATFINITE, __NV_E4M3);
-    return __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
-}
-
-// nearest of {0, 0.5, 1, 1.5, 2, 3, 4, 6} to a magnitude in [0, 6]
-__device__ __forceinline__ float activation_nearest_fp4(float m)
-{
-    if (m < 2.0f) return __fmul_rn(rintf(__fmul_rn(m, 2.0f)), 0.5f);
-    if (m < 4.0f) return rintf(m);
-    return __fmul_rn(rintf(__fmul_rn(m, 0.5f)), 2.0f);
-}
 
 __global__ void __launch_bounds__(kActivationThreads)
 activation_quant_kernel(const yvx_activation_args a, unsigned int padded)
@@ -120,8 +92,6 @@ activation_quant_warp_kernel(const yvx_activation_args a)
     const unsigned int count = (unsigned int)a.count;
     const unsigned int group = a.block_width / 4u;
     const bool fp8 = a.quantization == 8u;
-    const float limit = fp8 ? 448.0f : 6.0f;
-    const float floor_amax = fp8 ? 1.0e-4f : __uint_as_float(0x01c00000u);  // 6 * 2^-126
     bool finite = true;
 #pragma unroll 4
     for (unsigned int start = 0u; start < (HADAMARD ? 1u : count); start += 128u) {
@@ -134,37 +104,7 @@ activation_quant_warp_kernel(const yvx_activation_args a)
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) finite = finite && isfinite(v[k]);
-        if (HADAMARD) {
-            float t0 = __fadd_rn(v[0], v[1]), t1 = __fsub_rn(v[0], v[1]);
-            float t2 = __fadd_rn(v[2], v[3]), t3 = __fsub_rn(v[2], v[3]);
-            v[0] = __fadd_rn(t0, t2), v[2] = __fsub_rn(t0, t2);
-            v[1] = __fadd_rn(t1, t3), v[3] = __fsub_rn(t1, t3);
-#pragma unroll
-            for (unsigned int m = 1u; m < 32u; m <<= 1) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[k], m);
-                    v[k] = (lane & m) ? __fsub_rn(other, v[k]) : __fadd_rn(v[k], other);
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) v[k] = __fmul_rn(v[k], a.hadamard_scale);
-        }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        amax = fmaxf(amax, floor_amax);
-        for (unsigned int m = 1u; m < group; m <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-        const uint32_t ratio = __float_as_uint(__fdiv_rn(amax, limit));
-        uint32_t exponent = (ratio >> 23) + ((ratio & 0x007fffffu) ? 1u : 0u);
-        exponent = exponent > 254u ? 254u : exponent;
-        const float scale = __uint_as_float(exponent ? exponent << 23 : 0x00400000u);
-        // 1 / scale is a power of two as well (2^-127 for the largest scale), so the division is a product
-        const float inverse = __uint_as_float(exponent == 254u ? 0x00400000u : (254u - exponent) << 23);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float magnitude = fminf(fabsf(__fmul_rn(v[k], inverse)), limit);
-            const float nearest = fp8 ? activation_nearest_fp8_cvt(magnitude) : activation_nearest_fp4(magnitude);
-            v[k] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(copysignf(nearest, v[k]), scale)));  // finite here
-        }
+        activation_segment<HADAMARD>(v, lane, group, fp8, a.hadamard_scale);
         if (active) *reinterpret_cast<float4 *>(values + base) = make_float4(v[0], v[1], v[2], v[3]);
     }
     if (!finite) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);

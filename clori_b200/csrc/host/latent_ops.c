@@ -558,6 +558,87 @@ int yvex_b200_attention_activation_execute(yvex_backend *backend,
     return YVEX_OK;
 }
 
+static int publish_refuse(yvex_b200_attention_failure *failure, yvex_b200_attention_failure_code code,
+                          unsigned long long expected, unsigned long long actual, yvex_error *err,
+                          yvex_status status, const char *message)
+{
+    if (failure) {
+        failure->code = code;
+        failure->stage = "publish";
+        failure->expected = expected;
+        failure->actual = actual;
+    }
+    return yvx_fail(err, status, "b200.attention.publish", message);
+}
+
+int yvex_b200_attention_publish_execute(yvex_backend *backend, const yvex_b200_attention_publish_request *r,
+                                        yvex_b200_attention_failure *failure,
+                                        yvex_backend_operation_facts *facts, yvex_error *err)
+{
+    const char *where = "b200.attention.publish";
+    unsigned long long elements = 0ull;
+    yvx_rows_publish_args a;
+    int rc;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    if (!r || !facts || !r->values || !r->width || !r->rows_per_token)
+        return publish_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, 1ull, 0ull, err,
+                              YVEX_ERR_INVALID_ARG, "publication requires rows, a width and rows per token");
+    memset(facts, 0, sizeof(*facts));
+    rc = yvx_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (r->row_stride < r->width || !yvx_u64_mul(r->rows ? r->rows : 1ull, r->row_stride, &elements) ||
+        !view_ok(backend, r->values, YVEX_DTYPE_F32, elements - (r->row_stride - r->width)) ||
+        (r->norm_mode == 2 && (!r->norm_weights || !view_ok(backend, r->norm_weights, YVEX_DTYPE_F32, r->width))) ||
+        (r->rope_dimension &&
+         (!r->rope_frequency || !view_ok(backend, r->rope_frequency, YVEX_DTYPE_F64, r->rope_dimension / 2ull))))
+        return publish_refuse(failure, YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT, elements, r->values->bytes, err,
+                              YVEX_ERR_FORMAT, "tensor views do not cover the stated geometry");
+    memset(&a, 0, sizeof(a));
+    a.values = (float *)r->values->data;
+    a.rows = r->rows;
+    a.rows_per_token = r->rows_per_token;
+    a.row_stride = r->row_stride;
+    a.width = r->width;
+    a.norm_mode = r->norm_mode;
+    a.norm_weights = r->norm_mode == 2 ? (const float *)r->norm_weights->data : NULL;
+    a.epsilon = r->rms_norm_epsilon;
+    a.rope_dims = r->rope_dimension;
+    a.rope_frequency = r->rope_dimension ? (const double *)r->rope_frequency->data : NULL;
+    a.start_position = r->token_position;
+    a.quantization = r->activation_quantization;
+    a.activation_count = r->activation_count;
+    a.block_width = r->activation_block_width;
+    a.hadamard = r->activation_hadamard;
+    a.status = backend->status_device;
+    rc = yvx_backend_status_arm(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_rows_publish(&a, backend->stream);
+    if (rc != 0) {
+        /* the shim's refusals are argument refusals, not device failures */
+        if (rc == YVEX_ERR_INVALID_ARG || rc == YVEX_ERR_UNSUPPORTED || rc == YVEX_ERR_BOUNDS || rc == YVEX_ERR_FORMAT)
+            return publish_refuse(failure, rc == YVEX_ERR_UNSUPPORTED ? YVEX_B200_ATTENTION_FAILURE_CAPABILITY
+                                                                      : YVEX_B200_ATTENTION_FAILURE_INVALID_ARGUMENT,
+                                  0ull, 0ull, err, (yvex_status)rc, "publication chain refused its arguments");
+        if (failure) {
+            failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
+            failure->stage = "publish";
+        }
+        return yvx_backend_device_fail(backend, rc, where, err);
+    }
+    rc = finish(backend, facts, r->rows ? 1u : 0u, 0ull, where, err);
+    if (rc != YVEX_OK) {
+        if (failure) {
+            failure->code = rc == YVEX_ERR_FORMAT ? YVEX_B200_ATTENTION_FAILURE_NUMERIC
+                                                  : YVEX_B200_ATTENTION_FAILURE_SYNCHRONIZE;
+            failure->stage = "publish";
+        }
+        return rc;
+    }
+    r->values->is_written = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
 int yvex_b200_kv_append_rotary_execute(yvex_backend *backend, const yvex_b200_kv_append_request *r,
                                        yvex_backend_operation_facts *facts, yvex_error *err)
 {

@@ -280,6 +280,29 @@ int yvex_b200_attention_activation_execute(yvex_backend *backend,
                                            yvex_b200_attention_failure *failure,
                                            yvex_backend_operation_facts *facts, yvex_error *err);
 
+/* The publication chain of projected rows (query heads, new local rows, index queries):
+ * optional RMS norm -> bf16 -> optional rotation -> bf16 -> optional activation fake
+ * quantisation, in one launch (CPU reference: src/graph/attention_execute.c:527-612 and
+ * :970-1003; on the reference's device path a launch per step, src/backend/cuda/
+ * attention.c:1162-1236). norm_mode: 0 none, 1 unit RMS norm, 2 learned weights. */
+typedef struct yvex_b200_attention_publish_request {
+    yvex_device_tensor *values;                       /* F32 [rows][row_stride] */
+    unsigned long long rows, rows_per_token, row_stride, width;
+    unsigned long long token_position;                /* position of the first token */
+    int norm_mode;
+    const yvex_device_tensor *norm_weights;           /* F32 [width] */
+    double rms_norm_epsilon;
+    unsigned long long rope_dimension;
+    const yvex_device_tensor *rope_frequency;         /* F64 [rope_dimension/2] */
+    unsigned int activation_quantization;             /* 0 none, 8, 4 */
+    unsigned long long activation_count, activation_block_width;
+    int activation_hadamard;
+} yvex_b200_attention_publish_request;
+int yvex_b200_attention_publish_execute(yvex_backend *backend,
+                                        const yvex_b200_attention_publish_request *request,
+                                        yvex_b200_attention_failure *failure,
+                                        yvex_backend_operation_facts *facts, yvex_error *err);
+
 int yvex_b200_attention_reduce_execute(yvex_backend *backend,
                                        const yvex_b200_attention_reduce_request *request,
                                        yvex_b200_attention_failure *failure,

@@ -369,6 +369,37 @@ typedef struct yvx_activation_args {
 } yvx_activation_args;
 int yvx_cuda_activation_quant(const yvx_activation_args *args, void *stream);
 
+/* ---- publication chain of projected rows of the latent attention (one launch) ---------
+ * Replaces, for the rows a projection has produced, the per-row sequence of the reference
+ * (CPU: src/graph/attention_execute.c:527-612 and :970-1003; CUDA: the weighted_norm /
+ * unit norm, rope and activation launches of src/backend/cuda/attention.c:1162-1236):
+ *   norm_mode 1: RMS norm without weights, 2: with learned weights; then bf16 publication
+ *   rope_dims > 0: rotation of the last rope_dims lanes (adjacent pairs) at the row's token
+ *     position, then bf16 publication of the row
+ *   quantization 8 / 4: the activation fake quantisation of yvx_cuda_activation_quant over the
+ *     first activation_count lanes
+ * Query heads take (1, rope, none); new local rows (2, rope, FP8 on the lanes in front of the
+ * rotated ones); index queries (0, rope, transform + FP4 on the whole head). Row r belongs to
+ * the token at start_position + r / rows_per_token. Sums of squares and the scaling run in
+ * double precision, the rotation as in yvx_cuda_latent_reduce. Contract: width a multiple of 4
+ * and at most 1024, rows 16-byte aligned, rope_dims even, activation blocks of 4 << k <= 128
+ * lanes; with the transform activation_count in (64, 128]. status: 1 non-finite. */
+typedef struct yvx_rows_publish_args {
+    float *values;                            /* [rows][row_stride] */
+    unsigned long long rows, rows_per_token, row_stride, width;
+    int norm_mode;
+    const float *norm_weights;                /* [width] */
+    double epsilon;
+    unsigned long long rope_dims;
+    const double *rope_frequency;             /* [rope_dims/2] */
+    unsigned long long start_position;
+    unsigned int quantization;
+    unsigned long long activation_count, block_width;
+    int hadamard;
+    int *status;
+} yvx_rows_publish_args;
+int yvx_cuda_rows_publish(const yvx_rows_publish_args *args, void *stream);
+
 /* ---- KV append with rotary embedding (one launch per step) ---------------------------
  * Replaces, for the new rows of a step, the two rotate-half launches on Q and K
  * (yvex_cuda_transformer_rotary_half / _rotary_half_f32, src/backend/cuda/transformer.c:

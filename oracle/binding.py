@@ -102,6 +102,35 @@ def _compressor_call(call, ratio, head_dim, overlap, start, token_kv, token_scor
     return compressed[:n].copy(), positions[:n].copy(), after_kv, after_score
 
 
+class PublishArgs(C.Structure):
+    """yvx_oracle_publish_args (host pointers here, device pointers in the library)."""
+    _fields_ = [("values", C.c_void_p), ("rows", _u64), ("rows_per_token", _u64), ("row_stride", _u64),
+                ("width", _u64), ("norm_mode", C.c_int), ("norm_weights", C.c_void_p), ("epsilon", C.c_double),
+                ("rope_dims", _u64), ("rope_frequency", C.c_void_p), ("start_position", _u64),
+                ("quantization", C.c_uint), ("activation_count", _u64), ("block_width", _u64),
+                ("hadamard", C.c_int), ("device_status", C.c_void_p)]
+
+
+def _publish_call(call, rows, rows_per_token, start, norm_mode=0, norm_weights=None, epsilon=1e-6, rope_dims=0,
+                  rope_frequency=None, quantization=0, activation_count=0, block_width=0, hadamard=0):
+    out = np.ascontiguousarray(rows, np.float32).copy()
+    a = PublishArgs()
+    a.values, a.rows, a.rows_per_token, a.row_stride, a.width = out.ctypes.data, out.shape[0], rows_per_token, \
+        out.shape[1], out.shape[1]
+    keep = []
+    a.norm_mode, a.epsilon = norm_mode, float(epsilon)
+    if norm_weights is not None:
+        keep.append(np.ascontiguousarray(norm_weights, np.float32))
+        a.norm_weights = keep[-1].ctypes.data
+    a.rope_dims, a.start_position = rope_dims, start
+    if rope_frequency is not None:
+        keep.append(np.ascontiguousarray(rope_frequency, np.float64))
+        a.rope_frequency = keep[-1].ctypes.data
+    a.quantization, a.activation_count, a.block_width, a.hadamard = quantization, activation_count, block_width, \
+        int(hadamard)
+    return out if call(a) == 1 else None
+
+
 def _activation_call(function, rows, quantization, block_width, hadamard):
     function.argtypes = [_f32p, _u64, C.c_uint, _u64, C.c_int]
     out = np.ascontiguousarray(rows, np.float32).copy()
@@ -378,6 +407,14 @@ class Oracle(_Gqa):
             ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv, state_score,
             norm_weights, epsilon, rope_dims, rope_frequency)
 
+    def rows_publish(self, rows, rows_per_token, start, **chain):
+        """Norm / rotation / activation chain over float32 [rows, width] -> new array, or None.
+        chain: norm_mode, norm_weights, epsilon, rope_dims, rope_frequency, quantization,
+        activation_count, block_width, hadamard."""
+        self.lib.yvx_oracle_rows_publish.argtypes = [C.c_void_p]
+        return _publish_call(lambda a: self.lib.yvx_oracle_rows_publish(C.addressof(a)), rows, rows_per_token,
+                             start, **chain)
+
     def activation_quant(self, rows, quantization, block_width, hadamard):
         """Fake quantisation of every row of a float32 [rows, count] array -> new array, or None."""
         return _activation_call(self.lib.yvx_oracle_activation_quant, rows, quantization, block_width, hadamard)
@@ -456,6 +493,13 @@ class Reference(_Gqa):
             ratio, head_dim, overlap, start, token_kv, token_score, ape, state_kv, state_score,
             norm_weights, epsilon, rope_dims, None)
 
+
+    def rows_publish(self, rows, rows_per_token, start, policy=None, **chain):
+        """The reference's own functions in its order; the rotation takes the policy, not frequencies."""
+        chain.pop("rope_frequency", None)
+        self.lib.yvx_ref_rows_publish.argtypes = [C.c_void_p, C.c_void_p]
+        return _publish_call(lambda a: self.lib.yvx_ref_rows_publish(
+            C.addressof(a), C.addressof(policy) if policy is not None else None), rows, rows_per_token, start, **chain)
 
     def activation_quant(self, rows, quantization, block_width, hadamard):
         return _activation_call(self.lib.yvx_ref_activation_quant, rows, quantization, block_width, hadamard)

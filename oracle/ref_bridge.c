@@ -506,3 +506,31 @@ int yvx_ref_activation_quant(float *values, unsigned long long count, unsigned i
     return yvex_attention_activation_apply(&policy, values, count, 0ull, YVEX_TENSOR_ROLE_UNKNOWN,
                                            &scratch, &failure, &err) == YVEX_OK;
 }
+
+/* The reference's publication chain of projected rows, step by step with its own
+ * functions, in the order its chunk executor applies them. */
+int yvx_ref_rows_publish(const yvx_oracle_publish_args *a, const yvx_oracle_position_policy *policy)
+{
+    yvex_attention_position_policy position;
+    unsigned long long r;
+    if (policy) ref_position(policy, a->rope_dims, &position);
+    for (r = 0; r < a->rows; ++r) {
+        float *row = a->values + r * a->row_stride;
+        if (a->norm_mode) {
+            int ok = a->norm_mode == 2 ? yvex_attention_rms_norm(row, a->width, a->norm_weights, a->epsilon)
+                                       : yvex_attention_unit_rms_norm(row, a->width, a->epsilon);
+            if (!ok || !yvex_attention_compute_round(YVEX_ATTENTION_COMPUTE_BF16_F32_RNE_V1, row, a->width))
+                return 0;
+        }
+        if (a->rope_dims &&
+            (!policy ||
+             !yvex_attention_rope_apply(row, a->width, a->rope_dims, a->start_position + r / a->rows_per_token,
+                                        &position, 0) ||
+             !yvex_attention_compute_round(YVEX_ATTENTION_COMPUTE_BF16_F32_RNE_V1, row, a->width)))
+            return 0;
+        if (a->quantization && a->activation_count &&
+            !yvx_ref_activation_quant(row, a->activation_count, a->quantization, a->block_width, a->hadamard))
+            return 0;
+    }
+    return 1;
+}

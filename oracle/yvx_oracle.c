@@ -1312,3 +1312,50 @@ int yvx_oracle_activation_quant(float *values, unsigned long long count, unsigne
         if (!activation_block(values + offset, block_width, quantization)) return 0;
     return 1;
 }
+
+/* ---- publication chain of projected rows -------------------------------------- */
+
+/* src/graph/attention_execute.c:527-612 (query heads: unit norm, round, rotation, round; new
+ * local rows: weighted norm, round, rotation, round, activation of the lanes in front of the
+ * rotated ones) and :970-1003 (index queries: rotation, round, activation of the whole head). */
+int yvx_oracle_rows_publish(const yvx_oracle_publish_args *a)
+{
+    unsigned long long r, i;
+    if (!a || !a->values || !a->width || a->row_stride < a->width || !a->rows_per_token) return 0;
+    for (r = 0; r < a->rows; ++r) {
+        float *row = a->values + r * a->row_stride;
+        if (a->norm_mode) {
+            double mean = 0.0, inverse;
+            if (!isfinite(a->epsilon) || a->epsilon <= 0.0) return 0;
+            if (a->norm_mode == 2) {
+                if (!a->norm_weights || !compressor_rms_norm(row, a->width, a->norm_weights, a->epsilon)) return 0;
+            } else {
+                /* attention_rms_norm_apply without weights (src/graph/numeric.c:630-654) */
+                for (i = 0; i < a->width; ++i) {
+                    double v = row[i];
+                    if (!isfinite(v)) return 0;
+                    mean += v * v;
+                }
+                mean /= (double)a->width;
+                inverse = 1.0 / sqrt(mean + a->epsilon);
+                if (!isfinite(inverse)) return 0;
+                for (i = 0; i < a->width; ++i) {
+                    double v = (double)row[i] * inverse;
+                    if (!isfinite(v)) return 0;
+                    row[i] = (float)v;
+                }
+            }
+            if (!compressor_round(row, a->width)) return 0;
+        }
+        if (a->rope_dims) {
+            if (!yvx_oracle_rope_apply(row, a->width, a->rope_dims, a->start_position + r / a->rows_per_token,
+                                       a->rope_frequency, 0) ||
+                !compressor_round(row, a->width))
+                return 0;
+        }
+        if (a->quantization && a->activation_count &&
+            !yvx_oracle_activation_quant(row, a->activation_count, a->quantization, a->block_width, a->hadamard))
+            return 0;
+    }
+    return 1;
+}

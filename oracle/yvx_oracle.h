@@ -188,6 +188,28 @@ int yvx_oracle_compressor_chunk(const yvx_oracle_compressor_args *args,
 int yvx_oracle_activation_quant(float *values, unsigned long long count, unsigned int quantization,
                                 unsigned long long block_width, int hadamard);
 
+/* The chain the reference runs on every projected row of the latent attention before it is
+ * attended or stored (query heads, new local rows, index queries): an optional RMS norm
+ * (norm_mode 1: unit, 2: learned weights) with bf16 publication, an optional position
+ * rotation of the last rope_dims lanes with bf16 publication, an optional activation fake
+ * quantisation of the first activation_count lanes. Row r belongs to the token at
+ * start_position + r / rows_per_token. Returns 1, or 0 on a refusal. */
+typedef struct {
+    float *values;                            /* [rows][row_stride], width lanes used */
+    unsigned long long rows, rows_per_token, row_stride, width;
+    int norm_mode;
+    const float *norm_weights;                /* [width] for norm_mode 2 */
+    double epsilon;
+    unsigned long long rope_dims;             /* 0: no rotation */
+    const double *rope_frequency;             /* [rope_dims/2] */
+    unsigned long long start_position;
+    unsigned int quantization;                /* 0 none, 8, 4 */
+    unsigned long long activation_count, block_width;
+    int hadamard;
+    int *device_status;                       /* unused here */
+} yvx_oracle_publish_args;
+int yvx_oracle_rows_publish(const yvx_oracle_publish_args *args);
+
 /* Latent decode with a separate rope key and an absorbed up-projection. */
 int yvx_oracle_mla_decode(const unsigned short *q_nope_bf16,
                           const unsigned short *q_rope_bf16,

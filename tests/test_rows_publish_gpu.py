@@ -1,0 +1,148 @@
+"""Publication chain of projected rows on a B200 against the CPU checker (pinned to the
+reference's compiled code by the CPU suite) and the reference-made fixtures.
+
+Without a norm the chain is rotation -> bf16 -> activation: exact given its inputs, so rows must
+be bit-equal. With a norm the sum of squares is reduced in a tree instead of serially and the
+device square root / sine / cosine may differ from libm in the last place, so a published bf16
+lane may land on the other side of a rounding tie: at most 1 lane in 200, by one bf16 ulp
+(relative 2^-7). The activation is exact given the published row, so it is checked bit for bit
+against the checker's activation of the device's own published rows."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from clori_b200 import abi
+from oracle.binding import PositionPolicy
+from publish_cases import CASES, POLICY, build
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rows_publish.npz")
+
+
+def same_bits(a, b):
+    return a.shape == b.shape and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def run_gpu(backend, x, rpt, start, norm_mode=0, norm_weights=None, epsilon=1e-6, rope_dims=0, rope_frequency=None,
+            quantization=0, activation_count=0, block_width=0, hadamard=0, expect_rc=0):
+    lib, s = backend.lib, backend.stream
+    t = backend.tensor("x", x)
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    a = abi.RowsPublishArgs()
+    a.values, a.rows, a.rows_per_token, a.row_stride, a.width = t.data_ptr, x.shape[0], rpt, x.shape[1], x.shape[1]
+    a.norm_mode, a.epsilon = norm_mode, epsilon
+    keep = []
+    if norm_mode == 2:
+        keep.append(backend.tensor("w", norm_weights))
+        a.norm_weights = keep[-1].data_ptr
+    if rope_dims:
+        keep.append(backend.tensor("f", np.ascontiguousarray(rope_frequency, np.float64), dtype=abi.DTYPE_F64))
+        a.rope_dims, a.rope_frequency = rope_dims, keep[-1].data_ptr
+    a.start_position = start
+    a.quantization, a.activation_count, a.block_width, a.hadamard = quantization, activation_count, block_width, hadamard
+    a.status = status.data_ptr
+    rc = lib.yvx_cuda_rows_publish(C.byref(a), s)
+    assert rc == expect_rc, lib.yvx_cuda_last_error_text()
+    if rc:
+        return None
+    assert lib.yvx_cuda_stream_synchronize(s) == 0, lib.yvx_cuda_last_error_text()
+    return t.read(), int(status.read()[0])
+
+
+def check(backend, oracle, x, w, rpt, start, chain, freq, reference_rows=None):
+    plain = {k: v for k, v in chain.items() if k not in ("quantization", "activation_count", "block_width", "hadamard")}
+    expected = oracle.rows_publish(x, rpt, start, norm_weights=w, rope_frequency=freq, **plain)
+    got, status = run_gpu(backend, x, rpt, start, norm_weights=w, rope_frequency=freq, **plain)
+    assert status == 0
+    if chain.get("norm_mode"):
+        differ = got != expected
+        assert differ.sum() <= max(1, got.size // 200)
+        assert np.all(np.abs(got - expected)[differ] <= 2.0 ** -7 * np.abs(expected)[differ])
+    else:
+        assert same_bits(got, expected)
+    if chain.get("quantization"):
+        full, status = run_gpu(backend, x, rpt, start, norm_weights=w, rope_frequency=freq, **chain)
+        assert status == 0
+        count = chain["activation_count"]
+        device_expected = got.copy()
+        device_expected[:, :count] = oracle.activation_quant(np.ascontiguousarray(got[:, :count]), chain["quantization"],
+                                                             chain["block_width"], chain.get("hadamard", 0))
+        assert same_bits(full, device_expected)
+        if reference_rows is not None and same_bits(got, expected):
+            assert same_bits(full, reference_rows)
+    elif reference_rows is not None and same_bits(got, expected):
+        assert same_bits(got, reference_rows)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_rows_against_the_checker(backend, oracle, case):
+    name, width, rpt, tokens, start, chain = case
+    x, w = build(400 + width, width, rpt * tokens)
+    freq = oracle.rope_frequencies(PositionPolicy(*POLICY), chain["rope_dims"]) if chain.get("rope_dims") else None
+    check(backend, oracle, x, w, rpt, start, chain, freq)
+
+
+def test_reference_fixtures(backend, oracle):
+    g = np.load(GOLDEN)
+    for i, (name, width, rpt, tokens, start, chain) in enumerate(CASES):
+        freq = g[f"frequency{i}"] if chain.get("rope_dims") else None
+        check(backend, oracle, g[f"in{i}"], g[f"weights{i}"], rpt, start, chain, freq, reference_rows=g[f"out{i}"])
+
+
+def test_prefill_sized_batch(backend, oracle):
+    # 4096 tokens x 64 query heads of 512 lanes (537 MB): a sample of rows against the checker
+    name, width, rpt, tokens, start, chain = CASES[0]
+    x, w = build(77, width, rpt * 4096)
+    freq = oracle.rope_frequencies(PositionPolicy(*POLICY), 64)
+    got, status = run_gpu(backend, x, rpt, start, rope_frequency=freq, **chain)
+    assert status == 0
+    for token in (0, 1777, 4095):
+        rows = slice(token * rpt, token * rpt + rpt)
+        expected = oracle.rows_publish(x[rows], rpt, start + token, rope_frequency=freq, **chain)
+        differ = got[rows] != expected
+        assert differ.sum() <= max(1, expected.size // 200)
+        assert np.all(np.abs(got[rows] - expected)[differ] <= 2.0 ** -7 * np.abs(expected)[differ])
+    # publishing a published, unit-norm row again moves nothing but rounding ties: idempotent norm, new rotation
+    again, _ = run_gpu(backend, got, rpt, start, norm_mode=1)
+    assert np.abs(again - got).max() <= 2.0 ** -6 * np.abs(got).max()
+
+
+def test_refusals_and_status(backend):
+    x = np.ones((4, 128), np.float32)
+    f = np.ones(32, np.float64)
+    assert run_gpu(backend, x[:, :126].copy(), 1, 0, norm_mode=1, expect_rc=abi.YVEX_ERR_UNSUPPORTED) is None
+    assert run_gpu(backend, x, 1, 0, norm_mode=1, epsilon=0.0, expect_rc=abi.YVEX_ERR_INVALID_ARG) is None
+    assert run_gpu(backend, x, 1, 0, rope_dims=63, rope_frequency=f, expect_rc=abi.YVEX_ERR_INVALID_ARG) is None
+    assert run_gpu(backend, x, 1, 0, quantization=8, activation_count=96, block_width=64,
+                   expect_rc=abi.YVEX_ERR_BOUNDS) is None
+    assert run_gpu(backend, x, 1, 0, quantization=3, activation_count=64, block_width=64,
+                   expect_rc=abi.YVEX_ERR_FORMAT) is None
+    x[2, 9] = np.inf
+    assert run_gpu(backend, x, 1, 0, norm_mode=1)[1] == 1
+
+
+def ptr(tensor):
+    return C.cast(tensor.ptr, C.c_void_p) if tensor is not None else None
+
+
+def test_operator_entry(backend, oracle):
+    name, width, rpt, tokens, start, chain = CASES[2]          # index queries: exact chain
+    x, w = build(5, width, rpt * tokens)
+    freq = oracle.rope_frequencies(PositionPolicy(*POLICY), chain["rope_dims"])
+    t, f = backend.tensor("x", x), backend.tensor("f", freq, dtype=abi.DTYPE_F64)
+    r = abi.AttentionPublishRequest()
+    r.values, r.rows, r.rows_per_token, r.row_stride, r.width = ptr(t), x.shape[0], rpt, width, width
+    r.token_position, r.norm_mode, r.rope_dimension, r.rope_frequency = start, 0, chain["rope_dims"], ptr(f)
+    r.activation_quantization, r.activation_count, r.activation_block_width, r.activation_hadamard = 4, 128, 32, 1
+    failure, facts, err = abi.AttentionFailure(), abi.OperationFacts(), abi.Error()
+    call = lambda: backend.lib.yvex_b200_attention_publish_execute(backend.handle, C.byref(r), C.byref(failure),
+                                                                   C.byref(facts), C.byref(err))
+    assert call() == 0, err.message
+    assert facts.kernel_launches == 1
+    assert same_bits(t.read(), oracle.rows_publish(x, rpt, start, rope_frequency=freq, **chain))
+    r.activation_block_width = 48
+    assert call() == abi.YVEX_ERR_BOUNDS and failure.stage == b"publish"
+    r.activation_block_width, r.rows = 32, x.shape[0] + 1
+    assert call() == abi.YVEX_ERR_FORMAT
