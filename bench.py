@@ -801,6 +801,72 @@ def bench_activation(lib, backend, abi, hbm_peak, repeats, rows=131072):
     return result, None
 
 
+def bench_publish(lib, backend, abi, hbm_peak, repeats, tokens=4096):
+    """Publication chain of projected rows in place: the query heads of `tokens` tokens (64 heads of 512
+    lanes: unit RMS norm, bf16, rotation of the last 64 lanes, bf16) and the new local rows of 16 x as many
+    tokens (512 lanes: weighted norm, bf16, rotation, bf16, FP8 activation of the 448 leading lanes)."""
+    from oracle.binding import Oracle, PositionPolicy
+    oracle = Oracle()
+    frequency = oracle.rope_frequencies(PositionPolicy(10000, 16, 65536, 32, 1), 64)
+    out = {}
+    for name, rpt, n_tokens, chain in (("query_heads", 64, tokens, dict(norm_mode=1, rope_dims=64)),
+                                       ("local_rows", 1, tokens * 16, dict(norm_mode=2, rope_dims=64, quantization=8,
+                                                                           activation_count=448, block_width=64))):
+        rows, width = rpt * n_tokens, 512
+        nbytes = rows * width * 4
+        dev = {k: _alloc(lib, n) for k, n in (("values", nbytes), ("source", nbytes), ("weights", width * 4),
+                                              ("freq", frequency.nbytes), ("status", 4))}
+        lib.yvx_cuda_fill_normal(dev["source"], abi.DTYPE_F32, rows * width, 821, 1.0, backend.stream)
+        lib.yvx_cuda_fill_normal(dev["weights"], abi.DTYPE_F32, width, 822, 1.0, backend.stream)
+        lib.yvx_cuda_upload_async(dev["freq"], frequency.ctypes.data, frequency.nbytes, backend.stream)
+        lib.yvx_cuda_memset_async(dev["status"], 0, 4, backend.stream)
+        a = abi.RowsPublishArgs()
+        a.values, a.rows, a.rows_per_token, a.row_stride, a.width = dev["values"], rows, rpt, width, width
+        a.norm_mode, a.norm_weights, a.epsilon = chain["norm_mode"], dev["weights"], 1e-6
+        a.rope_dims, a.rope_frequency, a.start_position = 64, dev["freq"], 5000
+        a.quantization, a.activation_count = chain.get("quantization", 0), chain.get("activation_count", 0)
+        a.block_width, a.status = chain.get("block_width", 0), dev["status"]
+        sample, weights = np.zeros((rpt * 2, width), np.float32), np.zeros(width, np.float32)
+        lib.yvx_cuda_download_async(sample.ctypes.data, dev["source"], sample.nbytes, backend.stream)
+        lib.yvx_cuda_download_async(weights.ctypes.data, dev["weights"], weights.nbytes, backend.stream)
+
+        def event():
+            e = C.c_void_p()
+            assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+            return e
+        first, last = event(), event()
+        total = 0.0
+        for i in range(repeats + 2):
+            lib.yvx_cuda_copy_async(dev["values"], dev["source"], nbytes, backend.stream)
+            lib.yvx_cuda_event_record(first, backend.stream)
+            assert lib.yvx_cuda_rows_publish(C.byref(a), backend.stream) == 0
+            lib.yvx_cuda_event_record(last, backend.stream)
+            assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+            ms = C.c_float()
+            lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+            total += ms.value if i >= 2 else 0.0
+        step = total / repeats
+        got, st = np.zeros_like(sample), np.zeros(1, np.int32)
+        lib.yvx_cuda_download_async(got.ctypes.data, dev["values"], got.nbytes, backend.stream)
+        lib.yvx_cuda_download_async(st.ctypes.data, dev["status"], 4, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
+        plain = {k: v for k, v in chain.items() if k in ("norm_mode", "rope_dims")}
+        expected = oracle.rows_publish(sample, rpt, 5000, norm_weights=weights, rope_frequency=frequency, **plain)
+        out[name] = {"rows": rows, "kernel_ms": step, "algorithmic_bytes": 2 * nbytes,
+                     "achieved_gbs": 2 * nbytes / (step * 1e-3) / 1e9,
+                     "frac_of_measured_hbm": 2 * nbytes / (step * 1e-3) / 1e9 / hbm_peak, "status_word": int(st[0])}
+        if "quantization" not in chain:
+            out[name]["lanes_differing_from_cpu_on_sample"] = int((got != expected).sum())
+            out[name]["sample_lanes"] = int(got.size)
+        for ptr in dev.values():
+            lib.yvx_cuda_free(ptr)
+    return {"workload": f"publication chain of projected rows in place: query heads of {tokens} tokens (64 x 512 lanes) "
+                        f"and local rows of {tokens * 16} tokens (512 lanes, FP8 activation on 448)",
+            "kernel": "rows_publish_kernel", "launches_per_step": 1,
+            "l2": "each launch works on a fresh copy of its rows (537 MB)",
+            "replaces": "a norm launch, a rotation launch and an activation launch per step of the chain", **out}, None
+
+
 def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
     """One decode step of a sparse shared-latent layer at the reference configuration's
     widths (64 heads x 512 with the last 64 lanes rotated, window 128, ratio 4, 64 index
@@ -1209,7 +1275,7 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
-                                 "compressor", "activation"],
+                                 "compressor", "activation", "publish"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1259,6 +1325,9 @@ def main():
                                   sessions=min(args.sessions, 32))
         elif args.workload == "latent_sparse":
             result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
+        elif args.workload == "publish":
+            result, _ = bench_publish(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
+                                      tokens=min(args.tokens // 2, 4096))
         elif args.workload == "activation":
             result, _ = bench_activation(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                          rows=min(args.tokens * 16, 131072))
@@ -1341,6 +1410,7 @@ def main():
         others["latent_sparse_decode"], _ = bench_latent_sparse(lib, b, w.abi, 20)
         others["rolling_compressor"], _ = bench_compressor(lib, b, w.abi, hbm_peak, 10)
         others["activation_quant"], _ = bench_activation(lib, b, w.abi, hbm_peak, 5)
+        others["rows_publish"], _ = bench_publish(lib, b, w.abi, hbm_peak, 5)
 
     if rank != 0:
         if dist is not None:

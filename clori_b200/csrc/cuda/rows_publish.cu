@@ -17,12 +17,16 @@ namespace yvx {
 constexpr int kPublishThreads = 128;
 constexpr int kPublishSegments = 8;  // width <= 1024
 
+// round to nearest even; only finite values are ever published (a non-finite lane sets the status
+// word and the row is not written), so the reference's NaN quieting does not come into it
 __device__ __forceinline__ float publish_bf16(float v)
 {
-    return __uint_as_float((uint32_t)bf16_bits_rne(v) << 16);
+    return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-__global__ void __launch_bounds__(kPublishThreads)
+// SEGMENTS = 128-lane segments a thread holds (the smallest of 1, 2, 4, 8 that covers the width).
+template <int SEGMENTS>
+__global__ void __launch_bounds__(kPublishThreads, SEGMENTS <= 4 ? 6 : 3)
 rows_publish_kernel(const yvx_rows_publish_args a)
 {
     const unsigned int lane = threadIdx.x & 31u;
@@ -31,10 +35,10 @@ rows_publish_kernel(const yvx_rows_publish_args a)
     float *row = a.values + r * a.row_stride;
     const unsigned int width = (unsigned int)a.width;
     const unsigned int segments = (width + 127u) / 128u;
-    float v[kPublishSegments][4];
+    float v[SEGMENTS][4];
     bool finite = true;
 #pragma unroll
-    for (int s = 0; s < kPublishSegments; ++s) {
+    for (int s = 0; s < SEGMENTS; ++s) {
         const unsigned int base = (unsigned int)s * 128u + lane * 4u;
         v[s][0] = v[s][1] = v[s][2] = v[s][3] = 0.0f;
         if (s < (int)segments && base < width) {
@@ -47,7 +51,7 @@ rows_publish_kernel(const yvx_rows_publish_args a)
     if (a.norm_mode) {
         double squares = 0.0;
 #pragma unroll
-        for (int s = 0; s < kPublishSegments; ++s)
+        for (int s = 0; s < SEGMENTS; ++s)
 #pragma unroll
             for (int k = 0; k < 4; ++k) squares = __dadd_rn(squares, __dmul_rn((double)v[s][k], (double)v[s][k]));
 #pragma unroll
@@ -56,7 +60,7 @@ rows_publish_kernel(const yvx_rows_publish_args a)
         const double inverse = __ddiv_rn(1.0, sqrt(__dadd_rn(__ddiv_rn(squares, (double)width), a.epsilon)));
         finite = finite && isfinite(inverse);
 #pragma unroll
-        for (int s = 0; s < kPublishSegments; ++s) {
+        for (int s = 0; s < SEGMENTS; ++s) {
             const unsigned int base = (unsigned int)s * 128u + lane * 4u;
             if (s >= (int)segments || base >= width) continue;
             float weight[4] = {1.0f, 1.0f, 1.0f, 1.0f};
@@ -75,28 +79,54 @@ rows_publish_kernel(const yvx_rows_publish_args a)
         }
     }
     if (a.rope_dims) {
-        const unsigned int rope_start = width - (unsigned int)a.rope_dims;
+        // Pair p (lanes rope_start + 2p, + 2p + 1) is rotated by the thread that holds it, but its sine and
+        // cosine are computed by thread p % 32, so the 32 threads share the work; up to two pairs per thread
+        // this way (rope_dims <= 128), beyond that each holder computes its own.
+        const unsigned int rope_start = width - (unsigned int)a.rope_dims, pairs = (unsigned int)a.rope_dims / 2u;
         const unsigned long long position = a.start_position + r / a.rows_per_token;
+        const bool shared = pairs <= 64u;
+        double cs[2] = {1.0, 1.0}, sn[2] = {0.0, 0.0};
+        if (shared) {
 #pragma unroll
-        for (int s = 0; s < kPublishSegments; ++s) {
+            for (int j = 0; j < 2; ++j) {
+                const unsigned int p = lane + 32u * j;
+                if (p < pairs) sincos(__dmul_rn((double)position, a.rope_frequency[p]), &sn[j], &cs[j]);
+                finite = finite && isfinite(cs[j]) && isfinite(sn[j]);
+            }
+        }
+#pragma unroll
+        for (int s = 0; s < SEGMENTS; ++s) {
+            if ((unsigned int)(s + 1) * 128u <= rope_start || s >= (int)segments) continue;   // uniform over the warp
             const unsigned int base = (unsigned int)s * 128u + lane * 4u;
-            if (s >= (int)segments || base >= width) continue;
 #pragma unroll
             for (int k = 0; k < 4; k += 2) {
-                if (base + k >= rope_start) {
-                    const unsigned int i = base + k - rope_start;
-                    const double angle = __dmul_rn((double)position, a.rope_frequency[i >> 1]);
-                    double sn, c;
-                    sincos(angle, &sn, &c);
+                const bool rotated = base + k >= rope_start && base < width;
+                const unsigned int p = rotated ? (base + k - rope_start) >> 1 : 0u;
+                double c, sine;
+                if (shared) {
+                    const int source = (int)(p & 31u);
+                    const double c0 = __shfl_sync(0xffffffffu, cs[0], source), c1 = __shfl_sync(0xffffffffu, cs[1], source);
+                    const double s0 = __shfl_sync(0xffffffffu, sn[0], source), s1 = __shfl_sync(0xffffffffu, sn[1], source);
+                    c = p < 32u ? c0 : c1;
+                    sine = p < 32u ? s0 : s1;
+                } else if (rotated) {
+                    sincos(__dmul_rn((double)position, a.rope_frequency[p]), &sine, &c);
+                    finite = finite && isfinite(c) && isfinite(sine);
+                }
+                if (rotated) {
                     const double x = (double)v[s][k], y = (double)v[s][k + 1];
-                    const float rx = __double2float_rn(__dsub_rn(__dmul_rn(x, c), __dmul_rn(y, sn)));
-                    const float ry = __double2float_rn(__dadd_rn(__dmul_rn(x, sn), __dmul_rn(y, c)));
-                    finite = finite && isfinite(c) && isfinite(sn) && isfinite(rx) && isfinite(ry);
+                    const float rx = __double2float_rn(__dsub_rn(__dmul_rn(x, c), __dmul_rn(y, sine)));
+                    const float ry = __double2float_rn(__dadd_rn(__dmul_rn(x, sine), __dmul_rn(y, c)));
+                    finite = finite && isfinite(rx) && isfinite(ry);
                     v[s][k] = rx, v[s][k + 1] = ry;
                 }
             }
+        }
+        if (finite) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) v[s][k] = publish_bf16(v[s][k]);
+            for (int s = 0; s < SEGMENTS; ++s)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[s][k] = publish_bf16(v[s][k]);
         }
     }
     if (a.quantization) {
@@ -105,7 +135,7 @@ rows_publish_kernel(const yvx_rows_publish_args a)
         const bool fp8 = a.quantization == 8u;
         const float hadamard_scale = a.hadamard ? __fdiv_rn(1.0f, sqrtf((float)count)) : 1.0f;
 #pragma unroll
-        for (int s = 0; s < kPublishSegments; ++s) {
+        for (int s = 0; s < SEGMENTS; ++s) {
             if ((unsigned int)s * 128u >= count) continue;       // uniform over the warp
             const unsigned int base = (unsigned int)s * 128u + lane * 4u;
             const bool active = base < count;
@@ -125,7 +155,7 @@ rows_publish_kernel(const yvx_rows_publish_args a)
         return;
     }
 #pragma unroll
-    for (int s = 0; s < kPublishSegments; ++s) {
+    for (int s = 0; s < SEGMENTS; ++s) {
         const unsigned int base = (unsigned int)s * 128u + lane * 4u;
         if (s < (int)segments && base < width)
             *reinterpret_cast<float4 *>(row + base) = make_float4(v[s][0], v[s][1], v[s][2], v[s][3]);
@@ -156,7 +186,11 @@ extern "C" int yvx_cuda_rows_publish(const yvx_rows_publish_args *a, void *strea
             return YVEX_ERR_UNSUPPORTED;
     }
     if (!a->rows) return 0;
-    yvx::rows_publish_kernel<<<(unsigned int)((a->rows + 3ull) / 4ull), yvx::kPublishThreads, 0,
-                               (cudaStream_t)stream>>>(*a);
+    const unsigned int grid = (unsigned int)((a->rows + 3ull) / 4ull);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (a->width <= 128ull) yvx::rows_publish_kernel<1><<<grid, yvx::kPublishThreads, 0, s>>>(*a);
+    else if (a->width <= 256ull) yvx::rows_publish_kernel<2><<<grid, yvx::kPublishThreads, 0, s>>>(*a);
+    else if (a->width <= 512ull) yvx::rows_publish_kernel<4><<<grid, yvx::kPublishThreads, 0, s>>>(*a);
+    else yvx::rows_publish_kernel<8><<<grid, yvx::kPublishThreads, 0, s>>>(*a);
     return yvx_cuda_check(cudaGetLastError(), "rows_publish_kernel");
 }
