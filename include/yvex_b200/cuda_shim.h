@@ -41,7 +41,8 @@ int yvx_cuda_event_elapsed_ms(void *start, void *stop, float *milliseconds);
 /* Capture of the calls made on `stream` into a replayable graph (no reference entry
  * point of this name; the reference's operators are capture-aware, src/backend/cuda/
  * capability.c:802-805). The yvx_cuda_gqa_attention, _mla_decode, _latent_reduce,
- * _kv_append_rotary and _lse_combine entries may be called between begin and end. */
+ * _kv_append_rotary, _lse_combine, _rows_publish, _compressor_chunk and _activation_quant
+ * entries may be called between begin and end. */
 int yvx_cuda_graph_capture_begin(void *stream);
 int yvx_cuda_graph_capture_end(void *stream, void **executable);
 int yvx_cuda_graph_launch(void *executable, void *stream);

@@ -146,3 +146,64 @@ def test_operator_entry(backend, oracle):
     assert call() == abi.YVEX_ERR_BOUNDS and failure.stage == b"publish"
     r.activation_block_width, r.rows = 32, x.shape[0] + 1
     assert call() == abi.YVEX_ERR_FORMAT
+
+
+def test_chain_compressor_and_activation_inside_a_stream_capture(backend, oracle):
+    """The three stage entries enqueue work only (no allocation, no synchronisation), so a decode
+    step's calls can be captured once and replayed: the replayed graph leaves the same bits as the
+    direct calls."""
+    from compressor_cases import build as build_compressor
+    from oracle.binding import compressor_initial_state
+    lib, s = backend.lib, backend.stream
+    name, width, rpt, tokens, start, chain = CASES[0]
+    x, w = build(31, width, rpt)
+    freq = oracle.rope_frequencies(PositionPolicy(*POLICY), 64)
+    ratio, hd = 4, 128
+    case = build_compressor(32, ratio, hd, 1, (ratio,))
+    kv0, score0 = compressor_initial_state(ratio, hd, 1)
+    t = dict(x=backend.tensor("x", x), f=backend.tensor("f", freq, dtype=abi.DTYPE_F64),
+             kv=backend.tensor("kv", case["token_kv"]), sc=backend.tensor("sc", case["token_score"]),
+             ape=backend.tensor("ape", case["ape"]), skv=backend.tensor("skv", kv0), ssc=backend.tensor("ssc", score0),
+             akv=backend.alloc("akv", abi.DTYPE_F32, kv0.shape), asc=backend.alloc("asc", abi.DTYPE_F32, kv0.shape),
+             norm=backend.tensor("norm", case["norm"]), rows=backend.alloc("rows", abi.DTYPE_F32, (1, hd)),
+             status=backend.tensor("status", np.zeros(1, np.int32)))
+    p = abi.RowsPublishArgs()
+    p.values, p.rows, p.rows_per_token, p.row_stride, p.width = t["x"].data_ptr, rpt, rpt, width, width
+    p.norm_mode, p.epsilon, p.rope_dims, p.rope_frequency, p.start_position = 1, 1e-6, 64, t["f"].data_ptr, start
+    p.status = t["status"].data_ptr
+    c = abi.CompressorArgs()
+    c.ratio, c.head_dim, c.overlap, c.start_position, c.token_count = ratio, hd, 1, 0, ratio
+    c.token_kv, c.token_score, c.token_stride, c.ape = t["kv"].data_ptr, t["sc"].data_ptr, 2 * hd, t["ape"].data_ptr
+    c.state_kv, c.state_score, c.after_kv, c.after_score = (t[k].data_ptr for k in ("skv", "ssc", "akv", "asc"))
+    c.compressed, c.compressed_stride = t["rows"].data_ptr, hd
+    c.norm_weights, c.epsilon, c.rope_dims, c.rope_frequency = t["norm"].data_ptr, 1e-6, 64, t["f"].data_ptr
+    c.status = t["status"].data_ptr
+    q = abi.ActivationArgs()
+    q.values, q.rows, q.row_stride, q.count = t["rows"].data_ptr, 1, hd, hd
+    q.quantization, q.block_width, q.hadamard = 4, 32, 1
+    q.hadamard_scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+    q.status = t["status"].data_ptr
+    emitted = C.c_ulonglong()
+
+    def step():
+        assert lib.yvx_cuda_rows_publish(C.byref(p), s) == 0
+        assert lib.yvx_cuda_compressor_chunk(C.byref(c), s, C.byref(emitted)) == 0
+        assert lib.yvx_cuda_activation_quant(C.byref(q), s) == 0
+
+    step()
+    assert lib.yvx_cuda_stream_synchronize(s) == 0, lib.yvx_cuda_last_error_text()
+    for k in ("rows", "akv", "asc"):
+        t[k].struct.is_written = 1
+    direct = [t[k].read() for k in ("x", "rows", "akv", "asc")]
+    assert emitted.value == 1 and int(t["status"].read()[0]) == 0
+    t["x"].write(x)                      # the publication is in place: start again from the projected rows
+    assert lib.yvx_cuda_graph_capture_begin(s) == 0, lib.yvx_cuda_last_error_text()
+    step()
+    graph = C.c_void_p()
+    assert lib.yvx_cuda_graph_capture_end(s, C.byref(graph)) == 0, lib.yvx_cuda_last_error_text()
+    assert lib.yvx_cuda_graph_launch(graph, s) == 0
+    assert lib.yvx_cuda_stream_synchronize(s) == 0, lib.yvx_cuda_last_error_text()
+    replayed = [t[k].read() for k in ("x", "rows", "akv", "asc")]
+    for a, b in zip(direct, replayed):
+        assert same_bits(a, b)
+    assert lib.yvx_cuda_graph_destroy(graph) == 0
