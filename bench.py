@@ -943,6 +943,83 @@ def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
         lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
         return ms.value / repeats
     select_ms, reduce_ms, step_ms = timed(select), timed(reduce), timed(select, reduce)
+
+    # ---- the whole device side of the step between the projections and the output projection: the
+    # publication chains of the query heads, the new local row and the index queries, both rolling
+    # compressors with their activation, then selection and reduce. The preparation stages work on
+    # scratch rows of their own so that the CPU check of selection and reduce below stays valid.
+    from oracle.binding import compressor_initial_state
+    prep = {"q": tokens * heads * hd, "l": tokens * hd, "iq": tokens * ih * idim, "w": hd,
+            "mkv": tokens * 2 * hd, "msc": tokens * 2 * hd, "mape": ratio * 2 * hd, "mrow": hd,
+            "ikv": tokens * 2 * idim, "isc": tokens * 2 * idim, "iape": ratio * 2 * idim, "irow": idim}
+    for i, (name, n) in enumerate(prep.items()):
+        dev["p_" + name] = _alloc(lib, n * 4)
+        lib.yvx_cuda_fill_normal(dev["p_" + name], abi.DTYPE_F32, n, 901 + i, 1.0, backend.stream)
+    for name, width in (("m", hd), ("i", idim)):
+        kv0, score0 = compressor_initial_state(ratio, width, 1)
+        for part, array in (("skv", kv0), ("ssc", score0), ("akv", kv0), ("asc", score0)):
+            dev[f"p_{name}{part}"] = _alloc(lib, array.nbytes)
+            lib.yvx_cuda_upload_async(dev[f"p_{name}{part}"], array.ctypes.data, array.nbytes, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
+
+    def publish_args(values, n_rows, rpt, width, **kw):
+        a = abi.RowsPublishArgs()
+        a.values, a.rows, a.rows_per_token, a.row_stride, a.width = values, n_rows, rpt, width, width
+        a.epsilon, a.rope_dims, a.rope_frequency, a.start_position = 1e-6, rope, dev["frequency"], start
+        a.status = dev["status"]
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return a
+
+    def compressor_args(tag, width, row):
+        a = abi.CompressorArgs()
+        a.ratio, a.head_dim, a.overlap, a.start_position, a.token_count = ratio, width, 1, start, tokens
+        a.token_kv, a.token_score, a.token_stride, a.ape = dev[f"p_{tag}kv"], dev[f"p_{tag}sc"], 2 * width, dev[f"p_{tag}ape"]
+        a.state_kv, a.state_score = dev[f"p_{tag}skv"], dev[f"p_{tag}ssc"]
+        a.after_kv, a.after_score = dev[f"p_{tag}akv"], dev[f"p_{tag}asc"]
+        a.compressed, a.compressed_stride = dev[row], width
+        a.norm_weights, a.epsilon, a.rope_dims, a.rope_frequency = dev["p_w"], 1e-6, rope, dev["frequency"]
+        a.status = dev["status"]
+        return a
+
+    def activation_args(values, width, count, quantization, block, hadamard):
+        a = abi.ActivationArgs()
+        a.values, a.rows, a.row_stride, a.count = values, 1, width, count
+        a.quantization, a.block_width, a.hadamard = quantization, block, hadamard
+        a.hadamard_scale, a.status = float(np.float32(1.0) / np.sqrt(np.float32(count))), dev["status"]
+        return a
+    stages = [
+        (lib.yvx_cuda_rows_publish, publish_args(dev["p_q"], tokens * heads, heads, hd, norm_mode=1)),
+        (lib.yvx_cuda_rows_publish, publish_args(dev["p_l"], tokens, 1, hd, norm_mode=2, norm_weights=dev["p_w"],
+                                                 quantization=8, activation_count=hd - rope, block_width=64)),
+        (lib.yvx_cuda_rows_publish, publish_args(dev["p_iq"], tokens * ih, ih, idim, quantization=4,
+                                                 activation_count=idim, block_width=32, hadamard=1)),
+        (lib.yvx_cuda_activation_quant, activation_args(dev["p_mrow"], hd, hd - rope, 8, 64, 0)),
+        (lib.yvx_cuda_activation_quant, activation_args(dev["p_irow"], idim, idim, 4, 32, 1)),
+    ]
+    compressors = [compressor_args("m", hd, "p_mrow"), compressor_args("i", idim, "p_irow")]
+    emitted = C.c_ulonglong()
+
+    # one launch for the three publication chains; the activation rides in each compressor's launch
+    batch = (abi.RowsPublishArgs * 3)(*[a for _, a in stages[:3]])
+    for a, (_, q) in zip(compressors, stages[3:]):
+        a.activation_quantization, a.activation_count = q.quantization, q.count
+        a.activation_block_width, a.activation_hadamard = q.block_width, q.hadamard
+
+    def prepare():
+        assert lib.yvx_cuda_rows_publish_batch(batch, 3, backend.stream) == 0, lib.yvx_cuda_last_error_text()
+        for a in compressors:
+            assert lib.yvx_cuda_compressor_chunk(C.byref(a), backend.stream, C.byref(emitted)) == 0, \
+                lib.yvx_cuda_last_error_text()
+    prepare_ms, full_ms = timed(prepare), timed(prepare, select, reduce)
+    prepare_launches = 3
+    graph_ms = None
+    graph = C.c_void_p()
+    if lib.yvx_cuda_graph_capture_begin(backend.stream) == 0:
+        prepare(); select(); reduce()
+        if lib.yvx_cuda_graph_capture_end(backend.stream, C.byref(graph)) == 0 and graph:
+            graph_ms = timed(lambda: lib.yvx_cuda_graph_launch(graph, backend.stream))
+            lib.yvx_cuda_graph_destroy(graph)
     got = {name: np.zeros(shape, dtype) for name, shape, dtype in (
         ("selected", (tokens, topk), np.uint64), ("count", (tokens,), np.uint64), ("status", (1,), np.int32),
         ("out", (tokens, heads * hd), np.float32))}
@@ -956,6 +1033,10 @@ def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
               "kernels": "csa_score_kernel, csa_rank_rows_kernel, csa_rank_lists_kernel, latent_reduce_kernel, latent_fold_kernel",
               "launches_per_step": int(launches.value) + int(reduce_launches.value), "select_ms": select_ms, "reduce_ms": reduce_ms,
               "step_ms": step_ms, "score_fp64_tflops": flops / (select_ms * 1e-3) / 1e12,
+              "prepare_ms": prepare_ms, "prepare_launches": prepare_launches,
+              "prepare_stages": "publication chains of query heads, local row and index queries; main and index "
+                                "rolling compressors with their activation",
+              "full_step_ms": full_ms, "full_step_graph_replay_ms": graph_ms,
               "score_note": "scores keep the reference's double-precision order: FP64 pipe bound, keys (%.0f MB) stay in L2"
                             % (rows * idim * 4 / 1e6),
               "status_word": int(got["status"][0])}

@@ -261,6 +261,8 @@ class CompressorArgs(C.Structure):
         ("compressed", C.c_void_p), ("compressed_stride", u64), ("positions", C.c_void_p),
         ("norm_weights", C.c_void_p), ("epsilon", C.c_double), ("rope_dims", u64), ("rope_frequency", C.c_void_p),
         ("status", C.c_void_p),
+        ("activation_quantization", C.c_uint), ("activation_count", u64), ("activation_block_width", u64),
+        ("activation_hadamard", C.c_int),
     ]
 
 
@@ -377,7 +379,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
     "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
     "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
-    "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk", "yvx_cuda_activation_quant", "yvx_cuda_rows_publish",
+    "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk", "yvx_cuda_activation_quant", "yvx_cuda_rows_publish", "yvx_cuda_rows_publish_batch",
 ]
 
 _lib = None
@@ -438,6 +440,7 @@ def load():
     lib.yvex_b200_attention_publish_execute.argtypes = [
         vp, P(AttentionPublishRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
     lib.yvx_cuda_rows_publish.argtypes = [P(RowsPublishArgs), vp]
+    lib.yvx_cuda_rows_publish_batch.argtypes = [P(RowsPublishArgs), C.c_uint, vp]
     lib.yvex_b200_kv_append_rotary_execute.argtypes = [vp, P(KvAppendRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_mla_decode_execute.argtypes = [vp, P(MlaDecodeRequest), P(OperationFacts), P(Error)]
     lib.yvex_b200_kv_pool_create.restype = vp

@@ -12,7 +12,7 @@
 // (bf16 round, RMS norm, bf16 round, rotation, bf16 round) while the row is still in
 // registers. Per lane the softmax runs in double in the reference's order (previous
 // half before current half, slot by slot), products and sums separately rounded.
-#include "common.cuh"
+#include "activation.cuh"
 
 namespace yvx {
 
@@ -414,6 +414,26 @@ compressor_chunk4_kernel(const yvx_compressor_args a, unsigned long long emitted
             }
         }
     }
+    if (a.activation_quantization) {
+        // warp w holds lanes [128 w, 128 w + 128): one segment of the activation's layout
+        const unsigned int count = (unsigned int)a.activation_count, segment = (tid >> 5) * 128u;
+        if (segment < count) {
+            const bool quantised = lane0 < count;
+            float q[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) q[k] = quantised ? value[k] : 0.0f;
+            const unsigned int group = (unsigned int)a.activation_block_width / 4u;
+            if (a.activation_hadamard)
+                activation_segment<true>(q, tid & 31u, group, a.activation_quantization == 8u,
+                                         __fdiv_rn(1.0f, sqrtf((float)count)));
+            else
+                activation_segment<false>(q, tid & 31u, group, a.activation_quantization == 8u, 1.0f);
+            if (quantised) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) value[k] = q[k];
+            }
+        }
+    }
     if (!finite) {
         atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
         return;
@@ -458,6 +478,16 @@ extern "C" int yvx_cuda_compressor_chunk(const yvx_compressor_args *a, void *str
         (unsigned long long)args.compressed | (unsigned long long)args.norm_weights;
     const bool vector = !(a->head_dim & 3ull) && !(a->token_stride & 3ull) && !(a->compressed_stride & 3ull) &&
                         !(misaligned & 15ull);
+    if (a->activation_quantization) {
+        if (a->activation_quantization != 8u && a->activation_quantization != 4u) return YVEX_ERR_FORMAT;
+        if (!a->activation_count || a->activation_count > a->head_dim || !a->activation_block_width)
+            return YVEX_ERR_INVALID_ARG;
+        if (a->activation_count % a->activation_block_width) return YVEX_ERR_BOUNDS;
+        if (!vector || (a->activation_count & 3ull) || a->activation_block_width < 4ull ||
+            a->activation_block_width > 128ull || (a->activation_block_width & (a->activation_block_width - 1ull)) ||
+            (a->activation_hadamard && (a->activation_count <= 64ull || a->activation_count > 128ull)))
+            return YVEX_ERR_UNSUPPORTED;
+    }
     const unsigned int grid = (unsigned int)(emitted + slots);
     const unsigned int threads4 = (unsigned int)((a->head_dim / 4ull + 31ull) / 32ull * 32ull);
     if (vector && a->overlap)

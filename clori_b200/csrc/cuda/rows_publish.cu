@@ -16,6 +16,7 @@ namespace yvx {
 
 constexpr int kPublishThreads = 128;
 constexpr int kPublishSegments = 8;  // width <= 1024
+constexpr int kPublishBatch = 4;     // row sets per batched launch
 
 // round to nearest even; only finite values are ever published (a non-finite lane sets the status
 // word and the row is not written), so the reference's NaN quieting does not come into it
@@ -26,12 +27,8 @@ __device__ __forceinline__ float publish_bf16(float v)
 
 // SEGMENTS = 128-lane segments a thread holds (the smallest of 1, 2, 4, 8 that covers the width).
 template <int SEGMENTS>
-__global__ void __launch_bounds__(kPublishThreads, SEGMENTS <= 4 ? 6 : 3)
-rows_publish_kernel(const yvx_rows_publish_args a)
+__device__ __forceinline__ void publish_row(const yvx_rows_publish_args &a, unsigned long long r, unsigned int lane)
 {
-    const unsigned int lane = threadIdx.x & 31u;
-    const unsigned long long r = (unsigned long long)blockIdx.x * (kPublishThreads / 32) + (threadIdx.x >> 5);
-    if (r >= a.rows) return;
     float *row = a.values + r * a.row_stride;
     const unsigned int width = (unsigned int)a.width;
     const unsigned int segments = (width + 127u) / 128u;
@@ -162,9 +159,69 @@ rows_publish_kernel(const yvx_rows_publish_args a)
     }
 }
 
+template <int SEGMENTS>
+__global__ void __launch_bounds__(kPublishThreads, SEGMENTS <= 4 ? 6 : 3)
+rows_publish_kernel(const yvx_rows_publish_args a)
+{
+    const unsigned long long r = (unsigned long long)blockIdx.x * (kPublishThreads / 32) + (threadIdx.x >> 5);
+    if (r < a.rows) publish_row<SEGMENTS>(a, r, threadIdx.x & 31u);
+}
+
+// Several row sets in one launch (a decode step publishes its query heads, its new local
+// row and its index queries): CTAs [first[i], first[i + 1]) belong to set i.
+struct publish_batch {
+    yvx_rows_publish_args set[kPublishBatch];
+    unsigned int first[kPublishBatch + 1];
+};
+
+template <int SEGMENTS>
+__global__ void __launch_bounds__(kPublishThreads, SEGMENTS <= 4 ? 6 : 3)
+rows_publish_batch_kernel(const __grid_constant__ publish_batch batch)
+{
+    int i = 0;
+#pragma unroll
+    for (int k = 1; k < kPublishBatch; ++k)
+        if (blockIdx.x >= batch.first[k]) i = k;
+    const yvx_rows_publish_args &a = batch.set[i];
+    const unsigned long long r =
+        (unsigned long long)(blockIdx.x - batch.first[i]) * (kPublishThreads / 32) + (threadIdx.x >> 5);
+    if (r < a.rows) publish_row<SEGMENTS>(a, r, threadIdx.x & 31u);
+}
+
 }  // namespace yvx
 
-extern "C" int yvx_cuda_rows_publish(const yvx_rows_publish_args *a, void *stream)
+static int rows_publish_admit(const yvx_rows_publish_args *a);
+
+extern "C" int yvx_cuda_rows_publish_batch(const yvx_rows_publish_args *sets, unsigned int count, void *stream)
+{
+    if (!sets || !count || count > (unsigned int)yvx::kPublishBatch) return YVEX_ERR_INVALID_ARG;
+    yvx::publish_batch batch;
+    unsigned long long widest = 0ull, ctas = 0ull;
+    for (unsigned int i = 0; i < (unsigned int)yvx::kPublishBatch; ++i) {
+        batch.first[i] = (unsigned int)ctas;
+        if (i < count) {
+            const int rc = rows_publish_admit(&sets[i]);
+            if (rc != 0) return rc;
+            batch.set[i] = sets[i];
+            widest = sets[i].width > widest ? sets[i].width : widest;
+            ctas += (sets[i].rows + 3ull) / 4ull;
+        } else {
+            batch.set[i] = sets[0];
+            batch.set[i].rows = 0ull;
+        }
+    }
+    batch.first[yvx::kPublishBatch] = (unsigned int)ctas;
+    if (ctas > 0x7fffffffull) return YVEX_ERR_UNSUPPORTED;
+    if (!ctas) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (widest <= 128ull) yvx::rows_publish_batch_kernel<1><<<(unsigned int)ctas, yvx::kPublishThreads, 0, s>>>(batch);
+    else if (widest <= 256ull) yvx::rows_publish_batch_kernel<2><<<(unsigned int)ctas, yvx::kPublishThreads, 0, s>>>(batch);
+    else if (widest <= 512ull) yvx::rows_publish_batch_kernel<4><<<(unsigned int)ctas, yvx::kPublishThreads, 0, s>>>(batch);
+    else yvx::rows_publish_batch_kernel<8><<<(unsigned int)ctas, yvx::kPublishThreads, 0, s>>>(batch);
+    return yvx_cuda_check(cudaGetLastError(), "rows_publish_batch_kernel");
+}
+
+static int rows_publish_admit(const yvx_rows_publish_args *a)
 {
     if (!a || !a->values || !a->status || !a->width || !a->rows_per_token || a->row_stride < a->width)
         return YVEX_ERR_INVALID_ARG;
@@ -185,6 +242,13 @@ extern "C" int yvx_cuda_rows_publish(const yvx_rows_publish_args *a, void *strea
             (a->hadamard && (a->activation_count <= 64ull || a->activation_count > 128ull)))
             return YVEX_ERR_UNSUPPORTED;
     }
+    return 0;
+}
+
+extern "C" int yvx_cuda_rows_publish(const yvx_rows_publish_args *a, void *stream)
+{
+    const int rc = rows_publish_admit(a);
+    if (rc != 0) return rc;
     if (!a->rows) return 0;
     const unsigned int grid = (unsigned int)((a->rows + 3ull) / 4ull);
     cudaStream_t s = (cudaStream_t)stream;

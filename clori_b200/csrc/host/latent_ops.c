@@ -341,7 +341,7 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
     unsigned long long width = 0ull, slots = 0ull, elements = 0ull, emitted, launched = 0ull;
     yvx_compressor_args a;
     unsigned int activation_launches = 0u;
-    int overlap, rc;
+    int overlap, rc, separate_activation = 0;
     if (failure) memset(failure, 0, sizeof(*failure));
     if (!r || !facts || !r->position_rows || !r->state_kv || !r->state_score || !r->next_state_kv ||
         !r->next_state_score || (r->token_count && (!r->token_kv || !r->token_score)))
@@ -431,7 +431,23 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
     a.status = backend->status_device;
     rc = yvx_backend_status_arm(backend, where, err);
     if (rc != YVEX_OK) return rc;
+    if (r->activation_quantization && emitted) {
+        /* main rows keep their rotated lanes; index rows are quantised whole
+         * (src/graph/attention_execute.c:807-818). Fused into the compressor's launch where its
+         * row geometry allows, else a launch of its own behind it. */
+        a.activation_quantization = r->activation_quantization;
+        a.activation_count = r->kind == YVEX_B200_ROLLING_MAIN ? r->head_dimension - r->rope_dimension
+                                                                : r->head_dimension;
+        a.activation_block_width = r->activation_block_width;
+        a.activation_hadamard = r->activation_hadamard;
+        if (!a.activation_count) a.activation_quantization = 0u;
+    }
     rc = yvx_cuda_compressor_chunk(&a, backend->stream, &launched);
+    if (rc == YVEX_ERR_UNSUPPORTED && a.activation_quantization) {
+        a.activation_quantization = 0u;
+        separate_activation = 1;
+        rc = yvx_cuda_compressor_chunk(&a, backend->stream, &launched);
+    }
     if (rc != 0) {
         if (failure) {
             failure->code = YVEX_B200_ATTENTION_FAILURE_LAUNCH;
@@ -439,9 +455,7 @@ int yvex_b200_attention_compress_execute(yvex_backend *backend, yvex_b200_attent
         }
         return yvx_backend_device_fail(backend, rc, where, err);
     }
-    if (r->activation_quantization && emitted) {
-        /* main rows keep their rotated lanes; index rows are quantised whole
-         * (src/graph/attention_execute.c:807-818) */
+    if (separate_activation) {
         yvx_activation_args q;
         memset(&q, 0, sizeof(q));
         q.values = a.compressed;

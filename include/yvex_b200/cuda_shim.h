@@ -341,6 +341,13 @@ typedef struct yvx_compressor_args {
     unsigned long long rope_dims;             /* 0: no rotation */
     const double *rope_frequency;             /* [rope_dims/2] radians per position */
     int *status;
+    /* optional, behind the publication chain and in the same launch: the activation fake
+     * quantisation of yvx_cuda_activation_quant over the first activation_count lanes of every
+     * emitted row (0: none; needs the 16-byte row geometry, blocks of 4 << k <= 128 lanes, and
+     * with the transform activation_count in (64, 128]; otherwise YVEX_ERR_UNSUPPORTED) */
+    unsigned int activation_quantization;
+    unsigned long long activation_count, activation_block_width;
+    int activation_hadamard;
 } yvx_compressor_args;
 int yvx_cuda_compressor_chunk(const yvx_compressor_args *args, void *stream,
                               unsigned long long *emitted);
@@ -400,6 +407,9 @@ typedef struct yvx_rows_publish_args {
     int *status;
 } yvx_rows_publish_args;
 int yvx_cuda_rows_publish(const yvx_rows_publish_args *args, void *stream);
+/* Up to four row sets in ONE launch (a decode step publishes its query heads, its new local
+ * row and its index queries); each set as in yvx_cuda_rows_publish, results identical. */
+int yvx_cuda_rows_publish_batch(const yvx_rows_publish_args *sets, unsigned int count, void *stream);
 
 /* ---- KV append with rotary embedding (one launch per step) ---------------------------
  * Replaces, for the new rows of a step, the two rotate-half launches on Q and K

@@ -124,7 +124,7 @@ def test_operator_entries(backend, oracle):
         rc = backend.lib.yvex_b200_attention_compress_execute(backend.handle, C.byref(c), C.byref(failure),
                                                               C.byref(facts), C.byref(err))
         assert rc == 0, err.message
-        assert c.emitted == 3 and facts.kernel_launches == 2
+        assert c.emitted == 3 and facts.kernel_launches == 1      # the activation rides in the compressor's launch
         got = d["rows"].read()
         # the chain in front may differ from the CPU in a last place (see the compressor tests); where the
         # published rows agree, the quantised rows must agree exactly

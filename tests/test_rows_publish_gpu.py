@@ -123,6 +123,39 @@ def test_refusals_and_status(backend):
     assert run_gpu(backend, x, 1, 0, norm_mode=1)[1] == 1
 
 
+def test_batched_launch_equals_separate_launches(backend, oracle):
+    """The three row sets of a decode step in one launch: bit-equal to one launch per set."""
+    lib, s = backend.lib, backend.stream
+    freq = backend.tensor("f", oracle.rope_frequencies(PositionPolicy(*POLICY), 64), dtype=abi.DTYPE_F64)
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    inputs, tensors, descriptors = [], [], (abi.RowsPublishArgs * 3)()
+    for i, (name, width, rpt, tokens, start, chain) in enumerate(CASES[:3]):
+        x, w = build(700 + i, width, rpt * 2)
+        weights = backend.tensor("w", w)
+        inputs.append(x)
+        tensors.append((backend.tensor("x", x), weights))
+        a = descriptors[i]
+        a.values, a.rows, a.rows_per_token, a.row_stride, a.width = tensors[i][0].data_ptr, x.shape[0], rpt, width, width
+        a.norm_mode, a.norm_weights, a.epsilon = chain.get("norm_mode", 0), weights.data_ptr, 1e-6
+        a.rope_dims, a.rope_frequency, a.start_position = 64, freq.data_ptr, start
+        a.quantization, a.activation_count = chain.get("quantization", 0), chain.get("activation_count", 0)
+        a.block_width, a.hadamard, a.status = chain.get("block_width", 0), chain.get("hadamard", 0), status.data_ptr
+    for i in range(3):
+        assert lib.yvx_cuda_rows_publish(C.byref(descriptors[i]), s) == 0, lib.yvx_cuda_last_error_text()
+    assert lib.yvx_cuda_stream_synchronize(s) == 0
+    separate = [t.read() for t, _ in tensors]
+    for (t, _), x in zip(tensors, inputs):
+        t.write(x)
+    assert lib.yvx_cuda_rows_publish_batch(descriptors, 3, s) == 0, lib.yvx_cuda_last_error_text()
+    assert lib.yvx_cuda_stream_synchronize(s) == 0, lib.yvx_cuda_last_error_text()
+    for (t, _), expected in zip(tensors, separate):
+        assert same_bits(t.read(), expected)
+    assert int(status.read()[0]) == 0
+    assert lib.yvx_cuda_rows_publish_batch(descriptors, 5, s) == abi.YVEX_ERR_INVALID_ARG
+    descriptors[1].width = 510
+    assert lib.yvx_cuda_rows_publish_batch(descriptors, 3, s) == abi.YVEX_ERR_UNSUPPORTED
+
+
 def ptr(tensor):
     return C.cast(tensor.ptr, C.c_void_p) if tensor is not None else None
 
