@@ -161,9 +161,30 @@ int yvx_backend_scratch(yvex_backend *backend, unsigned long long bytes, void **
     return YVEX_OK;
 }
 
+/* Host-side fault injection for tests, in the style of the reference's
+ * YVEX_TEST_CUDA_LAUNCH_FAILURE / YVEX_TEST_CUDA_SYNC_FAILURE hooks
+ * (src/backend/cuda/capability.c:763,806): when the variable names the operator (its `where`
+ * string, e.g. "b200.attention.reduce") or "*", the call that would have launched or
+ * synchronised reports a backend failure instead and nothing is enqueued. The GPU is never
+ * made to fail; what is exercised is the host's handling: typed error, sticky refusal. */
+static int injected_failure(const char *variable, const char *where)
+{
+    const char *value = getenv(variable);
+    return value && value[0] && (!strcmp(value, "*") || !strcmp(value, where));
+}
+
+static int inject(yvex_backend *backend, const char *what, const char *where, yvex_error *err)
+{
+    backend->failed = 1;
+    yvex_error_set(err, YVEX_ERR_BACKEND, where, what);
+    return YVEX_ERR_BACKEND;
+}
+
 int yvx_backend_status_arm(yvex_backend *backend, const char *where, yvex_error *err)
 {
     int rc;
+    if (injected_failure("YVEX_B200_TEST_LAUNCH_FAILURE", where))
+        return inject(backend, "injected launch failure (test hook)", where, err);
     if (backend->status_pending) {
         rc = yvx_backend_status_collect(backend, NULL, where, err);
         if (rc != YVEX_OK) return rc;
@@ -176,8 +197,15 @@ int yvx_backend_status_arm(yvex_backend *backend, const char *where, yvex_error 
 int yvx_backend_status_collect(yvex_backend *backend, yvex_backend_operation_facts *facts,
                                const char *where, yvex_error *err)
 {
-    int rc = yvx_cuda_download_async(backend->status_host, backend->status_device, sizeof(int),
-                                     backend->stream);
+    int rc;
+    if (injected_failure("YVEX_B200_TEST_SYNC_FAILURE", where)) {
+        /* the real work was enqueued: drain it so that nothing is in flight behind the refusal */
+        (void)yvx_cuda_stream_synchronize(backend->stream);
+        backend->status_pending = 0;
+        return inject(backend, "injected synchronisation failure (test hook)", where, err);
+    }
+    rc = yvx_cuda_download_async(backend->status_host, backend->status_device, sizeof(int),
+                                 backend->stream);
     if (rc == 0) rc = yvx_cuda_stream_synchronize(backend->stream);
     backend->status_pending = 0;
     if (rc != 0) return yvx_backend_device_fail(backend, rc, where, err);
