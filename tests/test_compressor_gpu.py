@@ -135,6 +135,33 @@ def test_prefill_sized_chunk_does_not_depend_on_the_split(backend, oracle, ratio
     assert same_bits(whole[2], ref[2]) and same_bits(whole[3], ref[3])
 
 
+@pytest.mark.parametrize("ratio,hd,overlap,pad", [
+    (4, 6, 1, 0),        # lanes that are no multiple of four: the one-lane-per-thread kernel
+    (3, 34, 0, 0),       # odd ratio
+    (4, 64, 1, 3),       # token rows whose stride breaks the 16-byte alignment
+    (2, 1024, 1, 0),     # the widest head: 2048-lane rows
+    (2, 1022, 0, 0),     # the widest head of the one-lane-per-thread kernel
+])
+def test_geometries_off_the_fast_path_and_at_the_limits(backend, oracle, ratio, hd, overlap, pad):
+    rope = 2 if hd < 8 else 16
+    case = build(600 + hd, ratio, hd, overlap, (3 * ratio + 1,))
+    freq = oracle.rope_frequencies(PositionPolicy(10000, 0, 0, 0, 0), rope)
+    kv, score = case["state"]
+    width = case["token_kv"].shape[1]
+    tk = np.zeros((case["token_kv"].shape[0], width + pad), np.float32)
+    ts = np.zeros_like(tk)
+    tk[:, :width], ts[:, :width] = case["token_kv"], case["token_score"]
+    ref = oracle.compressor_chunk(ratio, hd, overlap, 0, case["token_kv"], case["token_score"], case["ape"], kv, score,
+                                  case["norm"], 1e-6, rope, freq)
+    got = run_gpu(backend, ratio, hd, overlap, 0, tk, ts, case["ape"], kv, score, case["norm"], 1e-6, rope, freq)
+    assert got[4] == 0 and np.array_equal(got[1], ref[1])
+    check_rows(got[0], ref[0], True)
+    assert same_bits(got[2], ref[2]) and same_bits(got[3], ref[3])
+    raw = run_gpu(backend, ratio, hd, overlap, 0, tk, ts, case["ape"], kv, score)
+    check_rows(raw[0], oracle.compressor_chunk(ratio, hd, overlap, 0, case["token_kv"], case["token_score"],
+                                               case["ape"], kv, score)[0], False)
+
+
 def test_refusals_and_status(backend):
     ratio, hd = 4, 64
     kv, score = compressor_initial_state(ratio, hd, 0)
