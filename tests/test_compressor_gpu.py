@@ -162,6 +162,33 @@ def test_geometries_off_the_fast_path_and_at_the_limits(backend, oracle, ratio, 
                                                case["ape"], kv, score)[0], False)
 
 
+def test_random_geometries_positions_and_chunk_lengths(backend, oracle):
+    """The next-state arithmetic (which row the serial process wrote to a slot last) and the row
+    sources of an emission (chunk, or the state the chunk started from) over random ratios, widths,
+    start positions and chunk lengths, empty chunks and chunks shorter than a group included."""
+    rng = np.random.default_rng(2026)
+    for trial in range(40):
+        ratio = int(rng.choice([2, 3, 4, 5, 8, 16, 128]))
+        hd = int(rng.choice([4, 6, 8, 32, 64, 100, 128]))
+        overlap = int(rng.integers(0, 2))
+        start = int(rng.integers(0, 3 * ratio + 1))
+        length = int(rng.choice([0, 1, ratio - 1, ratio, ratio + 1, 2 * ratio, int(rng.integers(0, 4 * ratio + 2))]))
+        case = build(3000 + trial, ratio, hd, overlap, (start + length,))
+        kv, score = case["state"]
+        head = oracle.compressor_chunk(ratio, hd, overlap, 0, case["token_kv"][:start], case["token_score"][:start],
+                                       case["ape"], kv, score)
+        tk, ts = case["token_kv"][start:], case["token_score"][start:]
+        ref = oracle.compressor_chunk(ratio, hd, overlap, start, tk, ts, case["ape"], head[2], head[3])
+        if length == 0:
+            tk = ts = np.zeros((0, case["token_kv"].shape[1]), np.float32)
+        got = run_gpu(backend, ratio, hd, overlap, start, tk, ts, case["ape"], head[2], head[3])
+        label = (trial, ratio, hd, overlap, start, length)
+        assert got[4] == 0, label
+        assert np.array_equal(got[1], ref[1]), label
+        assert same_bits(got[2], ref[2]) and same_bits(got[3], ref[3]), label
+        check_rows(got[0], ref[0], False)
+
+
 def test_refusals_and_status(backend):
     ratio, hd = 4, 64
     kv, score = compressor_initial_state(ratio, hd, 0)
