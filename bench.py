@@ -1013,13 +1013,35 @@ def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
                 lib.yvx_cuda_last_error_text()
     prepare_ms, full_ms = timed(prepare), timed(prepare, select, reduce)
     prepare_launches = 3
-    graph_ms = None
+    graph_ms = forked_ms = None
     graph = C.c_void_p()
     if lib.yvx_cuda_graph_capture_begin(backend.stream) == 0:
         prepare(); select(); reduce()
         if lib.yvx_cuda_graph_capture_end(backend.stream, C.byref(graph)) == 0 and graph:
             graph_ms = timed(lambda: lib.yvx_cuda_graph_launch(graph, backend.stream))
             lib.yvx_cuda_graph_destroy(graph)
+    # The same step captured with its data flow: the main compressor feeds only the reduce, so it runs
+    # on a second stream beside publication -> index compressor -> selection and joins before the reduce.
+    side, fork, join = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    if (lib.yvx_cuda_stream_create(C.byref(side)) == 0 and lib.yvx_cuda_event_create(C.byref(fork)) == 0 and
+            lib.yvx_cuda_event_create(C.byref(join)) == 0 and lib.yvx_cuda_graph_capture_begin(backend.stream) == 0):
+        main = backend.stream
+        ok = lib.yvx_cuda_event_record(fork, main) == 0 and lib.yvx_cuda_stream_wait_event(side, fork) == 0
+        ok = ok and lib.yvx_cuda_compressor_chunk(C.byref(compressors[0]), side, C.byref(emitted)) == 0
+        ok = ok and lib.yvx_cuda_event_record(join, side) == 0
+        ok = ok and lib.yvx_cuda_rows_publish_batch(batch, 3, main) == 0
+        ok = ok and lib.yvx_cuda_compressor_chunk(C.byref(compressors[1]), main, C.byref(emitted)) == 0
+        if ok:
+            select()
+        ok = ok and lib.yvx_cuda_stream_wait_event(main, join) == 0
+        if ok:
+            reduce()
+        graph = C.c_void_p()
+        if lib.yvx_cuda_graph_capture_end(main, C.byref(graph)) == 0 and graph and ok:
+            forked_ms = timed(lambda: lib.yvx_cuda_graph_launch(graph, main))
+            lib.yvx_cuda_graph_destroy(graph)
+        lib.yvx_cuda_stream_synchronize(main)
+        lib.yvx_cuda_stream_destroy(side)
     got = {name: np.zeros(shape, dtype) for name, shape, dtype in (
         ("selected", (tokens, topk), np.uint64), ("count", (tokens,), np.uint64), ("status", (1,), np.int32),
         ("out", (tokens, heads * hd), np.float32))}
@@ -1037,6 +1059,7 @@ def bench_latent_sparse(lib, backend, abi, repeats, context=131072, tokens=1):
               "prepare_stages": "publication chains of query heads, local row and index queries; main and index "
                                 "rolling compressors with their activation",
               "full_step_ms": full_ms, "full_step_graph_replay_ms": graph_ms,
+              "full_step_graph_replay_two_streams_ms": forked_ms,
               "score_note": "scores keep the reference's double-precision order: FP64 pipe bound, keys (%.0f MB) stay in L2"
                             % (rows * idim * 4 / 1e6),
               "status_word": int(got["status"][0])}

@@ -367,7 +367,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_memset_async", "yvx_cuda_upload_async", "yvx_cuda_download_async",
     "yvx_cuda_copy_async", "yvx_cuda_stream_create", "yvx_cuda_stream_destroy",
     "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
-    "yvx_cuda_event_record", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
+    "yvx_cuda_event_record", "yvx_cuda_stream_wait_event", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
     "yvx_cuda_lse_exchange_bytes", "yvx_cuda_lse_exchange_counter_offset", "yvx_cuda_gqa_attention_exchange",
     "yvx_cuda_lse_exchange_emulated", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
     "yvx_cuda_graph_capture_begin", "yvx_cuda_graph_capture_end", "yvx_cuda_graph_launch", "yvx_cuda_graph_destroy",
@@ -482,6 +482,7 @@ def load():
     lib.yvx_cuda_event_create.argtypes = [P(vp)]
     lib.yvx_cuda_event_destroy.argtypes = [vp]
     lib.yvx_cuda_event_record.argtypes = [vp, vp]
+    lib.yvx_cuda_stream_wait_event.argtypes = [vp, vp]
     lib.yvx_cuda_lse_exchange_bytes.restype = u64
     lib.yvx_cuda_lse_exchange_bytes.argtypes = [C.c_uint, C.c_uint, C.c_uint]
     lib.yvx_cuda_lse_exchange_counter_offset.restype = u64

@@ -219,6 +219,13 @@ int yvx_cuda_event_record(void *event, void *stream)
     return 0;
 }
 
+int yvx_cuda_stream_wait_event(void *stream, void *event)
+{
+    if (!event) return YVEX_ERR_INVALID_ARG;
+    YVX_CUDA_TRY(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+    return 0;
+}
+
 int yvx_cuda_event_elapsed_ms(void *start, void *stop, float *milliseconds)
 {
     YVX_CUDA_TRY(cudaEventSynchronize((cudaEvent_t)stop));

@@ -37,6 +37,9 @@ int yvx_cuda_stream_synchronize(void *stream);
 int yvx_cuda_event_create(void **event);
 int yvx_cuda_event_destroy(void *event);
 int yvx_cuda_event_record(void *event, void *stream);
+/* Work enqueued on `stream` after this call waits for the work `event` recorded (another
+ * stream's, as a rule). Inside a stream capture it forks / joins the captured graph. */
+int yvx_cuda_stream_wait_event(void *stream, void *event);
 int yvx_cuda_event_elapsed_ms(void *start, void *stop, float *milliseconds);
 /* Capture of the calls made on `stream` into a replayable graph (no reference entry
  * point of this name; the reference's operators are capture-aware, src/backend/cuda/
