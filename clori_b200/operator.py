@@ -276,6 +276,52 @@ class Backend:
             _raise(err)
         return rc, facts
 
+    def _latent_stage(self, function, request, fields, check):
+        """Fill a latent-stage request from keyword fields (Tensors become pointers) and call it.
+        Returns (rc, facts, failure, request)."""
+        for name, value in fields.items():
+            setattr(request, name, C.cast(value.ptr, C.c_void_p) if isinstance(value, Tensor) else value)
+        failure, facts, err = abi.AttentionFailure(), abi.OperationFacts(), abi.Error()
+        rc = function(self.handle, C.byref(request), C.byref(failure), C.byref(facts), C.byref(err))
+        if rc and check:
+            _raise(err)
+        return rc, facts, failure, request
+
+    def attention_publish(self, values, *, check=True, **fields):
+        """yvex_b200_attention_publish_execute over an F32 [rows, width] tensor in place. Fields as in
+        yvex_b200_attention_publish_request (rows_per_token, token_position, norm_mode, norm_weights,
+        rms_norm_epsilon, rope_dimension, rope_frequency, activation_*); rows / row_stride / width
+        default to the tensor's shape."""
+        fields = {"rows": values.shape[0], "row_stride": values.shape[1], "width": values.shape[1],
+                  "rows_per_token": 1, **fields}
+        return self._latent_stage(self.lib.yvex_b200_attention_publish_execute, abi.AttentionPublishRequest(),
+                                  {"values": values, **fields}, check)[:3]
+
+    def attention_activation(self, values, *, quantization, block_width, hadamard=False, count=None, check=True):
+        """yvex_b200_attention_activation_execute over the first `count` lanes of every row, in place."""
+        fields = {"values": values, "rows": values.shape[0], "row_stride": values.shape[1],
+                  "count": values.shape[1] if count is None else count, "quantization": quantization,
+                  "block_width": block_width, "hadamard": int(hadamard)}
+        return self._latent_stage(self.lib.yvex_b200_attention_activation_execute,
+                                  abi.AttentionActivationRequest(), fields, check)[:3]
+
+    def attention_compress(self, *, check=True, **fields):
+        """yvex_b200_attention_compress_execute; fields as in yvex_b200_attention_compress_request.
+        Returns (rc, facts, failure, emitted rows)."""
+        rc, facts, failure, request = self._latent_stage(self.lib.yvex_b200_attention_compress_execute,
+                                                         abi.AttentionCompressRequest(), fields, check)
+        return rc, facts, failure, int(request.emitted)
+
+    def attention_select(self, *, check=True, **fields):
+        """yvex_b200_attention_select_execute; fields as in yvex_b200_attention_select_request."""
+        return self._latent_stage(self.lib.yvex_b200_attention_select_execute, abi.AttentionSelectRequest(),
+                                  fields, check)[:3]
+
+    def attention_reduce(self, *, check=True, **fields):
+        """yvex_b200_attention_reduce_execute; fields as in yvex_b200_attention_reduce_request."""
+        return self._latent_stage(self.lib.yvex_b200_attention_reduce_execute, abi.AttentionReduceRequest(),
+                                  fields, check)[:3]
+
     # -- lifecycle -----------------------------------------------------------
     def bind_stream(self, stream, synchronous=True):
         err = abi.Error()

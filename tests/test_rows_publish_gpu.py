@@ -240,3 +240,37 @@ def test_chain_compressor_and_activation_inside_a_stream_capture(backend, oracle
     for a, b in zip(direct, replayed):
         assert same_bits(a, b)
     assert lib.yvx_cuda_graph_destroy(graph) == 0
+
+
+def test_python_stage_wrappers(backend, oracle):
+    """Backend.attention_publish / _activation / _compress: the operator entries behind keyword calls."""
+    from compressor_cases import build as build_compressor
+    from oracle.binding import compressor_initial_state
+    name, width, rpt, tokens, start, chain = CASES[2]
+    x, _ = build(15, width, rpt * tokens)
+    freq = oracle.rope_frequencies(PositionPolicy(*POLICY), 64)
+    t, f = backend.tensor("x", x), backend.tensor("f", freq, dtype=abi.DTYPE_F64)
+    rc, facts, failure = backend.attention_publish(
+        t, rows_per_token=rpt, token_position=start, rope_dimension=64, rope_frequency=f,
+        activation_quantization=4, activation_count=width, activation_block_width=32, activation_hadamard=1)
+    assert rc == 0 and facts.kernel_launches == 1
+    assert same_bits(t.read(), oracle.rows_publish(x, rpt, start, rope_frequency=freq, **chain))
+    y = backend.tensor("y", x)
+    rc, facts, failure = backend.attention_activation(y, quantization=8, block_width=64)
+    assert rc == 0 and same_bits(y.read(), oracle.activation_quant(x, 8, 64, 0))
+    rc, _, failure = backend.attention_activation(y, quantization=8, block_width=48, check=False)
+    assert rc == abi.YVEX_ERR_BOUNDS and failure.stage == b"activation"
+    ratio, hd = 4, 128
+    case = build_compressor(16, ratio, hd, 1, (9,))
+    kv0, score0 = compressor_initial_state(ratio, hd, 1)
+    ref = oracle.compressor_chunk(ratio, hd, 1, 0, case["token_kv"], case["token_score"], case["ape"], kv0, score0)
+    rows = backend.alloc("rows", abi.DTYPE_F32, (2, hd))
+    akv, asc = backend.alloc("akv", abi.DTYPE_F32, kv0.shape), backend.alloc("asc", abi.DTYPE_F32, kv0.shape)
+    rc, facts, failure, emitted = backend.attention_compress(
+        kind=2, attention_class=1, token_position=0, token_count=9, compression_ratio=ratio, head_dimension=hd,
+        token_kv=backend.tensor("kv", case["token_kv"]), token_score=backend.tensor("sc", case["token_score"]),
+        token_stride=2 * hd, position_rows=backend.tensor("ape", case["ape"]), state_kv=backend.tensor("skv", kv0),
+        state_score=backend.tensor("ssc", score0), next_state_kv=akv, next_state_score=asc, compressed=rows)
+    assert rc == 0 and emitted == 2
+    assert np.all(np.abs(rows.read() - ref[0]) <= 5e-7 * np.abs(ref[0]) + 1e-30)
+    assert same_bits(akv.read(), ref[2]) and same_bits(asc.read(), ref[3])
