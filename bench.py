@@ -44,6 +44,7 @@ LOW, HIGH, SEED = 512, 32768, 1
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.011
 METRIC = "decode_attention_tokens_per_s"
 UNIT = "tokens/s"
+SUSTAIN_SECONDS = 2.0          # length of the back-to-back run reported as "sustained"
 WORKLOAD = ("batched_decode_block_table: 64 sessions, ctx~U[512,32768] seed 1, 40q/8kv heads, "
             "hd128, bf16, 64-token blocks, 1 query token/session")
 
@@ -58,13 +59,15 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """Samples nvidia-smi clocks and throttle reasons (with timestamps) from before the first
+    timed region until after the last leg; `window` summarises the samples of one leg."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, device):
-        self.device, self.proc, self.path = device, None, None
+        self.device, self.proc, self.path, self.samples = device, None, None, None
 
     def start(self):
         try:
@@ -78,32 +81,53 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        """Ends the sampling and parses the samples: (epoch seconds, MHz, max MHz, watts, reasons)."""
+        self.samples = []
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        clocks, maxima, reasons = [], [], set()
+        import datetime
         with open(self.path) as f:
             for line in f:
                 parts = [p.strip() for p in line.split(",")]
                 if len(parts) < 9:
                     continue
                 try:
-                    clocks.append(float(parts[1]))
-                    maxima.append(float(parts[2]))
+                    stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    clock, maximum = float(parts[1]), float(parts[2])
                 except ValueError:
                     continue
-                for name, flag in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                       "sw_power_cap"), parts[5:9]):
-                    if flag.lower().startswith("active"):
-                        reasons.add(name)
+                try:
+                    watts = float(parts[3])
+                except ValueError:
+                    watts = None
+                active = [name for name, flag in zip(self.REASONS, parts[5:9]) if flag.lower().startswith("active")]
+                self.samples.append((stamp, clock, maximum, watts, active))
         os.unlink(self.path)
-        return {"sm_mhz": float(np.median(clocks)) if clocks else None,
-                "sm_max_mhz": max(maxima) if maxima else None,
-                "samples": len(clocks), "reasons": sorted(reasons)}
+
+    def window(self, begin=None, end=None):
+        """Median SM clock and the throttle reasons seen between two time.time() stamps (the
+        whole record without them). A leg shorter than the sampling period takes the samples
+        within 0.1 s of it."""
+        if self.samples is None:
+            self.stop()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
+        chosen = self.samples
+        if begin is not None:
+            chosen = [x for x in self.samples if begin - 0.1 <= x[0] <= end + 0.1]
+            if not chosen:
+                middle = 0.5 * (begin + end)
+                chosen = [min(self.samples, key=lambda x: abs(x[0] - middle))]
+        reasons = sorted({r for x in chosen for r in x[4]})
+        watts = [x[3] for x in chosen if x[3] is not None]
+        return {"sm_mhz": float(np.median([x[1] for x in chosen])), "sm_max_mhz": max(x[2] for x in chosen),
+                "samples": len(chosen), "reasons": reasons,
+                "power_w_max": max(watts) if watts else None}
 
 
 def algorithmic_bytes(lengths, out_bytes):
@@ -372,6 +396,8 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
                              ("v", v.value + last * kv_elems * 4, kv_elems), ("o", out.value, hq * hd)):
         host[name] = np.empty(count, np.float32)
         lib.yvx_cuda_download_async(host[name].ctypes.data, ptr, count * 4, backend.stream)
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
     lib.yvx_cuda_stream_synchronize(backend.stream)
     nbytes = 2 * kv_elems * 4 + 2 * hq * hd * 4
     result = {"workload": "decode 1x1 token, 32q/8kv heads, hd128, KV 4096, F32 (exact-F32 contract)",
@@ -381,7 +407,7 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
               "step_ms": _timed_launches.step_ms, "graph_step_ms": _timed_launches.graph_step_ms,
               "tokens_per_s": 1.0 / (_timed_launches.step_ms * 1e-3),
               "l2": f"{copies} rotating KV copies ({copies * 2 * kv_elems * 4 / 1e6:.0f} MB) exceed L2",
-              "chunk_tokens": problems[0].chunk_tokens}
+              "chunk_tokens": problems[0].chunk_tokens, "status_word": int(st[0])}
     for ptr in (k, v, q, out, status, scratch):
         lib.yvx_cuda_free(ptr)
     return result, host
@@ -451,14 +477,17 @@ def bench_verify_q8(lib, backend, abi, peak, repeats, chunk=None):
 
 def bench_prefill(lib, backend, abi, repeats, tokens=8192, batch=2):
     """Config 3: causal prefill, batch x tokens, 40/8 heads, hd 128, bf16 in and out.
-    Device-generated N(0, 0.5^2): RoPE is a rotation, so post-RoPE values of i.i.d.
-    normal inputs have the same distribution."""
+    Device-generated N(0, 0.5^2), Q and K rotated (theta 1e6, positions 0..tokens-1,
+    rotate-half over the full head width) before the bf16 rounding, V left as drawn."""
     hq, hkv, hd = 40, 8, 128
     qn, kn = batch * tokens * hq * hd, batch * tokens * hkv * hd
     q, k, v, out = _alloc(lib, qn * 2), _alloc(lib, kn * 2), _alloc(lib, kn * 2), _alloc(lib, qn * 2)
     status = _alloc(lib, 4)
-    for ptr, n, seed in ((q, qn, 301), (k, kn, 302), (v, kn, 303)):
-        lib.yvx_cuda_fill_normal(ptr, abi.DTYPE_BF16, n, seed, 0.5, backend.stream)
+    for ptr, heads, seed in ((q, hq, 301), (k, hkv, 302)):
+        rc = lib.yvx_cuda_fill_normal_rope_bf16(ptr, batch * tokens, tokens, heads, hd, seed, 0.5, 1.0e6,
+                                                backend.stream)
+        assert rc == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_fill_normal(v, abi.DTYPE_BF16, kn, 303, 0.5, backend.stream)
     lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
     p = abi.GqaProblem()
     p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = batch, tokens, hq, hkv, hd
@@ -476,6 +505,18 @@ def bench_prefill(lib, backend, abi, repeats, tokens=8192, batch=2):
     p.partials, p.status = scratch, status
     main, combine, launches = _timed_launches(lib, backend, [p], repeats)
     flops = 4.0 * batch * hq * hd * tokens * (tokens + 1) / 2.0
+    # sustained: launches back to back for about two seconds (power-capped clocks)
+    sustained_launches = max(int(2000.0 / max(main, 1e-3)), repeats) if tokens >= 8192 else repeats
+    first, last, ms, n = C.c_void_p(), C.c_void_p(), C.c_float(), C.c_uint()
+    lib.yvx_cuda_event_create(C.byref(first)); lib.yvx_cuda_event_create(C.byref(last))
+    lib.yvx_cuda_event_record(first, backend.stream)
+    for _ in range(sustained_launches):
+        assert lib.yvx_cuda_gqa_attention(C.byref(p), backend.stream, C.byref(n)) == 0
+    lib.yvx_cuda_event_record(last, backend.stream)
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+    sustained_ms = ms.value / sustained_launches
+    lib.yvx_cuda_event_destroy(first); lib.yvx_cuda_event_destroy(last)
     st = np.zeros(1, np.int32)
     lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
     # sample for the CPU check: batch 0, KV head 0, query head 0, the last 128 rows
@@ -490,15 +531,22 @@ def bench_prefill(lib, backend, abi, repeats, tokens=8192, batch=2):
     lib.yvx_cuda_download_async(v_host.ctypes.data, v, v_host.nbytes, backend.stream)
     lib.yvx_cuda_stream_synchronize(backend.stream)
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    tf_peak, tf_kind = 1590.0, "fallback"
+    tf_peak, tf_sustained_peak, tf_kind = 1590.0, 1400.0, "fallback"
     if os.path.exists(peaks_path):
         with open(peaks_path) as f:
-            tf_peak, tf_kind = float(json.load(f)["bf16_tflops"]), "measured"
+            peaks = json.load(f)
+        tf_peak, tf_kind = float(peaks["bf16_tflops"]), "measured"
+        tf_sustained_peak = float(peaks.get("bf16_tflops_sustained", tf_peak))
     achieved = flops / (main * 1e-3) / 1e12
     result = {"workload": f"causal prefill {batch} x {tokens} tokens, 40q/8kv heads, hd128, bf16",
               "kernel": "prefill_tcgen05_kernel", "launches_per_step": launches, "kernel_ms": main,
               "flops_causal": flops, "achieved_tflops": achieved, "peak_tflops": tf_peak,
               "peak_kind": tf_kind + " (burst, kernel timed alone)", "frac_of_bf16_peak": achieved / tf_peak,
+              "sustained_ms": sustained_ms, "sustained_launches": sustained_launches,
+              "sustained_tflops": flops / (sustained_ms * 1e-3) / 1e12,
+              "sustained_frac_of_burst_peak": flops / (sustained_ms * 1e-3) / 1e12 / tf_peak,
+              "sustained_frac_of_sustained_peak": flops / (sustained_ms * 1e-3) / 1e12 / tf_sustained_peak,
+              "peak_tflops_sustained": tf_sustained_peak,
               "tokens_per_s": batch * tokens / (main * 1e-3), "status_word": int(st[0]),
               "l2": "Q+K+V+O = %.0f MB exceed L2" % ((2 * qn + 2 * kn) * 2 / 1e6)}
     for ptr in (q, k, v, out, status, scratch):
@@ -1327,6 +1375,15 @@ def cpu_sample_run(engine, sample, threads):
     return time.perf_counter() - start, outs
 
 
+def cpu_sample_sessions(lengths):
+    """Eight sessions spread over the length distribution (every eighth by rank of length,
+    starting at the fourth shortest), so the sample's share of KV tokens is close to its
+    share of sessions; the CPU time is scaled to the whole batch by KV tokens either way."""
+    order = np.argsort(np.asarray(lengths), kind="stable")
+    step = max(len(order) // 8, 1)
+    return sorted(int(s) for s in order[step // 2::step][:8])
+
+
 def synth_host_sample(sample_ids, lengths, seed):
     """Host-generated inputs of the sampled sessions (reference arm: no GPU)."""
     rng = np.random.Generator(np.random.PCG64(seed + 5))
@@ -1348,17 +1405,19 @@ def run_reference(args, rank):
     engine, kind = cpu_engine()
     threads = os.cpu_count() or 1
     lengths = workloads.session_lengths(SEED, SESSIONS, LOW, HIGH)
-    sample_ids = list(range(0, SESSIONS, 8))
+    sample_ids = cpu_sample_sessions(lengths)
     sample = synth_host_sample(sample_ids, lengths, SEED)
     times = []
     for i in range(args.warmup + args.steps):
         seconds, _ = cpu_sample_run(engine, sample, threads)
         if i >= args.warmup:
             times.append(seconds)
-    per_step = float(np.mean(times))
-    value = len(sample_ids) / per_step
-    sample_text = (f"sessions {sample_ids} of {SESSIONS} ({int(lengths[sample_ids].sum())} of "
-                   f"{int(lengths.sum())} KV tokens) per step, F32 host arrays widened from bf16")
+    sample_tokens, total_tokens = int(lengths[sample_ids].sum()), int(lengths.sum())
+    # one step of the whole batch = the sample's time scaled by KV tokens (the work is linear in them)
+    per_step = float(np.mean(times)) * total_tokens / sample_tokens
+    value = SESSIONS / per_step
+    sample_text = (f"sessions {sample_ids} of {SESSIONS} ({sample_tokens} of {total_tokens} KV tokens) "
+                   "per step, F32 host arrays widened from bf16; time scaled to the whole batch by KV tokens")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
@@ -1452,6 +1511,7 @@ def main():
 
     w = Workload(local_rank, SEED + 1000 * rank if world > 1 else SEED)
     lib, b = w.lib, w.backend
+    legs = {}                      # leg name -> (time.time() at its start, at its end)
 
     # ---- device-resident throughput: operator call, asynchronous ----------
     b.bind_stream(None, synchronous=False)
@@ -1463,6 +1523,7 @@ def main():
     barrier()
     start, stop = w.event(), w.event()
     lib.yvx_cuda_stream_synchronize(b.stream)
+    leg_begin = time.time()
     w.record(start)
     launches = 0
     for _ in range(args.steps):
@@ -1470,8 +1531,21 @@ def main():
         launches += int(facts.kernel_launches)
     w.record(stop)
     b.sync()
+    legs["headline"] = (leg_begin, time.time())
     barrier()
     device_ms = max_over_ranks(w.elapsed_ms(start, stop))
+
+    # ---- the same step back to back for SUSTAIN_SECONDS (power-capped clocks) ----
+    sustained_steps = max(int(SUSTAIN_SECONDS * 1e3 / (device_ms / args.steps)), args.steps)
+    leg_begin = time.time()
+    w.record(start)
+    for _ in range(sustained_steps):
+        w.step()
+    w.record(stop)
+    b.sync()
+    legs["sustained"] = (leg_begin, time.time())
+    barrier()
+    sustained_ms = max_over_ranks(w.elapsed_ms(start, stop)) / sustained_steps
 
     # ---- end to end: host buffers, synchronous operator --------------------
     b.bind_stream(None, synchronous=True)
@@ -1479,6 +1553,7 @@ def main():
         w.step_e2e()
     barrier()
     lib.yvx_cuda_stream_synchronize(b.stream)
+    leg_begin = time.time()
     e2e_start = time.perf_counter()
     w.record(start)
     for _ in range(args.steps):
@@ -1486,35 +1561,51 @@ def main():
     w.record(stop)
     lib.yvx_cuda_stream_synchronize(b.stream)
     e2e_wall_ms = (time.perf_counter() - e2e_start) * 1e3
+    legs["e2e"] = (leg_begin, time.time())
     e2e_ms = max_over_ranks(max(w.elapsed_ms(start, stop), e2e_wall_ms))
     barrier()
 
     # ---- the attention kernel alone ----------------------------------------
+    leg_begin = time.time()
     kernel_ms, combine_ms, (chunk, splits) = w.kernel_ms(min(max(args.steps, 10), 100), args.chunk)
-    clocks = sampler.stop()
+    legs["kernel"] = (leg_begin, time.time())
     sharded = None
     if world > 1 and not args.headline_only:
         import torch
         # The kernels and the NCCL all-gather must be ordered on ONE stream: a torch
         # side stream (the legacy default stream has no handle to bind).
         side = torch.cuda.Stream()
+        leg_begin = time.time()
         with torch.cuda.stream(side):
             b.bind_stream(side.cuda_stream, synchronous=False)
             sharded = bench_verify_q8_sharded(lib, b, w.abi, rank, world, dist, torch, 20)
         side.synchronize()
+        legs["cfg4_sharded"] = (leg_begin, time.time())
         b.bind_stream(None, synchronous=True)
     others, other_samples = {}, {}
     if world == 1 and not args.headline_only:
         hbm_peak = measured_peaks()[0]
-        others["decode_f32_config1"], other_samples["f32"] = bench_decode_f32(lib, b, w.abi, hbm_peak, 64)
-        others["verify_q8_config4_1gpu"], other_samples["q8"] = bench_verify_q8(lib, b, w.abi, hbm_peak, 20)
-        others["prefill_config3"], other_samples["prefill"] = bench_prefill(lib, b, w.abi, 10)
-        others["latent_decode_config5"], other_samples["mla"] = bench_mla(lib, b, w.abi, hbm_peak, 10)
-        others["kv_append_rotary"], _ = bench_kv_append(lib, b, w.abi, hbm_peak, 10)
-        others["latent_sparse_decode"], _ = bench_latent_sparse(lib, b, w.abi, 20)
-        others["rolling_compressor"], _ = bench_compressor(lib, b, w.abi, hbm_peak, 10)
-        others["activation_quant"], _ = bench_activation(lib, b, w.abi, hbm_peak, 5)
-        others["rows_publish"], _ = bench_publish(lib, b, w.abi, hbm_peak, 5)
+        plan = (("decode_f32_config1", "f32", lambda: bench_decode_f32(lib, b, w.abi, hbm_peak, 64)),
+                ("verify_q8_config4_1gpu", "q8", lambda: bench_verify_q8(lib, b, w.abi, hbm_peak, 20)),
+                ("prefill_config3", "prefill", lambda: bench_prefill(lib, b, w.abi, 10)),
+                ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 10)),
+                ("kv_append_rotary", None, lambda: bench_kv_append(lib, b, w.abi, hbm_peak, 10)),
+                ("latent_sparse_decode", None, lambda: bench_latent_sparse(lib, b, w.abi, 20)),
+                ("rolling_compressor", None, lambda: bench_compressor(lib, b, w.abi, hbm_peak, 10)),
+                ("activation_quant", None, lambda: bench_activation(lib, b, w.abi, hbm_peak, 5)),
+                ("rows_publish", None, lambda: bench_publish(lib, b, w.abi, hbm_peak, 5)))
+        for name, sample_key, run in plan:
+            leg_begin = time.time()
+            others[name], sample = run()
+            legs[name] = (leg_begin, time.time())
+            if sample_key:
+                other_samples[sample_key] = sample
+    sampler.stop()
+    clocks = sampler.window(*legs["headline"])
+    for name, result in others.items():
+        result["clocks"] = {k: v for k, v in sampler.window(*legs[name]).items() if k != "sm_max_mhz"}
+    if sharded:
+        sharded["clocks"] = sampler.window(*legs["cfg4_sharded"])
 
     if rank != 0:
         if dist is not None:
@@ -1535,9 +1626,13 @@ def main():
                    "kv_tokens_total": int(w.lengths.sum()), "chunk_tokens": chunk,
                    "max_splits": splits, "sharding": "sessions per rank, no collective"},
         "hbm_gbs_whole_step": w.bytes / (ms_per_step * 1e-3) / 1e9,
+        "sustained": {"value": tokens / (sustained_ms * 1e-3), "unit": UNIT, "ms_per_step": sustained_ms,
+                      "steps": sustained_steps, "seconds": sustained_ms * sustained_steps * 1e-3,
+                      "hbm_gbs_whole_step": w.bytes / (sustained_ms * 1e-3) / 1e9,
+                      "clocks": sampler.window(*legs["sustained"])},
         "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms / args.steps},
+                "ms_per_step": e2e_ms / args.steps, "clocks": sampler.window(*legs["e2e"])},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -1545,14 +1640,17 @@ def main():
                      "traffic_source": "ncu dram read+write of a reduced launch (8 sessions), "
                                        "scaled by KV tokens: 1.011 x algorithmic bytes",
                      "peak_kind": peak_kind,
+                     "peak_note": "the peak is a read+write copy (half reads, half writes); a kernel "
+                                  "that almost only reads can exceed it",
                      "kernel": "gqa split attention (combine excluded)",
                      "kernel_ms": kernel_ms, "combine_ms": combine_ms,
-                     "algorithmic_bytes": w.bytes, "frac_of_8000_spec": achieved / 8000.0},
+                     "algorithmic_bytes": w.bytes, "frac_of_8000_spec": achieved / 8000.0,
+                     "clocks": sampler.window(*legs["kernel"])},
     }
     if world == 1 and not args.no_cpu:
         engine, kind = cpu_engine()
         threads = os.cpu_count() or 1
-        sample_ids = list(range(0, SESSIONS, 8))
+        sample_ids = cpu_sample_sessions(w.lengths)
         sample = [w.host_session(s) for s in sample_ids]
         best, outs = None, None
         for _ in range(3):
@@ -1560,12 +1658,15 @@ def main():
             best = seconds if best is None else min(best, seconds)
         gpu = w.cl.bf16_bits_to_f32(w.out.read())
         worst = max(float(np.abs(gpu[s, 0] - o[0]).max()) for s, o in zip(sample_ids, outs))
+        sample_tokens, total_tokens = int(w.lengths[sample_ids].sum()), int(w.lengths.sum())
+        whole_job_seconds = best * total_tokens / sample_tokens
         line["cpu_baseline"] = {
-            "value": len(sample_ids) / best, "unit": UNIT, "cores": threads, "kind": kind,
+            "value": SESSIONS / whole_job_seconds, "unit": UNIT, "cores": threads, "kind": kind,
             "sample": f"sessions {sample_ids} of {SESSIONS} "
-                      f"({int(w.lengths[sample_ids].sum())} of {int(w.lengths.sum())} KV tokens), "
-                      "best of 3 passes, KV copied back from the device and widened to F32",
-            "seconds": best, "gpu_vs_cpu_max_abs_on_sample": worst}
+                      f"({sample_tokens} of {total_tokens} KV tokens), best of 3 passes, KV copied back "
+                      "from the device and widened to F32; time scaled to the whole batch by KV tokens",
+            "seconds": best, "whole_job_seconds_by_tokens": whole_job_seconds,
+            "gpu_vs_cpu_max_abs_on_sample": worst}
         if "f32" in other_samples:
             err, seconds = check_decode_f32(engine, other_samples["f32"], threads)
             others["decode_f32_config1"].update(gpu_vs_cpu_max_abs=err, cpu_ms=seconds * 1e3, cpu_cores=threads)
@@ -1583,14 +1684,54 @@ def main():
             err, seconds = check_mla(other_samples["mla"])
             others["latent_decode_config5"].update(
                 gpu_vs_cpu_max_abs_on_sample=err, cpu_sample_ms=seconds * 1e3, cpu_cores=1,
-                cpu_sample="session 0, heads 0..7 (CPU restatement; no reference counterpart)")
+                cpu_sample="session 0, heads 0..7 (CPU restatement, pinned to the reference's reduce)")
     if sharded:
         others["verify_q8_config4_sharded"] = sharded
     if others:
         line["other_workloads"] = others
+    # Last and compact, so a reader that keeps only the end of the line still has every
+    # configuration: [kernel ms, fraction of the binding measured peak, median SM MHz, max-abs vs CPU].
+    line["summary"] = summary_of(line, others)
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def _r(x, digits=4):
+    return None if x is None else float(f"{x:.{digits}g}")
+
+
+def summary_of(line, others):
+    out = {"cfg2": {"ms": _r(line["roofline"]["kernel_ms"]), "hbm": _r(line["roofline"]["frac"], 3),
+                    "burst_tok_s": _r(line["value"]), "sustained_tok_s": _r(line["sustained"]["value"]),
+                    "e2e_tok_s": _r(line["e2e"]["value"]), "mhz": line["clocks"]["sm_mhz"],
+                    "err": _r(line.get("cpu_baseline", {}).get("gpu_vs_cpu_max_abs_on_sample"), 2)}}
+    short = (("cfg1", "decode_f32_config1", "frac_of_measured_hbm", "hbm", "gpu_vs_cpu_max_abs"),
+             ("cfg4", "verify_q8_config4_1gpu", "frac_of_measured_hbm", "hbm", "gpu_vs_cpu_max_abs_on_sample"),
+             ("cfg3", "prefill_config3", "frac_of_bf16_peak", "tc", "gpu_vs_cpu_max_abs_on_sample"),
+             ("cfg5", "latent_decode_config5", "frac_of_measured_hbm", "hbm", "gpu_vs_cpu_max_abs_on_sample"))
+    for tag, name, frac_key, frac_tag, err_key in short:
+        r = others.get(name)
+        if not r:
+            continue
+        entry = {"ms": _r(r["kernel_ms"]), frac_tag: _r(r[frac_key], 3), "mhz": r.get("clocks", {}).get("sm_mhz"),
+                 "err": _r(r.get(err_key), 2)}
+        if "graph_step_ms" in r:
+            entry["graph_ms"] = _r(r["graph_step_ms"])
+        if tag == "cfg3":
+            entry["tflops"] = _r(r["achieved_tflops"])
+            if "sustained_tflops" in r:
+                entry["sustained_tflops"] = _r(r["sustained_tflops"])
+        if tag == "cfg5":
+            entry["tc"] = _r(r["frac_of_bf16_peak"], 3)
+            entry["step_ms"] = _r(r["absorb_ms"] + r["kernel_ms"] + r["combine_ms"])
+        out[tag] = entry
+    sharded = others.get("verify_q8_config4_sharded")
+    if sharded:
+        out["cfg4_sharded"] = {k: _r(v) if isinstance(v, float) else v for k, v in sharded.items()
+                               if k in ("ranks", "nccl_step_us", "fused_step_us", "one_launch_step_us",
+                                        "single_gpu_step_us", "max_abs_vs_nccl_path")}
+    return out
 
 
 if __name__ == "__main__":

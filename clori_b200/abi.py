@@ -319,7 +319,7 @@ class KvAppendArgs(C.Structure):
         ("key_pool", C.c_void_p), ("value_pool", C.c_void_p), ("block_table", C.c_void_p),
         ("block_tokens", C.c_uint), ("block_table_stride", C.c_uint), ("pool_blocks", C.c_uint),
         ("pool_token_stride", u64), ("pool_head_stride", u64), ("pool_block_stride", u64),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("row_capacity", C.c_uint),
     ]
 
 
@@ -366,7 +366,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_malloc", "yvx_cuda_free", "yvx_cuda_host_alloc", "yvx_cuda_host_free",
     "yvx_cuda_memset_async", "yvx_cuda_upload_async", "yvx_cuda_download_async",
     "yvx_cuda_copy_async", "yvx_cuda_stream_create", "yvx_cuda_stream_destroy",
-    "yvx_cuda_stream_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
+    "yvx_cuda_stream_synchronize", "yvx_cuda_device_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_stream_wait_event", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
     "yvx_cuda_lse_exchange_bytes", "yvx_cuda_lse_exchange_counter_offset", "yvx_cuda_gqa_attention_exchange",
     "yvx_cuda_lse_exchange_emulated", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
@@ -374,7 +374,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
     "yvx_cuda_gqa_attention_profiled",
-    "yvx_cuda_fill_normal", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
+    "yvx_cuda_fill_normal", "yvx_cuda_fill_normal_rope_bf16", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
     "yvx_cuda_gqa_static_scratch_capacity", "yvx_cuda_gqa_attention_static_scratch",
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
     "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
@@ -504,6 +504,7 @@ def load():
     lib.yvx_cuda_gqa_attention.argtypes = [P(GqaProblem), vp, P(C.c_uint)]
     lib.yvx_cuda_gqa_attention_profiled.argtypes = [P(GqaProblem), vp, vp * 3, P(C.c_uint)]
     lib.yvx_cuda_fill_normal.argtypes = [vp, C.c_int, u64, u64, C.c_float, vp]
+    lib.yvx_cuda_fill_normal_rope_bf16.argtypes = [vp, u64, C.c_uint, C.c_uint, C.c_uint, u64, C.c_float, C.c_double, vp]
     lib.yvx_cuda_fill_q8_lanes.argtypes = [vp, u64, u64, vp]
     lib.yvx_cuda_fill_f16_uniform.argtypes = [vp, u64, u64, C.c_float, C.c_float, vp]
     lib.yvx_cuda_gqa_static_scratch_capacity.restype = u64

@@ -17,6 +17,7 @@
 // Maps a CUDA runtime error to the yvex_status the reference reports for
 // launch and copy failures (YVEX_ERR_BACKEND) and remembers the text.
 int yvx_cuda_check(cudaError_t error, const char *what);
+void yvx_cuda_set_error_text(const char *text);
 
 #define YVX_CUDA_TRY(call)                                 \
     do {                                                   \
@@ -70,6 +71,24 @@ __device__ __forceinline__ unsigned short bf16_bits_rne(float value)
         return (unsigned short)(high | 0x0040u);
     if (low > 0x8000u || (low == 0x8000u && (high & 1u))) high += 1u;
     return (unsigned short)high;
+}
+
+// A session's length as the kernels use it. Lengths live in device memory, where the
+// host cannot check them; the host admitted `maximum` (it sized the split scratch, the
+// block-table row and the tensor maps for it). A stored length beyond it (a negative
+// value read as unsigned included) is a contract failure: it is recorded in the status
+// word and the session is treated as empty, so that no row, table entry or partial
+// outside the admitted range is ever addressed.
+__device__ __forceinline__ unsigned int admitted_kv_tokens(const unsigned int *lengths, unsigned int b,
+                                                           unsigned int uniform, unsigned int maximum,
+                                                           int *status)
+{
+    const unsigned int n = lengths ? lengths[b] : uniform;
+    if (n > maximum) {
+        atomicCAS(status, 0, YVX_STATUS_CONTRACT);
+        return 0u;
+    }
+    return n;
 }
 
 __device__ __forceinline__ void store_output(void *base, int dtype, unsigned long long index,

@@ -83,7 +83,7 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
     const unsigned int group = p.query_heads / p.kv_heads;
     const unsigned int vectors = p.query_rows * group;
     const unsigned int split = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
-    const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     long long query_start;
     if (p.query_start)
         query_start = (long long)p.query_start[b];

@@ -44,7 +44,7 @@ struct DecodeSession {
 __device__ __forceinline__ DecodeSession decode_session(const yvx_gqa_problem &p, unsigned int b)
 {
     DecodeSession s;
-    s.kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    s.kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     long long start;
     if (p.query_start)
         start = (long long)p.query_start[b];

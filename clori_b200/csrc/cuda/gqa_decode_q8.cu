@@ -42,7 +42,7 @@ struct Q8Session {
 __device__ __forceinline__ Q8Session q8_session(const yvx_gqa_problem &p, unsigned int b)
 {
     Q8Session s;
-    s.kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    s.kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     long long start;
     if (p.query_start)
         start = (long long)p.query_start[b];

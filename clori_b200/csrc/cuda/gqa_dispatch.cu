@@ -77,6 +77,16 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
         p->query_heads % p->kv_heads || !p->head_dim || !p->chunk_tokens || !p->max_splits ||
         (p->max_splits > 1u && !p->partials) || (p->block_table && !p->block_tokens))
         return YVEX_ERR_INVALID_ARG;
+    // Launch limits, refused with a typed error before anything is enqueued: sessions ride in
+    // grid.z and the decode kernels' (kv head, row tile) pairs in grid.y, both at most 65535.
+    {
+        const unsigned long long decode_vectors = (unsigned long long)p->query_rows * (p->query_heads / p->kv_heads);
+        if (p->sessions > 65535u || p->max_splits > 0x7fffffffu ||
+            (decode_vectors <= 64ull && (unsigned long long)p->kv_heads * ((decode_vectors + 15ull) / 16ull) > 65535ull)) {
+            yvx_cuda_set_error_text("the attention grid exceeds the launch limits (65535 sessions, 65535 (kv head, row tile) pairs)");
+            return YVEX_ERR_BOUNDS;
+        }
+    }
     cudaStream_t s = (cudaStream_t)stream;
     if (events) cudaEventRecord(events[0], s);
     // Specialised kernels return 1 when they took the problem, 0 when its shape

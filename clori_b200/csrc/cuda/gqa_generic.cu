@@ -33,7 +33,7 @@ struct SessionView {
 __device__ __forceinline__ SessionView session_view(const yvx_gqa_problem &p, unsigned int b)
 {
     SessionView s;
-    s.kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    s.kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     long long start;
     if (p.query_start)
         start = (long long)p.query_start[b];
@@ -73,7 +73,8 @@ __device__ __forceinline__ const KT *kv_row(const void *base, const yvx_gqa_prob
     return reinterpret_cast<const KT *>(base) + offset + (unsigned long long)kv_head * head_stride;
 }
 
-// grid: x = split, y = kv_head * vector_tiles + tile, z = session.
+// grid: x = (kv_head * vector_tiles + tile) * max_splits + split, z = session (a prefill-sized
+// call has more (head, tile) pairs than grid.y admits, so they share x with the splits).
 // A "vector" is one (query row, query head of the group) pair; a CTA carries
 // VT of them so each KV row it loads serves VT dot products.
 template <typename QT, typename KT, int SLOTS, int VT>
@@ -89,8 +90,9 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
     const unsigned int group = p.query_heads / p.kv_heads;
     const unsigned int vectors = p.query_rows * group;
     const unsigned int tiles = (vectors + VT - 1) / VT;
-    const unsigned int kv_head = blockIdx.y / tiles, tile = blockIdx.y % tiles;
-    const unsigned int b = blockIdx.z, split = blockIdx.x;
+    const unsigned int head_tile = blockIdx.x / p.max_splits, split = blockIdx.x % p.max_splits;
+    const unsigned int kv_head = head_tile / tiles, tile = head_tile % tiles;
+    const unsigned int b = blockIdx.z;
     const unsigned int hd = p.head_dim;
     const SessionView s = session_view(p, b);
 
@@ -257,7 +259,8 @@ gqa_combine_kernel(const yvx_gqa_problem p)
     const unsigned int b = (unsigned int)(item / ((unsigned long long)p.query_rows * p.query_heads));
     const unsigned int hd = p.head_dim;
     const SessionView s = session_view(p, b);
-    const unsigned int splits = (s.kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens;
+    // never more parts than the scratch holds per item, whatever the stored length says
+    const unsigned int splits = min((s.kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens, p.max_splits);
     combine_parts(p.partials + item * p.max_splits * (hd + 2ull), splits, hd + 2u, hd, p.output,
                   p.output_dtype, item * hd,
                   p.partial_output ? p.partial_output + item * (hd + 2ull) : nullptr, p.status);
@@ -335,13 +338,18 @@ static int launch_generic(const yvx_gqa_problem &p, cudaStream_t stream)
 {
     const unsigned int group = p.query_heads / p.kv_heads;
     const unsigned int vectors = p.query_rows * group;
-    if (vectors <= 4u) {
-        const dim3 grid(p.max_splits, p.kv_heads * ((vectors + 3u) / 4u), p.sessions);
-        gqa_split_generic_kernel<QT, KT, SLOTS, 4><<<grid, kGenericThreads, 0, stream>>>(p);
-    } else {
-        const dim3 grid(p.max_splits, p.kv_heads * ((vectors + 7u) / 8u), p.sessions);
-        gqa_split_generic_kernel<QT, KT, SLOTS, 8><<<grid, kGenericThreads, 0, stream>>>(p);
+    const unsigned int per_cta = vectors <= 4u ? 4u : 8u;
+    const unsigned long long ctas =
+        (unsigned long long)p.kv_heads * ((vectors + per_cta - 1u) / per_cta) * p.max_splits;
+    if (ctas > 0x7fffffffull || p.sessions > 65535u) {
+        yvx_cuda_set_error_text("the attention grid exceeds the launch limits (2^31-1 CTAs per session, 65535 sessions)");
+        return YVEX_ERR_BOUNDS;
     }
+    const dim3 grid((unsigned int)ctas, 1, p.sessions);
+    if (per_cta == 4u)
+        gqa_split_generic_kernel<QT, KT, SLOTS, 4><<<grid, kGenericThreads, 0, stream>>>(p);
+    else
+        gqa_split_generic_kernel<QT, KT, SLOTS, 8><<<grid, kGenericThreads, 0, stream>>>(p);
     return yvx_cuda_check(cudaGetLastError(), "gqa_split_generic_kernel");
 }
 

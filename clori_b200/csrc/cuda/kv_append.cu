@@ -38,6 +38,18 @@ __device__ __forceinline__ void rotate_pair(float first, float second, float cos
     }
 }
 
+// Rows a session can hold: the caller's row_capacity, and never more than its block-table row
+// addresses.
+__device__ __forceinline__ unsigned long long append_row_capacity(const yvx_kv_append_args &a)
+{
+    unsigned long long capacity = a.row_capacity ? a.row_capacity : ~0ull;
+    if (a.key_pool) {
+        const unsigned long long table_rows = (unsigned long long)a.block_table_stride * a.block_tokens;
+        capacity = table_rows < capacity ? table_rows : capacity;
+    }
+    return capacity;
+}
+
 // grid: x = token, y = session; one CTA moves the whole new row of a session:
 // query heads in place, then key heads and value heads into the history.
 template <bool STAGED>
@@ -49,6 +61,15 @@ kv_append_rotary_kernel(const yvx_kv_append_args a)
     const unsigned long long vector = (unsigned long long)b * a.tokens + token;
     const float *cosines = a.cosines + vector * a.rotary_dim;
     const float *sines = a.sines + vector * a.rotary_dim;
+    // The row this CTA appends. Stored lengths live in device memory; a row at or beyond the
+    // capacity the caller admitted (a negative length read as unsigned included) would land in
+    // another session's rows or table entries: recorded as a contract failure, nothing written.
+    const unsigned long long row =
+        (unsigned long long)(a.kv_tokens ? (unsigned int)a.kv_tokens[b] : a.kv_tokens_uniform) + token;
+    if (row >= append_row_capacity(a)) {
+        if (threadIdx.x == 0) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
+        return;
+    }
     if (a.query) {
         float *q = a.query + vector * a.query_heads * hd;
         for (unsigned int i = threadIdx.x; i < a.query_heads * half; i += kAppendThreads) {
@@ -60,8 +81,6 @@ kv_append_rotary_kernel(const yvx_kv_append_args a)
             v[half + lane] = second;
         }
     }
-    const unsigned long long row =
-        (unsigned long long)(a.kv_tokens ? (unsigned int)a.kv_tokens[b] : a.kv_tokens_uniform) + token;
     // destination A: F32 state row, K heads then V heads
     float *state = nullptr;
     if (a.state_values)
@@ -125,6 +144,15 @@ kv_append_rotary_vec4_kernel(const yvx_kv_append_args a)
         rotate_pair<STAGED>(x.z, y.z, c.z, s.z, first.z, second.z);
         rotate_pair<STAGED>(x.w, y.w, c.w, s.w, first.w, second.w);
     };
+    // The row this CTA appends. Stored lengths live in device memory; a row at or beyond the
+    // capacity the caller admitted (a negative length read as unsigned included) would land in
+    // another session's rows or table entries: recorded as a contract failure, nothing written.
+    const unsigned long long row =
+        (unsigned long long)(a.kv_tokens ? (unsigned int)a.kv_tokens[b] : a.kv_tokens_uniform) + token;
+    if (row >= append_row_capacity(a)) {
+        if (threadIdx.x == 0) atomicCAS(a.status, 0, YVX_STATUS_CONTRACT);
+        return;
+    }
     if (a.query) {
         float *q = a.query + vector * a.query_heads * hd;
         for (unsigned int i = threadIdx.x; i < a.query_heads * quads; i += kAppendThreads) {
@@ -137,8 +165,6 @@ kv_append_rotary_vec4_kernel(const yvx_kv_append_args a)
             *hi = second;
         }
     }
-    const unsigned long long row =
-        (unsigned long long)(a.kv_tokens ? (unsigned int)a.kv_tokens[b] : a.kv_tokens_uniform) + token;
     float *state = nullptr;
     if (a.state_values)
         state = a.state_values + (unsigned long long)b * a.state_session_stride + row * a.state_row_stride;

@@ -41,8 +41,8 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
     // 1. this rank's row
     if (p.max_splits > 1u && !emulated) {
         const unsigned int b = (unsigned int)(item / ((unsigned long long)p.query_rows * p.query_heads));
-        const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
-        const unsigned int splits = (kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens;
+        const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
+        const unsigned int splits = min((kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens, p.max_splits);
         combine_parts(p.partials + (unsigned long long)item * p.max_splits * stride, splits, stride, hd, nullptr,
                       0, 0ull, row, p.status);
     } else {

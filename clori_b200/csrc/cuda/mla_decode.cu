@@ -163,7 +163,7 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int half = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
-    const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     const unsigned int t0 = split * p.chunk_tokens;
     const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
     const unsigned long long part_stride = kMlaHalf + 2;

@@ -97,7 +97,7 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
     const unsigned int qhead = (blockIdx.x % lanes_of_work) % p.query_heads;
     const unsigned int b = (blockIdx.x % lanes_of_work) / p.query_heads;
     const unsigned int kv_head = qhead / (p.query_heads / p.kv_heads);
-    const unsigned int kv_tokens = p.kv_tokens ? p.kv_tokens[b] : p.kv_tokens_uniform;
+    const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     const long long query_start =
         p.query_start ? (long long)p.query_start[b]
                       : (p.query_start_from_end ? (long long)kv_tokens - (long long)p.query_rows

@@ -14,9 +14,21 @@ int yvx_cuda_check(cudaError_t error, const char *what)
     return error == cudaErrorMemoryAllocation ? YVEX_ERR_NOMEM : YVEX_ERR_BACKEND;
 }
 
+// Records a refusal that no CUDA call made (a shape beyond a launch limit, a full scratch).
+void yvx_cuda_set_error_text(const char *text)
+{
+    snprintf(yvx_error_text, sizeof(yvx_error_text), "%s", text ? text : "");
+}
+
 extern "C" {
 
 const char *yvx_cuda_last_error_text(void) { return yvx_error_text; }
+
+int yvx_cuda_device_synchronize(void)
+{
+    YVX_CUDA_TRY(cudaDeviceSynchronize());
+    return 0;
+}
 
 int yvx_cuda_device_count(int *count)
 {

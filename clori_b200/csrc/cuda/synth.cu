@@ -153,3 +153,58 @@ extern "C" int yvx_cuda_fill_q8_records(void *records, unsigned long long record
         (unsigned char *)records, record_count, seed, lo, hi);
     return yvx_cuda_check(cudaGetLastError(), "fill_q8_records_kernel");
 }
+
+namespace yvx {
+
+__device__ __forceinline__ float normal_element(unsigned long long seed, unsigned long long e, float sigma)
+{
+    const uint64_t h = splitmix64(seed * 0xD1342543DE82EF95ull + (e >> 1));
+    const float u1 = ((float)(uint32_t)(h >> 32) + 1.0f) * (1.0f / 4294967296.0f);
+    const float u2 = (float)(uint32_t)h * (1.0f / 4294967296.0f);
+    const float radius = sqrtf(-2.0f * logf(u1)) * sigma;
+    float s, c;
+    sincospif(2.0f * u2, &s, &c);
+    return (e & 1ull) ? radius * s : radius * c;
+}
+
+// The values fill_normal_kernel would write as F32, rotated before the bf16 rounding:
+// rotate-half over the full head width, pairs (lane, lane + dim/2), frequency
+// theta^(-2*pair/dim), cosine and sine tables rounded to bf16 (the convention of the
+// reference's rotary tables, src/runtime/decoder.c:1080-1094). Rows are
+// [session][token][head][dim]; the position of a row is its token index.
+__global__ void fill_normal_rope_kernel(unsigned short *dst, unsigned long long rows,
+                                        unsigned int tokens, unsigned int heads, unsigned int dim,
+                                        unsigned long long seed, float sigma, double theta)
+{
+    const unsigned int half = dim / 2u;
+    const unsigned long long pairs = rows * heads * half;
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < pairs;
+         i += stride) {
+        const unsigned int pair = (unsigned int)(i % half);
+        const unsigned long long vector = i / half;           // row * heads + head
+        const unsigned long long row = vector / heads;
+        const unsigned int position = (unsigned int)(row % tokens);
+        const unsigned long long lo_index = vector * dim + pair, hi_index = lo_index + half;
+        const float lo = normal_element(seed, lo_index, sigma), hi = normal_element(seed, hi_index, sigma);
+        const double angle = (double)position * pow(theta, -2.0 * (double)pair / (double)dim);
+        const float c = __uint_as_float((uint32_t)bf16_bits_rne((float)cos(angle)) << 16);
+        const float sn = __uint_as_float((uint32_t)bf16_bits_rne((float)sin(angle)) << 16);
+        dst[lo_index] = bf16_bits_rne(__fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn)));
+        dst[hi_index] = bf16_bits_rne(__fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, sn)));
+    }
+}
+
+}  // namespace yvx
+
+extern "C" int yvx_cuda_fill_normal_rope_bf16(void *dst, unsigned long long rows, unsigned int tokens,
+                                              unsigned int heads, unsigned int dim,
+                                              unsigned long long seed, float sigma, double theta,
+                                              void *stream)
+{
+    if (!dst || !rows || !tokens || !heads || !dim || (dim & 1u) || !(theta > 1.0))
+        return YVEX_ERR_INVALID_ARG;
+    yvx::fill_normal_rope_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(
+        (unsigned short *)dst, rows, tokens, heads, dim, seed, sigma, theta);
+    return yvx_cuda_check(cudaGetLastError(), "fill_normal_rope_kernel");
+}

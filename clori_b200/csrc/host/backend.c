@@ -148,8 +148,9 @@ int yvx_backend_scratch(yvex_backend *backend, unsigned long long bytes, void **
     if (!bytes) return YVEX_OK;
     if (bytes > backend->scratch_bytes) {
         unsigned long long grown = bytes + bytes / 4ull;
-        /* The old arena may still be read by enqueued work. */
-        rc = yvx_cuda_stream_synchronize(backend->stream);
+        /* The old arena may still be read by work enqueued on this stream or on one bound
+         * earlier (bind_stream): wait for the whole device before releasing it. */
+        rc = yvx_cuda_device_synchronize();
         if (rc == 0) rc = yvx_cuda_free(backend->scratch);
         backend->scratch = NULL;
         backend->scratch_bytes = 0ull;
@@ -216,6 +217,16 @@ int yvx_backend_status_collect(yvex_backend *backend, yvex_backend_operation_fac
     }
     if (*backend->status_host == 1)
         return yvx_fail(err, YVEX_ERR_FORMAT, where, "attention produced a non-finite value");
+    if (*backend->status_host == 3) {
+        /* A bounded device-side wait gave up: a copy that never landed, or a peer that never
+         * wrote its rows. Unlike a bad block table this is the device (or a peer) not answering,
+         * so it is a backend failure and sticky, as the reference treats a failed synchronisation
+         * (src/backend/cuda/capability.c:757-817). After an exchange timeout the arrival counters
+         * are out of step with the epoch: the exchange area must be zeroed before it is reused. */
+        backend->failed = 1;
+        return yvx_fail(err, YVEX_ERR_BACKEND, where,
+                        "a bounded device-side wait timed out (a copy or a peer never arrived)");
+    }
     if (*backend->status_host != 0)
         return yvx_fail(err, YVEX_ERR_FORMAT, where, "attention kernel reported a contract failure");
     yvex_error_clear(err);

@@ -38,6 +38,7 @@ yvex_b200_kv_pool *yvex_b200_kv_pool_create(unsigned int blocks, unsigned int bl
 {
     yvex_b200_kv_pool *pool;
     unsigned int i;
+    size_t cell;
     if (!blocks || !block_tokens || !max_sessions || !max_blocks_per_session || blocks > 0x7fffffffu) return NULL;
     pool = (yvex_b200_kv_pool *)calloc(1, sizeof(*pool));
     if (!pool) return NULL;
@@ -58,7 +59,7 @@ yvex_b200_kv_pool *yvex_b200_kv_pool_create(unsigned int blocks, unsigned int bl
     /* block 0 is handed out first: the stack holds blocks-1 .. 0 */
     for (i = 0; i < blocks; ++i) pool->free_list[i] = blocks - 1u - i;
     pool->free_count = blocks;
-    for (i = 0; i < max_sessions * max_blocks_per_session; ++i) pool->table[i] = -1;
+    for (cell = 0; cell < (size_t)max_sessions * max_blocks_per_session; ++cell) pool->table[cell] = -1;
     return pool;
 }
 
@@ -160,6 +161,9 @@ int yvex_b200_kv_pool_reserve(yvex_b200_kv_pool *pool, unsigned int session, uns
         release_block(pool, row[j]);
         row[j] = -1;
     }
+    /* the candidates are gone whatever follows: a refusal below must not leave a reserved
+     * range whose table entries were just released */
+    pool->reserved[session] = first;
     first_block = (unsigned int)(first / pool->block_tokens);
     fresh = need - have;
     if (first % pool->block_tokens && pool->refcount[row[first_block]] > 1u) fresh += 1u;

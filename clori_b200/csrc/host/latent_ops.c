@@ -741,6 +741,8 @@ int yvex_b200_kv_append_rotary_execute(yvex_backend *backend, const yvex_b200_kv
     a.kv_tokens_uniform = (unsigned int)r->max_kv_tokens;
     a.token_position = r->token_position ? (const unsigned long long *)r->token_position->data : NULL;
     a.status = backend->status_device;
+    if (r->state_values)
+        a.row_capacity = r->state_capacity > 0xffffffffull ? 0xffffffffu : (unsigned int)r->state_capacity;
     rc = yvx_backend_status_arm(backend, where, err);
     if (rc != YVEX_OK) return rc;
     rc = yvx_cuda_kv_append_rotary(&a, backend->stream);

@@ -51,6 +51,9 @@ int yvx_cuda_graph_capture_end(void *stream, void **executable);
 int yvx_cuda_graph_launch(void *executable, void *stream);
 int yvx_cuda_graph_destroy(void *executable);
 const char *yvx_cuda_last_error_text(void);
+/* Waits for every stream of the current device (used before an arena that enqueued work on
+ * any stream may still read is released). */
+int yvx_cuda_device_synchronize(void);
 
 /* ---- grouped-query attention over a KV cache ------------------------------
  * Replaces the launch of yvex_gqa_f32 / yvex_gqa_wide_f32
@@ -451,6 +454,10 @@ typedef struct yvx_kv_append_args {
     unsigned int block_tokens, block_table_stride, pool_blocks;
     unsigned long long pool_token_stride, pool_head_stride, pool_block_stride;
     int *status;
+    /* Rows a session's state bank can hold (0: unbounded). A row at or beyond it, or beyond
+     * block_table_stride * block_tokens for the pools, is refused on the device: status 2,
+     * nothing of that row written. */
+    unsigned int row_capacity;
 } yvx_kv_append_args;
 int yvx_cuda_kv_append_rotary(const yvx_kv_append_args *args, void *stream);
 
@@ -519,6 +526,13 @@ int yvx_cuda_q8_kv_pack(const void *k_rows, const void *v_rows, unsigned int tok
  * [-127, 127], f16 values uniform in [lo, hi). */
 int yvx_cuda_fill_normal(void *dst, int dtype, unsigned long long count,
                          unsigned long long seed, float sigma, void *stream);
+/* The F32 values yvx_cuda_fill_normal draws for the same seed, rotated before the bf16
+ * rounding: rows [session][token][head][dim], position = token index, rotate-half pairs
+ * (lane, lane + dim/2), frequency theta^(-2 pair/dim), cosine / sine rounded to bf16 (the
+ * convention of the reference's rotary tables, src/runtime/decoder.c:1080-1094). */
+int yvx_cuda_fill_normal_rope_bf16(void *dst, unsigned long long rows, unsigned int tokens,
+                                   unsigned int heads, unsigned int dim, unsigned long long seed,
+                                   float sigma, double theta, void *stream);
 int yvx_cuda_fill_q8_lanes(void *dst, unsigned long long count, unsigned long long seed,
                            void *stream);
 int yvx_cuda_fill_f16_uniform(void *dst, unsigned long long count, unsigned long long seed,

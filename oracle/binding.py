@@ -140,11 +140,23 @@ def _activation_call(function, rows, quantization, block_width, hadamard):
     return out
 
 
-def build_oracle(reference_tree="/root/reference"):
+def reference_tree():
+    """Where the reference's sources lie: the YVEX_REFERENCE_TREE environment variable,
+    else a checkout named `reference` beside this repository; None when neither exists."""
+    candidates = [os.environ.get("YVEX_REFERENCE_TREE"),
+                  os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for tree in candidates:
+        if tree and os.path.isdir(os.path.join(tree, "src", "backend")):
+            return tree
+    return None
+
+
+def build_oracle(tree=None):
     """Compile the restatement, and the reference build when its tree exists."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
-    if os.path.isdir(os.path.join(reference_tree, "src", "backend")):
-        subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={reference_tree}"], check=True)
+    reference_tree_path = tree or reference_tree()
+    if reference_tree_path:
+        subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={reference_tree_path}"], check=True)
 
 
 class _Gqa:
@@ -419,21 +431,26 @@ class Oracle(_Gqa):
         """Fake quantisation of every row of a float32 [rows, count] array -> new array, or None."""
         return _activation_call(self.lib.yvx_oracle_activation_quant, rows, quantization, block_width, hadamard)
 
-    def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale):
+    def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale, with_absorbed=False):
         """bf16 bit arrays: q_nope [H,dn], q_rope [H,dr], w_uk [H,dn,dc],
-        latent [L,dc], rope_key [L,dr] -> float32 [H,dc]."""
+        latent [L,dc], rope_key [L,dr] -> float32 [H,dc]; with_absorbed also returns the
+        absorbed query float32 [H,dc] (bf16-valued)."""
         heads, nope = q_nope.shape
         context, dc = latent.shape
         dr = q_rope.shape[1]
         out = np.zeros((heads, dc), np.float32)
+        absorbed = np.zeros((heads, dc), np.float32) if with_absorbed else None
         ok = self.lib.yvx_oracle_mla_decode(
             np.ascontiguousarray(q_nope, np.uint16).reshape(-1),
             np.ascontiguousarray(q_rope, np.uint16).reshape(-1),
             np.ascontiguousarray(w_uk, np.uint16).reshape(-1),
             np.ascontiguousarray(latent, np.uint16).reshape(-1),
             np.ascontiguousarray(rope_key, np.uint16).reshape(-1),
-            out.reshape(-1), heads, nope, dc, dr, context, float(scale), None)
-        return out if ok else None
+            out.reshape(-1), heads, nope, dc, dr, context, float(scale),
+            absorbed.ctypes.data if absorbed is not None else None)
+        if not ok:
+            return None
+        return (out, absorbed) if absorbed is not None else out
 
 
 class Reference(_Gqa):
@@ -481,6 +498,45 @@ class Reference(_Gqa):
             counts, positions.reshape(-1))
         return (out, counts, positions) if ok == 1 else None
 
+
+    def mla_decode_embedded(self, q_absorbed, q_rope, latent, rope_key, softmax_dim=192):
+        """The split-rope latent decode of one session computed by the reference's own
+        yvex_attention_reduce_chunk (src/graph/core.c:608-701). The decode is a shared-row
+        K == V attention in disguise: history rows are [latent | rope_key] (width dc + dr),
+        the query of a head is [absorbed query | rope query], every row is visible (window
+        class, window wider than the history, one new token at the last position) and the
+        sinks sit at -100 as tests/unit/deepseek_attention.c:593 has them, which leaves no
+        sink mass in single precision. The reference fixes the softmax scale at
+        1/sqrt(row width); sqrt(row width / softmax_dim) is folded into the query. The
+        reference's inverse output rotation touches only the trailing dr lanes, which are
+        dropped: the first dc lanes are the bf16-published mix of latent rows.
+
+        q_absorbed float32 [H, dc] (bf16-valued), q_rope / latent / rope_key float32
+        -> float32 [H, dc], or None when the reference refuses."""
+        from clori_b200 import abi
+        heads, dc = q_absorbed.shape
+        context, dr = rope_key.shape
+        width = dc + dr
+        rows = np.ascontiguousarray(np.concatenate([latent, rope_key], axis=1), np.float32)
+        fold = np.float32(np.sqrt(float(width) / float(softmax_dim)))
+        query = np.ascontiguousarray(
+            (np.concatenate([q_absorbed, q_rope], axis=1).astype(np.float32) * fold).reshape(1, heads * width))
+        positions = np.arange(context, dtype=np.uint64)
+        sinks = np.full(heads, -100.0, np.float32)
+        nothing_u64, nothing_f32 = np.zeros(1, np.uint64), np.zeros(width, np.float32)
+        a = abi.LatentReduceArgs()
+        a.query, a.local, a.local_positions = query.ctypes.data, rows.ctypes.data, positions.ctypes.data
+        a.initial_local_count, a.local_stride = context - 1, width
+        a.compressed, a.compressed_positions, a.compressed_stride = nothing_f32.ctypes.data, nothing_u64.ctypes.data, width
+        a.selected, a.selected_count, a.topk_capacity = nothing_u64.ctypes.data, nothing_u64.ctypes.data, 1
+        a.sinks, a.query_heads, a.head_dim = sinks.ctypes.data, heads, width
+        a.sliding_window, a.ratio, a.attention_class = context + 1, 0, 0
+        a.phase_start_position, a.token_count, a.candidate_block_visible = context - 1, 1, 0
+        a.rope_dims = dr
+        result = self.latent_reduce_chunk(a, 0, PositionPolicy(10000, 0, 0, 0, 0), None, 1, heads, width)
+        if result is None:
+            return None
+        return np.ascontiguousarray(result[0].reshape(heads, width)[:, :dc])
 
     def compressor_chunk(self, kind, ratio, head_dim, overlap, start, token_kv, token_score, ape,
                          state_kv, state_score, norm_weights=None, epsilon=1e-6, rope_dims=0, policy=None):

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 
 def append(backend, q, k, v, cos, sin, heads, kv_heads, hd, rotary, staged, kv_tokens=None, uniform=0,
-           state=None, positions=None, token_position=None, pools=None):
+           state=None, positions=None, token_position=None, pools=None, row_capacity=0):
     """q/k/v [sessions, tokens, heads*hd] float32. Returns dict of device results."""
     sessions, tokens = k.shape[0], k.shape[1]
     t = dict(k=backend.tensor("k", k), v=backend.tensor("v", v), cos=backend.tensor("cos", cos),
@@ -51,6 +51,7 @@ def append(backend, q, k, v, cos, sin, heads, kv_heads, hd, rotary, staged, kv_t
         a.block_tokens, a.block_table_stride, a.pool_blocks = block_tokens, table.shape[1], kp.shape[0]
         a.pool_token_stride, a.pool_head_stride, a.pool_block_stride = kv_heads * hd, hd, block_tokens * kv_heads * hd
     a.status = t["status"].data_ptr
+    a.row_capacity = row_capacity
     rc = backend.lib.yvx_cuda_kv_append_rotary(C.byref(a), backend.stream)
     assert rc == 0, backend.lib.yvx_cuda_last_error_text()
     assert backend.lib.yvx_cuda_stream_synchronize(backend.stream) == 0

@@ -96,6 +96,28 @@ def test_exhaustion_and_bad_arguments(pool):
     assert not lib.yvex_b200_kv_pool_create(0, 4, 1, 1)
 
 
+def test_refused_reserve_forgets_the_candidates_it_released(pool):
+    # A reserve that runs out of blocks has already released the session's old candidate
+    # blocks; the reserved range must go with them, or a later commit would accept rows
+    # whose table entries are -1.
+    lib, h = pool
+    a, b, copy = C.c_uint(), C.c_uint(), abi.KvCopy()
+    assert lib.yvex_b200_kv_pool_session_open(h, C.byref(a)) == OK
+    assert lib.yvex_b200_kv_pool_session_open(h, C.byref(b)) == OK
+    assert lib.yvex_b200_kv_pool_reserve(h, a.value, 16, C.byref(copy)) == OK      # 4 of 8 blocks
+    assert lib.yvex_b200_kv_pool_commit(h, a.value, 16) == OK
+    assert lib.yvex_b200_kv_pool_reserve(h, b.value, 8, C.byref(copy)) == OK       # 2 candidate blocks
+    free_before = lib.yvex_b200_kv_pool_free_blocks(h)
+    assert lib.yvex_b200_kv_pool_session_open(h, C.byref(C.c_uint())) == OK
+    assert lib.yvex_b200_kv_pool_reserve(h, 2, 8, C.byref(copy)) == OK             # takes the last 2 blocks
+    assert lib.yvex_b200_kv_pool_free_blocks(h) == free_before - 2 == 0
+    assert lib.yvex_b200_kv_pool_reserve(h, b.value, 16, C.byref(copy)) == NOMEM   # old candidates released, 4 needed
+    assert lib.yvex_b200_kv_pool_commit(h, b.value, 1) == BOUNDS                   # nothing is reserved any more
+    assert lib.yvex_b200_kv_pool_committed(h, b.value) == 0
+    assert lib.yvex_b200_kv_pool_reserve(h, b.value, 8, C.byref(copy)) == OK       # the released blocks serve again
+    assert lib.yvex_b200_kv_pool_commit(h, b.value, 8) == OK
+
+
 def test_random_walk_keeps_every_row_addressable_and_counts_balanced(library):
     lib = library
     rng = np.random.default_rng(5)

@@ -32,7 +32,15 @@ def _case(backend, seed, lengths, rows, hq, hkv):
                 k_outer_stride=cap * width, v_outer_stride=cap * width, kv_max=cap)
 
 
-def test_static_scratch_entry_equals_the_regular_entry_twice_in_a_row(backend):
+def _oracle_session(oracle, case, host, s):
+    """CPU attention of session s of a case over its first lengths[s] rows."""
+    f = clori_b200.bf16_bits_to_f32
+    n = case["lengths"][s]
+    return oracle.gqa_attention(f(host["q"][s]), f(host["k"][s, :n]), f(host["v"][s, :n]), n - case["rows"],
+                                case["hq"], case["hkv"], HD, threads=4)
+
+
+def test_static_scratch_entry_equals_the_regular_entry_twice_in_a_row(backend, oracle):
     # Two different problems back to back through the shared array: the second
     # call sees the first call's bytes in the scratch and must not be affected.
     first = _case(backend, 1, [4096, 700, 65, 3000], 1, 40, 8)
@@ -47,6 +55,12 @@ def test_static_scratch_entry_equals_the_regular_entry_twice_in_a_row(backend):
         # inside the 2e-3 max-abs tolerance the bf16 parity tests use.
         assert np.abs(got - want).max() <= 2e-3
         assert np.array_equal(got, want)
+        # and against the CPU attention itself (bf16 operands: 2e-3 max-abs), on the two
+        # shortest sessions of the case
+        host = {name: case[name].read() for name in ("q", "k", "v")}
+        for s in np.argsort(case["lengths"])[:2]:
+            ref = _oracle_session(oracle, case, host, int(s))
+            assert np.abs(got[s] - ref).max() <= 2e-3
 
 
 def test_static_scratch_entry_refuses_problems_beyond_its_capacity(backend):
