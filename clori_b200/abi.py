@@ -37,7 +37,7 @@ NUMERIC_BF16_F32_ACCUMULATE = 2
 NUMERIC_Q8_0_KV_F32_ACCUMULATE = 3
 BACKEND_KIND_CPU, BACKEND_KIND_CUDA = 0, 1
 KV_CONTIGUOUS, KV_BLOCK_TABLE = 0, 1
-MAX_DIMS = 8
+MAX_DIMS = 4
 u64 = C.c_ulonglong
 
 
@@ -336,9 +336,145 @@ class MlaProblem(C.Structure):
         ("status", C.c_void_p),
     ]
 
+# ---- the encoded attention job (include/yvex_b200/attention_job.h) -----------------------
+ATTENTION_JOB_SCHEMA = 3
+(WEIGHT_Q_A, WEIGHT_Q_A_NORM, WEIGHT_Q_B, WEIGHT_KV, WEIGHT_KV_NORM, WEIGHT_SINKS, WEIGHT_OUT_A, WEIGHT_OUT_B,
+ WEIGHT_MAIN_KV, WEIGHT_MAIN_GATE, WEIGHT_MAIN_APE, WEIGHT_MAIN_NORM, WEIGHT_INDEX_KV, WEIGHT_INDEX_GATE,
+ WEIGHT_INDEX_APE, WEIGHT_INDEX_NORM, WEIGHT_INDEX_Q, WEIGHT_INDEX_PROJECTION, WEIGHT_MHC_FUNCTION,
+ WEIGHT_MHC_BASE, WEIGHT_MHC_SCALE, WEIGHT_INPUT_NORM, WEIGHT_COUNT) = range(23)
+QTYPE_F32, QTYPE_F16, QTYPE_Q8_0, QTYPE_BF16 = 0, 1, 8, 30
+ATTENTION_SWA, ATTENTION_CSA, ATTENTION_HCA = 0, 1, 2
+ATTENTION_COMPUTE_BF16_F32_RNE_V1 = 1
+ATTENTION_SCOPE_CORE, ATTENTION_SCOPE_ENVELOPE = 0, 1
+ATTENTION_PHASE_PREFILL, ATTENTION_PHASE_DECODE = 0, 1
+(JOB_FAILURE_NONE, JOB_FAILURE_INVALID_ARGUMENT, JOB_FAILURE_CAPABILITY, JOB_FAILURE_BUDGET,
+ JOB_FAILURE_ALLOCATION, JOB_FAILURE_COPY, JOB_FAILURE_LAUNCH, JOB_FAILURE_SYNCHRONIZE, JOB_FAILURE_NUMERIC,
+ JOB_FAILURE_CANCELLED, JOB_FAILURE_CLEANUP) = range(11)
+(VARIANT_TENSOR_ALLOC, VARIANT_TENSOR_ZERO, VARIANT_TENSOR_WRITE, VARIANT_TENSOR_READ, VARIANT_TENSOR_COPY,
+ VARIANT_EMBED_F32_TO_F32, VARIANT_EMBED_F16_TO_F32, VARIANT_RMS_NORM_F32_WEIGHT_F32,
+ VARIANT_RMS_NORM_F32_WEIGHT_F16, VARIANT_ROPE_F32, VARIANT_MATMUL_F32, VARIANT_MLP_DENSE_F32,
+ VARIANT_MLP_ROUTED_F32, VARIANT_ATTENTION_CAUSAL_F32, VARIANT_ATTENTION_NONCAUSAL_F32, VARIANT_QTYPE_ROW_DOT,
+ VARIANT_ATTENTION_ENCODED, VARIANT_COUNT) = range(18)
+CAPABILITY_UNSUPPORTED, CAPABILITY_SUPPORTED, CAPABILITY_FAILED = 0, 1, 2
+CANCELLED_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
+
+
+class JobWeight(C.Structure):
+    _fields_ = [("encoded", C.c_void_p), ("encoded_bytes", C.c_size_t), ("row_bytes", u64), ("row_width", u64),
+                ("row_count", u64), ("qtype", C.c_uint), ("present", C.c_int)]
+
+
+class JobPosition(C.Structure):
+    _fields_ = [(n, u64) for n in ("theta", "scaling_factor", "original_context", "beta_fast", "beta_slow",
+                                   "rope_dimensions")]
+
+
+class JobActivation(C.Structure):
+    _fields_ = [("required", C.c_int), ("block_width", u64), ("quantization", C.c_uint), ("hadamard", C.c_int)]
+
+
+class JobCancellation(C.Structure):
+    _fields_ = [("requested", CANCELLED_FN), ("context", C.c_void_p)]
+
+
+class FloatSpan(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("capacity", u64)]
+
+
+class U64Span(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("capacity", u64)]
+
+
+class JobRolling(C.Structure):
+    _fields_ = [("present", C.c_int), ("overlap", C.c_int), ("next_token_position", u64), ("ratio", u64),
+                ("head_dimension", u64), ("state_width", u64), ("state_slots", u64), ("cursor", u64),
+                ("previous_fill", u64), ("current_fill", u64), ("kv_state", C.c_void_p), ("score_state", C.c_void_p),
+                ("kv_state_capacity", u64), ("score_state_capacity", u64)]
+
+
+class AttentionJob(C.Structure):
+    _fields_ = [
+        ("schema", C.c_uint), ("phase", C.c_int), ("attention_class", C.c_int), ("compute_contract", C.c_int),
+        ("operation_scope", C.c_int),
+        ("token_position", u64), ("token_count", u64), ("input_stride", u64),
+        ("hidden_width", u64), ("q_rank", u64), ("query_heads", u64), ("head_dimension", u64), ("kv_width", u64),
+        ("sliding_window", u64), ("compression_ratio", u64),
+        ("output_groups", u64), ("output_group_input_width", u64), ("output_rank", u64),
+        ("indexer_heads", u64), ("indexer_head_dimension", u64), ("indexer_topk", u64),
+        ("residual_stream_count", u64), ("residual_stream_width", u64), ("residual_expanded_width", u64),
+        ("mhc_mixing_rows", u64), ("mhc_sinkhorn_iterations", u64),
+        ("rms_epsilon", C.c_double), ("mhc_epsilon", C.c_double), ("mhc_residual_post_multiplier", C.c_double),
+        ("position", JobPosition),
+        ("attention_kv_activation", JobActivation), ("compressor_activation", JobActivation),
+        ("compressor_rotated_activation", JobActivation), ("indexer_query_activation", JobActivation),
+        ("weights", JobWeight * WEIGHT_COUNT),
+        ("input", C.c_void_p), ("local_kv", C.c_void_p), ("compressed_kv", C.c_void_p), ("indexer_kv", C.c_void_p),
+        ("device_input", C.POINTER(DeviceTensor)), ("device_output", C.POINTER(DeviceTensor)),
+        ("local_positions", C.c_void_p), ("compressed_positions", C.c_void_p), ("indexer_positions", C.c_void_p),
+        ("local_count", u64), ("local_stride", u64), ("compressed_count", u64), ("compressed_stride", u64),
+        ("indexer_count", u64), ("indexer_stride", u64),
+        ("main_rolling", JobRolling), ("indexer_rolling", JobRolling),
+        ("cancellation", C.POINTER(JobCancellation)), ("device_completion", C.c_void_p),
+        ("evidence_level", C.c_uint), ("measure_device_time", C.c_int),
+        ("candidate_block_visible", C.c_int), ("retain_prefix_checkpoints", C.c_int), ("native_execution", C.c_int),
+        ("max_host_bytes", u64), ("max_device_bytes", u64),
+    ]
+
+
+class AttentionJobOutput(C.Structure):
+    _fields_ = (
+        [(n, FloatSpan) for n in ("core_input", "q_low", "query", "raw_kv", "compressed_kv", "indexer_kv",
+                                  "index_query", "index_weights", "attention_values", "output", "envelope_output")] +
+        [(n, U64Span) for n in ("compressed_positions", "indexer_positions", "topk_positions", "topk_counts",
+                                "valid_candidate_counts")] +
+        [(n, FloatSpan) for n in ("main_kv_state", "main_score_state", "indexer_kv_state", "indexer_score_state")] +
+        [(n, u64) for n in ("tokens_executed", "compressed_count", "indexer_count", "topk_count",
+                            "valid_candidate_count", "host_bytes", "peak_host_bytes", "device_bytes",
+                            "peak_device_bytes", "kernel_launches", "accelerated_matrix_launches", "h2d_bytes",
+                            "d2h_bytes", "d2d_bytes", "device_state_staged_bytes", "queue_synchronizations",
+                            "device_synchronizations", "device_execution_elapsed_ns", "host_workspace_capacity",
+                            "host_workspace_used", "host_workspace_peak", "host_workspace_allocation_count")] +
+        [("host_workspace_reused", C.c_int), ("device_state_staged", C.c_int)])
+
+
+class AttentionJobFailure(C.Structure):
+    _fields_ = [("code", C.c_int), ("stage", C.c_char_p), ("expected", u64), ("actual", u64)]
+
+
+class CompletionTransfer(C.Structure):
+    _fields_ = [("output", C.c_void_p), ("staged", C.c_void_p), ("capacity", u64), ("output_capacity", u64),
+                ("used", u64), ("width", C.c_size_t), ("stage", C.c_char_p)]
+
+
+class AttentionCompletion(C.Structure):
+    _fields_ = [("defer", C.c_int), ("stack_start", C.c_int), ("pending", C.c_int), ("barrier_observed", C.c_int),
+                ("output", AttentionJobOutput), ("failure", AttentionJobFailure), ("host_status", C.c_void_p),
+                ("host_selected_counts", C.c_void_p), ("host_candidate_counts", C.c_void_p),
+                ("attention_class", C.c_uint), ("token_count", u64), ("indexer_topk", u64),
+                ("candidate_capacity", u64), ("transfer_count", C.c_uint), ("transfers", CompletionTransfer * 20)]
+
+
+class CapabilityResult(C.Structure):
+    _fields_ = [("backend_kind", C.c_int), ("variant", C.c_int), ("state", C.c_int), ("reason", C.c_int),
+                ("input_dtype", C.c_int), ("weight_dtype", C.c_int), ("output_dtype", C.c_int),
+                ("context_available", C.c_int), ("kernel_bundle_available", C.c_int),
+                ("function_available", C.c_int)]
+
+
+class MatvecArgs(C.Structure):
+    """yvx_matvec_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [("weights", C.c_void_p), ("qtype", C.c_uint), ("first_row", u64), ("rows", u64), ("width", u64),
+                ("row_bytes", u64), ("input", C.c_void_p), ("tokens", u64), ("input_stride", u64),
+                ("output", C.c_void_p), ("output_stride", u64), ("groups", u64), ("round_bf16", C.c_int),
+                ("status", C.c_void_p)]
+
 
 # Every symbol the headers declare; tests check the library exports each one.
 EXPORTED_SYMBOLS = [
+    # attention_job.h
+    "yvex_backend_attention_execute", "yvex_backend_attention_complete", "yvex_backend_query_capability",
+    "yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
+    "yvex_backend_capability_reason_name",
     # attention.h
     "yvex_error_clear", "yvex_error_set", "yvex_status_name",
     "yvex_backend_open", "yvex_backend_close_checked", "yvex_backend_close",
@@ -379,6 +515,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
     "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
     "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
+    "yvx_cuda_qtype_row_bytes", "yvx_cuda_qtype_matvec", "yvx_cuda_qtype_decode_rows", "yvx_cuda_round_bf16_rows",
     "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk", "yvx_cuda_activation_quant", "yvx_cuda_rows_publish", "yvx_cuda_rows_publish_batch",
 ]
 
@@ -434,6 +571,19 @@ def load():
     lib.yvex_b200_attention_compress_execute.argtypes = [
         vp, P(AttentionCompressRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
     lib.yvx_cuda_compressor_chunk.argtypes = [P(CompressorArgs), vp, P(u64)]
+    lib.yvex_backend_attention_execute.argtypes = [vp, P(AttentionJob), P(AttentionJobOutput),
+                                                   P(AttentionJobFailure), P(Error)]
+    lib.yvex_backend_attention_complete.argtypes = [vp, P(AttentionCompletion), C.c_int, P(Error)]
+    lib.yvex_backend_query_capability.argtypes = [vp, C.c_int, P(CapabilityResult), P(Error)]
+    for name in ("yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
+                 "yvex_backend_capability_reason_name"):
+        getattr(lib, name).restype = C.c_char_p
+        getattr(lib, name).argtypes = [C.c_int]
+    lib.yvx_cuda_qtype_row_bytes.restype = u64
+    lib.yvx_cuda_qtype_row_bytes.argtypes = [C.c_uint, u64]
+    lib.yvx_cuda_qtype_matvec.argtypes = [P(MatvecArgs), vp]
+    lib.yvx_cuda_qtype_decode_rows.argtypes = [vp, C.c_uint, u64, u64, u64, vp, vp, vp]
+    lib.yvx_cuda_round_bf16_rows.argtypes = [vp, u64, u64, u64, vp, vp]
     lib.yvex_b200_attention_activation_execute.argtypes = [
         vp, P(AttentionActivationRequest), P(AttentionFailure), P(OperationFacts), P(Error)]
     lib.yvx_cuda_activation_quant.argtypes = [P(ActivationArgs), vp]

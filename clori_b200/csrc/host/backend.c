@@ -16,7 +16,10 @@ int yvex_backend_cuda_available(void)
 
 int yvx_backend_device_fail(yvex_backend *backend, int rc, const char *where, yvex_error *err)
 {
-    if (backend && rc == YVEX_ERR_BACKEND) backend->failed = 1;
+    if (backend && rc == YVEX_ERR_BACKEND) {
+        backend->failed = 1;
+        if (!backend->failure_reason) backend->failure_reason = 8; /* launch failed */
+    }
     yvex_error_set(err, (yvex_status)rc, where, yvx_cuda_last_error_text());
     return rc;
 }
@@ -98,6 +101,11 @@ int yvex_backend_close_checked(yvex_backend **handle, yvex_error *err)
     yvx_cuda_device_select(backend->device);
     yvx_cuda_stream_synchronize(backend->stream);
     yvx_cuda_free(backend->scratch);
+    {
+        unsigned int i;
+        for (i = 0; i < backend->weight_count; ++i) yvx_cuda_free(backend->weights[i].device);
+        free(backend->weights);
+    }
     yvx_cuda_free(backend->status_device);
     yvx_cuda_host_free(backend->status_host);
     yvx_cuda_stream_destroy(backend->own_stream);
@@ -177,6 +185,7 @@ static int injected_failure(const char *variable, const char *where)
 static int inject(yvex_backend *backend, const char *what, const char *where, yvex_error *err)
 {
     backend->failed = 1;
+    backend->failure_reason = strstr(what, "launch") ? 8 : 9;
     yvex_error_set(err, YVEX_ERR_BACKEND, where, what);
     return YVEX_ERR_BACKEND;
 }
@@ -209,7 +218,10 @@ int yvx_backend_status_collect(yvex_backend *backend, yvex_backend_operation_fac
                                  backend->stream);
     if (rc == 0) rc = yvx_cuda_stream_synchronize(backend->stream);
     backend->status_pending = 0;
-    if (rc != 0) return yvx_backend_device_fail(backend, rc, where, err);
+    if (rc != 0) {
+        if (rc == YVEX_ERR_BACKEND) backend->failure_reason = 9; /* synchronisation failed */
+        return yvx_backend_device_fail(backend, rc, where, err);
+    }
     if (facts) {
         facts->d2h_bytes += sizeof(int);
         facts->download_count += 1ull;
@@ -224,6 +236,7 @@ int yvx_backend_status_collect(yvex_backend *backend, yvex_backend_operation_fac
          * (src/backend/cuda/capability.c:757-817). After an exchange timeout the arrival counters
          * are out of step with the epoch: the exchange area must be zeroed before it is reused. */
         backend->failed = 1;
+        backend->failure_reason = 9; /* synchronisation failed */
         return yvx_fail(err, YVEX_ERR_BACKEND, where,
                         "a bounded device-side wait timed out (a copy or a peer never arrived)");
     }

@@ -25,6 +25,18 @@ struct yvex_backend {
     int *status_device; /* device status word the kernels publish into */
     int *status_host;   /* pinned mirror */
     int status_pending; /* an asynchronous operator has not been checked yet */
+    /* why `failed` was set, in the capability vocabulary (yvex_backend_capability_reason):
+     * 8 a launch failed, 9 a synchronisation failed or a bounded device wait ran out */
+    int failure_reason;
+    /* Encoded weights of the attention job, uploaded on first use and kept until close:
+     * the reference resolves weights to resident device memory by their host address
+     * (src/backend/cuda/attention.c:560-580); the artifact bytes behind it are immutable. */
+    struct yvx_resident_weight {
+        const void *host;
+        unsigned long long bytes;
+        void *device;
+    } *weights;
+    unsigned int weight_count, weight_capacity;
 };
 
 static inline int yvx_u64_add(unsigned long long a, unsigned long long b,

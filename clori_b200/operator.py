@@ -137,6 +137,9 @@ class Backend:
         desc = abi.TensorDesc()
         desc.name = name.encode()
         desc.dtype = dtype
+        shape = tuple(int(d) for d in shape)
+        if len(shape) > abi.MAX_DIMS:  # the ABI holds four dims: fold the leading ones
+            shape = (int(np.prod(shape[:len(shape) - abi.MAX_DIMS + 1])),) + shape[len(shape) - abi.MAX_DIMS + 1:]
         desc.rank = len(shape)
         for i, d in enumerate(shape):
             desc.dims[i] = int(d)

@@ -52,7 +52,7 @@ typedef enum {
     YVEX_DTYPE_Q8_0 = 13
 } yvex_dtype;
 
-#define YVEX_TENSOR_MAX_DIMS 8
+#define YVEX_TENSOR_MAX_DIMS 4u /* include/yvex/model.h:85 */
 
 typedef struct yvex_backend yvex_backend;
 

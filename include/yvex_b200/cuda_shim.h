@@ -417,6 +417,45 @@ int yvx_cuda_rows_publish(const yvx_rows_publish_args *args, void *stream);
  * row and its index queries); each set as in yvx_cuda_rows_publish, results identical. */
 int yvx_cuda_rows_publish_batch(const yvx_rows_publish_args *sets, unsigned int count, void *stream);
 
+/* ---- projections of the encoded attention operator ---------------------------------
+ * Encoded weight rows times activation rows. Replaces, for the admitted encodings, the
+ * reference's yvex_qtype_matvec / yvex_qtype_grouped_rows launches
+ * (src/backend/cuda/kernels.cu:436-866) as src/backend/cuda/attention.c:1162-1236 and
+ * :1424-1451 use them; CPU twin yvex_attention_dot_batch (src/graph/core.c:1107-1215):
+ * every lane decoded to float, products and sum in double, narrowed to float, and with
+ * round_bf16 published as bf16 (nearest even). qtype: the GGUF type ids of the reference
+ * (include/yvex/qtype.h:20-50); F32, F16, BF16 and Q8_0 are admitted, every other id is
+ * YVEX_ERR_UNSUPPORTED. output[t][g * rows + r] = weights row (first_row + g * rows + r)
+ * . input[t][g * width .. (g + 1) * width); groups 0 or 1 is the plain product.
+ * status: 1 when a result is not finite. */
+#define YVX_QTYPE_F32 0u
+#define YVX_QTYPE_F16 1u
+#define YVX_QTYPE_Q8_0 8u
+#define YVX_QTYPE_BF16 30u
+typedef struct yvx_matvec_args {
+    const void *weights;                      /* encoded rows, row_bytes apart */
+    unsigned int qtype;
+    unsigned long long first_row, rows, width, row_bytes;
+    const float *input;                       /* [tokens][input_stride] */
+    unsigned long long tokens, input_stride;
+    float *output;                            /* [tokens][output_stride] */
+    unsigned long long output_stride;
+    unsigned long long groups;
+    int round_bf16;
+    int *status;
+} yvx_matvec_args;
+unsigned long long yvx_cuda_qtype_row_bytes(unsigned int qtype, unsigned long long width);
+int yvx_cuda_qtype_matvec(const yvx_matvec_args *args, void *stream);
+/* Encoded rows [first_row, first_row + rows) decoded to F32 [rows][width] (norm weights,
+ * sinks, position biases: yvex_attention_decode_row, src/graph/core.c:1029-1105). */
+int yvx_cuda_qtype_decode_rows(const void *weights, unsigned int qtype, unsigned long long first_row,
+                               unsigned long long rows, unsigned long long width, float *out, int *status,
+                               void *stream);
+/* bf16 publication in place of the first `width` lanes of F32 rows (yvex_attention_compute_round,
+ * src/graph/numeric.c:614-628). status: 1 when a lane is not finite. */
+int yvx_cuda_round_bf16_rows(float *values, unsigned long long rows, unsigned long long width,
+                             unsigned long long row_stride, int *status, void *stream);
+
 /* ---- KV append with rotary embedding (one launch per step) ---------------------------
  * Replaces, for the new rows of a step, the two rotate-half launches on Q and K
  * (yvex_cuda_transformer_rotary_half / _rotary_half_f32, src/backend/cuda/transformer.c:

@@ -431,6 +431,49 @@ class Oracle(_Gqa):
         """Fake quantisation of every row of a float32 [rows, count] array -> new array, or None."""
         return _activation_call(self.lib.yvx_oracle_activation_quant, rows, quantization, block_width, hadamard)
 
+    def qtype_encode_rows(self, values, qtype):
+        """float32 [rows, width] -> encoded uint8 [rows, row_bytes] (F32 0, F16 1, Q8_0 8, BF16 30)."""
+        values = np.ascontiguousarray(values, np.float32)
+        rows = values.shape[0]
+        if qtype == 0:
+            return values.view(np.uint8).reshape(rows, -1).copy()
+        if qtype == 1:
+            return values.astype(np.float16).view(np.uint8).reshape(rows, -1).copy()
+        if qtype == 30:
+            return self.bf16_round_bits(values).view(np.uint8).reshape(rows, -1).copy()
+        if qtype == 8:
+            return self.q8_0_encode_rows(values).reshape(rows, -1)
+        raise ValueError(qtype)
+
+    def bf16_round_bits(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros(x.shape, np.uint16)
+        self.lib.yvx_oracle_bf16_encode_array(x.reshape(-1), out.reshape(-1), x.size)
+        return out
+
+    def qtype_decode_rows(self, encoded, qtype, width, first_row=0, rows=None):
+        """Encoded uint8 [all rows, row_bytes] -> float32 [rows, width]."""
+        encoded = np.ascontiguousarray(encoded, np.uint8)
+        rows = encoded.shape[0] - first_row if rows is None else rows
+        out = np.zeros((rows, width), np.float32)
+        self.lib.yvx_oracle_qtype_decode_row.argtypes = [C.c_uint, C.c_void_p, _u64, _f32p]
+        for r in range(rows):
+            assert self.lib.yvx_oracle_qtype_decode_row(qtype, encoded[first_row + r].ctypes.data, width, out[r]) == 1
+        return out
+
+    def qtype_matvec(self, encoded, qtype, width, inputs, first_row=0, rows=None, round_bf16=True):
+        """inputs float32 [tokens, >= width] -> float32 [tokens, rows]; None on a refusal."""
+        encoded = np.ascontiguousarray(encoded, np.uint8)
+        inputs = np.ascontiguousarray(inputs, np.float32)
+        rows = encoded.shape[0] - first_row if rows is None else rows
+        out = np.zeros((inputs.shape[0], rows), np.float32)
+        self.lib.yvx_oracle_qtype_matvec.argtypes = [C.c_uint, C.c_void_p, _u64, _u64, _u64, _f32p, _u64, _u64,
+                                                     _f32p, _u64, C.c_int]
+        ok = self.lib.yvx_oracle_qtype_matvec(qtype, encoded.ctypes.data, first_row, rows, width,
+                                              inputs.reshape(-1), inputs.shape[0], inputs.shape[1],
+                                              out.reshape(-1), rows, int(round_bf16))
+        return out if ok == 1 else None
+
     def mla_decode(self, q_nope, q_rope, w_uk, latent, rope_key, scale, with_absorbed=False):
         """bf16 bit arrays: q_nope [H,dn], q_rope [H,dr], w_uk [H,dn,dc],
         latent [L,dc], rope_key [L,dr] -> float32 [H,dc]; with_absorbed also returns the
@@ -498,6 +541,22 @@ class Reference(_Gqa):
             counts, positions.reshape(-1))
         return (out, counts, positions) if ok == 1 else None
 
+
+    def qtype_dot(self, encoded_row, qtype, vector):
+        """The reference's yvex_quant_cpu_dot of one encoded row with one vector -> float or None."""
+        encoded_row = np.ascontiguousarray(encoded_row, np.uint8)
+        vector = np.ascontiguousarray(vector, np.float32)
+        out = C.c_float()
+        self.lib.yvx_ref_qtype_dot.argtypes = [C.c_uint, C.c_void_p, _u64, _f32p, _u64, C.POINTER(C.c_float)]
+        ok = self.lib.yvx_ref_qtype_dot(qtype, encoded_row.ctypes.data, encoded_row.size, vector, vector.size,
+                                        C.byref(out))
+        return float(out.value) if ok == 1 else None
+
+    def qtype_decode_row(self, encoded_row, qtype, width):
+        encoded_row = np.ascontiguousarray(encoded_row, np.uint8)
+        out = np.zeros(width, np.float32)
+        self.lib.yvx_ref_qtype_decode_row.argtypes = [C.c_uint, C.c_void_p, _u64, _f32p]
+        return out if self.lib.yvx_ref_qtype_decode_row(qtype, encoded_row.ctypes.data, width, out) == 1 else None
 
     def mla_decode_embedded(self, q_absorbed, q_rope, latent, rope_key, softmax_dim=192):
         """The split-rope latent decode of one session computed by the reference's own

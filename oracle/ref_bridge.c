@@ -534,3 +534,31 @@ int yvx_ref_rows_publish(const yvx_oracle_publish_args *a, const yvx_oracle_posi
     }
     return 1;
 }
+
+/* The reference's own encoded-row dot and decode (src/gguf/quant_compute.c:116-181,
+ * src/gguf/quant_block.c:780-832) for one row of `width` lanes. */
+int yvx_ref_qtype_dot(unsigned int qtype, const unsigned char *encoded, unsigned long long row_bytes,
+                      const float *vector, unsigned long long width, float *out)
+{
+    yvex_quant_failure failure;
+    yvex_error err;
+    return yvex_quant_cpu_dot(qtype, encoded, (size_t)row_bytes, vector, width, out, &failure, &err) == YVEX_OK;
+}
+
+int yvx_ref_qtype_decode_row(unsigned int qtype, const unsigned char *encoded, unsigned long long width,
+                             float *out)
+{
+    const yvex_gguf_qtype_geometry *geometry = yvex_gguf_qtype_geometry_find(qtype);
+    unsigned long long block, blocks;
+    if (!geometry || !geometry->block_size || width % geometry->block_size) return 0;
+    blocks = width / geometry->block_size;
+    for (block = 0; block < blocks; ++block) {
+        yvex_quant_failure failure;
+        yvex_error err;
+        if (yvex_quant_decode_block(qtype, encoded + block * geometry->bytes_per_block,
+                                    geometry->bytes_per_block, out + block * geometry->block_size,
+                                    geometry->block_size, &failure, &err) != YVEX_OK)
+            return 0;
+    }
+    return 1;
+}

@@ -175,6 +175,90 @@ int yvx_oracle_q8_0_decode_rows(const unsigned char *encoded, float *out, size_t
     return 1;
 }
 
+/* ---- encoded weight rows: decode and row dot ------------------------------------
+ * yvex_quant_decode_block for the F32, F16, BF16 and Q8_0 encodings
+ * (src/gguf/quant_block.c:805-832) and yvex_quant_cpu_dot over it
+ * (src/gguf/quant_compute.c:116-181): every lane decoded to float, the products and
+ * the running sum in double in lane order, the sum narrowed to float; a term or a
+ * partial sum that is not finite is refused. qtype: the GGUF ids (F32 0, F16 1,
+ * Q8_0 8, BF16 30). */
+unsigned long long yvx_oracle_qtype_row_bytes(unsigned int qtype, unsigned long long width)
+{
+    switch (qtype) {
+    case 0u: return width * 4ull;
+    case 1u:
+    case 30u: return width * 2ull;
+    case 8u: return width % Q8_0_ELEMENTS ? 0ull : width / Q8_0_ELEMENTS * Q8_0_BYTES;
+    default: return 0ull;
+    }
+}
+
+int yvx_oracle_qtype_decode_row(unsigned int qtype, const unsigned char *encoded,
+                                unsigned long long width, float *out)
+{
+    unsigned long long i;
+    if (!encoded || !out || !yvx_oracle_qtype_row_bytes(qtype, width)) return 0;
+    if (qtype == 8u) return yvx_oracle_q8_0_decode_rows(encoded, out, (size_t)width);
+    for (i = 0; i < width; ++i) {
+        if (qtype == 0u) memcpy(&out[i], encoded + 4ull * i, 4u);
+        else if (qtype == 1u) out[i] = yvx_oracle_f16_decode(load_u16le(encoded + 2ull * i));
+        else out[i] = yvx_oracle_bf16_decode(load_u16le(encoded + 2ull * i));
+    }
+    return 1;
+}
+
+int yvx_oracle_qtype_dot(unsigned int qtype, const unsigned char *encoded, unsigned long long width,
+                         const float *vector, float *out)
+{
+    float *row = malloc((size_t)width * sizeof(float));
+    double sum = 0.0;
+    unsigned long long i;
+    int ok = row && yvx_oracle_qtype_decode_row(qtype, encoded, width, row);
+    for (i = 0; ok && i < width; ++i) {
+        double term = (double)row[i] * vector[i];
+        if (!isfinite(term) || !isfinite(sum + term)) ok = 0;
+        sum += term;
+    }
+    free(row);
+    if (!ok) return 0;
+    *out = (float)sum;
+    return isfinite(*out);
+}
+
+/* yvex_attention_dot_batch (src/graph/core.c:1107-1215) with the publication that follows
+ * it where the caller rounds (src/graph/attention_execute.c:461-522): output[t][r] =
+ * row (first_row + r) . input[t], optionally rounded to bf16. */
+int yvx_oracle_qtype_matvec(unsigned int qtype, const unsigned char *encoded,
+                            unsigned long long first_row, unsigned long long rows,
+                            unsigned long long width, const float *input, unsigned long long tokens,
+                            unsigned long long input_stride, float *output,
+                            unsigned long long output_stride, int round_bf16)
+{
+    const unsigned long long row_bytes = yvx_oracle_qtype_row_bytes(qtype, width);
+    float *row = malloc((size_t)width * sizeof(float));
+    unsigned long long r, t, i;
+    int ok = row && row_bytes;
+    for (r = 0; ok && r < rows; ++r) {
+        ok = yvx_oracle_qtype_decode_row(qtype, encoded + (first_row + r) * row_bytes, width, row);
+        for (t = 0; ok && t < tokens; ++t) {
+            const float *vector = input + t * input_stride;
+            double sum = 0.0;
+            float value;
+            for (i = 0; i < width; ++i) {
+                double term = (double)row[i] * vector[i];
+                if (!isfinite(term) || !isfinite(sum + term)) ok = 0;
+                sum += term;
+            }
+            value = (float)sum;
+            if (!isfinite(value)) ok = 0;
+            if (round_bf16) value = yvx_oracle_bf16_decode(yvx_oracle_bf16_encode(value));
+            output[t * output_stride + r] = value;
+        }
+    }
+    free(row);
+    return ok;
+}
+
 /* ---- the CPU attention primitive --------------------------------------- */
 
 /* src/backend/cpu.c:217-255: range reduction by ln2 into [-0.5, 0.5], an

@@ -234,6 +234,19 @@ int yvx_oracle_full_attention_f32(const float *qkv, unsigned long long rows,
                                   unsigned long long heads, unsigned long long head_width,
                                   float *output, float *scratch);
 
+/* Encoded weight rows (GGUF ids F32 0, F16 1, Q8_0 8, BF16 30): decode, row dot in double,
+ * and the batch product the projections of the encoded attention operator are made of. */
+unsigned long long yvx_oracle_qtype_row_bytes(unsigned int qtype, unsigned long long width);
+int yvx_oracle_qtype_decode_row(unsigned int qtype, const unsigned char *encoded,
+                                unsigned long long width, float *out);
+int yvx_oracle_qtype_dot(unsigned int qtype, const unsigned char *encoded, unsigned long long width,
+                         const float *vector, float *out);
+int yvx_oracle_qtype_matvec(unsigned int qtype, const unsigned char *encoded,
+                            unsigned long long first_row, unsigned long long rows,
+                            unsigned long long width, const float *input, unsigned long long tokens,
+                            unsigned long long input_stride, float *output,
+                            unsigned long long output_stride, int round_bf16);
+
 #ifdef __cplusplus
 }
 #endif

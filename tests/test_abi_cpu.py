@@ -35,7 +35,7 @@ def test_library_exports_every_declared_symbol(library):
 def test_struct_sizes_match_the_reference_abi():
     # include/yvex/core.h: code + 96 + 256; include/yvex/internal/backend.h:215-228
     assert C.sizeof(abi.Error) == 356
-    assert C.sizeof(abi.DeviceTensor) == 152
+    assert C.sizeof(abi.DeviceTensor) == 120          # four dims: include/yvex/model.h:85
     assert C.sizeof(abi.OperationFacts) == 13 * 8 + 8
     assert C.sizeof(abi.AttentionRequirement) == 9 * 8 + 8 * 4
     assert C.sizeof(abi.AttentionRequest) == C.sizeof(abi.AttentionRequirement) + 4 * 8
@@ -133,3 +133,36 @@ def test_bf16_helpers_equal_the_oracle(oracle):
     bits, widened = oracle.bf16_round(x)
     assert np.array_equal(clori_b200.f32_to_bf16_bits(x), bits)
     assert np.array_equal(clori_b200.bf16_bits_to_f32(bits).view(np.uint32), widened.view(np.uint32))
+
+
+def test_struct_layouts_equal_the_reference_headers():
+    """sizeof and every field offset of the structures that cross the boundary, and the enum
+    values the caller passes, against tests/golden/abi_layout.json (written from the
+    reference's own headers by tests/golden/make_abi_layout.py): once for the C headers of
+    this library, once for the ctypes mirrors the Python tests use."""
+    import json
+    import sys
+    golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, golden)
+    import make_abi_layout as probe
+    with open(os.path.join(golden, "abi_layout.json")) as f:
+        reference = json.load(f)
+    ours = probe.layout([os.path.join(os.path.dirname(golden), "..", "include")], probe.LIBRARY_HEADERS)
+    assert ours == reference
+    mirrors = {"yvex_error": abi.Error, "yvex_device_tensor": abi.DeviceTensor,
+               "yvex_backend_operation_facts": abi.OperationFacts,
+               "yvex_transformer_attention_requirement": abi.AttentionRequirement,
+               "yvex_transformer_attention_request": abi.AttentionRequest,
+               "yvex_backend_attention_weight": abi.JobWeight, "yvex_backend_attention_position": abi.JobPosition,
+               "yvex_backend_attention_activation": abi.JobActivation,
+               "yvex_backend_attention_rolling": abi.JobRolling, "yvex_backend_attention_job": abi.AttentionJob,
+               "yvex_backend_attention_output": abi.AttentionJobOutput,
+               "yvex_backend_attention_failure": abi.AttentionJobFailure,
+               "yvex_backend_attention_completion_transfer": abi.CompletionTransfer,
+               "struct yvex_backend_attention_completion": abi.AttentionCompletion,
+               "yvex_backend_capability_result": abi.CapabilityResult}
+    for name, mirror in mirrors.items():
+        assert C.sizeof(mirror) == reference[name], name
+        for field, _ in mirror._fields_[:]:
+            assert getattr(mirror, field).offset == reference[f"{name}.{field}"], (name, field)
+        assert len(mirror._fields_) == len(probe.STRUCTS[name]), name
