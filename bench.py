@@ -336,6 +336,7 @@ def _timed_launches(lib, backend, problems, repeats):
     _timed_launches.step_ms = ms.value / repeats
     # The same calls captured once into a CUDA graph and replayed (launch gaps shrink).
     _timed_launches.graph_step_ms = None
+    _timed_launches.last_problem = (repeats - 1) % len(problems)     # whose outputs the buffers hold now
     calls = max(len(problems), 8)
     if lib.yvx_cuda_graph_capture_begin(backend.stream) == 0:
         ok = all(lib.yvx_cuda_gqa_attention(C.byref(problems[i % len(problems)]), backend.stream, C.byref(n)) == 0
@@ -347,6 +348,7 @@ def _timed_launches(lib, backend, problems, repeats):
             lib.yvx_cuda_event_record(first, backend.stream)
             for _ in range(replays):
                 lib.yvx_cuda_graph_launch(graph, backend.stream)
+            _timed_launches.last_problem = (calls - 1) % len(problems)
             lib.yvx_cuda_event_record(last, backend.stream)
             if lib.yvx_cuda_stream_synchronize(backend.stream) == 0:
                 lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
@@ -389,8 +391,8 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
         p.partials, p.status = scratch, status
         problems.append(p)
     main, combine, launches = _timed_launches(lib, backend, problems, repeats)
-    # full-size parity of copy (repeats-1) % copies against the CPU oracle
-    last = (repeats - 1) % copies
+    # full-size parity of the copy the last launch read, against the CPU oracle
+    last = _timed_launches.last_problem
     host = {}
     for name, ptr, count in (("q", q.value, hq * hd), ("k", k.value + last * kv_elems * 4, kv_elems),
                              ("v", v.value + last * kv_elems * 4, kv_elems), ("o", out.value, hq * hd)):
@@ -447,7 +449,7 @@ def bench_verify_q8(lib, backend, abi, peak, repeats, chunk=None):
         p.partials, p.status = scratch, status
         problems.append(p)
     main, combine, launches = _timed_launches(lib, backend, problems, repeats)
-    last = (repeats - 1) % copies
+    last = _timed_launches.last_problem
     # sample for the CPU check: KV head 0 (query heads 0..3), every record of it
     head0 = np.empty((blocks, record), np.uint8)
     for j in range(blocks):

@@ -473,6 +473,7 @@ class MatvecArgs(C.Structure):
 EXPORTED_SYMBOLS = [
     # attention_job.h
     "yvex_backend_attention_execute", "yvex_backend_attention_complete", "yvex_backend_query_capability",
+    "yvex_b200_backend_weights_forget",
     "yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
     "yvex_backend_capability_reason_name",
     # attention.h
@@ -574,6 +575,7 @@ def load():
     lib.yvex_backend_attention_execute.argtypes = [vp, P(AttentionJob), P(AttentionJobOutput),
                                                    P(AttentionJobFailure), P(Error)]
     lib.yvex_backend_attention_complete.argtypes = [vp, P(AttentionCompletion), C.c_int, P(Error)]
+    lib.yvex_b200_backend_weights_forget.argtypes = [vp, P(Error)]
     lib.yvex_backend_query_capability.argtypes = [vp, C.c_int, P(CapabilityResult), P(Error)]
     for name in ("yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
                  "yvex_backend_capability_reason_name"):

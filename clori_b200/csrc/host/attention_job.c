@@ -160,16 +160,47 @@ static int job_weight_check(job_run *run, unsigned int slot, unsigned long long 
     return YVEX_OK;
 }
 
-/* Device residence of an encoded weight: uploaded on first use, found by host address after. */
+/* A cheap content fingerprint of an encoded weight: its size, its first and last 4 KiB and
+ * 256 samples of 16 bytes spread over it (FNV-1a). Host memory that was freed and handed
+ * out again with other weights at the same address is told apart by it; a caller that
+ * rewrites weights in place calls yvex_b200_backend_weights_forget. */
+static unsigned long long weight_fingerprint(const unsigned char *bytes, unsigned long long count)
+{
+    unsigned long long h = 1469598103934665603ull ^ count, i, k;
+    const unsigned long long edge = count < 4096ull ? count : 4096ull;
+#define MIX(byte) (h = (h ^ (unsigned long long)(byte)) * 1099511628211ull)
+    for (i = 0; i < edge; ++i) MIX(bytes[i]);
+    for (i = count - edge; i < count; ++i) MIX(bytes[i]);
+    if (count > 8192ull)
+        for (k = 0; k < 256ull; ++k) {
+            const unsigned long long at = 4096ull + (count - 8192ull) / 256ull * k;
+            for (i = 0; i < 16ull && at + i < count; ++i) MIX(bytes[at + i]);
+        }
+#undef MIX
+    return h;
+}
+
+/* Device residence of an encoded weight: uploaded on first use, found again by host address,
+ * size and fingerprint (the reference resolves resident weights by host address:
+ * src/backend/cuda/attention.c:560-580). An address whose content changed is uploaded anew
+ * into the same slot. */
 static int job_weight_resident(job_run *run, unsigned int slot, const void **device)
 {
     yvex_backend *b = run->backend;
     const yvex_backend_attention_weight *w = &run->job->weights[slot];
+    const unsigned long long fingerprint = weight_fingerprint(w->encoded, w->encoded_bytes);
     unsigned int i;
     void *memory = NULL;
     int rc;
     for (i = 0; i < b->weight_count; ++i)
         if (b->weights[i].host == w->encoded && b->weights[i].bytes == w->encoded_bytes) {
+            if (b->weights[i].fingerprint != fingerprint) {
+                rc = yvx_cuda_upload_async(b->weights[i].device, w->encoded, w->encoded_bytes, b->stream);
+                if (rc != 0) return job_device_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_COPY, weight_stage[slot], rc);
+                b->weights[i].fingerprint = fingerprint;
+                run->h2d += w->encoded_bytes;
+                run->work_pending = 1;
+            }
             *device = b->weights[i].device;
             return YVEX_OK;
         }
@@ -193,6 +224,7 @@ static int job_weight_resident(job_run *run, unsigned int slot, const void **dev
     run->work_pending = 1;
     b->weights[b->weight_count].host = w->encoded;
     b->weights[b->weight_count].bytes = w->encoded_bytes;
+    b->weights[b->weight_count].fingerprint = fingerprint;
     b->weights[b->weight_count].device = memory;
     b->weight_count++;
     *device = memory;
@@ -571,7 +603,7 @@ static int job_stage_inputs(job_run *run)
     policy.original_context = job->position.original_context;
     policy.beta_fast = job->position.beta_fast;
     policy.beta_slow = job->position.beta_slow;
-    if (!yvex_b200_rope_frequencies(&policy, job->position.rope_dimensions, frequency)) {
+    if (yvex_b200_rope_frequencies(&policy, job->position.rope_dimensions, frequency) != YVEX_OK) {
         free(frequency);
         return job_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_INVALID_ARGUMENT, "cuda.attention.query_rope",
                         job->position.rope_dimensions, 0ull, YVEX_ERR_INVALID_ARG, "position policy has no rotation frequencies");
@@ -1085,6 +1117,21 @@ int yvex_backend_attention_execute(yvex_backend *backend, const yvex_backend_att
     free(run);
     if (rc == YVEX_OK) yvex_error_clear(err);
     return rc;
+}
+
+/* Drops every resident weight (a caller that rewrites or unloads weights calls this; nothing
+ * may be in flight on the backend's stream). No counterpart in the reference. */
+int yvex_b200_backend_weights_forget(yvex_backend *backend, yvex_error *err)
+{
+    unsigned int i;
+    int rc = yvx_backend_admit(backend, "b200.weights.forget", err);
+    if (rc != YVEX_OK) return rc;
+    rc = yvx_cuda_device_synchronize();
+    if (rc != 0) return yvx_backend_device_fail(backend, rc, "b200.weights.forget", err);
+    for (i = 0; i < backend->weight_count; ++i) (void)yvx_cuda_free(backend->weights[i].device);
+    backend->weight_count = 0u;
+    yvex_error_clear(err);
+    return YVEX_OK;
 }
 
 /* Deferred completion is refused at execute, so a completion object never has work

@@ -33,7 +33,7 @@ struct yvex_backend {
      * (src/backend/cuda/attention.c:560-580); the artifact bytes behind it are immutable. */
     struct yvx_resident_weight {
         const void *host;
-        unsigned long long bytes;
+        unsigned long long bytes, fingerprint;
         void *device;
     } *weights;
     unsigned int weight_count, weight_capacity;

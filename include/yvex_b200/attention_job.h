@@ -222,6 +222,11 @@ int yvex_backend_attention_complete(yvex_backend *backend,
                                     yvex_backend_attention_completion *completion,
                                     int barrier_observed, yvex_error *err);
 
+/* No counterpart in the reference. The job keeps encoded weights resident on the device,
+ * found again by host address, size and a sampled content fingerprint; a caller that
+ * rewrites weights in place, or unloads a model, drops them with this call. */
+int yvex_b200_backend_weights_forget(yvex_backend *backend, yvex_error *err);
+
 /* ---- capability query ----------------------------------------------------------- */
 typedef enum {
     YVEX_BACKEND_VARIANT_TENSOR_ALLOC = 0,

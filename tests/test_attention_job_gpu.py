@@ -205,7 +205,7 @@ def test_projection_kernel_is_bit_equal_to_the_cpu_dot(backend, oracle, qtype):
         encoded = oracle.qtype_encode_rows(values, qtype)
         stride = groups * width + 8
         x = job_cases.bf16_valued(rng, (tokens, stride))
-        w, xi = backend.tensor("w", encoded), backend.tensor("x", x)
+        w, xi = backend.tensor("w", encoded.view(np.int8), dtype=abi.DTYPE_I8), backend.tensor("x", x)
         out = backend.alloc("y", abi.DTYPE_F32, (tokens, groups * rows + 3))
         status = backend.tensor("status", np.zeros(1, np.int32))
         for rounded in (0, 1):
