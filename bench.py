@@ -556,6 +556,81 @@ def bench_prefill(lib, backend, abi, repeats, tokens=8192, batch=2):
     return result, (q_host, k_host, v_host, o_host, tokens, rows)
 
 
+def bench_prefill_f32(lib, backend, abi, repeats, tokens=21741, heads=56):
+    """The exact-F32 contract at the reference's largest tested prefill geometry (MHA, 21741 tokens x 56
+    heads, hd 128, tests/unit/cuda/quant_qtype.c:2868-2970): F32 Q/K/V whose values bf16 holds exactly
+    (what the reference's linears publish), F32 output. Staging to bf16, the tensor-core kernel and the
+    (idle) exact kernel are all inside the timed step."""
+    hd = 128
+    n = tokens * heads * hd
+    q, k, v, out = (_alloc(lib, n * 4) for _ in range(4))
+    status = _alloc(lib, 4)
+    for ptr, seed in ((q, 701), (k, 702), (v, 703)):
+        assert lib.yvx_cuda_fill_normal(ptr, -abi.DTYPE_F32, n, seed, 0.5, backend.stream) == 0
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    p = abi.GqaProblem()
+    p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, tokens, heads, heads, hd
+    p.causal, p.scale = 1, 1.0 / np.sqrt(hd)
+    p.query_dtype = p.kv_dtype = p.output_dtype = abi.DTYPE_F32
+    p.query, p.query_row_stride, p.output = q, heads * hd, out
+    p.key, p.value = k, v
+    p.key_token_stride = p.value_token_stride = heads * hd
+    p.key_head_stride = p.value_head_stride = hd
+    p.kv_tokens_uniform = p.kv_tokens_max = tokens
+    lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+    partial_bytes = (lib.yvx_cuda_gqa_partials_bytes(C.byref(p)) + 255) & ~255
+    staging_bytes = lib.yvx_cuda_gqa_f32_staging_bytes(C.byref(p))
+    scratch = _alloc(lib, max(partial_bytes + staging_bytes, 16))
+    p.partials, p.status = scratch, status
+    p.f32_staging = scratch.value + partial_bytes
+    first, last, ms, launches = C.c_void_p(), C.c_void_p(), C.c_float(), C.c_uint()
+    lib.yvx_cuda_event_create(C.byref(first)); lib.yvx_cuda_event_create(C.byref(last))
+    assert lib.yvx_cuda_gqa_attention(C.byref(p), backend.stream, C.byref(launches)) == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_event_record(first, backend.stream)
+    for _ in range(repeats):
+        assert lib.yvx_cuda_gqa_attention(C.byref(p), backend.stream, C.byref(launches)) == 0
+    lib.yvx_cuda_event_record(last, backend.stream)
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+    step_ms = ms.value / repeats
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    # sample for the CPU check: head 0, the last 64 rows against every token
+    rows = 64
+    host = {}
+    for name, ptr, first_row, count in (("q", q, tokens - rows, rows), ("o", out, tokens - rows, rows),
+                                        ("k", k, 0, tokens), ("v", v, 0, tokens)):
+        full = np.empty((count, heads * hd), np.float32)
+        lib.yvx_cuda_download_async(full.ctypes.data, ptr.value + first_row * heads * hd * 4, full.nbytes, backend.stream)
+        host[name] = full
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    sample = {name: np.ascontiguousarray(a[:, :hd]) for name, a in host.items()}
+    flops = 4.0 * heads * hd * tokens * (tokens + 1) / 2.0
+    tf_peak = 1699.0
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            tf_peak = float(json.load(f)["bf16_tflops"])
+    result = {"workload": f"exact-F32 contract causal prefill, {tokens} tokens x {heads} heads (MHA), hd128, F32 in/out, bf16-valued",
+              "kernel": "f32_stage_rows_kernel x3 + prefill_tcgen05_kernel (+ gated exact kernel)",
+              "launches_per_step": int(launches.value), "step_ms": step_ms, "kernel_ms": step_ms, "flops_causal": flops,
+              "achieved_tflops": flops / (step_ms * 1e-3) / 1e12, "frac_of_bf16_peak": flops / (step_ms * 1e-3) / 1e12 / tf_peak,
+              "tokens_per_s": tokens / (step_ms * 1e-3), "status_word": int(st[0]),
+              "l2": "Q+K+V+O = %.0f MB exceed L2" % (4 * n * 4 / 1e6)}
+    for ptr in (q, k, v, out, status, scratch):
+        lib.yvx_cuda_free(ptr)
+    lib.yvx_cuda_event_destroy(first); lib.yvx_cuda_event_destroy(last)
+    return result, (sample, tokens, rows)
+
+
+def check_prefill_f32(engine, sample_tuple, threads):
+    sample, tokens, rows = sample_tuple
+    start = time.perf_counter()
+    ref = engine.gqa_attention(sample["q"], sample["k"], sample["v"], tokens - rows, 1, 1, 128, threads=threads)
+    seconds = time.perf_counter() - start
+    return float((np.abs(ref - sample["o"]) / (1.0 + np.abs(ref))).max()), seconds
+
+
 def check_prefill(engine, sample, threads):
     from clori_b200 import bf16_bits_to_f32
     q, k, v, o, tokens, rows = sample
@@ -1440,7 +1515,7 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
-                                 "compressor", "activation", "publish"],
+                                 "compressor", "activation", "publish", "prefill_f32"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1504,6 +1579,9 @@ def main():
                                         tokens=args.tokens)
         elif args.workload == "prefill":
             result, _ = bench_prefill(abi.load(), backend, abi, max(args.steps, 3), tokens=args.tokens)
+        elif args.workload == "prefill_f32":
+            result, _ = bench_prefill_f32(abi.load(), backend, abi, max(args.steps, 3),
+                                          tokens=args.tokens if args.tokens != 8192 else 21741)
         else:
             run = {"decode_f32": bench_decode_f32, "verify_q8": bench_verify_q8}[args.workload]
             extra = {"chunk": args.chunk} if args.workload == "verify_q8" and args.chunk else {}
@@ -1536,18 +1614,6 @@ def main():
     legs["headline"] = (leg_begin, time.time())
     barrier()
     device_ms = max_over_ranks(w.elapsed_ms(start, stop))
-
-    # ---- the same step back to back for SUSTAIN_SECONDS (power-capped clocks) ----
-    sustained_steps = max(int(SUSTAIN_SECONDS * 1e3 / (device_ms / args.steps)), args.steps)
-    leg_begin = time.time()
-    w.record(start)
-    for _ in range(sustained_steps):
-        w.step()
-    w.record(stop)
-    b.sync()
-    legs["sustained"] = (leg_begin, time.time())
-    barrier()
-    sustained_ms = max_over_ranks(w.elapsed_ms(start, stop)) / sustained_steps
 
     # ---- end to end: host buffers, synchronous operator --------------------
     b.bind_stream(None, synchronous=True)
@@ -1590,6 +1656,7 @@ def main():
         plan = (("decode_f32_config1", "f32", lambda: bench_decode_f32(lib, b, w.abi, hbm_peak, 64)),
                 ("verify_q8_config4_1gpu", "q8", lambda: bench_verify_q8(lib, b, w.abi, hbm_peak, 20)),
                 ("prefill_config3", "prefill", lambda: bench_prefill(lib, b, w.abi, 10)),
+                ("prefill_f32_contract", "prefill_f32", lambda: bench_prefill_f32(lib, b, w.abi, 3)),
                 ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 10)),
                 ("kv_append_rotary", None, lambda: bench_kv_append(lib, b, w.abi, hbm_peak, 10)),
                 ("latent_sparse_decode", None, lambda: bench_latent_sparse(lib, b, w.abi, 20)),
@@ -1602,6 +1669,20 @@ def main():
             legs[name] = (leg_begin, time.time())
             if sample_key:
                 other_samples[sample_key] = sample
+    # ---- the same step back to back for SUSTAIN_SECONDS (power-capped clocks); last, so that the
+    # short legs above are not measured on a GPU this run has just heated ----
+    b.bind_stream(None, synchronous=False)
+    sustained_steps = max(int(SUSTAIN_SECONDS * 1e3 / (device_ms / args.steps)), args.steps)
+    leg_begin = time.time()
+    w.record(start)
+    for _ in range(sustained_steps):
+        w.step()
+    w.record(stop)
+    b.sync()
+    legs["sustained"] = (leg_begin, time.time())
+    barrier()
+    sustained_ms = max_over_ranks(w.elapsed_ms(start, stop)) / sustained_steps
+
     sampler.stop()
     clocks = sampler.window(*legs["headline"])
     for name, result in others.items():
@@ -1682,6 +1763,11 @@ def main():
             others["prefill_config3"].update(
                 gpu_vs_cpu_max_abs_on_sample=err, cpu_sample_ms=seconds * 1e3, cpu_cores=threads,
                 cpu_sample="batch 0, query head 0: last 128 rows x 8192 tokens")
+        if "prefill_f32" in other_samples:
+            err, seconds = check_prefill_f32(engine, other_samples["prefill_f32"], threads)
+            others["prefill_f32_contract"].update(
+                gpu_vs_cpu_max_scaled_error_on_sample=err, tolerance="2e-3 * (1 + |ref|)", cpu_sample_ms=seconds * 1e3,
+                cpu_sample="head 0: last 64 rows x 21741 tokens")
         if "mla" in other_samples:
             err, seconds = check_mla(other_samples["mla"])
             others["latent_decode_config5"].update(
@@ -1711,6 +1797,7 @@ def summary_of(line, others):
     short = (("cfg1", "decode_f32_config1", "frac_of_measured_hbm", "hbm", "gpu_vs_cpu_max_abs"),
              ("cfg4", "verify_q8_config4_1gpu", "frac_of_measured_hbm", "hbm", "gpu_vs_cpu_max_abs_on_sample"),
              ("cfg3", "prefill_config3", "frac_of_bf16_peak", "tc", "gpu_vs_cpu_max_abs_on_sample"),
+             ("f32_prefill", "prefill_f32_contract", "frac_of_bf16_peak", "tc", "gpu_vs_cpu_max_scaled_error_on_sample"),
              ("cfg5", "latent_decode_config5", "frac_of_measured_hbm", "hbm", "gpu_vs_cpu_max_abs_on_sample"))
     for tag, name, frac_key, frac_tag, err_key in short:
         r = others.get(name)

@@ -137,6 +137,7 @@ class GqaProblem(C.Structure):
         ("chunk_tokens", C.c_uint), ("max_splits", C.c_uint),
         ("partials", C.c_void_p), ("partial_output", C.c_void_p), ("status", C.c_void_p),
         ("force_general", C.c_int), ("query_head_stride", u64),
+        ("f32_staging", C.c_void_p), ("gate", C.c_void_p), ("gate_value", C.c_int),
     ]
 
 
@@ -461,6 +462,26 @@ class CapabilityResult(C.Structure):
                 ("function_available", C.c_int)]
 
 
+class KvBankComponent(C.Structure):
+    _fields_ = [("history", C.c_int), ("capacity", u64), ("value_width", u64), ("kv_state_extent", u64),
+                ("score_state_extent", u64)]
+
+
+class KvBankSpan(C.Structure):
+    _fields_ = [("offset", u64 * 3), ("bytes", u64 * 3)]
+
+
+class KvBankArgs(C.Structure):
+    """yvx_kv_bank_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [("sessions", C.c_uint), ("kv_heads", C.c_uint), ("head_dim", C.c_uint), ("kv_tokens", C.c_void_p),
+                ("kv_tokens_uniform", C.c_uint), ("row_capacity", C.c_uint), ("bank", C.c_void_p),
+                ("bank_session_bytes", u64), ("values_offset", u64), ("positions_offset", u64), ("value_width", u64),
+                ("position_base", u64), ("key_pool", C.c_void_p), ("value_pool", C.c_void_p),
+                ("block_table", C.c_void_p), ("block_tokens", C.c_uint), ("block_table_stride", C.c_uint),
+                ("pool_blocks", C.c_uint), ("pool_token_stride", u64), ("pool_head_stride", u64),
+                ("pool_block_stride", u64), ("status", C.c_void_p)]
+
+
 class MatvecArgs(C.Structure):
     """yvx_matvec_args (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [("weights", C.c_void_p), ("qtype", C.c_uint), ("first_row", u64), ("rows", u64), ("width", u64),
@@ -473,7 +494,7 @@ class MatvecArgs(C.Structure):
 EXPORTED_SYMBOLS = [
     # attention_job.h
     "yvex_backend_attention_execute", "yvex_backend_attention_complete", "yvex_backend_query_capability",
-    "yvex_b200_backend_weights_forget",
+    "yvex_b200_backend_weights_forget", "yvex_b200_kv_bank_layout",
     "yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
     "yvex_backend_capability_reason_name",
     # attention.h
@@ -508,7 +529,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_lse_exchange_bytes", "yvx_cuda_lse_exchange_counter_offset", "yvx_cuda_gqa_attention_exchange",
     "yvx_cuda_lse_exchange_emulated", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
     "yvx_cuda_graph_capture_begin", "yvx_cuda_graph_capture_end", "yvx_cuda_graph_launch", "yvx_cuda_graph_destroy",
-    "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
+    "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_f32_staging_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
     "yvx_cuda_gqa_attention_profiled",
     "yvx_cuda_fill_normal", "yvx_cuda_fill_normal_rope_bf16", "yvx_cuda_fill_q8_lanes", "yvx_cuda_fill_f16_uniform",
@@ -516,7 +537,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_q8_record_bytes", "yvx_cuda_q8_kv_pack", "yvx_cuda_fill_q8_records",
     "yvx_cuda_latent_reduce", "yvx_cuda_latent_reduce_launches", "yvx_cuda_latent_reduce_workspace_bytes",
     "yvx_cuda_csa_select", "yvx_cuda_csa_select_workspace_bytes", "yvx_cuda_kv_append_rotary", "yvx_cuda_mla_plan", "yvx_cuda_mla_absorbed_bytes", "yvx_cuda_mla_partials_bytes",
-    "yvx_cuda_qtype_row_bytes", "yvx_cuda_qtype_matvec", "yvx_cuda_qtype_decode_rows", "yvx_cuda_round_bf16_rows",
+    "yvx_cuda_kv_bank_transfer", "yvx_cuda_qtype_row_bytes", "yvx_cuda_qtype_matvec", "yvx_cuda_qtype_decode_rows", "yvx_cuda_round_bf16_rows",
     "yvx_cuda_mla_decode", "yvx_cuda_compressor_chunk", "yvx_cuda_activation_quant", "yvx_cuda_rows_publish", "yvx_cuda_rows_publish_batch",
 ]
 
@@ -581,6 +602,10 @@ def load():
                  "yvex_backend_capability_reason_name"):
         getattr(lib, name).restype = C.c_char_p
         getattr(lib, name).argtypes = [C.c_int]
+    lib.yvx_cuda_kv_bank_transfer.argtypes = [P(KvBankArgs), C.c_int, vp]
+    lib.yvex_b200_kv_bank_layout.argtypes = [P(KvBankComponent), C.c_uint, P(KvBankSpan), P(u64)]
+    lib.yvx_cuda_gqa_f32_staging_bytes.restype = u64
+    lib.yvx_cuda_gqa_f32_staging_bytes.argtypes = [P(GqaProblem)]
     lib.yvx_cuda_qtype_row_bytes.restype = u64
     lib.yvx_cuda_qtype_row_bytes.argtypes = [C.c_uint, u64]
     lib.yvx_cuda_qtype_matvec.argtypes = [P(MatvecArgs), vp]

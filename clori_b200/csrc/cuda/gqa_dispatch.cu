@@ -11,6 +11,53 @@ int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int lse_exchange_launch(const yvx_gqa_problem &p, const yvx_lse_exchange &x, cudaStream_t stream);
+
+// ---- F32 problems on the tensor-core prefill kernel ---------------------------------------
+// Staging layout: [flag, 256 bytes][Q bf16 packed rows][K bf16 packed rows][V bf16 packed rows].
+constexpr unsigned long long kStageFlagBytes = 256ull;
+
+static bool f32_tensor_path_shape(const yvx_gqa_problem &p)
+{
+    if (p.query_dtype != YVEX_DTYPE_F32 || p.kv_dtype != YVEX_DTYPE_F32 || p.output_dtype != YVEX_DTYPE_F32 ||
+        p.head_dim != 128u || p.block_table || p.partial_output || p.kv_position_base || p.kv_tokens ||
+        p.query_start || p.force_general || !p.kv_heads || p.query_heads % p.kv_heads ||
+        (p.query_head_stride && p.query_head_stride != p.head_dim) || p.sessions != 1u)
+        return false;
+    return (unsigned long long)p.query_rows * (p.query_heads / p.kv_heads) > 64ull;
+}
+
+// One row per CTA-iteration: F32 [rows][stride] -> bf16 packed [rows][width]; a lane that bf16
+// cannot hold exactly (or that is not finite) raises the flag.
+__global__ void f32_stage_rows_kernel(const float *source, unsigned long long rows, unsigned long long width,
+                                      unsigned long long stride, unsigned short *packed, int *flag)
+{
+    const unsigned long long quads = width / 4ull, total = rows * quads;
+    const unsigned long long step = (unsigned long long)gridDim.x * blockDim.x;
+    bool exact = true;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) {
+        const unsigned long long row = i / quads, quad = i % quads;
+        const float4 v = *reinterpret_cast<const float4 *>(source + row * stride + 4ull * quad);
+        const uint32_t bits[4] = {__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w)};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            exact = exact && !(bits[j] & 0xffffu) && (bits[j] & 0x7f800000u) != 0x7f800000u;
+        uint2 out;
+        out.x = (bits[0] >> 16) | (bits[1] & 0xffff0000u);
+        out.y = (bits[2] >> 16) | (bits[3] & 0xffff0000u);
+        *reinterpret_cast<uint2 *>(packed + row * width + 4ull * quad) = out;
+    }
+    if (!exact) atomicExch(flag, 1);
+}
+
+static int f32_stage_launch(const float *source, unsigned long long rows, unsigned long long width,
+                            unsigned long long stride, unsigned short *packed, int *flag, cudaStream_t s)
+{
+    const unsigned long long total = rows * (width / 4ull);
+    const unsigned int blocks = (unsigned int)((total + 255ull) / 256ull < 148ull * 16ull ? (total + 255ull) / 256ull
+                                                                                      : 148ull * 16ull);
+    f32_stage_rows_kernel<<<blocks ? blocks : 1u, 256, 0, s>>>(source, rows, width, stride, packed, flag);
+    return yvx_cuda_check(cudaGetLastError(), "f32_stage_rows_kernel");
+}
 }
 
 extern "C" {
@@ -66,6 +113,61 @@ unsigned long long yvx_cuda_gqa_partials_bytes(const yvx_gqa_problem *p)
            (p->head_dim + 2ull) * sizeof(float);
 }
 
+unsigned long long yvx_cuda_gqa_f32_staging_bytes(const yvx_gqa_problem *p)
+{
+    if (!p || !yvx::f32_tensor_path_shape(*p)) return 0ull;
+    const unsigned long long q = (unsigned long long)p->query_rows * p->query_heads * p->head_dim;
+    const unsigned long long kv = (unsigned long long)p->kv_tokens_max * p->kv_heads * p->head_dim;
+    return yvx::kStageFlagBytes + (q + 2ull * kv) * 2ull;
+}
+
+// The F32 problem on the tensor cores: stage (1 launch per tensor, 3 in all), the tensor-core
+// kernel gated on "every lane was bf16", the general kernel (and its combine) gated on the opposite.
+static int gqa_launch_f32_tensor(const yvx_gqa_problem *p, cudaStream_t s, unsigned int *count)
+{
+    const unsigned long long qw = (unsigned long long)p->query_heads * p->head_dim;
+    const unsigned long long kw = (unsigned long long)p->kv_heads * p->head_dim;
+    unsigned char *base = reinterpret_cast<unsigned char *>(p->f32_staging);
+    int *flag = reinterpret_cast<int *>(base);
+    unsigned short *q16 = reinterpret_cast<unsigned short *>(base + yvx::kStageFlagBytes);
+    unsigned short *k16 = q16 + (unsigned long long)p->query_rows * qw;
+    unsigned short *v16 = k16 + (unsigned long long)p->kv_tokens_max * kw;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (p->query_row_stride & 3ull) || (p->key_token_stride & 3ull) ||
+        (p->value_token_stride & 3ull) || (reinterpret_cast<uintptr_t>(p->query) & 15u) ||
+        (reinterpret_cast<uintptr_t>(p->key) & 15u) || (reinterpret_cast<uintptr_t>(p->value) & 15u) ||
+        p->key_head_stride != p->head_dim || p->value_head_stride != p->head_dim)
+        return 0;
+    int rc = yvx_cuda_check(cudaMemsetAsync(flag, 0, sizeof(int), s), "f32 staging flag");
+    if (rc == 0) rc = yvx::f32_stage_launch((const float *)p->query, p->query_rows, qw, p->query_row_stride, q16, flag, s);
+    if (rc == 0) rc = yvx::f32_stage_launch((const float *)p->key, p->kv_tokens_max, kw, p->key_token_stride, k16, flag, s);
+    if (rc == 0) rc = yvx::f32_stage_launch((const float *)p->value, p->kv_tokens_max, kw, p->value_token_stride, v16, flag, s);
+    if (rc != 0) return rc;
+    yvx_gqa_problem staged = *p;
+    staged.query_dtype = staged.kv_dtype = YVEX_DTYPE_BF16;
+    staged.query = q16;
+    staged.key = k16;
+    staged.value = v16;
+    staged.query_row_stride = qw;
+    staged.key_token_stride = staged.value_token_stride = kw;
+    staged.gate = flag;
+    staged.gate_value = 0;
+    rc = yvx::prefill_tcgen05_launch(staged, s);
+    if (rc == 0) return YVEX_ERR_UNSUPPORTED;  // the staged shape is the prefill kernel's by construction
+    if (rc < 0) return rc;
+    yvx_gqa_problem exact = *p;
+    exact.gate = flag;
+    exact.gate_value = 1;
+    rc = yvx::gqa_generic_main_launch(exact, s);
+    if (rc != 0) return rc;
+    *count = 5u;
+    if (exact.max_splits > 1u) {
+        rc = yvx::gqa_combine_launch(exact, s);
+        if (rc != 0) return rc;
+        *count = 6u;
+    }
+    return 1;
+}
+
 static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *events,
                       unsigned int *launches, const yvx_lse_exchange *exchange = nullptr)
 {
@@ -101,7 +203,20 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     if (rc == 0 && !p->force_general && packed_heads) rc = yvx::gqa_decode_f32_launch(*p, s);
     if (rc == 0 && !p->force_general && packed_heads)
         rc = vectors <= 64u ? yvx::gqa_decode_mma_launch(*p, s) : yvx::prefill_tcgen05_launch(*p, s);
-    const bool final_output = rc == 2;
+    bool final_output = rc == 2;
+    if (rc == 0 && p->f32_staging && yvx::f32_tensor_path_shape(*p)) {
+        unsigned int staged_launches = 0u;
+        rc = gqa_launch_f32_tensor(p, s, &staged_launches);
+        if (rc == 1) {
+            if (events) {
+                cudaEventRecord(events[1], s);
+                cudaEventRecord(events[2], s);
+            }
+            if (launches) *launches = staged_launches;
+            return 0;
+        }
+        if (rc < 0) return rc;
+    }
     if (rc == 0) rc = yvx::gqa_generic_main_launch(*p, s);
     else if (rc == 1 || rc == 2) rc = 0;
     if (rc != 0) return rc;

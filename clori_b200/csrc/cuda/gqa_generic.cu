@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(kGenericThreads)
 gqa_split_generic_kernel(const yvx_gqa_problem p)
 {
     constexpr int HD_CAP = SLOTS * 32;
+    if (p.gate && *p.gate != p.gate_value) return;  // the other kernel of the pair owns this problem
     __shared__ float sm_acc[kGenericWarps][VT][HD_CAP];
     __shared__ float sm_m[kGenericWarps][VT];
     __shared__ float sm_l[kGenericWarps][VT];
@@ -255,6 +256,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32)
 gqa_combine_kernel(const yvx_gqa_problem p)
 {
     pdl_wait();  // the split kernel's partials must be complete and visible
+    if (p.gate && *p.gate != p.gate_value) return;
     const unsigned long long item = blockIdx.x;
     const unsigned int b = (unsigned int)(item / ((unsigned long long)p.query_rows * p.query_heads));
     const unsigned int hd = p.head_dim;

@@ -75,14 +75,18 @@ __device__ __forceinline__ unsigned int prefill_tile_count(const yvx_gqa_problem
     return visible_end > 0 ? (unsigned int)((visible_end + kPfN - 1) / kPfN) : 0u;
 }
 
-// grid: one dimension, ordered longest first over the whole launch: the pair of
-// query tiles varies slowest, (session, query head) fastest, so the CTAs left
-// for the tail of the launch are the short ones and neighbours share K / V.
+// grid: one dimension. The (session, query head) lanes are taken in groups of `lane_group`
+// whose K and V streams fit the L2 together (all of them when they do: grouped-query shapes;
+// a few heads at a time for long multi-head prefills, where every head has its own K and V).
+// Inside a group the pair of query tiles varies slowest, longest first, and the lane fastest,
+// so the CTAs left for the tail are the short ones and neighbours share K / V.
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillMaps maps,
-                       const int head_major)
+                       const int head_major, const unsigned int lane_group)
 {
     extern __shared__ unsigned char smem_raw[];
+    // uniform over the grid, before any barrier or tensor memory exists
+    if (p.gate && *p.gate != p.gate_value) return;
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     unsigned char *q_tiles_smem = smem;                          // tile A, then tile B
@@ -93,9 +97,12 @@ prefill_tcgen05_kernel(const yvx_gqa_problem p, const __grid_constant__ PrefillM
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int pairs = (p.query_rows + 2 * kPfM - 1) / (2 * kPfM);
     const unsigned int lanes_of_work = p.query_heads * p.sessions;
-    const unsigned int q0 = (pairs - 1u - blockIdx.x / lanes_of_work) * 2u * kPfM;
-    const unsigned int qhead = (blockIdx.x % lanes_of_work) % p.query_heads;
-    const unsigned int b = (blockIdx.x % lanes_of_work) / p.query_heads;
+    const unsigned int within = blockIdx.x % (pairs * lane_group);
+    const unsigned int work_lane = blockIdx.x / (pairs * lane_group) * lane_group + within % lane_group;
+    if (work_lane >= lanes_of_work) return;  // the last group may be short; uniform over the CTA
+    const unsigned int q0 = (pairs - 1u - within / lane_group) * 2u * kPfM;
+    const unsigned int qhead = work_lane % p.query_heads;
+    const unsigned int b = work_lane / p.query_heads;
     const unsigned int kv_head = qhead / (p.query_heads / p.kv_heads);
     const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     const long long query_start =
@@ -449,11 +456,20 @@ int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream)
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kPfSmemBytes);
     if (error != cudaSuccess) return yvx_cuda_check(error, "prefill_tcgen05_kernel attribute");
-    const unsigned long long ctas = (unsigned long long)((p.query_rows + 2 * kPfM - 1) / (2 * kPfM)) *
-                                    p.query_heads * p.sessions;
+    // lanes whose K + V (bf16) fit half of the 126 MB L2 together form a group
+    const unsigned long long lanes = (unsigned long long)p.query_heads * p.sessions;
+    const unsigned long long group = p.query_heads / p.kv_heads;
+    const unsigned long long stream_bytes = (unsigned long long)p.kv_tokens_max * kPfD * 2ull * 2ull;
+    unsigned long long streams = stream_bytes ? (64ull << 20) / stream_bytes : lanes;
+    if (streams < 1ull) streams = 1ull;
+    unsigned long long lane_group = streams * group;
+    if (lane_group > lanes) lane_group = lanes;
+    const unsigned long long pairs = (p.query_rows + 2 * kPfM - 1) / (2 * kPfM);
+    const unsigned long long ctas = (lanes + lane_group - 1ull) / lane_group * lane_group * pairs;
     if (ctas == 0ull || ctas > 0x7fffffffull) return 0;
     const dim3 grid((unsigned int)ctas, 1, 1);
-    prefill_tcgen05_kernel<<<grid, kPfThreads, kPfSmemBytes, stream>>>(p, maps, kv_head_first ? 1 : 0);
+    prefill_tcgen05_kernel<<<grid, kPfThreads, kPfSmemBytes, stream>>>(p, maps, kv_head_first ? 1 : 0,
+                                                                       (unsigned int)lane_group);
     const int rc = yvx_cuda_check(cudaGetLastError(), "prefill_tcgen05_kernel");
     return rc != 0 ? rc : 2;
 }

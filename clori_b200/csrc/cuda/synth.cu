@@ -33,6 +33,11 @@ __global__ void fill_normal_kernel(void *dst, int dtype, unsigned long long coun
             unsigned short *out = reinterpret_cast<unsigned short *>(dst);
             out[2 * i] = bf16_bits_rne(a);
             if (2 * i + 1 < count) out[2 * i + 1] = bf16_bits_rne(b);
+        } else if (dtype == -YVEX_DTYPE_F32) {
+            // F32 storage of values that bf16 holds exactly (what the reference's linears publish)
+            float *out = reinterpret_cast<float *>(dst);
+            out[2 * i] = __uint_as_float((uint32_t)bf16_bits_rne(a) << 16);
+            if (2 * i + 1 < count) out[2 * i + 1] = __uint_as_float((uint32_t)bf16_bits_rne(b) << 16);
         } else {
             float *out = reinterpret_cast<float *>(dst);
             out[2 * i] = a;
@@ -83,7 +88,7 @@ extern "C" {
 int yvx_cuda_fill_normal(void *dst, int dtype, unsigned long long count,
                          unsigned long long seed, float sigma, void *stream)
 {
-    if (!dst || !count || (dtype != YVEX_DTYPE_F32 && dtype != YVEX_DTYPE_BF16))
+    if (!dst || !count || (dtype != YVEX_DTYPE_F32 && dtype != YVEX_DTYPE_BF16 && dtype != -YVEX_DTYPE_F32))
         return YVEX_ERR_INVALID_ARG;
     yvx::fill_normal_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>(dst, dtype, count, seed, sigma);
     return yvx_cuda_check(cudaGetLastError(), "fill_normal_kernel");

@@ -133,15 +133,22 @@ int yvex_b200_transformer_attention_execute(yvex_backend *backend,
     problem.query_start_uniform = (unsigned int)r->query_start;
     problem.status = backend->status_device;
     yvx_cuda_gqa_plan_splits(&problem, backend->sm_count);
-    rc = yvx_backend_scratch(backend, yvx_cuda_gqa_partials_bytes(&problem), &scratch, where, err);
-    if (rc != YVEX_OK) return rc;
-    problem.partials = scratch;
+    {
+        /* one arena: the split partials, then (prefill-sized problems) the bf16 staging of the
+         * tensor-core path */
+        const unsigned long long partial_bytes = (yvx_cuda_gqa_partials_bytes(&problem) + 255ull) & ~255ull;
+        const unsigned long long staging_bytes = yvx_cuda_gqa_f32_staging_bytes(&problem);
+        rc = yvx_backend_scratch(backend, partial_bytes + staging_bytes, &scratch, where, err);
+        if (rc != YVEX_OK) return rc;
+        problem.partials = partial_bytes ? scratch : NULL;
+        if (staging_bytes) problem.f32_staging = (unsigned char *)scratch + partial_bytes;
+    }
     rc = yvx_backend_status_arm(backend, where, err);
     if (rc != YVEX_OK) return rc;
     rc = yvx_cuda_gqa_attention(&problem, backend->stream, &launches);
     if (rc != 0) return yvx_backend_device_fail(backend, rc, where, err);
     facts->kernel_launches = launches;
-    facts->temporary_bytes = yvx_cuda_gqa_partials_bytes(&problem);
+    facts->temporary_bytes = yvx_cuda_gqa_partials_bytes(&problem) + yvx_cuda_gqa_f32_staging_bytes(&problem);
     facts->state_bytes = (key_elements + value_elements) * sizeof(float);
     facts->activation_bytes = (query_elements + output_elements) * sizeof(float);
     facts->compulsory_memory_facts_available = 1;

@@ -115,3 +115,39 @@ int yvex_b200_kv_sequence_shard(unsigned long long tokens, unsigned int shards, 
     if (*end > tokens) *end = tokens;
     return 1;
 }
+
+/* The byte layout of one layer's state bank (src/runtime/state_residency.c:44-54, 346-395):
+ * per component three spans, values, positions, auxiliary, each starting at the next 8-byte
+ * boundary of a running cursor. A history component holds capacity * value_width floats and
+ * capacity u64 positions and no auxiliary bytes; a rolling component holds its kv-state floats
+ * as values and its score-state floats as auxiliary. Returns 0 on overflow or bad arguments. */
+int yvex_b200_kv_bank_layout(const yvex_b200_kv_bank_component *components, unsigned int count,
+                             yvex_b200_kv_bank_span *spans, unsigned long long *bank_bytes)
+{
+    unsigned long long cursor = 0ull;
+    unsigned int i, k;
+    if (!components || !spans || !bank_bytes || !count || count > 16u) return 0;
+    for (i = 0; i < count; ++i) {
+        unsigned long long bytes[3] = {0ull, 0ull, 0ull};
+        if (components[i].history) {
+            if (!yvx_u64_mul(components[i].capacity, components[i].value_width, &bytes[0]) ||
+                !yvx_u64_mul(bytes[0], sizeof(float), &bytes[0]) ||
+                !yvx_u64_mul(components[i].capacity, sizeof(unsigned long long), &bytes[1]))
+                return 0;
+        } else if (!yvx_u64_mul(components[i].kv_state_extent, sizeof(float), &bytes[0]) ||
+                   !yvx_u64_mul(components[i].score_state_extent, sizeof(float), &bytes[2])) {
+            return 0;
+        }
+        for (k = 0; k < 3u; ++k) {
+            unsigned long long aligned;
+            if (cursor > ULLONG_MAX - 7ull) return 0;
+            aligned = (cursor + 7ull) & ~7ull;
+            if (bytes[k] > ULLONG_MAX - aligned) return 0;
+            spans[i].offset[k] = aligned;
+            spans[i].bytes[k] = bytes[k];
+            cursor = aligned + bytes[k];
+        }
+    }
+    *bank_bytes = cursor;
+    return 1;
+}

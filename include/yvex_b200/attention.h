@@ -379,6 +379,24 @@ int yvex_b200_kv_page_touch(unsigned long long element_start, unsigned long long
 int yvex_b200_kv_sequence_shard(unsigned long long tokens, unsigned int shards, unsigned int index,
                                 unsigned long long block_tokens, unsigned long long *begin,
                                 unsigned long long *end);
+/* The byte layout of one layer's state bank in the reference: per component the spans
+ * [values, positions, auxiliary], each at the next 8-byte boundary of a running cursor
+ * (src/runtime/state_residency.c:44-54, 346-395). A history component (history != 0) holds
+ * capacity * value_width floats and capacity u64 positions; a rolling-compressor component
+ * holds its kv-state floats as values and its score-state floats as auxiliary. This is the
+ * payload layout the reference's checkpoints carry (src/runtime/state_store.c:1-9);
+ * yvx_cuda_kv_bank_transfer moves a pooled session into it and back. Returns 1, or 0 on
+ * overflow / bad arguments. */
+typedef struct {
+    int history;
+    unsigned long long capacity, value_width;            /* history */
+    unsigned long long kv_state_extent, score_state_extent; /* rolling */
+} yvex_b200_kv_bank_component;
+typedef struct {
+    unsigned long long offset[3], bytes[3];              /* values, positions, auxiliary */
+} yvex_b200_kv_bank_span;
+int yvex_b200_kv_bank_layout(const yvex_b200_kv_bank_component *components, unsigned int count,
+                             yvex_b200_kv_bank_span *spans, unsigned long long *bank_bytes);
 /* ---- block pool bookkeeping (host side; extension) ----------------------------
  * Which pool blocks a session owns in the pooled KV layout, with shared prefixes
  * (fork), copy-on-write of a shared partial block, and the committed / candidate

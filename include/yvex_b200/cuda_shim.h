@@ -117,7 +117,23 @@ typedef struct yvx_gqa_problem {
     unsigned long long query_head_stride; /* elements between query heads of a row; 0 = head_dim.
                                         Anything else (interleaved [head][Q|K|V][dim] rows,
                                         src/graph/numeric.c:1771-1826) takes the general kernel */
+    void *f32_staging;               /* optional, F32 problems only: yvx_cuda_gqa_f32_staging_bytes()
+                                        bytes of scratch. With it a prefill-sized F32 problem
+                                        (head_dim 128, more than 64 vectors per KV head, contiguous
+                                        KV) whose Q, K and V lanes are all representable in bf16 runs
+                                        on the tensor-core prefill kernel (bf16 operands staged here,
+                                        F32 accumulation and output; the reference's tiled path and
+                                        its tolerance: src/backend/cuda/transformer.c:493-677,
+                                        tests/unit/cuda/quant_qtype.c:2717-2866); any other lane value
+                                        is found on the device and the exact general kernel runs
+                                        instead, with no host round trip (three launches either way) */
+    const int *gate;                 /* kernels of this problem run only while *gate == gate_value;
+                                        NULL: always (set by the launcher for the path above) */
+    int gate_value;
 } yvx_gqa_problem;
+
+/* Scratch the tensor-core path of an F32 problem needs (0 when the shape never takes it). */
+unsigned long long yvx_cuda_gqa_f32_staging_bytes(const yvx_gqa_problem *problem);
 
 /* Scratch bytes `partials` must hold for a problem (0 when one split suffices). */
 unsigned long long yvx_cuda_gqa_partials_bytes(const yvx_gqa_problem *problem);
@@ -417,6 +433,31 @@ int yvx_cuda_rows_publish(const yvx_rows_publish_args *args, void *stream);
  * row and its index queries); each set as in yvx_cuda_rows_publish, results identical. */
 int yvx_cuda_rows_publish_batch(const yvx_rows_publish_args *sets, unsigned int count, void *stream);
 
+/* ---- a session's KV history between the block pool and the reference's state bank ------
+ * The reference keeps a layer's state in one byte buffer per bank with the components
+ * [values, positions, auxiliary] at 8-byte aligned offsets (src/runtime/state_residency.c:
+ * 346-395; yvex_b200_kv_bank_layout restates the offsets), values = F32 rows
+ * [row][K heads | V heads], positions = u64 per row; that bank is what its checkpoints carry
+ * (src/runtime/state_store.c:1-9). export: rows [0, kv_tokens[b]) of every session go from the
+ * bf16 pools behind the block table into the bank (positions[row] = position_base + row);
+ * import: the other way. Exact both ways for the bf16-representable values the reference
+ * stores; importing a value bf16 cannot hold is status 2. */
+typedef struct yvx_kv_bank_args {
+    unsigned int sessions, kv_heads, head_dim;
+    const int *kv_tokens;                     /* device [session] rows held; NULL: uniform */
+    unsigned int kv_tokens_uniform;
+    unsigned int row_capacity;                /* rows a session's bank holds */
+    void *bank;                               /* [session] banks, bank_session_bytes apart */
+    unsigned long long bank_session_bytes, values_offset, positions_offset, value_width;
+    unsigned long long position_base;
+    void *key_pool, *value_pool;              /* bf16 */
+    const int *block_table;
+    unsigned int block_tokens, block_table_stride, pool_blocks;
+    unsigned long long pool_token_stride, pool_head_stride, pool_block_stride;
+    int *status;
+} yvx_kv_bank_args;
+int yvx_cuda_kv_bank_transfer(const yvx_kv_bank_args *args, int export_direction, void *stream);
+
 /* ---- projections of the encoded attention operator ---------------------------------
  * Encoded weight rows times activation rows. Replaces, for the admitted encodings, the
  * reference's yvex_qtype_matvec / yvex_qtype_grouped_rows launches
@@ -561,7 +602,8 @@ int yvx_cuda_q8_kv_pack(const void *k_rows, const void *v_rows, unsigned int tok
 
 /* ---- seeded device-side fills for benchmark workloads ------------------------
  * No counterpart in the reference. Counter-based (splitmix64 of seed and
- * element index): N(0, sigma^2) as F32 or BF16, int8 lanes uniform in
+ * element index): N(0, sigma^2) as F32 or BF16 (dtype = -YVEX_DTYPE_F32: F32 storage of
+ * values rounded to bf16, what the reference's linears publish), int8 lanes uniform in
  * [-127, 127], f16 values uniform in [lo, hi). */
 int yvx_cuda_fill_normal(void *dst, int dtype, unsigned long long count,
                          unsigned long long seed, float sigma, void *stream);

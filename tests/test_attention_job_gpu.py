@@ -141,7 +141,7 @@ def test_typed_refusals(backend, oracle):
 def test_cancellation_between_the_phases_of_the_transaction(backend, oracle):
     # The predicate is polled on the host between the phases; the n-th poll cancels.
     stages = []
-    for cancel_at in range(1, 8):
+    for cancel_at in range(1, 7):
         polls = {"n": 0}
 
         def requested(_context, polls=polls, cancel_at=cancel_at):

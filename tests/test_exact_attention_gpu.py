@@ -132,7 +132,7 @@ def test_tile_sized_mha_repeats_bit_for_bit_and_rejects_nan(backend, oracle):
     b, _ = run(backend, q, k, v, 0, 1, 1, hd)
     assert a.tobytes() == b.tobytes()
     ref = oracle.gqa_attention(q, k, v, 0, 1, 1, hd)
-    assert np.all(np.abs(a - ref) < 2e-4 * (1 + np.abs(ref)))
+    assert np.all(np.abs(a - ref) < 2e-3 * (1 + np.abs(ref)))      # the reference's bar for this path
     for poisoned in ("q", "v"):
         qq, vv = q.copy(), v.copy()
         (qq if poisoned == "q" else vv)[3, 5] = np.nan
@@ -227,3 +227,43 @@ def test_op_attention_primitive(backend, oracle):
     o = backend.alloc("o", abi.DTYPE_F32, (4,))
     assert backend.op_attention(q, k, v, 3, 0, 0.5, 1, s, p, o) == 0
     assert np.all(np.abs(o.read() - vals[0]) < 1e-4)
+
+
+def _bf16_valued(rng, shape, scale=1.0):
+    x = rng.standard_normal(shape).astype(np.float32) * np.float32(scale)
+    return clori_b200.bf16_bits_to_f32(clori_b200.f32_to_bf16_bits(x))
+
+
+@pytest.mark.parametrize("tokens,hq,hkv,causal", [(257, 1, 1, True), (300, 40, 8, True), (513, 4, 4, False),
+                                                  (1030, 8, 2, True)])
+def test_prefill_sized_f32_problems_run_on_the_tensor_cores(backend, oracle, tokens, hq, hkv, causal):
+    # quant_qtype.c:2717-2866: inputs that bf16 holds exactly, 2e-3 * (1 + |ref|), identical repeats
+    rng = np.random.default_rng(tokens)
+    q, k, v = (_bf16_valued(rng, (tokens, h * 128), 0.5) for h in (hq, hkv, hkv))
+    out, facts = run(backend, q, k, v, 0, hq, hkv, 128, causal=causal)
+    assert facts.kernel_launches >= 5           # three staging launches, the gated pair
+    rows = np.r_[0:40, tokens - 40:tokens]
+    for first in (0, tokens - 40):
+        ref = oracle.gqa_f32_reference(q[first:first + 40], k, v, first, hq, hkv, 128, causal)
+        assert np.all(np.abs(out[first:first + 40] - ref) <= 2e-3 * (1 + np.abs(ref)))
+    again, _ = run(backend, q, k, v, 0, hq, hkv, 128, causal=causal)
+    assert np.array_equal(out.view(np.uint32), again.view(np.uint32))
+    # one lane that bf16 cannot hold: found on the device, the exact kernel answers (2e-4)
+    k2 = k.copy()
+    k2[tokens // 2, 5] = np.float32(0.3)
+    exact, _ = run(backend, q, k2, v, 0, hq, hkv, 128, causal=causal)
+    for first in (0, tokens - 40):
+        ref = oracle.gqa_f32_reference(q[first:first + 40], k2, v, first, hq, hkv, 128, causal)
+        assert np.all(np.abs(exact[first:first + 40] - ref) <= 2e-4 * (1 + np.abs(ref)))
+    assert rows.size == 80
+
+
+def test_prefill_sized_f32_problem_with_a_nan_is_refused(backend):
+    rng = np.random.default_rng(5)
+    q, k, v = (_bf16_valued(rng, (300, h * 128)) for h in (8, 2, 2))
+    v[17, 3] = np.nan
+    r = clori_b200.attention_requirement(300, 300, 0, 8, 2, 128)
+    out = backend.alloc("o", abi.DTYPE_F32, (300, 8 * 128))
+    with pytest.raises(clori_b200.YvexError) as refusal:
+        backend.attention_execute(r, backend.tensor("q", q), backend.tensor("k", k), backend.tensor("v", v), out)
+    assert refusal.value.code == abi.YVEX_ERR_FORMAT
