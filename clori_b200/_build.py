@@ -3,6 +3,11 @@
 Run as `python -m clori_b200._build` or through `__graft_entry__.build()`.
 nvcc cross-compiles without a GPU. Objects land in clori_b200/csrc/_obj/ and
 are rebuilt only when a source or header is newer.
+
+`python -m clori_b200._build --checked` builds libyvex_b200_checked.so beside it: the same
+sources with -DYVX_CHECKED, which compiles index checks in front of the kernels' global
+stores (a failing check records status 4 and skips the store). Setting the environment
+variable YVEX_B200_LIBRARY=checked makes the Python mirror (and so the tests) load it.
 """
 import os
 import subprocess
@@ -47,23 +52,26 @@ def _stale(target, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(verbose=False, ptxas_info=False):
-    os.makedirs(OBJ, exist_ok=True)
+def build(verbose=False, ptxas_info=False, checked=False):
+    obj_dir = OBJ + ("_checked" if checked else "")
+    lib = LIB.replace(".so", "_checked.so") if checked else LIB
+    define = ["-DYVX_CHECKED"] if checked else []
+    os.makedirs(obj_dir, exist_ok=True)
     cuda, host = _sources()
     headers = _headers()
     objects = []
     jobs = []
     for src in cuda:
-        obj = os.path.join(OBJ, os.path.basename(src) + ".o")
+        obj = os.path.join(obj_dir, os.path.basename(src) + ".o")
         objects.append(obj)
         if _stale(obj, [src] + headers):
-            cmd = [NVCC] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
+            cmd = [NVCC] + NVCC_FLAGS + define + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", src, "-o", obj]
             jobs.append((src, cmd))
     for src in host:
-        obj = os.path.join(OBJ, os.path.basename(src) + ".o")
+        obj = os.path.join(obj_dir, os.path.basename(src) + ".o")
         objects.append(obj)
         if _stale(obj, [src] + headers):
-            jobs.append((src, [CC] + CC_FLAGS + ["-c", src, "-o", obj]))
+            jobs.append((src, [CC] + CC_FLAGS + define + ["-c", src, "-o", obj]))
     procs = [(src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
              for src, cmd in jobs]
     failed = False
@@ -76,10 +84,10 @@ def build(verbose=False, ptxas_info=False):
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("libyvex_b200 build failed")
-    if jobs or _stale(LIB, objects):
-        subprocess.run([NVCC, "-shared", "-o", LIB] + objects + ["-lm"], check=True)
-    return LIB
+    if jobs or _stale(lib, objects):
+        subprocess.run([NVCC, "-shared", "-o", lib] + objects + ["-lm"], check=True)
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(verbose=True, ptxas_info="--ptxas" in sys.argv))
+    print(build(verbose=True, ptxas_info="--ptxas" in sys.argv, checked="--checked" in sys.argv))

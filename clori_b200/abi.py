@@ -7,7 +7,9 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libyvex_b200.so")
+# YVEX_B200_LIBRARY=checked selects the build with index checks compiled in (clori_b200/_build.py).
+LIB_PATH = os.path.join(PKG, "libyvex_b200_checked.so" if os.environ.get("YVEX_B200_LIBRARY") == "checked"
+                        else "libyvex_b200.so")
 
 # yvex_status (include/yvex_b200/abi.h)
 YVEX_OK = 0
@@ -358,6 +360,7 @@ ATTENTION_PHASE_PREFILL, ATTENTION_PHASE_DECODE = 0, 1
  VARIANT_ATTENTION_ENCODED, VARIANT_COUNT) = range(18)
 CAPABILITY_UNSUPPORTED, CAPABILITY_SUPPORTED, CAPABILITY_FAILED = 0, 1, 2
 CANCELLED_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
+STATE_RESOLVE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, u64, C.POINTER(u64))
 
 
 class JobWeight(C.Structure):
@@ -495,6 +498,10 @@ EXPORTED_SYMBOLS = [
     # attention_job.h
     "yvex_backend_attention_execute", "yvex_backend_attention_complete", "yvex_backend_query_capability",
     "yvex_b200_backend_weights_forget", "yvex_b200_kv_bank_layout",
+    "yvex_backend_resident_attach", "yvex_backend_resident_detach", "yvex_backend_resident_resolve",
+    "yvex_backend_state_residency_attach", "yvex_backend_state_residency_validate_generation",
+    "yvex_backend_state_residency_publish_generation", "yvex_backend_state_residency_detach",
+    "yvex_backend_state_residency_resolve",
     "yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
     "yvex_backend_capability_reason_name",
     # attention.h
@@ -597,6 +604,16 @@ def load():
                                                    P(AttentionJobFailure), P(Error)]
     lib.yvex_backend_attention_complete.argtypes = [vp, P(AttentionCompletion), C.c_int, P(Error)]
     lib.yvex_b200_backend_weights_forget.argtypes = [vp, P(Error)]
+    lib.yvex_backend_resident_attach.argtypes = [vp, vp, u64, P(DeviceTensor), u64, P(Error)]
+    lib.yvex_backend_resident_detach.argtypes = [vp, P(Error)]
+    lib.yvex_backend_resident_resolve.argtypes = [vp, vp, u64, P(u64)]
+    lib.yvex_backend_state_residency_attach.argtypes = [vp, vp, STATE_RESOLVE_FN, u64, P(Error)]
+    lib.yvex_backend_state_residency_validate_generation.argtypes = [vp, u64, P(Error)]
+    lib.yvex_backend_state_residency_publish_generation.restype = None
+    lib.yvex_backend_state_residency_publish_generation.argtypes = [vp, u64]
+    lib.yvex_backend_state_residency_detach.restype = None
+    lib.yvex_backend_state_residency_detach.argtypes = [vp]
+    lib.yvex_backend_state_residency_resolve.argtypes = [vp, vp, u64, P(u64)]
     lib.yvex_backend_query_capability.argtypes = [vp, C.c_int, P(CapabilityResult), P(Error)]
     for name in ("yvex_backend_operation_variant_name", "yvex_backend_capability_state_name",
                  "yvex_backend_capability_reason_name"):

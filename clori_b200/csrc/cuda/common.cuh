@@ -12,6 +12,7 @@
 #define YVX_STATUS_OK 0
 #define YVX_STATUS_NONFINITE 1
 #define YVX_STATUS_CONTRACT 2
+#define YVX_STATUS_CHECKED 4 /* an index check of a checked build (-DYVX_CHECKED) failed */
 #define YVX_STATUS_TIMEOUT 3
 
 // Maps a CUDA runtime error to the yvex_status the reference reports for
@@ -72,6 +73,15 @@ __device__ __forceinline__ unsigned short bf16_bits_rne(float value)
     if (low > 0x8000u || (low == 0x8000u && (high & 1u))) high += 1u;
     return (unsigned short)high;
 }
+
+// Checked builds (-DYVX_CHECKED; the stand-in for a memory checker where none can be run):
+// index and extent checks in front of the kernels' global stores. A failing check records
+// status 4 and the store is skipped; nothing traps. Compiled out of the product build.
+#ifdef YVX_CHECKED
+#define YVX_CHECKED_INDEX(condition, status) ((condition) ? true : (atomicCAS((status), 0, YVX_STATUS_CHECKED), false))
+#else
+#define YVX_CHECKED_INDEX(condition, status) (true)
+#endif
 
 // A session's length as the kernels use it. Lengths live in device memory, where the
 // host cannot check them; the host admitted `maximum` (it sized the split scratch, the

@@ -250,6 +250,9 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
         }
         const unsigned int row = v / group, qhead = kv_head * group + v % group;
         const unsigned long long item = ((unsigned long long)b * p.query_rows + row) * p.query_heads + qhead;
+        if (!YVX_CHECKED_INDEX(item < (unsigned long long)p.sessions * p.query_rows * p.query_heads &&
+                                   split < p.max_splits && qhead < p.query_heads, p.status))
+            continue;
         if (direct) {
             const float value = o / ll;
             if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);

@@ -231,6 +231,9 @@ gqa_split_generic_kernel(const yvx_gqa_problem p)
         const float inverse = ll > 0.0f ? 1.0f / ll : 0.0f;
         const unsigned long long item =
             ((unsigned long long)b * p.query_rows + row) * p.query_heads + qhead;
+        if (!YVX_CHECKED_INDEX(item < (unsigned long long)p.sessions * p.query_rows * p.query_heads &&
+                                   split < p.max_splits && qhead < p.query_heads && row < p.query_rows, p.status))
+            continue;
         for (unsigned int d = threadIdx.x; d < hd; d += kGenericThreads) {
             float o = 0.0f;
 #pragma unroll

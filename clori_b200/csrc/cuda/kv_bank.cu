@@ -31,6 +31,7 @@ kv_bank_transfer_kernel(const yvx_kv_bank_args a, const int export_direction)
     const unsigned long long pool_row =
         (unsigned long long)entry * a.pool_block_stride + (unsigned long long)(row % a.block_tokens) * a.pool_token_stride;
     const unsigned int kv_width = a.kv_heads * a.head_dim;
+    if (!YVX_CHECKED_INDEX(row < a.row_capacity && 2ull * kv_width <= a.value_width, a.status)) return;
     unsigned char *bank = reinterpret_cast<unsigned char *>(a.bank) + (unsigned long long)b * a.bank_session_bytes;
     float *values = reinterpret_cast<float *>(bank + a.values_offset) + (unsigned long long)row * a.value_width;
     unsigned long long *positions = reinterpret_cast<unsigned long long *>(bank + a.positions_offset);

@@ -120,6 +120,7 @@ qtype_matvec_kernel(const yvx_matvec_args a)
             float value = (float)acc[t];
             if (!isfinite(value)) atomicCAS(a.status, 0, YVX_STATUS_NONFINITE);
             if (a.round_bf16) value = bf16_bits_to_float(bf16_bits_rne(value));
+            if (!YVX_CHECKED_INDEX(token0 + t < a.tokens && group * a.rows + row < a.output_stride, a.status)) continue;
             a.output[(token0 + t) * a.output_stride + group * a.rows + row] = value;
         }
     }

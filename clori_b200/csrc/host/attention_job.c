@@ -30,6 +30,7 @@
 #include "yvex_b200/attention_job.h"
 
 #include <math.h>
+#include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -68,7 +69,7 @@ typedef struct {
     double *rope_frequency;
     void *select_workspace, *reduce_workspace;
     /* accounting */
-    unsigned long long launches, h2d, d2h, d2d, device_bytes;
+    unsigned long long launches, h2d, d2h, d2d, device_bytes, staged_state;
 } job_run;
 
 static int job_fail(job_run *run, yvex_backend_attention_failure_code code, const char *stage,
@@ -188,10 +189,20 @@ static int job_weight_resident(job_run *run, unsigned int slot, const void **dev
 {
     yvex_backend *b = run->backend;
     const yvex_backend_attention_weight *w = &run->job->weights[slot];
-    const unsigned long long fingerprint = weight_fingerprint(w->encoded, w->encoded_bytes);
+    unsigned long long address = 0ull, fingerprint;
     unsigned int i;
     void *memory = NULL;
     int rc;
+    /* the runtime's resident arena first: read in place, nothing is copied */
+    rc = yvex_backend_resident_resolve(b, w->encoded, w->encoded_bytes, &address);
+    if (rc == YVEX_BACKEND_RESIDENT_INVALID)
+        return job_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_COPY, weight_stage[slot], w->encoded_bytes, 0ull,
+                        YVEX_ERR_STATE, "resident weight mapping is invalid");
+    if (rc == YVEX_BACKEND_RESIDENT_HIT) {
+        *device = (const void *)(uintptr_t)address;
+        return YVEX_OK;
+    }
+    fingerprint = weight_fingerprint(w->encoded, w->encoded_bytes);
     for (i = 0; i < b->weight_count; ++i)
         if (b->weights[i].host == w->encoded && b->weights[i].bytes == w->encoded_bytes) {
             if (b->weights[i].fingerprint != fingerprint) {
@@ -228,6 +239,31 @@ static int job_weight_resident(job_run *run, unsigned int slot, const void **dev
     b->weights[b->weight_count].device = memory;
     b->weight_count++;
     *device = memory;
+    return YVEX_OK;
+}
+
+/* Session state (histories, positions, rolling states): a copy on the device when the runtime's
+ * state residency knows the range, an upload otherwise. */
+static int job_state(job_run *run, void *device, const void *host, unsigned long long bytes, const char *stage)
+{
+    unsigned long long address = 0ull;
+    int rc;
+    if (!bytes) return YVEX_OK;
+    rc = yvex_backend_state_residency_resolve(run->backend, host, bytes, &address);
+    if (rc == YVEX_BACKEND_RESIDENT_INVALID)
+        return job_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_COPY, stage, bytes, 0ull, YVEX_ERR_STATE,
+                        "persistent device state mapping is invalid");
+    if (rc != YVEX_BACKEND_RESIDENT_HIT) {
+        rc = yvx_cuda_upload_async(device, host, bytes, run->backend->stream);
+        if (rc != 0) return job_device_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_COPY, stage, rc);
+        run->h2d += bytes;
+    } else {
+        rc = yvx_cuda_copy_async(device, (const void *)(uintptr_t)address, bytes, run->backend->stream);
+        if (rc != 0) return job_device_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_COPY, stage, rc);
+        run->d2d += bytes;
+        run->staged_state += bytes;
+    }
+    run->work_pending = 1;
     return YVEX_OK;
 }
 
@@ -560,36 +596,36 @@ static int job_stage_inputs(job_run *run)
     if (rc == YVEX_OK) rc = yvx_cuda_stream_synchronize(b->stream) ? YVEX_ERR_BACKEND : YVEX_OK;
     free(positions);
     if (rc != YVEX_OK) return job_device_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_COPY, "cuda.attention.alloc.local_positions", rc);
-    rc = job_upload(run, run->local, job->local_kv, job->local_count * local_stride * sizeof(float),
+    rc = job_state(run, run->local, job->local_kv, job->local_count * local_stride * sizeof(float),
                     "cuda.attention.alloc.local_history");
     if (rc != YVEX_OK) return rc;
     if (job->attention_class != YVEX_BACKEND_ATTENTION_SWA) {
         const yvex_backend_attention_rolling *m = &job->main_rolling;
-        rc = job_upload(run, run->compressed, job->compressed_kv,
+        rc = job_state(run, run->compressed, job->compressed_kv,
                         job->compressed_count * run->compressed_stride * sizeof(float), "cuda.attention.alloc.compressed_history");
         if (rc == YVEX_OK)
-            rc = job_upload(run, run->compressed_positions, job->compressed_positions,
+            rc = job_state(run, run->compressed_positions, job->compressed_positions,
                             job->compressed_count * sizeof(unsigned long long), "cuda.attention.alloc.compressed_positions");
         if (rc == YVEX_OK)
-            rc = job_upload(run, run->rolling[0].before_kv, m->kv_state, m->state_slots * m->state_width * sizeof(float),
+            rc = job_state(run, run->rolling[0].before_kv, m->kv_state, m->state_slots * m->state_width * sizeof(float),
                             "cuda.attention.alloc.main_kv_state");
         if (rc == YVEX_OK)
-            rc = job_upload(run, run->rolling[0].before_score, m->score_state, m->state_slots * m->state_width * sizeof(float),
+            rc = job_state(run, run->rolling[0].before_score, m->score_state, m->state_slots * m->state_width * sizeof(float),
                             "cuda.attention.alloc.main_score_state");
         if (rc != YVEX_OK) return rc;
     }
     if (job->attention_class == YVEX_BACKEND_ATTENTION_CSA) {
         const yvex_backend_attention_rolling *x = &job->indexer_rolling;
-        rc = job_upload(run, run->indexer, job->indexer_kv, job->indexer_count * run->indexer_stride * sizeof(float),
+        rc = job_state(run, run->indexer, job->indexer_kv, job->indexer_count * run->indexer_stride * sizeof(float),
                         "cuda.attention.alloc.indexer_history");
         if (rc == YVEX_OK)
-            rc = job_upload(run, run->indexer_positions, job->indexer_positions,
+            rc = job_state(run, run->indexer_positions, job->indexer_positions,
                             job->indexer_count * sizeof(unsigned long long), "cuda.attention.alloc.indexer_positions");
         if (rc == YVEX_OK)
-            rc = job_upload(run, run->rolling[1].before_kv, x->kv_state, x->state_slots * x->state_width * sizeof(float),
+            rc = job_state(run, run->rolling[1].before_kv, x->kv_state, x->state_slots * x->state_width * sizeof(float),
                             "cuda.attention.alloc.index_kv_state");
         if (rc == YVEX_OK)
-            rc = job_upload(run, run->rolling[1].before_score, x->score_state, x->state_slots * x->state_width * sizeof(float),
+            rc = job_state(run, run->rolling[1].before_score, x->score_state, x->state_slots * x->state_width * sizeof(float),
                             "cuda.attention.alloc.index_score_state");
         if (rc != YVEX_OK) return rc;
     }
@@ -1108,6 +1144,8 @@ int yvex_backend_attention_execute(yvex_backend *backend, const yvex_backend_att
     output->d2h_bytes = run->d2h;
     output->d2d_bytes = run->d2d;
     output->device_bytes = output->peak_device_bytes = run->device_bytes;
+    output->device_state_staged_bytes = run->staged_state;
+    output->device_state_staged = run->staged_state != 0ull;
     output->device_synchronizations = rc == YVEX_OK ? 1ull : 0ull;
     if (job->device_completion) {
         job->device_completion->pending = 0;
@@ -1117,6 +1155,107 @@ int yvex_backend_attention_execute(yvex_backend *backend, const yvex_backend_att
     free(run);
     if (rc == YVEX_OK) yvex_error_clear(err);
     return rc;
+}
+
+/* ---- residency mappings (src/backend/residency.c:24-207) ------------------------------- */
+
+int yvex_backend_resident_attach(yvex_backend *backend, const unsigned char *host_base, unsigned long long bytes,
+                                 const yvex_device_tensor *device_tensor, unsigned long long generation,
+                                 yvex_error *err)
+{
+    const char *where = "backend.residency.attach";
+    if (!backend || backend->failed || !host_base || !bytes || !device_tensor || !yvx_tensor_owned(backend, device_tensor) ||
+        !device_tensor->bytes || !generation)
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, where, "a CUDA tensor of this backend covering the host range is required");
+    if (backend->resident_host_base)
+        return yvx_fail(err, YVEX_ERR_STATE, where, "backend residency mapping is already attached");
+    if (device_tensor->bytes < bytes)
+        return yvx_fail(err, YVEX_ERR_STATE, where, "the device tensor is smaller than the host range");
+    backend->resident_host_base = host_base;
+    backend->resident_host_bytes = bytes;
+    backend->resident_device_address = (unsigned long long)(uintptr_t)device_tensor->data;
+    backend->resident_generation = generation;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_backend_resident_detach(yvex_backend *backend, yvex_error *err)
+{
+    if (backend) {
+        backend->resident_host_base = NULL;
+        backend->resident_host_bytes = backend->resident_device_address = backend->resident_generation = 0ull;
+    }
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_backend_resident_resolve(const yvex_backend *backend, const unsigned char *host, unsigned long long bytes,
+                                  unsigned long long *device_address)
+{
+    unsigned long long offset;
+    if (device_address) *device_address = 0ull;
+    if (!backend || backend->failed || !host || !bytes || !device_address || !backend->resident_host_base ||
+        (uintptr_t)host < (uintptr_t)backend->resident_host_base)
+        return YVEX_BACKEND_RESIDENT_MISS;
+    offset = (unsigned long long)((uintptr_t)host - (uintptr_t)backend->resident_host_base);
+    if (offset > backend->resident_host_bytes || bytes > backend->resident_host_bytes - offset)
+        return YVEX_BACKEND_RESIDENT_MISS;
+    if (backend->resident_device_address > ULLONG_MAX - offset) return YVEX_BACKEND_RESIDENT_INVALID;
+    *device_address = backend->resident_device_address + offset;
+    return YVEX_BACKEND_RESIDENT_HIT;
+}
+
+int yvex_backend_state_residency_attach(yvex_backend *backend, const void *context,
+                                        yvex_backend_state_resolve_fn resolve, unsigned long long generation,
+                                        yvex_error *err)
+{
+    if (!backend || !context || !resolve || !generation)
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, "backend.state.attach", "CUDA backend and complete state resolver are required");
+    if (backend->state_residency_context)
+        return yvx_fail(err, YVEX_ERR_STATE, "backend.state.attach", "backend state residency is already attached");
+    backend->state_residency_context = context;
+    backend->state_residency_resolve = resolve;
+    backend->state_residency_generation = generation;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_backend_state_residency_validate_generation(yvex_backend *backend, unsigned long long generation,
+                                                     yvex_error *err)
+{
+    if (!backend || backend->failed || !generation)
+        return yvx_fail(err, YVEX_ERR_INVALID_ARG, "backend.state.publish", "attached state owner and generation are required");
+    if ((backend->state_residency_context == NULL) != (backend->state_residency_resolve == NULL))
+        return yvx_fail(err, YVEX_ERR_STATE, "backend.state.publish", "state generation owner is partially attached");
+    if (generation < backend->state_residency_generation)
+        return yvx_fail(err, YVEX_ERR_STATE, "backend.state.publish", "state generation cannot regress");
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+void yvex_backend_state_residency_publish_generation(yvex_backend *backend, unsigned long long generation)
+{
+    if (backend) backend->state_residency_generation = generation;
+}
+
+void yvex_backend_state_residency_detach(yvex_backend *backend)
+{
+    if (!backend) return;
+    backend->state_residency_context = NULL;
+    backend->state_residency_resolve = NULL;
+    backend->state_residency_generation = 0ull;
+}
+
+int yvex_backend_state_residency_resolve(const yvex_backend *backend, const void *host, unsigned long long bytes,
+                                         unsigned long long *device_address)
+{
+    int result;
+    if (device_address) *device_address = 0ull;
+    if (!backend || !host || !bytes || !device_address || !backend->state_residency_context ||
+        !backend->state_residency_resolve)
+        return YVEX_BACKEND_RESIDENT_MISS;
+    result = backend->state_residency_resolve(backend->state_residency_context, host, bytes, device_address);
+    return result == YVEX_BACKEND_RESIDENT_HIT && !*device_address ? YVEX_BACKEND_RESIDENT_INVALID : result;
 }
 
 /* Drops every resident weight (a caller that rewrites or unloads weights calls this; nothing

@@ -37,6 +37,15 @@ struct yvex_backend {
         void *device;
     } *weights;
     unsigned int weight_count, weight_capacity;
+    /* The runtime's resident weight arena (yvex_backend_resident_attach) and its resolver for
+     * mutable state (yvex_backend_state_residency_attach): borrowed mappings from host ranges
+     * to device memory the runtime owns (src/backend/residency.c:24-207). */
+    const unsigned char *resident_host_base;
+    unsigned long long resident_host_bytes, resident_device_address, resident_generation;
+    const void *state_residency_context;
+    int (*state_residency_resolve)(const void *context, const void *host, unsigned long long bytes,
+                                   unsigned long long *device_address);
+    unsigned long long state_residency_generation;
 };
 
 static inline int yvx_u64_add(unsigned long long a, unsigned long long b,

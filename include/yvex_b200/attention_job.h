@@ -222,6 +222,36 @@ int yvex_backend_attention_complete(yvex_backend *backend,
                                     yvex_backend_attention_completion *completion,
                                     int barrier_observed, yvex_error *err);
 
+/* ---- residency: the runtime's device copies of weights and of session state -------------
+ * include/yvex/internal/backend.h:200-202, 275-283, 315-322; src/backend/residency.c:24-207.
+ * The reference's runtime owns a device arena of weights and device banks of session state
+ * and tells the backend how host addresses map into them. With these attached, a job's
+ * weights are read where they lie (no upload) and its histories and rolling states are
+ * copied on the device instead of over PCIe. resolve returns HIT, MISS (outside every
+ * mapping: the job uploads) or INVALID. The backend owns none of the memory. */
+typedef int (*yvex_backend_state_resolve_fn)(const void *context, const void *host, unsigned long long bytes,
+                                             unsigned long long *device_address);
+typedef enum {
+    YVEX_BACKEND_RESIDENT_INVALID = -1,
+    YVEX_BACKEND_RESIDENT_MISS = 0,
+    YVEX_BACKEND_RESIDENT_HIT = 1
+} yvex_backend_resident_result;
+int yvex_backend_resident_attach(yvex_backend *backend, const unsigned char *host_base, unsigned long long bytes,
+                                 const yvex_device_tensor *device_tensor, unsigned long long generation,
+                                 yvex_error *err);
+int yvex_backend_resident_detach(yvex_backend *backend, yvex_error *err);
+int yvex_backend_resident_resolve(const yvex_backend *backend, const unsigned char *host, unsigned long long bytes,
+                                  unsigned long long *device_address);
+int yvex_backend_state_residency_attach(yvex_backend *backend, const void *context,
+                                        yvex_backend_state_resolve_fn resolve, unsigned long long generation,
+                                        yvex_error *err);
+int yvex_backend_state_residency_validate_generation(yvex_backend *backend, unsigned long long generation,
+                                                     yvex_error *err);
+void yvex_backend_state_residency_publish_generation(yvex_backend *backend, unsigned long long generation);
+void yvex_backend_state_residency_detach(yvex_backend *backend);
+int yvex_backend_state_residency_resolve(const yvex_backend *backend, const void *host, unsigned long long bytes,
+                                         unsigned long long *device_address);
+
 /* No counterpart in the reference. The job keeps encoded weights resident on the device,
  * found again by host address, size and a sampled content fingerprint; a caller that
  * rewrites weights in place, or unloads a model, drops them with this call. */

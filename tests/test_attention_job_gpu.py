@@ -93,6 +93,64 @@ def test_job_through_device_tensors_and_without_evidence_spans(backend, oracle):
     assert rc == 0 and out.h2d_bytes < first_upload // 4
 
 
+def test_job_reads_resident_weights_and_state_where_the_runtime_keeps_them(backend, oracle, library):
+    # The runtime's side of src/backend/residency.c: one device arena mirroring a host range
+    # of weights, and a resolver from host state ranges to device copies.
+    job = job_cases.build(oracle, abi.ATTENTION_CSA, 4, 45, seed=11)
+    want = job_cases.evaluate(oracle, job)
+    rc, plain, uploaded, _, err = job_cases.run(backend, job, want=("output",))
+    assert rc == 0 and plain.device_state_staged == 0
+    a, b = uploaded["output"].astype(np.float64), want["output"].astype(np.float64)
+    assert np.all(np.abs(a - b) <= 5e-4 + 2.0 ** -6 * np.abs(b).max(axis=1, keepdims=True))
+    # weights: pack every encoded weight into one host arena, mirror it on the device
+    encoded = [job.weights[slot][0] for slot in sorted(job.weights)]
+    offsets = np.cumsum([0] + [(e.nbytes + 255) & ~255 for e in encoded])
+    arena = np.zeros(int(offsets[-1]), np.uint8)
+    for slot, e, at in zip(sorted(job.weights), encoded, offsets):
+        arena[at:at + e.nbytes] = e.reshape(-1)
+        job.struct.weights[slot].encoded = arena.ctypes.data + int(at)
+    mirror = backend.tensor("weights", arena.view(np.int8), dtype=abi.DTYPE_I8)
+    err = abi.Error()
+    assert library.yvex_backend_resident_attach(backend.handle, arena.ctypes.data, arena.nbytes, C.byref(mirror.struct), 1,
+                                                C.byref(err)) == 0, err.message
+    assert library.yvex_backend_resident_attach(backend.handle, arena.ctypes.data, arena.nbytes, C.byref(mirror.struct), 1,
+                                                C.byref(err)) == abi.YVEX_ERR_STATE
+    address = abi.u64()
+    assert library.yvex_backend_resident_resolve(backend.handle, arena.ctypes.data + 300, 10, C.byref(address)) == 1
+    assert address.value == mirror.data_ptr + 300
+    assert library.yvex_backend_resident_resolve(backend.handle, arena.ctypes.data + arena.nbytes - 4, 10, C.byref(address)) == 0
+    # state: device copies of the histories and rolling states, found by host address
+    state = {}
+    for array in (job.local, job.local_positions, job.compressed, job.compressed_positions, job.indexer):
+        state[array.ctypes.data] = (array.nbytes, backend.tensor("s", array.view(np.int8).reshape(-1), dtype=abi.DTYPE_I8))
+    for kv, score, _, _, _ in job.rolling.values():
+        for array in (kv, score):
+            state[array.ctypes.data] = (array.nbytes, backend.tensor("s", array.view(np.int8).reshape(-1), dtype=abi.DTYPE_I8))
+    calls = {"hit": 0, "miss": 0}
+
+    def resolve(_context, host, nbytes, out):
+        for base, (size, tensor) in state.items():
+            if base <= host and host + nbytes <= base + size:
+                out[0] = tensor.data_ptr + (host - base)
+                calls["hit"] += 1
+                return 1
+        calls["miss"] += 1
+        return 0
+    callback = abi.STATE_RESOLVE_FN(resolve)
+    marker = C.c_int(1)
+    assert library.yvex_backend_state_residency_attach(backend.handle, C.byref(marker), callback, 5, C.byref(err)) == 0
+    assert library.yvex_backend_state_residency_validate_generation(backend.handle, 4, C.byref(err)) == abi.YVEX_ERR_STATE
+    assert library.yvex_backend_state_residency_validate_generation(backend.handle, 6, C.byref(err)) == 0
+    rc, resident, got, _, err = job_cases.run(backend, job, want=("output",))
+    assert rc == 0, (err.where, err.message)
+    assert np.array_equal(got["output"], uploaded["output"])      # same numbers either way
+    assert calls["hit"] >= 8 and resident.device_state_staged == 1 and resident.device_state_staged_bytes > 0
+    assert resident.h2d_bytes < plain.h2d_bytes // 10           # only the new tokens' input goes over the bus
+    library.yvex_backend_state_residency_detach(backend.handle)
+    assert library.yvex_backend_resident_detach(backend.handle, C.byref(err)) == 0
+    assert library.yvex_backend_resident_resolve(backend.handle, arena.ctypes.data, 10, C.byref(address)) == 0
+
+
 def test_typed_refusals(backend, oracle):
     def refused(mutate, code, status, stage=None):
         job = job_cases.build(oracle, abi.ATTENTION_CSA, 2, 9, seed=3)
