@@ -369,6 +369,8 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
     q = _alloc(lib, hq * hd * 4)
     out = _alloc(lib, hq * hd * 4)
     status = _alloc(lib, 4)
+    tickets = _alloc(lib, 8 * hkv)
+    lib.yvx_cuda_memset_async(tickets, 0, 8 * hkv, backend.stream)
     lib.yvx_cuda_fill_normal(k, abi.DTYPE_F32, copies * kv_elems, 101, 1.0, backend.stream)
     lib.yvx_cuda_fill_normal(v, abi.DTYPE_F32, copies * kv_elems, 102, 1.0, backend.stream)
     lib.yvx_cuda_fill_normal(q, abi.DTYPE_F32, hq * hd, 103, 1.0, backend.stream)
@@ -388,7 +390,7 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
         lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
         if scratch is None:
             scratch = _alloc(lib, max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
-        p.partials, p.status = scratch, status
+        p.partials, p.status, p.tickets = scratch, status, tickets
         problems.append(p)
     main, combine, launches = _timed_launches(lib, backend, problems, repeats)
     # full-size parity of the copy the last launch read, against the CPU oracle
@@ -410,7 +412,7 @@ def bench_decode_f32(lib, backend, abi, peak, repeats):
               "tokens_per_s": 1.0 / (_timed_launches.step_ms * 1e-3),
               "l2": f"{copies} rotating KV copies ({copies * 2 * kv_elems * 4 / 1e6:.0f} MB) exceed L2",
               "chunk_tokens": problems[0].chunk_tokens, "status_word": int(st[0])}
-    for ptr in (k, v, q, out, status, scratch):
+    for ptr in (k, v, q, out, status, scratch, tickets):
         lib.yvx_cuda_free(ptr)
     return result, host
 

@@ -139,7 +139,7 @@ class GqaProblem(C.Structure):
         ("chunk_tokens", C.c_uint), ("max_splits", C.c_uint),
         ("partials", C.c_void_p), ("partial_output", C.c_void_p), ("status", C.c_void_p),
         ("force_general", C.c_int), ("query_head_stride", u64),
-        ("f32_staging", C.c_void_p), ("gate", C.c_void_p), ("gate_value", C.c_int),
+        ("f32_staging", C.c_void_p), ("gate", C.c_void_p), ("gate_value", C.c_int), ("tickets", C.c_void_p),
     ]
 
 
@@ -162,7 +162,7 @@ class LatentReduceArgs(C.Structure):
 class LseExchange(C.Structure):
     """yvx_lse_exchange (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [("ranks", C.c_uint), ("rank", C.c_uint), ("epoch", C.c_uint),
-                ("gather", C.c_void_p), ("arrivals", C.c_void_p)]
+                ("gather", C.c_void_p), ("arrivals", C.c_void_p), ("one_launch", C.c_int)]
 
 
 class KvCopy(C.Structure):

@@ -1,0 +1,177 @@
+// The cross-GPU exchange of (o, m, l) rows over NVLink peer memory, shared by the exchange
+// kernel and by the attention kernels that fold it into their own tail.
+//
+// Every rank owns an exchange area [2 epochs][ranks][items][head_dim + 2] floats, [items]
+// arrival counters and (behind them) split tickets, and maps its peers' areas (CUDA IPC).
+// For one item a group of threads
+//   1. stores this rank's row into slot `rank` of the item in EVERY rank's area (peer stores),
+//      fences system-wide and adds 1 to the item's arrival counter on every rank;
+//   2. waits, bounded, until its own counter shows all ranks' rows of this epoch;
+//   3. folds the ranks' rows in rank order (deterministic) and writes the output.
+// Counters only grow (epoch * ranks is the target) and the area is double-buffered by epoch
+// parity, so nothing is reset and a rank cannot overwrite rows a peer still reads: finishing
+// an epoch needs every peer's row of that epoch. Plain peer loads and stores only.
+#pragma once
+
+#include "combine.cuh"
+
+namespace yvx {
+
+constexpr unsigned int kExchangeSpinLimit = 1u << 23;  // about a second of 100 ns polls, then status 3
+
+// Release / acquire at system scope (peers are other GPUs).
+__device__ __forceinline__ void fence_acq_rel_system()
+{
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+
+// Steps 1-3 for one item. `row` [hd + 2] and `flag` live in shared memory; the `threads`
+// participants (tid 0 .. threads-1, at least x.ranks of them) meet at Sync::sync(). Returns
+// false, with status 3 recorded, when the wait ran out.
+template <typename Sync>
+__device__ __forceinline__ bool exchange_item(const yvx_lse_exchange &x, unsigned int rank, unsigned int items,
+                                              unsigned int item, unsigned int hd, const float *row, int *flag,
+                                              unsigned int tid, unsigned int threads, void *output,
+                                              int output_dtype, unsigned long long output_index, int *status)
+{
+    const unsigned int stride = hd + 2u;
+    const unsigned long long slot = ((unsigned long long)(x.epoch & 1u) * x.ranks + rank) * items + item;
+    for (unsigned int r = 0; r < x.ranks; ++r) {
+        float *dst = x.gather[r] + slot * stride;
+        for (unsigned int d = tid; d < stride; d += threads) dst[d] = row[d];
+    }
+    Sync::sync();
+    // Thread r tells rank r. Its system-wide fence after the barrier orders every thread's peer
+    // stores (they happen before it through the barrier) ahead of the count.
+    if (tid < x.ranks) {
+        fence_acq_rel_system();
+        atomicAdd_system(x.arrivals[tid] + item, 1u);
+    }
+    if (tid == 0) {
+        const volatile unsigned int *counter = x.arrivals[rank] + item;
+        const unsigned int target = x.epoch * x.ranks;
+        int ok = 0;
+        for (unsigned int spin = 0; spin < kExchangeSpinLimit; ++spin) {
+            if ((int)(*counter - target) >= 0) {
+                ok = 1;
+                break;
+            }
+            __nanosleep(100);
+        }
+        // Acquire side: this fence, then the barrier, order every thread's reads of the peers'
+        // rows after the observation of the counter.
+        fence_acq_rel_system();
+        *flag = ok;
+    }
+    Sync::sync();
+    if (!*flag) {
+        if (tid == 0) atomicCAS(status, 0, YVX_STATUS_TIMEOUT);
+        return false;
+    }
+    // Peers wrote the rows, so bypass L1; the loads of up to eight ranks are issued before the
+    // first use (one trip to L2 per batch).
+    const float *base = x.gather[rank] + ((unsigned long long)(x.epoch & 1u) * x.ranks * items + item) * stride;
+    const unsigned long long rank_stride = (unsigned long long)items * stride;
+    for (unsigned int d = tid; d < hd; d += threads) {
+        float run_max = -INFINITY, run_sum = 0.0f, acc = 0.0f;
+        for (unsigned int r0 = 0; r0 < x.ranks; r0 += 8u) {
+            float mr[8], lr[8], orow[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const bool live = r0 + u < x.ranks;
+                const float *part = base + (unsigned long long)(live ? r0 + u : r0) * rank_stride;
+                mr[u] = live ? __ldcg(part + hd) : -INFINITY;
+                lr[u] = __ldcg(part + hd + 1u);
+                orow[u] = __ldcg(part + d);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (mr[u] == -INFINITY) continue;  // empty shard or past the last rank
+                const float new_max = fmaxf(run_max, mr[u]);
+                const float keep = expf(run_max - new_max);
+                const float weight = lr[u] * expf(mr[u] - new_max);
+                run_sum = fmaf(run_sum, keep, weight);
+                acc = fmaf(acc, keep, orow[u] * weight);
+                run_max = new_max;
+            }
+        }
+        const float value = acc / run_sum;
+        if (!isfinite(value)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
+        store_output(output, output_dtype, output_index + d, value);
+    }
+    return true;
+}
+
+// The fold of one item's split partials by `WARPS` warps that meet at Sync::sync(): warp w takes
+// splits w, w + WARPS, ...; a lane owns four dimensions (head_dim 128); the warps' running states
+// are merged in warp order through `scratch` ([WARPS][head_dim + 2] floats of shared memory) into
+// `row` [head_dim + 2] = (o normalised, m, l). Deterministic.
+template <int WARPS, typename Sync>
+__device__ __forceinline__ void fold_splits_128(const float *parts, unsigned int count, float *scratch, float *row,
+                                                unsigned int tid)
+{
+    constexpr unsigned int kHd = 128u, kStride = kHd + 2u;
+    const unsigned int warp = tid >> 5, lane = tid & 31u;
+    float run_max = -INFINITY, run_sum = 0.0f;
+    float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (unsigned int j0 = warp; j0 < count; j0 += WARPS * 4u) {
+        float2 lo[4], hi[4];
+        float mj[4], lj[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const unsigned int j = j0 + u * WARPS;
+            const bool live = j < count;
+            const float *part = parts + (unsigned long long)(live ? j : j0) * kStride;
+            lo[u] = __ldcg(reinterpret_cast<const float2 *>(part + 4u * lane));
+            hi[u] = __ldcg(reinterpret_cast<const float2 *>(part + 4u * lane + 2u));
+            mj[u] = live ? __ldcg(part + kHd) : -INFINITY;
+            lj[u] = __ldcg(part + kHd + 1u);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (mj[u] == -INFINITY) continue;
+            const float fresh = fmaxf(run_max, mj[u]);
+            const float keep = expf(run_max - fresh);
+            const float weight = lj[u] * expf(mj[u] - fresh);
+            run_sum = fmaf(run_sum, keep, weight);
+            total.x = fmaf(total.x, keep, lo[u].x * weight);
+            total.y = fmaf(total.y, keep, lo[u].y * weight);
+            total.z = fmaf(total.z, keep, hi[u].x * weight);
+            total.w = fmaf(total.w, keep, hi[u].y * weight);
+            run_max = fresh;
+        }
+    }
+    float *mine = scratch + warp * kStride;
+    mine[4u * lane] = total.x;
+    mine[4u * lane + 1u] = total.y;
+    mine[4u * lane + 2u] = total.z;
+    mine[4u * lane + 3u] = total.w;
+    if (lane == 0) {
+        mine[kHd] = run_max;
+        mine[kHd + 1u] = run_sum;
+    }
+    Sync::sync();
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, scratch[w * kStride + kHd]);
+    float ll = 0.0f, scale_w[WARPS];
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+        const float mw = scratch[w * kStride + kHd];
+        scale_w[w] = mw == -INFINITY ? 0.0f : expf(mw - mm);
+        ll = fmaf(scratch[w * kStride + kHd + 1u], scale_w[w], ll);
+    }
+    for (unsigned int d = tid; d < kHd; d += WARPS * 32u) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) o = fmaf(scratch[w * kStride + d], scale_w[w], o);
+        row[d] = ll > 0.0f ? o / ll : 0.0f;
+    }
+    if (tid == 0) {
+        row[kHd] = mm;
+        row[kHd + 1u] = ll;
+    }
+    Sync::sync();
+}
+
+}  // namespace yvx

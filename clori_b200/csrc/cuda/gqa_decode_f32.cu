@@ -1,11 +1,15 @@
 // Decode / verify over F32 KV rows under the exact-F32 contract (head_dim 128,
 // at most 8 query vectors per KV head, contiguous KV), for launches too short
-// for a streaming loop to reach the DRAM rate: a CTA's chunk (up to 112 tokens
-// of K and V for one KV head) is requested with TMA at the start, in sub-chunks
-// of 16 tokens with their own mbarriers, and each warp consumes sub-chunks as
-// they land. Six sub-chunk buffers (96 KB, two CTAs per SM); a seventh sub-chunk
-// goes into buffer 0 once the warp that owns that buffer has consumed it. All
-// arithmetic is single-precision FMA.
+// for a streaming loop to reach the DRAM rate: a CTA's whole chunk (up to 112
+// tokens of K and V for one KV head, 112 KB) is requested with TMA at the start,
+// in sub-chunks of 16 tokens with their own mbarriers, and each warp consumes
+// sub-chunks as they land. Seven sub-chunk buffers: two CTAs fit an SM only because
+// nothing else lives in shared memory (the softmax weights of a sub-chunk go
+// through the K rows the warp has just taken into registers; the merge reuses
+// consumed buffers). With tickets the kernel also folds its own splits: the CTA
+// that arrives last for a KV head combines every split's partial in split order
+// and writes the output, so a decode step is ONE launch. All arithmetic is
+// single-precision FMA.
 //
 //   scores   lanes own 4 dims; the 16 partial dot products per vector are summed
 //            across lanes by a halving exchange (16 shuffles for 16 tokens, four
@@ -17,6 +21,7 @@
 // Same partial format and combine as the general kernel, which it replaces for
 // these shapes (reference: yvex_gqa_f32_body, src/backend/cuda/
 // transformer_kernels.cu:137-238, one CTA per query head walking all rows).
+#include "exchange.cuh"
 #include "pipeline.cuh"
 
 namespace yvx {
@@ -28,9 +33,10 @@ constexpr int kF32Sub = 16;                       // tokens per sub-chunk
 #define F32_MAXSUBS 7
 #endif
 constexpr int kF32MaxSubs = F32_MAXSUBS;                    // 112 tokens per CTA
-constexpr int kF32Buffers = 6;                    // sub-chunk buffers (K and V each)
+constexpr int kF32Buffers = kF32MaxSubs;           // one buffer per sub-chunk: everything is in flight at once
 constexpr int kF32SubBytes = kF32Sub * kF32HeadDim * 4;          // 8 KB
-constexpr int kF32SmemBytes = 2 * kF32Buffers * kF32SubBytes + 1024 + 256;
+constexpr int kF32TailBytes = 384;                // barriers, merge statistics, the arrival flag
+constexpr int kF32SmemBytes = 2 * kF32Buffers * kF32SubBytes + kF32TailBytes;
 constexpr unsigned int kF32MaxSplits = 256;
 
 struct F32Maps {
@@ -65,19 +71,25 @@ __device__ __forceinline__ void reduce16x4(float (&x)[4][16], unsigned int lane,
     for (int v = 0; v < 4; ++v) total[v] = x[v][0] + __shfl_xor_sync(0xffffffffu, x[v][0], 1);
 }
 
+struct F32BlockSync {
+    static __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+
 // grid: x = split, y = kv head, z = session. VT = vectors per CTA (4 or 8).
 template <int VT>
 __global__ void __launch_bounds__(kF32Threads)
-gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps maps, const int head_major)
+gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps maps, const int head_major,
+                      const int cooperative)
 {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>(
-        (reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    // No static shared memory: the dynamic window starts on a 1024-byte boundary and the two
+    // resident CTAs of an SM need every byte (2 x (112 KB + 256 B + the 1 KB the system keeps)).
+    extern __shared__ __align__(1024) unsigned char smem[];
     float *k_smem = reinterpret_cast<float *>(smem);
     float *v_smem = reinterpret_cast<float *>(smem + kF32Buffers * kF32SubBytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * kF32Buffers * kF32SubBytes);
-    __shared__ float weights[kF32Warps][VT][kF32Sub];
-    __shared__ float merge_m[kF32Warps][VT], merge_l[kF32Warps][VT];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * kF32Buffers * kF32SubBytes);     // 7 x 8 B
+    float (*merge_m)[VT] = reinterpret_cast<float (*)[VT]>(smem + 2 * kF32Buffers * kF32SubBytes + 64);
+    float (*merge_l)[VT] = merge_m + kF32Warps;                                               // 2 x 128 B at most
+    int *arrival = reinterpret_cast<int *>(smem + 2 * kF32Buffers * kF32SubBytes + kF32TailBytes - 4);
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int group = p.query_heads / p.kv_heads;
@@ -117,9 +129,10 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
         fence_barrier_init();
     }
     __syncthreads();
-    // Warp 3 owns a single buffer, so its first lane has time to issue the requests.
+    // Every sub-chunk of the CTA is requested now (warp 3 owns a single buffer, so its first lane
+    // has the time).
     if (threadIdx.x == 96)
-        for (unsigned int i = 0; i < min(subs, (unsigned int)kF32Buffers); ++i) request(i);
+        for (unsigned int i = 0; i < subs; ++i) request(i);
 
     // Per-vector query (scores in log2 units), visibility limit, running state.
     float4 q[VT];
@@ -144,18 +157,22 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
     }
 
     bool ok = true;
-    // A buffer belongs to one warp (buffer % 4), so the warp that has consumed
-    // sub-chunk sb can itself request sub-chunk sb + 6 into the same buffer.
+    // A buffer (= a sub-chunk) belongs to one warp (buffer % 4).
     for (unsigned int sb = 0; sb < subs; ++sb) {
-        const unsigned int buffer = sb % kF32Buffers;
+        const unsigned int buffer = sb;
         if (buffer % kF32Warps != warp) continue;
-        if (ok) ok = mbar_wait(&bars[buffer], (sb / kF32Buffers) & 1u);
-        const float *kb = k_smem + buffer * kF32Sub * kF32HeadDim, *vb = v_smem + buffer * kF32Sub * kF32HeadDim;
+        if (ok) ok = mbar_wait(&bars[buffer], 0u);
+        float *kb = k_smem + buffer * kF32Sub * kF32HeadDim;
+        const float *vb = v_smem + buffer * kF32Sub * kF32HeadDim;
+        // the sub-chunk's softmax weights [VT][16] go where its K row 0 was: the rows are in
+        // registers by then, and the buffer is this warp's alone
+        float (*weights)[kF32Sub] = reinterpret_cast<float (*)[kF32Sub]>(kb);
         const long long base = (long long)t0 + (long long)sb * kF32Sub;
         const unsigned int valid = min((unsigned int)kF32Sub, t1 - (unsigned int)base);
         float4 krow[kF32Sub];
 #pragma unroll
         for (int t = 0; t < kF32Sub; ++t) krow[t] = reinterpret_cast<const float4 *>(kb + t * kF32HeadDim)[lane];
+        __syncwarp();  // every lane holds its K before any lane stores a weight over row 0
 #pragma unroll
         for (int v0 = 0; v0 < VT; v0 += 4) {
             float part[4][kF32Sub], score[4];
@@ -187,7 +204,7 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
                 m[v] = fresh;
                 l[v] = l[v] * keep + ((lane & 1u) ? 0.0f : weight);
                 acc[v] = make_float4(acc[v].x * keep, acc[v].y * keep, acc[v].z * keep, acc[v].w * keep);
-                if (!(lane & 1u)) weights[warp][v][lane >> 1] = weight;
+                if (!(lane & 1u)) weights[v][lane >> 1] = weight;
             }
         }
         __syncwarp();
@@ -200,7 +217,7 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
                 vrow[j] = reinterpret_cast<const float4 *>(vb + (4 * t4 + j) * kF32HeadDim)[lane];
 #pragma unroll
             for (int v = 0; v < VT; ++v) {
-                const float4 w = *reinterpret_cast<const float4 *>(&weights[warp][v][4 * t4]);
+                const float4 w = *reinterpret_cast<const float4 *>(&weights[v][4 * t4]);
                 const float ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -213,10 +230,6 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
             }
         }
         __syncwarp();
-        if (sb + kF32Buffers < subs && lane == 0) {
-            fence_proxy_async();  // this warp's reads of the buffer come before the next copy into it
-            request(sb + kF32Buffers);
-        }
     }
     if (!__all_sync(0xffffffffu, ok) && lane == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
 
@@ -236,6 +249,7 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
     }
     __syncthreads();
     const bool direct = p.max_splits == 1u;
+    const bool fold_here = !direct && p.tickets != nullptr;
     const unsigned int d = threadIdx.x;  // one head dimension per thread
     for (unsigned int v = 0; v < min((unsigned int)VT, vectors); ++v) {
         float mm = -INFINITY;
@@ -265,6 +279,77 @@ gqa_decode_f32_kernel(const yvx_gqa_problem p, const __grid_constant__ F32Maps m
                 part[kF32HeadDim + 1] = ll;
             }
         }
+    }
+    if (!fold_here) return;
+
+    // ---- the fold, inside the same launch ---------------------------------------------------
+    // Every CTA publishes its partials (fence) and takes a ticket of its (session, KV head).
+    // cooperative != 0 (every CTA of the grid is resident): the CTAs with split < vectors wait,
+    // bounded, for all the group's tickets and fold one vector each, four warps sharing its
+    // splits, so the folds of a KV head run side by side. Otherwise whichever CTA arrives last
+    // folds all the group's vectors, and nobody waits for anybody.
+    __threadfence();
+    __syncthreads();
+    const unsigned int live_splits = min((kv_tokens + p.chunk_tokens - 1u) / p.chunk_tokens, p.max_splits);
+    int *ticket = p.tickets + 2ull * ((unsigned long long)b * p.kv_heads + kv_head);
+    const unsigned int folders = min(min((unsigned int)VT, vectors), live_splits);
+    float *fold_scratch = k_smem;                                   // [4][130]: the buffers are consumed
+    float *fold_row = fold_scratch + kF32Warps * (kF32HeadDim + 2);
+    if (cooperative) {
+        if (threadIdx.x == 0) atomicAdd(ticket, 1);
+        if (split >= folders) return;
+        if (threadIdx.x == 0) {
+            const volatile int *counter = ticket;
+            int ok = 0;
+            for (unsigned int spin = 0; spin < (1u << 22); ++spin) {
+                if (*counter >= (int)live_splits) {
+                    ok = 1;
+                    break;
+                }
+                __nanosleep(20);
+            }
+            *arrival = ok;
+            // the last folder to have seen the full count leaves both counters at zero
+            if (ok && atomicAdd(ticket + 1, 1) == (int)folders - 1) {
+                ticket[1] = 0;
+                ticket[0] = 0;
+            }
+        }
+        __syncthreads();
+        if (!*arrival) {
+            if (threadIdx.x == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+            return;
+        }
+        __threadfence();
+        for (unsigned int v = split; v < min((unsigned int)VT, vectors); v += folders) {
+            const unsigned int row = v / group, qhead = kv_head * group + v % group;
+            const unsigned long long item = ((unsigned long long)b * p.query_rows + row) * p.query_heads + qhead;
+            fold_splits_128<kF32Warps, F32BlockSync>(p.partials + item * p.max_splits * (kF32HeadDim + 2ull), live_splits,
+                                                     fold_scratch, fold_row, threadIdx.x);
+            const float value = fold_row[d];
+            if (!isfinite(value) || !(fold_row[kF32HeadDim + 1] > 0.0f)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+            store_output(p.output, p.output_dtype, item * kF32HeadDim + d, value);
+            __syncthreads();
+        }
+        return;
+    }
+    if (threadIdx.x == 0) {
+        const int taken = atomicAdd(ticket, 1);
+        *arrival = taken == (int)live_splits - 1;
+        if (*arrival) *ticket = 0;  // left at zero for the next call
+    }
+    __syncthreads();
+    if (!*arrival) return;
+    __threadfence();
+    for (unsigned int v = 0; v < min((unsigned int)VT, vectors); ++v) {
+        const unsigned int row = v / group, qhead = kv_head * group + v % group;
+        const unsigned long long item = ((unsigned long long)b * p.query_rows + row) * p.query_heads + qhead;
+        fold_splits_128<kF32Warps, F32BlockSync>(p.partials + item * p.max_splits * (kF32HeadDim + 2ull), live_splits,
+                                                 fold_scratch, fold_row, threadIdx.x);
+        const float value = fold_row[d];
+        if (!isfinite(value) || !(fold_row[kF32HeadDim + 1] > 0.0f)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+        store_output(p.output, p.output_dtype, item * kF32HeadDim + d, value);
+        __syncthreads();
     }
 }
 
@@ -367,17 +452,47 @@ int gqa_decode_f32_launch(const yvx_gqa_problem &p, cudaStream_t stream)
     const unsigned int vectors = p.query_rows * (p.query_heads / p.kv_heads);
     const dim3 grid(p.max_splits, p.kv_heads, p.sessions);
     cudaError_t error;
+    const bool fold_here = p.tickets && p.max_splits > 1u;
+    if (fold_here) {
+        // every CTA resident at once (the planner's single wave): a cooperative launch lets the
+        // group's own CTAs fold side by side; a grid that does not fit folds in its last arrivals
+        int device = 0, sms = 0, per_sm = 0, coop = 0;
+        const void *kernel = vectors <= 4u ? (const void *)gqa_decode_f32_kernel<4> : (const void *)gqa_decode_f32_kernel<8>;
+        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
+        if (error == cudaSuccess) error = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
+        if (cudaGetDevice(&device) == cudaSuccess &&
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
+            cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device) == cudaSuccess && coop &&
+            (vectors <= 4u ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_f32_kernel<4>, kF32Threads, kF32SmemBytes)
+                           : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_f32_kernel<8>, kF32Threads, kF32SmemBytes)) ==
+                cudaSuccess &&
+            (unsigned long long)grid.x * grid.y * grid.z <= (unsigned long long)sms * per_sm) {
+            yvx_gqa_problem problem = p;
+            F32Maps tensor_maps = maps;
+            int major = head_first ? 1 : 0, cooperative = 1;
+            void *args[] = {&problem, &tensor_maps, &major, &cooperative};
+            error = cudaLaunchCooperativeKernel(kernel, grid, dim3(kF32Threads, 1, 1), args, kF32SmemBytes, stream);
+            if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel (cooperative)");
+            return 2;
+        }
+    }
     if (vectors <= 4u) {
         error = cudaFuncSetAttribute(gqa_decode_f32_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
+        if (error == cudaSuccess)
+            error = cudaFuncSetAttribute(gqa_decode_f32_kernel<4>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
-        gqa_decode_f32_kernel<4><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0);
+        gqa_decode_f32_kernel<4><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0, 0);
     } else {
         error = cudaFuncSetAttribute(gqa_decode_f32_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
+        if (error == cudaSuccess)
+            error = cudaFuncSetAttribute(gqa_decode_f32_kernel<8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
-        gqa_decode_f32_kernel<8><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0);
+        gqa_decode_f32_kernel<8><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0, 0);
     }
     const int rc = yvx_cuda_check(cudaGetLastError(), "gqa_decode_f32_kernel");
-    return rc != 0 ? rc : 1;
+    // with tickets the kernel has folded its splits itself: the output is final
+    return rc != 0 ? rc : (p.tickets && p.max_splits > 1u ? 2 : 1);
 }
 
 }  // namespace yvx

@@ -18,6 +18,7 @@
 // carried out exactly. For V the scale is folded into the f16 operand (one
 // rounding, 2^-12 relative). P is f16 (11 significant bits). Softmax and all
 // accumulation are f32.
+#include "exchange.cuh"
 #include "pipeline.cuh"
 
 namespace yvx {
@@ -100,9 +101,17 @@ __device__ __forceinline__ float f16_hi(uint32_t pair)
     return __half2float(__ushort_as_half((unsigned short)(pair >> 16)));
 }
 
+struct Q8ConsumerSync {
+    static __device__ __forceinline__ void sync() { named_barrier(1, kQ8ConsumerWarps * 32); }
+};
+
 // grid: x = split, y = kv_head * row_tiles + row_tile, z = session.
+// With an exchange (x.gather != NULL; cooperative launch, so every CTA is resident) the step
+// is ONE launch: after its partial rows a CTA takes a ticket of its (session, KV head, row
+// tile); the CTAs with split < live wait (bounded) for all the group's tickets, fold the
+// splits of item vector_base + split, and run the cross-GPU exchange of that item.
 __global__ void __launch_bounds__(kQ8Threads, 2)
-gqa_decode_q8_kernel(const yvx_gqa_problem p)
+gqa_decode_q8_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x)
 {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -451,9 +460,59 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p)
             }
         }
     }
+    if (!x.gather) return;
+
+    // ---- one-launch step: this group's splits are folded and exchanged by its own CTAs -------
+    const unsigned int items = p.sessions * p.query_rows * p.query_heads;
+    unsigned int *ticket = x.arrivals[x.rank] + items + ((unsigned long long)b * gridDim.y + blockIdx.y);
+    __threadfence();  // the partial rows above, before the ticket
+    Q8ConsumerSync::sync();
+    if (threadIdx.x == 0) atomicAdd(ticket, 1u);
+    if (split >= live) return;
+    float *fold_scratch = reinterpret_cast<float *>(stages);             // [4][130], the ring is drained
+    float *fold_row = fold_scratch + kQ8ConsumerWarps * (kQ8HeadDim + 2);
+    int *flag = reinterpret_cast<int *>(fold_row + kQ8HeadDim + 2);
+    if (threadIdx.x == 0) {
+        // tickets only grow: epoch e is complete at e * splits (the plan is the same every epoch)
+        const volatile unsigned int *counter = ticket;
+        const unsigned int target = x.epoch * gridDim.x;
+        int ok = 0;
+        for (unsigned int spin = 0; spin < kExchangeSpinLimit; ++spin) {
+            if ((int)(*counter - target) >= 0) {
+                ok = 1;
+                break;
+            }
+            __nanosleep(40);
+        }
+        *flag = ok;
+    }
+    Q8ConsumerSync::sync();
+    if (!*flag) {
+        if (threadIdx.x == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+        return;
+    }
+    __threadfence();
+    for (unsigned int i = split; i < live; i += gridDim.x) {
+        const unsigned int v = vector_base + i;
+        const unsigned int qrow = v / group, qhead = kv_head * group + v % group;
+        const unsigned long long item = ((unsigned long long)b * p.query_rows + qrow) * p.query_heads + qhead;
+        if (direct) {
+            const float *mine = p.partial_output + item * (kQ8HeadDim + 2ull);
+            for (unsigned int e = threadIdx.x; e < (unsigned)kQ8HeadDim + 2u; e += kQ8ConsumerWarps * 32u)
+                fold_row[e] = __ldcg(mine + e);
+            Q8ConsumerSync::sync();
+        } else {
+            fold_splits_128<kQ8ConsumerWarps, Q8ConsumerSync>(
+                p.partials + item * p.max_splits * (kQ8HeadDim + 2ull), p.max_splits, fold_scratch, fold_row, threadIdx.x);
+        }
+        if (!exchange_item<Q8ConsumerSync>(x, x.rank, items, (unsigned int)item, kQ8HeadDim, fold_row, flag, threadIdx.x,
+                                           kQ8ConsumerWarps * 32u, p.output, p.output_dtype, item * kQ8HeadDim, p.status))
+            return;
+        Q8ConsumerSync::sync();
+    }
 }
 
-int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream)
+int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream, const yvx_lse_exchange *exchange)
 {
     if (p.kv_dtype != YVEX_DTYPE_Q8_0) return 0;
     if (p.head_dim != (unsigned)kQ8HeadDim || p.query_dtype != YVEX_DTYPE_BF16 ||
@@ -472,7 +531,28 @@ int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream)
                                              kQ8SmemBytes);
     if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_q8_kernel attribute");
     const dim3 grid(p.max_splits, p.kv_heads * ((vectors + 15u) / 16u), p.sessions);
-    gqa_decode_q8_kernel<<<grid, kQ8Threads, kQ8SmemBytes, stream>>>(p);
+    if (exchange) {
+        // The one-launch step: CTAs wait on one another's tickets, so all of them must be resident:
+        // a cooperative launch, or (when the grid does not fit, or the shape is not the tail's) the
+        // caller's two-launch path. Lengths must be uniform so that every CTA of the grid arrives.
+        int device = 0, sms = 0, per_sm = 0;
+        if (p.kv_tokens || !p.output || (p.max_splits == 1u && !p.partial_output) || exchange->ranks > 128u) return 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_q8_kernel, kQ8Threads, kQ8SmemBytes) !=
+                cudaSuccess)
+            return 0;
+        if ((unsigned long long)grid.x * grid.y * grid.z > (unsigned long long)sms * per_sm) return 0;
+        yvx_gqa_problem problem = p;
+        yvx_lse_exchange x = *exchange;
+        void *args[] = {&problem, &x};
+        const cudaError_t launched = cudaLaunchCooperativeKernel((const void *)gqa_decode_q8_kernel, grid,
+                                                                 dim3(kQ8Threads, 1, 1), args, kQ8SmemBytes, stream);
+        if (launched != cudaSuccess) return yvx_cuda_check(launched, "gqa_decode_q8_kernel (cooperative)");
+        return 3;  // launched, folded and exchanged: the output is final
+    }
+    yvx_lse_exchange none = {};
+    gqa_decode_q8_kernel<<<grid, kQ8Threads, kQ8SmemBytes, stream>>>(p, none);
     const int rc = yvx_cuda_check(cudaGetLastError(), "gqa_decode_q8_kernel");
     return rc != 0 ? rc : 1;
 }

@@ -8,7 +8,7 @@ bool gqa_decode_f32_admits(const yvx_gqa_problem &p);
 void gqa_decode_f32_plan(yvx_gqa_problem *p, int sm_count);
 int gqa_decode_f32_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int gqa_decode_mma_launch(const yvx_gqa_problem &p, cudaStream_t stream);
-int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream);
+int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream, const yvx_lse_exchange *exchange = nullptr);
 int prefill_tcgen05_launch(const yvx_gqa_problem &p, cudaStream_t stream);
 int lse_exchange_launch(const yvx_gqa_problem &p, const yvx_lse_exchange &x, cudaStream_t stream);
 
@@ -197,8 +197,22 @@ static int gqa_launch(const yvx_gqa_problem *p, void *stream, cudaEvent_t *event
     // final, 0 = not this kernel's shape, negative = error.
     // Query heads that are not packed at head_dim are the general kernel's alone.
     const bool packed_heads = !p->query_head_stride || p->query_head_stride == p->head_dim;
-    int rc = packed_heads ? yvx::gqa_decode_q8_launch(*p, s)
-                          : (p->kv_dtype == YVEX_DTYPE_Q8_0 ? YVEX_ERR_UNSUPPORTED : 0);
+    int rc = 0;
+    if (exchange && exchange->one_launch && packed_heads && p->kv_dtype == YVEX_DTYPE_Q8_0) {
+        // the whole step in one cooperative launch when the shape allows; else the two-launch path
+        rc = yvx::gqa_decode_q8_launch(*p, s, exchange);
+        if (rc == 3) {
+            if (events) {
+                cudaEventRecord(events[1], s);
+                cudaEventRecord(events[2], s);
+            }
+            if (launches) *launches = 1u;
+            return 0;
+        }
+        if (rc < 0) return rc;
+    }
+    rc = packed_heads ? yvx::gqa_decode_q8_launch(*p, s)
+                      : (p->kv_dtype == YVEX_DTYPE_Q8_0 ? YVEX_ERR_UNSUPPORTED : 0);
     const unsigned int vectors = p->query_rows * (p->query_heads / p->kv_heads);
     if (rc == 0 && !p->force_general && packed_heads) rc = yvx::gqa_decode_f32_launch(*p, s);
     if (rc == 0 && !p->force_general && packed_heads)
@@ -259,7 +273,8 @@ unsigned long long yvx_cuda_lse_exchange_counter_offset(unsigned int ranks, unsi
 
 unsigned long long yvx_cuda_lse_exchange_bytes(unsigned int ranks, unsigned int items, unsigned int head_dim)
 {
-    return yvx_cuda_lse_exchange_counter_offset(ranks, items, head_dim) + (unsigned long long)items * 4ull;
+    // [items] arrival counters, then [items] split tickets of the one-launch step
+    return yvx_cuda_lse_exchange_counter_offset(ranks, items, head_dim) + (unsigned long long)items * 8ull;
 }
 
 int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *p, void *stream, void *events[3],

@@ -14,19 +14,15 @@
 // epoch parity, so no reset and no reuse hazard: a rank cannot be two epochs ahead
 // of a peer, because finishing an epoch needs that peer's row of the same epoch.
 // Plain peer loads and stores only; no multicast, no TMA.
-#include "combine.cuh"
+#include "exchange.cuh"
 
 namespace yvx {
 
 constexpr int kExchangeThreads = kCombineWarps * 32;
-constexpr unsigned int kExchangeSpinLimit = 1u << 23;  // about a second of 100 ns polls, then status 3
 
-// Release / acquire at system scope (peers are other GPUs); lighter than the
-// sequentially consistent fence and all this protocol needs.
-__device__ __forceinline__ void fence_acq_rel_system()
-{
-    asm volatile("fence.acq_rel.sys;" ::: "memory");
-}
+struct BlockSync {
+    static __device__ __forceinline__ void sync() { __syncthreads(); }
+};
 
 __global__ void __launch_bounds__(kExchangeThreads)
 lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const unsigned int items,
@@ -38,7 +34,7 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
     const unsigned int item = blockIdx.x;
     const unsigned int rank = emulated ? blockIdx.y : x.rank;
     const unsigned int hd = p.head_dim, stride = hd + 2u;
-    // 1. this rank's row
+    // this rank's row
     if (p.max_splits > 1u && !emulated) {
         const unsigned int b = (unsigned int)(item / ((unsigned long long)p.query_rows * p.query_heads));
         const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
@@ -50,73 +46,9 @@ lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const uns
         for (unsigned int d = threadIdx.x; d < stride; d += kExchangeThreads) row[d] = mine[d];
     }
     __syncthreads();
-    // 2. publish to every rank, then count
-    const unsigned long long slot = ((unsigned long long)(x.epoch & 1u) * x.ranks + rank) * items + item;
-    for (unsigned int r = 0; r < x.ranks; ++r) {
-        float *dst = x.gather[r] + slot * stride;
-        for (unsigned int d = threadIdx.x; d < stride; d += kExchangeThreads) dst[d] = row[d];
-    }
-    __syncthreads();
-    // Thread r tells rank r. Its system-wide fence after the barrier orders every
-    // thread's peer stores (they happen before it through the barrier) ahead of the count.
-    if (threadIdx.x < x.ranks) {
-        fence_acq_rel_system();
-        atomicAdd_system(x.arrivals[threadIdx.x] + item, 1u);
-    }
-    if (threadIdx.x == 0) {
-        // 3. bounded wait for the rows of all ranks
-        const volatile unsigned int *counter = x.arrivals[rank] + item;
-        const unsigned int target = x.epoch * x.ranks;
-        int ok = 0;
-        for (unsigned int spin = 0; spin < kExchangeSpinLimit; ++spin) {
-            if ((int)(*counter - target) >= 0) {
-                ok = 1;
-                break;
-            }
-            __nanosleep(100);
-        }
-        // Acquire side: this fence, then the barrier, order every thread's reads of the
-        // peers' rows after the observation of the counter.
-        fence_acq_rel_system();
-        arrived = ok;
-    }
-    __syncthreads();
-    if (!arrived) {
-        if (threadIdx.x == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
-        return;
-    }
-    // 4. fold the ranks' rows in rank order; peers wrote them, so bypass L1. All loads
-    // of up to eight ranks are issued before the first use (one trip to L2 per batch).
-    const float *base = x.gather[rank] + ((unsigned long long)(x.epoch & 1u) * x.ranks * items + item) * stride;
-    const unsigned long long rank_stride = (unsigned long long)items * stride;
-    for (unsigned int d = threadIdx.x; d < hd; d += kExchangeThreads) {
-        float run_max = -INFINITY, run_sum = 0.0f, acc = 0.0f;
-        for (unsigned int r0 = 0; r0 < x.ranks; r0 += 8u) {
-            float mr[8], lr[8], orow[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const bool live = r0 + u < x.ranks;
-                const float *part = base + (unsigned long long)(live ? r0 + u : r0) * rank_stride;
-                mr[u] = live ? __ldcg(part + hd) : -INFINITY;
-                lr[u] = __ldcg(part + hd + 1u);
-                orow[u] = __ldcg(part + d);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (mr[u] == -INFINITY) continue;  // empty shard or past the last rank
-                const float new_max = fmaxf(run_max, mr[u]);
-                const float keep = expf(run_max - new_max);
-                const float weight = lr[u] * expf(mr[u] - new_max);
-                run_sum = fmaf(run_sum, keep, weight);
-                acc = fmaf(acc, keep, orow[u] * weight);
-                run_max = new_max;
-            }
-        }
-        const float value = acc / run_sum;
-        if (!isfinite(value)) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
-        store_output(emulated ? (void *)((float *)p.output + (unsigned long long)rank * items * hd) : p.output,
-                     p.output_dtype, (unsigned long long)item * hd + d, value);
-    }
+    exchange_item<BlockSync>(x, rank, items, item, hd, row, &arrived, threadIdx.x, kExchangeThreads,
+                             emulated ? (void *)((float *)p.output + (unsigned long long)rank * items * hd) : p.output,
+                             p.output_dtype, (unsigned long long)item * hd, p.status);
 }
 
 int lse_exchange_launch(const yvx_gqa_problem &p, const yvx_lse_exchange &x, cudaStream_t stream)

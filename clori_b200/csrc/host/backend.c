@@ -74,7 +74,12 @@ int yvex_backend_open(yvex_backend **out, const yvex_backend_options *options, y
                         "kernels are built for sm_100a only; this device is not compute capability 10.x");
     }
     if (rc == 0) rc = yvx_cuda_stream_create(&backend->own_stream);
-    if (rc == 0) rc = yvx_cuda_malloc((void **)&backend->status_device, sizeof(int));
+    /* the status word, and behind it (256 bytes on) the arrival tickets of the single-launch
+     * split kernels: zero once here, every kernel that uses one leaves it at zero again */
+    if (rc == 0) rc = yvx_cuda_malloc((void **)&backend->status_device, 256u + YVX_BACKEND_TICKETS * sizeof(int));
+    if (rc == 0) rc = yvx_cuda_memset_async(backend->status_device, 0, 256u + YVX_BACKEND_TICKETS * sizeof(int), backend->own_stream);
+    if (rc == 0) rc = yvx_cuda_stream_synchronize(backend->own_stream);
+    if (rc == 0) backend->tickets = backend->status_device + 64;
     if (rc == 0) rc = yvx_cuda_host_alloc((void **)&backend->status_host, sizeof(int));
     if (rc != 0) {
         yvex_error_set(err, (yvex_status)rc, where, yvx_cuda_last_error_text());

@@ -132,6 +132,8 @@ int yvex_b200_transformer_attention_execute(yvex_backend *backend,
     problem.kv_tokens_uniform = problem.kv_tokens_max = (unsigned int)r->key_value_tokens;
     problem.query_start_uniform = (unsigned int)r->query_start;
     problem.status = backend->status_device;
+    if (2ull * problem.sessions * problem.kv_heads <= (unsigned long long)YVX_BACKEND_TICKETS)
+        problem.tickets = backend->tickets;
     yvx_cuda_gqa_plan_splits(&problem, backend->sm_count);
     {
         /* one arena: the split partials, then (prefill-sized problems) the bf16 staging of the

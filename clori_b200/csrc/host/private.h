@@ -9,6 +9,8 @@
 #include "yvex_b200/attention.h"
 #include "yvex_b200/cuda_shim.h"
 
+enum { YVX_BACKEND_TICKETS = 4096 };
+
 struct yvex_backend {
     int device, sm_count, cc_major, cc_minor;
     char device_name[128];
@@ -23,6 +25,7 @@ struct yvex_backend {
     void *scratch;
     unsigned long long scratch_bytes;
     int *status_device; /* device status word the kernels publish into */
+    int *tickets;       /* YVX_BACKEND_TICKETS zeroed device counters (arrival tickets) */
     int *status_host;   /* pinned mirror */
     int status_pending; /* an asynchronous operator has not been checked yet */
     /* why `failed` was set, in the capability vocabulary (yvex_backend_capability_reason):

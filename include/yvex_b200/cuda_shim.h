@@ -130,6 +130,12 @@ typedef struct yvx_gqa_problem {
     const int *gate;                 /* kernels of this problem run only while *gate == gate_value;
                                         NULL: always (set by the launcher for the path above) */
     int gate_value;
+    int *tickets;                    /* optional: 2 * sessions * kv_heads device counters, zero before the
+                                        first call (the kernels leave them at zero). With them the short
+                                        F32 decode kernel folds its own splits: the CTA that arrives last
+                                        for a KV head reads every split's partial, in split order, and
+                                        writes the output: one launch instead of two. Calls that overlap
+                                        on the GPU must not share tickets */
 } yvx_gqa_problem;
 
 /* Scratch the tensor-core path of an F32 problem needs (0 when the shape never takes it). */
@@ -170,6 +176,11 @@ typedef struct yvx_lse_exchange {
     unsigned int ranks, rank, epoch;
     float *const *gather;            /* device array [ranks]: base of rank r's area */
     unsigned int *const *arrivals;   /* device array [ranks]: rank r's arrival counters */
+    int one_launch;                  /* 1: fold the splits and run the exchange in the tail of the
+                                        attention kernel itself (one cooperative launch per step:
+                                        Q8_0 KV, uniform lengths, a grid that is resident at once,
+                                        and the same split plan every epoch of an area; otherwise
+                                        the two-launch path is taken silently) */
 } yvx_lse_exchange;
 unsigned long long yvx_cuda_lse_exchange_bytes(unsigned int ranks, unsigned int items, unsigned int head_dim);
 unsigned long long yvx_cuda_lse_exchange_counter_offset(unsigned int ranks, unsigned int items,

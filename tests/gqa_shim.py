@@ -14,7 +14,7 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
                 k_outer_stride, v_outer_stride, v_offset_elems=0, kv_max=None,
                 force_general=False, chunk_tokens=None, query_start=None, position_base=0,
                 partial_output=False, entry="yvx_cuda_gqa_attention", own_scratch=True,
-                k_offset_elems=0, q_row_stride=None, q_head_stride=0):
+                k_offset_elems=0, q_row_stride=None, q_head_stride=0, tickets=None):
     """q: device Tensor [sessions, rows, hq*hd]; k, v: device Tensors holding the
     cache in any layout described by the strides (elements). Returns the output
     array (or the (o, m, l) partials) and the launch count."""
@@ -48,6 +48,8 @@ def run_problem(backend, *, q, k, v, lengths, rows, hq, hkv, hd, dtype, out_dtyp
         p.query_start = qs.data_ptr
     p.kv_position_base = position_base
     p.force_general = int(force_general)
+    if tickets is not None:
+        p.tickets = tickets.data_ptr
     lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
     if chunk_tokens:
         p.chunk_tokens = chunk_tokens

@@ -110,3 +110,28 @@ def test_calls_can_be_captured_into_a_graph_and_replayed(backend, oracle):
     assert np.array_equal(replayed, direct)
     assert lib.yvx_cuda_graph_destroy(captured["graph"]) == 0
     del lib.capture_entry
+
+
+@pytest.mark.parametrize("rows,hq,hkv,n", [(1, 32, 8, 4096), (2, 8, 2, 1500), (1, 40, 8, 333), (2, 16, 4, 112), (8, 2, 2, 25000)])
+def test_single_launch_fold_by_the_last_cta(backend, oracle, rows, hq, hkv, n):
+    """With arrival tickets the kernel folds its own splits: one launch, the same numbers as the
+    two-launch path to rounding, identical repeats, and the tickets back at zero."""
+    rng = np.random.Generator(np.random.PCG64(14 + n))
+    width = hkv * HD
+    q = rng.standard_normal((1, rows, hq * HD), dtype=np.float32)
+    k = rng.standard_normal((1, n, width), dtype=np.float32)
+    v = rng.standard_normal((1, n, width), dtype=np.float32)
+    kw = dict(q=backend.tensor("q", q), k=backend.tensor("k", k), v=backend.tensor("v", v), lengths=[n], rows=rows,
+              hq=hq, hkv=hkv, hd=HD, dtype=abi.DTYPE_F32, k_token_stride=width, v_token_stride=width,
+              k_head_stride=HD, v_head_stride=HD, k_outer_stride=n * width, v_outer_stride=n * width)
+    two, status, launches, plan = run_problem(backend, **kw)
+    assert status == 0 and launches == (2 if plan[1] > 1 else 1)
+    tickets = backend.tensor("tickets", np.zeros(2 * hkv, np.int32))
+    one, status, launches, _ = run_problem(backend, tickets=tickets, **kw)
+    again, _, _, _ = run_problem(backend, tickets=tickets, **kw)
+    assert status == 0 and launches == 1
+    assert np.array_equal(one, again)
+    assert np.abs(one - two).max() <= 1e-6
+    assert not tickets.read().any()
+    ref = oracle.gqa_attention(q[0], k[0], v[0], n - rows, hq, hkv, HD, threads=8)
+    assert close(one[0], ref)

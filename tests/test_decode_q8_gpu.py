@@ -177,3 +177,69 @@ def test_sequence_sharded_q8_partials_combine_to_the_whole(backend, oracle):
     got = out.read()
     assert np.abs(got - ref).max() <= 2e-3
     assert cosine(got, ref) >= 0.9999
+
+
+@pytest.mark.parametrize("tokens,chunk", [(64 * 23 + 17, 256), (8192, 512), (8192, 64), (100, 0)])
+def test_one_launch_step_folds_and_exchanges_in_the_kernel_tail(backend, oracle, tokens, chunk):
+    # The whole step (attention, fold of the splits, exchange, fold of the ranks) in ONE
+    # cooperative launch, here with a single rank: the exchange area is this GPU's own, so every
+    # wait is satisfied by the launch itself. Three epochs over the same area; the result equals
+    # the CPU attention and repeats bit for bit.
+    hq, hkv, rows = 32, 8, 4
+    k_rows, v_rows = workloads.q8_0_kv(seed=10, kv_tokens=tokens, kv_heads=hkv)
+    q = workloads.verify_queries_bf16(seed=10, rows=rows, query_heads=hq)
+    blocks = (tokens + 63) // 64
+    records = device_pack(backend, k_rows, v_rows, hkv, None, blocks)
+    tq = backend.tensor("q", q)
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    lib, items, record = backend.lib, rows * hq, q8_records.RECORD_BYTES
+    area_bytes = lib.yvx_cuda_lse_exchange_bytes(1, items, HD)
+    counter_offset = lib.yvx_cuda_lse_exchange_counter_offset(1, items, HD)
+    area = backend.tensor("area", np.zeros(area_bytes // 4, np.int32))
+    gather = backend.tensor("gather", np.array([area.data_ptr], np.int64), dtype=abi.DTYPE_I64)
+    arrivals = backend.tensor("arrivals", np.array([area.data_ptr + counter_offset], np.int64), dtype=abi.DTYPE_I64)
+    mine = backend.alloc("mine", abi.DTYPE_F32, (items, HD + 2))
+    out = backend.alloc("out", abi.DTYPE_F32, (rows, hq * HD))
+    p = abi.GqaProblem()
+    p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, rows, hq, hkv, HD
+    p.causal, p.scale = 1, 1.0 / np.sqrt(HD)
+    p.query_dtype, p.kv_dtype, p.output_dtype = abi.DTYPE_BF16, abi.DTYPE_Q8_0, abi.DTYPE_F32
+    p.query, p.query_row_stride, p.query_session_stride = tq.data_ptr, hq * HD, rows * hq * HD
+    p.key = records.data_ptr
+    p.key_head_stride, p.key_block_stride, p.block_tokens = record, hkv * record, 64
+    p.kv_tokens_uniform = p.kv_tokens_max = tokens
+    p.query_start_uniform = tokens - rows
+    p.partial_output, p.output = mine.data_ptr, out.data_ptr
+    lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+    if chunk:
+        p.chunk_tokens, p.max_splits = chunk, (tokens + chunk - 1) // chunk
+    scratch = backend.alloc("scratch", abi.DTYPE_F32, (1,), max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+    p.partials, p.status = scratch.data_ptr, status.data_ptr
+    x = abi.LseExchange()
+    x.ranks, x.rank, x.gather, x.arrivals, x.one_launch = 1, 0, gather.data_ptr, arrivals.data_ptr, 1
+    results = []
+    for epoch in (1, 2, 3):
+        x.epoch = epoch
+        n = C.c_uint()
+        rc = lib.yvx_cuda_gqa_attention_exchange(C.byref(p), C.byref(x), backend.stream, C.byref(n))
+        assert rc == 0, lib.yvx_cuda_last_error_text()
+        assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+        # 8192 tokens in 64-token splits are 1024 CTAs, more than are resident at once: that plan
+        # silently takes the two-launch path; every other case here is a single launch
+        assert n.value == (2 if chunk == 64 else 1)
+        out.struct.is_written = 1
+        results.append(out.read().copy())
+        assert int(status.read()[0]) == 0
+    assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
+    kf, vf = dequant(oracle, k_rows, tokens, hkv * HD), dequant(oracle, v_rows, tokens, hkv * HD)
+    ref = oracle.gqa_attention(clori_b200.bf16_bits_to_f32(q), kf, vf, tokens - rows, hq, hkv, HD, threads=8)
+    assert np.abs(results[0] - ref).max() <= 2e-3 and cosine(results[0], ref) >= 0.9999
+    counters = area.read()[counter_offset // 4: counter_offset // 4 + items]
+    assert counters.tolist() == [3] * items
+    if chunk == 64:
+        return
+    # an epoch the tickets cannot reach runs into the bounded wait instead of hanging
+    x.epoch = 9
+    rc = lib.yvx_cuda_gqa_attention_exchange(C.byref(p), C.byref(x), backend.stream, C.byref(n))
+    assert rc == 0 and lib.yvx_cuda_stream_synchronize(backend.stream) == 0
+    assert int(status.read()[0]) == 3
