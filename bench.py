@@ -451,7 +451,39 @@ def bench_verify_q8(lib, backend, abi, peak, repeats, chunk=None):
         p.partials, p.status = scratch, status
         problems.append(p)
     main, combine, launches = _timed_launches(lib, backend, problems, repeats)
-    last = _timed_launches.last_problem
+    step_ms, graph_step_ms = _timed_launches.step_ms, _timed_launches.graph_step_ms
+    # The same step as ONE cooperative launch: the splits are folded by the kernel's own CTAs
+    # (the exchange tail with a single rank, whose area is this GPU's own memory).
+    items = rows * hq
+    area_bytes = lib.yvx_cuda_lse_exchange_bytes(1, items, hd)
+    area, table, mine = _alloc(lib, area_bytes), _alloc(lib, 16), _alloc(lib, items * (hd + 2) * 4)
+    lib.yvx_cuda_memset_async(area, 0, area_bytes, backend.stream)
+    pointers = np.array([area.value, area.value + lib.yvx_cuda_lse_exchange_counter_offset(1, items, hd)], np.uint64)
+    lib.yvx_cuda_upload_async(table, pointers.ctypes.data, 16, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    exchange = abi.LseExchange()
+    exchange.ranks, exchange.rank, exchange.gather, exchange.arrivals, exchange.one_launch = 1, 0, table.value, table.value + 8, 1
+    for p in problems:
+        p.partial_output = mine
+    first, final, ms, n = C.c_void_p(), C.c_void_p(), C.c_float(), C.c_uint()
+    lib.yvx_cuda_event_create(C.byref(first)); lib.yvx_cuda_event_create(C.byref(final))
+    epoch = 0
+    for timed in (False, True):
+        if timed:
+            lib.yvx_cuda_event_record(first, backend.stream)
+        for i in range(repeats if timed else 3):
+            epoch += 1
+            exchange.epoch = epoch
+            rc = lib.yvx_cuda_gqa_attention_exchange(C.byref(problems[i % copies]), C.byref(exchange), backend.stream, C.byref(n))
+            assert rc == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_event_record(final, backend.stream)
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_event_elapsed_ms(first, final, C.byref(ms))
+    one_launch_ms, one_launch_launches = ms.value / repeats, int(n.value)
+    lib.yvx_cuda_event_destroy(first); lib.yvx_cuda_event_destroy(final)
+    for p in problems:
+        p.partial_output = None
+    last = (repeats - 1) % copies
     # sample for the CPU check: KV head 0 (query heads 0..3), every record of it
     head0 = np.empty((blocks, record), np.uint8)
     for j in range(blocks):
@@ -469,11 +501,12 @@ def bench_verify_q8(lib, backend, abi, peak, repeats, chunk=None):
               "kernel": "gqa_decode_q8_kernel", "launches_per_step": launches, "kernel_ms": main,
               "combine_ms": combine, "algorithmic_bytes": nbytes, "status_word": int(st[0]),
               "achieved_gbs": nbytes / (main * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (main * 1e-3) / 1e9 / peak,
-              "step_ms": _timed_launches.step_ms, "graph_step_ms": _timed_launches.graph_step_ms,
-              "tokens_per_s": rows / (_timed_launches.step_ms * 1e-3),
+              "step_ms": step_ms, "graph_step_ms": graph_step_ms,
+              "one_launch_step_ms": one_launch_ms, "one_launch_launches": one_launch_launches,
+              "tokens_per_s": rows / (min(step_ms, one_launch_ms) * 1e-3),
               "l2": f"{copies} rotating record pools ({copies * pool_bytes / 1e6:.0f} MB) exceed L2",
               "chunk_tokens": problems[0].chunk_tokens}
-    for ptr in (records, q, out, status, scratch):
+    for ptr in (records, q, out, status, scratch, area, table, mine):
         lib.yvx_cuda_free(ptr)
     return result, (head0, q_host.reshape(rows, hq * hd), o_host.reshape(rows, hq * hd))
 
@@ -1302,49 +1335,66 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
     ms = float(t.item())
     sharded = out.clone()
 
-    # ---- the same step with the exchange fused into the fold (no NCCL on the data path):
-    # peer stores of each rank's (o, m, l) rows over NVLink, arrival counters, bounded wait.
-    fused_result = {"unavailable": "peer mapping of the exchange areas failed on some rank"}
+    # ---- the same step without NCCL on the data path: each rank's (o, m, l) rows go to every
+    # rank by peer stores over NVLink, with arrival counters and bounded waits. Twice: the
+    # exchange as a second (dependent) launch, and folded into the attention kernel's own tail
+    # (ONE cooperative launch per step). Each variant has its own exchange area.
     area_bytes = lib.yvx_cuda_lse_exchange_bytes(world, items, hd)
     counter_offset = lib.yvx_cuda_lse_exchange_counter_offset(world, items, hd)
-    area = _alloc(lib, area_bytes)
-    lib.yvx_cuda_memset_async(area, 0, area_bytes, backend.stream)
-    torch.cuda.synchronize()
-    handle = (C.c_ubyte * 64)()
-    exported = lib.yvx_cuda_ipc_export(area, handle) == 0
-    handles = [None] * world
-    dist.all_gather_object(handles, bytes(handle) if exported else None)
-    peers, mapped_ok = [], exported and all(h is not None for h in handles)
-    for r in range(world):
-        if r == rank or not mapped_ok:
-            peers.append(area.value)
-            continue
-        mapped = C.c_void_p()
-        raw = (C.c_ubyte * 64).from_buffer_copy(handles[r])
-        if lib.yvx_cuda_ipc_open(raw, C.byref(mapped)) != 0:
-            mapped_ok = False
-            peers.append(area.value)
-        else:
-            peers.append(mapped.value)
-    agreed = torch.tensor([1 if mapped_ok else 0], dtype=torch.int32, device=device)
-    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-    pointer_table = _alloc(lib, 2 * world * 8)
-    if int(agreed.item()) == 1 and not os.environ.get("YVEX_BENCH_NO_FUSED_EXCHANGE"):
+    opened, owned = [], []
+
+    def exchange_area():
+        """Allocates, zeroes and maps one exchange area on every rank -> LseExchange or None."""
+        area = _alloc(lib, area_bytes)
+        owned.append(area)
+        lib.yvx_cuda_memset_async(area, 0, area_bytes, backend.stream)
+        torch.cuda.synchronize()
+        handle = (C.c_ubyte * 64)()
+        exported = lib.yvx_cuda_ipc_export(area, handle) == 0
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle) if exported else None)
+        peers, mapped_ok = [], exported and all(h is not None for h in handles)
+        for r in range(world):
+            if r == rank or not mapped_ok:
+                peers.append(area.value)
+                continue
+            mapped = C.c_void_p()
+            raw = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+            if lib.yvx_cuda_ipc_open(raw, C.byref(mapped)) != 0:
+                mapped_ok = False
+                peers.append(area.value)
+            else:
+                peers.append(mapped.value)
+                opened.append(mapped.value)
+        agreed = torch.tensor([1 if mapped_ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) != 1:
+            return None
+        table = _alloc(lib, 2 * world * 8)
+        owned.append(table)
         gather_host = np.array(peers, np.uint64)
         arrivals_host = gather_host + np.uint64(counter_offset)
-        lib.yvx_cuda_upload_async(pointer_table, gather_host.ctypes.data, world * 8, backend.stream)
-        lib.yvx_cuda_upload_async(pointer_table.value + world * 8, arrivals_host.ctypes.data, world * 8,
-                                  backend.stream)
-        fused_out = torch.zeros((rows, hq * hd), dtype=torch.float32, device=device)
-        fused = []
-        for i in range(copies):
-            fp = problem(i, begin.value, end.value, mine)
-            fp.output = fused_out.data_ptr()
-            fp.partials = scratch
-            fused.append(fp)
+        lib.yvx_cuda_upload_async(table, gather_host.ctypes.data, world * 8, backend.stream)
+        lib.yvx_cuda_upload_async(table.value + world * 8, arrivals_host.ctypes.data, world * 8, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
         exchange = abi.LseExchange()
         exchange.ranks, exchange.rank = world, rank
-        exchange.gather, exchange.arrivals = pointer_table.value, pointer_table.value + world * 8
+        exchange.gather, exchange.arrivals = table.value, table.value + world * 8
+        return exchange
+
+    fused_out = torch.zeros((rows, hq * hd), dtype=torch.float32, device=device)
+    fused = []
+    for i in range(copies):
+        fp = problem(i, begin.value, end.value, mine)
+        fp.output = fused_out.data_ptr()
+        fp.partials = scratch
+        fused.append(fp)
+
+    def exchange_run(one_launch):
+        exchange = exchange_area()
+        if exchange is None or os.environ.get("YVEX_BENCH_NO_FUSED_EXCHANGE"):
+            return {"unavailable": "peer mapping of the exchange areas failed on some rank"}
+        exchange.one_launch = one_launch
         epoch = [0]
 
         def fused_step(i):
@@ -1355,6 +1405,7 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
                                                      C.byref(n))
             assert rc == 0, lib.yvx_cuda_last_error_text()
             return n.value
+        fused_out.zero_()
         torch.cuda.synchronize()
         dist.barrier()          # every area is zeroed and mapped before the first peer store
         for i in range(3):
@@ -1370,12 +1421,14 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
         t = torch.tensor([start.elapsed_time(stop) / repeats], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         fused_ms = float(t.item())
-        fused_result = {"ms_per_step": fused_ms, "tokens_per_s": rows / (fused_ms * 1e-3),
-                        "aggregate_gbs": (pool_bytes + rows * hq * hd * (2 + 4)) / (fused_ms * 1e-3) / 1e9,
-                        "launches_per_step": fused_launches,
-                        "collective": "none: peer stores of %d bytes to each rank inside the fold kernel"
-                                      % (items * (hd + 2) * 4),
-                        "max_abs_vs_nccl_path": float((fused_out - sharded).abs().max().item())}
+        return {"ms_per_step": fused_ms, "tokens_per_s": rows / (fused_ms * 1e-3),
+                "aggregate_gbs": (pool_bytes + rows * hq * hd * (2 + 4)) / (fused_ms * 1e-3) / 1e9,
+                "launches_per_step": fused_launches,
+                "collective": "none: peer stores of %d bytes to each rank inside the %s"
+                              % (items * (hd + 2) * 4, "attention kernel's tail" if one_launch else "fold kernel"),
+                "max_abs_vs_nccl_path": float((fused_out - sharded).abs().max().item())}
+    fused_result = exchange_run(0)
+    one_launch_result = exchange_run(1)
     # cross-check on rank 0: the same pool copy, unsharded, on one GPU
     diff = None
     if rank == 0:
@@ -1397,12 +1450,14 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
               "collective": "one NCCL all-gather of %d bytes per rank" % (items * (hd + 2) * 4),
               "shard_tokens": end.value - begin.value, "status_word": int(st[0]),
               "sharded_vs_single_gpu_max_abs": diff,
-              "fused_exchange": fused_result}
+              "fused_exchange": fused_result, "one_launch_exchange": one_launch_result,
+              "ranks": world, "nccl_step_us": ms * 1e3,
+              "fused_step_us": fused_result.get("ms_per_step", float("nan")) * 1e3,
+              "one_launch_step_us": one_launch_result.get("ms_per_step", float("nan")) * 1e3}
     dist.barrier()          # nobody unmaps while a peer may still store
-    for r in range(world):
-        if r != rank and peers[r] != area.value:
-            lib.yvx_cuda_ipc_close(C.c_void_p(peers[r]))
-    for ptr in (records, q, status, scratch, area, pointer_table):
+    for mapped in opened:
+        lib.yvx_cuda_ipc_close(C.c_void_p(mapped))
+    for ptr in [records, q, status, scratch] + owned:
         lib.yvx_cuda_free(ptr)
     return result
 

@@ -453,41 +453,43 @@ int gqa_decode_f32_launch(const yvx_gqa_problem &p, cudaStream_t stream)
     const dim3 grid(p.max_splits, p.kv_heads, p.sessions);
     cudaError_t error;
     const bool fold_here = p.tickets && p.max_splits > 1u;
-    if (fold_here) {
+    // per device, once: attributes and resident-CTA capacities of both instantiations
+    static int configured_device = -1, resident[2] = {0, 0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return YVEX_ERR_BACKEND;
+    if (configured_device != device) {
+        int sms = 0, coop = 0, per_sm[2] = {0, 0};
+        const void *kernels[2] = {(const void *)gqa_decode_f32_kernel<4>, (const void *)gqa_decode_f32_kernel<8>};
+        for (int i = 0; i < 2; ++i) {
+            error = cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
+            if (error == cudaSuccess)
+                error = cudaFuncSetAttribute(kernels[i], cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+            if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
+        }
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm[0], gqa_decode_f32_kernel<4>, kF32Threads, kF32SmemBytes) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm[1], gqa_decode_f32_kernel<8>, kF32Threads, kF32SmemBytes) != cudaSuccess)
+            return YVEX_ERR_BACKEND;
+        resident[0] = coop ? sms * per_sm[0] : 0;
+        resident[1] = coop ? sms * per_sm[1] : 0;
+        configured_device = device;
+    }
+    if (fold_here && (unsigned long long)grid.x * grid.y * grid.z <= (unsigned long long)resident[vectors <= 4u ? 0 : 1]) {
         // every CTA resident at once (the planner's single wave): a cooperative launch lets the
         // group's own CTAs fold side by side; a grid that does not fit folds in its last arrivals
-        int device = 0, sms = 0, per_sm = 0, coop = 0;
         const void *kernel = vectors <= 4u ? (const void *)gqa_decode_f32_kernel<4> : (const void *)gqa_decode_f32_kernel<8>;
-        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
-        if (error == cudaSuccess) error = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
-        if (cudaGetDevice(&device) == cudaSuccess &&
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess &&
-            cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, device) == cudaSuccess && coop &&
-            (vectors <= 4u ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_f32_kernel<4>, kF32Threads, kF32SmemBytes)
-                           : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_f32_kernel<8>, kF32Threads, kF32SmemBytes)) ==
-                cudaSuccess &&
-            (unsigned long long)grid.x * grid.y * grid.z <= (unsigned long long)sms * per_sm) {
-            yvx_gqa_problem problem = p;
-            F32Maps tensor_maps = maps;
-            int major = head_first ? 1 : 0, cooperative = 1;
-            void *args[] = {&problem, &tensor_maps, &major, &cooperative};
-            error = cudaLaunchCooperativeKernel(kernel, grid, dim3(kF32Threads, 1, 1), args, kF32SmemBytes, stream);
-            if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel (cooperative)");
-            return 2;
-        }
+        yvx_gqa_problem problem = p;
+        F32Maps tensor_maps = maps;
+        int major = head_first ? 1 : 0, cooperative = 1;
+        void *args[] = {&problem, &tensor_maps, &major, &cooperative};
+        error = cudaLaunchCooperativeKernel(kernel, grid, dim3(kF32Threads, 1, 1), args, kF32SmemBytes, stream);
+        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel (cooperative)");
+        return 2;
     }
     if (vectors <= 4u) {
-        error = cudaFuncSetAttribute(gqa_decode_f32_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
-        if (error == cudaSuccess)
-            error = cudaFuncSetAttribute(gqa_decode_f32_kernel<4>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
         gqa_decode_f32_kernel<4><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0, 0);
     } else {
-        error = cudaFuncSetAttribute(gqa_decode_f32_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF32SmemBytes);
-        if (error == cudaSuccess)
-            error = cudaFuncSetAttribute(gqa_decode_f32_kernel<8>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_f32_kernel attribute");
         gqa_decode_f32_kernel<8><<<grid, kF32Threads, kF32SmemBytes, stream>>>(p, maps, head_first ? 1 : 0, 0);
     }
     const int rc = yvx_cuda_check(cudaGetLastError(), "gqa_decode_f32_kernel");

@@ -526,23 +526,30 @@ int gqa_decode_q8_launch(const yvx_gqa_problem &p, cudaStream_t stream, const yv
     const unsigned int group = p.query_heads / p.kv_heads;
     const unsigned int vectors = p.query_rows * group;
     if (vectors > 64u) return YVEX_ERR_UNSUPPORTED;
-    cudaError_t error = cudaFuncSetAttribute(gqa_decode_q8_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kQ8SmemBytes);
-    if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_q8_kernel attribute");
+    // per device, once: the attribute and the resident-CTA capacity (host calls that would
+    // otherwise sit in front of every launch of a latency-sized step)
+    static int configured_device = -1, resident_ctas = 0;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return YVEX_ERR_BACKEND;
+    if (configured_device != device) {
+        int sms = 0, per_sm = 0;
+        cudaError_t error = cudaFuncSetAttribute(gqa_decode_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 kQ8SmemBytes);
+        if (error != cudaSuccess) return yvx_cuda_check(error, "gqa_decode_q8_kernel attribute");
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_q8_kernel, kQ8Threads, kQ8SmemBytes) !=
+                cudaSuccess)
+            return YVEX_ERR_BACKEND;
+        resident_ctas = sms * per_sm;
+        configured_device = device;
+    }
     const dim3 grid(p.max_splits, p.kv_heads * ((vectors + 15u) / 16u), p.sessions);
     if (exchange) {
         // The one-launch step: CTAs wait on one another's tickets, so all of them must be resident:
         // a cooperative launch, or (when the grid does not fit, or the shape is not the tail's) the
         // caller's two-launch path. Lengths must be uniform so that every CTA of the grid arrives.
-        int device = 0, sms = 0, per_sm = 0;
         if (p.kv_tokens || !p.output || (p.max_splits == 1u && !p.partial_output) || exchange->ranks > 128u) return 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gqa_decode_q8_kernel, kQ8Threads, kQ8SmemBytes) !=
-                cudaSuccess)
-            return 0;
-        if ((unsigned long long)grid.x * grid.y * grid.z > (unsigned long long)sms * per_sm) return 0;
+        if ((unsigned long long)grid.x * grid.y * grid.z > (unsigned long long)resident_ctas) return 0;
         yvx_gqa_problem problem = p;
         yvx_lse_exchange x = *exchange;
         void *args[] = {&problem, &x};
