@@ -896,6 +896,142 @@ def bench_compressor(lib, backend, abi, hbm_peak, repeats, tokens=32768):
     return result, None
 
 
+def bench_projections(lib, backend, abi, hbm_peak, repeats, tokens=1):
+    """The five projections around the latent attention of one decode step at the reference
+    configuration's widths (hidden 4096, query rank 1024, 64 heads x 512, 8 output groups,
+    output rank 1024): q_a [1024 x 4096], q_b [32768 x 1024], kv [512 x 4096], grouped out_a
+    [8 x 1024 x 4096], out_b [4096 x 8192]; 106.9 M weights, once as BF16 and once as Q8_0.
+    Every weight byte is read once per step (two copies of the weights alternate so that no
+    step finds them in L2); the roofline is encoded bytes / measured HBM peak. Sample rows of
+    every projection are compared with the CPU restatement of the reference's dot bit for bit."""
+    from oracle.binding import Oracle
+    oracle = Oracle()
+    shapes = (("q_a", 1024, 4096, 1), ("q_b", 32768, 1024, 1), ("kv", 512, 4096, 1), ("out_a", 1024, 4096, 8),
+              ("out_b", 4096, 8192, 1))
+    rng = np.random.default_rng(SEED + 91)
+    copies, sample_rows = 2, 16
+    out = {}
+
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    first, last, ms = event(), event(), C.c_float()
+    status = _alloc(lib, 4)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+    for label, qtype in (("bf16", abi.QTYPE_BF16), ("q8_0", abi.QTYPE_Q8_0)):
+        owned, calls, checks, weight_bytes = [], [[] for _ in range(copies)], [], 0
+        for name, rows, width, groups in shapes:
+            row_bytes = lib.yvx_cuda_qtype_row_bytes(qtype, width)
+            total_rows = rows * groups
+            weight_bytes += total_rows * row_bytes
+            if qtype == abi.QTYPE_Q8_0:
+                blocks = np.zeros((total_rows * (width // 32), 34), np.uint8)
+                blocks[:, :2] = rng.uniform(0.002, 0.02, blocks.shape[0]).astype(np.float16).view(np.uint8).reshape(-1, 2)
+                blocks[:, 2:] = rng.integers(-127, 128, (blocks.shape[0], 32), dtype=np.int8).view(np.uint8)
+                host = blocks.reshape(total_rows, row_bytes)
+            else:
+                host = None
+            x_host = np.zeros((tokens, groups * width), np.float32)
+            x = _alloc(lib, x_host.nbytes)
+            lib.yvx_cuda_fill_normal(x, -abi.DTYPE_F32, x_host.size, 300 + len(owned), 1.0, backend.stream)
+            lib.yvx_cuda_download_async(x_host.ctypes.data, x, x_host.nbytes, backend.stream)
+            y = _alloc(lib, tokens * total_rows * 4)
+            owned += [x, y]
+            for c in range(copies):
+                w = _alloc(lib, total_rows * row_bytes)
+                owned.append(w)
+                if host is not None:
+                    lib.yvx_cuda_upload_async(w, host.ctypes.data, host.nbytes, backend.stream)
+                else:
+                    lib.yvx_cuda_fill_normal(w, abi.DTYPE_BF16, total_rows * width, 400 + len(owned), 0.02, backend.stream)
+                a = abi.MatvecArgs()
+                a.weights, a.qtype, a.rows, a.width, a.row_bytes = w, qtype, rows, width, row_bytes
+                a.input, a.tokens, a.input_stride = x, tokens, groups * width
+                a.output, a.output_stride, a.groups, a.round_bf16, a.status = y, total_rows, groups, 1, status
+                calls[c].append(a)
+            lib.yvx_cuda_stream_synchronize(backend.stream)     # the host block array may go
+            checks.append((name, rows, width, groups, row_bytes, x_host, y, calls[(repeats - 1) % copies][-1]))
+
+        def step(i):
+            for a in calls[i % copies]:
+                assert lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream) == 0, lib.yvx_cuda_last_error_text()
+        for i in range(3):
+            step(i)
+        lib.yvx_cuda_event_record(first, backend.stream)
+        for i in range(repeats):
+            step(i)
+        lib.yvx_cuda_event_record(last, backend.stream)
+        assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+        lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+        step_ms = ms.value / repeats
+        # each projection alone (events around its launch)
+        alone = {}
+        for k, (name, rows, width, groups, row_bytes, _, _, _) in enumerate(checks):
+            total = 0.0
+            for i in range(repeats):
+                a = calls[i % copies][k]
+                lib.yvx_cuda_event_record(first, backend.stream)
+                lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream)
+                lib.yvx_cuda_event_record(last, backend.stream)
+                lib.yvx_cuda_stream_synchronize(backend.stream)
+                lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+                total += ms.value
+            nbytes = rows * groups * row_bytes
+            alone[name] = {"kernel_us": total / repeats * 1e3, "gbs": nbytes / (total / repeats * 1e-3) / 1e9}
+        graph_ms = None
+        if lib.yvx_cuda_graph_capture_begin(backend.stream) == 0:
+            for i in range(2 * copies):
+                step(i)
+            graph = C.c_void_p()
+            if lib.yvx_cuda_graph_capture_end(backend.stream, C.byref(graph)) == 0:
+                lib.yvx_cuda_graph_launch(graph, backend.stream)
+                lib.yvx_cuda_event_record(first, backend.stream)
+                replays = max(repeats // (2 * copies), 3)
+                for _ in range(replays):
+                    lib.yvx_cuda_graph_launch(graph, backend.stream)
+                lib.yvx_cuda_event_record(last, backend.stream)
+                if lib.yvx_cuda_stream_synchronize(backend.stream) == 0:
+                    lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+                    graph_ms = ms.value / (replays * 2 * copies)
+                lib.yvx_cuda_graph_destroy(graph)
+        # sample rows against the CPU dot
+        equal = True
+        for name, rows, width, groups, row_bytes, x_host, y, a in checks:
+            got = np.zeros((tokens, rows * groups), np.float32)
+            lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream)
+            lib.yvx_cuda_download_async(got.ctypes.data, y, got.nbytes, backend.stream)
+            sample = np.zeros((sample_rows, row_bytes), np.uint8)
+            last_group_first = (groups - 1) * rows
+            lib.yvx_cuda_download_async(sample.ctypes.data, a.weights + last_group_first * row_bytes, sample.nbytes,
+                                        backend.stream)
+            lib.yvx_cuda_stream_synchronize(backend.stream)
+            want = oracle.qtype_matvec(sample, qtype, width,
+                                       np.ascontiguousarray(x_host[:, (groups - 1) * width:groups * width]), 0,
+                                       sample_rows, True)
+            equal = equal and want is not None and bool(np.array_equal(
+                got[:, last_group_first:last_group_first + sample_rows].view(np.uint32), want.view(np.uint32)))
+        best = min(step_ms, graph_ms or step_ms)
+        out[label] = {"step_ms": step_ms, "graph_step_ms": graph_ms, "encoded_bytes": weight_bytes,
+                      "bytes_per_weight": weight_bytes / 106954752.0,
+                      "achieved_gbs": weight_bytes / (best * 1e-3) / 1e9,
+                      "frac_of_measured_hbm": weight_bytes / (best * 1e-3) / 1e9 / hbm_peak,
+                      "per_projection": alone, "sample_rows_bit_equal_to_cpu_dot": equal}
+        for ptr in owned:
+            lib.yvx_cuda_free(ptr)
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    lib.yvx_cuda_free(status)
+    for e in (first, last):
+        lib.yvx_cuda_event_destroy(e)
+    result = {"workload": "projections of one latent decode step (q_a, q_b, kv, grouped out_a, out_b; 106.9 M weights, "
+                          "%d token%s), encoded weights read once per step" % (tokens, "" if tokens == 1 else "s"),
+              "kernel": "qtype_matvec_kernel", "launches_per_step": 5, "status_word": int(st[0]),
+              "roofline_unit": "encoded weight bytes / measured HBM peak", **out}
+    return result, None
+
+
 def bench_activation(lib, backend, abi, hbm_peak, repeats, rows=131072):
     """Activation fake quantisation in place: FP8 E4M3 in blocks of 64 over the 448 leading lanes of
     512-lane rows (what the reference applies to new local rows and emitted compressed rows), and the
@@ -1429,6 +1565,11 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
                 "max_abs_vs_nccl_path": float((fused_out - sharded).abs().max().item())}
     fused_result = exchange_run(0)
     one_launch_result = exchange_run(1)
+    # this rank's shard alone (no exchange, no collective): what the step adds on top of it
+    shard_main_ms, shard_combine_ms, _ = _timed_launches(lib, backend, local, repeats)
+    shard = torch.tensor([shard_main_ms + shard_combine_ms, _timed_launches.step_ms,
+                          _timed_launches.graph_step_ms or 0.0], dtype=torch.float64, device=device)
+    dist.all_reduce(shard, op=dist.ReduceOp.MAX)
     # cross-check on rank 0: the same pool copy, unsharded, on one GPU
     diff = None
     if rank == 0:
@@ -1451,9 +1592,12 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
               "shard_tokens": end.value - begin.value, "status_word": int(st[0]),
               "sharded_vs_single_gpu_max_abs": diff,
               "fused_exchange": fused_result, "one_launch_exchange": one_launch_result,
+              "shard_alone": {"kernels_ms": float(shard[0]), "step_ms": float(shard[1]),
+                              "graph_step_ms": float(shard[2]) or None},
               "ranks": world, "nccl_step_us": ms * 1e3,
               "fused_step_us": fused_result.get("ms_per_step", float("nan")) * 1e3,
-              "one_launch_step_us": one_launch_result.get("ms_per_step", float("nan")) * 1e3}
+              "one_launch_step_us": one_launch_result.get("ms_per_step", float("nan")) * 1e3,
+              "shard_alone_us": float(shard[2] or shard[1]) * 1e3}
     dist.barrier()          # nobody unmaps while a peer may still store
     for mapped in opened:
         lib.yvx_cuda_ipc_close(C.c_void_p(mapped))
@@ -1572,7 +1716,8 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
-                                 "compressor", "activation", "publish", "prefill_f32"],
+                                 "compressor", "activation", "publish", "prefill_f32", "verify_q8_sharded",
+                                 "projections"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1617,11 +1762,30 @@ def main():
         import clori_b200
         from clori_b200 import abi
         backend = clori_b200.Backend(local_rank)
+        if args.workload == "verify_q8_sharded":
+            if dist is None:
+                print(json.dumps({"workload_only": args.workload, "unavailable": "needs two or more ranks"}))
+                return
+            import torch
+            side = torch.cuda.Stream()      # kernels and the all-gather ordered on one stream
+            with torch.cuda.stream(side):
+                backend.bind_stream(side.cuda_stream, synchronous=False)
+                result = bench_verify_q8_sharded(abi.load(), backend, abi, rank, world, dist, torch,
+                                                 max(args.steps, 3))
+            side.synchronize()
+            if rank == 0:
+                print(json.dumps({"workload_only": args.workload, **result}))
+            dist.barrier()
+            dist.destroy_process_group()
+            return
         if args.workload == "mla":
             result, _ = bench_mla(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                   sessions=min(args.sessions, 32))
         elif args.workload == "latent_sparse":
             result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
+        elif args.workload == "projections":
+            result, _ = bench_projections(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
+                                          tokens=max(1, min(args.tokens, 4)) if args.tokens != 8192 else 1)
         elif args.workload == "publish":
             result, _ = bench_publish(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                       tokens=min(args.tokens // 2, 4096))
@@ -1715,6 +1879,7 @@ def main():
                 ("prefill_config3", "prefill", lambda: bench_prefill(lib, b, w.abi, 10)),
                 ("prefill_f32_contract", "prefill_f32", lambda: bench_prefill_f32(lib, b, w.abi, 3)),
                 ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 10)),
+                ("projections_decode_step", "proj", lambda: bench_projections(lib, b, w.abi, hbm_peak, 20)),
                 ("kv_append_rotary", None, lambda: bench_kv_append(lib, b, w.abi, hbm_peak, 10)),
                 ("latent_sparse_decode", None, lambda: bench_latent_sparse(lib, b, w.abi, 20)),
                 ("rolling_compressor", None, lambda: bench_compressor(lib, b, w.abi, hbm_peak, 10)),
@@ -1876,7 +2041,7 @@ def summary_of(line, others):
     if sharded:
         out["cfg4_sharded"] = {k: _r(v) if isinstance(v, float) else v for k, v in sharded.items()
                                if k in ("ranks", "nccl_step_us", "fused_step_us", "one_launch_step_us",
-                                        "single_gpu_step_us", "max_abs_vs_nccl_path")}
+                                        "single_gpu_step_us", "max_abs_vs_nccl_path", "shard_alone_us")}
     return out
 
 

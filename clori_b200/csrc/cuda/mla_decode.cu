@@ -43,6 +43,17 @@ constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256
 constexpr uint32_t kMlaTmemColumns = 512;
 constexpr float kMlaRescaleThreshold = 8.0f;
 
+#ifdef YVX_MLA_TRACE
+// Cycle counters of CTA (0, 0, 0), a development aid compiled out of the library.
+__device__ unsigned long long yvx_mla_trace[16];
+#define MLA_TRACE_BEGIN(t) const long long t = clock64()
+#define MLA_TRACE_ADD(slot, t) \
+    do { if (traced) trace_local[slot] += (unsigned long long)(clock64() - t); } while (0)
+#else
+#define MLA_TRACE_BEGIN(t) do { } while (0)
+#define MLA_TRACE_ADD(slot, t) do { } while (0)
+#endif
+
 struct MlaMaps {
     CUtensorMap query, latent, rope;
 };
@@ -163,6 +174,11 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int half = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+#ifdef YVX_MLA_TRACE
+    const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+    unsigned long long trace_local[4] = {0, 0, 0, 0};
+    const long long trace_start = clock64();
+#endif
     const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
     const unsigned int t0 = split * p.chunk_tokens;
     const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
@@ -220,10 +236,12 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 unsigned char *dst = kv_tiles + stage * kMlaKvBytes;
                 const int token = (int)(t0 + j * kMlaN);
                 // Scores-only part: free as soon as the first 20 k-steps of Q K^T have run.
+                MLA_TRACE_BEGIN(tp0);
                 if (j >= (unsigned)kMlaStages && !mbar_wait(&bars->ka_done[stage], parity)) {
                     atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
                     break;
                 }
+                MLA_TRACE_ADD(0, tp0);
                 mbar_expect_tx(&bars->ka_full[stage], kMlaKOnlyBytes);
                 for (int u = 0; u < 4; ++u)
                     tma_load_3d(dst + kMlaVPartBytes + u * kMlaKvSubBytes, &maps.latent,
@@ -231,15 +249,23 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 tma_load_3d(dst + kMlaVPartBytes + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka_full[stage], 0,
                             token, (int)b);
                 // Own latent half: K of the last 16 k-steps and V of P V; free after P V.
+                MLA_TRACE_BEGIN(tp1);
                 if (j >= (unsigned)kMlaStages && !mbar_wait(&bars->v_done[stage], parity)) {
                     atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
                     break;
                 }
+                MLA_TRACE_ADD(1, tp1);
                 mbar_expect_tx(&bars->kb_full[stage], kMlaVPartBytes);
                 for (int u = 0; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full[stage],
                                 64 * (own0 + u), token, (int)b);
             }
+#ifdef YVX_MLA_TRACE
+            if (traced) {
+                yvx_mla_trace[0] = trace_local[0];   // producer: waiting for a scores-only part to free
+                yvx_mla_trace[1] = trace_local[1];   // producer: waiting for an own-half part to free
+            }
+#endif
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
@@ -251,7 +277,9 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         // operands in shared memory. Frees the scores-only part of the stage.
         auto qk_a = [&](unsigned int j) -> bool {
             const unsigned int stage = j % kMlaStages;
+            MLA_TRACE_BEGIN(tm0);
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->ka_full[stage], (j / kMlaStages) & 1u))) return false;
+            MLA_TRACE_ADD(0, tm0);
             tc_fence_after_sync();
             const uint32_t k_addr = smem_u32(kv_tiles + stage * kMlaKvBytes + kMlaVPartBytes);
 #pragma unroll
@@ -268,7 +296,9 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         // Last 16 k-steps: this CTA's own latent half, query operand in tensor memory.
         auto qk_b = [&](unsigned int j) -> bool {
             const unsigned int stage = j % kMlaStages;
+            MLA_TRACE_BEGIN(tm1);
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->kb_full[stage], (j / kMlaStages) & 1u))) return false;
+            MLA_TRACE_ADD(1, tm1);
             tc_fence_after_sync();
             const uint32_t k_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
 #pragma unroll
@@ -281,7 +311,9 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         };
         auto pv = [&](unsigned int j) -> bool {
             const unsigned int stage = j % kMlaStages;
+            MLA_TRACE_BEGIN(tm2);
             if (!__all_sync(0xffffffffu, mbar_wait(&bars->p_full[j & 1u], (j >> 1) & 1u))) return false;
+            MLA_TRACE_ADD(2, tm2);
             tc_fence_after_sync();
             const uint32_t v_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
 #pragma unroll
@@ -296,15 +328,45 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         bool ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full, 0)) &&
                   __all_sync(0xffffffffu, mbar_wait(&bars->q_tmem_full, 0));
         ok = ok && qk_a(0) && qk_b(0);
-        // Tensor-pipe order per tile: S(j+1) first part, P(j) V(j), S(j+1) second part.
-        // The softmax of tile j runs under the first and the load of the own half of
-        // tile j+1 (which had to wait for P V of tile j-1) lands under the first two.
+        // Tensor-pipe order per tile: S(j+1) first part, then whichever of the two is ready
+        // first: S(j+1) second part (its own-half load had to wait for P V of tile j-1) or
+        // P(j) V(j) (the softmax of tile j). With the second part first the softmax of tile j
+        // has all of S(j+1) to hide under, and that of tile j+1 starts under P(j) V(j).
         for (unsigned int j = 0; ok && j < tiles; ++j) {
-            if (j + 1 < tiles) ok = qk_a(j + 1);
-            ok = ok && pv(j);
-            if (ok && j + 1 < tiles) ok = qk_b(j + 1);
+            bool scores_first = false;
+            if (j + 1 < tiles) {
+                ok = qk_a(j + 1);
+                const unsigned int next = j + 1u;
+                for (uint32_t spin = 0; ok && spin < kWaitSpinLimit; ++spin) {
+                    const bool loaded = mbar_test(&bars->kb_full[next % kMlaStages], (next / kMlaStages) & 1u);
+                    const bool weights = mbar_test(&bars->p_full[j & 1u], (j >> 1) & 1u);
+                    if (__any_sync(0xffffffffu, loaded)) {
+                        scores_first = true;
+#ifdef YVX_MLA_TRACE
+                        trace_local[3] += 1ull;
+#endif
+                        break;
+                    }
+                    if (__any_sync(0xffffffffu, weights)) break;
+                }
+            }
+            if (scores_first) ok = ok && qk_b(j + 1) && pv(j);
+            else {
+                ok = ok && pv(j);
+                if (ok && j + 1 < tiles) ok = qk_b(j + 1);
+            }
         }
         if (!ok && lane == 0) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+#ifdef YVX_MLA_TRACE
+        if (traced) {
+            yvx_mla_trace[2] = trace_local[0];   // issuer: waiting for a scores-only part to land
+            yvx_mla_trace[3] = trace_local[1];   // issuer: waiting for an own-half part to land
+            yvx_mla_trace[4] = trace_local[2];   // issuer: waiting for the softmax weights
+            yvx_mla_trace[5] = trace_local[3];   // tiles whose second score part went first
+            yvx_mla_trace[6] = (unsigned long long)(clock64() - trace_start);
+            yvx_mla_trace[7] = tiles;
+        }
+#endif
     } else {
         // ------------------------------ softmax warps -----------------------------
         const unsigned int head = threadIdx.x;
@@ -340,10 +402,13 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         bool ok = true;
         for (unsigned int j = 0; j < tiles; ++j) {
             const uint32_t s_col = tmem_s + lane_base + (j & 1u) * kMlaN;
+            MLA_TRACE_BEGIN(ts0);
             if (!mbar_wait(&bars->s_full[j & 1u], (j >> 1) & 1u)) {
                 ok = false;
                 break;
             }
+            MLA_TRACE_ADD(0, ts0);
+            MLA_TRACE_BEGIN(ts1);
             tc_fence_after_sync();
             uint32_t s[2][32];
             tmem_ld32(s_col, s[0]);
@@ -368,6 +433,9 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             const float m_tile = row_max * sscale;
             const bool grow = m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY;
             if (__any_sync(0xffffffffu, grow)) {
+#ifdef YVX_MLA_TRACE
+                trace_local[2] += 1ull;
+#endif
                 const float m_new = fmaxf(m_used, m_tile);
                 const float factor = m_new == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
                 l *= factor;
@@ -409,7 +477,16 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&bars->p_full[j & 1u]);
+            MLA_TRACE_ADD(1, ts1);
         }
+#ifdef YVX_MLA_TRACE
+        if (traced && warp == 0) {
+            yvx_mla_trace[8] = trace_local[0];   // softmax warp 0: waiting for scores
+            yvx_mla_trace[9] = trace_local[1];   // softmax warp 0: scores to weights
+            yvx_mla_trace[10] = trace_local[2];  // tiles that rescaled the accumulator
+            yvx_mla_trace[11] = (unsigned long long)(clock64() - trace_start);
+        }
+#endif
         if (ok) ok = mbar_wait(&bars->pv_done, (tiles - 1u) & 1u);
         // The tile loop is over: let the combine kernel's launch overlap the epilogue.
         pdl_launch_dependents();
@@ -529,6 +606,13 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
     p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
     if (!p->max_splits) p->max_splits = 1u;
 }
+
+#ifdef YVX_MLA_TRACE
+int yvx_cuda_mla_trace_read(unsigned long long out[16])
+{
+    return cudaMemcpyFromSymbol(out, yvx::yvx_mla_trace, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 unsigned long long yvx_cuda_mla_absorbed_bytes(const yvx_mla_problem *p)
 {

@@ -64,6 +64,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
     return false;
 }
 
+// One non-blocking look at a barrier phase (for choosing between two pieces of ready work).
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0u;
+}
+
 // 4-D tiled TMA load into shared memory, completion counted on `bar`.
 __device__ __forceinline__ void tma_load_4d(void *dst, const CUtensorMap *map, uint64_t *bar,
                                             int c0, int c1, int c2, int c3)

@@ -258,7 +258,9 @@ def test_capability_query_is_truthful(backend, library, monkeypatch):
 @pytest.mark.parametrize("qtype", [abi.QTYPE_F32, abi.QTYPE_F16, abi.QTYPE_BF16, abi.QTYPE_Q8_0])
 def test_projection_kernel_is_bit_equal_to_the_cpu_dot(backend, oracle, qtype):
     rng = np.random.default_rng(60 + qtype)
-    for rows, width, tokens, groups in ((40, 96, 1, 1), (130, 1024, 5, 1), (64, 4096, 3, 1), (24, 256, 6, 4)):
+    # the last three reach the streaming kernel with 1, 2 and 4 rows per warp (row counts against the SM count)
+    for rows, width, tokens, groups in ((40, 96, 1, 1), (130, 1024, 5, 1), (64, 4096, 3, 1), (24, 256, 6, 4),
+                                        (5000, 1280, 1, 1), (9601, 512, 2, 1), (1300, 2304, 1, 8)):
         values = job_cases.bf16_valued(rng, (rows * groups, width), 1.0 / np.sqrt(width))
         encoded = oracle.qtype_encode_rows(values, qtype)
         stride = groups * width + 8
@@ -281,3 +283,47 @@ def test_projection_kernel_is_bit_equal_to_the_cpu_dot(backend, oracle, qtype):
         assert int(status.read()[0]) == 0
     a.qtype = 10
     assert backend.lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream) == abi.YVEX_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("qtype", [abi.QTYPE_F16, abi.QTYPE_BF16])
+def test_projection_kernel_keeps_subnormal_weights_and_reports_infinite_ones(backend, oracle, qtype):
+    """16-bit weights are placed into doubles bit field by bit field: zeros, subnormals and the
+    largest finite values must come out exactly, an infinite weight must raise the status word."""
+    rng = np.random.default_rng(70 + qtype)
+    rows, width = 64, 512
+    values = job_cases.bf16_valued(rng, (rows, width), 1.0 / np.sqrt(width))
+    tiny = 2.0 ** -24 if qtype == abi.QTYPE_F16 else 2.0 ** -133      # subnormal in the encoding
+    values[::3, ::5] = tiny * rng.integers(1, 64, values[::3, ::5].shape)
+    values[1::7, 3::11] = 0.0
+    values[5, 7] = -0.0
+    values[2::9, 1::13] = 32768.0 if qtype == abi.QTYPE_F16 else 2.0 ** 120
+    encoded = oracle.qtype_encode_rows(values, qtype)
+    decoded = oracle.qtype_decode_rows(encoded, qtype, width)
+    special = np.zeros(values.shape, bool)
+    special[::3, ::5] = special[1::7, 3::11] = special[2::9, 1::13] = True
+    assert np.array_equal(decoded[special], values[special])        # the planted values are exactly representable
+    assert np.signbit(decoded[5, 7]) and decoded[5, 7] == 0.0
+    x = job_cases.bf16_valued(rng, (3, width))
+    x[:, ::17] *= 2.0 ** -30
+    w, xi = backend.tensor("w", encoded.view(np.int8), dtype=abi.DTYPE_I8), backend.tensor("x", x)
+    out = backend.alloc("y", abi.DTYPE_F32, (3, rows))
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    a = abi.MatvecArgs()
+    a.weights, a.qtype, a.rows, a.width, a.row_bytes = w.data_ptr, qtype, rows, width, encoded.shape[1]
+    a.input, a.tokens, a.input_stride = xi.data_ptr, 3, width
+    a.output, a.output_stride, a.groups, a.round_bf16, a.status = out.data_ptr, rows, 1, 0, status.data_ptr
+    assert backend.lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream) == 0
+    assert backend.lib.yvx_cuda_stream_synchronize(backend.stream) == 0
+    out.struct.is_written = 1
+    want = oracle.qtype_matvec(encoded, qtype, width, x, 0, rows, False)
+    assert np.array_equal(out.read().view(np.uint32), want.view(np.uint32))
+    assert int(status.read()[0]) == 0
+    # one infinite weight: the CPU dot refuses, the kernel raises the non-finite status
+    bad = encoded.copy()
+    bad.view(np.uint16)[9, 100] = 0x7c00 if qtype == abi.QTYPE_F16 else 0x7f80
+    assert oracle.qtype_matvec(bad, qtype, width, x, 0, rows, False) is None
+    w2 = backend.tensor("w2", bad.view(np.int8), dtype=abi.DTYPE_I8)
+    a.weights = w2.data_ptr
+    assert backend.lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream) == 0
+    assert backend.lib.yvx_cuda_stream_synchronize(backend.stream) == 0
+    assert int(status.read()[0]) == 1
