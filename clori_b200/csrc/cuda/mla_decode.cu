@@ -30,7 +30,7 @@ constexpr int kMlaWidth = kMlaLatent + kMlaRope;          // 576
 constexpr int kMlaN = 64;                                  // tokens per tile
 constexpr int kMlaHalf = kMlaLatent / 2;                   // accumulator columns per CTA
 constexpr int kMlaStages = 2;
-constexpr int kMlaThreads = 192;
+constexpr int kMlaThreads = 320;   // 4 + 4 softmax warps, the TMA warp (4) and the MMA warp (5)
 constexpr int kMlaQSubBytes = kMlaHeads * 64 * 2;          // [128][64] bf16 = 16 KB
 constexpr int kMlaQTmemDims = kMlaHalf;                   // own-half query dims held in tensor memory                         // query dims held in tensor memory
 constexpr int kMlaQSmemSubs = (kMlaWidth - kMlaQTmemDims) / 64;  // 5 sub-tiles stay in shared memory
@@ -39,7 +39,7 @@ constexpr int kMlaKvSubBytes = kMlaN * 64 * 2;             // [64][64] bf16 = 8 
 constexpr int kMlaKvBytes = (kMlaWidth / 64) * kMlaKvSubBytes; // 72 KB
 constexpr int kMlaVPartBytes = (kMlaHalf / 64) * kMlaKvSubBytes;    // own latent half, first in a stage
 constexpr int kMlaKOnlyBytes = kMlaKvBytes - kMlaVPartBytes;       // other half + rope
-constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256;
+constexpr int kMlaSmemBytes = kMlaQBytes + kMlaStages * kMlaKvBytes + 1024 + 256 + 1024;  // + the softmax halves' exchange
 constexpr uint32_t kMlaTmemColumns = 512;
 constexpr float kMlaRescaleThreshold = 8.0f;
 
@@ -208,7 +208,7 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             mbar_init(&bars->ka_done[i], 1);
             mbar_init(&bars->v_done[i], 1);
             mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], kMlaHeads);
+            mbar_init(&bars->p_full[i], 2 * kMlaHeads);
         }
         mbar_init(&bars->pv_done, 1);
         fence_barrier_init();
@@ -225,6 +225,9 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 
     if (warp == 4) {
         // ------------------------------ TMA producer ------------------------------
+        // Two lanes, one per part of a stage, each with its own free barrier: the scores-only
+        // part of tile j + 2 is requested as soon as the first 20 k-steps of tile j have run,
+        // without queueing behind the own-half part, which has to wait for P V of tile j.
         if (lane == 0) {
             mbar_expect_tx(&bars->q_full, kMlaQBytes);
             for (int u = 0; u < kMlaQSmemSubs; ++u)
@@ -235,7 +238,6 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                 const uint32_t parity = ((j / kMlaStages) - 1u) & 1u;
                 unsigned char *dst = kv_tiles + stage * kMlaKvBytes;
                 const int token = (int)(t0 + j * kMlaN);
-                // Scores-only part: free as soon as the first 20 k-steps of Q K^T have run.
                 MLA_TRACE_BEGIN(tp0);
                 if (j >= (unsigned)kMlaStages && !mbar_wait(&bars->ka_done[stage], parity)) {
                     atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
@@ -248,24 +250,26 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                                 &bars->ka_full[stage], 64 * (other0 + u), token, (int)b);
                 tma_load_3d(dst + kMlaVPartBytes + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka_full[stage], 0,
                             token, (int)b);
+            }
+#ifdef YVX_MLA_TRACE
+            if (traced) yvx_mla_trace[0] = trace_local[0];   // producer: waiting for a scores-only part to free
+#endif
+        } else if (lane == 1) {
+            for (unsigned int j = 0; j < tiles; ++j) {
+                const unsigned int stage = j % kMlaStages;
+                const uint32_t parity = ((j / kMlaStages) - 1u) & 1u;
+                unsigned char *dst = kv_tiles + stage * kMlaKvBytes;
+                const int token = (int)(t0 + j * kMlaN);
                 // Own latent half: K of the last 16 k-steps and V of P V; free after P V.
-                MLA_TRACE_BEGIN(tp1);
                 if (j >= (unsigned)kMlaStages && !mbar_wait(&bars->v_done[stage], parity)) {
                     atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
                     break;
                 }
-                MLA_TRACE_ADD(1, tp1);
                 mbar_expect_tx(&bars->kb_full[stage], kMlaVPartBytes);
                 for (int u = 0; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full[stage],
                                 64 * (own0 + u), token, (int)b);
             }
-#ifdef YVX_MLA_TRACE
-            if (traced) {
-                yvx_mla_trace[0] = trace_local[0];   // producer: waiting for a scores-only part to free
-                yvx_mla_trace[1] = trace_local[1];   // producer: waiting for an own-half part to free
-            }
-#endif
         }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer --------------------------------
@@ -273,6 +277,8 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
         constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
         const uint32_t q_addr = smem_u32(q_tile);
+        const uint32_t elected = tc_elect_one() ? 1u : 0u;   // the one lane that issues everything below
+        constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
         // First 20 k-steps of S(j): the other latent half and the rope dims, both
         // operands in shared memory. Frees the scores-only part of the stage.
         auto qk_a = [&](unsigned int j) -> bool {
@@ -282,15 +288,23 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             MLA_TRACE_ADD(0, tm0);
             tc_fence_after_sync();
             const uint32_t k_addr = smem_u32(kv_tiles + stage * kMlaKvBytes + kMlaVPartBytes);
+#ifdef YVX_MLA_TRACE
+            const long long issue_start = clock64();
+#endif
+            {
+                const uint32_t a_lo = smem_desc_sw128_lo(q_addr, 16), b_lo = smem_desc_sw128_lo(k_addr, 16);
 #pragma unroll
-            for (int ks = 0; ks < 4 * kMlaQSmemSubs; ++ks) {
-                const uint32_t off = (ks & 3) * 32;
-                tc_mma_ss_elect(tmem_s + (j & 1u) * kMlaN,
-                                smem_desc_sw128(q_addr + (ks >> 2) * kMlaQSubBytes + off, 16, 1024),
-                                smem_desc_sw128(k_addr + (ks >> 2) * kMlaKvSubBytes + off, 16, 1024),
-                                idesc_qk, ks ? 1u : 0u);
+                for (int ks = 0; ks < 4 * kMlaQSmemSubs; ++ks) {
+                    const uint32_t off = (ks & 3) * 32;
+                    tc_mma_ss_pred(elected, tmem_s + (j & 1u) * kMlaN, a_lo + (((ks >> 2) * kMlaQSubBytes + off) >> 4), desc_hi,
+                                   b_lo + (((ks >> 2) * kMlaKvSubBytes + off) >> 4), desc_hi, idesc_qk, ks ? 1u : 0u);
+                }
+                tc_commit_pred(elected, &bars->ka_done[stage]);
             }
-            tc_commit_elect(&bars->ka_done[stage]);
+#ifdef YVX_MLA_TRACE
+            if (traced && j == 0) yvx_mla_trace[12] = (unsigned long long)(clock64() - issue_start);   // 20 issues, idle pipe
+            if (traced && j == 40) yvx_mla_trace[13] = (unsigned long long)(clock64() - issue_start);  // 20 issues, steady state
+#endif
             return true;
         };
         // Last 16 k-steps: this CTA's own latent half, query operand in tensor memory.
@@ -301,12 +315,14 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             MLA_TRACE_ADD(1, tm1);
             tc_fence_after_sync();
             const uint32_t k_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
+            {
+                const uint32_t b_lo = smem_desc_sw128_lo(k_addr, 16);
 #pragma unroll
-            for (int ks = 0; ks < kMlaQTmemDims / 16; ++ks)
-                tc_mma_ts_elect(tmem_s + (j & 1u) * kMlaN, tmem_q + ks * 8,
-                                smem_desc_sw128(k_addr + (ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32, 16, 1024),
-                                idesc_qk, 1u);
-            tc_commit_elect(&bars->s_full[j & 1u]);
+                for (int ks = 0; ks < kMlaQTmemDims / 16; ++ks)
+                    tc_mma_ts_pred(elected, tmem_s + (j & 1u) * kMlaN, tmem_q + ks * 8,
+                                   b_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+                tc_commit_pred(elected, &bars->s_full[j & 1u]);
+            }
             return true;
         };
         auto pv = [&](unsigned int j) -> bool {
@@ -316,13 +332,15 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             MLA_TRACE_ADD(2, tm2);
             tc_fence_after_sync();
             const uint32_t v_addr = smem_u32(kv_tiles + stage * kMlaKvBytes);
+            {
+                const uint32_t b_lo = smem_desc_sw128_lo(v_addr, kMlaKvSubBytes);
 #pragma unroll
-            for (int kk = 0; kk < kMlaN / 16; ++kk)
-                tc_mma_ts_elect(tmem_o, tmem_s + (j & 1u) * kMlaN + kk * 8,
-                                smem_desc_sw128(v_addr + kk * 2048, kMlaKvSubBytes, 1024), idesc_pv,
-                                (j || kk) ? 1u : 0u);
-            tc_commit_elect(&bars->v_done[stage]);
-            tc_commit_elect(&bars->pv_done);
+                for (int kk = 0; kk < kMlaN / 16; ++kk)
+                    tc_mma_ts_pred(elected, tmem_o, tmem_s + (j & 1u) * kMlaN + kk * 8, b_lo + ((kk * 2048) >> 4), desc_hi,
+                                   idesc_pv, (j || kk) ? 1u : 0u);
+                tc_commit_pred(elected, &bars->v_done[stage]);
+                tc_commit_pred(elected, &bars->pv_done);
+            }
             return true;
         };
         bool ok = __all_sync(0xffffffffu, mbar_wait(&bars->q_full, 0)) &&
@@ -369,11 +387,18 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 #endif
     } else {
         // ------------------------------ softmax warps -----------------------------
-        const unsigned int head = threadIdx.x;
-        const uint32_t lane_base = ((warp * 32u) << 16);
-        // This head's absorbed-query dims of the CTA's own latent half go to tensor
-        // memory: bf16 pairs are already the 32-bit words the A operand wants.
-        {
+        // Two warps per 32 heads: warps 0-3 take the first 32 tokens of every tile (and the
+        // first half of the accumulator columns), warps 6-9 the last 32 (and the second half).
+        // A warp reaches the tensor-memory lanes 32 * (warp % 4) ..., so the partner of warp w
+        // is the warp of the other group with the same w % 4; the two meet at a named barrier
+        // per tile to agree on the row maximum.
+        const unsigned int side = warp < 4u ? 0u : 1u, quadrant = warp & 3u;
+        const unsigned int head = quadrant * 32u + lane;
+        const uint32_t lane_base = ((quadrant * 32u) << 16);
+        float *exchange = reinterpret_cast<float *>(bars + 1);    // [2 sides][128 heads]
+        if (side == 0u) {
+            // This head's absorbed-query dims of the CTA's own latent half go to tensor
+            // memory: bf16 pairs are already the 32-bit words the A operand wants.
             const uint4 *src = reinterpret_cast<const uint4 *>(
                 reinterpret_cast<const unsigned short *>(p.q_absorbed) +
                 ((unsigned long long)b * kMlaHeads + head) * kMlaWidth + (unsigned long long)half * kMlaHalf);
@@ -410,28 +435,28 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
             MLA_TRACE_ADD(0, ts0);
             MLA_TRACE_BEGIN(ts1);
             tc_fence_after_sync();
-            uint32_t s[2][32];
-            tmem_ld32(s_col, s[0]);
-            tmem_ld32(s_col + 32, s[1]);
+            uint32_t s[32];
+            tmem_ld32(s_col + 32u * side, s);
             tmem_wait_ld();
-            const unsigned int k0 = t0 + j * kMlaN;
-            if (k0 + kMlaN > t1) {
+            const unsigned int k0 = t0 + j * kMlaN + 32u * side;
+            if (k0 + 32u > t1) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (k0 + 32 * i + c >= t1) s[i][c] = 0xff800000u;  // -inf
+                for (int c = 0; c < 32; ++c)
+                    if (k0 + c >= t1) s[c] = 0xff800000u;  // -inf
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-#pragma unroll
-                for (int c = 0; c < 32; c += 2)
-                    mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[i][c]),
-                                            __uint_as_float(s[i][c + 1]));
-            const float row_max = max3(mx[0], mx[1], fmaxf(mx[2], mx[3]));
+            for (int c = 0; c < 32; c += 2)
+                mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+            // both halves of the row have been read (the weights of one half overwrite score
+            // columns of the other) and the row maximum is the larger of the two halves'
+            if (j > 0) named_barrier(2 + (int)quadrant, 64);   // the partner has read the previous tile's maximum
+            exchange[side * kMlaHeads + head] = max3(mx[0], mx[1], fmaxf(mx[2], mx[3]));
+            named_barrier(2 + (int)quadrant, 64);
+            const float row_max = fmaxf(exchange[head], exchange[kMlaHeads + head]);
             const float m_tile = row_max * sscale;
             const bool grow = m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY;
+            // the same rows on both sides: the partner warp takes the same branch
             if (__any_sync(0xffffffffu, grow)) {
 #ifdef YVX_MLA_TRACE
                 trace_local[2] += 1ull;
@@ -448,32 +473,31 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
                     }
                     tc_fence_after_sync();
 #pragma unroll 1
-                    for (int i = 0; i < kMlaHalf / 32; ++i) {
+                    for (int i = 0; i < kMlaHalf / 64; ++i) {
                         uint32_t o[32];
-                        tmem_ld32(tmem_o + lane_base + 32 * i, o);
+                        const uint32_t column = tmem_o + lane_base + 128u * side + 32u * i;
+                        tmem_ld32(column, o);
                         tmem_wait_ld();
 #pragma unroll
                         for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-                        tmem_st32(tmem_o + lane_base + 32 * i, o);
+                        tmem_st32(column, o);
                     }
                     tmem_wait_st();
                 }
             }
             const float offset = m_used == -INFINITY ? 0.0f : -m_used;
-            uint32_t packed[32];
+            uint32_t packed[16];
             float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
-#pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(s[i][c]), sscale, offset));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(s[i][c + 1]), sscale, offset));
-                    sum0 += p0;
-                    sum1 += p1;
-                    packed[16 * i + (c >> 1)] = pack_bf16(p0, p1);
-                }
+            for (int c = 0; c < 32; c += 2) {
+                const float p0 = exp2_approx(fmaf(__uint_as_float(s[c]), sscale, offset));
+                const float p1 = exp2_approx(fmaf(__uint_as_float(s[c + 1]), sscale, offset));
+                sum0 += p0;
+                sum1 += p1;
+                packed[c >> 1] = pack_bf16(p0, p1);
+            }
             l += sum0 + sum1;
-            tmem_st32(s_col, packed);
+            tmem_st16(s_col + 16u * side, packed);
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&bars->p_full[j & 1u]);
@@ -491,30 +515,37 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
         // The tile loop is over: let the combine kernel's launch overlap the epilogue.
         pdl_launch_dependents();
         // A wait that gave up is recorded; the rows are still written out so that
-        // every softmax thread reaches the named barrier below exactly once.
+        // every softmax thread reaches the named barriers below exactly once.
         if (!__all_sync(0xffffffffu, ok)) atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
         {
             tc_fence_after_sync();
+            // the row's denominator is the sum of the two halves'
+            named_barrier(2 + (int)quadrant, 64);          // the last tile's maxima have been read
+            exchange[side * kMlaHeads + head] = l;
+            named_barrier(2 + (int)quadrant, 64);
+            l = exchange[head] + exchange[kMlaHeads + head];
             const float inverse = l > 0.0f ? 1.0f / l : 0.0f;
             // Every tile has been consumed, so the tile ring is free: the normalised
             // rows go through it, and each warp then writes whole partial rows with
             // coalesced 8-byte stores (a partial row is 8-byte aligned only).
             float *staged = reinterpret_cast<float *>(kv_tiles);
-            float *mine = staged + head * (unsigned)part_stride;
+            float *mine = staged + head * (unsigned)part_stride + 128u * side;
 #pragma unroll 1
-            for (int i = 0; i < kMlaHalf / 32; ++i) {
+            for (int i = 0; i < kMlaHalf / 64; ++i) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + lane_base + 32 * i, o);
+                tmem_ld32(tmem_o + lane_base + 128u * side + 32 * i, o);
                 tmem_wait_ld();
 #pragma unroll
                 for (int c = 0; c < 32; c += 2)
                     *reinterpret_cast<float2 *>(mine + 32 * i + c) =
                         make_float2(__uint_as_float(o[c]) * inverse, __uint_as_float(o[c + 1]) * inverse);
             }
-            *reinterpret_cast<float2 *>(mine + kMlaHalf) =
-                make_float2(m_used == -INFINITY ? -INFINITY : m_used * 0.6931471805599453f, l);
-            named_barrier(1, kMlaHeads);
-            for (unsigned int r = warp; r < (unsigned)kMlaHeads; r += 4u) {
+            if (side == 1u)
+                *reinterpret_cast<float2 *>(staged + head * (unsigned)part_stride + kMlaHalf) =
+                    make_float2(m_used == -INFINITY ? -INFINITY : m_used * 0.6931471805599453f, l);
+            named_barrier(1, 2 * kMlaHeads);
+            const unsigned int writer = side * 4u + quadrant;
+            for (unsigned int r = writer; r < (unsigned)kMlaHeads; r += 8u) {
                 float2 *dst = reinterpret_cast<float2 *>(
                     p.partials +
                     ((((unsigned long long)b * kMlaHeads + r) * 2ull + half) * p.max_splits + split) * part_stride);

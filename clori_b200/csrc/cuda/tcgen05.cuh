@@ -87,6 +87,19 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         : "memory");
 }
 
+// True in exactly one lane of a converged warp (the lane that then issues a batch of
+// tcgen05 instructions on its own: one election per batch, not per instruction).
+__device__ __forceinline__ bool tc_elect_one()
+{
+    uint32_t elected;
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, pe;\n\t}"
+        : "=r"(elected));
+    return elected != 0u;
+}
+
 // Warp-converged forms: every lane of the warp executes the call with the same
 // (warp-uniform) arguments and one elected lane issues the instruction, so the
 // descriptors can stay in uniform registers instead of being broadcast per issue.
@@ -119,6 +132,53 @@ __device__ __forceinline__ void tc_mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem
         "setp.ne.b32 pa, %4, 0;\n\t"
         "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pa;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Predicated forms for a batch: `elected` comes from ONE tc_elect_one() (nonzero in one lane),
+// every lane executes the call converged, the descriptors are given as their low words (start
+// address field + leading offset: base + a per-step constant) and one shared high word, so a
+// k-step costs one add per operand instead of rebuilding a 64-bit descriptor.
+__host__ __device__ constexpr uint32_t smem_desc_sw128_hi(uint32_t sbo_bytes)
+{
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_sw128_lo(uint32_t smem_addr, uint32_t lbo_bytes)
+{
+    return ((smem_addr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ void tc_mma_ss_pred(uint32_t elected, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                               uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred pe, pa;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 pe, %0, 0;\n\t"
+        "setp.ne.b32 pa, %7, 0;\n\t"
+        "mov.b64 da, {%2, %3};\n\t"
+        "mov.b64 db, {%4, %5};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%1], da, db, %6, pa;\n\t}"
+        ::"r"(elected), "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_pred(uint32_t elected, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred pe, pa;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 pe, %0, 0;\n\t"
+        "setp.ne.b32 pa, %6, 0;\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], db, %5, pa;\n\t}"
+        ::"r"(elected), "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pred(uint32_t elected, uint64_t *bar)
+{
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t"
+        "setp.ne.b32 pe, %0, 0;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+        ::"r"(elected), "r"(smem_u32(bar))
         : "memory");
 }
 
