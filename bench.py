@@ -899,6 +899,115 @@ def bench_compressor(lib, backend, abi, hbm_peak, repeats, tokens=32768):
     return result, None
 
 
+def bench_reference_gpu(lib, backend, abi, repeats=5):
+    """The reference's OWN CUDA attention kernel (yvex_gqa_f32, src/backend/cuda/transformer_kernels.cu:137-238,
+    compiled for sm_100 from its source into oracle/_ref by `make -C oracle ref_cuda`) launched with the
+    reference's geometry (src/backend/cuda/transformer.c:790-803: 128 threads = 4 query rows per block, one block
+    per (row tile, query head), 2 * head_dim floats of shared memory) on config 1 and on a small F32 causal
+    prefill, timed between CUDA events, its output compared with this library's on the same device buffers."""
+    from oracle.binding import REFERENCE_CUBIN
+    if not os.path.exists(REFERENCE_CUBIN):
+        return {"unavailable": "oracle/_ref/transformer_kernels.sm_100.cubin is not built (make -C oracle ref_cuda)"}
+    try:
+        from cuda.bindings import driver as cu
+    except Exception as error:       # pragma: no cover
+        return {"unavailable": f"cuda-python is not importable: {error}"}
+    err, module = cu.cuModuleLoadData(open(REFERENCE_CUBIN, "rb").read())
+    if int(err) != 0:
+        return {"unavailable": f"cuModuleLoadData: {err}"}
+    err, function = cu.cuModuleGetFunction(module, b"yvex_gqa_f32")
+    assert int(err) == 0, err
+
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    first, last, ms = event(), event(), C.c_float()
+    out = {}
+    # the third case has bf16-valued F32 inputs (what the reference's runtime feeds its attention) and
+    # takes this library's default dispatch: staged to bf16 for the tensor cores behind the device gate
+    for name, rows, tokens, hq, hkv, hd, copies, valued in (("config1_decode_f32", 1, 4096, 32, 8, 128, 16, 0),
+                                                            ("prefill_f32_2048x16q4kv_exact", 2048, 2048, 16, 4, 128, 1, 0),
+                                                            ("prefill_f32_2048x16q4kv_bf16_valued", 2048, 2048, 16, 4, 128, 1, 1)):
+        width = hkv * hd
+        kv_elems = tokens * width
+        k, v = _alloc(lib, copies * kv_elems * 4), _alloc(lib, copies * kv_elems * 4)
+        q, mine, theirs = _alloc(lib, rows * hq * hd * 4), _alloc(lib, rows * hq * hd * 4), _alloc(lib, rows * hq * hd * 4)
+        status, tickets = _alloc(lib, 4), _alloc(lib, 8 * hkv)
+        lib.yvx_cuda_memset_async(tickets, 0, 8 * hkv, backend.stream)
+        lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+        fill = -abi.DTYPE_F32 if valued else abi.DTYPE_F32
+        lib.yvx_cuda_fill_normal(k, fill, copies * kv_elems, 601, 1.0, backend.stream)
+        lib.yvx_cuda_fill_normal(v, fill, copies * kv_elems, 602, 1.0, backend.stream)
+        lib.yvx_cuda_fill_normal(q, fill, rows * hq * hd, 603, 1.0, backend.stream)
+        staging = None
+        problems, scratch = [], None
+        for i in range(copies):
+            p = abi.GqaProblem()
+            p.sessions, p.query_rows, p.query_heads, p.kv_heads, p.head_dim = 1, rows, hq, hkv, hd
+            p.causal, p.scale = 1, 1.0 / np.sqrt(hd)
+            p.query_dtype = p.kv_dtype = p.output_dtype = abi.DTYPE_F32
+            p.query, p.query_row_stride, p.output = q, hq * hd, mine
+            p.key, p.value = k.value + i * kv_elems * 4, v.value + i * kv_elems * 4
+            p.key_token_stride = p.value_token_stride = width
+            p.key_head_stride = p.value_head_stride = hd
+            p.kv_tokens_uniform = p.kv_tokens_max = tokens
+            p.query_start_uniform = tokens - rows
+            p.force_general = 1 if rows > 1 and not valued else 0
+            lib.yvx_cuda_gqa_plan_splits(C.byref(p), backend.sm_count)
+            if scratch is None:
+                scratch = _alloc(lib, max(lib.yvx_cuda_gqa_partials_bytes(C.byref(p)), 16))
+                staging_bytes = lib.yvx_cuda_gqa_f32_staging_bytes(C.byref(p)) if valued else 0
+                staging = _alloc(lib, staging_bytes) if staging_bytes else None
+            p.partials, p.status, p.tickets = scratch, status, tickets
+            if staging is not None:
+                p.f32_staging = staging
+            problems.append(p)
+        n = C.c_uint()
+
+        def ours(i):
+            assert lib.yvx_cuda_gqa_attention(C.byref(problems[i % copies]), backend.stream, C.byref(n)) == 0
+
+        def reference(i):
+            values = [C.c_void_p(q.value), C.c_void_p(k.value + (i % copies) * kv_elems * 4),
+                      C.c_void_p(v.value + (i % copies) * kv_elems * 4), C.c_void_p(theirs.value),
+                      C.c_ulonglong(rows), C.c_ulonglong(tokens), C.c_ulonglong(tokens - rows), C.c_ulonglong(hq),
+                      C.c_ulonglong(hkv), C.c_ulonglong(hd), C.c_ulonglong(hq * hd), C.c_ulonglong(width),
+                      C.c_ulonglong(width), C.c_float(1.0 / np.sqrt(hd)), C.c_int(1)]
+            params = (C.c_void_p * len(values))(*[C.addressof(x) for x in values])
+            grid = ((rows + 3) // 4) * hq
+            stream = cu.CUstream(backend.stream.value if hasattr(backend.stream, "value") else int(backend.stream))
+            err, = cu.cuLaunchKernel(function, grid, 1, 1, 128, 1, 1, 2 * hd * 4, stream, C.addressof(params), 0)
+            assert int(err) == 0, err
+        timings = {}
+        for label, run in (("ours", ours), ("reference", reference)):
+            run(0)
+            lib.yvx_cuda_event_record(first, backend.stream)
+            for i in range(repeats):
+                run(i)
+            lib.yvx_cuda_event_record(last, backend.stream)
+            assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+            lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+            timings[label] = ms.value / repeats
+        # both on the same copy, then compare
+        ours(0)
+        reference(0)
+        a, b = np.empty(rows * hq * hd, np.float32), np.empty(rows * hq * hd, np.float32)
+        lib.yvx_cuda_download_async(a.ctypes.data, mine, a.nbytes, backend.stream)
+        lib.yvx_cuda_download_async(b.ctypes.data, theirs, b.nbytes, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
+        out[name] = {"reference_gpu_ms": timings["reference"], "this_library_ms": timings["ours"],
+                     "speedup": timings["reference"] / timings["ours"],
+                     "max_scaled_difference": float(np.max(np.abs(a - b) / (1.0 + np.abs(b)))),
+                     "grid": ((rows + 3) // 4) * hq}
+        for ptr in (k, v, q, mine, theirs, status, tickets, scratch) + ((staging,) if staging is not None else ()):
+            lib.yvx_cuda_free(ptr)
+    for e in (first, last):
+        lib.yvx_cuda_event_destroy(e)
+    cu.cuModuleUnload(module)
+    return {"kernel": "yvex_gqa_f32 (the reference's CUDA kernel, compiled for sm_100 from its source)", **out}
+
+
 def bench_projections(lib, backend, abi, hbm_peak, repeats, tokens=1):
     """The five projections around the latent attention of one decode step at the reference
     configuration's widths (hidden 4096, query rank 1024, 64 heads x 512, 8 output groups,
@@ -1529,11 +1638,12 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
         fp.partials = scratch
         fused.append(fp)
 
-    def exchange_run(one_launch):
+    def exchange_run(one_launch, tagged=0):
         exchange = exchange_area()
         if exchange is None or os.environ.get("YVEX_BENCH_NO_FUSED_EXCHANGE"):
             return {"unavailable": "peer mapping of the exchange areas failed on some rank"}
         exchange.one_launch = one_launch
+        exchange.tagged_words = tagged
         epoch = [0]
 
         def fused_step(i):
@@ -1563,11 +1673,15 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
         return {"ms_per_step": fused_ms, "tokens_per_s": rows / (fused_ms * 1e-3),
                 "aggregate_gbs": (pool_bytes + rows * hq * hd * (2 + 4)) / (fused_ms * 1e-3) / 1e9,
                 "launches_per_step": fused_launches,
-                "collective": "none: peer stores of %d bytes to each rank inside the %s"
-                              % (items * (hd + 2) * 4, "attention kernel's tail" if one_launch else "fold kernel"),
+                "collective": "none: peer stores of %d bytes to each rank inside the %s%s"
+                              % (items * (hd + 2) * (8 if tagged else 4),
+                                 "attention kernel's tail" if one_launch else "fold kernel",
+                                 " as (value, epoch) words, no fence, no counter" if tagged else ""),
                 "max_abs_vs_nccl_path": float((fused_out - sharded).abs().max().item())}
     fused_result = exchange_run(0)
     one_launch_result = exchange_run(1)
+    fused_tagged_result = exchange_run(0, 1)
+    one_launch_tagged_result = exchange_run(1, 1)
     # this rank's shard alone (no exchange, no collective): what the step adds on top of it
     shard_main_ms, shard_combine_ms, _ = _timed_launches(lib, backend, local, repeats)
     shard = torch.tensor([shard_main_ms + shard_combine_ms, _timed_launches.step_ms,
@@ -1595,6 +1709,9 @@ def bench_verify_q8_sharded(lib, backend, abi, rank, world, dist, torch, repeats
               "shard_tokens": end.value - begin.value, "status_word": int(st[0]),
               "sharded_vs_single_gpu_max_abs": diff,
               "fused_exchange": fused_result, "one_launch_exchange": one_launch_result,
+              "fused_tagged_exchange": fused_tagged_result, "one_launch_tagged_exchange": one_launch_tagged_result,
+              "fused_tagged_step_us": fused_tagged_result.get("ms_per_step", float("nan")) * 1e3,
+              "one_launch_tagged_step_us": one_launch_tagged_result.get("ms_per_step", float("nan")) * 1e3,
               "shard_alone": {"kernels_ms": float(shard[0]), "step_ms": float(shard[1]),
                               "graph_step_ms": float(shard[2]) or None},
               "ranks": world, "nccl_step_us": ms * 1e3,
@@ -1720,7 +1837,7 @@ def main():
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
                                  "compressor", "activation", "publish", "prefill_f32", "verify_q8_sharded",
-                                 "projections"],
+                                 "projections", "reference_gpu"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1786,6 +1903,8 @@ def main():
                                   sessions=min(args.sessions, 32))
         elif args.workload == "latent_sparse":
             result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
+        elif args.workload == "reference_gpu":
+            result = bench_reference_gpu(abi.load(), backend, abi, max(args.steps, 3) if args.steps != 200 else 5)
         elif args.workload == "projections":
             result, _ = bench_projections(abi.load(), backend, abi, measured_peaks()[0], max(args.steps, 3),
                                           tokens=max(1, min(args.tokens, 4)) if args.tokens != 8192 else 1)
@@ -2051,6 +2170,7 @@ def summary_of(line, others):
     if sharded:
         out["cfg4_sharded"] = {k: _r(v) if isinstance(v, float) else v for k, v in sharded.items()
                                if k in ("ranks", "nccl_step_us", "fused_step_us", "one_launch_step_us",
+                                        "fused_tagged_step_us", "one_launch_tagged_step_us",
                                         "single_gpu_step_us", "max_abs_vs_nccl_path", "shard_alone_us")}
     return out
 

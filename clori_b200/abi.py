@@ -162,7 +162,8 @@ class LatentReduceArgs(C.Structure):
 class LseExchange(C.Structure):
     """yvx_lse_exchange (include/yvex_b200/cuda_shim.h)."""
     _fields_ = [("ranks", C.c_uint), ("rank", C.c_uint), ("epoch", C.c_uint),
-                ("gather", C.c_void_p), ("arrivals", C.c_void_p), ("one_launch", C.c_int)]
+                ("gather", C.c_void_p), ("arrivals", C.c_void_p), ("one_launch", C.c_int),
+                ("tagged_words", C.c_int)]
 
 
 class KvCopy(C.Structure):
@@ -534,7 +535,7 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_stream_synchronize", "yvx_cuda_device_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_stream_wait_event", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
     "yvx_cuda_lse_exchange_bytes", "yvx_cuda_lse_exchange_counter_offset", "yvx_cuda_gqa_attention_exchange",
-    "yvx_cuda_lse_exchange_emulated", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
+    "yvx_cuda_lse_exchange_emulated", "yvx_cuda_lse_exchange_emulated_form", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
     "yvx_cuda_graph_capture_begin", "yvx_cuda_graph_capture_end", "yvx_cuda_graph_launch", "yvx_cuda_graph_destroy",
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_f32_staging_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
@@ -683,6 +684,8 @@ def load():
     lib.yvx_cuda_lse_exchange_counter_offset.argtypes = [C.c_uint, C.c_uint, C.c_uint]
     lib.yvx_cuda_gqa_attention_exchange.argtypes = [P(GqaProblem), P(LseExchange), vp, P(C.c_uint)]
     lib.yvx_cuda_lse_exchange_emulated.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, vp, C.c_uint, vp, vp, vp]
+    lib.yvx_cuda_lse_exchange_emulated_form.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, vp, C.c_uint, vp, vp, vp,
+                                                        C.c_int, C.c_int]
     lib.yvx_cuda_ipc_export.argtypes = [vp, vp]
     lib.yvx_cuda_ipc_open.argtypes = [vp, P(vp)]
     lib.yvx_cuda_ipc_close.argtypes = [vp]

@@ -102,6 +102,104 @@ __device__ __forceinline__ bool exchange_item(const yvx_lse_exchange &x, unsigne
     return true;
 }
 
+
+// ---- the same exchange without fences or counters ------------------------------------------
+// Every 32-bit lane of a row travels in its own 8-byte word (value, epoch): an aligned 8-byte
+// store is indivisible, so a receiver that reads the epoch of this step in a word has its value
+// too, and nothing has to be ordered: no system-wide fence, no arrival counter, one NVLink store
+// latency from the sender's last store to the receiver's fold. The area is [2 epochs][ranks]
+// [items][head_dim + 2] words of 8 bytes, zero-filled once; epochs count from 1 and only grow,
+// and the parity double buffer keeps a fast rank from overwriting words a slow one still reads
+// (finishing an epoch needs every peer's words of that epoch). Waits are bounded.
+__device__ __forceinline__ void store_word_system(uint2 *address, uint32_t value, uint32_t tag)
+{
+    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(address), "r"(value), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 load_word_system(const uint2 *address)
+{
+    uint2 word;
+    asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];" : "=r"(word.x), "=r"(word.y) : "l"(address) : "memory");
+    return word;
+}
+
+// Bounded wait for one tagged word; returns false when the tag did not come (or when another
+// thread of the group has already given up: `alive` in shared memory turns 0).
+__device__ __forceinline__ bool wait_word_system(const uint2 *address, uint32_t tag, float *value,
+                                                 const volatile int *alive)
+{
+    for (unsigned int spin = 0; spin < kExchangeSpinLimit; ++spin) {
+        const uint2 word = load_word_system(address);
+        if (word.y == tag) {
+            *value = __uint_as_float(word.x);
+            return true;
+        }
+        if (spin > 64u) {
+            __nanosleep(100);
+            if ((spin & 1023u) == 0u && !*alive) break;
+        }
+    }
+    *value = 0.0f;
+    return false;
+}
+
+// `row` [hd + 2], `scales` [2 * ranks floats] and `flag` live in shared memory; `threads`
+// participants (at least x.ranks) meet at Sync::sync().
+template <typename Sync>
+__device__ __forceinline__ bool exchange_item_tagged(const yvx_lse_exchange &x, unsigned int rank, unsigned int items,
+                                                     unsigned int item, unsigned int hd, const float *row,
+                                                     float *scales, int *flag, unsigned int tid, unsigned int threads,
+                                                     void *output, int output_dtype, unsigned long long output_index,
+                                                     int *status, bool publish = true)
+{
+    const unsigned int stride = hd + 2u;
+    const unsigned long long slot = ((unsigned long long)(x.epoch & 1u) * x.ranks + rank) * items + item;
+    for (unsigned int r = 0; publish && r < x.ranks; ++r) {   // (publish = false: a rank that never comes, for tests)
+        uint2 *dst = reinterpret_cast<uint2 *>(x.gather[r]) + slot * stride;
+        for (unsigned int d = tid; d < stride; d += threads) store_word_system(dst + d, __float_as_uint(row[d]), x.epoch);
+    }
+    if (tid == 0) *flag = 1;
+    Sync::sync();
+    const uint2 *base = reinterpret_cast<const uint2 *>(x.gather[rank]) +
+                        ((unsigned long long)(x.epoch & 1u) * x.ranks * items + item) * stride;
+    const unsigned long long rank_stride = (unsigned long long)items * stride;
+    // thread r fetches rank r's (m, l)
+    for (unsigned int r = tid; r < x.ranks; r += threads) {
+        float m, l;
+        const bool came = wait_word_system(base + r * rank_stride + hd, x.epoch, &m, flag) &&
+                          wait_word_system(base + r * rank_stride + hd + 1u, x.epoch, &l, flag);
+        if (!came) *flag = 0;
+        scales[2u * r] = came ? m : -INFINITY;
+        scales[2u * r + 1u] = came ? l : 0.0f;
+    }
+    Sync::sync();   // the (m, l) of every rank are in shared memory
+    bool mine_came = true;
+    for (unsigned int d = tid; d < hd; d += threads) {
+        float run_max = -INFINITY, run_sum = 0.0f, acc = 0.0f;
+        for (unsigned int r = 0; r < x.ranks; ++r) {
+            float value;
+            mine_came = wait_word_system(base + r * rank_stride + d, x.epoch, &value, flag) && mine_came;
+            const float mr = scales[2u * r], lr = scales[2u * r + 1u];
+            if (mr == -INFINITY) continue;  // empty shard
+            const float new_max = fmaxf(run_max, mr);
+            const float keep = expf(run_max - new_max);
+            const float weight = lr * expf(mr - new_max);
+            run_sum = fmaf(run_sum, keep, weight);
+            acc = fmaf(acc, keep, value * weight);
+            run_max = new_max;
+        }
+        const float value = acc / run_sum;
+        if (mine_came && *flag) {
+            if (!isfinite(value)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
+            store_output(output, output_dtype, output_index + d, value);
+        }
+    }
+    if (!mine_came || !*flag) {
+        atomicCAS(status, 0, YVX_STATUS_TIMEOUT);
+        return false;
+    }
+    return true;
+}
+
 // The fold of one item's split partials by `WARPS` warps that meet at Sync::sync(): warp w takes
 // splits w, w + WARPS, ...; a lane owns four dimensions (head_dim 128); the warps' running states
 // are merged in warp order through `scratch` ([WARPS][head_dim + 2] floats of shared memory) into

@@ -505,9 +505,15 @@ gqa_decode_q8_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x)
             fold_splits_128<kQ8ConsumerWarps, Q8ConsumerSync>(
                 p.partials + item * p.max_splits * (kQ8HeadDim + 2ull), p.max_splits, fold_scratch, fold_row, threadIdx.x);
         }
-        if (!exchange_item<Q8ConsumerSync>(x, x.rank, items, (unsigned int)item, kQ8HeadDim, fold_row, flag, threadIdx.x,
-                                           kQ8ConsumerWarps * 32u, p.output, p.output_dtype, item * kQ8HeadDim, p.status))
-            return;
+        const bool came =
+            x.tagged_words
+                ? exchange_item_tagged<Q8ConsumerSync>(x, x.rank, items, (unsigned int)item, kQ8HeadDim, fold_row,
+                                                       fold_scratch, flag, threadIdx.x, kQ8ConsumerWarps * 32u, p.output,
+                                                       p.output_dtype, item * kQ8HeadDim, p.status)
+                : exchange_item<Q8ConsumerSync>(x, x.rank, items, (unsigned int)item, kQ8HeadDim, fold_row, flag,
+                                                threadIdx.x, kQ8ConsumerWarps * 32u, p.output, p.output_dtype,
+                                                item * kQ8HeadDim, p.status);
+        if (!came) return;
         Q8ConsumerSync::sync();
     }
 }

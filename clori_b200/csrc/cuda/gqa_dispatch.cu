@@ -267,7 +267,8 @@ int yvx_cuda_gqa_attention_exchange(const yvx_gqa_problem *p, const yvx_lse_exch
 unsigned long long yvx_cuda_lse_exchange_counter_offset(unsigned int ranks, unsigned int items,
                                                         unsigned int head_dim)
 {
-    const unsigned long long bytes = 2ull * ranks * items * (head_dim + 2ull) * sizeof(float);
+    // sized for the tagged-word form (8 bytes per lane); the float form uses the first half
+    const unsigned long long bytes = 2ull * ranks * items * (head_dim + 2ull) * 8ull;
     return (bytes + 255ull) & ~255ull;
 }
 

@@ -166,8 +166,8 @@ int yvx_cuda_gqa_attention_profiled(const yvx_gqa_problem *problem, void *stream
  * counterpart (the reference is single-device); it replaces the sequence local
  * combine -> NCCL all-gather -> yvx_cuda_lse_combine_strided.
  * Each rank allocates an area of yvx_cuda_lse_exchange_bytes(ranks, items, head_dim)
- * bytes: [2][ranks][items][head_dim + 2] floats followed by [items] 32-bit arrival
- * counters, zero-filled once; exports it with yvx_cuda_ipc_export, opens its peers'
+ * bytes: room for [2][ranks][items][head_dim + 2] 8-byte words (the float form uses the
+ * first half) followed by [items] 32-bit arrival counters and [items] tickets, zero-filled once; exports it with yvx_cuda_ipc_export, opens its peers'
  * handles with yvx_cuda_ipc_open, and passes device arrays of the `ranks` area
  * pointers and counter pointers (own entries are the local addresses). `epoch`
  * counts calls from 1 and must be the same on every rank for the same step.
@@ -181,6 +181,11 @@ typedef struct yvx_lse_exchange {
                                         Q8_0 KV, uniform lengths, a grid that is resident at once,
                                         and the same split plan every epoch of an area; otherwise
                                         the two-launch path is taken silently) */
+    int tagged_words;                /* 1: every 32-bit lane of a row travels as an 8-byte (value, epoch)
+                                        word and receivers poll the words themselves: no system-wide fence
+                                        and no arrival counter on the path. The area is then laid out as
+                                        [2][ranks][items][head_dim + 2] 8-byte words; an area serves one
+                                        of the two forms for its whole life */
 } yvx_lse_exchange;
 unsigned long long yvx_cuda_lse_exchange_bytes(unsigned int ranks, unsigned int items, unsigned int head_dim);
 unsigned long long yvx_cuda_lse_exchange_counter_offset(unsigned int ranks, unsigned int items,
@@ -193,6 +198,12 @@ int yvx_cuda_lse_exchange_emulated(const float *rows, unsigned int ranks, unsign
                                    unsigned int head_dim, float *const *gather,
                                    unsigned int *const *arrivals, unsigned int epoch, float *output,
                                    int *status, void *stream);
+/* The same with the form of the area chosen (tagged_words as in yvx_lse_exchange) and, in the
+ * tagged form, one rank that never publishes (absent_rank >= 0): the others' bounded waits run out. */
+int yvx_cuda_lse_exchange_emulated_form(const float *rows, unsigned int ranks, unsigned int items,
+                                        unsigned int head_dim, float *const *gather,
+                                        unsigned int *const *arrivals, unsigned int epoch, float *output,
+                                        int *status, void *stream, int tagged_words, int absent_rank);
 /* CUDA IPC for the exchange areas: a 64-byte handle of a yvx_cuda_malloc allocation,
  * and the mapping of a peer's handle into this process (peer access is enabled). */
 int yvx_cuda_ipc_export(void *device_pointer, void *handle_64_bytes);

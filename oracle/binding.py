@@ -157,6 +157,15 @@ def build_oracle(tree=None):
     reference_tree_path = tree or reference_tree()
     if reference_tree_path:
         subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={reference_tree_path}"], check=True)
+        import shutil
+        nvcc = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        if os.path.exists(nvcc):
+            # the reference's CUDA attention kernels as a cubin (timed by bench.py as "reference_gpu")
+            subprocess.run(["make", "-s", "-C", HERE, "ref_cuda", f"REF={reference_tree_path}", f"NVCC={nvcc}"],
+                           check=True)
+
+
+REFERENCE_CUBIN = os.path.join(HERE, "_ref", "transformer_kernels.sm_100.cubin")
 
 
 class _Gqa:

@@ -22,8 +22,9 @@ def fold(rows):
     return (rows[:, :, :hd].astype(np.float64) * w[:, :, None]).sum(axis=0) / w.sum(axis=0)[:, None]
 
 
+@pytest.mark.parametrize("tagged", [0, 1])
 @pytest.mark.parametrize("ranks,items,hd", [(2, 16, 128), (4, 128, 128), (8, 40, 64)])
-def test_emulated_ranks_fold_each_others_rows(backend, ranks, items, hd):
+def test_emulated_ranks_fold_each_others_rows(backend, ranks, items, hd, tagged):
     lib, rng = backend.lib, np.random.default_rng(ranks * 100 + items)
     area_bytes = lib.yvx_cuda_lse_exchange_bytes(ranks, items, hd)
     counter_offset = lib.yvx_cuda_lse_exchange_counter_offset(ranks, items, hd)
@@ -39,8 +40,8 @@ def test_emulated_ranks_fold_each_others_rows(backend, ranks, items, hd):
         if epoch == 2:
             rows[0, :, hd], rows[0, :, hd + 1] = -np.inf, 0.0                            # an empty shard
         t = backend.tensor("rows", rows)
-        rc = lib.yvx_cuda_lse_exchange_emulated(t.data_ptr, ranks, items, hd, gather.data_ptr, arrivals.data_ptr,
-                                                epoch, out.data_ptr, status.data_ptr, backend.stream)
+        rc = lib.yvx_cuda_lse_exchange_emulated_form(t.data_ptr, ranks, items, hd, gather.data_ptr, arrivals.data_ptr,
+                                                     epoch, out.data_ptr, status.data_ptr, backend.stream, tagged, -1)
         assert rc == 0, lib.yvx_cuda_last_error_text()
         assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
         out.struct.is_written = 1
@@ -50,7 +51,8 @@ def test_emulated_ranks_fold_each_others_rows(backend, ranks, items, hd):
             assert np.abs(got[r] - ref).max() <= 1e-5 * (1.0 + np.abs(ref).max())
             assert np.array_equal(got[r], got[0])          # every rank computes the same bits
     counters = areas[0].read()[counter_offset // 4: counter_offset // 4 + items]
-    assert counters.tolist() == [3 * ranks] * items
+    # the tagged form has no arrival counters on its path
+    assert counters.tolist() == ([0] * items if tagged else [3 * ranks] * items)
 
 
 def test_a_missing_rank_runs_into_the_bounded_wait(backend):
@@ -69,6 +71,25 @@ def test_a_missing_rank_runs_into_the_bounded_wait(backend):
     rows = backend.tensor("rows", np.ones((ranks, items, hd + 2), np.float32))
     rc = lib.yvx_cuda_lse_exchange_emulated(rows.data_ptr, ranks, items, hd, gather.data_ptr, arrivals.data_ptr,
                                             2, out.data_ptr, status.data_ptr, backend.stream)
+    assert rc == 0
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0
+    assert int(status.read()[0]) == 3
+
+
+def test_a_rank_that_never_publishes_runs_the_tagged_waits_out(backend):
+    lib = backend.lib
+    ranks, items, hd = 3, 4, 64
+    area_bytes = lib.yvx_cuda_lse_exchange_bytes(ranks, items, hd)
+    counter_offset = lib.yvx_cuda_lse_exchange_counter_offset(ranks, items, hd)
+    areas = [backend.tensor(f"area{r}", np.zeros(area_bytes // 4, np.int32)) for r in range(ranks)]
+    gather = backend.tensor("gather", np.array([a.data_ptr for a in areas], np.int64), dtype=abi.DTYPE_I64)
+    arrivals = backend.tensor("arrivals", np.array([a.data_ptr + counter_offset for a in areas], np.int64),
+                              dtype=abi.DTYPE_I64)
+    status = backend.tensor("status", np.zeros(1, np.int32))
+    out = backend.alloc("out", abi.DTYPE_F32, (ranks, items, hd))
+    rows = backend.tensor("rows", np.ones((ranks, items, hd + 2), np.float32))
+    rc = lib.yvx_cuda_lse_exchange_emulated_form(rows.data_ptr, ranks, items, hd, gather.data_ptr, arrivals.data_ptr,
+                                                 1, out.data_ptr, status.data_ptr, backend.stream, 1, 1)
     assert rc == 0
     assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0
     assert int(status.read()[0]) == 3
