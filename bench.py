@@ -2002,6 +2002,7 @@ def main():
                 ("prefill_f32_contract", "prefill_f32", lambda: bench_prefill_f32(lib, b, w.abi, 3)),
                 ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 10)),
                 ("projections_decode_step", "proj", lambda: bench_projections(lib, b, w.abi, hbm_peak, 20)),
+                ("reference_gpu_kernels", None, lambda: (bench_reference_gpu(lib, b, w.abi), None)),
                 ("kv_append_rotary", None, lambda: bench_kv_append(lib, b, w.abi, hbm_peak, 10)),
                 ("latent_sparse_decode", None, lambda: bench_latent_sparse(lib, b, w.abi, 20)),
                 ("rolling_compressor", None, lambda: bench_compressor(lib, b, w.abi, hbm_peak, 10)),
@@ -2162,6 +2163,10 @@ def summary_of(line, others):
             entry["tc"] = _r(r["frac_of_bf16_peak"], 3)
             entry["step_ms"] = _r(r["absorb_ms"] + r["kernel_ms"] + r["combine_ms"])
         out[tag] = entry
+    ref_gpu = others.get("reference_gpu_kernels")
+    if ref_gpu and "config1_decode_f32" in ref_gpu:
+        out["vs_reference_gpu"] = {k.replace("prefill_f32_2048x16q4kv_", "prefill_"): _r(v["speedup"], 3)
+                                   for k, v in ref_gpu.items() if isinstance(v, dict)}
     proj = others.get("projections_decode_step")
     if proj:
         out["proj"] = {k: {"us": _r((proj[k]["graph_step_ms"] or proj[k]["step_ms"]) * 1e3), "hbm": _r(proj[k]["frac_of_measured_hbm"], 3),

@@ -162,42 +162,74 @@ __device__ __forceinline__ bool exchange_item_tagged(const yvx_lse_exchange &x, 
     const uint2 *base = reinterpret_cast<const uint2 *>(x.gather[rank]) +
                         ((unsigned long long)(x.epoch & 1u) * x.ranks * items + item) * stride;
     const unsigned long long rank_stride = (unsigned long long)items * stride;
-    // thread r fetches rank r's (m, l)
-    for (unsigned int r = tid; r < x.ranks; r += threads) {
+    // The (m, l) words of rank r are polled by thread threads - 1 - r (the high threads, which
+    // have no lane when there are more threads than lanes) into shared memory.
+    bool mine_came = true;
+    for (unsigned int r = threads - 1u - tid; r < x.ranks; r += threads) {
         float m, l;
         const bool came = wait_word_system(base + r * rank_stride + hd, x.epoch, &m, flag) &&
                           wait_word_system(base + r * rank_stride + hd + 1u, x.epoch, &l, flag);
-        if (!came) *flag = 0;
+        if (!came) {
+            *flag = 0;
+            mine_came = false;
+        }
         scales[2u * r] = came ? m : -INFINITY;
         scales[2u * r + 1u] = came ? l : 0.0f;
     }
-    Sync::sync();   // the (m, l) of every rank are in shared memory
-    bool mine_came = true;
-    for (unsigned int d = tid; d < hd; d += threads) {
+    Sync::sync();
+    // A thread polls its lane of up to eight ranks with all loads in flight at once (one trip to
+    // L2 per round, not one per rank); what has not come is polled again.
+    for (unsigned int d = tid; d < hd && *flag; d += threads) {
         float run_max = -INFINITY, run_sum = 0.0f, acc = 0.0f;
-        for (unsigned int r = 0; r < x.ranks; ++r) {
-            float value;
-            mine_came = wait_word_system(base + r * rank_stride + d, x.epoch, &value, flag) && mine_came;
-            const float mr = scales[2u * r], lr = scales[2u * r + 1u];
-            if (mr == -INFINITY) continue;  // empty shard
-            const float new_max = fmaxf(run_max, mr);
-            const float keep = expf(run_max - new_max);
-            const float weight = lr * expf(mr - new_max);
-            run_sum = fmaf(run_sum, keep, weight);
-            acc = fmaf(acc, keep, value * weight);
-            run_max = new_max;
+        for (unsigned int r0 = 0; r0 < x.ranks && mine_came; r0 += 8u) {
+            float value[8];
+            unsigned int missing = 0u;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (r0 + u < x.ranks) missing |= 1u << u;
+            for (unsigned int spin = 0; missing && spin < kExchangeSpinLimit; ++spin) {
+                uint2 word[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (missing >> u & 1u) word[u] = load_word_system(base + (r0 + u) * rank_stride + d);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if ((missing >> u & 1u) && word[u].y == x.epoch) {
+                        value[u] = __uint_as_float(word[u].x);
+                        missing &= ~(1u << u);
+                    }
+                if (missing && spin > 64u) {
+                    __nanosleep(100);
+                    if ((spin & 1023u) == 0u && !*flag) break;
+                }
+            }
+            if (missing) {
+                mine_came = false;
+                *flag = 0;
+                break;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u >= x.ranks) break;
+                const float mr = scales[2u * (r0 + u)], lr = scales[2u * (r0 + u) + 1u];
+                if (mr == -INFINITY) continue;  // empty shard
+                const float new_max = fmaxf(run_max, mr);
+                const float keep = expf(run_max - new_max);
+                const float weight = lr * expf(mr - new_max);
+                run_sum = fmaf(run_sum, keep, weight);
+                acc = fmaf(acc, keep, value[u] * weight);
+                run_max = new_max;
+            }
         }
-        const float value = acc / run_sum;
-        if (mine_came && *flag) {
-            if (!isfinite(value)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
-            store_output(output, output_dtype, output_index + d, value);
+        const float result = acc / run_sum;
+        if (mine_came) {
+            if (!isfinite(result)) atomicCAS(status, 0, YVX_STATUS_NONFINITE);
+            store_output(output, output_dtype, output_index + d, result);
         }
     }
-    if (!mine_came || !*flag) {
-        atomicCAS(status, 0, YVX_STATUS_TIMEOUT);
-        return false;
-    }
-    return true;
+    if (!mine_came) atomicCAS(status, 0, YVX_STATUS_TIMEOUT);
+    Sync::sync();   // the caller reuses `row`; and one thread's verdict becomes the group's
+    return *flag != 0;
 }
 
 // The fold of one item's split partials by `WARPS` warps that meet at Sync::sync(): warp w takes

@@ -24,7 +24,8 @@ struct BlockSync {
     static __device__ __forceinline__ void sync() { __syncthreads(); }
 };
 
-__global__ void __launch_bounds__(kExchangeThreads)
+// four CTAs per SM: the emulation of all ranks on one GPU needs ranks x items of them resident
+__global__ void __launch_bounds__(kExchangeThreads, 4)
 lse_exchange_kernel(const yvx_gqa_problem p, const yvx_lse_exchange x, const unsigned int items,
                     const int emulated)
 {
