@@ -1796,6 +1796,31 @@ def synth_host_sample(sample_ids, lengths, seed):
     return sample
 
 
+def pin_to_gpu_cores(device_index):
+    """Runs this rank's host thread on the CPU cores NVML names as nearest to its GPU (the
+    same NUMA node as the GPU's PCIe root), so that the per-step host copies of the
+    end-to-end leg do not cross the socket interconnect. Reads NVML only; changes nothing
+    on the GPU. A process that cannot ask (no NVML, no permission) keeps its affinity."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        entry = visible.split(",")[device_index].strip() if visible else ""
+        if entry.startswith("GPU-"):
+            handle = pynvml.nvmlDeviceGetHandleByUUID(entry)
+        else:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(int(entry) if entry else device_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cores = {64 * i + bit for i, word in enumerate(words) for bit in range(64) if word >> bit & 1}
+        allowed = cores & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        pynvml.nvmlShutdown()
+        return sorted(allowed)
+    except Exception:
+        return None
+
+
 def run_reference(args, rank):
     from clori_b200 import workloads
     if rank != 0:
@@ -1859,6 +1884,7 @@ def main():
         run_reference(args, rank)
         return
 
+    pin_to_gpu_cores(local_rank)
     dist = None
     if world > 1:
         import torch
