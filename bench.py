@@ -1144,6 +1144,97 @@ def bench_projections(lib, backend, abi, hbm_peak, repeats, tokens=1):
     return result, None
 
 
+def bench_projections_prefill(lib, backend, abi, repeats, tokens=4096):
+    """The same five projections for a prefill chunk of `tokens` tokens on the tensor cores
+    (yvx_cuda_bf16_gemm: tcgen05, BF16 weights, bf16-valued activations, publication fused into the
+    epilogue): 2 * tokens * 106.9 M flop per step. A sample of tokens is compared with the CPU twin."""
+    from oracle.binding import Oracle
+    oracle = Oracle()
+    shapes = (("q_a", 1024, 4096, 1), ("q_b", 32768, 1024, 1), ("kv", 512, 4096, 1), ("out_a", 1024, 4096, 8),
+              ("out_b", 4096, 8192, 1))
+    status = _alloc(lib, 4)
+    lib.yvx_cuda_memset_async(status, 0, 4, backend.stream)
+
+    def event():
+        e = C.c_void_p()
+        assert lib.yvx_cuda_event_create(C.byref(e)) == 0
+        return e
+    first, last, ms = event(), event(), C.c_float()
+    calls, owned, flops = [], [status], 0.0
+    for k, (name, rows, width, groups) in enumerate(shapes):
+        total_rows, lanes = rows * groups, groups * width
+        w, x, y = _alloc(lib, total_rows * width * 2), _alloc(lib, tokens * lanes * 4), _alloc(lib, tokens * total_rows * 4)
+        staging = _alloc(lib, lib.yvx_cuda_bf16_gemm_staging_bytes(tokens, groups, width))
+        owned += [w, x, y, staging]
+        lib.yvx_cuda_fill_normal(w, abi.DTYPE_BF16, total_rows * width, 500 + k, 0.02, backend.stream)
+        lib.yvx_cuda_fill_normal(x, -abi.DTYPE_F32, tokens * lanes, 520 + k, 1.0, backend.stream)
+        a = abi.GemmArgs()
+        a.weights, a.rows, a.width, a.input, a.tokens, a.input_stride = w, rows, width, x, tokens, lanes
+        a.output, a.output_stride, a.groups, a.round_bf16, a.staging, a.status = y, total_rows, groups, 1, staging, status
+        calls.append(a)
+        flops += 2.0 * tokens * total_rows * width
+
+    def step():
+        for a in calls:
+            assert lib.yvx_cuda_bf16_gemm(C.byref(a), backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    for _ in range(2):
+        step()
+    lib.yvx_cuda_event_record(first, backend.stream)
+    for _ in range(repeats):
+        step()
+    lib.yvx_cuda_event_record(last, backend.stream)
+    assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
+    lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+    step_ms = ms.value / repeats
+    alone = {}
+    for (name, rows, width, groups), a in zip(shapes, calls):
+        lib.yvx_cuda_event_record(first, backend.stream)
+        for _ in range(repeats):
+            lib.yvx_cuda_bf16_gemm(C.byref(a), backend.stream)
+        lib.yvx_cuda_event_record(last, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
+        lib.yvx_cuda_event_elapsed_ms(first, last, C.byref(ms))
+        t = ms.value / repeats
+        alone[name] = {"ms": t, "tflops": 2.0 * tokens * rows * groups * width / (t * 1e-3) / 1e12}
+    # sample: 4 tokens x 16 rows of every projection against the CPU twin
+    worst_steps, differing, compared = 0.0, 0, 0
+    for (name, rows, width, groups), a in zip(shapes, calls):
+        lanes, total_rows = groups * width, rows * groups
+        xs = np.zeros((4, lanes), np.float32)
+        ws = np.zeros((16, width * 2), np.uint8)
+        ys = np.zeros((4, total_rows), np.float32)
+        lib.yvx_cuda_download_async(xs.ctypes.data, a.input, xs.nbytes, backend.stream)
+        lib.yvx_cuda_download_async(ws.ctypes.data, a.weights + (groups - 1) * rows * width * 2, ws.nbytes, backend.stream)
+        lib.yvx_cuda_download_async(ys.ctypes.data, a.output, ys.nbytes, backend.stream)
+        lib.yvx_cuda_stream_synchronize(backend.stream)
+        want = oracle.qtype_matvec(ws, abi.QTYPE_BF16, width, np.ascontiguousarray(xs[:, (groups - 1) * width:]), 0, 16, True)
+        got = ys[:, (groups - 1) * rows:(groups - 1) * rows + 16]
+        step_size = np.exp2(np.floor(np.log2(np.maximum(np.maximum(np.abs(want), np.abs(got)), 1e-3))) - 7.0)
+        worst_steps = max(worst_steps, float(np.max(np.abs(got - want) / step_size)))
+        differing += int((got != want).sum())
+        compared += got.size
+    st = np.zeros(1, np.int32)
+    lib.yvx_cuda_download_async(st.ctypes.data, status, 4, backend.stream)
+    lib.yvx_cuda_stream_synchronize(backend.stream)
+    for e in (first, last):
+        lib.yvx_cuda_event_destroy(e)
+    for ptr in owned:
+        lib.yvx_cuda_free(ptr)
+    tf_peak = 1590.0
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        with open(peaks_path) as f:
+            tf_peak = float(json.load(f)["bf16_tflops"])
+    result = {"workload": "projections of one latent layer for a prefill chunk of %d tokens (BF16 weights, 106.9 M; "
+                          "activation staging inside the timed step)" % tokens,
+              "kernel": "bf16_gemm_tcgen05_kernel", "launches_per_step": 10, "step_ms": step_ms, "kernel_ms": step_ms,
+              "flops": flops, "achieved_tflops": flops / (step_ms * 1e-3) / 1e12,
+              "frac_of_bf16_peak": flops / (step_ms * 1e-3) / 1e12 / tf_peak, "per_projection": alone,
+              "status_word": int(st[0]), "sample_values": compared, "sample_values_differing_from_cpu": differing,
+              "sample_worst_difference_in_bf16_steps": worst_steps}
+    return result, None
+
+
 def bench_activation(lib, backend, abi, hbm_peak, repeats, rows=131072):
     """Activation fake quantisation in place: FP8 E4M3 in blocks of 64 over the 448 leading lanes of
     512-lane rows (what the reference applies to new local rows and emitted compressed rows), and the
@@ -1862,7 +1953,7 @@ def main():
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "decode_f32", "verify_q8", "prefill", "mla", "kv_append", "latent_sparse",
                                  "compressor", "activation", "publish", "prefill_f32", "verify_q8_sharded",
-                                 "projections", "reference_gpu"],
+                                 "projections", "reference_gpu", "projections_prefill"],
                         help="run ONE of the other configurations alone and print its numbers "
                              "(for profiler captures; not the bench line)")
     parser.add_argument("--tokens", type=int, default=8192,
@@ -1929,6 +2020,9 @@ def main():
                                   sessions=min(args.sessions, 32))
         elif args.workload == "latent_sparse":
             result, _ = bench_latent_sparse(abi.load(), backend, abi, max(args.steps, 3))
+        elif args.workload == "projections_prefill":
+            result, _ = bench_projections_prefill(abi.load(), backend, abi, max(min(args.steps, 20), 3),
+                                                  tokens=args.tokens if args.tokens != 8192 else 4096)
         elif args.workload == "reference_gpu":
             result = bench_reference_gpu(abi.load(), backend, abi, max(args.steps, 3) if args.steps != 200 else 5)
         elif args.workload == "projections":
@@ -2028,6 +2122,7 @@ def main():
                 ("prefill_f32_contract", "prefill_f32", lambda: bench_prefill_f32(lib, b, w.abi, 3)),
                 ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 10)),
                 ("projections_decode_step", "proj", lambda: bench_projections(lib, b, w.abi, hbm_peak, 20)),
+                ("projections_prefill_4096", None, lambda: bench_projections_prefill(lib, b, w.abi, 5)),
                 ("reference_gpu_kernels", None, lambda: (bench_reference_gpu(lib, b, w.abi), None)),
                 ("kv_append_rotary", None, lambda: bench_kv_append(lib, b, w.abi, hbm_peak, 10)),
                 ("latent_sparse_decode", None, lambda: bench_latent_sparse(lib, b, w.abi, 20)),
@@ -2193,6 +2288,11 @@ def summary_of(line, others):
     if ref_gpu and "config1_decode_f32" in ref_gpu:
         out["vs_reference_gpu"] = {k.replace("prefill_f32_2048x16q4kv_", "prefill_"): _r(v["speedup"], 3)
                                    for k, v in ref_gpu.items() if isinstance(v, dict)}
+    gemm = others.get("projections_prefill_4096")
+    if gemm:
+        out["proj_prefill"] = {"ms": _r(gemm["step_ms"]), "tflops": _r(gemm["achieved_tflops"]),
+                               "tc": _r(gemm["frac_of_bf16_peak"], 3),
+                               "worst_bf16_steps": _r(gemm["sample_worst_difference_in_bf16_steps"], 2)}
     proj = others.get("projections_decode_step")
     if proj:
         out["proj"] = {k: {"us": _r((proj[k]["graph_step_ms"] or proj[k]["step_ms"]) * 1e3), "hbm": _r(proj[k]["frac_of_measured_hbm"], 3),

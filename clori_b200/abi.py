@@ -494,11 +494,18 @@ class MatvecArgs(C.Structure):
                 ("status", C.c_void_p)]
 
 
+class GemmArgs(C.Structure):
+    """yvx_gemm_args (include/yvex_b200/cuda_shim.h)."""
+    _fields_ = [("weights", C.c_void_p), ("first_row", u64), ("rows", u64), ("width", u64), ("input", C.c_void_p),
+                ("tokens", u64), ("input_stride", u64), ("output", C.c_void_p), ("output_stride", u64),
+                ("groups", u64), ("round_bf16", C.c_int), ("staging", C.c_void_p), ("status", C.c_void_p)]
+
+
 # Every symbol the headers declare; tests check the library exports each one.
 EXPORTED_SYMBOLS = [
     # attention_job.h
     "yvex_backend_attention_execute", "yvex_backend_attention_complete", "yvex_backend_query_capability",
-    "yvex_b200_backend_weights_forget", "yvex_b200_kv_bank_layout",
+    "yvex_b200_backend_weights_forget", "yvex_b200_backend_projection_gemm", "yvex_b200_kv_bank_layout",
     "yvex_backend_resident_attach", "yvex_backend_resident_detach", "yvex_backend_resident_resolve",
     "yvex_backend_state_residency_attach", "yvex_backend_state_residency_validate_generation",
     "yvex_backend_state_residency_publish_generation", "yvex_backend_state_residency_detach",
@@ -535,7 +542,8 @@ EXPORTED_SYMBOLS = [
     "yvx_cuda_stream_synchronize", "yvx_cuda_device_synchronize", "yvx_cuda_event_create", "yvx_cuda_event_destroy",
     "yvx_cuda_event_record", "yvx_cuda_stream_wait_event", "yvx_cuda_event_elapsed_ms", "yvx_cuda_last_error_text",
     "yvx_cuda_lse_exchange_bytes", "yvx_cuda_lse_exchange_counter_offset", "yvx_cuda_gqa_attention_exchange",
-    "yvx_cuda_lse_exchange_emulated", "yvx_cuda_lse_exchange_emulated_form", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
+    "yvx_cuda_lse_exchange_emulated", "yvx_cuda_lse_exchange_emulated_form", "yvx_cuda_bf16_gemm",
+    "yvx_cuda_bf16_gemm_staging_bytes", "yvx_cuda_ipc_export", "yvx_cuda_ipc_open", "yvx_cuda_ipc_close",
     "yvx_cuda_graph_capture_begin", "yvx_cuda_graph_capture_end", "yvx_cuda_graph_launch", "yvx_cuda_graph_destroy",
     "yvx_cuda_gqa_partials_bytes", "yvx_cuda_gqa_f32_staging_bytes", "yvx_cuda_gqa_plan_splits", "yvx_cuda_gqa_attention",
     "yvx_cuda_lse_combine", "yvx_cuda_lse_combine_strided", "yvx_cuda_op_attention_f32",
@@ -684,6 +692,9 @@ def load():
     lib.yvx_cuda_lse_exchange_counter_offset.argtypes = [C.c_uint, C.c_uint, C.c_uint]
     lib.yvx_cuda_gqa_attention_exchange.argtypes = [P(GqaProblem), P(LseExchange), vp, P(C.c_uint)]
     lib.yvx_cuda_lse_exchange_emulated.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, vp, C.c_uint, vp, vp, vp]
+    lib.yvx_cuda_bf16_gemm.argtypes = [P(GemmArgs), vp]
+    lib.yvx_cuda_bf16_gemm_staging_bytes.restype = u64
+    lib.yvx_cuda_bf16_gemm_staging_bytes.argtypes = [u64, u64, u64]
     lib.yvx_cuda_lse_exchange_emulated_form.argtypes = [vp, C.c_uint, C.c_uint, C.c_uint, vp, vp, C.c_uint, vp, vp, vp,
                                                         C.c_int, C.c_int]
     lib.yvx_cuda_ipc_export.argtypes = [vp, vp]

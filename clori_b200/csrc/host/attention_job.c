@@ -278,6 +278,22 @@ static int job_upload(job_run *run, void *device, const void *host, unsigned lon
     return YVEX_OK;
 }
 
+/* The five row projections around the attention with BF16 weights; never the rolling state
+ * (bit-exact by contract) nor the index projections (a flipped lane there can change which
+ * rows are selected). */
+static int job_gemm_admits(const job_run *run, unsigned int slot, const yvex_backend_attention_weight *w,
+                           unsigned long long width, const float *input, unsigned long long input_stride,
+                           int round_bf16)
+{
+    const yvex_backend *b = run->backend;
+    const int row_projection = slot == YVEX_BACKEND_ATTENTION_WEIGHT_Q_A || slot == YVEX_BACKEND_ATTENTION_WEIGHT_Q_B ||
+                               slot == YVEX_BACKEND_ATTENTION_WEIGHT_KV || slot == YVEX_BACKEND_ATTENTION_WEIGHT_OUT_A ||
+                               slot == YVEX_BACKEND_ATTENTION_WEIGHT_OUT_B;
+    return row_projection && round_bf16 && b->projection_gemm_tokens && run->tokens >= b->projection_gemm_tokens &&
+           w->qtype == YVX_QTYPE_BF16 && width % 8ull == 0ull && input_stride % 2ull == 0ull &&
+           ((uintptr_t)input & 7u) == 0u;
+}
+
 static int job_matvec(job_run *run, unsigned int slot, unsigned long long rows, unsigned long long width,
                       unsigned long long groups, const float *input, unsigned long long input_stride,
                       float *output, unsigned long long output_stride, int round_bf16)
@@ -287,6 +303,40 @@ static int job_matvec(job_run *run, unsigned int slot, unsigned long long rows, 
     const void *device = NULL;
     int rc = job_weight_resident(run, slot, &device);
     if (rc != YVEX_OK) return rc;
+    if (job_gemm_admits(run, slot, w, width, input, input_stride, round_bf16)) {
+        /* prefill-sized token counts: the tensor-core projection (published values within one
+         * bf16 step of the exact sum; opted into with yvex_b200_backend_projection_gemm) */
+        yvex_backend *b = run->backend;
+        yvx_gemm_args g;
+        const unsigned long long need = yvx_cuda_bf16_gemm_staging_bytes(run->tokens, groups, width);
+        if (need > b->gemm_staging_bytes) {
+            rc = yvx_cuda_device_synchronize();
+            if (rc == 0) rc = yvx_cuda_free(b->gemm_staging);
+            b->gemm_staging = NULL;
+            b->gemm_staging_bytes = 0ull;
+            if (rc == 0) rc = yvx_cuda_malloc(&b->gemm_staging, need + need / 4ull);
+            if (rc != 0) return job_device_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_ALLOCATION, weight_stage[slot], rc);
+            b->gemm_staging_bytes = need + need / 4ull;
+        }
+        memset(&g, 0, sizeof(g));
+        g.weights = device;
+        g.rows = rows;
+        g.width = width;
+        g.input = input;
+        g.tokens = run->tokens;
+        g.input_stride = input_stride;
+        g.output = output;
+        g.output_stride = output_stride;
+        g.groups = groups;
+        g.round_bf16 = round_bf16;
+        g.staging = b->gemm_staging;
+        g.status = b->status_device;
+        rc = yvx_cuda_bf16_gemm(&g, b->stream);
+        if (rc != 0) return job_device_fail(run, YVEX_BACKEND_ATTENTION_FAILURE_LAUNCH, weight_stage[slot], rc);
+        run->launches += 2u;
+        run->work_pending = 1;
+        return YVEX_OK;
+    }
     memset(&a, 0, sizeof(a));
     a.weights = device;
     a.qtype = w->qtype;
@@ -1269,6 +1319,15 @@ int yvex_b200_backend_weights_forget(yvex_backend *backend, yvex_error *err)
     if (rc != 0) return yvx_backend_device_fail(backend, rc, "b200.weights.forget", err);
     for (i = 0; i < backend->weight_count; ++i) (void)yvx_cuda_free(backend->weights[i].device);
     backend->weight_count = 0u;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_b200_backend_projection_gemm(yvex_backend *backend, unsigned long long min_tokens, yvex_error *err)
+{
+    int rc = yvx_backend_admit(backend, "b200.projection.gemm", err);
+    if (rc != YVEX_OK) return rc;
+    backend->projection_gemm_tokens = min_tokens;
     yvex_error_clear(err);
     return YVEX_OK;
 }

@@ -106,6 +106,7 @@ int yvex_backend_close_checked(yvex_backend **handle, yvex_error *err)
     yvx_cuda_device_select(backend->device);
     yvx_cuda_stream_synchronize(backend->stream);
     yvx_cuda_free(backend->scratch);
+    yvx_cuda_free(backend->gemm_staging);
     {
         unsigned int i;
         for (i = 0; i < backend->weight_count; ++i) yvx_cuda_free(backend->weights[i].device);

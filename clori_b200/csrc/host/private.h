@@ -49,6 +49,12 @@ struct yvex_backend {
     int (*state_residency_resolve)(const void *context, const void *host, unsigned long long bytes,
                                    unsigned long long *device_address);
     unsigned long long state_residency_generation;
+    /* Row projections of the attention job go through the tensor-core GEMM from this many
+     * tokens on (0: never; yvex_b200_backend_projection_gemm). Its bf16 activation staging
+     * is a grow-only buffer of its own. */
+    unsigned long long projection_gemm_tokens;
+    void *gemm_staging;
+    unsigned long long gemm_staging_bytes;
 };
 
 static inline int yvx_u64_add(unsigned long long a, unsigned long long b,

@@ -256,6 +256,11 @@ int yvex_backend_state_residency_resolve(const yvex_backend *backend, const void
  * found again by host address, size and a sampled content fingerprint; a caller that
  * rewrites weights in place, or unloads a model, drops them with this call. */
 int yvex_b200_backend_weights_forget(yvex_backend *backend, yvex_error *err);
+/* Jobs of at least `min_tokens` tokens run their published row projections (q_a, q_b, kv,
+ * out_a, out_b) with BF16 weights on the tensor cores (yvx_cuda_bf16_gemm): a published value
+ * is then within one bf16 step of the exact sum instead of equal to it. 0 (the default): never.
+ * No reference counterpart (its CUDA projections are one matvec launch per token tile). */
+int yvex_b200_backend_projection_gemm(yvex_backend *backend, unsigned long long min_tokens, yvex_error *err);
 
 /* ---- capability query ----------------------------------------------------------- */
 typedef enum {

@@ -509,6 +509,28 @@ typedef struct yvx_matvec_args {
 } yvx_matvec_args;
 unsigned long long yvx_cuda_qtype_row_bytes(unsigned int qtype, unsigned long long width);
 int yvx_cuda_qtype_matvec(const yvx_matvec_args *args, void *stream);
+/* The same projection at prefill-sized token counts on the tensor cores (tcgen05, F32
+ * accumulation in tensor memory): BF16-encoded weight rows, activation rows that bf16 holds
+ * exactly (anything else raises status 2 and the output is not to be used), the bf16
+ * publication fused into the epilogue (round_bf16). A published value differs from
+ * yvx_cuda_qtype_matvec's (the CPU twin's exact sum) by at most one bf16 step. Groups as
+ * above. `staging` holds the activations as bf16: yvx_cuda_bf16_gemm_staging_bytes(). Two
+ * launches. width a multiple of 8, input 8-byte aligned with an even stride. */
+typedef struct yvx_gemm_args {
+    const void *weights;                      /* BF16 rows, 2 * width bytes apart, 16-byte aligned */
+    unsigned long long first_row, rows, width;
+    const float *input;                       /* [tokens][input_stride] */
+    unsigned long long tokens, input_stride;
+    float *output;                            /* [tokens][output_stride] */
+    unsigned long long output_stride;
+    unsigned long long groups;
+    int round_bf16;
+    void *staging;
+    int *status;
+} yvx_gemm_args;
+unsigned long long yvx_cuda_bf16_gemm_staging_bytes(unsigned long long tokens, unsigned long long groups,
+                                                    unsigned long long width);
+int yvx_cuda_bf16_gemm(const yvx_gemm_args *args, void *stream);
 /* Encoded rows [first_row, first_row + rows) decoded to F32 [rows][width] (norm weights,
  * sinks, position biases: yvex_attention_decode_row, src/graph/core.c:1029-1105). */
 int yvx_cuda_qtype_decode_rows(const void *weights, unsigned int qtype, unsigned long long first_row,

@@ -51,6 +51,11 @@ unsigned long long yvx_cuda_qtype_row_bytes(unsigned int q, unsigned long long w
            : (q == YVX_QTYPE_Q8_0 && w % 32ull == 0ull) ? w / 32ull * 34ull : 0ull;
 }
 REFUSE(yvx_cuda_qtype_matvec, const yvx_matvec_args *a, void *s)
+REFUSE(yvx_cuda_bf16_gemm, const yvx_gemm_args *a, void *s)
+unsigned long long yvx_cuda_bf16_gemm_staging_bytes(unsigned long long t, unsigned long long g, unsigned long long w)
+{
+    return t * (g ? g : 1ull) * w * 2ull;
+}
 REFUSE(yvx_cuda_qtype_decode_rows, const void *w, unsigned int q, unsigned long long f, unsigned long long r, unsigned long long wd, float *o, int *st, void *s)
 REFUSE(yvx_cuda_round_bf16_rows, float *v, unsigned long long r, unsigned long long w, unsigned long long st, int *status, void *s)
 unsigned long long yvx_cuda_q8_record_bytes(void) { return 17408ull; }

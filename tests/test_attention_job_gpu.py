@@ -327,3 +327,29 @@ def test_projection_kernel_keeps_subnormal_weights_and_reports_infinite_ones(bac
     assert backend.lib.yvx_cuda_qtype_matvec(C.byref(a), backend.stream) == 0
     assert backend.lib.yvx_cuda_stream_synchronize(backend.stream) == 0
     assert int(status.read()[0]) == 1
+
+
+def test_job_with_tensor_core_projections_stays_within_a_bf16_step(backend, oracle, library):
+    """Opted in, jobs of enough tokens run q_a, q_b, kv, out_a and out_b (BF16 weights) through the tcgen05 GEMM:
+    published rows may move by one bf16 step against the exact projections, the state stays bit-equal."""
+    cls, tokens, start = abi.ATTENTION_CSA, 9, 0
+    qtypes = {slot: abi.QTYPE_BF16 for slot in (abi.WEIGHT_Q_A, abi.WEIGHT_Q_B, abi.WEIGHT_KV, abi.WEIGHT_OUT_A,
+                                                abi.WEIGHT_OUT_B)}
+    job = job_cases.build(oracle, cls, tokens, start, seed=333, qtypes=qtypes)
+    rc, out0, exact, failure, err = job_cases.run(backend, job)
+    assert rc == 0, (err.where, err.message, failure.stage)
+    error = abi.Error()
+    library.yvex_b200_backend_projection_gemm.argtypes = [C.c_void_p, C.c_ulonglong, C.POINTER(abi.Error)]
+    assert library.yvex_b200_backend_projection_gemm(backend.handle, 4, C.byref(error)) == 0
+    rc, out1, got, failure, err = job_cases.run(backend, job)
+    assert library.yvex_b200_backend_projection_gemm(backend.handle, 0, C.byref(error)) == 0
+    assert rc == 0, (err.where, err.message, failure.stage)
+    assert out1.kernel_launches > out0.kernel_launches          # a staging launch per GEMM
+    for name in ("q_low", "query", "raw_kv"):
+        differ, beyond = ulp_lanes(got[name], exact[name])
+        assert beyond == 0 and differ <= max(2, got[name].size // 50), (name, differ, beyond)
+    for name in ("main_kv_state", "main_score_state", "indexer_kv_state", "indexer_score_state"):
+        if name in got:
+            assert np.array_equal(got[name].view(np.uint32), exact[name].view(np.uint32)), name
+    scale = np.abs(exact["output"]).max(axis=-1, keepdims=True)
+    assert np.all(np.abs(got["output"] - exact["output"]) <= 2.0 ** -6 * scale + 5e-4)
