@@ -21,6 +21,8 @@
 // part two, so the softmax of tile j and the tile loads hide under the MMAs.
 // Tensor memory map: O [0,256) | S0 [256,320) S1 [320,384), P(j) aliases the
 // first 32 columns of S(j % 2) | Q [384,512).
+#include <cstdlib>
+
 #include "tcgen05.cuh"
 
 namespace yvx {
@@ -559,6 +561,601 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
     if (warp == 5) tmem_dealloc(tmem, kMlaTmemColumns);
 }
 
+// ---- attention, paired form: a cluster of two CTAs computes every score tile ONCE ------------
+// The two CTAs of a (session, split) still own one latent half of the output each, but they take
+// turns at the score product: CTA r computes S = Q K^T and the softmax of the tiles j with j % 2 == r
+// and hands the weights P(j) (bf16, the operand layout of the P V product) to its peer through
+// distributed shared memory, with the running row maximum it used. Both run P(j) V(j) of EVERY tile
+// on their own 256 accumulator columns, A = P from shared memory. Per pair of tiles a CTA issues
+// one score product and two P V products instead of two and two.
+//
+// Shared memory (one CTA per SM): query dims that do not fit tensor memory (3 sub-tiles, 48 KB);
+// for the tiles this CTA scores the scores-only part (other latent half + rope, 40 KB, one buffer)
+// and the own-half part (32 KB: K of the last k-steps and V of P V, two buffers); for the peer's
+// tiles the own-half part alone (V, 32 KB); P of an own tile and P of a peer tile (16 KB each).
+// Tensor memory: O 256 | S 64 | Q 192 (384 query dims: the own half and 128 dims of the other).
+//
+// The row maximum is one sequence for both CTAs (their accumulators must carry the same scale):
+// a CTA processes the peer's message for tile j - 1 (adopting its maximum, rescaling O and l if
+// it grew) before it computes the weights of tile j. Every wait is bounded and gives up at once
+// when either CTA has recorded a failure; both CTAs always reach the cluster barrier at the end.
+constexpr int kPairThreads = 384;   // 8 softmax warps, the MMA warp (5), three TMA warps (4, 10, 11)
+constexpr int kPairQSmemSubs = 3, kPairQTmemCols = 192;
+constexpr int kPairOffQ = 0;
+constexpr int kPairOffKa = kPairQSmemSubs * kMlaQSubBytes;            // 49152
+constexpr int kPairKaBytes = 5 * kMlaKvSubBytes;                       // 40960
+constexpr int kPairOffKb = kPairOffKa + kPairKaBytes;                  // 90112
+constexpr int kPairOffVp = kPairOffKb + 2 * kMlaVPartBytes;            // 155648
+constexpr int kPairOffPOwn = kPairOffVp + kMlaVPartBytes;              // 188416
+constexpr int kPairPBytes = kMlaHeads * kMlaN * 2;                     // 16384
+constexpr int kPairOffPPeer = kPairOffPOwn + kPairPBytes;              // 204800
+constexpr int kPairOffTail = kPairOffPPeer + kPairPBytes;              // 221184
+constexpr int kPairSmemBytes = kPairOffTail + 256 + 4 * 1024 + 1024;   // barriers, 4 float boxes, alignment
+
+struct PairBarriers {
+    uint64_t q_full, q_tmem_full;
+    uint64_t ka_full, ka_done;            // scores-only part of an own tile: loaded / free again
+    uint64_t kb_full[2], kb_done[2];      // own-half part of an own tile
+    uint64_t vp_full, pvp_done;           // own-half part of a peer tile: loaded / its P V has run
+    uint64_t s_full, s_free;              // scores computed / read out of tensor memory
+    uint64_t p_own_full, pv_own_done;     // weights of an own tile written / consumed
+    uint64_t p_peer_full, peer_ready;     // the peer's weights have arrived / its message is processed
+    uint64_t p_peer_free;                 // the peer has consumed the weights this CTA sent it
+    uint64_t pv_done;                     // any P V
+    uint64_t halves[4], rows_staged;      // the two softmax warps of a quadrant meet; all rows are staged
+    uint32_t tmem_base;
+    int abort;
+    unsigned int written;                 // softmax warps that have written their part of an own tile's weights
+};
+static_assert(sizeof(PairBarriers) <= 256, "barrier block outgrew its shared-memory slot");
+
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_address, uint32_t rank)
+{
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void cluster_store_v4(uint32_t address, uint4 v)
+{
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void cluster_store_f32(uint32_t address, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(address), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_store_b32(uint32_t address, uint32_t v)
+{
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(address), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive_remote(uint32_t barrier_address)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(barrier_address) : "memory");
+}
+// Bulk copy from this CTA's shared memory into the peer's, completion counted in bytes on a barrier of the peer.
+__device__ __forceinline__ void cluster_bulk_copy(uint32_t peer_destination, const void *source, uint32_t bytes,
+                                                  uint32_t peer_barrier)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(peer_destination), "r"(smem_u32(source)), "r"(bytes), "r"(peer_barrier)
+        : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Bounded wait that also ends when either CTA has given up; acquire at cluster scope (a peer's
+// arrival publishes its stores into this CTA's shared memory).
+__device__ __forceinline__ bool pair_wait(uint64_t *bar, uint32_t parity, const volatile int *abort)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 255u) == 255u && *abort) return false;
+    }
+    return false;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps maps)
+{
+    extern __shared__ unsigned char pair_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(pair_smem_raw) + 1023u) & ~uintptr_t(1023));
+    PairBarriers *bars = reinterpret_cast<PairBarriers *>(smem + kPairOffTail);
+    float *exchange = reinterpret_cast<float *>(smem + kPairOffTail + 256);   // [2 sides][128]: the halves' row maxima
+    float *m_box = exchange + 2 * kMlaHeads;                                  // [128]: the peer's maximum after its tile
+    float *l_box = m_box + 2 * kMlaHeads;                                     // [2 sides][128]: the peer's denominators
+    float *m_out = l_box + 2 * kMlaHeads;                                     // [128]: this CTA's maximum, source of the copy to the peer
+
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned int half = blockIdx.x, split = blockIdx.y, b = blockIdx.z;   // half == rank in the cluster
+    const unsigned int peer = half ^ 1u;
+#ifdef YVX_MLA_TRACE
+    const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+    unsigned long long trace_local[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long trace_start = clock64();
+#endif
+    const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
+    const unsigned int t0 = split * p.chunk_tokens;
+    const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
+    const unsigned long long part_stride = kMlaHalf + 2;
+    if (t0 >= t1) {
+        // Nothing of this session falls into the split (true for both CTAs of the pair): an empty partial.
+        if (threadIdx.x < (unsigned)kMlaHeads) {
+            float *part = p.partials +
+                          ((((unsigned long long)b * kMlaHeads + threadIdx.x) * 2ull + half) * p.max_splits + split) *
+                              part_stride;
+            for (int d = 0; d < kMlaHalf; ++d) part[d] = 0.0f;
+            part[kMlaHalf] = -INFINITY;
+            part[kMlaHalf + 1] = 0.0f;
+        }
+        return;
+    }
+    const unsigned int tiles = (t1 - t0 + kMlaN - 1) / kMlaN;
+    const unsigned int own_tiles = (tiles + 1u - half) / 2u;     // tiles j with j % 2 == half
+    const unsigned int peer_tiles = tiles - own_tiles;
+    const int own0 = 4 * (int)half, other0 = 4 * (1 - (int)half);
+    volatile int *abort = &bars->abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_full, 1);
+        mbar_init(&bars->q_tmem_full, kMlaHeads);
+        mbar_init(&bars->ka_full, 1);
+        mbar_init(&bars->ka_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->kb_full[i], 1);
+            mbar_init(&bars->kb_done[i], 1);
+        }
+        mbar_init(&bars->vp_full, 1);
+        mbar_init(&bars->pvp_done, 1);
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->s_free, 2 * kMlaHeads);
+        mbar_init(&bars->p_own_full, 8);
+        mbar_init(&bars->pv_own_done, 1);
+        mbar_init(&bars->p_peer_full, 1);
+        mbar_init(&bars->peer_ready, 8);
+        mbar_init(&bars->p_peer_free, 1);
+        mbar_init(&bars->pv_done, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&bars->halves[i], 64);
+        mbar_init(&bars->rows_staged, 2 * kMlaHeads);
+        bars->abort = 0;
+        bars->written = 0u;
+        fence_barrier_init();
+        // the first message of the peer: its weights and its maxima, counted in bytes
+        if (peer_tiles) mbar_expect_tx(&bars->p_peer_full, kPairPBytes + kMlaHeads * 4);
+    }
+    if (warp == 5) {
+        tmem_alloc(&bars->tmem_base, kMlaTmemColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers exist before anything arrives on them
+    tc_fence_after_sync();
+    const uint32_t tmem = bars->tmem_base;
+    const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf, tmem_q = tmem + kMlaHalf + kMlaN;
+    const uint32_t peer_abort = cluster_map(smem_u32(&bars->abort), peer);
+    auto give_up = [&]() {   // records the failure here and at the peer, whose waits then end too
+        atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+        bars->abort = 1;
+        cluster_store_b32(peer_abort, 1u);
+    };
+
+    if (warp == 4 || warp >= 10u) {
+        // ------------------------------ TMA producers: one warp per kind of part (a lane that spins on
+        // a barrier beside other spinning lanes of its warp reacts late) ------------------------------
+        if (warp == 4 && lane == 0) {
+            mbar_expect_tx(&bars->q_full, kPairQSmemSubs * kMlaQSubBytes);
+            tma_load_3d(smem + kPairOffQ, &maps.query, &bars->q_full, 64 * (other0 + 2), 0, (int)b);
+            tma_load_3d(smem + kPairOffQ + kMlaQSubBytes, &maps.query, &bars->q_full, 64 * (other0 + 3), 0, (int)b);
+            tma_load_3d(smem + kPairOffQ + 2 * kMlaQSubBytes, &maps.query, &bars->q_full, kMlaLatent, 0, (int)b);
+            for (unsigned int i = 0; i < own_tiles; ++i) {
+                const int token = (int)(t0 + (2u * i + half) * kMlaN);
+                if (i > 0 && !pair_wait(&bars->ka_done, (i - 1u) & 1u, abort)) {
+                    give_up();
+                    break;
+                }
+                unsigned char *dst = smem + kPairOffKa;
+                mbar_expect_tx(&bars->ka_full, kPairKaBytes);
+                for (int u = 0; u < 4; ++u)
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka_full, 64 * (other0 + u), token, (int)b);
+                tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka_full, 0, token, (int)b);
+            }
+        } else if (warp == 10 && lane == 0) {
+            for (unsigned int i = 0; i < own_tiles; ++i) {
+                const unsigned int buffer = i & 1u;
+                const int token = (int)(t0 + (2u * i + half) * kMlaN);
+                if (i >= 2u && !pair_wait(&bars->kb_done[buffer], ((i >> 1) - 1u) & 1u, abort)) {
+                    give_up();
+                    break;
+                }
+                unsigned char *dst = smem + kPairOffKb + buffer * kMlaVPartBytes;
+                mbar_expect_tx(&bars->kb_full[buffer], kMlaVPartBytes);
+                for (int u = 0; u < 4; ++u)
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full[buffer], 64 * (own0 + u), token, (int)b);
+            }
+        } else if (warp == 11 && lane == 0) {
+            for (unsigned int i = 0; i < peer_tiles; ++i) {
+                const int token = (int)(t0 + (2u * i + peer) * kMlaN);
+                if (i > 0 && !pair_wait(&bars->pvp_done, (i - 1u) & 1u, abort)) {
+                    give_up();
+                    break;
+                }
+                unsigned char *dst = smem + kPairOffVp;
+                mbar_expect_tx(&bars->vp_full, kMlaVPartBytes);
+                for (int u = 0; u < 4; ++u)
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->vp_full, 64 * (own0 + u), token, (int)b);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
+        constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
+        constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
+        const uint32_t elected = tc_elect_one() ? 1u : 0u;
+        const uint32_t peer_credit = cluster_map(smem_u32(&bars->p_peer_free), peer);
+        const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffQ), 16);
+        const uint32_t ka_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKa), 16);
+        auto ready = [&](uint64_t *bar, uint32_t parity) {     // warp-uniform look at a barrier
+            return __any_sync(0xffffffffu, mbar_test(bar, parity)) != 0;
+        };
+        bool ok = __all_sync(0xffffffffu, pair_wait(&bars->q_full, 0, abort)) &&
+                  __all_sync(0xffffffffu, pair_wait(&bars->q_tmem_full, 0, abort));
+        unsigned int next_pv = 0, next_own = 0;    // tile index of the next P V; index (among own tiles) of the next score product
+        int score_stage = 0;                       // 0: first part pending, 1: second part pending
+        uint32_t idle = 0;
+        while (ok && next_pv < tiles) {
+            bool issued = false;
+            // P V of the oldest tile whose weights (and V) are there
+            {
+                const unsigned int j = next_pv, i = j >> 1;
+                const bool own = (j & 1u) == half;
+                const bool there = own ? ready(&bars->p_own_full, i & 1u)
+                                       : (ready(&bars->peer_ready, i & 1u) && ready(&bars->vp_full, i & 1u));
+                if (there) {
+                    tc_fence_after_sync();
+                    const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
+                    const uint32_t v_lo = smem_desc_sw128_lo(
+                        smem_u32(smem + (own ? kPairOffKb + (i & 1u) * kMlaVPartBytes : kPairOffVp)), kMlaKvSubBytes);
+#pragma unroll
+                    for (int kk = 0; kk < kMlaN / 16; ++kk)
+                        tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
+                                       (j || kk) ? 1u : 0u);
+                    if (own) {
+                        tc_commit_pred(elected, &bars->kb_done[i & 1u]);
+                        tc_commit_pred(elected, &bars->pv_own_done);
+                    } else {
+                        tc_commit_pred(elected, &bars->pvp_done);
+                        // ... and tells the peer at once that the weights it sent are consumed
+                        asm volatile(
+                            "{\n\t.reg .pred pe;\n\t"
+                            "setp.ne.b32 pe, %0, 0;\n\t"
+                            "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+                            ::"r"(elected), "r"(peer_credit)
+                            : "memory");
+                    }
+                    tc_commit_pred(elected, &bars->pv_done);
+                    ++next_pv;
+                    issued = true;
+                }
+            }
+            // the score product of this CTA's next tile, in two parts
+            if (!issued && next_own < own_tiles) {
+                const unsigned int i = next_own;
+                if (score_stage == 0) {
+                    // the score buffer is free once the softmax has read the previous own tile out of it
+                    if (ready(&bars->ka_full, i & 1u) && (i == 0u || ready(&bars->s_free, (i - 1u) & 1u))) {
+                        tc_fence_after_sync();
+                        // 8 k-steps against query dims in tensor memory (first two sub-tiles of the other half) ...
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks)
+                            tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
+                                           ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk,
+                                           ks ? 1u : 0u);
+                        // ... 12 against query dims in shared memory (its last two sub-tiles, then the rope dims)
+#pragma unroll
+                        for (int ks = 0; ks < 12; ++ks)
+                            tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
+                                           ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk,
+                                           1u);
+                        tc_commit_pred(elected, &bars->ka_done);
+                        score_stage = 1;
+                        issued = true;
+                    }
+                } else if (ready(&bars->kb_full[i & 1u], (i >> 1) & 1u)) {
+                    tc_fence_after_sync();
+                    const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
+#pragma unroll
+                    for (int ks = 0; ks < 16; ++ks)
+                        tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
+                                       kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+                    tc_commit_pred(elected, &bars->s_full);
+                    score_stage = 0;
+                    ++next_own;
+                    issued = true;
+                }
+            }
+#ifdef YVX_MLA_TRACE
+            if (!issued) trace_local[0] += 1ull;
+#endif
+            if (issued) {
+                idle = 0;
+            } else if (++idle > kWaitSpinLimit || ((idle & 255u) == 255u && *abort)) {
+                ok = false;
+            }
+        }
+        if (!ok && lane == 0) give_up();
+#ifdef YVX_MLA_TRACE
+        if (traced) {
+            yvx_mla_trace[8] = trace_local[0];
+            yvx_mla_trace[9] = (unsigned long long)(clock64() - trace_start);
+        }
+#endif
+    } else {
+        // ------------------------------ softmax warps (0-3: first 32 tokens, 6-9: last 32) ------------------------------
+        const unsigned int side = warp < 4u ? 0u : 1u, quadrant = warp & 3u;
+        const unsigned int head = quadrant * 32u + lane;
+        const uint32_t lane_base = ((quadrant * 32u) << 16);
+        if (side == 0u) {
+            // 384 query dims of this head into tensor memory: the own latent half, then 128 dims of the other
+            const unsigned short *row = reinterpret_cast<const unsigned short *>(p.q_absorbed) +
+                                        ((unsigned long long)b * kMlaHeads + head) * kMlaWidth;
+#pragma unroll 1
+            for (int i = 0; i < kPairQTmemCols / 32; ++i) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(
+                    row + (i < 4 ? (unsigned)half * kMlaHalf + 64u * i : (unsigned)(1u - half) * kMlaHalf + 64u * (i - 4)));
+                uint4 v[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = src[c];
+                uint32_t words[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    words[4 * c] = v[c].x;
+                    words[4 * c + 1] = v[c].y;
+                    words[4 * c + 2] = v[c].z;
+                    words[4 * c + 3] = v[c].w;
+                }
+                tmem_st32(tmem_q + lane_base + 32 * i, words);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bars->q_tmem_full);
+        }
+        const float sscale = p.scale * 1.4426950408889634f;
+        float m_used = -INFINITY, l = 0.0f;
+        bool ok = true;
+        // the two warps of a quadrant meet on a barrier whose wait is bounded like every other
+        unsigned int meetings = 0;
+        auto meet = [&]() -> bool {
+            mbar_arrive(&bars->halves[quadrant]);
+            return pair_wait(&bars->halves[quadrant], meetings++ & 1u, abort);
+        };
+        const uint32_t peer_p = cluster_map(smem_u32(smem + kPairOffPPeer), peer);
+        const uint32_t peer_m = cluster_map(smem_u32(m_box), peer);
+        const uint32_t peer_full = cluster_map(smem_u32(&bars->p_peer_full), peer);
+        // O columns of this thread's side are rescaled when the row maximum grows
+        auto rescale = [&](float factor) {
+#pragma unroll 1
+            for (int i = 0; i < kMlaHalf / 64; ++i) {
+                uint32_t o[32];
+                const uint32_t column = tmem_o + lane_base + 128u * side + 32u * i;
+                tmem_ld32(column, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                tmem_st32(column, o);
+            }
+            tmem_wait_st();
+        };
+        // m_used: the maximum this CTA's weights are scaled with (and its l); m_o: the scale the
+        // accumulator carries, a function of the tiles' scales in tile order and so the same in both CTAs
+        float m_o = -INFINITY;
+        // Lets the tensor pipe run P(j) V(j): first brings the accumulator to the scale the weights of
+        // tile j were computed with (up or down; rare), in tile order, after every earlier P V has landed.
+        auto release = [&](unsigned int j, float m_p, uint64_t *go) -> bool {
+            const bool differs = m_p != m_o && m_p != -INFINITY;
+            if (__any_sync(0xffffffffu, differs)) {
+                if (j > 0) {
+                    if (!pair_wait(&bars->pv_done, (j - 1u) & 1u, abort)) return false;
+                    tc_fence_after_sync();
+                    rescale(differs && m_o != -INFINITY ? exp2_approx(m_o - m_p) : 1.0f);
+                    tc_fence_before_sync();
+                }
+                if (differs) m_o = m_p;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(go);
+            return true;
+        };
+        // The peer's message for its tile j: its weights are in place, its maxima in m_box.
+        auto receive = [&](unsigned int j) -> bool {
+            const unsigned int ip = j >> 1;
+            MLA_TRACE_BEGIN(w4);
+            if (!pair_wait(&bars->p_peer_full, ip & 1u, abort)) return false;
+            MLA_TRACE_ADD(4, w4);
+            MLA_TRACE_BEGIN(w5);
+            if (warp == 0 && lane == 0 && ip + 1u < peer_tiles)   // the next message may be counted from now on
+                mbar_expect_tx(&bars->p_peer_full, kPairPBytes + kMlaHeads * 4);
+            const float m_in = m_box[head];
+            // adopt a larger maximum, so that the two CTAs' references stay together
+            if (m_in > m_used) {
+                l *= m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_in);
+                m_used = m_in;
+            }
+            const bool fine = release(j, m_in, &bars->peer_ready);
+            MLA_TRACE_ADD(5, w5);
+            return fine;
+        };
+        for (unsigned int i = 0; i < own_tiles && ok; ++i) {
+            const unsigned int j = 2u * i + half;
+            {
+                // ---- the weights of a tile this CTA scores; nothing here waits for the peer's softmax ----
+                MLA_TRACE_BEGIN(w0);
+                if (!pair_wait(&bars->s_full, i & 1u, abort)) {
+                    ok = false;
+                    break;
+                }
+                MLA_TRACE_ADD(0, w0);
+                MLA_TRACE_BEGIN(w1);
+                tc_fence_after_sync();
+                uint32_t s[32];
+                tmem_ld32(tmem_s + lane_base + 32u * side, s);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(&bars->s_free);
+                const unsigned int k0 = t0 + j * kMlaN + 32u * side;
+                if (k0 + 32u > t1) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (k0 + c >= t1) s[c] = 0xff800000u;  // -inf
+                }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+                if (i > 0 && !meet()) {   // the partner has read the previous maximum
+                    ok = false;
+                    break;
+                }
+                exchange[side * kMlaHeads + head] = max3(mx[0], mx[1], fmaxf(mx[2], mx[3]));
+                if (!meet()) {
+                    ok = false;
+                    break;
+                }
+                const float row_max = fmaxf(exchange[head], exchange[kMlaHeads + head]);
+                const float m_tile = row_max * sscale;
+                if (m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY) {
+                    const float m_new = fmaxf(m_used, m_tile);
+                    l *= m_new == -INFINITY || m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
+                    m_used = m_new;
+                }
+                const float offset = m_used == -INFINITY ? 0.0f : -m_used;
+                uint32_t packed[16];
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = exp2_approx(fmaf(__uint_as_float(s[c]), sscale, offset));
+                    const float p1 = exp2_approx(fmaf(__uint_as_float(s[c + 1]), sscale, offset));
+                    sum0 += p0;
+                    sum1 += p1;
+                    packed[c >> 1] = pack_bf16(p0, p1);
+                }
+                l += sum0 + sum1;
+                MLA_TRACE_ADD(1, w1);
+                MLA_TRACE_BEGIN(w2);
+                // both copies of the previous own tile's weights have been consumed
+                if (i > 0 && !(pair_wait(&bars->pv_own_done, (i - 1u) & 1u, abort) &&
+                               pair_wait(&bars->p_peer_free, (i - 1u) & 1u, abort))) {
+                    ok = false;
+                    break;
+                }
+                MLA_TRACE_ADD(2, w2);
+                MLA_TRACE_BEGIN(w3);
+                // row `head`, 16-byte chunks 4 * side .. 4 * side + 3 of its 128 bytes, under the 128-byte swizzle
+                {
+                    unsigned char *mine = smem + kPairOffPOwn + head * 128u;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4 *>(mine + ((4u * side + c) ^ (head & 7u)) * 16u) =
+                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                    if (side == 0u) m_out[head] = m_used;
+                }
+                fence_proxy_async();   // the tensor pipe and the bulk copy read these bytes through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    // the last of the eight warps sends the tile (and the maxima it was scaled with) to the peer:
+                    // two bulk copies between the shared memories, counted in bytes on the peer's barrier
+                    __threadfence_block();
+                    if ((atomicAdd(&bars->written, 1u) & 7u) == 7u) {
+                        __threadfence_block();
+                        fence_proxy_async();
+                        cluster_bulk_copy(peer_p, smem + kPairOffPOwn, kPairPBytes, peer_full);
+                        cluster_bulk_copy(peer_m, m_out, kMlaHeads * 4, peer_full);
+                    }
+                }
+                MLA_TRACE_ADD(3, w3);
+            }
+            // ---- P V in tile order: the peer's tile in front of this one, then this one ----
+            const float m_own = m_used;
+            if (j > 0) ok = receive(j - 1u);
+            if (ok) ok = release(j, m_own, &bars->p_own_full);
+        }
+        // the last tile when it is the peer's
+        if (ok && ((tiles - 1u) & 1u) != half) ok = receive(tiles - 1u);
+        if (ok) ok = pair_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
+        if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up();
+        // this CTA's share of the denominators, and the maximum it is relative to, go to the peer
+        cluster_store_f32(cluster_map(smem_u32(l_box + side * kMlaHeads + head), peer), l);
+        if (side == 0u) cluster_store_f32(cluster_map(smem_u32(m_box + kMlaHeads + head), peer), m_used);
+        pdl_launch_dependents();
+        // (the cluster barrier below is reached by every thread of both CTAs)
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        bool fine = ok && !*abort && meet();
+        if (fine) {
+            tc_fence_after_sync();
+            // the row's denominator: both sides of both CTAs
+            // both shares at the accumulator's scale
+            const float m_theirs = m_box[kMlaHeads + head];
+            const float mine_scaled = m_used == -INFINITY ? 0.0f : l * exp2_approx(m_used - m_o);
+            const float theirs_scaled = m_theirs == -INFINITY ? 0.0f : l_box[side * kMlaHeads + head] * exp2_approx(m_theirs - m_o);
+            exchange[side * kMlaHeads + head] = mine_scaled + theirs_scaled;
+            fine = meet();
+        }
+        float *staged = reinterpret_cast<float *>(smem);
+        if (fine) {
+            l = exchange[head] + exchange[kMlaHeads + head];
+            const float inverse = l > 0.0f ? 1.0f / l : 0.0f;
+            // every tile has been consumed: the tile buffers are free for the turn of the rows
+            float *mine = staged + head * (unsigned)part_stride + 128u * side;
+#pragma unroll 1
+            for (int i = 0; i < kMlaHalf / 64; ++i) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_base + 128u * side + 32 * i, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    *reinterpret_cast<float2 *>(mine + 32 * i + c) =
+                        make_float2(__uint_as_float(o[c]) * inverse, __uint_as_float(o[c + 1]) * inverse);
+            }
+            if (side == 1u)
+                *reinterpret_cast<float2 *>(staged + head * (unsigned)part_stride + kMlaHalf) =
+                    make_float2(m_o == -INFINITY ? -INFINITY : m_o * 0.6931471805599453f, l);
+            mbar_arrive(&bars->rows_staged);
+            fine = pair_wait(&bars->rows_staged, 0, abort);
+        }
+        if (fine) {
+            const unsigned int writer = side * 4u + quadrant;
+            for (unsigned int r = writer; r < (unsigned)kMlaHeads; r += 8u) {
+                float2 *dst = reinterpret_cast<float2 *>(
+                    p.partials +
+                    ((((unsigned long long)b * kMlaHeads + r) * 2ull + half) * p.max_splits + split) * part_stride);
+                const float2 *src = reinterpret_cast<const float2 *>(staged + r * (unsigned)part_stride);
+                for (unsigned int k = lane; k < (unsigned)part_stride / 2u; k += 32u) dst[k] = src[k];
+            }
+        }
+    }
+    if (warp == 4 || warp == 5 || warp >= 10u) {
+        // the producer and issuer warps meet the softmax warps at the cluster barrier
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, kMlaTmemColumns);
+}
+
 // ---- host side ------------------------------------------------------------------------
 
 typedef CUresult (*MlaEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -687,7 +1284,22 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
     if (events) cudaEventRecord((cudaEvent_t)events[0], s);
     mla_absorb_kernel<<<dim3(kMlaHeads, 4), 128, kAbsorbSmem, s>>>(*p);
     if (events) cudaEventRecord((cudaEvent_t)events[1], s);
-    mla_decode_tcgen05_kernel<<<dim3(2, p->max_splits, p->sessions), kMlaThreads, kMlaSmemBytes, s>>>(*p, maps);
+    // The paired form (one score product per tile for the two CTAs of a pair) is taken unless the
+    // environment asks for the independent form (YVEX_B200_MLA_INDEPENDENT=1, for comparisons).
+    static int paired = -1;
+    if (paired < 0) {
+        const char *choice = getenv("YVEX_B200_MLA_INDEPENDENT");
+        paired = choice && choice[0] == '1' ? 0 : 1;
+        if (paired && cudaFuncSetAttribute(mla_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kPairSmemBytes) != cudaSuccess) {
+            cudaGetLastError();
+            paired = 0;
+        }
+    }
+    if (paired)
+        mla_decode_pair_kernel<<<dim3(2, p->max_splits, p->sessions), kPairThreads, kPairSmemBytes, s>>>(*p, maps);
+    else
+        mla_decode_tcgen05_kernel<<<dim3(2, p->max_splits, p->sessions), kMlaThreads, kMlaSmemBytes, s>>>(*p, maps);
     if (events) cudaEventRecord((cudaEvent_t)events[2], s);
     int rc = yvx_cuda_check(cudaGetLastError(), "mla kernels");
     if (rc != 0) return rc;
