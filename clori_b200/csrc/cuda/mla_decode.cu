@@ -814,41 +814,42 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         unsigned int next_pv = 0, next_own = 0;    // tile index of the next P V; index (among own tiles) of the next score product
         int score_stage = 0;                       // 0: first part pending, 1: second part pending
         uint32_t idle = 0;
-        while (ok && next_pv < tiles) {
-            bool issued = false;
-            // P V of the oldest tile whose weights (and V) are there
-            {
-                const unsigned int j = next_pv, i = j >> 1;
-                const bool own = (j & 1u) == half;
-                const bool there = own ? ready(&bars->p_own_full, i & 1u)
-                                       : (ready(&bars->peer_ready, i & 1u) && ready(&bars->vp_full, i & 1u));
-                if (there) {
-                    tc_fence_after_sync();
-                    const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
-                    const uint32_t v_lo = smem_desc_sw128_lo(
-                        smem_u32(smem + (own ? kPairOffKb + (i & 1u) * kMlaVPartBytes : kPairOffVp)), kMlaKvSubBytes);
+        // P V of the oldest tile whose weights (and V) are there; also called between the k-steps of a
+        // score product, so that a tile the peer waits for does not queue behind twenty score instructions
+        auto try_pv = [&]() -> bool {
+            if (next_pv >= tiles) return false;
+            const unsigned int j = next_pv, i = j >> 1;
+            const bool own = (j & 1u) == half;
+            const bool there = own ? ready(&bars->p_own_full, i & 1u)
+                                   : (ready(&bars->peer_ready, i & 1u) && ready(&bars->vp_full, i & 1u));
+            if (!there) return false;
+            tc_fence_after_sync();
+            const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
+            const uint32_t v_lo = smem_desc_sw128_lo(
+                smem_u32(smem + (own ? kPairOffKb + (i & 1u) * kMlaVPartBytes : kPairOffVp)), kMlaKvSubBytes);
 #pragma unroll
-                    for (int kk = 0; kk < kMlaN / 16; ++kk)
-                        tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
-                                       (j || kk) ? 1u : 0u);
-                    if (own) {
-                        tc_commit_pred(elected, &bars->kb_done[i & 1u]);
-                        tc_commit_pred(elected, &bars->pv_own_done);
-                    } else {
-                        tc_commit_pred(elected, &bars->pvp_done);
-                        // ... and tells the peer at once that the weights it sent are consumed
-                        asm volatile(
-                            "{\n\t.reg .pred pe;\n\t"
-                            "setp.ne.b32 pe, %0, 0;\n\t"
-                            "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
-                            ::"r"(elected), "r"(peer_credit)
-                            : "memory");
-                    }
-                    tc_commit_pred(elected, &bars->pv_done);
-                    ++next_pv;
-                    issued = true;
-                }
+            for (int kk = 0; kk < kMlaN / 16; ++kk)
+                tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
+                               (j || kk) ? 1u : 0u);
+            if (own) {
+                tc_commit_pred(elected, &bars->kb_done[i & 1u]);
+                tc_commit_pred(elected, &bars->pv_own_done);
+            } else {
+                tc_commit_pred(elected, &bars->pvp_done);
+                // ... and tells the peer at once that the weights it sent are consumed
+                asm volatile(
+                    "{\n\t.reg .pred pe;\n\t"
+                    "setp.ne.b32 pe, %0, 0;\n\t"
+                    "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+                    ::"r"(elected), "r"(peer_credit)
+                    : "memory");
             }
+            tc_commit_pred(elected, &bars->pv_done);
+            ++next_pv;
+            return true;
+        };
+        while (ok && next_pv < tiles) {
+            bool issued = try_pv();
             // the score product of this CTA's next tile, in two parts
             if (!issued && next_own < own_tiles) {
                 const unsigned int i = next_own;
@@ -858,16 +859,19 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                         tc_fence_after_sync();
                         // 8 k-steps against query dims in tensor memory (first two sub-tiles of the other half) ...
 #pragma unroll
-                        for (int ks = 0; ks < 8; ++ks)
+                        for (int ks = 0; ks < 8; ++ks) {
                             tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
                                            ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk,
                                            ks ? 1u : 0u);
+                        }
                         // ... 12 against query dims in shared memory (its last two sub-tiles, then the rope dims)
 #pragma unroll
-                        for (int ks = 0; ks < 12; ++ks)
+                        for (int ks = 0; ks < 12; ++ks) {
+                            if (ks == 4) try_pv();
                             tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
                                            ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk,
                                            1u);
+                        }
                         tc_commit_pred(elected, &bars->ka_done);
                         score_stage = 1;
                         issued = true;
@@ -876,9 +880,11 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     tc_fence_after_sync();
                     const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
 #pragma unroll
-                    for (int ks = 0; ks < 16; ++ks)
+                    for (int ks = 0; ks < 16; ++ks) {
+                        if (ks == 8) try_pv();
                         tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
                                        kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+                    }
                     tc_commit_pred(elected, &bars->s_full);
                     score_stage = 0;
                     ++next_own;
@@ -998,6 +1004,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         };
         for (unsigned int i = 0; i < own_tiles && ok; ++i) {
             const unsigned int j = 2u * i + half;
+            bool received_early = false;
             {
                 // ---- the weights of a tile this CTA scores; nothing here waits for the peer's softmax ----
                 MLA_TRACE_BEGIN(w0);
@@ -1023,7 +1030,21 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
 #pragma unroll
                 for (int c = 0; c < 32; c += 2)
                     mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-                if (i > 0 && !meet()) {   // the partner has read the previous maximum
+                // Has the peer's message for the tile in front of this one arrived already? Then it is
+                // processed now (its P V can run, and the peer gets its buffer back, while this tile's
+                // exponentials are computed); otherwise after this tile's weights are out. The two warps
+                // of a quadrant must take the same turn (they share a row's maximum): the first decides.
+                int *early = reinterpret_cast<int *>(m_out + kMlaHeads) + quadrant;
+                if (side == 0u) {
+                    const int arrived = j > 0 && __shfl_sync(0xffffffffu, (int)mbar_test(&bars->p_peer_full, ((j - 1u) >> 1) & 1u), 0);
+                    if (lane == 0) *early = arrived;
+                }
+                if (!meet()) {   // (also: the partner has read the previous maximum)
+                    ok = false;
+                    break;
+                }
+                received_early = j > 0 && *early != 0;
+                if (received_early && !receive(j - 1u)) {
                     ok = false;
                     break;
                 }
@@ -1087,11 +1108,18 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             }
             // ---- P V in tile order: the peer's tile in front of this one, then this one ----
             const float m_own = m_used;
-            if (j > 0) ok = receive(j - 1u);
+            if (j > 0 && !received_early) ok = receive(j - 1u);
             if (ok) ok = release(j, m_own, &bars->p_own_full);
         }
         // the last tile when it is the peer's
         if (ok && ((tiles - 1u) & 1u) != half) ok = receive(tiles - 1u);
+#ifdef YVX_MLA_TRACE
+        if (traced && warp == 0) {
+            for (int i = 0; i < 6; ++i) yvx_mla_trace[i] = trace_local[i];
+            yvx_mla_trace[6] = (unsigned long long)(clock64() - trace_start);
+            yvx_mla_trace[7] = tiles;
+        }
+#endif
         if (ok) ok = pair_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
         if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up();
         // this CTA's share of the denominators, and the maximum it is relative to, go to the peer
@@ -1285,17 +1313,15 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
     mla_absorb_kernel<<<dim3(kMlaHeads, 4), 128, kAbsorbSmem, s>>>(*p);
     if (events) cudaEventRecord((cudaEvent_t)events[1], s);
     // The paired form (one score product per tile for the two CTAs of a pair) is taken unless the
-    // environment asks for the independent form (YVEX_B200_MLA_INDEPENDENT=1, for comparisons).
-    static int paired = -1;
-    if (paired < 0) {
-        const char *choice = getenv("YVEX_B200_MLA_INDEPENDENT");
-        paired = choice && choice[0] == '1' ? 0 : 1;
-        if (paired && cudaFuncSetAttribute(mla_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kPairSmemBytes) != cudaSuccess) {
-            cudaGetLastError();
-            paired = 0;
-        }
+    // environment asks for the independent form (YVEX_B200_MLA_INDEPENDENT=1: comparisons and tests).
+    static int pair_configured = -1;
+    if (pair_configured < 0) {
+        pair_configured = cudaFuncSetAttribute(mla_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               kPairSmemBytes) == cudaSuccess;
+        if (!pair_configured) cudaGetLastError();
     }
+    const char *choice = getenv("YVEX_B200_MLA_INDEPENDENT");
+    const bool paired = pair_configured && !(choice && choice[0] == '1');
     if (paired)
         mla_decode_pair_kernel<<<dim3(2, p->max_splits, p->sessions), kPairThreads, kPairSmemBytes, s>>>(*p, maps);
     else

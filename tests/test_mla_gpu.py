@@ -50,8 +50,19 @@ def cosine(a, b):
     return float(a @ b / np.sqrt((a @ a) * (b @ b)))
 
 
+@pytest.fixture(params=["paired", "independent"])
+def form(request, monkeypatch):
+    """Both forms of the attention kernel: a cluster of two CTAs that computes every score tile once and
+    exchanges the weights (the default), and two independent CTAs that both compute it."""
+    if request.param == "independent":
+        monkeypatch.setenv("YVEX_B200_MLA_INDEPENDENT", "1")
+    else:
+        monkeypatch.delenv("YVEX_B200_MLA_INDEPENDENT", raising=False)
+    return request.param
+
+
 @pytest.mark.parametrize("sessions,context", [(1, 32), (2, 100), (3, 700)])
-def test_mla_decode_matches_restatement(backend, oracle, sessions, context):
+def test_mla_decode_matches_restatement(backend, oracle, sessions, context, form):
     qn, qr, w, lat, rk = workloads.mla_decode_bf16(seed=4, batch=sessions, context=context)
     lengths = [context] * sessions
     if sessions > 1:
@@ -72,7 +83,28 @@ def test_mla_decode_matches_restatement(backend, oracle, sessions, context):
     assert np.array_equal(q_abs[:, :, 512:], qr)
 
 
-def test_mla_decode_matches_reference_made_fixtures(backend):
+@pytest.mark.parametrize("context", [64, 129, 1000, 2500])
+def test_mla_decode_with_maxima_that_grow_along_the_sequence(backend, oracle, context, form):
+    """Later rows score higher and higher, so the running maximum grows again and again: every path that
+    rescales the accumulator runs (in the paired form also the adoption of the peer's maximum and weights
+    that were scaled with a maximum the accumulator has already left behind)."""
+    qn, qr, w, lat, rk = workloads.mla_decode_bf16(seed=9, batch=2, context=context)
+    f, bits = clori_b200.bf16_bits_to_f32, clori_b200.f32_to_bf16_bits
+    ramp = (1.0 + 6.0 * (np.arange(context, dtype=np.float32) / context) ** 2)[None, :, None]
+    lat, rk = bits(f(lat) * ramp), bits(f(rk) * ramp)
+    lengths = [context, max(1, context - 21)]
+    scale = 1.0 / np.sqrt(192.0)
+    out, _, status, _, _ = run_mla(backend, qn, qr, w, lat, rk, lengths, scale)
+    assert status == 0
+    for s in range(2):
+        n = lengths[s]
+        ref = oracle.mla_decode(qn[s], qr[s], w, lat[s, :n], rk[s, :n], scale)
+        bar = 2e-3 * max(1.0, float(np.abs(ref).max()))
+        assert np.abs(out[s] - ref).max() <= bar, (float(np.abs(out[s] - ref).max()), bar)
+        assert cosine(out[s], ref) >= 0.9999
+
+
+def test_mla_decode_matches_reference_made_fixtures(backend, form):
     g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "mla_decode.npz"))
     f = clori_b200.bf16_bits_to_f32
     scale = 1.0 / np.sqrt(192.0)
