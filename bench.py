@@ -2287,7 +2287,7 @@ def summary_of(line, others):
     ref_gpu = others.get("reference_gpu_kernels")
     if ref_gpu and "config1_decode_f32" in ref_gpu:
         out["vs_reference_gpu"] = {k.replace("prefill_f32_2048x16q4kv_", "prefill_"): _r(v["speedup"], 3)
-                                   for k, v in ref_gpu.items() if isinstance(v, dict)}
+                                   for k, v in ref_gpu.items() if isinstance(v, dict) and "speedup" in v}
     gemm = others.get("projections_prefill_4096")
     if gemm:
         out["proj_prefill"] = {"ms": _r(gemm["step_ms"]), "tflops": _r(gemm["achieved_tflops"]),
