@@ -165,9 +165,25 @@ class Workload:
         rng = np.random.Generator(np.random.PCG64(seed + 77))
         self.q_host = clori_b200.f32_to_bf16_bits(
             rng.standard_normal((SESSIONS, 1, QUERY_HEADS * HEAD_DIM), dtype=np.float32))
-        self.q = b.tensor("q", self.q_host)
-        self.kv_tokens = b.tensor("kv_tokens", self.lengths)
-        self.block_table = b.tensor("block_table", self.table)
+        # The per-step inputs (queries, lengths, block table) live in ONE device allocation, so the
+        # end-to-end leg moves them with one host->device copy; the operator sees three tensors.
+        parts = (("q", self.q_host, abi.DTYPE_BF16), ("kv_tokens", self.lengths, abi.DTYPE_I32),
+                 ("block_table", self.table, abi.DTYPE_I32))
+        self.input_offsets, total = {}, 0
+        for name, array, _ in parts:
+            self.input_offsets[name] = total
+            total += (np.ascontiguousarray(array).nbytes + 255) // 256 * 256
+        self.inputs = b.alloc("step_inputs", abi.DTYPE_I8, (total,))
+        self.inputs_host = np.zeros(total, np.uint8)
+        for name, array, dtype in parts:
+            array = np.ascontiguousarray(array)
+            offset = self.input_offsets[name]
+            self.inputs_host[offset:offset + array.nbytes] = array.view(np.uint8).reshape(-1)
+            view = b.wrap(name, dtype, array.shape, self.inputs.data_ptr + offset, array.nbytes)
+            view.struct.is_written = 1
+            setattr(self, name if name != "q" else "q", view)
+        assert self.lib.yvx_cuda_upload_async(self.inputs.data_ptr, self.inputs_host.ctypes.data, total, b.stream) == 0
+        self.inputs.struct.is_written = 1
         self.out = b.alloc("out", abi.DTYPE_BF16, (SESSIONS, 1, QUERY_HEADS * HEAD_DIM))
         self.requirement = clori_b200.attention_requirement(
             1, int(self.lengths.max()), 0, QUERY_HEADS, KV_HEADS, HEAD_DIM, dtype=abi.DTYPE_BF16,
@@ -200,23 +216,18 @@ class Workload:
     # -- end to end: host buffers in, host buffer out -----------------------
     def pinned(self):
         if self._pinned is None:
-            sizes = {"q": self.q_host.nbytes, "lens": self.lengths.nbytes, "table": self.table.nbytes,
-                     "out": SESSIONS * QUERY_HEADS * HEAD_DIM * 2}
+            sizes = {"inputs": self.inputs_host.nbytes, "out": SESSIONS * QUERY_HEADS * HEAD_DIM * 2}
             self._pinned = {}
             for name, size in sizes.items():
                 p = C.c_void_p()
                 assert self.lib.yvx_cuda_host_alloc(C.byref(p), size) == 0
                 self._pinned[name] = (p, size)
-            C.memmove(self._pinned["q"][0], self.q_host.ctypes.data, self.q_host.nbytes)
-            C.memmove(self._pinned["lens"][0], self.lengths.ctypes.data, self.lengths.nbytes)
-            C.memmove(self._pinned["table"][0], self.table.ctypes.data, self.table.nbytes)
+            C.memmove(self._pinned["inputs"][0], self.inputs_host.ctypes.data, self.inputs_host.nbytes)
         return self._pinned
 
     def step_e2e(self):
         pin, s, lib = self.pinned(), self.backend.stream, self.lib
-        lib.yvx_cuda_upload_async(self.q.data_ptr, pin["q"][0], pin["q"][1], s)
-        lib.yvx_cuda_upload_async(self.kv_tokens.data_ptr, pin["lens"][0], pin["lens"][1], s)
-        lib.yvx_cuda_upload_async(self.block_table.data_ptr, pin["table"][0], pin["table"][1], s)
+        lib.yvx_cuda_upload_async(self.inputs.data_ptr, pin["inputs"][0], pin["inputs"][1], s)
         facts = self.step()
         lib.yvx_cuda_download_async(pin["out"][0], self.out.data_ptr, pin["out"][1], s)
         lib.yvx_cuda_stream_synchronize(s)
@@ -224,7 +235,7 @@ class Workload:
 
     def e2e_bytes(self):
         pin = self.pinned()
-        return pin["q"][1] + pin["lens"][1] + pin["table"][1], pin["out"][1]
+        return pin["inputs"][1], pin["out"][1]
 
     # -- the dominant kernel alone -------------------------------------------
     def kernel_ms(self, repeats, chunk=0):
