@@ -2127,11 +2127,11 @@ def main():
     others, other_samples = {}, {}
     if world == 1 and not args.headline_only:
         hbm_peak = measured_peaks()[0]
-        plan = (("decode_f32_config1", "f32", lambda: bench_decode_f32(lib, b, w.abi, hbm_peak, 64)),
-                ("verify_q8_config4_1gpu", "q8", lambda: bench_verify_q8(lib, b, w.abi, hbm_peak, 20)),
+        plan = (("decode_f32_config1", "f32", lambda: bench_decode_f32(lib, b, w.abi, hbm_peak, 200)),
+                ("verify_q8_config4_1gpu", "q8", lambda: bench_verify_q8(lib, b, w.abi, hbm_peak, 100)),
                 ("prefill_config3", "prefill", lambda: bench_prefill(lib, b, w.abi, 10)),
                 ("prefill_f32_contract", "prefill_f32", lambda: bench_prefill_f32(lib, b, w.abi, 3)),
-                ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 10)),
+                ("latent_decode_config5", "mla", lambda: bench_mla(lib, b, w.abi, hbm_peak, 20)),
                 ("projections_decode_step", "proj", lambda: bench_projections(lib, b, w.abi, hbm_peak, 20)),
                 ("projections_prefill_4096", None, lambda: bench_projections_prefill(lib, b, w.abi, 5)),
                 ("reference_gpu_kernels", None, lambda: (bench_reference_gpu(lib, b, w.abi), None)),
