@@ -579,7 +579,7 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 // a CTA processes the peer's message for tile j - 1 (adopting its maximum, rescaling O and l if
 // it grew) before it computes the weights of tile j. Every wait is bounded and gives up at once
 // when either CTA has recorded a failure; both CTAs always reach the cluster barrier at the end.
-constexpr int kPairThreads = 384;   // 8 softmax warps, the MMA warp (5), three TMA warps (4, 10, 11)
+constexpr int kPairThreads = 416;   // 8 softmax warps, the MMA warp (5), three TMA warps (4, 10, 11), the sender (12)
 constexpr int kPairQSmemSubs = 3, kPairQTmemCols = 192;
 constexpr int kPairOffQ = 0;
 constexpr int kPairOffKa = kPairQSmemSubs * kMlaQSubBytes;            // 49152
@@ -601,6 +601,7 @@ struct PairBarriers {
     uint64_t p_own_full, pv_own_done;     // weights of an own tile written / consumed
     uint64_t p_peer_full, peer_ready;     // the peer's weights have arrived / its message is processed
     uint64_t p_peer_free;                 // the peer has consumed the weights this CTA sent it
+    uint64_t p_written, p_own_sent;       // an own tile's weights are written / have left for the peer
     uint64_t pv_done;                     // any P V
     uint64_t halves[4], rows_staged;      // the two softmax warps of a quadrant meet; all rows are staged
     uint32_t tmem_base;
@@ -725,6 +726,8 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         mbar_init(&bars->p_peer_full, 1);
         mbar_init(&bars->peer_ready, 8);
         mbar_init(&bars->p_peer_free, 1);
+        mbar_init(&bars->p_written, 8);
+        mbar_init(&bars->p_own_sent, 1);
         mbar_init(&bars->pv_done, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&bars->halves[i], 64);
         mbar_init(&bars->rows_staged, 2 * kMlaHeads);
@@ -751,7 +754,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         cluster_store_b32(peer_abort, 1u);
     };
 
-    if (warp == 4 || warp >= 10u) {
+    if (warp == 4 || warp == 10 || warp == 11) {
         // ------------------------------ TMA producers: one warp per kind of part (a lane that spins on
         // a barrier beside other spinning lanes of its warp reacts late) ------------------------------
         if (warp == 4 && lane == 0) {
@@ -797,6 +800,31 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->vp_full, 64 * (own0 + u), token, (int)b);
             }
         }
+    } else if (warp == 12) {
+        // ------------------------------ sender ------------------------------
+        // The weights of an own tile (and the maxima they were scaled with) go to the peer as two bulk
+        // copies between the shared memories, counted in bytes on the peer's barrier, as soon as the
+        // peer has consumed the tile sent before. The softmax does not wait for that: its buffer is
+        // the second of the two tiles in flight (it waits for THIS tile to have left before it writes
+        // the next one).
+        if (lane == 0) {
+            const uint32_t peer_p = cluster_map(smem_u32(smem + kPairOffPPeer), peer);
+            const uint32_t peer_m = cluster_map(smem_u32(m_box), peer);
+            const uint32_t peer_full = cluster_map(smem_u32(&bars->p_peer_full), peer);
+            for (unsigned int i = 0; i < own_tiles; ++i) {
+                if (!pair_wait(&bars->p_written, i & 1u, abort) ||
+                    (i > 0 && !pair_wait(&bars->p_peer_free, (i - 1u) & 1u, abort))) {
+                    give_up();
+                    break;
+                }
+                fence_proxy_async();
+                cluster_bulk_copy(peer_p, smem + kPairOffPOwn, kPairPBytes, peer_full);
+                cluster_bulk_copy(peer_m, m_out, kMlaHeads * 4, peer_full);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                mbar_arrive(&bars->p_own_sent);
+            }
+        }
     } else if (warp == 5) {
         // ------------------------------ MMA issuer ------------------------------
         constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
@@ -806,23 +834,19 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         const uint32_t peer_credit = cluster_map(smem_u32(&bars->p_peer_free), peer);
         const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffQ), 16);
         const uint32_t ka_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKa), 16);
-        auto ready = [&](uint64_t *bar, uint32_t parity) {     // warp-uniform look at a barrier
-            return __any_sync(0xffffffffu, mbar_test(bar, parity)) != 0;
+        auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {    // every lane waits: the warp stays converged
+            return __all_sync(0xffffffffu, pair_wait(bar, parity, abort)) != 0;
         };
-        bool ok = __all_sync(0xffffffffu, pair_wait(&bars->q_full, 0, abort)) &&
-                  __all_sync(0xffffffffu, pair_wait(&bars->q_tmem_full, 0, abort));
-        unsigned int next_pv = 0, next_own = 0;    // tile index of the next P V; index (among own tiles) of the next score product
-        int score_stage = 0;                       // 0: first part pending, 1: second part pending
-        uint32_t idle = 0;
-        // P V of the oldest tile whose weights (and V) are there; also called between the k-steps of a
-        // score product, so that a tile the peer waits for does not queue behind twenty score instructions
-        auto try_pv = [&]() -> bool {
-            if (next_pv >= tiles) return false;
-            const unsigned int j = next_pv, i = j >> 1;
+        // P V of tile j, once its weights (and V) are there
+        auto pv = [&](unsigned int j) -> bool {
+            const unsigned int i = j >> 1;
             const bool own = (j & 1u) == half;
-            const bool there = own ? ready(&bars->p_own_full, i & 1u)
-                                   : (ready(&bars->peer_ready, i & 1u) && ready(&bars->vp_full, i & 1u));
-            if (!there) return false;
+            MLA_TRACE_BEGIN(tw);
+            if (own ? !wait_all(&bars->p_own_full, i & 1u)
+                    : !(wait_all(&bars->peer_ready, i & 1u) && wait_all(&bars->vp_full, i & 1u)))
+                return false;
+            MLA_TRACE_ADD(4, tw);
+            MLA_TRACE_BEGIN(tpv);
             tc_fence_after_sync();
             const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
             const uint32_t v_lo = smem_desc_sw128_lo(
@@ -845,66 +869,82 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     : "memory");
             }
             tc_commit_pred(elected, &bars->pv_done);
-            ++next_pv;
+            MLA_TRACE_ADD(1, tpv);
             return true;
         };
-        while (ok && next_pv < tiles) {
-            bool issued = try_pv();
-            // the score product of this CTA's next tile, in two parts
-            if (!issued && next_own < own_tiles) {
-                const unsigned int i = next_own;
-                if (score_stage == 0) {
-                    // the score buffer is free once the softmax has read the previous own tile out of it
-                    if (ready(&bars->ka_full, i & 1u) && (i == 0u || ready(&bars->s_free, (i - 1u) & 1u))) {
-                        tc_fence_after_sync();
-                        // 8 k-steps against query dims in tensor memory (first two sub-tiles of the other half) ...
-#pragma unroll
-                        for (int ks = 0; ks < 8; ++ks) {
-                            tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
-                                           ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk,
-                                           ks ? 1u : 0u);
-                        }
-                        // ... 12 against query dims in shared memory (its last two sub-tiles, then the rope dims)
-#pragma unroll
-                        for (int ks = 0; ks < 12; ++ks) {
-                            if (ks == 4) try_pv();
-                            tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
-                                           ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk,
-                                           1u);
-                        }
-                        tc_commit_pred(elected, &bars->ka_done);
-                        score_stage = 1;
-                        issued = true;
-                    }
-                } else if (ready(&bars->kb_full[i & 1u], (i >> 1) & 1u)) {
-                    tc_fence_after_sync();
-                    const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
-#pragma unroll
-                    for (int ks = 0; ks < 16; ++ks) {
-                        if (ks == 8) try_pv();
-                        tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
-                                       kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
-                    }
-                    tc_commit_pred(elected, &bars->s_full);
-                    score_stage = 0;
-                    ++next_own;
-                    issued = true;
-                }
+        // the score product of own tile i: 8 + 12 k-steps over the scores-only part, 16 over the own half
+        unsigned int next_pv = 0;
+        // one look (by the issuing lane; the warp follows) at whether the next tile's P V could run now
+        auto pv_could_run = [&](unsigned int limit) -> bool {
+            int there = 0;
+            if (elected && next_pv < limit) {
+                const unsigned int k = next_pv >> 1;
+                there = (next_pv & 1u) == half ? mbar_test(&bars->p_own_full, k & 1u)
+                                               : (mbar_test(&bars->peer_ready, k & 1u) && mbar_test(&bars->vp_full, k & 1u));
             }
-#ifdef YVX_MLA_TRACE
-            if (!issued) trace_local[0] += 1ull;
-#endif
-            if (issued) {
-                idle = 0;
-            } else if (++idle > kWaitSpinLimit || ((idle & 255u) == 255u && *abort)) {
-                ok = false;
-            }
+            return __any_sync(0xffffffffu, there) != 0;
+        };
+        auto scores = [&](unsigned int i, unsigned int pv_limit) -> bool {
+            MLA_TRACE_BEGIN(tw);
+            // the score buffer is free once the softmax has read the previous own tile out of it
+            if (!wait_all(&bars->ka_full, i & 1u)) return false;
+            MLA_TRACE_ADD(5, tw);
+            MLA_TRACE_BEGIN(tw3);
+            if (i > 0u && !wait_all(&bars->s_free, (i - 1u) & 1u)) return false;
+            MLA_TRACE_ADD(7, tw3);
+            MLA_TRACE_BEGIN(tqa);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)      // query dims in tensor memory (first two sub-tiles of the other half)
+                tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
+                               ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, ks ? 1u : 0u);
+#pragma unroll
+            for (int ks = 0; ks < 12; ++ks)     // query dims in shared memory (its last two sub-tiles, then the rope dims)
+                tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
+                               ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+            tc_commit_pred(elected, &bars->ka_done);
+            MLA_TRACE_ADD(2, tqa);
+            // between the two parts (the own-half part may still be landing): a P V that is ready
+            if (pv_could_run(pv_limit) && !pv(next_pv++)) return false;
+            MLA_TRACE_BEGIN(tw2);
+            if (!wait_all(&bars->kb_full[i & 1u], (i >> 1) & 1u)) return false;
+            MLA_TRACE_ADD(6, tw2);
+            MLA_TRACE_BEGIN(tqb);
+            tc_fence_after_sync();
+            const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
+#pragma unroll
+            for (int ks = 0; ks < 16; ++ks)
+                tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
+                               kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+            tc_commit_pred(elected, &bars->s_full);
+            MLA_TRACE_ADD(3, tqb);
+            return true;
+        };
+        // A fixed program, every wait blocking (a look at a barrier costs this warp 160 cycles, and the
+        // tensor pipe idles while it looks): the score product of the NEXT own tile runs under the softmax
+        // of the current one.
+        bool ok = wait_all(&bars->q_full, 0) && wait_all(&bars->q_tmem_full, 0);
+        if (ok && own_tiles) ok = scores(0, 0);
+        for (unsigned int i = 0; ok && i < own_tiles; ++i) {
+            // the score product of own tile i + 1 (with the peer's tile in front of own tile i between its
+            // parts if that is ready), then the P V products up to own tile i
+            const unsigned int own = 2u * i + half;
+            if (i + 1u < own_tiles) ok = scores(i + 1u, own);
+            for (; ok && next_pv <= own; ++next_pv) ok = pv(next_pv);
         }
+        for (; ok && next_pv < tiles; ++next_pv) ok = pv(next_pv);
         if (!ok && lane == 0) give_up();
 #ifdef YVX_MLA_TRACE
         if (traced) {
             yvx_mla_trace[8] = trace_local[0];
             yvx_mla_trace[9] = (unsigned long long)(clock64() - trace_start);
+            yvx_mla_trace[10] = trace_local[1];
+            yvx_mla_trace[11] = trace_local[2];
+            yvx_mla_trace[12] = trace_local[3];
+            yvx_mla_trace[13] = trace_local[4];
+            yvx_mla_trace[14] = trace_local[5];
+            yvx_mla_trace[15] = trace_local[7];
+            yvx_mla_trace[8] = trace_local[6];
         }
 #endif
     } else {
@@ -946,9 +986,6 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             mbar_arrive(&bars->halves[quadrant]);
             return pair_wait(&bars->halves[quadrant], meetings++ & 1u, abort);
         };
-        const uint32_t peer_p = cluster_map(smem_u32(smem + kPairOffPPeer), peer);
-        const uint32_t peer_m = cluster_map(smem_u32(m_box), peer);
-        const uint32_t peer_full = cluster_map(smem_u32(&bars->p_peer_full), peer);
         // O columns of this thread's side are rescaled when the row maximum grows
         auto rescale = [&](float factor) {
 #pragma unroll 1
@@ -984,6 +1021,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             return true;
         };
         // The peer's message for its tile j: its weights are in place, its maxima in m_box.
+        float m_heard = -INFINITY;
         auto receive = [&](unsigned int j) -> bool {
             const unsigned int ip = j >> 1;
             MLA_TRACE_BEGIN(w4);
@@ -993,11 +1031,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             if (warp == 0 && lane == 0 && ip + 1u < peer_tiles)   // the next message may be counted from now on
                 mbar_expect_tx(&bars->p_peer_full, kPairPBytes + kMlaHeads * 4);
             const float m_in = m_box[head];
-            // adopt a larger maximum, so that the two CTAs' references stay together
-            if (m_in > m_used) {
-                l *= m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_in);
-                m_used = m_in;
-            }
+            m_heard = m_in;     // adopted by the caller at a fixed point of its program (results must not depend on timing)
             const bool fine = release(j, m_in, &bars->peer_ready);
             MLA_TRACE_ADD(5, w5);
             return fine;
@@ -1074,9 +1108,9 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 l += sum0 + sum1;
                 MLA_TRACE_ADD(1, w1);
                 MLA_TRACE_BEGIN(w2);
-                // both copies of the previous own tile's weights have been consumed
+                // the previous own tile's weights have been consumed here and have left for the peer
                 if (i > 0 && !(pair_wait(&bars->pv_own_done, (i - 1u) & 1u, abort) &&
-                               pair_wait(&bars->p_peer_free, (i - 1u) & 1u, abort))) {
+                               pair_wait(&bars->p_own_sent, (i - 1u) & 1u, abort))) {
                     ok = false;
                     break;
                 }
@@ -1093,23 +1127,19 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 }
                 fence_proxy_async();   // the tensor pipe and the bulk copy read these bytes through the async proxy
                 __syncwarp();
-                if (lane == 0) {
-                    // the last of the eight warps sends the tile (and the maxima it was scaled with) to the peer:
-                    // two bulk copies between the shared memories, counted in bytes on the peer's barrier
-                    __threadfence_block();
-                    if ((atomicAdd(&bars->written, 1u) & 7u) == 7u) {
-                        __threadfence_block();
-                        fence_proxy_async();
-                        cluster_bulk_copy(peer_p, smem + kPairOffPOwn, kPairPBytes, peer_full);
-                        cluster_bulk_copy(peer_m, m_out, kMlaHeads * 4, peer_full);
-                    }
-                }
+                if (lane == 0) mbar_arrive(&bars->p_written);
                 MLA_TRACE_ADD(3, w3);
             }
             // ---- P V in tile order: the peer's tile in front of this one, then this one ----
             const float m_own = m_used;
             if (j > 0 && !received_early) ok = receive(j - 1u);
             if (ok) ok = release(j, m_own, &bars->p_own_full);
+            // Here, whether the peer's message was processed before or after this tile's exponentials:
+            // adopt a larger maximum, so that the two CTAs' references stay together.
+            if (m_heard > m_used) {
+                l *= m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_heard);
+                m_used = m_heard;
+            }
         }
         // the last tile when it is the peer's
         if (ok && ((tiles - 1u) & 1u) != half) ok = receive(tiles - 1u);
@@ -1174,7 +1204,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         }
     }
     if (warp == 4 || warp == 5 || warp >= 10u) {
-        // the producer and issuer warps meet the softmax warps at the cluster barrier
+        // the producer, sender and issuer warps meet the softmax warps at the cluster barrier
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
