@@ -48,11 +48,14 @@ constexpr float kMlaRescaleThreshold = 8.0f;
 #ifdef YVX_MLA_TRACE
 // Cycle counters of CTA (0, 0, 0), a development aid compiled out of the library.
 __device__ unsigned long long yvx_mla_trace[16];
+__device__ unsigned long long yvx_mla_marks[16];
+#define MLA_MARK(slot) do { if (traced && warp == 0) yvx_mla_marks[slot] = (unsigned long long)(clock64() - trace_start); } while (0)
 #define MLA_TRACE_BEGIN(t) const long long t = clock64()
 #define MLA_TRACE_ADD(slot, t) \
     do { if (traced) trace_local[slot] += (unsigned long long)(clock64() - t); } while (0)
 #else
 #define MLA_TRACE_BEGIN(t) do { } while (0)
+#define MLA_MARK(slot) do { } while (0)
 #define MLA_TRACE_ADD(slot, t) do { } while (0)
 #endif
 
@@ -579,7 +582,7 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 // a CTA processes the peer's message for tile j - 1 (adopting its maximum, rescaling O and l if
 // it grew) before it computes the weights of tile j. Every wait is bounded and gives up at once
 // when either CTA has recorded a failure; both CTAs always reach the cluster barrier at the end.
-constexpr int kPairThreads = 416;   // 8 softmax warps, the MMA warp (5), three TMA warps (4, 10, 11), the sender (12)
+constexpr int kPairThreads = 288;   // 4 softmax warps (0-3), three TMA warps (4, 6, 7), the MMA warp (5), the sender (8)
 constexpr int kPairQSmemSubs = 3, kPairQTmemCols = 192;
 constexpr int kPairOffQ = 0;
 constexpr int kPairOffKa = kPairQSmemSubs * kMlaQSubBytes;            // 49152
@@ -720,17 +723,17 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         mbar_init(&bars->vp_full, 1);
         mbar_init(&bars->pvp_done, 1);
         mbar_init(&bars->s_full, 1);
-        mbar_init(&bars->s_free, 2 * kMlaHeads);
-        mbar_init(&bars->p_own_full, 8);
+        mbar_init(&bars->s_free, kMlaHeads);
+        mbar_init(&bars->p_own_full, 4);
         mbar_init(&bars->pv_own_done, 1);
         mbar_init(&bars->p_peer_full, 1);
-        mbar_init(&bars->peer_ready, 8);
+        mbar_init(&bars->peer_ready, 4);
         mbar_init(&bars->p_peer_free, 1);
-        mbar_init(&bars->p_written, 8);
+        mbar_init(&bars->p_written, 4);
         mbar_init(&bars->p_own_sent, 1);
         mbar_init(&bars->pv_done, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&bars->halves[i], 64);
-        mbar_init(&bars->rows_staged, 2 * kMlaHeads);
+        mbar_init(&bars->rows_staged, kMlaHeads);
         bars->abort = 0;
         bars->written = 0u;
         fence_barrier_init();
@@ -746,6 +749,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
     cluster_sync_all();          // the peer's barriers exist before anything arrives on them
     tc_fence_after_sync();
     const uint32_t tmem = bars->tmem_base;
+    MLA_MARK(0);
     const uint32_t tmem_o = tmem, tmem_s = tmem + kMlaHalf, tmem_q = tmem + kMlaHalf + kMlaN;
     const uint32_t peer_abort = cluster_map(smem_u32(&bars->abort), peer);
     auto give_up = [&]() {   // records the failure here and at the peer, whose waits then end too
@@ -754,7 +758,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         cluster_store_b32(peer_abort, 1u);
     };
 
-    if (warp == 4 || warp == 10 || warp == 11) {
+    if (warp == 4 || warp == 6 || warp == 7) {
         // ------------------------------ TMA producers: one warp per kind of part (a lane that spins on
         // a barrier beside other spinning lanes of its warp reacts late) ------------------------------
         if (warp == 4 && lane == 0) {
@@ -774,7 +778,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka_full, 64 * (other0 + u), token, (int)b);
                 tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka_full, 0, token, (int)b);
             }
-        } else if (warp == 10 && lane == 0) {
+        } else if (warp == 6 && lane == 0) {
             for (unsigned int i = 0; i < own_tiles; ++i) {
                 const unsigned int buffer = i & 1u;
                 const int token = (int)(t0 + (2u * i + half) * kMlaN);
@@ -787,7 +791,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 for (int u = 0; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full[buffer], 64 * (own0 + u), token, (int)b);
             }
-        } else if (warp == 11 && lane == 0) {
+        } else if (warp == 7 && lane == 0) {
             for (unsigned int i = 0; i < peer_tiles; ++i) {
                 const int token = (int)(t0 + (2u * i + peer) * kMlaN);
                 if (i > 0 && !pair_wait(&bars->pvp_done, (i - 1u) & 1u, abort)) {
@@ -800,7 +804,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->vp_full, 64 * (own0 + u), token, (int)b);
             }
         }
-    } else if (warp == 12) {
+    } else if (warp == 8) {
         // ------------------------------ sender ------------------------------
         // The weights of an own tile (and the maxima they were scaled with) go to the peer as two bulk
         // copies between the shared memories, counted in bytes on the peer's barrier, as soon as the
@@ -948,50 +952,68 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         }
 #endif
     } else {
-        // ------------------------------ softmax warps (0-3: first 32 tokens, 6-9: last 32) ------------------------------
-        const unsigned int side = warp < 4u ? 0u : 1u, quadrant = warp & 3u;
+        // ------------------------------ softmax warps: a thread owns a head (a row of every tile) ------------------------------
+        // (Two warps per 32 heads, each with half of a tile's tokens, were slower here: the two had to agree on
+        // the row maximum through shared memory, and those meetings cost more than the exponentials they halved.)
+        const unsigned int quadrant = warp;
         const unsigned int head = quadrant * 32u + lane;
         const uint32_t lane_base = ((quadrant * 32u) << 16);
-        if (side == 0u) {
+        {
             // 384 query dims of this head into tensor memory: the own latent half, then 128 dims of the other
-            const unsigned short *row = reinterpret_cast<const unsigned short *>(p.q_absorbed) +
-                                        ((unsigned long long)b * kMlaHeads + head) * kMlaWidth;
+            const unsigned short *row0 = reinterpret_cast<const unsigned short *>(p.q_absorbed) +
+                                         ((unsigned long long)b * kMlaHeads + quadrant * 32u) * kMlaWidth;
+            // A warp reads 128-byte pieces of four rows per instruction (a thread reading its own row would touch 32
+            // lines per instruction) and turns them through its 4 KB of the (still unused) weights buffer; three
+            // 64-dim groups are in flight together.
+            unsigned char *turn = smem + kPairOffPOwn + quadrant * 4096u;
+            const unsigned int piece_row = lane >> 3, piece = lane & 7u;
 #pragma unroll 1
-            for (int i = 0; i < kPairQTmemCols / 32; ++i) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(
-                    row + (i < 4 ? (unsigned)half * kMlaHalf + 64u * i : (unsigned)(1u - half) * kMlaHalf + 64u * (i - 4)));
-                uint4 v[8];
+            for (int batch = 0; batch < kPairQTmemCols / 96; ++batch) {
+                uint4 v[3][8];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) v[c] = src[c];
-                uint32_t words[32];
+                for (int g = 0; g < 3; ++g) {
+                    const int i = 3 * batch + g;
+                    const unsigned short *group =
+                        row0 + (i < 4 ? (unsigned)half * kMlaHalf + 64u * i : (unsigned)(1u - half) * kMlaHalf + 64u * (i - 4));
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    words[4 * c] = v[c].x;
-                    words[4 * c + 1] = v[c].y;
-                    words[4 * c + 2] = v[c].z;
-                    words[4 * c + 3] = v[c].w;
+                    for (int c = 0; c < 8; ++c)
+                        v[g][c] = *reinterpret_cast<const uint4 *>(group + (4u * c + piece_row) * kMlaWidth + piece * 8u);
                 }
-                tmem_st32(tmem_q + lane_base + 32 * i, words);
+#pragma unroll
+                for (int g = 0; g < 3; ++g) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const unsigned int r = 4u * c + piece_row;
+                        *reinterpret_cast<uint4 *>(turn + r * 128u + ((piece ^ (r & 7u)) * 16u)) = v[g][c];
+                    }
+                    __syncwarp();
+                    uint32_t words[32];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(turn + lane * 128u + (((unsigned)c ^ (lane & 7u)) * 16u));
+                        words[4 * c] = w.x;
+                        words[4 * c + 1] = w.y;
+                        words[4 * c + 2] = w.z;
+                        words[4 * c + 3] = w.w;
+                    }
+                    __syncwarp();
+                    tmem_st32(tmem_q + lane_base + 32 * (3 * batch + g), words);
+                }
             }
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(&bars->q_tmem_full);
+            MLA_MARK(1);
         }
         const float sscale = p.scale * 1.4426950408889634f;
-        float m_used = -INFINITY, l = 0.0f;
+        // m_used: the maximum this CTA's weights are scaled with (and its l); m_o: the scale its accumulator carries
+        float m_used = -INFINITY, l = 0.0f, m_o = -INFINITY, m_heard = -INFINITY;
         bool ok = true;
-        // the two warps of a quadrant meet on a barrier whose wait is bounded like every other
-        unsigned int meetings = 0;
-        auto meet = [&]() -> bool {
-            mbar_arrive(&bars->halves[quadrant]);
-            return pair_wait(&bars->halves[quadrant], meetings++ & 1u, abort);
-        };
-        // O columns of this thread's side are rescaled when the row maximum grows
         auto rescale = [&](float factor) {
 #pragma unroll 1
-            for (int i = 0; i < kMlaHalf / 64; ++i) {
+            for (int i = 0; i < kMlaHalf / 32; ++i) {
                 uint32_t o[32];
-                const uint32_t column = tmem_o + lane_base + 128u * side + 32u * i;
+                const uint32_t column = tmem_o + lane_base + 32u * i;
                 tmem_ld32(column, o);
                 tmem_wait_ld();
 #pragma unroll
@@ -1000,9 +1022,6 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             }
             tmem_wait_st();
         };
-        // m_used: the maximum this CTA's weights are scaled with (and its l); m_o: the scale the
-        // accumulator carries, a function of the tiles' scales in tile order and so the same in both CTAs
-        float m_o = -INFINITY;
         // Lets the tensor pipe run P(j) V(j): first brings the accumulator to the scale the weights of
         // tile j were computed with (up or down; rare), in tile order, after every earlier P V has landed.
         auto release = [&](unsigned int j, float m_p, uint64_t *go) -> bool {
@@ -1021,7 +1040,6 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             return true;
         };
         // The peer's message for its tile j: its weights are in place, its maxima in m_box.
-        float m_heard = -INFINITY;
         auto receive = [&](unsigned int j) -> bool {
             const unsigned int ip = j >> 1;
             MLA_TRACE_BEGIN(w4);
@@ -1031,7 +1049,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             if (warp == 0 && lane == 0 && ip + 1u < peer_tiles)   // the next message may be counted from now on
                 mbar_expect_tx(&bars->p_peer_full, kPairPBytes + kMlaHeads * 4);
             const float m_in = m_box[head];
-            m_heard = m_in;     // adopted by the caller at a fixed point of its program (results must not depend on timing)
+            m_heard = m_in;     // adopted at a fixed point of the program (results must not depend on timing)
             const bool fine = release(j, m_in, &bars->peer_ready);
             MLA_TRACE_ADD(5, w5);
             return fine;
@@ -1047,64 +1065,57 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     break;
                 }
                 MLA_TRACE_ADD(0, w0);
+                if (i == 0) MLA_MARK(2);
+                if (i == 1) MLA_MARK(3);
                 MLA_TRACE_BEGIN(w1);
                 tc_fence_after_sync();
-                uint32_t s[32];
-                tmem_ld32(tmem_s + lane_base + 32u * side, s);
+                uint32_t s[2][32];
+                tmem_ld32(tmem_s + lane_base, s[0]);
+                tmem_ld32(tmem_s + lane_base + 32u, s[1]);
                 tmem_wait_ld();
                 tc_fence_before_sync();
                 mbar_arrive(&bars->s_free);
-                const unsigned int k0 = t0 + j * kMlaN + 32u * side;
-                if (k0 + 32u > t1) {
+                const unsigned int k0 = t0 + j * kMlaN;
+                if (k0 + kMlaN > t1) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (k0 + c >= t1) s[c] = 0xff800000u;  // -inf
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (k0 + 32 * h + c >= t1) s[h][c] = 0xff800000u;  // -inf
                 }
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int c = 0; c < 32; c += 2)
-                    mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
                 // Has the peer's message for the tile in front of this one arrived already? Then it is
                 // processed now (its P V can run, and the peer gets its buffer back, while this tile's
-                // exponentials are computed); otherwise after this tile's weights are out. The two warps
-                // of a quadrant must take the same turn (they share a row's maximum): the first decides.
-                int *early = reinterpret_cast<int *>(m_out + kMlaHeads) + quadrant;
-                if (side == 0u) {
-                    const int arrived = j > 0 && __shfl_sync(0xffffffffu, (int)mbar_test(&bars->p_peer_full, ((j - 1u) >> 1) & 1u), 0);
-                    if (lane == 0) *early = arrived;
-                }
-                if (!meet()) {   // (also: the partner has read the previous maximum)
-                    ok = false;
-                    break;
-                }
-                received_early = j > 0 && *early != 0;
+                // exponentials are computed); otherwise after this tile's weights are out.
+                received_early = j > 0 && __shfl_sync(0xffffffffu, (int)mbar_test(&bars->p_peer_full, ((j - 1u) >> 1) & 1u), 0) != 0;
                 if (received_early && !receive(j - 1u)) {
                     ok = false;
                     break;
                 }
-                exchange[side * kMlaHeads + head] = max3(mx[0], mx[1], fmaxf(mx[2], mx[3]));
-                if (!meet()) {
-                    ok = false;
-                    break;
-                }
-                const float row_max = fmaxf(exchange[head], exchange[kMlaHeads + head]);
-                const float m_tile = row_max * sscale;
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2)
+                        mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[h][c]), __uint_as_float(s[h][c + 1]));
+                const float m_tile = max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * sscale;
                 if (m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY) {
                     const float m_new = fmaxf(m_used, m_tile);
                     l *= m_new == -INFINITY || m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
                     m_used = m_new;
                 }
                 const float offset = m_used == -INFINITY ? 0.0f : -m_used;
-                uint32_t packed[16];
+                uint32_t packed[32];
                 float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float p0 = exp2_approx(fmaf(__uint_as_float(s[c]), sscale, offset));
-                    const float p1 = exp2_approx(fmaf(__uint_as_float(s[c + 1]), sscale, offset));
-                    sum0 += p0;
-                    sum1 += p1;
-                    packed[c >> 1] = pack_bf16(p0, p1);
-                }
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        const float p0 = exp2_approx(fmaf(__uint_as_float(s[h][c]), sscale, offset));
+                        const float p1 = exp2_approx(fmaf(__uint_as_float(s[h][c + 1]), sscale, offset));
+                        sum0 += p0;
+                        sum1 += p1;
+                        packed[16 * h + (c >> 1)] = pack_bf16(p0, p1);
+                    }
                 l += sum0 + sum1;
                 MLA_TRACE_ADD(1, w1);
                 MLA_TRACE_BEGIN(w2);
@@ -1116,14 +1127,14 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 }
                 MLA_TRACE_ADD(2, w2);
                 MLA_TRACE_BEGIN(w3);
-                // row `head`, 16-byte chunks 4 * side .. 4 * side + 3 of its 128 bytes, under the 128-byte swizzle
+                // row `head`: its eight 16-byte chunks under the 128-byte swizzle
                 {
                     unsigned char *mine = smem + kPairOffPOwn + head * 128u;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<uint4 *>(mine + ((4u * side + c) ^ (head & 7u)) * 16u) =
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4 *>(mine + ((unsigned)c ^ (head & 7u)) * 16u) =
                             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-                    if (side == 0u) m_out[head] = m_used;
+                    m_out[head] = m_used;
                 }
                 fence_proxy_async();   // the tensor pipe and the bulk copy read these bytes through the async proxy
                 __syncwarp();
@@ -1150,60 +1161,75 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             yvx_mla_trace[7] = tiles;
         }
 #endif
+        MLA_MARK(4);
         if (ok) ok = pair_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
+        MLA_MARK(5);
         if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up();
         // this CTA's share of the denominators, and the maximum it is relative to, go to the peer
-        cluster_store_f32(cluster_map(smem_u32(l_box + side * kMlaHeads + head), peer), l);
-        if (side == 0u) cluster_store_f32(cluster_map(smem_u32(m_box + kMlaHeads + head), peer), m_used);
+        cluster_store_f32(cluster_map(smem_u32(l_box + head), peer), l);
+        cluster_store_f32(cluster_map(smem_u32(m_box + kMlaHeads + head), peer), m_used);
         pdl_launch_dependents();
         // (the cluster barrier below is reached by every thread of both CTAs)
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        bool fine = ok && !*abort && meet();
-        if (fine) {
-            tc_fence_after_sync();
-            // the row's denominator: both sides of both CTAs
-            // both shares at the accumulator's scale
-            const float m_theirs = m_box[kMlaHeads + head];
-            const float mine_scaled = m_used == -INFINITY ? 0.0f : l * exp2_approx(m_used - m_o);
-            const float theirs_scaled = m_theirs == -INFINITY ? 0.0f : l_box[side * kMlaHeads + head] * exp2_approx(m_theirs - m_o);
-            exchange[side * kMlaHeads + head] = mine_scaled + theirs_scaled;
-            fine = meet();
-        }
+        bool fine = ok && !*abort;
+        MLA_MARK(6);
         float *staged = reinterpret_cast<float *>(smem);
         if (fine) {
-            l = exchange[head] + exchange[kMlaHeads + head];
+            tc_fence_after_sync();
+            // the row's denominator: both CTAs' shares at the accumulator's scale
+            const float m_theirs = m_box[kMlaHeads + head];
+            const float mine_scaled = m_used == -INFINITY ? 0.0f : l * exp2_approx(m_used - m_o);
+            const float theirs_scaled = m_theirs == -INFINITY ? 0.0f : l_box[head] * exp2_approx(m_theirs - m_o);
+            l = mine_scaled + theirs_scaled;
             const float inverse = l > 0.0f ? 1.0f / l : 0.0f;
             // every tile has been consumed: the tile buffers are free for the turn of the rows
-            float *mine = staged + head * (unsigned)part_stride + 128u * side;
+            float *mine = staged + head * (unsigned)part_stride;
 #pragma unroll 1
-            for (int i = 0; i < kMlaHalf / 64; ++i) {
+            for (int i = 0; i < kMlaHalf / 32; ++i) {
                 uint32_t o[32];
-                tmem_ld32(tmem_o + lane_base + 128u * side + 32 * i, o);
+                tmem_ld32(tmem_o + lane_base + 32 * i, o);
                 tmem_wait_ld();
 #pragma unroll
                 for (int c = 0; c < 32; c += 2)
                     *reinterpret_cast<float2 *>(mine + 32 * i + c) =
                         make_float2(__uint_as_float(o[c]) * inverse, __uint_as_float(o[c + 1]) * inverse);
             }
-            if (side == 1u)
-                *reinterpret_cast<float2 *>(staged + head * (unsigned)part_stride + kMlaHalf) =
-                    make_float2(m_o == -INFINITY ? -INFINITY : m_o * 0.6931471805599453f, l);
+            *reinterpret_cast<float2 *>(mine + kMlaHalf) =
+                make_float2(m_o == -INFINITY ? -INFINITY : m_o * 0.6931471805599453f, l);
             mbar_arrive(&bars->rows_staged);
+            MLA_MARK(8);
             fine = pair_wait(&bars->rows_staged, 0, abort);
+            MLA_MARK(9);
         }
         if (fine) {
-            const unsigned int writer = side * 4u + quadrant;
-            for (unsigned int r = writer; r < (unsigned)kMlaHeads; r += 8u) {
-                float2 *dst = reinterpret_cast<float2 *>(
-                    p.partials +
-                    ((((unsigned long long)b * kMlaHeads + r) * 2ull + half) * p.max_splits + split) * part_stride);
-                const float2 *src = reinterpret_cast<const float2 *>(staged + r * (unsigned)part_stride);
-                for (unsigned int k = lane; k < (unsigned)part_stride / 2u; k += 32u) dst[k] = src[k];
+            // four rows at a time, all of their loads from shared memory ahead of the stores (a row is 129
+            // 8-byte words: four full sweeps of the warp and one word)
+            constexpr unsigned int kRowWords = (unsigned)(kMlaHalf + 2) / 2u;
+#pragma unroll 1
+            for (unsigned int r0 = warp * 32u; r0 < warp * 32u + 32u; r0 += 4u) {
+                float2 v[4][5];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 *src = reinterpret_cast<const float2 *>(staged + (r0 + q) * (unsigned)part_stride);
+#pragma unroll
+                    for (int u = 0; u < 5; ++u)
+                        if (lane + 32u * u < kRowWords) v[q][u] = src[lane + 32u * u];
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float2 *dst = reinterpret_cast<float2 *>(
+                        p.partials +
+                        ((((unsigned long long)b * kMlaHeads + r0 + q) * 2ull + half) * p.max_splits + split) * part_stride);
+#pragma unroll
+                    for (int u = 0; u < 5; ++u)
+                        if (lane + 32u * u < kRowWords) dst[lane + 32u * u] = v[q][u];
+                }
             }
         }
+        MLA_MARK(7);
     }
-    if (warp == 4 || warp == 5 || warp >= 10u) {
+    if (warp >= 4u) {
         // the producer, sender and issuer warps meet the softmax warps at the cluster barrier
         __syncwarp();
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -1297,6 +1323,10 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
 int yvx_cuda_mla_trace_read(unsigned long long out[16])
 {
     return cudaMemcpyFromSymbol(out, yvx::yvx_mla_trace, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
+}
+int yvx_cuda_mla_marks_read(unsigned long long out[16])
+{
+    return cudaMemcpyFromSymbol(out, yvx::yvx_mla_marks, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
 }
 #endif
 
