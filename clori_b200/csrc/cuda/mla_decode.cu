@@ -582,7 +582,7 @@ mla_decode_tcgen05_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMa
 // a CTA processes the peer's message for tile j - 1 (adopting its maximum, rescaling O and l if
 // it grew) before it computes the weights of tile j. Every wait is bounded and gives up at once
 // when either CTA has recorded a failure; both CTAs always reach the cluster barrier at the end.
-constexpr int kPairThreads = 288;   // 4 softmax warps (0-3), three TMA warps (4, 6, 7), the MMA warp (5), the sender (8)
+constexpr int kPairThreads = 320;   // 4 softmax warps (0-3), three TMA warps (4, 6, 7), two MMA warps (5: scores, 9: P V), the sender (8)
 constexpr int kPairQSmemSubs = 3, kPairQTmemCols = 192;
 constexpr int kPairOffQ = 0;
 constexpr int kPairOffKa = kPairQSmemSubs * kMlaQSubBytes;            // 49152
@@ -829,126 +829,109 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 mbar_arrive(&bars->p_own_sent);
             }
         }
-    } else if (warp == 5) {
-        // ------------------------------ MMA issuer ------------------------------
+    } else if (warp == 5 || warp == 9) {
+        // ------------------------------ MMA issuers ------------------------------
+        // Two warps, one for the score products and one for the P V products: each blocks on its own operands
+        // and the tensor pipe takes whatever either has issued, so neither kind of product waits behind a wait
+        // for the other's operands. (Products of one kind stay in one thread, hence in order; what orders the
+        // two kinds against each other are the barriers: P V of an own tile follows that tile's scores through
+        // the softmax, so its commit also tells that the score product has left the tile's own-half part.)
         constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
         constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
         constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
         const uint32_t elected = tc_elect_one() ? 1u : 0u;
-        const uint32_t peer_credit = cluster_map(smem_u32(&bars->p_peer_free), peer);
-        const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffQ), 16);
-        const uint32_t ka_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKa), 16);
         auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {    // every lane waits: the warp stays converged
             return __all_sync(0xffffffffu, pair_wait(bar, parity, abort)) != 0;
         };
-        // P V of tile j, once its weights (and V) are there
-        auto pv = [&](unsigned int j) -> bool {
-            const unsigned int i = j >> 1;
-            const bool own = (j & 1u) == half;
-            MLA_TRACE_BEGIN(tw);
-            if (own ? !wait_all(&bars->p_own_full, i & 1u)
-                    : !(wait_all(&bars->peer_ready, i & 1u) && wait_all(&bars->vp_full, i & 1u)))
-                return false;
-            MLA_TRACE_ADD(4, tw);
-            MLA_TRACE_BEGIN(tpv);
-            tc_fence_after_sync();
-            const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
-            const uint32_t v_lo = smem_desc_sw128_lo(
-                smem_u32(smem + (own ? kPairOffKb + (i & 1u) * kMlaVPartBytes : kPairOffVp)), kMlaKvSubBytes);
+        bool ok = true;
+        if (warp == 9) {
+            const uint32_t peer_credit = cluster_map(smem_u32(&bars->p_peer_free), peer);
+            // P V of tile j, once its weights (and V) are there, in tile order
+            for (unsigned int j = 0; ok && j < tiles; ++j) {
+                const unsigned int i = j >> 1;
+                const bool own = (j & 1u) == half;
+                MLA_TRACE_BEGIN(tw);
+                ok = own ? wait_all(&bars->p_own_full, i & 1u)
+                         : (wait_all(&bars->peer_ready, i & 1u) && wait_all(&bars->vp_full, i & 1u));
+                if (!ok) break;
+                MLA_TRACE_ADD(4, tw);
+                MLA_TRACE_BEGIN(tpv);
+                tc_fence_after_sync();
+                const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
+                const uint32_t v_lo = smem_desc_sw128_lo(
+                    smem_u32(smem + (own ? kPairOffKb + (i & 1u) * kMlaVPartBytes : kPairOffVp)), kMlaKvSubBytes);
 #pragma unroll
-            for (int kk = 0; kk < kMlaN / 16; ++kk)
-                tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
-                               (j || kk) ? 1u : 0u);
-            if (own) {
-                tc_commit_pred(elected, &bars->kb_done[i & 1u]);
-                tc_commit_pred(elected, &bars->pv_own_done);
-            } else {
-                tc_commit_pred(elected, &bars->pvp_done);
-                // ... and tells the peer at once that the weights it sent are consumed
-                asm volatile(
-                    "{\n\t.reg .pred pe;\n\t"
-                    "setp.ne.b32 pe, %0, 0;\n\t"
-                    "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
-                    ::"r"(elected), "r"(peer_credit)
-                    : "memory");
+                for (int kk = 0; kk < kMlaN / 16; ++kk)
+                    tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
+                                   (j || kk) ? 1u : 0u);
+                if (own) {
+                    tc_commit_pred(elected, &bars->kb_done[i & 1u]);
+                    tc_commit_pred(elected, &bars->pv_own_done);
+                } else {
+                    tc_commit_pred(elected, &bars->pvp_done);
+                    // ... and tells the peer at once that the weights it sent are consumed
+                    asm volatile(
+                        "{\n\t.reg .pred pe;\n\t"
+                        "setp.ne.b32 pe, %0, 0;\n\t"
+                        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+                        ::"r"(elected), "r"(peer_credit)
+                        : "memory");
+                }
+                tc_commit_pred(elected, &bars->pv_done);
+                MLA_TRACE_ADD(1, tpv);
             }
-            tc_commit_pred(elected, &bars->pv_done);
-            MLA_TRACE_ADD(1, tpv);
-            return true;
-        };
-        // the score product of own tile i: 8 + 12 k-steps over the scores-only part, 16 over the own half
-        unsigned int next_pv = 0;
-        // one look (by the issuing lane; the warp follows) at whether the next tile's P V could run now
-        auto pv_could_run = [&](unsigned int limit) -> bool {
-            int there = 0;
-            if (elected && next_pv < limit) {
-                const unsigned int k = next_pv >> 1;
-                there = (next_pv & 1u) == half ? mbar_test(&bars->p_own_full, k & 1u)
-                                               : (mbar_test(&bars->peer_ready, k & 1u) && mbar_test(&bars->vp_full, k & 1u));
+        } else {
+            const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffQ), 16);
+            const uint32_t ka_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKa), 16);
+            ok = wait_all(&bars->q_full, 0) && wait_all(&bars->q_tmem_full, 0);
+            // the score product of own tile i: 8 + 12 k-steps over the scores-only part, 16 over the own half
+            for (unsigned int i = 0; ok && i < own_tiles; ++i) {
+                MLA_TRACE_BEGIN(tw);
+                if (!(ok = wait_all(&bars->ka_full, i & 1u))) break;
+                MLA_TRACE_ADD(5, tw);
+                MLA_TRACE_BEGIN(tw3);
+                // the score buffer is free once the softmax has read the previous own tile out of it
+                if (i > 0u && !(ok = wait_all(&bars->s_free, (i - 1u) & 1u))) break;
+                MLA_TRACE_ADD(7, tw3);
+                MLA_TRACE_BEGIN(tqa);
+                tc_fence_after_sync();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)      // query dims in tensor memory (first two sub-tiles of the other half)
+                    tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
+                                   ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, ks ? 1u : 0u);
+#pragma unroll
+                for (int ks = 0; ks < 12; ++ks)     // query dims in shared memory (its last two sub-tiles, then the rope dims)
+                    tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
+                                   ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+                tc_commit_pred(elected, &bars->ka_done);
+                MLA_TRACE_ADD(2, tqa);
+                MLA_TRACE_BEGIN(tw2);
+                if (!(ok = wait_all(&bars->kb_full[i & 1u], (i >> 1) & 1u))) break;
+                MLA_TRACE_ADD(6, tw2);
+                MLA_TRACE_BEGIN(tqb);
+                tc_fence_after_sync();
+                const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
+#pragma unroll
+                for (int ks = 0; ks < 16; ++ks)
+                    tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
+                                   kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+                tc_commit_pred(elected, &bars->s_full);
+                MLA_TRACE_ADD(3, tqb);
             }
-            return __any_sync(0xffffffffu, there) != 0;
-        };
-        auto scores = [&](unsigned int i, unsigned int pv_limit) -> bool {
-            MLA_TRACE_BEGIN(tw);
-            // the score buffer is free once the softmax has read the previous own tile out of it
-            if (!wait_all(&bars->ka_full, i & 1u)) return false;
-            MLA_TRACE_ADD(5, tw);
-            MLA_TRACE_BEGIN(tw3);
-            if (i > 0u && !wait_all(&bars->s_free, (i - 1u) & 1u)) return false;
-            MLA_TRACE_ADD(7, tw3);
-            MLA_TRACE_BEGIN(tqa);
-            tc_fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)      // query dims in tensor memory (first two sub-tiles of the other half)
-                tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
-                               ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, ks ? 1u : 0u);
-#pragma unroll
-            for (int ks = 0; ks < 12; ++ks)     // query dims in shared memory (its last two sub-tiles, then the rope dims)
-                tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
-                               ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
-            tc_commit_pred(elected, &bars->ka_done);
-            MLA_TRACE_ADD(2, tqa);
-            // between the two parts (the own-half part may still be landing): a P V that is ready
-            if (pv_could_run(pv_limit) && !pv(next_pv++)) return false;
-            MLA_TRACE_BEGIN(tw2);
-            if (!wait_all(&bars->kb_full[i & 1u], (i >> 1) & 1u)) return false;
-            MLA_TRACE_ADD(6, tw2);
-            MLA_TRACE_BEGIN(tqb);
-            tc_fence_after_sync();
-            const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
-#pragma unroll
-            for (int ks = 0; ks < 16; ++ks)
-                tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
-                               kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
-            tc_commit_pred(elected, &bars->s_full);
-            MLA_TRACE_ADD(3, tqb);
-            return true;
-        };
-        // A fixed program, every wait blocking (a look at a barrier costs this warp 160 cycles, and the
-        // tensor pipe idles while it looks): the score product of the NEXT own tile runs under the softmax
-        // of the current one.
-        bool ok = wait_all(&bars->q_full, 0) && wait_all(&bars->q_tmem_full, 0);
-        if (ok && own_tiles) ok = scores(0, 0);
-        for (unsigned int i = 0; ok && i < own_tiles; ++i) {
-            // the score product of own tile i + 1 (with the peer's tile in front of own tile i between its
-            // parts if that is ready), then the P V products up to own tile i
-            const unsigned int own = 2u * i + half;
-            if (i + 1u < own_tiles) ok = scores(i + 1u, own);
-            for (; ok && next_pv <= own; ++next_pv) ok = pv(next_pv);
         }
-        for (; ok && next_pv < tiles; ++next_pv) ok = pv(next_pv);
         if (!ok && lane == 0) give_up();
 #ifdef YVX_MLA_TRACE
-        if (traced) {
-            yvx_mla_trace[8] = trace_local[0];
+        if (traced && warp == 5) {
             yvx_mla_trace[9] = (unsigned long long)(clock64() - trace_start);
-            yvx_mla_trace[10] = trace_local[1];
             yvx_mla_trace[11] = trace_local[2];
             yvx_mla_trace[12] = trace_local[3];
-            yvx_mla_trace[13] = trace_local[4];
             yvx_mla_trace[14] = trace_local[5];
             yvx_mla_trace[15] = trace_local[7];
             yvx_mla_trace[8] = trace_local[6];
+        }
+        if (traced && warp == 9) {
+            yvx_mla_trace[10] = trace_local[1];
+            yvx_mla_trace[13] = trace_local[4];
         }
 #endif
     } else {

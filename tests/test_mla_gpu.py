@@ -16,7 +16,7 @@ from clori_b200 import abi, workloads
 pytestmark = pytest.mark.gpu
 
 
-def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale):
+def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale, chunk=None):
     lib = backend.lib
     sessions, heads, nope = q_nope.shape
     cap, dc = latent.shape[1], latent.shape[2]
@@ -31,6 +31,8 @@ def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale):
     lens = backend.tensor("lens", np.asarray(lengths, np.int32))
     p.kv_tokens, p.kv_tokens_max = lens.data_ptr, cap
     lib.yvx_cuda_mla_plan(C.byref(p), backend.sm_count)
+    if chunk:   # more (and shorter) splits than the planner would choose
+        p.chunk_tokens, p.max_splits = chunk, (cap + chunk - 1) // chunk
     q_abs = backend.alloc("qabs", abi.DTYPE_BF16, (sessions, heads, dc + dr))
     parts = backend.alloc("parts", abi.DTYPE_F32, (1,), lib.yvx_cuda_mla_partials_bytes(C.byref(p)))
     out = backend.alloc("out", abi.DTYPE_F32, (sessions, heads, dc))
@@ -81,6 +83,25 @@ def test_mla_decode_matches_restatement(backend, oracle, sessions, context, form
     got = f(q_abs[:, :, :512]).astype(np.float64)
     assert np.all(np.abs(got - exact) <= 2.0 ** -8 * np.abs(exact) + 1e-6)
     assert np.array_equal(q_abs[:, :, 512:], qr)
+
+
+def test_mla_decode_folds_many_splits_of_ragged_sessions(backend, oracle, form):
+    """Six splits of 128 tokens, of which a session fills six, three or one (the rest write empty partial rows):
+    the fold of the partial rows gives the same bits every time."""
+    context = 700
+    qn, qr, w, lat, rk = workloads.mla_decode_bf16(seed=12, batch=3, context=context)
+    lengths = [context, 300, 64]
+    scale = 1.0 / np.sqrt(192.0)
+    out, _, status, _, plan = run_mla(backend, qn, qr, w, lat, rk, lengths, scale, chunk=128)
+    assert status == 0 and plan == (128, 6)
+    for _ in range(3):
+        again, _, status, _, _ = run_mla(backend, qn, qr, w, lat, rk, lengths, scale, chunk=128)
+        assert status == 0 and np.array_equal(again.view(np.uint32), out.view(np.uint32))
+    for s in range(3):
+        n = lengths[s]
+        ref = oracle.mla_decode(qn[s], qr[s], w, lat[s, :n], rk[s, :n], scale)
+        assert np.abs(out[s] - ref).max() <= 2e-3, float(np.abs(out[s] - ref).max())
+        assert cosine(out[s], ref) >= 0.9999
 
 
 @pytest.mark.parametrize("context", [64, 129, 1000, 2500])
