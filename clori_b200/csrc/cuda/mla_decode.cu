@@ -606,7 +606,8 @@ struct PairBarriers {
     uint64_t p_peer_free;                 // the peer has consumed the weights this CTA sent it
     uint64_t p_written, p_own_sent;       // an own tile's weights are written / have left for the peer
     uint64_t pv_done;                     // any P V
-    uint64_t halves[4], rows_staged;      // the two softmax warps of a quadrant meet; all rows are staged
+    uint64_t ka2_full, ka2_done;          // ... its second piece (two sub-tiles of the other half and the rope keys)
+    uint64_t rows_staged;                 // all rows of the result are staged
     uint32_t tmem_base;
     int abort;
     unsigned int written;                 // softmax warps that have written their part of an own tile's weights
@@ -732,7 +733,8 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         mbar_init(&bars->p_written, 4);
         mbar_init(&bars->p_own_sent, 1);
         mbar_init(&bars->pv_done, 1);
-        for (int i = 0; i < 4; ++i) mbar_init(&bars->halves[i], 64);
+        mbar_init(&bars->ka2_full, 1);
+        mbar_init(&bars->ka2_done, 1);
         mbar_init(&bars->rows_staged, kMlaHeads);
         bars->abort = 0;
         bars->written = 0u;
@@ -768,15 +770,24 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             tma_load_3d(smem + kPairOffQ + 2 * kMlaQSubBytes, &maps.query, &bars->q_full, kMlaLatent, 0, (int)b);
             for (unsigned int i = 0; i < own_tiles; ++i) {
                 const int token = (int)(t0 + (2u * i + half) * kMlaN);
+                // two pieces with their own barriers: the first is free again (and its reload under way) while
+                // the score product still reads the second
                 if (i > 0 && !pair_wait(&bars->ka_done, (i - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
                 unsigned char *dst = smem + kPairOffKa;
-                mbar_expect_tx(&bars->ka_full, kPairKaBytes);
-                for (int u = 0; u < 4; ++u)
+                mbar_expect_tx(&bars->ka_full, 2 * kMlaKvSubBytes);
+                for (int u = 0; u < 2; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka_full, 64 * (other0 + u), token, (int)b);
-                tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka_full, 0, token, (int)b);
+                if (i > 0 && !pair_wait(&bars->ka2_done, (i - 1u) & 1u, abort)) {
+                    give_up();
+                    break;
+                }
+                mbar_expect_tx(&bars->ka2_full, 3 * kMlaKvSubBytes);
+                for (int u = 2; u < 4; ++u)
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka2_full, 64 * (other0 + u), token, (int)b);
+                tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka2_full, 0, token, (int)b);
             }
         } else if (warp == 6 && lane == 0) {
             for (unsigned int i = 0; i < own_tiles; ++i) {
@@ -899,11 +910,14 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 for (int ks = 0; ks < 8; ++ks)      // query dims in tensor memory (first two sub-tiles of the other half)
                     tc_mma_ts_pred(elected, tmem_s, tmem_q + 128 + ks * 8,
                                    ka_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, ks ? 1u : 0u);
+                tc_commit_pred(elected, &bars->ka_done);
+                if (!(ok = wait_all(&bars->ka2_full, i & 1u))) break;
+                tc_fence_after_sync();
 #pragma unroll
                 for (int ks = 0; ks < 12; ++ks)     // query dims in shared memory (its last two sub-tiles, then the rope dims)
                     tc_mma_ss_pred(elected, tmem_s, q_lo + (((ks >> 2) * kMlaQSubBytes + (ks & 3) * 32) >> 4), desc_hi,
                                    ka_lo + ((((ks >> 2) + 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
-                tc_commit_pred(elected, &bars->ka_done);
+                tc_commit_pred(elected, &bars->ka2_done);
                 MLA_TRACE_ADD(2, tqa);
                 MLA_TRACE_BEGIN(tw2);
                 if (!(ok = wait_all(&bars->kb_full[i & 1u], (i >> 1) & 1u))) break;
