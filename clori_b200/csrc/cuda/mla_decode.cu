@@ -588,8 +588,8 @@ constexpr int kPairOffQ = 0;
 constexpr int kPairOffKa = kPairQSmemSubs * kMlaQSubBytes;            // 49152
 constexpr int kPairKaBytes = 5 * kMlaKvSubBytes;                       // 40960
 constexpr int kPairOffKb = kPairOffKa + kPairKaBytes;                  // 90112
-constexpr int kPairOffVp = kPairOffKb + 2 * kMlaVPartBytes;            // 155648
-constexpr int kPairOffPOwn = kPairOffVp + kMlaVPartBytes;              // 188416
+constexpr int kPairOffV = kPairOffKb + kMlaVPartBytes;                 // 122880: two own-half parts as V of P V
+constexpr int kPairOffPOwn = kPairOffV + 2 * kMlaVPartBytes;           // 188416
 constexpr int kPairPBytes = kMlaHeads * kMlaN * 2;                     // 16384
 constexpr int kPairOffPPeer = kPairOffPOwn + kPairPBytes;              // 204800
 constexpr int kPairOffTail = kPairOffPPeer + kPairPBytes;              // 221184
@@ -598,8 +598,8 @@ constexpr int kPairSmemBytes = kPairOffTail + 256 + 4 * 1024 + 1024;   // barrie
 struct PairBarriers {
     uint64_t q_full, q_tmem_full;
     uint64_t ka_full, ka_done;            // scores-only part of an own tile: loaded / free again
-    uint64_t kb_full[2], kb_done[2];      // own-half part of an own tile
-    uint64_t vp_full, pvp_done;           // own-half part of a peer tile: loaded / its P V has run
+    uint64_t kb_full, kb_done;            // own-half part of an own tile, as K of its score product
+    uint64_t v_full[2], v_done[2];        // own-half part of ANY tile, as V of its P V (two slots, tile parity)
     uint64_t s_full, s_free;              // scores computed / read out of tensor memory
     uint64_t p_own_full, pv_own_done;     // weights of an own tile written / consumed
     uint64_t p_peer_full, peer_ready;     // the peer's weights have arrived / its message is processed
@@ -717,12 +717,12 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         mbar_init(&bars->q_tmem_full, kMlaHeads);
         mbar_init(&bars->ka_full, 1);
         mbar_init(&bars->ka_done, 1);
+        mbar_init(&bars->kb_full, 1);
+        mbar_init(&bars->kb_done, 1);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&bars->kb_full[i], 1);
-            mbar_init(&bars->kb_done[i], 1);
+            mbar_init(&bars->v_full[i], 1);
+            mbar_init(&bars->v_done[i], 1);
         }
-        mbar_init(&bars->vp_full, 1);
-        mbar_init(&bars->pvp_done, 1);
         mbar_init(&bars->s_full, 1);
         mbar_init(&bars->s_free, kMlaHeads);
         mbar_init(&bars->p_own_full, 4);
@@ -790,29 +790,34 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka2_full, 0, token, (int)b);
             }
         } else if (warp == 6 && lane == 0) {
+            // the own-half part of an own tile as K: one buffer, free again when the score product has read it
             for (unsigned int i = 0; i < own_tiles; ++i) {
-                const unsigned int buffer = i & 1u;
                 const int token = (int)(t0 + (2u * i + half) * kMlaN);
-                if (i >= 2u && !pair_wait(&bars->kb_done[buffer], ((i >> 1) - 1u) & 1u, abort)) {
+                if (i > 0 && !pair_wait(&bars->kb_done, (i - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
-                unsigned char *dst = smem + kPairOffKb + buffer * kMlaVPartBytes;
-                mbar_expect_tx(&bars->kb_full[buffer], kMlaVPartBytes);
+                unsigned char *dst = smem + kPairOffKb;
+                mbar_expect_tx(&bars->kb_full, kMlaVPartBytes);
                 for (int u = 0; u < 4; ++u)
-                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full[buffer], 64 * (own0 + u), token, (int)b);
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->kb_full, 64 * (own0 + u), token, (int)b);
             }
         } else if (warp == 7 && lane == 0) {
-            for (unsigned int i = 0; i < peer_tiles; ++i) {
-                const int token = (int)(t0 + (2u * i + peer) * kMlaN);
-                if (i > 0 && !pair_wait(&bars->pvp_done, (i - 1u) & 1u, abort)) {
+            // the own-half part of EVERY tile as V, two slots: asked for (out of L2, where the score product's
+            // load of the tile, this CTA's or the peer's, has just brought it) a whole tile pair ahead of its
+            // P V. Holding the K copy of an own tile until its P V instead kept that buffer for one and a half
+            // periods, and the score product of the tile after next waited for it.
+            for (unsigned int j = 0; j < tiles; ++j) {
+                const unsigned int slot = j & 1u;
+                const int token = (int)(t0 + j * kMlaN);
+                if (j >= 2u && !pair_wait(&bars->v_done[slot], ((j >> 1) - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
-                unsigned char *dst = smem + kPairOffVp;
-                mbar_expect_tx(&bars->vp_full, kMlaVPartBytes);
+                unsigned char *dst = smem + kPairOffV + slot * kMlaVPartBytes;
+                mbar_expect_tx(&bars->v_full[slot], kMlaVPartBytes);
                 for (int u = 0; u < 4; ++u)
-                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->vp_full, 64 * (own0 + u), token, (int)b);
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->v_full[slot], 64 * (own0 + u), token, (int)b);
             }
         }
     } else if (warp == 8) {
@@ -844,9 +849,8 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         // ------------------------------ MMA issuers ------------------------------
         // Two warps, one for the score products and one for the P V products: each blocks on its own operands
         // and the tensor pipe takes whatever either has issued, so neither kind of product waits behind a wait
-        // for the other's operands. (Products of one kind stay in one thread, hence in order; what orders the
-        // two kinds against each other are the barriers: P V of an own tile follows that tile's scores through
-        // the softmax, so its commit also tells that the score product has left the tile's own-half part.)
+        // for the other's operands. (Products of one kind stay in one thread, hence in order; the two kinds
+        // share no buffer: the score product reads the K copy of a tile's own-half part, P V its V copy.)
         constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
         constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kMlaHalf, true);
         constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
@@ -862,24 +866,21 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 const unsigned int i = j >> 1;
                 const bool own = (j & 1u) == half;
                 MLA_TRACE_BEGIN(tw);
-                ok = own ? wait_all(&bars->p_own_full, i & 1u)
-                         : (wait_all(&bars->peer_ready, i & 1u) && wait_all(&bars->vp_full, i & 1u));
+                ok = wait_all(own ? &bars->p_own_full : &bars->peer_ready, i & 1u) && wait_all(&bars->v_full[j & 1u], i & 1u);
                 if (!ok) break;
                 MLA_TRACE_ADD(4, tw);
                 MLA_TRACE_BEGIN(tpv);
                 tc_fence_after_sync();
                 const uint32_t p_lo = smem_desc_sw128_lo(smem_u32(smem + (own ? kPairOffPOwn : kPairOffPPeer)), 16);
-                const uint32_t v_lo = smem_desc_sw128_lo(
-                    smem_u32(smem + (own ? kPairOffKb + (i & 1u) * kMlaVPartBytes : kPairOffVp)), kMlaKvSubBytes);
+                const uint32_t v_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffV + (j & 1u) * kMlaVPartBytes), kMlaKvSubBytes);
 #pragma unroll
                 for (int kk = 0; kk < kMlaN / 16; ++kk)
                     tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
                                    (j || kk) ? 1u : 0u);
+                tc_commit_pred(elected, &bars->v_done[j & 1u]);
                 if (own) {
-                    tc_commit_pred(elected, &bars->kb_done[i & 1u]);
                     tc_commit_pred(elected, &bars->pv_own_done);
                 } else {
-                    tc_commit_pred(elected, &bars->pvp_done);
                     // ... and tells the peer at once that the weights it sent are consumed
                     asm volatile(
                         "{\n\t.reg .pred pe;\n\t"
@@ -920,15 +921,16 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 tc_commit_pred(elected, &bars->ka2_done);
                 MLA_TRACE_ADD(2, tqa);
                 MLA_TRACE_BEGIN(tw2);
-                if (!(ok = wait_all(&bars->kb_full[i & 1u], (i >> 1) & 1u))) break;
+                if (!(ok = wait_all(&bars->kb_full, i & 1u))) break;
                 MLA_TRACE_ADD(6, tw2);
                 MLA_TRACE_BEGIN(tqb);
                 tc_fence_after_sync();
-                const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb + (i & 1u) * kMlaVPartBytes), 16);
+                const uint32_t kb_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKb), 16);
 #pragma unroll
                 for (int ks = 0; ks < 16; ++ks)
                     tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
                                    kb_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, 1u);
+                tc_commit_pred(elected, &bars->kb_done);
                 tc_commit_pred(elected, &bars->s_full);
                 MLA_TRACE_ADD(3, tqb);
             }
