@@ -49,6 +49,7 @@ constexpr float kMlaRescaleThreshold = 8.0f;
 // Cycle counters of CTA (0, 0, 0), a development aid compiled out of the library.
 __device__ unsigned long long yvx_mla_trace[16];
 __device__ unsigned long long yvx_mla_marks[16];
+__device__ unsigned long long yvx_mla_spans[1024];
 #define MLA_MARK(slot) do { if (traced && warp == 0) yvx_mla_marks[slot] = (unsigned long long)(clock64() - trace_start); } while (0)
 #define MLA_TRACE_BEGIN(t) const long long t = clock64()
 #define MLA_TRACE_ADD(slot, t) \
@@ -610,8 +611,9 @@ struct PairBarriers {
     uint64_t rows_staged;                 // all rows of the result are staged
     uint32_t tmem_base;
     int abort;
-    unsigned int written;                 // softmax warps that have written their part of an own tile's weights
 };
+constexpr unsigned int kPairBarrierCount = 23u;   // the 64-bit barrier words above, from q_full on
+static_assert(offsetof(PairBarriers, tmem_base) == kPairBarrierCount * 8u, "barrier count out of step");
 static_assert(sizeof(PairBarriers) <= 256, "barrier block outgrew its shared-memory slot");
 
 __device__ __forceinline__ uint32_t cluster_map(uint32_t local_address, uint32_t rank)
@@ -670,6 +672,52 @@ __device__ __forceinline__ bool pair_wait(uint64_t *bar, uint32_t parity, const 
     return false;
 }
 
+// ---- the balanced plan (uniform lengths) --------------------------------------------------------------------
+// The sessions' tiles are laid end to end with kMlaItemCostTiles cost units in front of each session (what a
+// work item costs besides its tiles: query staging, the first tile's latency, writing its partial rows), and
+// the pairs take equal runs of that cost line: pair k the units [k * total / pairs, (k + 1) * total / pairs).
+// What a run holds of a session's tiles is one work item; the items of a session are numbered from the pair
+// that holds its first tile, and that number is the item's partial slot.
+constexpr unsigned int kMlaItemCostTiles = 10u;
+
+struct MlaBalance {
+    unsigned long long total, unit;   // cost units: all sessions, one session
+    unsigned int pairs;
+};
+
+__host__ __device__ inline MlaBalance mla_balance(unsigned int sessions, unsigned int kv_tokens, unsigned int pairs)
+{
+    MlaBalance g;
+    g.unit = kMlaItemCostTiles + (kv_tokens + (unsigned)kMlaN - 1u) / (unsigned)kMlaN;
+    g.total = g.unit * sessions;
+    g.pairs = pairs;
+    return g;
+}
+
+__host__ __device__ inline unsigned long long mla_run_begin(const MlaBalance &g, unsigned long long k)
+{
+    return g.total * k / g.pairs;
+}
+
+// What pair k holds of session b: tiles [*tile_lo, *tile_hi), partial slot, whether it ends the session.
+__host__ __device__ inline bool mla_balanced_item(const MlaBalance &g, unsigned int k, unsigned int b,
+                                                  unsigned int *tile_lo, unsigned int *tile_hi,
+                                                  unsigned int *slot, bool *ends_session)
+{
+    const unsigned long long lo = mla_run_begin(g, k), hi = mla_run_begin(g, k + 1ull);
+    const unsigned long long seg_lo = g.unit * b + kMlaItemCostTiles, seg_hi = g.unit * (b + 1ull);
+    const unsigned long long a = lo > seg_lo ? lo : seg_lo, e = hi < seg_hi ? hi : seg_hi;
+    if (a >= e) return false;
+    unsigned long long first = seg_lo * g.pairs / g.total;       // the pair whose run holds the session's first tile
+    while (mla_run_begin(g, first + 1ull) <= seg_lo) ++first;
+    while (mla_run_begin(g, first) > seg_lo) --first;
+    *tile_lo = (unsigned int)(a - seg_lo);
+    *tile_hi = (unsigned int)(e - seg_lo);
+    *slot = k - (unsigned int)first;
+    *ends_session = hi >= seg_hi;
+    return true;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps maps)
 {
@@ -683,36 +731,85 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
     float *m_out = l_box + 2 * kMlaHeads;                                     // [128]: this CTA's maximum, source of the copy to the peer
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const unsigned int half = blockIdx.x, split = blockIdx.y, b = blockIdx.z;   // half == rank in the cluster
+    const unsigned int half = blockIdx.x;   // half == rank in the cluster
     const unsigned int peer = half ^ 1u;
 #ifdef YVX_MLA_TRACE
     const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
     unsigned long long trace_local[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     const long long trace_start = clock64();
-#endif
-    const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
-    const unsigned int t0 = split * p.chunk_tokens;
-    const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
-    const unsigned long long part_stride = kMlaHalf + 2;
-    if (t0 >= t1) {
-        // Nothing of this session falls into the split (true for both CTAs of the pair): an empty partial.
-        if (threadIdx.x < (unsigned)kMlaHeads) {
-            float *part = p.partials +
-                          ((((unsigned long long)b * kMlaHeads + threadIdx.x) * 2ull + half) * p.max_splits + split) *
-                              part_stride;
-            for (int d = 0; d < kMlaHalf; ++d) part[d] = 0.0f;
-            part[kMlaHalf] = -INFINITY;
-            part[kMlaHalf + 1] = 0.0f;
-        }
-        return;
+    const unsigned int span_index = (blockIdx.z * gridDim.y + blockIdx.y) * 2u + blockIdx.x;
+    if (threadIdx.x == 0 && span_index < 512u) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        yvx_mla_spans[2u * span_index] = (now << 10) | smid;
     }
+#endif
+    const unsigned long long part_stride = kMlaHalf + 2;
+    const bool balanced = p.balanced_pairs != 0u;
+    const MlaBalance balance = mla_balance(p.sessions, p.kv_tokens_uniform, balanced ? p.balanced_pairs : 1u);
+    if (!balanced) {
+        const unsigned int kv_tokens =
+            admitted_kv_tokens(p.kv_tokens, blockIdx.z, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
+        if (blockIdx.y * p.chunk_tokens >= kv_tokens) {
+            // Nothing of this session falls into the split (true for both CTAs of the pair): an empty partial.
+            if (threadIdx.x < (unsigned)kMlaHeads) {
+                float *part = p.partials + ((((unsigned long long)blockIdx.z * kMlaHeads + threadIdx.x) * 2ull + half) *
+                                                p.max_splits + blockIdx.y) * part_stride;
+                for (int d = 0; d < kMlaHalf; ++d) part[d] = 0.0f;
+                part[kMlaHalf] = -INFINITY;
+                part[kMlaHalf + 1] = 0.0f;
+            }
+            return;
+        }
+    }
+    volatile int *abort = &bars->abort;
+    if (threadIdx.x == 0) bars->abort = 0;
+    if (warp == 5) {
+        tmem_alloc(&bars->tmem_base, kMlaTmemColumns);
+        tmem_relinquish();
+    }
+    // The work items of this pair: one (its session and split) in the grid of sessions x splits; in the balanced
+    // plan what its run of the cost line holds of each session it touches, one after the other.
+    const unsigned int session_first =
+        balanced ? (unsigned int)(mla_run_begin(balance, blockIdx.y) / balance.unit) : blockIdx.z;
+    const unsigned int session_last =
+        balanced ? (unsigned int)min((unsigned long long)p.sessions - 1ull,
+                                     (mla_run_begin(balance, blockIdx.y + 1ull) + balance.unit - 1ull) / balance.unit)
+                 : blockIdx.z;
+    bool first_item = true;
+    for (unsigned int b = session_first; b <= session_last; ++b) {
+    unsigned int split = blockIdx.y, t0, t1;
+    bool ends_session = false;
+    if (balanced) {
+        unsigned int tile_lo, tile_hi;
+        if (!mla_balanced_item(balance, blockIdx.y, b, &tile_lo, &tile_hi, &split, &ends_session)) continue;
+        t0 = tile_lo * kMlaN;
+        t1 = min(p.kv_tokens_uniform, tile_hi * (unsigned)kMlaN);
+    } else {
+        const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
+        t0 = split * p.chunk_tokens;
+        t1 = min(kv_tokens, t0 + p.chunk_tokens);
+    }
+    if (!first_item) {
+        // The item before has ended at a cluster barrier with nothing pending on any barrier of either CTA
+        // (every role has waited for the last phase of what it alone would have left open).
+        __syncthreads();
+        if (*abort) break;
+    }
+    const bool run_ends_here =
+        !balanced || mla_run_begin(balance, blockIdx.y + 1ull) <= balance.unit * (b + 1ull) + kMlaItemCostTiles;
     const unsigned int tiles = (t1 - t0 + kMlaN - 1) / kMlaN;
     const unsigned int own_tiles = (tiles + 1u - half) / 2u;     // tiles j with j % 2 == half
     const unsigned int peer_tiles = tiles - own_tiles;
     const int own0 = 4 * (int)half, other0 = 4 * (1 - (int)half);
-    volatile int *abort = &bars->abort;
 
     if (threadIdx.x == 0) {
+        if (!first_item) {
+            uint64_t *all = &bars->q_full;
+            for (unsigned int i = 0; i < kPairBarrierCount; ++i) mbar_inval(all + i);
+        }
         mbar_init(&bars->q_full, 1);
         mbar_init(&bars->q_tmem_full, kMlaHeads);
         mbar_init(&bars->ka_full, 1);
@@ -736,16 +833,11 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         mbar_init(&bars->ka2_full, 1);
         mbar_init(&bars->ka2_done, 1);
         mbar_init(&bars->rows_staged, kMlaHeads);
-        bars->abort = 0;
-        bars->written = 0u;
         fence_barrier_init();
         // the first message of the peer: its weights and its maxima, counted in bytes
         if (peer_tiles) mbar_expect_tx(&bars->p_peer_full, kPairPBytes + kMlaHeads * 4);
     }
-    if (warp == 5) {
-        tmem_alloc(&bars->tmem_base, kMlaTmemColumns);
-        tmem_relinquish();
-    }
+    first_item = false;
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();          // the peer's barriers exist before anything arrives on them
@@ -788,6 +880,15 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 for (int u = 2; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka2_full, 64 * (other0 + u), token, (int)b);
                 tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka2_full, 0, token, (int)b);
+#ifdef YVX_MLA_PREFETCH_TILE
+                // the next own tile (64 whole rows, contiguous) is asked into L2 in one piece
+                if (i + YVX_MLA_PREFETCH_TILE < own_tiles && (unsigned)token + (2u * YVX_MLA_PREFETCH_TILE + 1u) * kMlaN <= p.kv_tokens_max) {
+                    const unsigned short *rows = reinterpret_cast<const unsigned short *>(p.latent) +
+                                                 (unsigned long long)b * p.latent_session_stride +
+                                                 (unsigned long long)(token + 2 * YVX_MLA_PREFETCH_TILE * kMlaN) * kMlaLatent;
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(rows), "r"(kMlaN * kMlaLatent * 2) : "memory");
+                }
+#endif
             }
         } else if (warp == 6 && lane == 0) {
             // the own-half part of an own tile as K: one buffer, free again when the score product has read it
@@ -815,6 +916,9 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     break;
                 }
                 unsigned char *dst = smem + kPairOffV + slot * kMlaVPartBytes;
+#ifdef YVX_MLA_SKIP_OWN_V
+                if ((j & 1u) == half) { mbar_arrive(&bars->v_full[slot]); continue; }   // timing experiment only: results invalid
+#endif
                 mbar_expect_tx(&bars->v_full[slot], kMlaVPartBytes);
                 for (int u = 0; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->v_full[slot], 64 * (own0 + u), token, (int)b);
@@ -843,6 +947,8 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 mbar_arrive(&bars->p_own_sent);
+                // the last credit is nobody's to wait for otherwise: nothing may be pending when the item ends
+                if (i + 1u == own_tiles && !pair_wait(&bars->p_peer_free, i & 1u, abort)) give_up();
             }
         }
     } else if (warp == 5 || warp == 9) {
@@ -892,6 +998,12 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 tc_commit_pred(elected, &bars->pv_done);
                 MLA_TRACE_ADD(1, tpv);
             }
+            // nothing may be pending on a barrier when the item ends: the last phases nobody else waits for
+            for (unsigned int slot = 0; ok && slot < 2u; ++slot) {
+                const unsigned int uses = (tiles + 1u - slot) / 2u;
+                if (uses) ok = wait_all(&bars->v_done[slot], (uses - 1u) & 1u);
+            }
+            if (ok && own_tiles) ok = wait_all(&bars->pv_own_done, (own_tiles - 1u) & 1u);
         } else {
             const uint32_t q_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffQ), 16);
             const uint32_t ka_lo = smem_desc_sw128_lo(smem_u32(smem + kPairOffKa), 16);
@@ -934,6 +1046,9 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 tc_commit_pred(elected, &bars->s_full);
                 MLA_TRACE_ADD(3, tqb);
             }
+            if (ok && own_tiles)   // the last phases of the "free again" barriers (see the P V warp)
+                ok = wait_all(&bars->ka_done, (own_tiles - 1u) & 1u) && wait_all(&bars->ka2_done, (own_tiles - 1u) & 1u) &&
+                     wait_all(&bars->kb_done, (own_tiles - 1u) & 1u);
         }
         if (!ok && lane == 0) give_up();
 #ifdef YVX_MLA_TRACE
@@ -1167,7 +1282,14 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         // this CTA's share of the denominators, and the maximum it is relative to, go to the peer
         cluster_store_f32(cluster_map(smem_u32(l_box + head), peer), l);
         cluster_store_f32(cluster_map(smem_u32(m_box + kMlaHeads + head), peer), m_used);
-        pdl_launch_dependents();
+        if (run_ends_here) pdl_launch_dependents();
+        if (balanced && ends_session) {
+            // the slots of this session that no item fills read as empty parts in the fold
+            for (unsigned int unused = split + 1u; unused < p.max_splits; ++unused)
+                *reinterpret_cast<float2 *>(
+                    p.partials + ((((unsigned long long)b * kMlaHeads + head) * 2ull + half) * p.max_splits + unused) * part_stride +
+                    kMlaHalf) = make_float2(-INFINITY, 0.0f);
+        }
         // (the cluster barrier below is reached by every thread of both CTAs)
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -1234,9 +1356,17 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
+    }   // work items
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem, kMlaTmemColumns);
+#ifdef YVX_MLA_TRACE
+    if (threadIdx.x == 0 && span_index < 512u) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        yvx_mla_spans[2u * span_index + 1u] = now;
+    }
+#endif
+    if (warp == 5) tmem_dealloc(bars->tmem_base, kMlaTmemColumns);
 }
 
 // ---- host side ------------------------------------------------------------------------
@@ -1316,12 +1446,45 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
     p->chunk_tokens = best;
     p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
     if (!p->max_splits) p->max_splits = 1u;
+    p->balanced_pairs = 0u;
+    p->balanced_reserved = 0u;
+    // Uniform lengths (the host knows every session's tiles): equal runs of the sessions' tiles laid end to end,
+    // one per pair of SMs, when that costs less than the grid of sessions x splits (which leaves SMs idle
+    // whenever sessions x splits x 2 is not a multiple of them). YVEX_B200_MLA_PLAN=grid|balanced forces one.
+    const char *form = getenv("YVEX_B200_MLA_INDEPENDENT");
+    const char *forced = getenv("YVEX_B200_MLA_PLAN");
+    const bool uniform = !p->kv_tokens && p->kv_tokens_uniform > 0u && p->kv_tokens_uniform <= p->kv_tokens_max;
+    if (!uniform || !p->sessions || (form && form[0] == '1') || (forced && forced[0] == 'g')) return;
+    const unsigned int pairs = (unsigned int)(wave / 2ull ? wave / 2ull : 1ull);
+    const yvx::MlaBalance g = yvx::mla_balance(p->sessions, p->kv_tokens_uniform, pairs);
+    const unsigned long long balanced_cost = (g.total + pairs - 1ull) / pairs + yvx::kMlaItemCostTiles;
+    // (by an eighth at least: a run that crosses sessions pays the item cost twice, and measured on 32 x 16384
+    // tokens, where the model promises a tenth, the two plans take the same time)
+    if (!(forced && forced[0] == 'b') && balanced_cost * 8ull >= best_cost * 7ull) return;
+    unsigned int pieces = 1u;
+    for (unsigned int k = 0; k < pairs; ++k) {
+        const unsigned long long lo = yvx::mla_run_begin(g, k), hi = yvx::mla_run_begin(g, k + 1ull);
+        if (hi <= lo) continue;
+        for (unsigned long long b = lo / g.unit; b <= (hi - 1ull) / g.unit && b < p->sessions; ++b) {
+            unsigned int tile_lo, tile_hi, slot;
+            bool ends;
+            if (yvx::mla_balanced_item(g, k, (unsigned int)b, &tile_lo, &tile_hi, &slot, &ends) && slot + 1u > pieces)
+                pieces = slot + 1u;
+        }
+    }
+    p->balanced_pairs = pairs;
+    p->max_splits = pieces;
+    p->chunk_tokens = ((p->kv_tokens_uniform + 63u) / 64u) * 64u;   // not used by the balanced plan; kept a tile multiple
 }
 
 #ifdef YVX_MLA_TRACE
 int yvx_cuda_mla_trace_read(unsigned long long out[16])
 {
     return cudaMemcpyFromSymbol(out, yvx::yvx_mla_trace, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
+}
+int yvx_cuda_mla_spans_read(unsigned long long out[1024])
+{
+    return cudaMemcpyFromSymbol(out, yvx::yvx_mla_spans, 1024 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
 }
 int yvx_cuda_mla_marks_read(unsigned long long out[16])
 {
@@ -1353,6 +1516,8 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
         p->latent_dim != (unsigned)kMlaLatent || p->rope_dim != (unsigned)kMlaRope)
         return YVEX_ERR_UNSUPPORTED;
     if (p->chunk_tokens % kMlaN) return YVEX_ERR_INVALID_ARG;
+    if (p->balanced_pairs && (p->kv_tokens || !p->kv_tokens_uniform || p->balanced_pairs > 65535u))
+        return YVEX_ERR_INVALID_ARG;   // the balanced plan is for uniform lengths
     cudaStream_t s = (cudaStream_t)stream;
     MlaMaps maps;
     if (!mla_encode(&maps.query, p->q_absorbed, kMlaWidth, kMlaHeads, p->sessions,
@@ -1381,8 +1546,13 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
     }
     const char *choice = getenv("YVEX_B200_MLA_INDEPENDENT");
     const bool paired = pair_configured && !(choice && choice[0] == '1');
+    if (!paired && p->balanced_pairs) {
+        yvx_cuda_set_error_text("the balanced plan needs the paired form of the latent decode kernel");
+        return YVEX_ERR_UNSUPPORTED;
+    }
     if (paired)
-        mla_decode_pair_kernel<<<dim3(2, p->max_splits, p->sessions), kPairThreads, kPairSmemBytes, s>>>(*p, maps);
+        mla_decode_pair_kernel<<<p->balanced_pairs ? dim3(2, p->balanced_pairs, 1) : dim3(2, p->max_splits, p->sessions),
+                                 kPairThreads, kPairSmemBytes, s>>>(*p, maps);
     else
         mla_decode_tcgen05_kernel<<<dim3(2, p->max_splits, p->sessions), kMlaThreads, kMlaSmemBytes, s>>>(*p, maps);
     if (events) cudaEventRecord((cudaEvent_t)events[2], s);

@@ -607,6 +607,11 @@ typedef struct yvx_mla_problem {
     const unsigned int *kv_tokens; /* device [sessions]; NULL = uniform */
     unsigned int kv_tokens_uniform, kv_tokens_max;
     unsigned int chunk_tokens, max_splits; /* filled by yvx_cuda_mla_plan */
+    /* Filled by yvx_cuda_mla_plan. Nonzero (uniform lengths only): the sessions' tiles are laid end to end and
+     * cut into this many equal runs, one per pair of CTAs, so a pair may finish one session and start the next
+     * and every SM has work; max_splits is then the largest number of runs a session is cut into. Zero: a
+     * grid of sessions x splits of chunk_tokens. */
+    unsigned int balanced_pairs, balanced_reserved;
     void *q_absorbed;      /* scratch bf16 [session][head][latent_dim + rope_dim] */
     float *partials;       /* scratch [session][head][2][max_splits][latent_dim/2 + 2] */
     float *output;         /* f32 [session][head][latent_dim] */

@@ -166,3 +166,36 @@ def test_struct_layouts_equal_the_reference_headers():
         for field, _ in mirror._fields_[:]:
             assert getattr(mirror, field).offset == reference[f"{name}.{field}"], (name, field)
         assert len(mirror._fields_) == len(probe.STRUCTS[name]), name
+
+
+def test_latent_decode_plans(library, monkeypatch):
+    """The latent decode planner needs no device: a grid of sessions x splits, or (uniform lengths only, and only
+    where it saves an eighth of the estimated cost) equal runs of the sessions' tiles, one per pair of SMs."""
+    monkeypatch.delenv("YVEX_B200_MLA_PLAN", raising=False)
+    monkeypatch.delenv("YVEX_B200_MLA_INDEPENDENT", raising=False)
+
+    def plan(sessions, tokens, uniform=True, sms=148):
+        p = abi.MlaProblem()
+        p.sessions, p.heads, p.nope_dim, p.latent_dim, p.rope_dim = sessions, 128, 128, 512, 64
+        p.kv_tokens_max = tokens
+        if uniform:
+            p.kv_tokens, p.kv_tokens_uniform = None, tokens
+        else:
+            p.kv_tokens = 0x1000     # a device address as far as the planner is concerned: lengths it cannot read
+        library.yvx_cuda_mla_plan(C.byref(p), sms)
+        return p.chunk_tokens, p.max_splits, p.balanced_pairs
+
+    assert plan(32, 16384) == (8192, 2, 0)                 # 128 work items in one wave: nothing to gain
+    assert plan(32, 16384, uniform=False) == (8192, 2, 0)
+    chunk, pieces, pairs = plan(20, 16384)                 # 40 x 7 splits would be two waves
+    assert pairs == 74 and pieces == 5 and chunk == 16384
+    assert plan(20, 16384, uniform=False)[2] == 0          # lengths on the device: the grid
+    monkeypatch.setenv("YVEX_B200_MLA_PLAN", "balanced")
+    assert plan(32, 16384) == (16384, 4, 74)
+    assert plan(3, 700, sms=10) == (704, 2, 5)
+    monkeypatch.setenv("YVEX_B200_MLA_PLAN", "grid")
+    assert plan(20, 16384)[2] == 0
+    # the scratch grows with the partial slots
+    p = abi.MlaProblem()
+    p.sessions, p.heads, p.latent_dim, p.max_splits = 2, 128, 512, 3
+    assert library.yvx_cuda_mla_partials_bytes(C.byref(p)) == 2 * 128 * 2 * 3 * 258 * 4

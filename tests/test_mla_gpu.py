@@ -16,7 +16,7 @@ from clori_b200 import abi, workloads
 pytestmark = pytest.mark.gpu
 
 
-def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale, chunk=None):
+def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale, chunk=None, sm_count=None):
     lib = backend.lib
     sessions, heads, nope = q_nope.shape
     cap, dc = latent.shape[1], latent.shape[2]
@@ -28,9 +28,12 @@ def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale, chu
     p.q_nope, p.q_rope, p.w_uk = t["qn"].data_ptr, t["qr"].data_ptr, t["w"].data_ptr
     p.latent, p.rope_key = t["lat"].data_ptr, t["rk"].data_ptr
     p.latent_session_stride, p.rope_session_stride = cap * dc, cap * dr
-    lens = backend.tensor("lens", np.asarray(lengths, np.int32))
-    p.kv_tokens, p.kv_tokens_max = lens.data_ptr, cap
-    lib.yvx_cuda_mla_plan(C.byref(p), backend.sm_count)
+    if isinstance(lengths, int):    # every session has this many tokens, and the host knows it
+        p.kv_tokens, p.kv_tokens_uniform, p.kv_tokens_max = None, lengths, cap
+    else:
+        lens = backend.tensor("lens", np.asarray(lengths, np.int32))
+        p.kv_tokens, p.kv_tokens_max = lens.data_ptr, cap
+    lib.yvx_cuda_mla_plan(C.byref(p), sm_count or backend.sm_count)
     if chunk:   # more (and shorter) splits than the planner would choose
         p.chunk_tokens, p.max_splits = chunk, (cap + chunk - 1) // chunk
     q_abs = backend.alloc("qabs", abi.DTYPE_BF16, (sessions, heads, dc + dr))
@@ -44,7 +47,8 @@ def run_mla(backend, q_nope, q_rope, w_uk, latent, rope_key, lengths, scale, chu
     assert lib.yvx_cuda_stream_synchronize(backend.stream) == 0, lib.yvx_cuda_last_error_text()
     out.struct.is_written = 1
     q_abs.struct.is_written = 1
-    return out.read(), q_abs.read(), int(status.read()[0]), launches.value, (p.chunk_tokens, p.max_splits)
+    plan = (p.chunk_tokens, p.max_splits, p.balanced_pairs) if p.balanced_pairs else (p.chunk_tokens, p.max_splits)
+    return out.read(), q_abs.read(), int(status.read()[0]), launches.value, plan
 
 
 def cosine(a, b):
@@ -100,6 +104,27 @@ def test_mla_decode_folds_many_splits_of_ragged_sessions(backend, oracle, form):
     for s in range(3):
         n = lengths[s]
         ref = oracle.mla_decode(qn[s], qr[s], w, lat[s, :n], rk[s, :n], scale)
+        assert np.abs(out[s] - ref).max() <= 2e-3, float(np.abs(out[s] - ref).max())
+        assert cosine(out[s], ref) >= 0.9999
+
+
+@pytest.mark.parametrize("sms,pieces", [(4, 1), (10, 2), (14, 2), (30, 3), (40, 4)])
+def test_mla_decode_balanced_runs_across_sessions(backend, oracle, monkeypatch, sms, pieces):
+    """Uniform lengths under the balanced plan: the three sessions' tiles laid end to end are cut into one run
+    per pair of SMs (the plan is made for 4 to 40 SMs: one run holds two whole sessions, one holds nothing), so a pair finishes one session and starts the
+    next (its barriers begin again) and a session is cut into up to four items; same bits every time."""
+    monkeypatch.delenv("YVEX_B200_MLA_INDEPENDENT", raising=False)
+    monkeypatch.setenv("YVEX_B200_MLA_PLAN", "balanced")
+    context = 700
+    qn, qr, w, lat, rk = workloads.mla_decode_bf16(seed=21, batch=3, context=context)
+    scale = 1.0 / np.sqrt(192.0)
+    out, _, status, _, plan = run_mla(backend, qn, qr, w, lat, rk, context, scale, sm_count=sms)
+    assert status == 0 and plan == (704, pieces, sms // 2)
+    for _ in range(3):
+        again, _, status, _, _ = run_mla(backend, qn, qr, w, lat, rk, context, scale, sm_count=sms)
+        assert status == 0 and np.array_equal(again.view(np.uint32), out.view(np.uint32))
+    for s in range(3):
+        ref = oracle.mla_decode(qn[s], qr[s], w, lat[s], rk[s], scale)
         assert np.abs(out[s] - ref).max() <= 2e-3, float(np.abs(out[s] - ref).max())
         assert cosine(out[s], ref) >= 0.9999
 
