@@ -880,15 +880,6 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 for (int u = 2; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka2_full, 64 * (other0 + u), token, (int)b);
                 tma_load_3d(dst + 4 * kMlaKvSubBytes, &maps.rope, &bars->ka2_full, 0, token, (int)b);
-#ifdef YVX_MLA_PREFETCH_TILE
-                // the next own tile (64 whole rows, contiguous) is asked into L2 in one piece
-                if (i + YVX_MLA_PREFETCH_TILE < own_tiles && (unsigned)token + (2u * YVX_MLA_PREFETCH_TILE + 1u) * kMlaN <= p.kv_tokens_max) {
-                    const unsigned short *rows = reinterpret_cast<const unsigned short *>(p.latent) +
-                                                 (unsigned long long)b * p.latent_session_stride +
-                                                 (unsigned long long)(token + 2 * YVX_MLA_PREFETCH_TILE * kMlaN) * kMlaLatent;
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(rows), "r"(kMlaN * kMlaLatent * 2) : "memory");
-                }
-#endif
             }
         } else if (warp == 6 && lane == 0) {
             // the own-half part of an own tile as K: one buffer, free again when the score product has read it
@@ -916,9 +907,6 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                     break;
                 }
                 unsigned char *dst = smem + kPairOffV + slot * kMlaVPartBytes;
-#ifdef YVX_MLA_SKIP_OWN_V
-                if ((j & 1u) == half) { mbar_arrive(&bars->v_full[slot]); continue; }   // timing experiment only: results invalid
-#endif
                 mbar_expect_tx(&bars->v_full[slot], kMlaVPartBytes);
                 for (int u = 0; u < 4; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->v_full[slot], 64 * (own0 + u), token, (int)b);
