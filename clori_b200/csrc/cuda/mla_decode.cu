@@ -94,12 +94,37 @@ mla_absorb_kernel(const yvx_mla_problem p)
     const __nv_bfloat16 *q_nope = reinterpret_cast<const __nv_bfloat16 *>(p.q_nope);
     const __nv_bfloat16 *w = reinterpret_cast<const __nv_bfloat16 *>(p.w_uk) +
                              (unsigned long long)head * kMlaNope * kMlaLatent + quarter * 128u;
+    // A thread's two chunks of the next 16 sessions' query rows (16 rows x 16 chunks of 16 bytes), asked for a
+    // tile ahead; the first tile's and the rope chunks travel together with the weights.
+    uint4 a_next[2];
+    auto load_a = [&](unsigned int session0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const unsigned int i = threadIdx.x + 128u * u, row = i >> 4, chunk = i & 15u;
+            a_next[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (session0 + row < p.sessions)
+                a_next[u] = *reinterpret_cast<const uint4 *>(
+                    q_nope + ((unsigned long long)(session0 + row) * kMlaHeads + head) * kMlaNope + chunk * 8u);
+        }
+    };
+    const unsigned short *q_rope = reinterpret_cast<const unsigned short *>(p.q_rope);
+    uint4 rope_first[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
     {
         uint4 staged[16];
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
             const unsigned int i = threadIdx.x + 128u * u, k = i >> 4, chunk = i & 15u;
             staged[u] = *reinterpret_cast<const uint4 *>(w + (unsigned long long)k * kMlaLatent + chunk * 8u);
+        }
+        load_a(0u);
+        if (quarter == 0u) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const unsigned int i = threadIdx.x + 128u * u;
+                if (i < p.sessions * 8u)
+                    rope_first[u] = *reinterpret_cast<const uint4 *>(
+                        q_rope + ((unsigned long long)(i >> 3) * kMlaHeads + head) * kMlaRope + (i & 7u) * 8u);
+            }
         }
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
@@ -111,15 +136,12 @@ mla_absorb_kernel(const yvx_mla_problem p)
     const unsigned int g = lane >> 2, c = lane & 3u;
     for (unsigned int session0 = 0; session0 < p.sessions; session0 += 16u) {
         __syncthreads();  // the previous tile's fragments have been read (and W is staged)
-        // A: 16 rows x 16 chunks of 16 bytes
-        for (unsigned int i = threadIdx.x; i < 16u * 16u; i += 128u) {
-            const unsigned int row = i >> 4, chunk = i & 15u;
-            uint4 value = make_uint4(0u, 0u, 0u, 0u);
-            if (session0 + row < p.sessions)
-                value = *reinterpret_cast<const uint4 *>(
-                    q_nope + ((unsigned long long)(session0 + row) * kMlaHeads + head) * kMlaNope + chunk * 8u);
-            *reinterpret_cast<uint4 *>(a_smem + row * kAbsorbPitch + chunk * 16u) = value;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const unsigned int i = threadIdx.x + 128u * u, row = i >> 4, chunk = i & 15u;
+            *reinterpret_cast<uint4 *>(a_smem + row * kAbsorbPitch + chunk * 16u) = a_next[u];
         }
+        if (session0 + 16u < p.sessions) load_a(session0 + 16u);   // in flight under this tile's products
         __syncthreads();
         uint32_t qa[8][4];
         const unsigned int j = lane >> 3, i8 = lane & 7u;
@@ -157,8 +179,14 @@ mla_absorb_kernel(const yvx_mla_problem p)
     }
     // rope part: copied through by the first quarter's CTA
     if (quarter == 0u) {
-        const unsigned short *q_rope = reinterpret_cast<const unsigned short *>(p.q_rope);
-        for (unsigned int i = threadIdx.x; i < p.sessions * 8u; i += 128u) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const unsigned int i = threadIdx.x + 128u * u;
+            if (i < p.sessions * 8u)
+                *reinterpret_cast<uint4 *>(out + ((unsigned long long)(i >> 3) * kMlaHeads + head) * kMlaWidth + kMlaLatent +
+                                           (i & 7u) * 8u) = rope_first[u];
+        }
+        for (unsigned int i = threadIdx.x + 256u; i < p.sessions * 8u; i += 128u) {
             const unsigned int row = i >> 3, chunk = i & 7u;
             const unsigned long long item = (unsigned long long)row * kMlaHeads + head;
             *reinterpret_cast<uint4 *>(out + item * kMlaWidth + kMlaLatent + chunk * 8u) =
