@@ -1473,6 +1473,9 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
     if (!uniform || !p->sessions || (form && form[0] == '1') || (forced && forced[0] == 'g')) return;
     const unsigned int pairs = (unsigned int)(wave / 2ull ? wave / 2ull : 1ull);
     const yvx::MlaBalance g = yvx::mla_balance(p->sessions, p->kv_tokens_uniform, pairs);
+    // every run must hold at least one cost unit: the items of a session are numbered by the pairs between the
+    // one that holds its first tile and the one at hand, which only counts them if none of those runs is empty
+    if (g.total < pairs) return;
     const unsigned long long balanced_cost = (g.total + pairs - 1ull) / pairs + yvx::kMlaItemCostTiles;
     // (by an eighth at least: a run that crosses sessions pays the item cost twice, and measured on 32 x 16384
     // tokens, where the model promises a tenth, the two plans take the same time)

@@ -193,6 +193,7 @@ def test_latent_decode_plans(library, monkeypatch):
     monkeypatch.setenv("YVEX_B200_MLA_PLAN", "balanced")
     assert plan(32, 16384) == (16384, 4, 74)
     assert plan(3, 700, sms=10) == (704, 2, 5)
+    assert plan(1, 100)[2] == 0                            # fewer cost units than pairs: some runs would be empty
     monkeypatch.setenv("YVEX_B200_MLA_PLAN", "grid")
     assert plan(20, 16384)[2] == 0
     # the scratch grows with the partial slots
