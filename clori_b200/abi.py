@@ -336,7 +336,7 @@ class MlaProblem(C.Structure):
         ("rope_key", C.c_void_p), ("latent_session_stride", u64), ("rope_session_stride", u64),
         ("kv_tokens", C.c_void_p), ("kv_tokens_uniform", C.c_uint), ("kv_tokens_max", C.c_uint),
         ("chunk_tokens", C.c_uint), ("max_splits", C.c_uint),
-        ("balanced_pairs", C.c_uint), ("balanced_reserved", C.c_uint),
+        ("balanced_pairs", C.c_uint), ("cluster_ctas", C.c_uint),
         ("q_absorbed", C.c_void_p), ("partials", C.c_void_p), ("output", C.c_void_p),
         ("status", C.c_void_p),
     ]

@@ -1385,6 +1385,537 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
     if (warp == 5) tmem_dealloc(bars->tmem_base, kMlaTmemColumns);
 }
 
+// ---- the form with clusters of FOUR CTAs -------------------------------------------------------------------
+// CTA r of a cluster owns a quarter of the latent columns of O (128 tensor-memory columns), so all 576 query dims
+// fit tensor memory (288 columns) beside the score buffer: every score instruction reads its A operand there, and
+// shared memory holds tile buffers only. Tile j is scored by CTA j % 4, which sends the weights (with the row
+// maxima they were scaled with) to the other three; every CTA runs P V of every tile on its own quarter, with V
+// (a tile's own quarter, 16 KB) from a ring of four slots. With one cluster per session nothing is split: no
+// partial rows and no combine launch. Waits, failure handling and the scale bookkeeping are the paired form's.
+constexpr int kQuadThreads = 320;    // warps 0-3 softmax, 4: K pieces, 5: score issuer, 6: V ring, 7: idle, 8: sender, 9: P V issuer
+constexpr int kQuadCols = kMlaLatent / 4;                               // 128 accumulator columns per CTA
+constexpr int kQuadQCols = kMlaWidth / 2;                               // 288 columns of query dims
+constexpr int kQuadPieceBytes = 3 * kMlaKvSubBytes;                     // a third of a tile: 24 KB, 12 score instructions
+constexpr int kQuadOffK = 0;                                            // a whole tile as K: 9 sub-tiles, 72 KB
+constexpr int kQuadVSlotBytes = 2 * kMlaKvSubBytes;                     // a tile's own quarter as V: 16 KB
+constexpr int kQuadOffV = kMlaKvBytes;                                  // 73728, four slots
+constexpr int kQuadOffPOwn = kQuadOffV + 4 * kQuadVSlotBytes;           // 139264
+constexpr int kQuadOffPPeer = kQuadOffPOwn + kPairPBytes;               // 155648: one buffer per source
+constexpr int kQuadOffTail = kQuadOffPPeer + 3 * kPairPBytes;           // 204800
+constexpr int kQuadBoxBytes = 3 * kMlaHeads * 4;                        // three sources x 128 floats
+constexpr int kQuadSmemBytes = kQuadOffTail + 256 + 3 * kQuadBoxBytes + kMlaHeads * 4 + 1024;
+
+
+struct QuadBarriers {
+    uint64_t q_tmem_full;
+    uint64_t k_full[3], k_done[3];        // the three pieces of an own tile: loaded / read by their score instructions
+    uint64_t v_full[4], v_done[4];        // the own quarter of any tile as V, four slots (tile % 4)
+    uint64_t s_full, s_free;
+    uint64_t p_own_full, pv_own_done;
+    uint64_t p_peer_full[3], peer_ready[3];   // per source: its weights have arrived / its message is processed
+    uint64_t p_peer_free;                 // all three peers have consumed the weights this CTA sent them
+    uint64_t p_written, p_own_sent;
+    uint64_t pv_done;
+    uint64_t rows_staged;
+    uint32_t tmem_base;
+    int abort;
+};
+constexpr unsigned int kQuadBarrierCount = 30u;
+static_assert(offsetof(QuadBarriers, tmem_base) == kQuadBarrierCount * 8u, "barrier count out of step");
+static_assert(sizeof(QuadBarriers) <= 256, "barrier block outgrew its shared-memory slot");
+
+__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(kQuadThreads, 1)
+mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps maps)
+{
+    extern __shared__ unsigned char quad_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(quad_smem_raw) + 1023u) & ~uintptr_t(1023));
+    QuadBarriers *bars = reinterpret_cast<QuadBarriers *>(smem + kQuadOffTail);
+    float *m_box = reinterpret_cast<float *>(smem + kQuadOffTail + 256);   // [3 sources][128]: a source's maxima with its tile
+    float *l_box = m_box + 3 * kMlaHeads;                                  // [3][128]: the peers' denominators at the end
+    float *mfin_box = l_box + 3 * kMlaHeads;                               // [3][128]: ... and the maxima they are relative to
+    float *m_out = mfin_box + 3 * kMlaHeads;                               // [128]: source of the copies to the peers
+
+    const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const unsigned int rank = blockIdx.x, split = blockIdx.y, b = blockIdx.z;   // rank in the cluster
+    const unsigned int kv_tokens = admitted_kv_tokens(p.kv_tokens, b, p.kv_tokens_uniform, p.kv_tokens_max, p.status);
+    const unsigned int t0 = split * p.chunk_tokens;
+    const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
+    const bool direct = p.max_splits == 1u;    // one item per session: the result itself leaves, no partial rows
+    const unsigned long long part_stride = kQuadCols + 2;
+    if (t0 >= t1) {
+        // Nothing of this session falls into the split (true for all four CTAs): an empty partial; a session without
+        // any token has no result (0 / 0, reported), as the fold of nothing gives.
+        if (threadIdx.x < (unsigned)kMlaHeads) {
+            if (direct) {
+                float *row = p.output + ((unsigned long long)b * kMlaHeads + threadIdx.x) * kMlaLatent + rank * kQuadCols;
+                for (int d = 0; d < kQuadCols; ++d) row[d] = __int_as_float(0x7fc00000);
+                atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+            } else {
+                float *part = p.partials +
+                              ((((unsigned long long)b * kMlaHeads + threadIdx.x) * 4ull + rank) * p.max_splits + split) * part_stride;
+                for (int d = 0; d < kQuadCols; ++d) part[d] = 0.0f;
+                part[kQuadCols] = -INFINITY;
+                part[kQuadCols + 1] = 0.0f;
+            }
+        }
+        return;
+    }
+    const unsigned int tiles = (t1 - t0 + kMlaN - 1) / kMlaN;
+    const unsigned int own_tiles = (tiles + 3u - rank) / 4u;     // tiles j with j % 4 == rank
+    volatile int *abort = &bars->abort;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bars->q_tmem_full, kMlaHeads);
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&bars->k_full[i], 1);
+            mbar_init(&bars->k_done[i], 1);
+            mbar_init(&bars->p_peer_full[i], 1);
+            mbar_init(&bars->peer_ready[i], 4);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&bars->v_full[i], 1);
+            mbar_init(&bars->v_done[i], 1);
+        }
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->s_free, kMlaHeads);
+        mbar_init(&bars->p_own_full, 4);
+        mbar_init(&bars->pv_own_done, 1);
+        mbar_init(&bars->p_peer_free, 3);
+        mbar_init(&bars->p_written, 4);
+        mbar_init(&bars->p_own_sent, 1);
+        mbar_init(&bars->pv_done, 1);
+        mbar_init(&bars->rows_staged, kMlaHeads);
+        bars->abort = 0;
+        fence_barrier_init();
+        // the first message of every source that has a tile: its weights and its maxima, counted in bytes
+        for (unsigned int q = 0; q < 3u; ++q) {
+            const unsigned int source = (rank + 1u + q) & 3u;
+            if ((tiles + 3u - source) / 4u) mbar_expect_tx(&bars->p_peer_full[q], kPairPBytes + kMlaHeads * 4);
+        }
+    }
+    if (warp == 5) {
+        tmem_alloc(&bars->tmem_base, kMlaTmemColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();          // the peers' barriers exist before anything arrives on them
+    tc_fence_after_sync();
+    const uint32_t tmem = bars->tmem_base;
+    const uint32_t tmem_o = tmem, tmem_s = tmem + kQuadCols, tmem_q = tmem + kQuadCols + kMlaN;
+    auto give_up = [&]() {   // records the failure here and at the peers, whose waits then end too
+        atomicCAS(p.status, 0, YVX_STATUS_TIMEOUT);
+        bars->abort = 1;
+        for (unsigned int d = 1; d < 4u; ++d) cluster_store_b32(cluster_map(smem_u32(&bars->abort), (rank + d) & 3u), 1u);
+    };
+
+    if (warp == 4 || warp == 6 || warp == 7) {
+        if (warp == 4 && lane == 0) {
+            // an own tile as K, in three pieces with their own barriers (a piece is asked for again as soon as its
+            // twelve score instructions have read it)
+            for (unsigned int i = 0; i < own_tiles; ++i) {
+                const int token = (int)(t0 + (4u * i + rank) * kMlaN);
+                bool fine = true;
+                for (int piece = 0; piece < 3 && fine; ++piece) {
+                    if (i > 0 && !pair_wait(&bars->k_done[piece], (i - 1u) & 1u, abort)) {
+                        give_up();
+                        fine = false;
+                        break;
+                    }
+                    mbar_expect_tx(&bars->k_full[piece], kQuadPieceBytes);
+                    for (int u = 3 * piece; u < 3 * piece + 3; ++u) {
+                        unsigned char *dst = smem + kQuadOffK + u * kMlaKvSubBytes;
+                        if (u < 8)
+                            tma_load_3d(dst, &maps.latent, &bars->k_full[piece], 64 * u, token, (int)b);
+                        else
+                            tma_load_3d(dst, &maps.rope, &bars->k_full[piece], 0, token, (int)b);
+                    }
+                }
+                if (!fine) break;
+            }
+        } else if (warp == 6 && lane == 0) {
+            // the own quarter of EVERY tile as V (out of L2 for the most part: a score product's load of the tile has
+            // brought it there), four slots
+            for (unsigned int j = 0; j < tiles; ++j) {
+                const unsigned int slot = j & 3u;
+                const int token = (int)(t0 + j * kMlaN);
+                if (j >= 4u && !pair_wait(&bars->v_done[slot], ((j >> 2) - 1u) & 1u, abort)) {
+                    give_up();
+                    break;
+                }
+                unsigned char *dst = smem + kQuadOffV + slot * kQuadVSlotBytes;
+                mbar_expect_tx(&bars->v_full[slot], kQuadVSlotBytes);
+                for (int u = 0; u < 2; ++u)
+                    tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->v_full[slot], 64 * (2 * (int)rank + u), token, (int)b);
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------ sender ------------------------------
+        if (lane == 0) {
+            for (unsigned int i = 0; i < own_tiles; ++i) {
+                if (!pair_wait(&bars->p_written, i & 1u, abort) ||
+                    (i > 0 && !pair_wait(&bars->p_peer_free, (i - 1u) & 1u, abort))) {
+                    give_up();
+                    break;
+                }
+                fence_proxy_async();
+                for (unsigned int d = 1; d < 4u; ++d) {
+                    const unsigned int destination = (rank + d) & 3u, q = (3u - d) & 3u;   // this CTA's slot over there
+                    const uint32_t full = cluster_map(smem_u32(&bars->p_peer_full[q]), destination);
+                    cluster_bulk_copy(cluster_map(smem_u32(smem + kQuadOffPPeer + q * kPairPBytes), destination),
+                                      smem + kQuadOffPOwn, kPairPBytes, full);
+                    cluster_bulk_copy(cluster_map(smem_u32(m_box + q * kMlaHeads), destination), m_out, kMlaHeads * 4, full);
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                mbar_arrive(&bars->p_own_sent);
+                // the last credits are nobody's to wait for otherwise: nothing may be pending when the kernel ends
+                if (i + 1u == own_tiles && !pair_wait(&bars->p_peer_free, i & 1u, abort)) give_up();
+            }
+        }
+    } else if (warp == 5 || warp == 9) {
+        // ------------------------------ MMA issuers: one for the score products, one for the P V products ------
+        constexpr uint32_t idesc_qk = idesc_bf16_f32(kMlaHeads, kMlaN, false);
+        constexpr uint32_t idesc_pv = idesc_bf16_f32(kMlaHeads, kQuadCols, true);
+        constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
+        const uint32_t elected = tc_elect_one() ? 1u : 0u;
+        auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {    // every lane waits: the warp stays converged
+            return __all_sync(0xffffffffu, pair_wait(bar, parity, abort)) != 0;
+        };
+        bool ok = true;
+        if (warp == 9) {
+            for (unsigned int j = 0; ok && j < tiles; ++j) {
+                const unsigned int i = j >> 2, source = j & 3u, slot = j & 3u;
+                const bool own = source == rank;
+                const unsigned int q = (source - rank - 1u) & 3u;
+                ok = wait_all(own ? &bars->p_own_full : &bars->peer_ready[q], i & 1u) && wait_all(&bars->v_full[slot], i & 1u);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t p_lo =
+                    smem_desc_sw128_lo(smem_u32(smem + (own ? kQuadOffPOwn : kQuadOffPPeer + (int)q * kPairPBytes)), 16);
+                const uint32_t v_lo = smem_desc_sw128_lo(smem_u32(smem + kQuadOffV + slot * kQuadVSlotBytes), kMlaKvSubBytes);
+#pragma unroll
+                for (int kk = 0; kk < kMlaN / 16; ++kk)
+                    tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
+                                   (j || kk) ? 1u : 0u);
+                tc_commit_pred(elected, &bars->v_done[slot]);
+                if (own) {
+                    tc_commit_pred(elected, &bars->pv_own_done);
+                } else {
+                    // ... and tells the source at once that the weights it sent are consumed here
+                    const uint32_t credit = cluster_map(smem_u32(&bars->p_peer_free), source);
+                    asm volatile(
+                        "{\n\t.reg .pred pe;\n\t"
+                        "setp.ne.b32 pe, %0, 0;\n\t"
+                        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
+                        ::"r"(elected), "r"(credit)
+                        : "memory");
+                }
+                tc_commit_pred(elected, &bars->pv_done);
+            }
+            // nothing may be pending on a barrier when the kernel ends: the last phases nobody else waits for
+            for (unsigned int slot = 0; ok && slot < 4u; ++slot) {
+                const unsigned int uses = (tiles + 3u - slot) / 4u;
+                if (uses) ok = wait_all(&bars->v_done[slot], (uses - 1u) & 1u);
+            }
+            if (ok && own_tiles) ok = wait_all(&bars->pv_own_done, (own_tiles - 1u) & 1u);
+        } else {
+            const uint32_t k_lo = smem_desc_sw128_lo(smem_u32(smem + kQuadOffK), 16);
+            ok = wait_all(&bars->q_tmem_full, 0);
+            for (unsigned int i = 0; ok && i < own_tiles; ++i) {
+#pragma unroll
+                for (int piece = 0; piece < 3; ++piece) {
+                    if (!(ok = wait_all(&bars->k_full[piece], i & 1u))) break;
+                    // the score buffer is free once the softmax has read the previous own tile out of it
+                    if (piece == 0 && i > 0u && !(ok = wait_all(&bars->s_free, (i - 1u) & 1u))) break;
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int ks = 12 * piece; ks < 12 * piece + 12; ++ks)
+                        tc_mma_ts_pred(elected, tmem_s, tmem_q + ks * 8,
+                                       k_lo + (((ks >> 2) * kMlaKvSubBytes + (ks & 3) * 32) >> 4), desc_hi, idesc_qk, ks ? 1u : 0u);
+                    tc_commit_pred(elected, &bars->k_done[piece]);
+                }
+                if (!ok) break;
+                tc_commit_pred(elected, &bars->s_full);
+            }
+            for (int piece = 0; ok && own_tiles && piece < 3; ++piece) ok = wait_all(&bars->k_done[piece], (own_tiles - 1u) & 1u);
+        }
+        if (!ok && lane == 0) give_up();
+    } else {
+        // ------------------------------ softmax warps: a thread owns a head (a row of every tile) ------------------
+        const unsigned int quadrant = warp;
+        const unsigned int head = quadrant * 32u + lane;
+        const uint32_t lane_base = ((quadrant * 32u) << 16);
+        {
+            // all 576 query dims of this head into tensor memory. A warp reads 128-byte pieces of four rows per
+            // instruction and turns them through its 4 KB of the (still unused) weights buffer.
+            const unsigned short *row0 = reinterpret_cast<const unsigned short *>(p.q_absorbed) +
+                                         ((unsigned long long)b * kMlaHeads + quadrant * 32u) * kMlaWidth;
+            unsigned char *turn = smem + kQuadOffPOwn + quadrant * 4096u;
+            const unsigned int piece_row = lane >> 3, piece = lane & 7u;
+#pragma unroll 1
+            for (int batch = 0; batch < kQuadQCols / 96; ++batch) {
+                uint4 v[3][8];
+#pragma unroll
+                for (int g = 0; g < 3; ++g) {
+                    const unsigned short *group = row0 + 64u * (3 * batch + g);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        v[g][c] = *reinterpret_cast<const uint4 *>(group + (4u * c + piece_row) * kMlaWidth + piece * 8u);
+                }
+#pragma unroll
+                for (int g = 0; g < 3; ++g) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const unsigned int r = 4u * c + piece_row;
+                        *reinterpret_cast<uint4 *>(turn + r * 128u + ((piece ^ (r & 7u)) * 16u)) = v[g][c];
+                    }
+                    __syncwarp();
+                    uint32_t words[32];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(turn + lane * 128u + (((unsigned)c ^ (lane & 7u)) * 16u));
+                        words[4 * c] = w.x;
+                        words[4 * c + 1] = w.y;
+                        words[4 * c + 2] = w.z;
+                        words[4 * c + 3] = w.w;
+                    }
+                    __syncwarp();
+                    tmem_st32(tmem_q + lane_base + 32 * (3 * batch + g), words);
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(&bars->q_tmem_full);
+        }
+        const float sscale = p.scale * 1.4426950408889634f;
+        // m_used: the maximum this CTA's weights are scaled with (and its l); m_o: the scale its accumulator carries
+        float m_used = -INFINITY, l = 0.0f, m_o = -INFINITY, m_heard = -INFINITY;
+        bool ok = true;
+        auto rescale = [&](float factor) {
+#pragma unroll 1
+            for (int i = 0; i < kQuadCols / 32; ++i) {
+                uint32_t o[32];
+                const uint32_t column = tmem_o + lane_base + 32u * i;
+                tmem_ld32(column, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+                tmem_st32(column, o);
+            }
+            tmem_wait_st();
+        };
+        // Lets the tensor pipe run P(j) V(j): first brings the accumulator to the scale the weights of tile j were
+        // computed with (up or down; rare), in tile order, after every earlier P V has landed.
+        auto release = [&](unsigned int j, float m_p, uint64_t *go) -> bool {
+            const bool differs = m_p != m_o && m_p != -INFINITY;
+            if (__any_sync(0xffffffffu, differs)) {
+                if (j > 0) {
+                    if (!pair_wait(&bars->pv_done, (j - 1u) & 1u, abort)) return false;
+                    tc_fence_after_sync();
+                    rescale(differs && m_o != -INFINITY ? exp2_approx(m_o - m_p) : 1.0f);
+                    tc_fence_before_sync();
+                }
+                if (differs) m_o = m_p;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(go);
+            return true;
+        };
+        // A peer's message for its tile j: its weights are in place, its maxima in its box.
+        auto receive = [&](unsigned int j) -> bool {
+            const unsigned int source = j & 3u, q = (source - rank - 1u) & 3u, ip = j >> 2;
+            if (!pair_wait(&bars->p_peer_full[q], ip & 1u, abort)) return false;
+            if (warp == 0 && lane == 0 && ip + 1u < (tiles + 3u - source) / 4u)   // the source's next message may be counted from now on
+                mbar_expect_tx(&bars->p_peer_full[q], kPairPBytes + kMlaHeads * 4);
+            const float m_in = m_box[q * kMlaHeads + head];
+            m_heard = fmaxf(m_heard, m_in);   // adopted at a fixed point of the program (results must not depend on timing)
+            return release(j, m_in, &bars->peer_ready[q]);
+        };
+        unsigned int next_rx = rank == 0u ? 1u : 0u;     // the next tile of a peer to process, in tile order
+        auto advance_rx = [&]() {
+            ++next_rx;
+            if ((next_rx & 3u) == rank) ++next_rx;
+        };
+        for (unsigned int i = 0; i < own_tiles && ok; ++i) {
+            const unsigned int j = 4u * i + rank;
+            {
+                if (!pair_wait(&bars->s_full, i & 1u, abort)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t s[2][32];
+                tmem_ld32(tmem_s + lane_base, s[0]);
+                tmem_ld32(tmem_s + lane_base + 32u, s[1]);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                mbar_arrive(&bars->s_free);
+                const unsigned int k0 = t0 + j * kMlaN;
+                if (k0 + kMlaN > t1) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (k0 + 32 * h + c >= t1) s[h][c] = 0xff800000u;  // -inf
+                }
+                // Messages for the tiles in front of this one that have arrived already are processed now (their
+                // P V can run, and their sources get their buffers back, while this tile's exponentials are
+                // computed); the others after this tile's weights are out.
+                while (ok && next_rx < j) {
+                    const unsigned int source = next_rx & 3u, q = (source - rank - 1u) & 3u;
+                    if (!__shfl_sync(0xffffffffu, (int)mbar_test(&bars->p_peer_full[q], (next_rx >> 2) & 1u), 0)) break;
+                    ok = receive(next_rx);
+                    advance_rx();
+                }
+                if (!ok) break;
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2)
+                        mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[h][c]), __uint_as_float(s[h][c + 1]));
+                const float m_tile = max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * sscale;
+                if (m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY) {
+                    const float m_new = fmaxf(m_used, m_tile);
+                    l *= m_new == -INFINITY || m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
+                    m_used = m_new;
+                }
+                const float offset = m_used == -INFINITY ? 0.0f : -m_used;
+                uint32_t packed[32];
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        const float p0 = exp2_approx(fmaf(__uint_as_float(s[h][c]), sscale, offset));
+                        const float p1 = exp2_approx(fmaf(__uint_as_float(s[h][c + 1]), sscale, offset));
+                        sum0 += p0;
+                        sum1 += p1;
+                        packed[16 * h + (c >> 1)] = pack_bf16(p0, p1);
+                    }
+                l += sum0 + sum1;
+                // the previous own tile's weights have been consumed here and have left for the peers
+                if (i > 0 && !(pair_wait(&bars->pv_own_done, (i - 1u) & 1u, abort) &&
+                               pair_wait(&bars->p_own_sent, (i - 1u) & 1u, abort))) {
+                    ok = false;
+                    break;
+                }
+                {
+                    unsigned char *mine = smem + kQuadOffPOwn + head * 128u;   // row `head`: eight 16-byte chunks, 128-byte swizzle
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<uint4 *>(mine + ((unsigned)c ^ (head & 7u)) * 16u) =
+                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                    m_out[head] = m_used;
+                }
+                fence_proxy_async();   // the tensor pipe and the bulk copies read these bytes through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->p_written);
+            }
+            // ---- P V in tile order: the peers' tiles in front of this one, then this one ----
+            const float m_own = m_used;
+            while (ok && next_rx < j) {
+                ok = receive(next_rx);
+                advance_rx();
+            }
+            if (ok) ok = release(j, m_own, &bars->p_own_full);
+            // Here, whenever the peers' messages were processed: adopt a larger maximum, so that the four CTAs'
+            // references stay together.
+            if (m_heard > m_used) {
+                l *= m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_heard);
+                m_used = m_heard;
+            }
+        }
+        // the peers' tiles behind this CTA's last one
+        while (ok && next_rx < tiles) {
+            ok = receive(next_rx);
+            advance_rx();
+        }
+        if (ok) ok = pair_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
+        if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up();
+        // this CTA's share of the denominators, and the maximum it is relative to, go to the peers
+        for (unsigned int d = 1; d < 4u; ++d) {
+            const unsigned int destination = (rank + d) & 3u, q = (3u - d) & 3u;
+            cluster_store_f32(cluster_map(smem_u32(l_box + q * kMlaHeads + head), destination), l);
+            cluster_store_f32(cluster_map(smem_u32(mfin_box + q * kMlaHeads + head), destination), m_used);
+        }
+        pdl_launch_dependents();
+        // (the cluster barrier below is reached by every thread of all four CTAs)
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        bool fine = ok && !*abort;
+        float *staged = reinterpret_cast<float *>(smem);
+        if (fine) {
+            tc_fence_after_sync();
+            // the row's denominator: all four shares at the accumulator's scale
+            float total = m_used == -INFINITY ? 0.0f : l * exp2_approx(m_used - m_o);
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const float m_theirs = mfin_box[q * kMlaHeads + head];
+                total += m_theirs == -INFINITY ? 0.0f : l_box[q * kMlaHeads + head] * exp2_approx(m_theirs - m_o);
+            }
+            l = total;
+            const float inverse = direct ? 1.0f / l : (l > 0.0f ? 1.0f / l : 0.0f);
+            // every tile has been consumed: the tile buffers are free for the turn of the rows
+            float *mine = staged + head * (unsigned)part_stride;
+            bool finite = true;
+#pragma unroll 1
+            for (int i = 0; i < kQuadCols / 32; ++i) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_base + 32 * i, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float2 value = make_float2(__uint_as_float(o[c]) * inverse, __uint_as_float(o[c + 1]) * inverse);
+                    finite = finite && isfinite(value.x) && isfinite(value.y);
+                    *reinterpret_cast<float2 *>(mine + 32 * i + c) = value;
+                }
+            }
+            if (direct && !finite) atomicCAS(p.status, 0, YVX_STATUS_NONFINITE);
+            *reinterpret_cast<float2 *>(mine + kQuadCols) =
+                make_float2(m_o == -INFINITY ? -INFINITY : m_o * 0.6931471805599453f, l);
+            mbar_arrive(&bars->rows_staged);
+            fine = pair_wait(&bars->rows_staged, 0, abort);
+        }
+        if (fine) {
+            // four rows at a time, all of their loads from shared memory ahead of the stores
+            const unsigned int row_words = direct ? (unsigned)kQuadCols / 2u : (unsigned)(kQuadCols + 2) / 2u;
+#pragma unroll 1
+            for (unsigned int r0 = warp * 32u; r0 < warp * 32u + 32u; r0 += 4u) {
+                float2 v[4][3];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 *src = reinterpret_cast<const float2 *>(staged + (r0 + q) * (unsigned)part_stride);
+#pragma unroll
+                    for (int u = 0; u < 3; ++u)
+                        if (lane + 32u * u < row_words) v[q][u] = src[lane + 32u * u];
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float2 *dst = reinterpret_cast<float2 *>(
+                        direct ? p.output + ((unsigned long long)b * kMlaHeads + r0 + q) * kMlaLatent + rank * kQuadCols
+                               : p.partials + ((((unsigned long long)b * kMlaHeads + r0 + q) * 4ull + rank) * p.max_splits + split) *
+                                                  part_stride);
+#pragma unroll
+                    for (int u = 0; u < 3; ++u)
+                        if (lane + 32u * u < row_words) dst[lane + 32u * u] = v[q][u];
+                }
+            }
+        }
+    }
+    if (warp >= 4u) {
+        // the producer, sender and issuer warps meet the softmax warps at the cluster barrier
+        __syncwarp();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem, kMlaTmemColumns);
+}
+
 // ---- host side ------------------------------------------------------------------------
 
 typedef CUresult (*MlaEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -1463,7 +1994,22 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
     p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
     if (!p->max_splits) p->max_splits = 1u;
     p->balanced_pairs = 0u;
-    p->balanced_reserved = 0u;
+    p->cluster_ctas = 2u;
+    // Clusters of four CTAs (YVEX_B200_MLA_FORM=quad): one cluster per session and split, as many splits as keep
+    // the clusters within one wave (seven eighths of sm_count / 4: a cluster needs four free SMs of one GPC).
+    const char *shape = getenv("YVEX_B200_MLA_FORM");
+    if (shape && shape[0] == 'q' && p->sessions) {
+        const unsigned long long cap = wave / 4ull * 7ull / 8ull ? wave / 4ull * 7ull / 8ull : 1ull;
+        const unsigned long long tiles_max = (unsigned long long)(longest ? longest : 64u) / 64ull;
+        unsigned long long splits = cap / p->sessions;
+        if (splits < 1ull) splits = 1ull;
+        if (splits > tiles_max) splits = tiles_max;
+        p->chunk_tokens = (unsigned int)(((tiles_max + splits - 1ull) / splits) * 64ull);
+        p->max_splits = (p->kv_tokens_max + p->chunk_tokens - 1u) / p->chunk_tokens;
+        if (!p->max_splits) p->max_splits = 1u;
+        p->cluster_ctas = 4u;
+        return;
+    }
     // Uniform lengths (the host knows every session's tiles): equal runs of the sessions' tiles laid end to end,
     // one per pair of SMs, when that costs less than the grid of sessions x splits (which leaves SMs idle
     // whenever sessions x splits x 2 is not a multiple of them). YVEX_B200_MLA_PLAN=grid|balanced forces one.
@@ -1518,9 +2064,10 @@ unsigned long long yvx_cuda_mla_absorbed_bytes(const yvx_mla_problem *p)
 
 unsigned long long yvx_cuda_mla_partials_bytes(const yvx_mla_problem *p)
 {
-    return p ? (unsigned long long)p->sessions * p->heads * 2ull * p->max_splits *
-                   (p->latent_dim / 2ull + 2ull) * sizeof(float)
-             : 0ull;
+    if (!p) return 0ull;
+    if (p->cluster_ctas == 4u)   // (o[latent_dim / 4], m, l) per session, head, quarter and split
+        return (unsigned long long)p->sessions * p->heads * 4ull * p->max_splits * (p->latent_dim / 4ull + 2ull) * sizeof(float);
+    return (unsigned long long)p->sessions * p->heads * 2ull * p->max_splits * (p->latent_dim / 2ull + 2ull) * sizeof(float);
 }
 
 int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4], unsigned int *launches)
@@ -1565,6 +2112,29 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
     }
     const char *choice = getenv("YVEX_B200_MLA_INDEPENDENT");
     const bool paired = pair_configured && !(choice && choice[0] == '1');
+    if (p->cluster_ctas == 4u) {
+        static int quad_configured = -1;
+        if (quad_configured < 0) {
+            quad_configured = cudaFuncSetAttribute(mla_decode_quad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   kQuadSmemBytes) == cudaSuccess;
+            if (!quad_configured) cudaGetLastError();
+        }
+        if (!quad_configured || p->balanced_pairs) {
+            yvx_cuda_set_error_text("the four-CTA form of the latent decode kernel is not available for this plan");
+            return YVEX_ERR_UNSUPPORTED;
+        }
+        mla_decode_quad_kernel<<<dim3(4, p->max_splits, p->sessions), kQuadThreads, kQuadSmemBytes, s>>>(*p, maps);
+        if (events) cudaEventRecord((cudaEvent_t)events[2], s);
+        int quad_rc = yvx_cuda_check(cudaGetLastError(), "mla kernels");
+        if (quad_rc != 0) return quad_rc;
+        if (p->max_splits > 1u)
+            quad_rc = yvx_cuda_lse_combine(p->partials, p->sessions * kMlaHeads * 4u, p->max_splits, kQuadCols, p->output,
+                                           YVEX_DTYPE_F32, p->status, stream);
+        if (events) cudaEventRecord((cudaEvent_t)events[3], s);
+        if (quad_rc != 0) return quad_rc;
+        if (launches) *launches = p->max_splits > 1u ? 3u : 2u;
+        return 0;
+    }
     if (!paired && p->balanced_pairs) {
         yvx_cuda_set_error_text("the balanced plan needs the paired form of the latent decode kernel");
         return YVEX_ERR_UNSUPPORTED;

@@ -611,9 +611,13 @@ typedef struct yvx_mla_problem {
      * cut into this many equal runs, one per pair of CTAs, so a pair may finish one session and start the next
      * and every SM has work; max_splits is then the largest number of runs a session is cut into. Zero: a
      * grid of sessions x splits of chunk_tokens. */
-    unsigned int balanced_pairs, balanced_reserved;
+    unsigned int balanced_pairs;
+    /* Filled by yvx_cuda_mla_plan: 4 = the attention kernel runs as clusters of four CTAs, each with a quarter of the
+     * latent columns (grid 4 x splits x sessions; with max_splits == 1 the result is written by the kernel itself:
+     * no partial rows, no combine launch); 0 or 2 = pairs of CTAs with half of the columns each. */
+    unsigned int cluster_ctas;
     void *q_absorbed;      /* scratch bf16 [session][head][latent_dim + rope_dim] */
-    float *partials;       /* scratch [session][head][2][max_splits][latent_dim/2 + 2] */
+    float *partials;       /* scratch [session][head][2][max_splits][latent_dim/2 + 2] ([4][..][latent_dim/4 + 2] with cluster_ctas 4) */
     float *output;         /* f32 [session][head][latent_dim] */
     int *status;
 } yvx_mla_problem;

@@ -56,14 +56,17 @@ def cosine(a, b):
     return float(a @ b / np.sqrt((a @ a) * (b @ b)))
 
 
-@pytest.fixture(params=["paired", "independent"])
+@pytest.fixture(params=["paired", "independent", "quad"])
 def form(request, monkeypatch):
-    """Both forms of the attention kernel: a cluster of two CTAs that computes every score tile once and
-    exchanges the weights (the default), and two independent CTAs that both compute it."""
+    """The forms of the attention kernel: a cluster of two CTAs that computes every score tile once and
+    exchanges the weights, two independent CTAs that both compute it, and a cluster of four CTAs with a
+    quarter of the latent columns each."""
+    monkeypatch.delenv("YVEX_B200_MLA_INDEPENDENT", raising=False)
+    monkeypatch.delenv("YVEX_B200_MLA_FORM", raising=False)
     if request.param == "independent":
         monkeypatch.setenv("YVEX_B200_MLA_INDEPENDENT", "1")
-    else:
-        monkeypatch.delenv("YVEX_B200_MLA_INDEPENDENT", raising=False)
+    if request.param == "quad":
+        monkeypatch.setenv("YVEX_B200_MLA_FORM", "quad")
     return request.param
 
 
@@ -75,7 +78,7 @@ def test_mla_decode_matches_restatement(backend, oracle, sessions, context, form
         lengths[1] = max(1, context - 37)  # ragged: a length that is not a tile multiple
     scale = 1.0 / np.sqrt(192.0)
     out, q_abs, status, launches, plan = run_mla(backend, qn, qr, w, lat, rk, lengths, scale)
-    assert status == 0 and launches == 3
+    assert status == 0 and launches == (2 if form == "quad" and plan[1] == 1 else 3)   # one item per session: no fold
     for s in range(sessions):
         n = lengths[s]
         ref = oracle.mla_decode(qn[s], qr[s], w, lat[s, :n], rk[s, :n], scale)
@@ -114,6 +117,7 @@ def test_mla_decode_balanced_runs_across_sessions(backend, oracle, monkeypatch, 
     per pair of SMs (the plan is made for 4 to 40 SMs: one run holds two whole sessions, one holds nothing), so a pair finishes one session and starts the
     next (its barriers begin again) and a session is cut into up to four items; same bits every time."""
     monkeypatch.delenv("YVEX_B200_MLA_INDEPENDENT", raising=False)
+    monkeypatch.delenv("YVEX_B200_MLA_FORM", raising=False)
     monkeypatch.setenv("YVEX_B200_MLA_PLAN", "balanced")
     context = 700
     qn, qr, w, lat, rk = workloads.mla_decode_bf16(seed=21, batch=3, context=context)
