@@ -62,6 +62,7 @@ __device__ unsigned long long yvx_mla_spans[1024];
 
 struct MlaMaps {
     CUtensorMap query, latent, rope;
+    CUtensorMap weights;   // the four-CTA form's scratch slots: [slot][128 heads][64 tokens] bf16
 };
 
 struct MlaBarriers {
@@ -667,6 +668,11 @@ __device__ __forceinline__ void cluster_arrive_remote(uint32_t barrier_address)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(barrier_address) : "memory");
 }
+// ... where the arrival publishes nothing of this thread's (a credit): no release to wait for
+__device__ __forceinline__ void cluster_arrive_remote_relaxed(uint32_t barrier_address)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(barrier_address) : "memory");
+}
 // Bulk copy from this CTA's shared memory into the peer's, completion counted in bytes on a barrier of the peer.
 __device__ __forceinline__ void cluster_bulk_copy(uint32_t peer_destination, const void *source, uint32_t bytes,
                                                   uint32_t peer_barrier)
@@ -690,6 +696,25 @@ __device__ __forceinline__ bool pair_wait(uint64_t *bar, uint32_t parity, const 
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
             "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 255u) == 255u && *abort) return false;
+    }
+    return false;
+}
+// The same for a barrier that only this CTA's threads, bulk copies and tensor-pipe commits arrive on: acquire at
+// CTA scope (the cluster-scope acquire costs every look at a barrier some hundred cycles more).
+__device__ __forceinline__ bool local_wait(uint64_t *bar, uint32_t parity, const volatile int *abort)
+{
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
             : "r"(addr), "r"(parity)
@@ -892,7 +917,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 const int token = (int)(t0 + (2u * i + half) * kMlaN);
                 // two pieces with their own barriers: the first is free again (and its reload under way) while
                 // the score product still reads the second
-                if (i > 0 && !pair_wait(&bars->ka_done, (i - 1u) & 1u, abort)) {
+                if (i > 0 && !local_wait(&bars->ka_done, (i - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
@@ -900,7 +925,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 mbar_expect_tx(&bars->ka_full, 2 * kMlaKvSubBytes);
                 for (int u = 0; u < 2; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->ka_full, 64 * (other0 + u), token, (int)b);
-                if (i > 0 && !pair_wait(&bars->ka2_done, (i - 1u) & 1u, abort)) {
+                if (i > 0 && !local_wait(&bars->ka2_done, (i - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
@@ -913,7 +938,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             // the own-half part of an own tile as K: one buffer, free again when the score product has read it
             for (unsigned int i = 0; i < own_tiles; ++i) {
                 const int token = (int)(t0 + (2u * i + half) * kMlaN);
-                if (i > 0 && !pair_wait(&bars->kb_done, (i - 1u) & 1u, abort)) {
+                if (i > 0 && !local_wait(&bars->kb_done, (i - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
@@ -930,7 +955,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             for (unsigned int j = 0; j < tiles; ++j) {
                 const unsigned int slot = j & 1u;
                 const int token = (int)(t0 + j * kMlaN);
-                if (j >= 2u && !pair_wait(&bars->v_done[slot], ((j >> 1) - 1u) & 1u, abort)) {
+                if (j >= 2u && !local_wait(&bars->v_done[slot], ((j >> 1) - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
@@ -952,7 +977,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             const uint32_t peer_m = cluster_map(smem_u32(m_box), peer);
             const uint32_t peer_full = cluster_map(smem_u32(&bars->p_peer_full), peer);
             for (unsigned int i = 0; i < own_tiles; ++i) {
-                if (!pair_wait(&bars->p_written, i & 1u, abort) ||
+                if (!local_wait(&bars->p_written, i & 1u, abort) ||
                     (i > 0 && !pair_wait(&bars->p_peer_free, (i - 1u) & 1u, abort))) {
                     give_up();
                     break;
@@ -978,7 +1003,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
         const uint32_t elected = tc_elect_one() ? 1u : 0u;
         auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {    // every lane waits: the warp stays converged
-            return __all_sync(0xffffffffu, pair_wait(bar, parity, abort)) != 0;
+            return __all_sync(0xffffffffu, local_wait(bar, parity, abort)) != 0;
         };
         bool ok = true;
         if (warp == 9) {
@@ -1158,7 +1183,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             const bool differs = m_p != m_o && m_p != -INFINITY;
             if (__any_sync(0xffffffffu, differs)) {
                 if (j > 0) {
-                    if (!pair_wait(&bars->pv_done, (j - 1u) & 1u, abort)) return false;
+                    if (!local_wait(&bars->pv_done, (j - 1u) & 1u, abort)) return false;
                     tc_fence_after_sync();
                     rescale(differs && m_o != -INFINITY ? exp2_approx(m_o - m_p) : 1.0f);
                     tc_fence_before_sync();
@@ -1190,7 +1215,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             {
                 // ---- the weights of a tile this CTA scores; nothing here waits for the peer's softmax ----
                 MLA_TRACE_BEGIN(w0);
-                if (!pair_wait(&bars->s_full, i & 1u, abort)) {
+                if (!local_wait(&bars->s_full, i & 1u, abort)) {
                     ok = false;
                     break;
                 }
@@ -1250,8 +1275,8 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 MLA_TRACE_ADD(1, w1);
                 MLA_TRACE_BEGIN(w2);
                 // the previous own tile's weights have been consumed here and have left for the peer
-                if (i > 0 && !(pair_wait(&bars->pv_own_done, (i - 1u) & 1u, abort) &&
-                               pair_wait(&bars->p_own_sent, (i - 1u) & 1u, abort))) {
+                if (i > 0 && !(local_wait(&bars->pv_own_done, (i - 1u) & 1u, abort) &&
+                               local_wait(&bars->p_own_sent, (i - 1u) & 1u, abort))) {
                     ok = false;
                     break;
                 }
@@ -1292,7 +1317,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         }
 #endif
         MLA_MARK(4);
-        if (ok) ok = pair_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
+        if (ok) ok = local_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
         MLA_MARK(5);
         if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up();
         // this CTA's share of the denominators, and the maximum it is relative to, go to the peer
@@ -1336,7 +1361,7 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 make_float2(m_o == -INFINITY ? -INFINITY : m_o * 0.6931471805599453f, l);
             mbar_arrive(&bars->rows_staged);
             MLA_MARK(8);
-            fine = pair_wait(&bars->rows_staged, 0, abort);
+            fine = local_wait(&bars->rows_staged, 0, abort);
             MLA_MARK(9);
         }
         if (fine) {
@@ -1391,7 +1416,26 @@ mla_decode_pair_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
 // shared memory holds tile buffers only. Tile j is scored by CTA j % 4, which sends the weights (with the row
 // maxima they were scaled with) to the other three; every CTA runs P V of every tile on its own quarter, with V
 // (a tile's own quarter, 16 KB) from a ring of four slots. With one cluster per session nothing is split: no
-// partial rows and no combine launch. Waits, failure handling and the scale bookkeeping are the paired form's.
+// partial rows and no combine launch.
+// The weights travel through L2: the scorer's softmax threads write them (plain rows, coalesced) into one of two
+// slots of a scratch area in global memory and tell the peers; each peer's loader pulls them with one tiled TMA
+// load, which lays them out swizzled as the tensor pipe reads them. (Three bulk copies between shared memories
+// took 2650-3170 cycles per tile out of one SM, in series.) A CTA processes the tiles of a period (its own
+// included) one period late, at a fixed point of its program, so the transfer is hidden and results do not
+// depend on timing; its own weights are double-buffered for that. Every barrier that can run two phases ahead
+// of its waiter exists once per buffer.
+// Behind the partial rows of the four-CTA form: two scratch slots per (session, split, rank) for the weights of an own
+// tile ([128 heads][64 tokens] bf16) on their way to the peers, then as many slots of 128 maxima.
+__host__ __device__ inline unsigned long long mla_quad_rows_bytes(const yvx_mla_problem &p)
+{
+    const unsigned long long rows = (unsigned long long)p.sessions * kMlaHeads * 4ull * p.max_splits * (kMlaLatent / 4 + 2) * 4ull;
+    return (rows + 1023ull) & ~1023ull;
+}
+__host__ __device__ inline unsigned char *mla_quad_scratch(const yvx_mla_problem &p)
+{
+    return reinterpret_cast<unsigned char *>(p.partials) + mla_quad_rows_bytes(p);
+}
+
 constexpr int kQuadThreads = 320;    // warps 0-3 softmax, 4: K pieces, 5: score issuer, 6: V ring, 7: idle, 8: sender, 9: P V issuer
 constexpr int kQuadCols = kMlaLatent / 4;                               // 128 accumulator columns per CTA
 constexpr int kQuadQCols = kMlaWidth / 2;                               // 288 columns of query dims
@@ -1400,29 +1444,40 @@ constexpr int kQuadOffK = 0;                                            // a who
 constexpr int kQuadVSlotBytes = 2 * kMlaKvSubBytes;                     // a tile's own quarter as V: 16 KB
 constexpr int kQuadOffV = kMlaKvBytes;                                  // 73728, four slots
 constexpr int kQuadOffPOwn = kQuadOffV + 4 * kQuadVSlotBytes;           // 139264
-constexpr int kQuadOffPPeer = kQuadOffPOwn + kPairPBytes;               // 155648: one buffer per source
-constexpr int kQuadOffTail = kQuadOffPPeer + 3 * kPairPBytes;           // 204800
+constexpr int kQuadOffPPeer = kQuadOffPOwn + 2 * kPairPBytes;           // 172032: one buffer per source (own weights: two)
+constexpr int kQuadOffTail = kQuadOffPPeer + 3 * kPairPBytes;           // 221184
 constexpr int kQuadBoxBytes = 3 * kMlaHeads * 4;                        // three sources x 128 floats
-constexpr int kQuadSmemBytes = kQuadOffTail + 256 + 3 * kQuadBoxBytes + kMlaHeads * 4 + 1024;
+constexpr int kQuadSmemBytes = kQuadOffTail + 512 + 3 * kQuadBoxBytes + 2 * kMlaHeads * 4 + 1024;
+constexpr unsigned long long kQuadMessageBytes = kPairPBytes + kMlaHeads * 4;   // weights + the maxima they were scaled with
 
+#ifdef YVX_QUAD_TRACE
+__device__ unsigned long long yvx_quad_trace[16];
+#define QT_BEGIN(t) const long long t = clock64()
+#define QT_ADD(slot, t) do { if (qtraced) qt[slot] += (unsigned long long)(clock64() - t); } while (0)
+#else
+#define QT_BEGIN(t) do { } while (0)
+#define QT_ADD(slot, t) do { } while (0)
+#endif
 
 struct QuadBarriers {
     uint64_t q_tmem_full;
     uint64_t k_full[3], k_done[3];        // the three pieces of an own tile: loaded / read by their score instructions
     uint64_t v_full[4], v_done[4];        // the own quarter of any tile as V, four slots (tile % 4)
     uint64_t s_full, s_free;
-    uint64_t p_own_full, pv_own_done;
-    uint64_t p_peer_full[3], peer_ready[3];   // per source: its weights have arrived / its message is processed
-    uint64_t p_peer_free;                 // all three peers have consumed the weights this CTA sent them
-    uint64_t p_written, p_own_sent;
+    uint64_t p_own_full[2], pv_own_done[2];   // per buffer of own weights: released to the tensor pipe / consumed
+    uint64_t p_peer_full[3], peer_ready[3];   // per source: its weights have landed here / its message is processed
+    uint64_t p_avail[3][2];               // per source and scratch slot: its weights are in global memory
+    uint64_t peer_consumed[3];            // per source: the P V that read its weights has run
+    uint64_t g_free[2];                   // per scratch slot: all three peers have pulled this CTA's weights out of it
+    uint64_t p_written[2], p_own_sent[2]; // per buffer of own weights: written by the softmax / stored to the scratch slot
     uint64_t pv_done;
     uint64_t rows_staged;
     uint32_t tmem_base;
     int abort;
 };
-constexpr unsigned int kQuadBarrierCount = 30u;
+constexpr unsigned int kQuadBarrierCount = 44u;
 static_assert(offsetof(QuadBarriers, tmem_base) == kQuadBarrierCount * 8u, "barrier count out of step");
-static_assert(sizeof(QuadBarriers) <= 256, "barrier block outgrew its shared-memory slot");
+static_assert(sizeof(QuadBarriers) <= 512, "barrier block outgrew its shared-memory slot");
 
 __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(kQuadThreads, 1)
 mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps maps)
@@ -1431,10 +1486,10 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(quad_smem_raw) + 1023u) & ~uintptr_t(1023));
     QuadBarriers *bars = reinterpret_cast<QuadBarriers *>(smem + kQuadOffTail);
-    float *m_box = reinterpret_cast<float *>(smem + kQuadOffTail + 256);   // [3 sources][128]: a source's maxima with its tile
+    float *m_box = reinterpret_cast<float *>(smem + kQuadOffTail + 512);   // [3 sources][128]: a source's maxima with its tile
     float *l_box = m_box + 3 * kMlaHeads;                                  // [3][128]: the peers' denominators at the end
     float *mfin_box = l_box + 3 * kMlaHeads;                               // [3][128]: ... and the maxima they are relative to
-    float *m_out = mfin_box + 3 * kMlaHeads;                               // [128]: source of the copies to the peers
+    float *m_out = mfin_box + 3 * kMlaHeads;                               // [2 buffers][128]: the maxima of an own tile, source of its store
 
     const unsigned int warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const unsigned int rank = blockIdx.x, split = blockIdx.y, b = blockIdx.z;   // rank in the cluster
@@ -1443,6 +1498,11 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
     const unsigned int t1 = min(kv_tokens, t0 + p.chunk_tokens);
     const bool direct = p.max_splits == 1u;    // one item per session: the result itself leaves, no partial rows
     const unsigned long long part_stride = kQuadCols + 2;
+    // the scratch slots of this cluster's messages: slot index ((item * 4 + rank) * 2 + buffer), weights then maxima
+    const unsigned long long item_slot = ((unsigned long long)b * p.max_splits + split) * 8ull;
+    unsigned char *weights_scratch = mla_quad_scratch(p);
+    float *maxima_scratch = reinterpret_cast<float *>(weights_scratch +
+                                                      (unsigned long long)p.sessions * p.max_splits * 8ull * kPairPBytes);
     if (t0 >= t1) {
         // Nothing of this session falls into the split (true for all four CTAs): an empty partial; a session without
         // any token has no result (0 / 0, reported), as the fold of nothing gives.
@@ -1479,20 +1539,19 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         }
         mbar_init(&bars->s_full, 1);
         mbar_init(&bars->s_free, kMlaHeads);
-        mbar_init(&bars->p_own_full, 4);
-        mbar_init(&bars->pv_own_done, 1);
-        mbar_init(&bars->p_peer_free, 3);
-        mbar_init(&bars->p_written, 4);
-        mbar_init(&bars->p_own_sent, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->p_own_full[i], 4);
+            mbar_init(&bars->pv_own_done[i], 1);
+            mbar_init(&bars->g_free[i], 3);
+            mbar_init(&bars->p_written[i], 4);
+            mbar_init(&bars->p_own_sent[i], 1);
+            for (int q = 0; q < 3; ++q) mbar_init(&bars->p_avail[q][i], 1);
+        }
+        for (int q = 0; q < 3; ++q) mbar_init(&bars->peer_consumed[q], 1);
         mbar_init(&bars->pv_done, 1);
         mbar_init(&bars->rows_staged, kMlaHeads);
         bars->abort = 0;
         fence_barrier_init();
-        // the first message of every source that has a tile: its weights and its maxima, counted in bytes
-        for (unsigned int q = 0; q < 3u; ++q) {
-            const unsigned int source = (rank + 1u + q) & 3u;
-            if ((tiles + 3u - source) / 4u) mbar_expect_tx(&bars->p_peer_full[q], kPairPBytes + kMlaHeads * 4);
-        }
     }
     if (warp == 5) {
         tmem_alloc(&bars->tmem_base, kMlaTmemColumns);
@@ -1518,7 +1577,7 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 const int token = (int)(t0 + (4u * i + rank) * kMlaN);
                 bool fine = true;
                 for (int piece = 0; piece < 3 && fine; ++piece) {
-                    if (i > 0 && !pair_wait(&bars->k_done[piece], (i - 1u) & 1u, abort)) {
+                    if (i > 0 && !local_wait(&bars->k_done[piece], (i - 1u) & 1u, abort)) {
                         give_up();
                         fine = false;
                         break;
@@ -1540,7 +1599,7 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             for (unsigned int j = 0; j < tiles; ++j) {
                 const unsigned int slot = j & 3u;
                 const int token = (int)(t0 + j * kMlaN);
-                if (j >= 4u && !pair_wait(&bars->v_done[slot], ((j >> 2) - 1u) & 1u, abort)) {
+                if (j >= 4u && !local_wait(&bars->v_done[slot], ((j >> 2) - 1u) & 1u, abort)) {
                     give_up();
                     break;
                 }
@@ -1549,29 +1608,51 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 for (int u = 0; u < 2; ++u)
                     tma_load_3d(dst + u * kMlaKvSubBytes, &maps.latent, &bars->v_full[slot], 64 * (2 * (int)rank + u), token, (int)b);
             }
-        }
-    } else if (warp == 8) {
-        // ------------------------------ sender ------------------------------
-        if (lane == 0) {
-            for (unsigned int i = 0; i < own_tiles; ++i) {
-                if (!pair_wait(&bars->p_written, i & 1u, abort) ||
-                    (i > 0 && !pair_wait(&bars->p_peer_free, (i - 1u) & 1u, abort))) {
+        } else if (warp == 7 && lane == 0) {
+            // the peers' messages, pulled out of their scratch slots in tile order: once the source has said that the
+            // weights are in global memory and the P V that read its previous weights here has run
+            for (unsigned int j = 0; j < tiles; ++j) {
+                const unsigned int source = j & 3u, ii = j >> 2;
+                if (source == rank) continue;
+                const unsigned int q = (source - rank - 1u) & 3u;
+                if (!pair_wait(&bars->p_avail[q][ii & 1u], (ii >> 1) & 1u, abort) ||
+                    (ii > 0 && !local_wait(&bars->peer_consumed[q], (ii - 1u) & 1u, abort))) {
                     give_up();
                     break;
                 }
-                fence_proxy_async();
-                for (unsigned int d = 1; d < 4u; ++d) {
-                    const unsigned int destination = (rank + d) & 3u, q = (3u - d) & 3u;   // this CTA's slot over there
-                    const uint32_t full = cluster_map(smem_u32(&bars->p_peer_full[q]), destination);
-                    cluster_bulk_copy(cluster_map(smem_u32(smem + kQuadOffPPeer + q * kPairPBytes), destination),
-                                      smem + kQuadOffPOwn, kPairPBytes, full);
-                    cluster_bulk_copy(cluster_map(smem_u32(m_box + q * kMlaHeads), destination), m_out, kMlaHeads * 4, full);
+                const unsigned long long slot = item_slot + source * 2ull + (ii & 1u);
+                mbar_expect_tx(&bars->p_peer_full[q], (uint32_t)kQuadMessageBytes);
+                tma_load_3d(smem + kQuadOffPPeer + q * kPairPBytes, &maps.weights, &bars->p_peer_full[q], 0, 0, (int)slot);
+                bulk_load(m_box + q * kMlaHeads, maxima_scratch + slot * kMlaHeads, kMlaHeads * 4, &bars->p_peer_full[q]);
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------ sender ------------------------------
+        // An own tile's weights (and the maxima they were scaled with) leave for this CTA's scratch slot as bulk
+        // stores (the tiled one undoes the swizzle), and when those are complete the peers are told.
+        if (lane == 0) {
+            for (unsigned int i = 0; i < own_tiles; ++i) {
+                const unsigned int buffer = i & 1u;
+                if (!local_wait(&bars->p_written[buffer], (i >> 1) & 1u, abort) ||
+                    (i >= 2u && !pair_wait(&bars->g_free[buffer], ((i >> 1) - 1u) & 1u, abort))) {
+                    give_up();
+                    break;
                 }
+                const unsigned long long slot = item_slot + rank * 2ull + buffer;
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                             ::"l"(&maps.weights), "r"(0), "r"(0), "r"((int)slot),
+                               "r"(smem_u32(smem + kQuadOffPOwn + buffer * kPairPBytes))
+                             : "memory");
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(maxima_scratch + slot * kMlaHeads), "r"(smem_u32(m_out + buffer * kMlaHeads)), "r"(kMlaHeads * 4)
+                             : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                mbar_arrive(&bars->p_own_sent);
-                // the last credits are nobody's to wait for otherwise: nothing may be pending when the kernel ends
-                if (i + 1u == own_tiles && !pair_wait(&bars->p_peer_free, i & 1u, abort)) give_up();
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                mbar_arrive(&bars->p_own_sent[buffer]);
+                // one fence orders the completed stores before the three arrivals (a releasing arrival each costs more)
+                __threadfence();
+                for (unsigned int d = 1; d < 4u; ++d)
+                    cluster_arrive_remote_relaxed(cluster_map(smem_u32(&bars->p_avail[(3u - d) & 3u][buffer]), (rank + d) & 3u));
             }
         }
     } else if (warp == 5 || warp == 9) {
@@ -1581,7 +1662,7 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         constexpr uint32_t desc_hi = smem_desc_sw128_hi(1024);
         const uint32_t elected = tc_elect_one() ? 1u : 0u;
         auto wait_all = [&](uint64_t *bar, uint32_t parity) -> bool {    // every lane waits: the warp stays converged
-            return __all_sync(0xffffffffu, pair_wait(bar, parity, abort)) != 0;
+            return __all_sync(0xffffffffu, local_wait(bar, parity, abort)) != 0;
         };
         bool ok = true;
         if (warp == 9) {
@@ -1589,29 +1670,19 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 const unsigned int i = j >> 2, source = j & 3u, slot = j & 3u;
                 const bool own = source == rank;
                 const unsigned int q = (source - rank - 1u) & 3u;
-                ok = wait_all(own ? &bars->p_own_full : &bars->peer_ready[q], i & 1u) && wait_all(&bars->v_full[slot], i & 1u);
+                ok = (own ? wait_all(&bars->p_own_full[i & 1u], (i >> 1) & 1u) : wait_all(&bars->peer_ready[q], i & 1u)) &&
+                     wait_all(&bars->v_full[slot], i & 1u);
                 if (!ok) break;
                 tc_fence_after_sync();
-                const uint32_t p_lo =
-                    smem_desc_sw128_lo(smem_u32(smem + (own ? kQuadOffPOwn : kQuadOffPPeer + (int)q * kPairPBytes)), 16);
+                const uint32_t p_lo = smem_desc_sw128_lo(
+                    smem_u32(smem + (own ? kQuadOffPOwn + (int)(i & 1u) * kPairPBytes : kQuadOffPPeer + (int)q * kPairPBytes)), 16);
                 const uint32_t v_lo = smem_desc_sw128_lo(smem_u32(smem + kQuadOffV + slot * kQuadVSlotBytes), kMlaKvSubBytes);
 #pragma unroll
                 for (int kk = 0; kk < kMlaN / 16; ++kk)
                     tc_mma_ss_pred(elected, tmem_o, p_lo + 2u * kk, desc_hi, v_lo + ((kk * 2048) >> 4), desc_hi, idesc_pv,
                                    (j || kk) ? 1u : 0u);
                 tc_commit_pred(elected, &bars->v_done[slot]);
-                if (own) {
-                    tc_commit_pred(elected, &bars->pv_own_done);
-                } else {
-                    // ... and tells the source at once that the weights it sent are consumed here
-                    const uint32_t credit = cluster_map(smem_u32(&bars->p_peer_free), source);
-                    asm volatile(
-                        "{\n\t.reg .pred pe;\n\t"
-                        "setp.ne.b32 pe, %0, 0;\n\t"
-                        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}"
-                        ::"r"(elected), "r"(credit)
-                        : "memory");
-                }
+                tc_commit_pred(elected, own ? &bars->pv_own_done[i & 1u] : &bars->peer_consumed[q]);
                 tc_commit_pred(elected, &bars->pv_done);
             }
             // nothing may be pending on a barrier when the kernel ends: the last phases nobody else waits for
@@ -1619,7 +1690,7 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 const unsigned int uses = (tiles + 3u - slot) / 4u;
                 if (uses) ok = wait_all(&bars->v_done[slot], (uses - 1u) & 1u);
             }
-            if (ok && own_tiles) ok = wait_all(&bars->pv_own_done, (own_tiles - 1u) & 1u);
+            (void)own_tiles;
         } else {
             const uint32_t k_lo = smem_desc_sw128_lo(smem_u32(smem + kQuadOffK), 16);
             ok = wait_all(&bars->q_tmem_full, 0);
@@ -1689,6 +1760,11 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             tc_fence_before_sync();
             mbar_arrive(&bars->q_tmem_full);
         }
+#ifdef YVX_QUAD_TRACE
+        const bool qtraced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+        unsigned long long qt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long qt_start = clock64();
+#endif
         const float sscale = p.scale * 1.4426950408889634f;
         // m_used: the maximum this CTA's weights are scaled with (and its l); m_o: the scale its accumulator carries
         float m_used = -INFINITY, l = 0.0f, m_o = -INFINITY, m_heard = -INFINITY;
@@ -1712,9 +1788,14 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             const bool differs = m_p != m_o && m_p != -INFINITY;
             if (__any_sync(0xffffffffu, differs)) {
                 if (j > 0) {
-                    if (!pair_wait(&bars->pv_done, (j - 1u) & 1u, abort)) return false;
+                    QT_BEGIN(qr);
+                    if (!local_wait(&bars->pv_done, (j - 1u) & 1u, abort)) return false;
                     tc_fence_after_sync();
+#ifdef YVX_QUAD_TRACE
+                    if (qtraced) qt[6] += 1;
+#endif
                     rescale(differs && m_o != -INFINITY ? exp2_approx(m_o - m_p) : 1.0f);
+                    QT_ADD(7, qr);
                     tc_fence_before_sync();
                 }
                 if (differs) m_o = m_p;
@@ -1726,114 +1807,126 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
         // A peer's message for its tile j: its weights are in place, its maxima in its box.
         auto receive = [&](unsigned int j) -> bool {
             const unsigned int source = j & 3u, q = (source - rank - 1u) & 3u, ip = j >> 2;
-            if (!pair_wait(&bars->p_peer_full[q], ip & 1u, abort)) return false;
-            if (warp == 0 && lane == 0 && ip + 1u < (tiles + 3u - source) / 4u)   // the source's next message may be counted from now on
-                mbar_expect_tx(&bars->p_peer_full[q], kPairPBytes + kMlaHeads * 4);
+            QT_BEGIN(qw);
+            if (!local_wait(&bars->p_peer_full[q], ip & 1u, abort)) return false;   // completed by this CTA's own loads
+            QT_ADD(5, qw);
+            if (warp == q && lane == 0)   // the message has been pulled: the source may write that scratch slot again
+                cluster_arrive_remote_relaxed(cluster_map(smem_u32(&bars->g_free[ip & 1u]), source));
             const float m_in = m_box[q * kMlaHeads + head];
             m_heard = fmaxf(m_heard, m_in);   // adopted at a fixed point of the program (results must not depend on timing)
             return release(j, m_in, &bars->peer_ready[q]);
         };
-        unsigned int next_rx = rank == 0u ? 1u : 0u;     // the next tile of a peer to process, in tile order
-        auto advance_rx = [&]() {
-            ++next_rx;
-            if ((next_rx & 3u) == rank) ++next_rx;
+        // Tiles are processed (a peer's message received, an own tile released to the tensor pipe) in tile order and
+        // one period late: after the weights of own tile 4 i + rank are out, every tile below 4 i is processed,
+        // blocking; those messages were written a whole period ago. Nothing here depends on when a message arrives.
+        unsigned int next_tile = 0;
+        float m_own_saved[2] = {-INFINITY, -INFINITY};   // the maxima the weights of the own tiles not yet released were scaled with
+        auto process_until = [&](unsigned int limit) -> bool {
+            for (; next_tile < limit; ++next_tile) {
+                const bool fine = (next_tile & 3u) == rank
+                                      ? release(next_tile, m_own_saved[(next_tile >> 2) & 1u], &bars->p_own_full[(next_tile >> 2) & 1u])
+                                      : receive(next_tile);
+                if (!fine) return false;
+            }
+            return true;
         };
         for (unsigned int i = 0; i < own_tiles && ok; ++i) {
             const unsigned int j = 4u * i + rank;
+            QT_BEGIN(q0);
+            if (!local_wait(&bars->s_full, i & 1u, abort)) {
+                ok = false;
+                break;
+            }
+            QT_ADD(0, q0);
+            tc_fence_after_sync();
+            uint32_t s[2][32];
+            tmem_ld32(tmem_s + lane_base, s[0]);
+            tmem_ld32(tmem_s + lane_base + 32u, s[1]);
+            tmem_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(&bars->s_free);
+            const unsigned int k0 = t0 + j * kMlaN;
+            if (k0 + kMlaN > t1) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (k0 + 32 * h + c >= t1) s[h][c] = 0xff800000u;  // -inf
+            }
+            QT_BEGIN(q2);
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[h][c]), __uint_as_float(s[h][c + 1]));
+            const float m_tile = max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * sscale;
+            if (m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY) {
+                const float m_new = fmaxf(m_used, m_tile);
+                l *= m_new == -INFINITY || m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
+                m_used = m_new;
+            }
+            const float offset = m_used == -INFINITY ? 0.0f : -m_used;
+            uint32_t packed[32];
+            float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = exp2_approx(fmaf(__uint_as_float(s[h][c]), sscale, offset));
+                    const float p1 = exp2_approx(fmaf(__uint_as_float(s[h][c + 1]), sscale, offset));
+                    sum0 += p0;
+                    sum1 += p1;
+                    packed[16 * h + (c >> 1)] = pack_bf16(p0, p1);
+                }
+            l += sum0 + sum1;
+            QT_ADD(2, q2);
+            QT_BEGIN(q3);
+            // this buffer's last weights (own tile i - 2) have been consumed here and stored to the scratch slot
+            if (i >= 2u && !(local_wait(&bars->pv_own_done[i & 1u], ((i >> 1) - 1u) & 1u, abort) &&
+                             local_wait(&bars->p_own_sent[i & 1u], ((i >> 1) - 1u) & 1u, abort))) {
+                ok = false;
+                break;
+            }
+            QT_ADD(3, q3);
+            QT_BEGIN(q4);
             {
-                if (!pair_wait(&bars->s_full, i & 1u, abort)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                uint32_t s[2][32];
-                tmem_ld32(tmem_s + lane_base, s[0]);
-                tmem_ld32(tmem_s + lane_base + 32u, s[1]);
-                tmem_wait_ld();
-                tc_fence_before_sync();
-                mbar_arrive(&bars->s_free);
-                const unsigned int k0 = t0 + j * kMlaN;
-                if (k0 + kMlaN > t1) {
+                // row `head`: its eight 16-byte chunks under the 128-byte swizzle
+                unsigned char *mine = smem + kQuadOffPOwn + (i & 1u) * kPairPBytes + head * 128u;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (k0 + 32 * h + c >= t1) s[h][c] = 0xff800000u;  // -inf
-                }
-                // Messages for the tiles in front of this one that have arrived already are processed now (their
-                // P V can run, and their sources get their buffers back, while this tile's exponentials are
-                // computed); the others after this tile's weights are out.
-                while (ok && next_rx < j) {
-                    const unsigned int source = next_rx & 3u, q = (source - rank - 1u) & 3u;
-                    if (!__shfl_sync(0xffffffffu, (int)mbar_test(&bars->p_peer_full[q], (next_rx >> 2) & 1u), 0)) break;
-                    ok = receive(next_rx);
-                    advance_rx();
-                }
-                if (!ok) break;
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int c = 0; c < 32; c += 2)
-                        mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(s[h][c]), __uint_as_float(s[h][c + 1]));
-                const float m_tile = max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * sscale;
-                if (m_tile > m_used + kMlaRescaleThreshold || m_used == -INFINITY) {
-                    const float m_new = fmaxf(m_used, m_tile);
-                    l *= m_new == -INFINITY || m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_new);
-                    m_used = m_new;
-                }
-                const float offset = m_used == -INFINITY ? 0.0f : -m_used;
-                uint32_t packed[32];
-                float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        const float p0 = exp2_approx(fmaf(__uint_as_float(s[h][c]), sscale, offset));
-                        const float p1 = exp2_approx(fmaf(__uint_as_float(s[h][c + 1]), sscale, offset));
-                        sum0 += p0;
-                        sum1 += p1;
-                        packed[16 * h + (c >> 1)] = pack_bf16(p0, p1);
-                    }
-                l += sum0 + sum1;
-                // the previous own tile's weights have been consumed here and have left for the peers
-                if (i > 0 && !(pair_wait(&bars->pv_own_done, (i - 1u) & 1u, abort) &&
-                               pair_wait(&bars->p_own_sent, (i - 1u) & 1u, abort))) {
-                    ok = false;
-                    break;
-                }
-                {
-                    unsigned char *mine = smem + kQuadOffPOwn + head * 128u;   // row `head`: eight 16-byte chunks, 128-byte swizzle
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        *reinterpret_cast<uint4 *>(mine + ((unsigned)c ^ (head & 7u)) * 16u) =
-                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-                    m_out[head] = m_used;
-                }
-                fence_proxy_async();   // the tensor pipe and the bulk copies read these bytes through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->p_written);
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4 *>(mine + ((unsigned)c ^ (head & 7u)) * 16u) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                m_out[(i & 1u) * kMlaHeads + head] = m_used;
             }
-            // ---- P V in tile order: the peers' tiles in front of this one, then this one ----
-            const float m_own = m_used;
-            while (ok && next_rx < j) {
-                ok = receive(next_rx);
-                advance_rx();
-            }
-            if (ok) ok = release(j, m_own, &bars->p_own_full);
-            // Here, whenever the peers' messages were processed: adopt a larger maximum, so that the four CTAs'
-            // references stay together.
+            m_own_saved[i & 1u] = m_used;
+            fence_proxy_async();   // the tensor pipe and the bulk stores read these bytes through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_written[i & 1u]);
+            QT_ADD(4, q4);
+            // the tiles of the period before this one: their messages were written a whole period ago
+            QT_BEGIN(q1);
+            if (!(ok = process_until(4u * i))) break;
+            QT_ADD(1, q1);
+            // adopt a larger maximum heard from the peers (all of the periods before this one: a fixed set)
             if (m_heard > m_used) {
                 l *= m_used == -INFINITY ? 1.0f : exp2_approx(m_used - m_heard);
                 m_used = m_heard;
             }
         }
-        // the peers' tiles behind this CTA's last one
-        while (ok && next_rx < tiles) {
-            ok = receive(next_rx);
-            advance_rx();
+#ifdef YVX_QUAD_TRACE
+        if (qtraced) {
+            for (int k = 0; k < 5; ++k) yvx_quad_trace[k] = qt[k];
+            yvx_quad_trace[5] = (unsigned long long)(clock64() - qt_start);
+            yvx_quad_trace[6] = own_tiles;
+            yvx_quad_trace[7] = qt[5];
+            yvx_quad_trace[8] = qt[6];
+            yvx_quad_trace[9] = qt[7];
         }
-        if (ok) ok = pair_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
+#endif
+        // what is left: the last period's tiles, the peers' tiles behind this CTA's last one
+        if (ok) ok = process_until(tiles);
+        if (ok) ok = local_wait(&bars->pv_done, (tiles - 1u) & 1u, abort);
         if (!__all_sync(0xffffffffu, ok) && lane == 0) give_up();
         // this CTA's share of the denominators, and the maximum it is relative to, go to the peers
         for (unsigned int d = 1; d < 4u; ++d) {
@@ -1877,7 +1970,7 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
             *reinterpret_cast<float2 *>(mine + kQuadCols) =
                 make_float2(m_o == -INFINITY ? -INFINITY : m_o * 0.6931471805599453f, l);
             mbar_arrive(&bars->rows_staged);
-            fine = pair_wait(&bars->rows_staged, 0, abort);
+            fine = local_wait(&bars->rows_staged, 0, abort);
         }
         if (fine) {
             // four rows at a time, all of their loads from shared memory ahead of the stores
@@ -2042,6 +2135,12 @@ void yvx_cuda_mla_plan(yvx_mla_problem *p, int sm_count)
     p->chunk_tokens = ((p->kv_tokens_uniform + 63u) / 64u) * 64u;   // not used by the balanced plan; kept a tile multiple
 }
 
+#ifdef YVX_QUAD_TRACE
+int yvx_cuda_quad_trace_read(unsigned long long out[16])
+{
+    return cudaMemcpyFromSymbol(out, yvx::yvx_quad_trace, 16 * sizeof(unsigned long long)) == cudaSuccess ? 0 : 1;
+}
+#endif
 #ifdef YVX_MLA_TRACE
 int yvx_cuda_mla_trace_read(unsigned long long out[16])
 {
@@ -2065,8 +2164,8 @@ unsigned long long yvx_cuda_mla_absorbed_bytes(const yvx_mla_problem *p)
 unsigned long long yvx_cuda_mla_partials_bytes(const yvx_mla_problem *p)
 {
     if (!p) return 0ull;
-    if (p->cluster_ctas == 4u)   // (o[latent_dim / 4], m, l) per session, head, quarter and split
-        return (unsigned long long)p->sessions * p->heads * 4ull * p->max_splits * (p->latent_dim / 4ull + 2ull) * sizeof(float);
+    if (p->cluster_ctas == 4u)   // (o[latent_dim / 4], m, l) per session, head, quarter and split, then the messages' scratch slots
+        return yvx::mla_quad_rows_bytes(*p) + (unsigned long long)p->sessions * p->max_splits * 8ull * yvx::kQuadMessageBytes;
     return (unsigned long long)p->sessions * p->heads * 2ull * p->max_splits * (p->latent_dim / 2ull + 2ull) * sizeof(float);
 }
 
@@ -2119,7 +2218,9 @@ int yvx_cuda_mla_decode(const yvx_mla_problem *p, void *stream, void *events[4],
                                                    kQuadSmemBytes) == cudaSuccess;
             if (!quad_configured) cudaGetLastError();
         }
-        if (!quad_configured || p->balanced_pairs) {
+        if (!quad_configured || p->balanced_pairs ||
+            !mla_encode(&maps.weights, mla_quad_scratch(*p), 64, kMlaHeads, (unsigned long long)p->sessions * p->max_splits * 8ull,
+                        (unsigned long long)kMlaHeads * 64ull, kMlaHeads)) {
             yvx_cuda_set_error_text("the four-CTA form of the latent decode kernel is not available for this plan");
             return YVEX_ERR_UNSUPPORTED;
         }
