@@ -1649,8 +1649,9 @@ mla_decode_quad_kernel(const yvx_mla_problem p, const __grid_constant__ MlaMaps 
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
                 mbar_arrive(&bars->p_own_sent[buffer]);
-                // one fence orders the completed stores before the three arrivals (a releasing arrival each costs more)
-                __threadfence();
+                // one fence (the peers are in this cluster) orders the completed stores before the three arrivals: a
+                // releasing arrival each costs more, and so does a device-wide fence
+                asm volatile("fence.acq_rel.cluster;" ::: "memory");
                 for (unsigned int d = 1; d < 4u; ++d)
                     cluster_arrive_remote_relaxed(cluster_map(smem_u32(&bars->p_avail[(3u - d) & 3u][buffer]), (rank + d) & 3u));
             }
